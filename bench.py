@@ -1,0 +1,233 @@
+#!/usr/bin/env python
+"""Headline benchmark: small-batch SMA training throughput (images/s) of a CIFAR ResNet-32 / ImageNet ResNet-50.
+
+    python bench.py --gpus N --steps K --warmup W [--model resnet32|resnet50] [--replicas k] [--impl reference]
+
+One STEP = one synchronisation clock: every one of the k replicas of every GPU runs one task (forward, backward,
+local momentum-SGD update on a batch of 64 / 32 images) and then the fused SMA synchronisation runs across all
+replicas and GPUs.  Work per GPU is fixed (weak scaling); the reported value is the whole-job images/s.
+
+Two measurements, each K steps after W warm-up steps, bracketed by a barrier + device synchronise:
+  value     device time (CUDA events) of the step loop with the batches already staged on the device;
+  e2e.value the same loop through the public API (ExecutionContext.train), which copies every batch from pinned host
+            memory to the device and reads every task's loss/accuracy back on the host.
+Data is synthetic (seeded N(0,1) images, uniform labels); weights are freshly initialised.
+"""
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+CONFIGS = {
+    "resnet32": dict(build="resnet32", batch=64, shape=[3, 32, 32], classes=10, replicas=4),
+    "resnet50": dict(build="resnet50", batch=32, shape=[3, 224, 224], classes=1000, replicas=2),
+    "vgg16": dict(build="vgg16", batch=128, shape=[3, 32, 32], classes=10, replicas=1),
+    "lenet": dict(build="lenet-caffe", batch=16, shape=[1, 28, 28], classes=10, replicas=2),
+}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock, max clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index, period=0.1):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.stop_flag = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def reference_arm(args):
+    # The reference is a Java/Maven + CUDA 8 / cuDNN 6 project: `pip install /root/reference` finds neither setup.py
+    # nor pyproject.toml, there is no JVM on the image and its native code uses cuDNN APIs removed in cuDNN 8.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "reference is a Java/Maven project (no setup.py/pyproject.toml; pip install fails), no JVM on the "
+                      "image, native code needs cuDNN<=7 APIs; cannot be installed or run offline"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="resnet32", choices=sorted(CONFIGS))
+    ap.add_argument("--replicas", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--no-tc", action="store_true", help="CUDA-core convolution kernels only")
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--sync", default="fused", choices=["fused", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    from crossbow_b200 import Dataflow, ModelConf, Phase, SystemConf, UpdateModel
+    from crossbow_b200.context import ExecutionContext
+    from crossbow_b200.data import SyntheticDataset
+    from crossbow_b200.models import build
+    from crossbow_b200.parallel.peer import init_process_group
+
+    cfg = CONFIGS[args.model]
+    k = args.replicas or cfg["replicas"]
+    batch = args.batch or cfg["batch"]
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+    torch.cuda.set_device(local)
+    init_process_group("nccl")
+
+    sysc, mc = SystemConf.reset(), ModelConf.reset()
+    sysc.setGPU(True).setCPU(False).setNumberOfGpuModels(k).setDisplayInterval(0)
+    sysc.use_cuda_graphs = not args.no_graphs
+    sysc.use_tensor_cores = not args.no_tc
+    sysc.fused_sync = args.sync == "fused"
+    solver = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.1).setMomentum(0.9) \
+        .setWeightDecay(1e-4).setAlpha(0.1)
+    mc.setBatchSize(batch).setWpc(k).setUpdateModel(UpdateModel.SMA)
+    ring = max(2 * k, 8)
+    ds = SyntheticDataset(cfg["shape"], cfg["classes"], batch, batches=ring * world, seed=1234)
+    mc.setDataset(Phase.TRAIN, ds)
+    spec = build(cfg["build"], solver_conf=solver)
+    ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), None], quiet=True)
+    ctx.init()
+    eng = ctx.engine
+    lib = eng.lib
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------- device-only loop: batches staged on the device once, no host copies in the timed region --------
+    from crossbow_b200.ops import lib as L
+    x0, y0 = ds.batch(rank)
+    for l in eng.learners:
+        ex, lab = l.staging(Phase.TRAIN)
+        ex.copy_(x0.reshape(-1), non_blocking=True)
+        lab.copy_(y0, non_blocking=True)
+    torch.cuda.synchronize()
+    task_counter = [0]
+
+    def device_step():
+        for l in eng.learners:
+            p = eng.params(task_counter[0], True)
+            task_counter[0] += 1
+            L.check(lib.xb_learner_submit(l.handle, None, None, ctypes.byref(p), 0), "submit")
+        eng.synchronise()
+
+    for _ in range(args.warmup):
+        device_step()
+    barrier()
+    ev0, ev1 = lib.xb_event_create(1), lib.xb_event_create(1)
+    sampler = ClockSampler(local)
+    sampler.start()
+    lib.xb_event_record(ev0, eng.sync_stream)       # sync stream is idle: everything has been synchronised
+    for _ in range(args.steps):
+        device_step()
+    for l in eng.learners:                           # join: the end event follows every learner's last task
+        lib.xb_stream_wait_learner(eng.sync_stream, l.handle)
+    lib.xb_event_record(ev1, eng.sync_stream)
+    lib.xb_event_sync(ev1)
+    barrier()
+    dev_ms = max_over_ranks(lib.xb_event_elapsed_ms(ev0, ev1))
+    eng.finish()
+
+    # ---------------- end to end through the public API ----------------------------------------------------------------
+    ctx.train(args.warmup * k, "tasks")
+    barrier()
+    t0 = time.perf_counter()
+    ctx.train(args.steps * k, "tasks")              # copies every batch H2D, reads every loss back; ends synchronised
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+
+    images_per_step = batch * k * world
+    value = images_per_step * args.steps / (dev_ms / 1e3)
+    e2e = images_per_step * args.steps / e2e_s
+    launches_per_task = eng.gpu_launches_per_task()
+    arena_mb = sum(l.low_train.arena.total for l in eng.learners) / 1e6
+    if rank == 0:
+        out = {
+            "metric": f"{args.model} SMA training throughput", "value": round(value, 1), "unit": "images/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "tf32 tensor-core tiles, fp32 storage/accumulate" if eng.use_tc else "fp32", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": args.model, "global_batch": images_per_step, "batch_per_replica": batch, "replicas_per_gpu": k,
+                       "input": cfg["shape"], "parallelism": f"dp{world} x {k} replicas/GPU, SMA alpha 0.1, wpc = k*G",
+                       "optimizer": "momentum 0.9, wd 1e-4, lr 0.1", "sync": args.sync,
+                       "l2": f"no explicit flush: per-step working set {arena_mb:.0f} MB of activations/gradients exceeds the 126 MB L2"
+                             if arena_mb > 252 else f"working set {arena_mb:.0f} MB",
+                       "cuda_graphs": eng.use_graphs},
+            "e2e": {"value": round(e2e, 1), "unit": "images/s", "ms_per_step": round(e2e_s * 1e3 / args.steps, 4),
+                    "h2d_bytes_per_step": k * ds.batch_bytes(), "d2h_bytes_per_step": k * 8,
+                    "timing": "host wall clock around ExecutionContext.train, synchronised on both sides, max over ranks"},
+            "gpu_launches": args.steps * (k * launches_per_task + 1),
+            "launches_per_task": launches_per_task,
+            "clocks": sampler.summary(),
+            "final_loss": ctx.last_loss,
+        }
+        print(json.dumps(out))
+    ctx.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

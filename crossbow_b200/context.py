@@ -1,0 +1,249 @@
+"""``ExecutionContext``: the public entry point that trains and tests a model.
+
+API follows the reference (ExecutionContext.java:92-622): ``init()``, ``train(n, unit)``, ``trainAndTest(n, unit)``,
+``test()``, ``trainForDuration``, ``trainUntilCondition``, ``trainUntilConditionOrForDuration``, ``destroy()``.
+
+Scheduling model (what the reference spreads over the dispatcher, task queue, task/callback handler threads, the
+result collector and the model manager): tasks are numbered by a ``WorkClock``; each task goes to the next learner
+in round-robin order whose replica clock satisfies the staleness bound, the learner's previous result is collected
+first (that is the replica "lock"), the batch is copied from pinned host memory on the learner's stream and the
+task graph is launched.  Every ``wpc`` tasks the synchronisation step is enqueued on the synchronisation stream;
+ordering between tasks and synchronisation is expressed with CUDA events only, the host never blocks for it.
+"""
+from __future__ import annotations
+
+import time
+from typing import List, Optional
+
+import numpy as np
+
+from .conf import ModelConf, SystemConf
+from .graph import Dataflow
+from .model import Model, Shape
+from .types import DurationUnit, Phase, SynchronisationModel, TrainingUnit, UpdateModel
+from .utils.measure import MeasurementQueue, PerformanceMonitor
+from .workclock import WorkClock
+from .autotune import AutoTuner
+
+
+class ExecutionContext:
+    def __init__(self, dataflows: List[Optional[Dataflow]], system_conf: Optional[SystemConf] = None,
+                 model_conf: Optional[ModelConf] = None, input_shape=None, quiet=False):
+        self.dataflows = list(dataflows) + [None] * (2 - len(dataflows))
+        self.sys = system_conf or SystemConf.getInstance()
+        self.mc = model_conf or ModelConf.getInstance()
+        self.input_shape = list(input_shape) if input_shape is not None else None
+        self.model = Model()
+        self.engine = None
+        self.clock: Optional[WorkClock] = None
+        self.quiet = quiet
+        self.measurements = MeasurementQueue()
+        self.monitor: Optional[PerformanceMonitor] = None
+        self.autotuner: Optional[AutoTuner] = None
+        self.rank, self.world = 0, 1
+        self.tasks_done = 0
+        self.last_loss = float("nan")
+        self.last_accuracy = float("nan")
+        self.test_accuracy = float("nan")
+        self._next_learner = 0
+        self._checkpoint_version = 0
+
+    # ---- set-up ----
+    def init(self):
+        sys, mc = self.sys, self.mc
+        train_df, test_df = self.dataflows[0], self.dataflows[1]
+        if train_df is None:
+            raise ValueError("error: a training dataflow is required")
+        ds = mc.getDataset(Phase.TRAIN)
+        if self.input_shape is None:
+            if ds is None:
+                raise ValueError("error: neither an input shape nor a training data set is given")
+            self.input_shape = list(ds.example_shape)
+        while len(self.input_shape) < 3:
+            self.input_shape.append(1)
+        batch = mc.batch_size
+        ishape, lshape = Shape([batch] + self.input_shape), Shape([batch])
+        nid = train_df.getSubGraph().init(ishape, lshape, self.model, 0)
+        self.model.finalise()
+        if test_df is not None:
+            test_df.getSubGraph().init(ishape, lshape, self.model, nid)
+        solver = mc.getSolverConf()
+        if ds is not None:
+            solver.set_tasks_per_epoch(mc.numberOfTasksPerEpoch(Phase.TRAIN))
+        init = self.model.initial_values(sys.random_seed)
+        wpc = mc.wpc_in_tasks()
+        tg = train_df.getSubGraph()
+        sg = test_df.getSubGraph() if test_df is not None else None
+        if sys.gpu:
+            from .parallel.peer import dist_info
+            from .engine import GpuEngine
+            self.rank, self.world, local = dist_info()
+            self.engine = GpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,
+                                    replicas=sys.number_of_gpu_models, wpc=wpc, rank=self.rank, world=self.world,
+                                    device_index=local, use_graphs=sys.use_cuda_graphs, seed=sys.random_seed,
+                                    use_tc=sys.use_tensor_cores, fused_sync=sys.fused_sync,
+                                    sync_timeout_s=sys.sync_timeout)
+        else:
+            from .engine import CpuEngine
+            self.engine = CpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,
+                                    replicas=sys.number_of_cpu_models, wpc=wpc, devices=1, seed=sys.random_seed)
+        self.clock = WorkClock(wpc)
+        self.monitor = PerformanceMonitor(batch, ds.batch_bytes() if ds is not None else 0, sys.monitor_interval / 1000.0)
+        if sys.autotune_models:
+            self.autotuner = AutoTuner(sys.autotune_threshold, sys.autotune_interval)
+        if sys.model_directory:
+            from .checkpoint import load_checkpoint
+            load_checkpoint(self, sys.model_directory)
+        return self
+
+    # ---- helpers ----
+    def _learner_count(self):
+        e = self.engine
+        return e.k * (len(e.devs) if hasattr(e, "devs") else 1)
+
+    def _collect(self, learner: int, inflight: dict):
+        if learner in inflight:
+            task, phase = inflight.pop(learner)
+            loss, acc = self.engine.wait(learner)
+            if phase == Phase.TRAIN:
+                self.last_loss, self.last_accuracy = loss, acc
+                self.measurements.add(task, loss, acc)
+                self.monitor.task_done()
+                self.tasks_done += 1
+                di = self.sys.display_interval
+                if not self.quiet and di > 0 and (task + 1) % di == 0:
+                    print(f"[{task + 1:06d}] loss {loss:9.5f} accuracy {acc:7.4f} ({self.monitor.last_rate():9.1f} examples/s)", flush=True)
+            return loss, acc
+        return None
+
+    def _drain(self, inflight: dict):
+        for l in list(inflight):
+            self._collect(l, inflight)
+
+    def _train_tasks(self, ntasks: int):
+        e, mc, ds = self.engine, self.mc, self.mc.getDataset(Phase.TRAIN)
+        inflight = {}
+        solver = mc.getSolverConf()
+        done = 0
+        while done < ntasks:
+            task = self.clock.next_task()
+            nl = self._learner_count()
+            learner = self._next_learner % nl
+            self._next_learner += 1
+            self._collect(learner, inflight)                       # replica is free once its last result is in
+            x, y = ds.batch(task * self.world + self.rank)
+            e.submit(learner, x, y, task, Phase.TRAIN)
+            inflight[learner] = (task, Phase.TRAIN)
+            done += 1
+            if self.clock.is_barrier():
+                copy = solver.consume_copy_signal()
+                e.synchronise(copy=copy)
+                self.clock.tick()
+                if self.autotuner is not None:
+                    self._drain(inflight)
+                    delta = self.autotuner.decide(self.monitor.throughput_window())
+                    if delta > 0:
+                        e.add_learner()
+                        if not self.quiet:
+                            print(f"[autotune] +1 replica -> {e.k}", flush=True)
+                    elif delta < 0:
+                        e.remove_learner()
+                        if not self.quiet:
+                            print(f"[autotune] -1 replica -> {e.k}; tuning stops", flush=True)
+                ci = self.sys.checkpoint_interval
+                if ci > 0 and self.sys.checkpoint_directory and self.clock.clock % ci == 0:
+                    self._drain(inflight)
+                    self.checkpoint()
+        self._drain(inflight)
+        e.finish()
+        return done
+
+    def _tasks_of(self, n: int, unit) -> int:
+        unit = TrainingUnit.from_string(unit)
+        return n * self.mc.numberOfTasksPerEpoch(Phase.TRAIN) if unit == TrainingUnit.EPOCHS else n
+
+    # ---- public API ----
+    def train(self, n: int, unit=TrainingUnit.TASKS):
+        return self._train_tasks(self._tasks_of(n, unit))
+
+    def test(self) -> float:
+        """Run every test batch through the test graph against the central model; returns mean accuracy."""
+        e, ds = self.engine, self.mc.getDataset(Phase.CHECK)
+        if ds is None or self.dataflows[1] is None:
+            raise ValueError("error: no test dataflow / data set")
+        accs, inflight = [], {}
+        nl = self._learner_count()
+        for t in range(ds.number_of_batches()):
+            learner = t % nl
+            r = self._collect(learner, inflight)
+            if r is not None:
+                accs.append(r[1])
+            x, y = ds.batch(t)
+            e.submit(learner, x, y, t, Phase.CHECK)
+            inflight[learner] = (t, Phase.CHECK)
+        for l in list(inflight):
+            accs.append(self._collect(l, inflight)[1])
+        e.finish()
+        self.test_accuracy = float(np.mean(accs)) if accs else float("nan")
+        if not self.quiet:
+            print(f"[{self.clock.clock:06d}] Test accuracy is {self.test_accuracy:7.4f}", flush=True)
+        return self.test_accuracy
+
+    def trainAndTest(self, n: int, unit=TrainingUnit.TASKS):
+        """Interleave: every test interval (rounded up to a multiple of wpc, ExecutionContext.java:168-172) run the test set."""
+        total = self._tasks_of(n, unit)
+        interval = self._tasks_of(self.mc.test_interval, self.mc.test_interval_unit)
+        wpc = self.clock.wpc
+        interval = max(wpc, (interval + wpc - 1) // wpc * wpc)
+        done = 0
+        while done < total:
+            step = min(interval, total - done)
+            self._train_tasks(step)
+            done += step
+            self.test()
+        return done
+
+    def trainForDuration(self, duration: float, unit=DurationUnit.SECONDS):
+        deadline = time.time() + DurationUnit(unit).seconds(duration)
+        done = 0
+        chunk = max(self.clock.wpc, 4 * self._learner_count())
+        chunk = (chunk + self.clock.wpc - 1) // self.clock.wpc * self.clock.wpc
+        while time.time() < deadline:
+            done += self._train_tasks(chunk)
+        return done
+
+    def trainUntilCondition(self, target_loss: float, max_tasks: int = 1 << 30):
+        done = 0
+        chunk = (max(self.clock.wpc, self._learner_count()) + self.clock.wpc - 1) // self.clock.wpc * self.clock.wpc
+        while done < max_tasks:
+            done += self._train_tasks(chunk)
+            if self.last_loss <= target_loss:
+                break
+        return done
+
+    def trainUntilConditionOrForDuration(self, target_loss: float, duration: float, unit=DurationUnit.SECONDS):
+        deadline = time.time() + DurationUnit(unit).seconds(duration)
+        done = 0
+        chunk = (max(self.clock.wpc, self._learner_count()) + self.clock.wpc - 1) // self.clock.wpc * self.clock.wpc
+        while time.time() < deadline:
+            done += self._train_tasks(chunk)
+            if self.last_loss <= target_loss:
+                break
+        return done
+
+    def checkpoint(self, directory: Optional[str] = None):
+        from .checkpoint import save_checkpoint
+        return save_checkpoint(self, directory or self.sys.checkpoint_directory)
+
+    def destroy(self):
+        if self.engine is not None:
+            self.engine.destroy()
+            self.engine = None
+        if self.sys.queue_measurements and not self.quiet:
+            print(self.measurements.dump())
+
+    # snake_case aliases
+    train_and_test = trainAndTest
+    train_for_duration = trainForDuration
+    train_until_condition = trainUntilCondition
+

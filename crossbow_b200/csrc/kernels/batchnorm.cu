@@ -1,0 +1,281 @@
+// Spatial batch normalisation, channels-last, with ReLU and residual-add fused into the normalise pass.
+//
+// Training forward is two passes over x: (1) per-channel sum / sum of squares (often produced for free by the
+// convolution epilogue, see igemm kernels), (2) normalise + scale/shift (+ residual) (+ ReLU).  Pass 2 also stores
+// the batch mean / inverse std for the backward pass and blends the running statistics, which are ONE buffer per
+// (operator, device) shared by all replicas on that device, as in the reference
+// (clib-multigpu/kernels/cudnnbatchnorm.cu:99-151, cudnn/cudnnbatchnormparams.c:91-100).
+// Backward is (1) per-channel sums of dz and dz*xhat, (2) dx (+ residual gradient) and dgamma/dbeta
+// (cudnnbatchnormgradient.cu:77-93).  dz = dy masked by the fused ReLU.
+//
+// Thread mapping: a thread keeps the same 4 channels for its whole life ("column-persistent"), so the per-channel
+// constants are computed once and rows are streamed with 16-byte loads.
+#include "common.cuh"
+
+namespace {
+
+constexpr int NT = 256;
+
+template <int VEC> struct VecT;
+template <> struct VecT<4> { using T = float4; };
+template <> struct VecT<1> { using T = float; };
+
+template <int VEC> __device__ __forceinline__ void ld(const float* p, float (&v)[VEC]) {
+  if constexpr (VEC == 4) { float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+  else v[0] = *p;
+}
+template <int VEC> __device__ __forceinline__ void st(float* p, const float (&v)[VEC]) {
+  if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else *p = v[0];
+}
+
+// Column-persistent iteration space: CV = C/VEC column groups; a block covers `rows_per_iter` rows per step.
+struct Tiling { int cv, rows_per_iter, col_passes; };
+__host__ __device__ inline Tiling make_tiling(int C, int vec) {
+  Tiling t; t.cv = C / vec;
+  if (t.cv >= NT) { t.rows_per_iter = 1; t.col_passes = (t.cv + NT - 1) / NT; }
+  else { t.rows_per_iter = NT / t.cv; t.col_passes = 1; }
+  return t;
+}
+
+// sums[0..C) += sum_x, sums[C..2C) += sum_x^2 ; optionally of a*(mask) for backward
+template <int VEC>
+__global__ void __launch_bounds__(NT) bn_stats_kernel(const float* __restrict__ x, float* __restrict__ sums, int M, int C, int rows_per_block) {
+  const Tiling t = make_tiling(C, VEC);
+  __shared__ float red[2][NT * VEC];
+  const int r_begin = blockIdx.x * rows_per_block, r_end = min(M, r_begin + rows_per_block);
+  for (int pass = 0; pass < t.col_passes; ++pass) {
+    int cg = (t.col_passes == 1) ? (threadIdx.x % t.cv) : (pass * NT + threadIdx.x);
+    int rsub = (t.col_passes == 1) ? (threadIdx.x / t.cv) : 0;
+    bool active = cg < t.cv && rsub < t.rows_per_iter;
+    float s[VEC], q[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { s[e] = 0.f; q[e] = 0.f; }
+    if (active)
+      for (int r = r_begin + rsub; r < r_end; r += t.rows_per_iter) {
+        float v[VEC]; ld<VEC>(x + (long long)r * C + cg * VEC, v);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { s[e] += v[e]; q[e] += v[e] * v[e]; }
+      }
+    // reduce over rsub within the block
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { red[0][threadIdx.x * VEC + e] = s[e]; red[1][threadIdx.x * VEC + e] = q[e]; }
+    __syncthreads();
+    if (active && rsub == 0) {
+      for (int j = 1; j < t.rows_per_iter; ++j) {
+        int o = (threadIdx.x + j * t.cv) * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { s[e] += red[0][o + e]; q[e] += red[1][o + e]; }
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) { atomicAdd(&sums[cg * VEC + e], s[e]); atomicAdd(&sums[C + cg * VEC + e], q[e]); }
+    }
+    __syncthreads();
+  }
+}
+
+struct BnArgs {
+  const float* x; const float* res; float* y;
+  const float* sums;              // training: sum, sumsq [2C]
+  const float* gamma; const float* beta;
+  float* run_mean; float* run_var;
+  float* save_mean; float* save_invstd;
+  const XbTaskParams* tp;
+  int M, C; float eps; int relu; int training; int cma; float fraction_factor;
+  int rows_per_block;
+};
+
+template <int VEC>
+__global__ void __launch_bounds__(NT) bn_fwd_kernel(BnArgs a) {
+  const Tiling t = make_tiling(a.C, VEC);
+  const int r_begin = blockIdx.x * a.rows_per_block, r_end = min(a.M, r_begin + a.rows_per_block);
+  const float invM = 1.f / (float)a.M;
+  for (int pass = 0; pass < t.col_passes; ++pass) {
+    int cg = (t.col_passes == 1) ? (threadIdx.x % t.cv) : (pass * NT + threadIdx.x);
+    int rsub = (t.col_passes == 1) ? (threadIdx.x / t.cv) : 0;
+    if (cg >= t.cv || rsub >= t.rows_per_iter) continue;
+    float sc[VEC], sh[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      int c = cg * VEC + e;
+      float mean, invstd;
+      if (a.training) {
+        mean = a.sums[c] * invM;
+        float var = fmaxf(a.sums[a.C + c] * invM - mean * mean, 0.f);
+        invstd = rsqrtf(var + a.eps);
+        if (blockIdx.x == 0 && rsub == 0) {
+          a.save_mean[c] = mean; a.save_invstd[c] = invstd;
+          float f = a.cma ? a.tp->bn_factor : a.fraction_factor;
+          float unb = var * ((float)a.M / (float)max(1, a.M - 1));
+          // shared by all replicas of the device: blend with atomics so concurrent learners do not tear values
+          atomicAdd(&a.run_mean[c], f * (mean - a.run_mean[c]));
+          atomicAdd(&a.run_var[c], f * (unb - a.run_var[c]));
+        }
+      } else {
+        mean = a.run_mean[c];
+        invstd = rsqrtf(a.run_var[c] + a.eps);
+      }
+      sc[e] = a.gamma[c] * invstd;
+      sh[e] = a.beta[c] - mean * sc[e];
+    }
+    for (int r = r_begin + rsub; r < r_end; r += t.rows_per_iter) {
+      long long off = (long long)r * a.C + cg * VEC;
+      float v[VEC]; ld<VEC>(a.x + off, v);
+      float rr[VEC];
+      if (a.res) ld<VEC>(a.res + off, rr);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float o = fmaf(v[e], sc[e], sh[e]);
+        if (a.res) o += rr[e];
+        if (a.relu) o = fmaxf(o, 0.f);
+        v[e] = o;
+      }
+      st<VEC>(a.y + off, v);
+    }
+  }
+}
+
+struct BnBwdArgs {
+  const float* dy; const float* x; const float* y;   // y = forward output (ReLU mask) or null
+  const float* save_mean; const float* save_invstd; const float* gamma;
+  float* dsums;                                      // [2C]: sum dz, sum dz*xhat
+  float* dx; float* dres; float* dgamma; float* dbeta;
+  int M, C; int relu; int accum_dx; int accum_dres; int rows_per_block;
+};
+
+template <int VEC>
+__global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
+  const Tiling t = make_tiling(a.C, VEC);
+  __shared__ float red[2][NT * VEC];
+  const int r_begin = blockIdx.x * a.rows_per_block, r_end = min(a.M, r_begin + a.rows_per_block);
+  for (int pass = 0; pass < t.col_passes; ++pass) {
+    int cg = (t.col_passes == 1) ? (threadIdx.x % t.cv) : (pass * NT + threadIdx.x);
+    int rsub = (t.col_passes == 1) ? (threadIdx.x / t.cv) : 0;
+    bool active = cg < t.cv && rsub < t.rows_per_iter;
+    float s1[VEC], s2[VEC], mean[VEC], istd[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { s1[e] = 0.f; s2[e] = 0.f; mean[e] = 0.f; istd[e] = 0.f; }
+    if (active) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) { mean[e] = a.save_mean[cg * VEC + e]; istd[e] = a.save_invstd[cg * VEC + e]; }
+      for (int r = r_begin + rsub; r < r_end; r += t.rows_per_iter) {
+        long long off = (long long)r * a.C + cg * VEC;
+        float g[VEC], xv[VEC], yv[VEC];
+        ld<VEC>(a.dy + off, g); ld<VEC>(a.x + off, xv);
+        if (a.relu) ld<VEC>(a.y + off, yv);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float dz = (a.relu && !(yv[e] > 0.f)) ? 0.f : g[e];
+          s1[e] += dz; s2[e] += dz * (xv[e] - mean[e]) * istd[e];
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { red[0][threadIdx.x * VEC + e] = s1[e]; red[1][threadIdx.x * VEC + e] = s2[e]; }
+    __syncthreads();
+    if (active && rsub == 0) {
+      for (int j = 1; j < t.rows_per_iter; ++j) {
+        int o = (threadIdx.x + j * t.cv) * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { s1[e] += red[0][o + e]; s2[e] += red[1][o + e]; }
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) { atomicAdd(&a.dsums[cg * VEC + e], s1[e]); atomicAdd(&a.dsums[a.C + cg * VEC + e], s2[e]); }
+    }
+    __syncthreads();
+  }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
+  const Tiling t = make_tiling(a.C, VEC);
+  const int r_begin = blockIdx.x * a.rows_per_block, r_end = min(a.M, r_begin + a.rows_per_block);
+  const float invM = 1.f / (float)a.M;
+  for (int pass = 0; pass < t.col_passes; ++pass) {
+    int cg = (t.col_passes == 1) ? (threadIdx.x % t.cv) : (pass * NT + threadIdx.x);
+    int rsub = (t.col_passes == 1) ? (threadIdx.x / t.cv) : 0;
+    if (cg >= t.cv || rsub >= t.rows_per_iter) continue;
+    float mean[VEC], istd[VEC], k0[VEC], k1[VEC], k2[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      int c = cg * VEC + e;
+      mean[e] = a.save_mean[c]; istd[e] = a.save_invstd[c];
+      float s1 = a.dsums[c], s2 = a.dsums[a.C + c];
+      float gi = a.gamma[c] * istd[e];
+      k0[e] = gi; k1[e] = gi * s1 * invM; k2[e] = gi * s2 * invM;
+      if (blockIdx.x == 0 && rsub == 0) { atomicAdd(&a.dgamma[c], s2); atomicAdd(&a.dbeta[c], s1); }
+    }
+    for (int r = r_begin + rsub; r < r_end; r += t.rows_per_iter) {
+      long long off = (long long)r * a.C + cg * VEC;
+      float g[VEC], xv[VEC], yv[VEC], o[VEC], old[VEC];
+      ld<VEC>(a.dy + off, g); ld<VEC>(a.x + off, xv);
+      if (a.relu) ld<VEC>(a.y + off, yv);
+      if (a.accum_dx) ld<VEC>(a.dx + off, old);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        float dz = (a.relu && !(yv[e] > 0.f)) ? 0.f : g[e];
+        g[e] = dz;
+        float xhat = (xv[e] - mean[e]) * istd[e];
+        o[e] = k0[e] * dz - k1[e] - k2[e] * xhat;
+        if (a.accum_dx) o[e] += old[e];
+      }
+      st<VEC>(a.dx + off, o);
+      if (a.dres) {
+        if (a.accum_dres) {
+          float rr[VEC]; ld<VEC>(a.dres + off, rr);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) g[e] += rr[e];
+        }
+        st<VEC>(a.dres + off, g);
+      }
+    }
+  }
+}
+
+inline int rows_per_block_for(int M, int C, int vec, int& blocks) {
+  Tiling t = make_tiling(C, vec);
+  // aim for ~4 waves of 148 SMs at most, at least 8 row-steps per block
+  int min_rows = t.rows_per_iter * 8;
+  int rpb = xb_ceil_div(M, 592);
+  if (rpb < min_rows) rpb = min_rows;
+  rpb = xb_ceil_div(rpb, t.rows_per_iter) * t.rows_per_iter;
+  blocks = xb_ceil_div(M, rpb);
+  return rpb;
+}
+
+inline bool can_vec4(int C, const void* a, const void* b, const void* c, const void* d) {
+  return (C % 4 == 0) && ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c) | ((uintptr_t)d)) % 16 == 0);
+}
+
+}  // namespace
+
+XB_API int xb_bn_stats(const float* x, float* sums, int M, int C, cudaStream_t st) {
+  bool v4 = can_vec4(C, x, nullptr, nullptr, nullptr);
+  int blocks; int rpb = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
+  if (v4) bn_stats_kernel<4><<<blocks, NT, 0, st>>>(x, sums, M, C, rpb);
+  else    bn_stats_kernel<1><<<blocks, NT, 0, st>>>(x, sums, M, C, rpb);
+  return (int)cudaGetLastError();
+}
+
+XB_API int xb_bn_forward(const float* x, const float* res, float* y, const float* sums, const float* gamma, const float* beta,
+                         float* run_mean, float* run_var, float* save_mean, float* save_invstd, const XbTaskParams* tp,
+                         int M, int C, float eps, int relu, int training, int cma, float fraction_factor, cudaStream_t st) {
+  BnArgs a{x, res, y, sums, gamma, beta, run_mean, run_var, save_mean, save_invstd, tp, M, C, eps, relu, training, cma, fraction_factor, 0};
+  bool v4 = can_vec4(C, x, res, y, nullptr);
+  int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
+  if (v4) bn_fwd_kernel<4><<<blocks, NT, 0, st>>>(a);
+  else    bn_fwd_kernel<1><<<blocks, NT, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// dsums must be zero on entry.  dgamma/dbeta are accumulated (+=).
+XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const float* save_mean, const float* save_invstd,
+                          const float* gamma, float* dsums, float* dx, float* dres, float* dgamma, float* dbeta,
+                          int M, int C, int relu, int accum_dx, int accum_dres, cudaStream_t st) {
+  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, dsums, dx, dres, dgamma, dbeta, M, C, relu, accum_dx, accum_dres, 0};
+  bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
+  int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
+  if (v4) { bn_bwd_reduce_kernel<4><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); }
+  else    { bn_bwd_reduce_kernel<1><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a); }
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,309 @@
+// Element-wise operators, channels-last: activations, weighted sums, dropout, channel concat / slice, pooling,
+// local response normalisation, input transform.  Each replaces a cuDNN / cuBLAS call of the reference:
+//   cudnnrelu.cu / cudnnrelugradient.cu, elementwiseop.cu / elementwiseopgradient.cu (saxpy per input),
+//   cudnndropout.cu / cudnndropoutgradient.cu, concat.cu / concatgradient.cu, cudnnpool.cu / cudnnpoolgradient.cu,
+//   datatransform.cu.  LRN has no GPU implementation in the reference (executioncontext.c:374,395).
+#include "common.cuh"
+#include <float.h>
+#include <string.h>
+
+namespace {
+constexpr int NT = 256;
+inline int grid_for(long long n, int per_thread = 1) {
+  long long b = (n + (long long)NT * per_thread - 1) / ((long long)NT * per_thread);
+  if (b > 148 * 32) b = 148 * 32;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+// mode: 0 sigmoid, 1 relu (with negative slope), 2 tanh, 3 clipped relu
+__global__ void act_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, long long n, int mode, float slope, float ceiling) {
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    float v = x[i], o;
+    if (mode == 1) o = v > 0.f ? v : v * slope;
+    else if (mode == 0) o = 1.f / (1.f + __expf(-v));
+    else if (mode == 2) o = tanhf(v);
+    else o = fminf(fmaxf(v, 0.f), ceiling);
+    y[i] = o;
+  }
+}
+__global__ void act_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ y,
+                               float* __restrict__ dx, long long n, int mode, float slope, float ceiling, int accum) {
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    float g = dy[i], o;
+    if (mode == 1) o = y[i] > 0.f ? g : g * slope;      // y>0 <=> x>0 for slope>=0
+    else if (mode == 0) { float s = y[i]; o = g * s * (1.f - s); }
+    else if (mode == 2) { float t = y[i]; o = g * (1.f - t * t); }
+    else { float v = x[i]; o = (v > 0.f && v < ceiling) ? g : 0.f; }
+    dx[i] = accum ? dx[i] + o : o;
+  }
+}
+
+// y = (accum ? y : 0) + sum_i coef[i]*x[i]
+struct SumArgs { const float* x[4]; float coef[4]; int n_in; };
+__global__ void weighted_sum_kernel(SumArgs a, float* __restrict__ y, long long n4, long long n, int accum) {
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n4; i += (long long)gridDim.x * NT) {
+    float4 o = accum ? reinterpret_cast<float4*>(y)[i] : make_float4(0, 0, 0, 0);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (k < a.n_in) {
+        float4 v = reinterpret_cast<const float4*>(a.x[k])[i];
+        o.x = fmaf(a.coef[k], v.x, o.x); o.y = fmaf(a.coef[k], v.y, o.y); o.z = fmaf(a.coef[k], v.z, o.z); o.w = fmaf(a.coef[k], v.w, o.w);
+      }
+    reinterpret_cast<float4*>(y)[i] = o;
+  }
+  // tail
+  for (long long t = n4 * 4 + blockIdx.x * (long long)NT + threadIdx.x; t < n; t += (long long)gridDim.x * NT) {
+    float o = accum ? y[t] : 0.f;
+    for (int k = 0; k < a.n_in; ++k) o = fmaf(a.coef[k], a.x[k][t], o);
+    y[t] = o;
+  }
+}
+
+// Inverted dropout. Element i uses lane i%4 of Philox(counter = i/4, task, stream); keep iff u >= ratio.
+__global__ void dropout_kernel(const float* __restrict__ x, float* __restrict__ y, long long n, float ratio, unsigned stream,
+                               const XbTaskParams* __restrict__ tp, int accum) {
+  const float scale = 1.f / (1.f - ratio);
+  const unsigned task = tp->task_id, k0 = tp->seed_lo, k1 = tp->seed_hi;
+  long long groups = (n + 3) / 4;
+  for (long long gidx = blockIdx.x * (long long)NT + threadIdx.x; gidx < groups; gidx += (long long)gridDim.x * NT) {
+    uint4 r = xb_philox4x32((uint32_t)gidx, task, stream, 0u, k0, k1);
+    uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      long long i = gidx * 4 + e;
+      if (i < n) {
+        float o = (xb_u24(rr[e]) >= ratio) ? x[i] * scale : 0.f;
+        y[i] = accum ? y[i] + o : o;
+      }
+    }
+  }
+}
+
+// copy a [M, Cs] matrix into / out of columns [coff, coff+Cs) of a [M, Ct] matrix
+__global__ void concat_copy_kernel(const float* __restrict__ src, float* __restrict__ dst, long long M, int Cs, int Ct, int coff, int to_wide, int accum) {
+  long long n = M * Cs;
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    long long m = i / Cs; int c = (int)(i % Cs);
+    long long wide = m * Ct + coff + c;
+    if (to_wide) dst[wide] = src[i];
+    else dst[i] = accum ? dst[i] + src[wide] : src[wide];
+  }
+}
+
+struct PoolGeom { int N, H, W, C, P, Q, kh, kw, sh, sw, ph, pw; };
+
+// max pooling forward: first maximum wins (NaN propagates as in cuDNN's PROPAGATE_NAN only if it is the first element)
+__global__ void maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, PoolGeom g) {
+  long long n = (long long)g.N * g.P * g.Q * g.C;
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    int c = (int)(i % g.C); long long t = i / g.C; int q = (int)(t % g.Q); t /= g.Q; int p = (int)(t % g.P); int b = (int)(t / g.P);
+    float best = -FLT_MAX;
+    for (int r = 0; r < g.kh; ++r) {
+      int iy = p * g.sh - g.ph + r; if (iy < 0 || iy >= g.H) continue;
+      for (int s = 0; s < g.kw; ++s) {
+        int ix = q * g.sw - g.pw + s; if (ix < 0 || ix >= g.W) continue;
+        float v = x[(((long long)b * g.H + iy) * g.W + ix) * g.C + c];
+        if (v > best) best = v;
+      }
+    }
+    y[i] = best;
+  }
+}
+// dx must be zeroed (or hold values to accumulate onto)
+__global__ void maxpool_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x, float* __restrict__ dx, PoolGeom g) {
+  long long n = (long long)g.N * g.P * g.Q * g.C;
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    int c = (int)(i % g.C); long long t = i / g.C; int q = (int)(t % g.Q); t /= g.Q; int p = (int)(t % g.P); int b = (int)(t / g.P);
+    float best = -FLT_MAX; long long arg = -1;
+    for (int r = 0; r < g.kh; ++r) {
+      int iy = p * g.sh - g.ph + r; if (iy < 0 || iy >= g.H) continue;
+      for (int s = 0; s < g.kw; ++s) {
+        int ix = q * g.sw - g.pw + s; if (ix < 0 || ix >= g.W) continue;
+        long long o = (((long long)b * g.H + iy) * g.W + ix) * g.C + c;
+        float v = x[o];
+        if (v > best) { best = v; arg = o; }
+      }
+    }
+    if (arg >= 0) atomicAdd(&dx[arg], dy[i]);
+  }
+}
+// average pooling, divisor = kh*kw always (padding counted)
+__global__ void avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, PoolGeom g) {
+  long long n = (long long)g.N * g.P * g.Q * g.C;
+  const float inv = 1.f / (float)(g.kh * g.kw);
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    int c = (int)(i % g.C); long long t = i / g.C; int q = (int)(t % g.Q); t /= g.Q; int p = (int)(t % g.P); int b = (int)(t / g.P);
+    float s = 0.f;
+    for (int r = 0; r < g.kh; ++r) {
+      int iy = p * g.sh - g.ph + r; if (iy < 0 || iy >= g.H) continue;
+      for (int ss = 0; ss < g.kw; ++ss) {
+        int ix = q * g.sw - g.pw + ss; if (ix < 0 || ix >= g.W) continue;
+        s += x[(((long long)b * g.H + iy) * g.W + ix) * g.C + c];
+      }
+    }
+    y[i] = s * inv;
+  }
+}
+// gather form: each input element sums the windows that cover it (no atomics)
+__global__ void avgpool_bwd_kernel(const float* __restrict__ dy, float* __restrict__ dx, PoolGeom g, int accum) {
+  long long n = (long long)g.N * g.H * g.W * g.C;
+  const float inv = 1.f / (float)(g.kh * g.kw);
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    int c = (int)(i % g.C); long long t = i / g.C; int ix = (int)(t % g.W); t /= g.W; int iy = (int)(t % g.H); int b = (int)(t / g.H);
+    float s = 0.f;
+    for (int r = 0; r < g.kh; ++r) {
+      int ty = iy + g.ph - r; if (ty < 0 || ty % g.sh) continue; int p = ty / g.sh; if (p >= g.P) continue;
+      for (int ss = 0; ss < g.kw; ++ss) {
+        int tx = ix + g.pw - ss; if (tx < 0 || tx % g.sw) continue; int q = tx / g.sw; if (q >= g.Q) continue;
+        s += dy[(((long long)b * g.P + p) * g.Q + q) * g.C + c];
+      }
+    }
+    dx[i] = accum ? dx[i] + s * inv : s * inv;
+  }
+}
+
+// across-channel LRN (Caffe): y = x * (k + alpha/size * sum_{window} x^2)^-beta
+__global__ void lrn_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ scale, long long M, int C, int size, float alpha, float beta, float k) {
+  long long n = M * C; int half = size / 2;
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    long long m = i / C; int c = (int)(i % C);
+    float s = 0.f;
+    for (int j = max(0, c - half); j <= min(C - 1, c + half); ++j) { float v = x[m * C + j]; s += v * v; }
+    float sc = k + alpha / size * s;
+    scale[i] = sc;
+    y[i] = x[i] * __powf(sc, -beta);
+  }
+}
+__global__ void lrn_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ scale,
+                               float* __restrict__ dx, long long M, int C, int size, float alpha, float beta, int accum) {
+  long long n = M * C; int half = size / 2;
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    long long m = i / C; int c = (int)(i % C);
+    float s = 0.f;
+    for (int j = max(0, c - half); j <= min(C - 1, c + half); ++j) s += dy[m * C + j] * y[m * C + j] / scale[m * C + j];
+    float o = dy[i] * __powf(scale[i], -beta) - 2.f * alpha * beta / size * x[i] * s;
+    dx[i] = accum ? dx[i] + o : o;
+  }
+}
+
+// Input transform: NCHW source -> channels-last destination with crop / mirror / mean / scale.
+// Per example three Philox words (counter = example): crop row, crop column, mirror bit.
+struct TransformArgs { int N, C, H, W, OH, OW; int mirror; int training; float scale; int mean_mode; /*0 none,1 per channel,2 per pixel (full image)*/ unsigned stream; };
+__global__ void transform_kernel(const float* __restrict__ src, float* __restrict__ dst, const float* __restrict__ mean, TransformArgs a,
+                                 const XbTaskParams* __restrict__ tp) {
+  long long n = (long long)a.N * a.OH * a.OW * a.C;
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    int c = (int)(i % a.C); long long t = i / a.C; int ox = (int)(t % a.OW); t /= a.OW; int oy = (int)(t % a.OH); int b = (int)(t / a.OH);
+    int ho = (a.H - a.OH) / 2, wo = (a.W - a.OW) / 2; bool flip = false;
+    if (a.training) {
+      // example b uses elements 3b, 3b+1, 3b+2 of the stream
+      uint32_t r[3];
+#pragma unroll
+      for (int e = 0; e < 3; ++e) {
+        uint32_t idx = 3u * b + e;
+        uint4 w = xb_philox4x32(idx >> 2, tp->task_id, a.stream, 0u, tp->seed_lo, tp->seed_hi);
+        uint32_t lanes[4] = {w.x, w.y, w.z, w.w};
+        r[e] = lanes[idx & 3u];
+      }
+      ho = (int)(r[0] % (uint32_t)(a.H - a.OH + 1));
+      wo = (int)(r[1] % (uint32_t)(a.W - a.OW + 1));
+      flip = a.mirror && (r[2] & 1u);
+    }
+    int sx = flip ? (a.OW - 1 - ox) : ox;
+    int iy = oy + ho, ix = sx + wo;
+    float v = src[(((long long)b * a.C + c) * a.H + iy) * a.W + ix];
+    if (a.mean_mode == 1) v -= mean[c];
+    else if (a.mean_mode == 2) v -= mean[((long long)c * a.H + iy) * a.W + ix];
+    dst[i] = v * a.scale;
+  }
+}
+// channels-last -> NCHW (used to hand activations back in the public layout)
+__global__ void nhwc_to_nchw_kernel(const float* __restrict__ src, float* __restrict__ dst, int N, int C, int H, int W) {
+  long long n = (long long)N * C * H * W;
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n; i += (long long)gridDim.x * NT) {
+    int x = (int)(i % W); long long t = i / W; int y = (int)(t % H); t /= H; int c = (int)(t % C); int b = (int)(t / C);
+    dst[i] = src[(((long long)b * H + y) * W + x) * C + c];
+  }
+}
+// column sums: out[c] += sum_m a[m][c]  (bias gradients)
+__global__ void colsum_kernel(const float* __restrict__ a, float* __restrict__ out, int M, int C, int rows_per_block) {
+  int r0 = blockIdx.x * rows_per_block, r1 = min(M, r0 + rows_per_block);
+  for (int c = threadIdx.x; c < C; c += NT) {
+    float s = 0.f;
+    for (int r = r0; r < r1; ++r) s += a[(long long)r * C + c];
+    atomicAdd(&out[c], s);
+  }
+}
+}  // namespace
+
+XB_API int xb_act_forward(const float* x, float* y, long long n, int mode, float slope, float ceiling, cudaStream_t st) {
+  act_fwd_kernel<<<grid_for(n, 4), NT, 0, st>>>(x, y, n, mode, slope, ceiling);
+  return (int)cudaGetLastError();
+}
+XB_API int xb_act_backward(const float* dy, const float* x, const float* y, float* dx, long long n, int mode, float slope, float ceiling,
+                           int accum, cudaStream_t st) {
+  act_bwd_kernel<<<grid_for(n, 4), NT, 0, st>>>(dy, x, y, dx, n, mode, slope, ceiling, accum);
+  return (int)cudaGetLastError();
+}
+XB_API int xb_weighted_sum(const float* const* xs, const float* coef, int n_in, float* y, long long n, int accum, cudaStream_t st) {
+  if (n_in < 1 || n_in > 4) return -XB_BAD_ARG;
+  SumArgs a; a.n_in = n_in;
+  bool aligned = ((uintptr_t)y % 16) == 0;
+  for (int i = 0; i < 4; ++i) { a.x[i] = i < n_in ? xs[i] : nullptr; a.coef[i] = i < n_in ? coef[i] : 0.f; if (i < n_in && ((uintptr_t)xs[i] % 16)) aligned = false; }
+  long long n4 = aligned ? n / 4 : 0;
+  long long work = n4 > (n - n4 * 4) ? n4 : (n - n4 * 4);
+  int blocks = grid_for(work);
+  weighted_sum_kernel<<<blocks, NT, 0, st>>>(a, y, n4, n, accum);
+  return (int)cudaGetLastError();
+}
+XB_API int xb_dropout(const float* x, float* y, long long n, float ratio, unsigned stream, const XbTaskParams* tp, int accum, cudaStream_t st) {
+  dropout_kernel<<<grid_for((n + 3) / 4), NT, 0, st>>>(x, y, n, ratio, stream, tp, accum);
+  return (int)cudaGetLastError();
+}
+XB_API int xb_concat_copy(const float* src, float* dst, long long M, int Cs, int Ct, int coff, int to_wide, int accum, cudaStream_t st) {
+  concat_copy_kernel<<<grid_for(M * Cs, 2), NT, 0, st>>>(src, dst, M, Cs, Ct, coff, to_wide, accum);
+  return (int)cudaGetLastError();
+}
+XB_API int xb_pool_forward(const float* x, float* y, const int* geom12, int average, cudaStream_t st) {
+  PoolGeom g; memcpy(&g, geom12, sizeof(g));
+  long long n = (long long)g.N * g.P * g.Q * g.C;
+  if (average) avgpool_fwd_kernel<<<grid_for(n), NT, 0, st>>>(x, y, g);
+  else maxpool_fwd_kernel<<<grid_for(n), NT, 0, st>>>(x, y, g);
+  return (int)cudaGetLastError();
+}
+// max: dx must be pre-zeroed unless accumulating (scatter with atomics); average: gather form
+XB_API int xb_pool_backward(const float* dy, const float* x, float* dx, const int* geom12, int average, int accum, cudaStream_t st) {
+  PoolGeom g; memcpy(&g, geom12, sizeof(g));
+  if (average) {
+    avgpool_bwd_kernel<<<grid_for((long long)g.N * g.H * g.W * g.C), NT, 0, st>>>(dy, dx, g, accum);
+  } else {
+    if (!accum) { cudaError_t e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.N * g.H * g.W * g.C, st); if (e != cudaSuccess) return (int)e; }
+    maxpool_bwd_kernel<<<grid_for((long long)g.N * g.P * g.Q * g.C), NT, 0, st>>>(dy, x, dx, g);
+  }
+  return (int)cudaGetLastError();
+}
+XB_API int xb_lrn_forward(const float* x, float* y, float* scale, long long M, int C, int size, float alpha, float beta, float k, cudaStream_t st) {
+  lrn_fwd_kernel<<<grid_for(M * C), NT, 0, st>>>(x, y, scale, M, C, size, alpha, beta, k);
+  return (int)cudaGetLastError();
+}
+XB_API int xb_lrn_backward(const float* dy, const float* x, const float* y, const float* scale, float* dx, long long M, int C, int size,
+                           float alpha, float beta, int accum, cudaStream_t st) {
+  lrn_bwd_kernel<<<grid_for(M * C), NT, 0, st>>>(dy, x, y, scale, dx, M, C, size, alpha, beta, accum);
+  return (int)cudaGetLastError();
+}
+XB_API int xb_transform(const float* src, float* dst, const float* mean, int N, int C, int H, int W, int OH, int OW, int mirror, int training,
+                        float scale, int mean_mode, unsigned stream, const XbTaskParams* tp, cudaStream_t st) {
+  TransformArgs a{N, C, H, W, OH, OW, mirror, training, scale, mean_mode, stream};
+  transform_kernel<<<grid_for((long long)N * OH * OW * C), NT, 0, st>>>(src, dst, mean, a, tp);
+  return (int)cudaGetLastError();
+}
+XB_API int xb_nhwc_to_nchw(const float* src, float* dst, int N, int C, int H, int W, cudaStream_t st) {
+  nhwc_to_nchw_kernel<<<grid_for((long long)N * C * H * W), NT, 0, st>>>(src, dst, N, C, H, W);
+  return (int)cudaGetLastError();
+}
+XB_API int xb_colsum(const float* a, float* out, int M, int C, cudaStream_t st) {
+  int rpb = xb_ceil_div(M, 148); if (rpb < 32) rpb = 32;
+  colsum_kernel<<<xb_ceil_div(M, rpb), NT, 0, st>>>(a, out, M, C, rpb);
+  return (int)cudaGetLastError();
+}

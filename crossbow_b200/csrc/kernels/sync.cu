@@ -1,0 +1,332 @@
+// Fused model synchronisation: ONE kernel per GPU per clock.
+//
+// What the reference does with ~4k+6 cuBLAS launches, two cudaDeviceSynchronize and an ncclAllReduce per clock
+// (clib-multigpu/synch/sma.c:13-231, synch/common.c:3-57, synch/synchronoussgd.c:13-110) happens here in a single
+// persistent kernel per GPU:
+//
+//   phase 1 (local)   per 16 KB chunk: reduce the k replicas of this GPU against the central average model z,
+//                     correct every replica in place, and PUSH the partial sum over NVLink into the inbox of the
+//                     GPU(s) that need it (all peers: one-shot; the chunk's owner: two-shot), then raise a flag there.
+//   phase 2 (owner)   two-shot only: the owner of a chunk waits for all partials, adds them in rank order and pushes
+//                     the total into every GPU's result buffer, then raises the second flag.
+//   phase 3 (update)  wait for the chunk's total (one-shot: for all partials, summed locally in rank order, so every
+//                     GPU gets bit-identical z), apply momentum to the total, update z, optionally overwrite replicas.
+//
+// Transport is plain st.global on peer-mapped pointers plus st.release.sys / ld.acquire.sys flags; no TMA and no
+// cluster multicast anywhere in this file.  Flags carry the synchronisation epoch, so nothing is ever reset, and the
+// data buffers are double-buffered by epoch parity.  All blocks of a launch are resident at once (grid <= SM count;
+// the multi-rank-on-one-GPU test entry uses a cooperative launch) because blocks wait on other GPUs' blocks.
+// Every wait is bounded by a wall-clock limit: on expiry the kernel records XB_TIMEOUT_FLAG in `status`, skips the
+// chunk's update and carries on to the end, so the context stays usable and the host can raise an error.
+#include "common.cuh"
+#include <string.h>
+
+namespace {
+
+constexpr int CHUNK = 4096;          // floats per chunk (16 KB)
+constexpr int NT = 256;
+constexpr int MAXK = 16, MAXG = 8;
+
+enum Algo : int { ALGO_SMA = 0, ALGO_SSGD = 1, ALGO_POLYAK = 2 };
+
+struct SyncArgs {
+  int rank, G, k, algo;
+  long long n;                 // elements (multiple of 4)
+  int nchunks;
+  unsigned int epoch;          // >= 1, increases by one per call
+  int two_shot;
+  int copy_to_replicas;        // overwrite replicas with z at the end
+  int use_prev;                // SMA: difference against the pre-update snapshot (1) or current weights (0)
+  float alpha, mu, scale;      // scale: 1/wpc (S-SGD), 1/(k*G) (Polyak), unused (SMA)
+  float blend;                 // Polyak: running-average factor
+  float* w[MAXK];
+  const float* prev[MAXK];
+  float* z; float* zlast; float* gacc;
+  float* inbox[MAXG];          // inbox base of every GPU (index = destination GPU)
+  float* result[MAXG];         // two-shot result buffer of every GPU
+  unsigned int* ready1[MAXG];  // [G][nchunks] on every GPU: partial of (src, chunk) has landed
+  unsigned int* ready2[MAXG];  // [nchunks] on every GPU: total of chunk has landed
+  int* status;
+  unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait until *p >= epoch (wrap-safe). Returns false on timeout.
+__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int epoch, unsigned long long timeout_ns) {
+  if ((int)(ld_acquire_sys(p) - epoch) >= 0) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if ((int)(ld_acquire_sys(p) - epoch) >= 0) return true;
+      __nanosleep(64);
+    }
+    if (global_ns() - t0 > timeout_ns) return false;
+  }
+}
+
+__device__ __forceinline__ float4 f4add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 f4axpy(float s, float4 a, float4 b) { return make_float4(fmaf(s, a.x, b.x), fmaf(s, a.y, b.y), fmaf(s, a.z, b.z), fmaf(s, a.w, b.w)); }
+__device__ __forceinline__ float4 f4sub(float4 a, float4 b) { return make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w); }
+__device__ __forceinline__ float4 f4scale(float s, float4 a) { return make_float4(s * a.x, s * a.y, s * a.z, s * a.w); }
+
+// local reduction of one float4 lane + in-place replica correction
+__device__ __forceinline__ float4 local_part(const SyncArgs& a, long long i4) {
+  float4 acc = make_float4(0, 0, 0, 0);
+  if (a.algo == ALGO_SMA) {
+    const float4 z = reinterpret_cast<const float4*>(a.z)[i4];
+    for (int r = 0; r < a.k; ++r) {
+      float4* wp = reinterpret_cast<float4*>(a.w[r]) + i4;
+      float4 w = *wp;
+      float4 src = a.use_prev ? reinterpret_cast<const float4*>(a.prev[r])[i4] : w;
+      float4 d = f4scale(a.alpha, f4sub(src, z));
+      *wp = f4sub(w, d);
+      acc = f4add(acc, d);
+    }
+  } else if (a.algo == ALGO_SSGD) {
+    float4* gp = reinterpret_cast<float4*>(a.gacc) + i4;
+    acc = *gp;
+    *gp = make_float4(0, 0, 0, 0);
+  } else {  // ALGO_POLYAK: sum of replicas
+    for (int r = 0; r < a.k; ++r) acc = f4add(acc, reinterpret_cast<const float4*>(a.w[r])[i4]);
+  }
+  return acc;
+}
+
+// apply the all-reduced value D to z (and replicas)
+__device__ __forceinline__ void apply_total(const SyncArgs& a, long long i4, float4 D) {
+  float4* zp = reinterpret_cast<float4*>(a.z) + i4;
+  float4 z = *zp;
+  if (a.algo == ALGO_POLYAK) {
+    float4 mean = f4scale(a.scale, D);
+    z = make_float4(z.x + a.blend * (mean.x - z.x), z.y + a.blend * (mean.y - z.y), z.z + a.blend * (mean.z - z.z), z.w + a.blend * (mean.w - z.w));
+    *zp = z;
+    if (a.alpha > 0.f)
+      for (int r = 0; r < a.k; ++r) {
+        float4* wp = reinterpret_cast<float4*>(a.w[r]) + i4;
+        float4 w = *wp;
+        *wp = f4sub(w, f4scale(a.alpha, f4sub(w, z)));
+      }
+    return;
+  }
+  if (a.algo == ALGO_SSGD) D = f4scale(a.scale, D);
+  if (a.mu > 0.f) {
+    float4* lp = reinterpret_cast<float4*>(a.zlast) + i4;
+    D = f4axpy(a.mu, *lp, D);
+    *lp = D;
+  }
+  z = f4add(z, D);
+  *zp = z;
+  if (a.copy_to_replicas || a.algo == ALGO_SSGD)
+    for (int r = 0; r < a.k; ++r) reinterpret_cast<float4*>(a.w[r])[i4] = z;
+}
+
+__global__ void __launch_bounds__(NT) fused_sync_kernel(const SyncArgs* __restrict__ per_rank) {
+  const SyncArgs& a = per_rank[blockIdx.y];
+  __shared__ int s_fail;
+  const int tid = threadIdx.x, B = gridDim.x, G = a.G, me = a.rank;
+  const long long n4 = a.n / 4;
+  const int parity = a.epoch & 1;
+
+  if (G == 1) {   // no exchange: one pass
+    for (int c = blockIdx.x; c < a.nchunks; c += B)
+      for (int j = tid; j < CHUNK / 4; j += NT) {
+        long long i4 = (long long)c * (CHUNK / 4) + j;
+        if (i4 < n4) apply_total(a, i4, local_part(a, i4));
+      }
+    return;
+  }
+
+  const int owned_slots = (a.nchunks + G - 1) / G;
+  const long long slot_elems = (long long)(a.two_shot ? owned_slots : a.nchunks) * CHUNK;
+
+  // ---- phase 1: local reduce, replica correction, push partials -------------------------------------------
+  for (int c = blockIdx.x; c < a.nchunks; c += B) {
+    const int owner = c % G;
+    const long long dst_chunk = a.two_shot ? (c / G) : c;
+    const long long off4 = (((long long)parity * G + me) * slot_elems + dst_chunk * CHUNK) / 4;
+    for (int j = tid; j < CHUNK / 4; j += NT) {
+      long long i4 = (long long)c * (CHUNK / 4) + j;
+      float4 acc = (i4 < n4) ? local_part(a, i4) : make_float4(0, 0, 0, 0);
+      if (a.two_shot) {
+        reinterpret_cast<float4*>(a.inbox[owner])[off4 + j] = acc;
+      } else {
+        for (int g = 0; g < G; ++g) reinterpret_cast<float4*>(a.inbox[g])[off4 + j] = acc;
+      }
+    }
+    __syncthreads();
+    if (a.two_shot) {
+      if (tid == 0) { __threadfence_system(); st_release_sys(a.ready1[owner] + (long long)me * a.nchunks + c, a.epoch); }
+    } else if (tid < G) {
+      __threadfence_system();
+      st_release_sys(a.ready1[tid] + (long long)me * a.nchunks + c, a.epoch);
+    }
+  }
+
+  // ---- phase 2 (two-shot): owners reduce and broadcast the totals -----------------------------------------
+  if (a.two_shot) {
+    int jb = 0;
+    for (int c = me; c < a.nchunks; c += G, ++jb) {
+      if (jb % B != (int)blockIdx.x) continue;
+      if (tid == 0) s_fail = 0;
+      __syncthreads();
+      if (tid < G && !wait_flag(a.ready1[me] + (long long)tid * a.nchunks + c, a.epoch, a.timeout_ns)) { s_fail = 1; atomicExch(a.status, XB_TIMEOUT_FLAG); }
+      __syncthreads();
+      const bool ok = !s_fail;
+      const long long res4 = ((long long)parity * a.nchunks + c) * (CHUNK / 4);
+      for (int j = tid; j < CHUNK / 4 && ok; j += NT) {
+        float4 t = make_float4(0, 0, 0, 0);
+        for (int src = 0; src < G; ++src) {
+          long long o4 = (((long long)parity * G + src) * slot_elems + (long long)(c / G) * CHUNK) / 4 + j;
+          t = f4add(t, __ldcg(reinterpret_cast<const float4*>(a.inbox[me]) + o4));
+        }
+        for (int g = 0; g < G; ++g) reinterpret_cast<float4*>(a.result[g])[res4 + j] = t;
+      }
+      __syncthreads();
+      if (ok && tid < G) { __threadfence_system(); st_release_sys(a.ready2[tid] + c, a.epoch); }
+    }
+  }
+
+  // ---- phase 3: totals -> z (and replicas) ----------------------------------------------------------------
+  for (int c = blockIdx.x; c < a.nchunks; c += B) {
+    if (tid == 0) s_fail = 0;
+    __syncthreads();
+    if (a.two_shot) {
+      if (tid == 0 && !wait_flag(a.ready2[me] + c, a.epoch, a.timeout_ns)) { s_fail = 1; atomicExch(a.status, XB_TIMEOUT_FLAG); }
+    } else if (tid < G) {
+      if (!wait_flag(a.ready1[me] + (long long)tid * a.nchunks + c, a.epoch, a.timeout_ns)) { s_fail = 1; atomicExch(a.status, XB_TIMEOUT_FLAG); }
+    }
+    __syncthreads();
+    const bool fail = s_fail != 0;
+    __syncthreads();            // everyone has read s_fail before thread 0 may reset it in the next iteration
+    if (fail) continue;
+    for (int j = tid; j < CHUNK / 4; j += NT) {
+      long long i4 = (long long)c * (CHUNK / 4) + j;
+      if (i4 >= n4) break;
+      float4 D;
+      if (a.two_shot) {
+        D = __ldcg(reinterpret_cast<const float4*>(a.result[me]) + ((long long)parity * a.nchunks + c) * (CHUNK / 4) + j);
+      } else {
+        D = make_float4(0, 0, 0, 0);
+        for (int src = 0; src < G; ++src) {
+          long long o4 = (((long long)parity * G + src) * slot_elems + (long long)c * CHUNK) / 4 + j;
+          D = f4add(D, __ldcg(reinterpret_cast<const float4*>(a.inbox[me]) + o4));
+        }
+      }
+      apply_total(a, i4, D);
+    }
+    __syncthreads();
+  }
+}
+
+// replicas <- z (DEFAULT update model, and LR-drop copies when no averaging is due)
+__global__ void broadcast_z_kernel(const float* __restrict__ z, float* const* w, int k, long long n4) {
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n4; i += (long long)gridDim.x * NT) {
+    float4 v = reinterpret_cast<const float4*>(z)[i];
+    for (int r = 0; r < k; ++r) reinterpret_cast<float4*>(w[r])[i] = v;
+  }
+}
+
+}  // namespace
+
+// Sizes (in floats / words) of the peer-visible buffers a GPU must allocate for vectors of n elements.
+XB_API long long xb_sync_chunk() { return CHUNK; }
+XB_API long long xb_sync_nchunks(long long n) { return (n + CHUNK - 1) / CHUNK; }
+XB_API long long xb_sync_inbox_floats(long long n, int G, int two_shot) {
+  long long nc = xb_sync_nchunks(n);
+  long long slots = two_shot ? (nc + G - 1) / G : nc;
+  return 2LL * G * slots * CHUNK;
+}
+XB_API long long xb_sync_result_floats(long long n) { return 2LL * xb_sync_nchunks(n) * CHUNK; }
+XB_API long long xb_sync_flag_words(long long n, int G) { return (long long)(G + 1) * xb_sync_nchunks(n); }
+XB_API int xb_sync_args_size() { return (int)sizeof(SyncArgs); }
+
+// Host-side mirror used by the Python binding to fill SyncArgs without knowing its layout.
+struct XbSyncDesc {
+  int rank, G, k, algo;
+  long long n;
+  unsigned int epoch;
+  int two_shot, copy_to_replicas, use_prev;
+  float alpha, mu, scale, blend;
+  float* w[MAXK];
+  const float* prev[MAXK];
+  float* z; float* zlast; float* gacc;
+  float* inbox[MAXG]; float* result[MAXG];
+  unsigned int* flags[MAXG];      // per GPU: ready1 [G*nchunks] followed by ready2 [nchunks]
+  int* status;
+  double timeout_s;
+};
+
+static void fill_args(SyncArgs& a, const XbSyncDesc& d) {
+  memset(&a, 0, sizeof(a));
+  a.rank = d.rank; a.G = d.G; a.k = d.k; a.algo = d.algo; a.n = d.n; a.nchunks = (int)xb_sync_nchunks(d.n);
+  a.epoch = d.epoch; a.two_shot = d.two_shot; a.copy_to_replicas = d.copy_to_replicas; a.use_prev = d.use_prev;
+  a.alpha = d.alpha; a.mu = d.mu; a.scale = d.scale; a.blend = d.blend;
+  for (int i = 0; i < MAXK; ++i) { a.w[i] = d.w[i]; a.prev[i] = d.prev[i]; }
+  a.z = d.z; a.zlast = d.zlast; a.gacc = d.gacc;
+  for (int g = 0; g < MAXG; ++g) {
+    a.inbox[g] = d.inbox[g]; a.result[g] = d.result[g];
+    a.ready1[g] = d.flags[g];
+    a.ready2[g] = d.flags[g] ? d.flags[g] + (long long)d.G * a.nchunks : nullptr;
+  }
+  a.status = d.status;
+  a.timeout_ns = (unsigned long long)(d.timeout_s * 1e9);
+}
+
+static int sync_grid(int nchunks, int max_blocks) {
+  int b = nchunks < max_blocks ? nchunks : max_blocks;
+  return b < 1 ? 1 : b;
+}
+
+// One rank (this process's GPU). `args_dev` is a device buffer of xb_sync_args_size() bytes owned by the caller;
+// `args_pinned` a pinned host staging buffer of the same size.
+XB_API int xb_fused_sync(const XbSyncDesc* d, void* args_dev, void* args_pinned, int max_blocks, cudaStream_t st) {
+  if (d->n % 4 || d->k < 0 || d->k > MAXK || d->G < 1 || d->G > MAXG) return -XB_BAD_ARG;
+  SyncArgs* h = reinterpret_cast<SyncArgs*>(args_pinned);
+  fill_args(*h, *d);
+  XB_CUDA_CHECK(cudaMemcpyAsync(args_dev, h, sizeof(SyncArgs), cudaMemcpyHostToDevice, st));
+  dim3 grid(sync_grid(h->nchunks, max_blocks > 0 ? max_blocks : 148), 1);
+  fused_sync_kernel<<<grid, NT, 0, st>>>(reinterpret_cast<const SyncArgs*>(args_dev));
+  return (int)cudaGetLastError();
+}
+
+// G ranks emulated on ONE GPU: a single cooperative launch with gridDim.y = G, so every rank's blocks are resident
+// together (separate launches that wait on one another must never share a GPU).
+XB_API int xb_fused_sync_emulated(const XbSyncDesc* descs, int G, void* args_dev, int blocks_per_rank, cudaStream_t st) {
+  if (G < 1 || G > MAXG) return -XB_BAD_ARG;
+  SyncArgs h[MAXG];
+  for (int g = 0; g < G; ++g) { if (descs[g].n % 4 || descs[g].k > MAXK) return -XB_BAD_ARG; fill_args(h[g], descs[g]); }
+  XB_CUDA_CHECK(cudaMemcpyAsync(args_dev, h, sizeof(SyncArgs) * G, cudaMemcpyHostToDevice, st));
+  XB_CUDA_CHECK(cudaStreamSynchronize(st));   // h is on the stack
+  int dev = 0, sms = 0, per_sm = 0;
+  XB_CUDA_CHECK(cudaGetDevice(&dev));
+  XB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  XB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_sync_kernel, NT, 0));
+  int bpr = sync_grid(h[0].nchunks, blocks_per_rank > 0 ? blocks_per_rank : 16);
+  while (bpr > 1 && (long long)bpr * G > (long long)sms * per_sm) --bpr;
+  dim3 grid(bpr, G);
+  const SyncArgs* p = reinterpret_cast<const SyncArgs*>(args_dev);
+  void* kargs[] = {(void*)&p};
+  XB_CUDA_CHECK(cudaLaunchCooperativeKernel((void*)fused_sync_kernel, grid, dim3(NT), kargs, 0, st));
+  return (int)cudaGetLastError();
+}
+
+XB_API int xb_broadcast_model(const float* z, float* const* w_dev_array, int k, long long n, cudaStream_t st) {
+  if (n % 4) return -XB_BAD_ARG;
+  long long n4 = n / 4;
+  int blocks = (int)((n4 + NT - 1) / NT); if (blocks > 148 * 8) blocks = 148 * 8; if (blocks < 1) blocks = 1;
+  broadcast_z_kernel<<<blocks, NT, 0, st>>>(z, w_dev_array, k, n4);
+  return (int)cudaGetLastError();
+}

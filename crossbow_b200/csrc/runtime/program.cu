@@ -1,0 +1,322 @@
+// Device program = the flat list of kernel launches one task needs, plus the learner that owns it.
+//
+// The reference walks its operator list on the host for every task and calls one function pointer per operator,
+// each of which issues several library calls (clib-multigpu/executioncontext.c:558-726, taskhandler.c:24-151,
+// operator.c:57-60, kernelmap.c:27-50).  Here the graph is lowered ONCE into an array of XbOp records with all
+// pointers and shapes resolved; a learner replays it either directly or, normally, as a captured CUDA graph, so a
+// task costs one graph launch on the host.  Values that differ between tasks (learning rate, task id, ...) live in a
+// per-learner XbTaskParams block that is uploaded by the first node of the program.
+#include "../kernels/common.cuh"
+#include <vector>
+#include <string.h>
+#include <stdio.h>
+
+// ---- kernel entry points implemented in ../kernels --------------------------------------------------------------
+struct XbTransposeDesc;
+XB_API int xb_conv_fprop_simt(const float*, const float*, const float*, float*, float*, const XbConvGeom*, int, cudaStream_t);
+XB_API int xb_conv_dgrad_simt(const float*, const float*, float*, const XbConvGeom*, int, cudaStream_t);
+XB_API int xb_conv_wgrad_simt(const float*, const float*, float*, const XbConvGeom*, cudaStream_t);
+XB_API int xb_conv_fprop_tc(const float*, const float*, const float*, float*, float*, const XbConvGeom*, int, int*, cudaStream_t);
+XB_API int xb_conv_dgrad_tc(const float*, const float*, float*, const XbConvGeom*, int, int*, cudaStream_t);
+XB_API int xb_conv_wgrad_tc(const float*, const float*, float*, const XbConvGeom*, int*, cudaStream_t);
+XB_API int xb_tc_supported(const XbConvGeom*, int which);
+XB_API int xb_transpose_weights(const float*, float*, const XbTransposeDesc*, int, int, cudaStream_t);
+XB_API int xb_bn_stats(const float*, float*, int, int, cudaStream_t);
+XB_API int xb_bn_forward(const float*, const float*, float*, const float*, const float*, const float*, float*, float*, float*, float*,
+                         const XbTaskParams*, int, int, float, int, int, int, float, cudaStream_t);
+XB_API int xb_bn_backward(const float*, const float*, const float*, const float*, const float*, const float*, float*, float*, float*, float*,
+                          float*, int, int, int, int, int, cudaStream_t);
+XB_API int xb_act_forward(const float*, float*, long long, int, float, float, cudaStream_t);
+XB_API int xb_act_backward(const float*, const float*, const float*, float*, long long, int, float, float, int, cudaStream_t);
+XB_API int xb_weighted_sum(const float* const*, const float*, int, float*, long long, int, cudaStream_t);
+XB_API int xb_dropout(const float*, float*, long long, float, unsigned, const XbTaskParams*, int, cudaStream_t);
+XB_API int xb_concat_copy(const float*, float*, long long, int, int, int, int, int, cudaStream_t);
+XB_API int xb_pool_forward(const float*, float*, const int*, int, cudaStream_t);
+XB_API int xb_pool_backward(const float*, const float*, float*, const int*, int, int, cudaStream_t);
+XB_API int xb_lrn_forward(const float*, float*, float*, long long, int, int, float, float, float, cudaStream_t);
+XB_API int xb_lrn_backward(const float*, const float*, const float*, const float*, float*, long long, int, int, float, float, int, cudaStream_t);
+XB_API int xb_transform(const float*, float*, const float*, int, int, int, int, int, int, int, int, float, int, unsigned, const XbTaskParams*, cudaStream_t);
+XB_API int xb_colsum(const float*, float*, int, int, cudaStream_t);
+XB_API int xb_softmax_xent(const float*, const int*, float*, float*, float*, int, int, int, int, cudaStream_t);
+XB_API int xb_classify(const float*, float*, int, int, cudaStream_t);
+XB_API int xb_grad_sumsq(const float*, float*, long long, cudaStream_t);
+XB_API int xb_fused_optimiser(float*, float*, float*, float*, float*, const float*, const float*, const XbTaskParams*, long long, int, cudaStream_t);
+
+enum XbOpKind : int {
+  OP_MEMSET = 0, OP_UPLOAD = 1, OP_TRANSFORM = 2, OP_CONV_FPROP = 3, OP_CONV_DGRAD = 4, OP_CONV_WGRAD = 5, OP_COLSUM = 6,
+  OP_BN_STATS = 7, OP_BN_FWD = 8, OP_BN_BWD = 9, OP_ACT_FWD = 10, OP_ACT_BWD = 11, OP_SUM = 12, OP_DROPOUT = 13,
+  OP_CONCAT = 14, OP_POOL_FWD = 15, OP_POOL_BWD = 16, OP_LRN_FWD = 17, OP_LRN_BWD = 18, OP_SOFTMAX_XENT = 19,
+  OP_CLASSIFY = 20, OP_TRANSPOSE_W = 21, OP_GRAD_SUMSQ = 22, OP_OPTIMISER = 23, OP_COPY = 24,
+};
+
+// One launch. Field meaning depends on `kind` (documented where the Python lowering fills them).
+struct XbOp {
+  int kind;
+  int flags;
+  int ia[16];
+  float fa[8];
+  long long la[4];
+  void* p[12];
+};
+
+struct XbProgram {
+  std::vector<XbOp> ops;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  int launches = 0;       // kernel launches issued by one replay (for accounting)
+  int use_tc = 1;         // allow tensor-core convolution kernels
+  int* tc_status = nullptr;
+};
+
+static inline XbConvGeom geom_of(const XbOp& o) {
+  XbConvGeom g;
+  memcpy(&g, o.ia, sizeof(XbConvGeom));
+  return g;
+}
+
+static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
+  switch (o.kind) {
+    case OP_MEMSET: return (int)cudaMemsetAsync(o.p[0], 0, (size_t)o.la[0], st);
+    case OP_UPLOAD: return (int)cudaMemcpyAsync(o.p[0], o.p[1], (size_t)o.la[0], cudaMemcpyHostToDevice, st);
+    case OP_COPY:   return (int)cudaMemcpyAsync(o.p[0], o.p[1], (size_t)o.la[0], cudaMemcpyDeviceToDevice, st);
+    case OP_TRANSFORM:
+      return xb_transform((const float*)o.p[0], (float*)o.p[1], (const float*)o.p[2], o.ia[0], o.ia[1], o.ia[2], o.ia[3], o.ia[4], o.ia[5],
+                          o.ia[6], o.ia[7], o.fa[0], o.ia[8], (unsigned)o.ia[9], (const XbTaskParams*)o.p[3], st);
+    case OP_CONV_FPROP: {
+      XbConvGeom g = geom_of(o);
+      if (pr->use_tc && (o.flags & 0x100) && xb_tc_supported(&g, 0))
+        return xb_conv_fprop_tc((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (float*)o.p[3], (float*)o.p[4], &g, o.flags & 0xff, pr->tc_status, st);
+      return xb_conv_fprop_simt((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (float*)o.p[3], (float*)o.p[4], &g, o.flags & 0xff, st);
+    }
+    case OP_CONV_DGRAD: {
+      XbConvGeom g = geom_of(o);
+      if (pr->use_tc && (o.flags & 0x100) && xb_tc_supported(&g, 1))
+        return xb_conv_dgrad_tc((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, pr->tc_status, st);
+      return xb_conv_dgrad_simt((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, st);
+    }
+    case OP_CONV_WGRAD: {
+      XbConvGeom g = geom_of(o);
+      if (pr->use_tc && (o.flags & 0x100) && xb_tc_supported(&g, 2))
+        return xb_conv_wgrad_tc((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, pr->tc_status, st);
+      return xb_conv_wgrad_simt((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, st);
+    }
+    case OP_COLSUM: return xb_colsum((const float*)o.p[0], (float*)o.p[1], o.ia[0], o.ia[1], st);
+    case OP_BN_STATS: return xb_bn_stats((const float*)o.p[0], (float*)o.p[1], o.ia[0], o.ia[1], st);
+    case OP_BN_FWD:
+      return xb_bn_forward((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], (const float*)o.p[3], (const float*)o.p[4],
+                           (const float*)o.p[5], (float*)o.p[6], (float*)o.p[7], (float*)o.p[8], (float*)o.p[9], (const XbTaskParams*)o.p[10],
+                           o.ia[0], o.ia[1], o.fa[0], o.ia[2], o.ia[3], o.ia[4], o.fa[1], st);
+    case OP_BN_BWD:
+      return xb_bn_backward((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (const float*)o.p[3], (const float*)o.p[4],
+                            (const float*)o.p[5], (float*)o.p[6], (float*)o.p[7], (float*)o.p[8], (float*)o.p[9], (float*)o.p[10],
+                            o.ia[0], o.ia[1], o.ia[2], o.ia[3], o.ia[4], st);
+    case OP_ACT_FWD: return xb_act_forward((const float*)o.p[0], (float*)o.p[1], o.la[0], o.ia[0], o.fa[0], o.fa[1], st);
+    case OP_ACT_BWD:
+      return xb_act_backward((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (float*)o.p[3], o.la[0], o.ia[0], o.fa[0], o.fa[1], o.ia[1], st);
+    case OP_SUM: {
+      const float* xs[4] = {(const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (const float*)o.p[3]};
+      return xb_weighted_sum(xs, o.fa, o.ia[0], (float*)o.p[4], o.la[0], o.ia[1], st);
+    }
+    case OP_DROPOUT: return xb_dropout((const float*)o.p[0], (float*)o.p[1], o.la[0], o.fa[0], (unsigned)o.ia[0], (const XbTaskParams*)o.p[2], o.ia[1], st);
+    case OP_CONCAT: return xb_concat_copy((const float*)o.p[0], (float*)o.p[1], o.la[0], o.ia[0], o.ia[1], o.ia[2], o.ia[3], o.ia[4], st);
+    case OP_POOL_FWD: return xb_pool_forward((const float*)o.p[0], (float*)o.p[1], o.ia, o.flags & 1, st);
+    case OP_POOL_BWD: return xb_pool_backward((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], o.ia, o.flags & 1, (o.flags >> 1) & 1, st);
+    case OP_LRN_FWD: return xb_lrn_forward((const float*)o.p[0], (float*)o.p[1], (float*)o.p[2], o.la[0], o.ia[0], o.ia[1], o.fa[0], o.fa[1], o.fa[2], st);
+    case OP_LRN_BWD:
+      return xb_lrn_backward((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (const float*)o.p[3], (float*)o.p[4], o.la[0], o.ia[0],
+                             o.ia[1], o.fa[0], o.fa[1], o.ia[2], st);
+    case OP_SOFTMAX_XENT:
+      return xb_softmax_xent((const float*)o.p[0], (const int*)o.p[1], (float*)o.p[2], (float*)o.p[3], (float*)o.p[4], o.ia[0], o.ia[1], o.ia[2], o.ia[3], st);
+    case OP_CLASSIFY: return xb_classify((const float*)o.p[0], (float*)o.p[1], o.ia[0], o.ia[1], st);
+    case OP_TRANSPOSE_W: return xb_transpose_weights((const float*)o.p[0], (float*)o.p[1], (const XbTransposeDesc*)o.p[2], o.ia[0], o.ia[1], st);
+    case OP_GRAD_SUMSQ: return xb_grad_sumsq((const float*)o.p[0], (float*)o.p[1], o.la[0], st);
+    case OP_OPTIMISER:
+      return xb_fused_optimiser((float*)o.p[0], (float*)o.p[1], (float*)o.p[2], (float*)o.p[3], (float*)o.p[4], (const float*)o.p[5],
+                                (const float*)o.p[6], (const XbTaskParams*)o.p[7], o.la[0], o.ia[0], st);
+  }
+  return -XB_BAD_ARG;
+}
+
+XB_API int xb_op_size() { return (int)sizeof(XbOp); }
+
+XB_API XbProgram* xb_program_create(const XbOp* ops, int n, int use_tc, int* tc_status_dev) {
+  XbProgram* p = new XbProgram();
+  p->ops.assign(ops, ops + n);
+  p->use_tc = use_tc;
+  p->tc_status = tc_status_dev;
+  int l = 0;
+  for (int i = 0; i < n; ++i) {
+    int k = ops[i].kind;
+    if (k == OP_MEMSET || k == OP_UPLOAD || k == OP_COPY) continue;
+    l += (k == OP_BN_BWD) ? 2 : 1;
+  }
+  p->launches = l;
+  return p;
+}
+XB_API void xb_program_destroy(XbProgram* p) {
+  if (!p) return;
+  if (p->exec) cudaGraphExecDestroy(p->exec);
+  if (p->graph) cudaGraphDestroy(p->graph);
+  delete p;
+}
+XB_API int xb_program_launches(XbProgram* p) { return p->launches; }
+XB_API int xb_program_num_ops(XbProgram* p) { return (int)p->ops.size(); }
+
+// Issue every op on `st`. Returns 0 or (1000*op_index + error) so the caller can name the failing op.
+XB_API int xb_program_run(XbProgram* p, cudaStream_t st) {
+  for (size_t i = 0; i < p->ops.size(); ++i) {
+    int e = run_op(p, p->ops[i], st);
+    if (e != 0) return (int)(1000 * (i + 1) + (e < 0 ? -e : e));
+  }
+  return 0;
+}
+// Run a sub-range [first, last) - used by tests that inspect intermediate tensors.
+XB_API int xb_program_run_range(XbProgram* p, int first, int last, cudaStream_t st) {
+  for (int i = first; i < last && i < (int)p->ops.size(); ++i) {
+    int e = run_op(p, p->ops[i], st);
+    if (e != 0) return 1000 * (i + 1) + (e < 0 ? -e : e);
+  }
+  return 0;
+}
+
+// Record the program into a CUDA graph (the stream must not be the legacy default stream).
+XB_API int xb_program_capture(XbProgram* p, cudaStream_t st) {
+  if (p->exec) { cudaGraphExecDestroy(p->exec); p->exec = nullptr; }
+  if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
+  XB_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+  int e = xb_program_run(p, st);
+  cudaGraph_t g = nullptr;
+  cudaError_t ce = cudaStreamEndCapture(st, &g);
+  if (e != 0) { if (g) cudaGraphDestroy(g); return e; }
+  if (ce != cudaSuccess) return (int)ce;
+  p->graph = g;
+  XB_CUDA_CHECK(cudaGraphInstantiate(&p->exec, g, 0));
+  return 0;
+}
+XB_API int xb_program_launch(XbProgram* p, cudaStream_t st) {
+  if (p->exec) return (int)cudaGraphLaunch(p->exec, st);
+  return xb_program_run(p, st);
+}
+
+// ---- learner: stream + staging buffers + programs ------------------------------------------------------------------
+struct XbLearner {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t done = nullptr, start = nullptr;
+  XbProgram* train = nullptr;
+  XbProgram* test = nullptr;
+  void* d_examples = nullptr; size_t examples_bytes = 0;
+  void* d_labels = nullptr; size_t labels_bytes = 0;
+  XbTaskParams* h_params = nullptr;   // pinned; uploaded by the program's first node
+  float* h_result = nullptr;          // pinned + mapped: [loss, accuracy] written by the loss kernel
+  float* d_result = nullptr;          // device alias of h_result
+  int busy = 0;
+};
+
+XB_API XbLearner* xb_learner_create(int priority, void* d_examples, long long examples_bytes, void* d_labels, long long labels_bytes) {
+  XbLearner* l = new XbLearner();
+  int lo = 0, hi = 0;
+  cudaDeviceGetStreamPriorityRange(&lo, &hi);
+  int pr = priority < hi ? hi : (priority > lo ? lo : priority);
+  if (cudaStreamCreateWithPriority(&l->stream, cudaStreamNonBlocking, pr) != cudaSuccess) { delete l; return nullptr; }
+  cudaEventCreateWithFlags(&l->done, cudaEventDisableTiming);
+  cudaEventCreate(&l->start);
+  cudaHostAlloc((void**)&l->h_params, sizeof(XbTaskParams), cudaHostAllocDefault);
+  cudaHostAlloc((void**)&l->h_result, 64, cudaHostAllocMapped);
+  memset(l->h_params, 0, sizeof(XbTaskParams));
+  memset(l->h_result, 0, 64);
+  cudaHostGetDevicePointer((void**)&l->d_result, l->h_result, 0);
+  l->d_examples = d_examples; l->examples_bytes = (size_t)examples_bytes;
+  l->d_labels = d_labels; l->labels_bytes = (size_t)labels_bytes;
+  return l;
+}
+XB_API void xb_learner_destroy(XbLearner* l) {
+  if (!l) return;
+  cudaStreamSynchronize(l->stream);
+  cudaEventDestroy(l->done); cudaEventDestroy(l->start);
+  cudaFreeHost(l->h_params); cudaFreeHost(l->h_result);
+  cudaStreamDestroy(l->stream);
+  delete l;
+}
+XB_API void* xb_learner_stream(XbLearner* l) { return (void*)l->stream; }
+XB_API XbTaskParams* xb_learner_params(XbLearner* l) { return l->h_params; }
+XB_API float* xb_learner_result_host(XbLearner* l) { return l->h_result; }
+XB_API float* xb_learner_result_dev(XbLearner* l) { return l->d_result; }
+XB_API void xb_learner_set_programs(XbLearner* l, XbProgram* train, XbProgram* test) { l->train = train; l->test = test; }
+
+// Enqueue one task: copy the batch from (pinned) host memory, replay the program, record the completion event.
+// phase 0 = train, 1 = test.  Never blocks.
+XB_API int xb_learner_submit(XbLearner* l, const void* h_examples, const void* h_labels, const XbTaskParams* params, int phase) {
+  XbProgram* p = phase == 0 ? l->train : l->test;
+  if (!p) return -XB_BAD_ARG;
+  *l->h_params = *params;
+  if (h_examples) XB_CUDA_CHECK(cudaMemcpyAsync(l->d_examples, h_examples, l->examples_bytes, cudaMemcpyHostToDevice, l->stream));
+  if (h_labels) XB_CUDA_CHECK(cudaMemcpyAsync(l->d_labels, h_labels, l->labels_bytes, cudaMemcpyHostToDevice, l->stream));
+  int e = xb_program_launch(p, l->stream);
+  if (e) return e;
+  XB_CUDA_CHECK(cudaEventRecord(l->done, l->stream));
+  l->busy = 1;
+  return 0;
+}
+// Block until the learner's last task has finished; loss/accuracy are then valid in the result slot.
+XB_API int xb_learner_wait(XbLearner* l, float* loss, float* accuracy) {
+  XB_CUDA_CHECK(cudaEventSynchronize(l->done));
+  l->busy = 0;
+  if (loss) *loss = l->h_result[0];
+  if (accuracy) *accuracy = l->h_result[1];
+  return 0;
+}
+XB_API int xb_learner_query(XbLearner* l) {
+  cudaError_t e = cudaEventQuery(l->done);
+  if (e == cudaSuccess) return 1;
+  if (e == cudaErrorNotReady) { return 0; }
+  return -(int)e;
+}
+// Make stream `st` wait for this learner's last task (used by the synchroniser) and vice versa.
+XB_API int xb_stream_wait_learner(cudaStream_t st, XbLearner* l) { return (int)cudaStreamWaitEvent(st, l->done, 0); }
+XB_API int xb_learner_wait_event(XbLearner* l, cudaEvent_t ev) { return (int)cudaStreamWaitEvent(l->stream, ev, 0); }
+
+// ---- small CUDA plumbing used from Python (keeps torch out of the hot path) -----------------------------------------
+XB_API void* xb_stream_create(int priority) {
+  cudaStream_t s; int lo = 0, hi = 0;
+  cudaDeviceGetStreamPriorityRange(&lo, &hi);
+  int pr = priority < hi ? hi : (priority > lo ? lo : priority);
+  if (cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, pr) != cudaSuccess) return nullptr;
+  return (void*)s;
+}
+XB_API int xb_stream_destroy(void* s) { return (int)cudaStreamDestroy((cudaStream_t)s); }
+XB_API int xb_stream_sync(void* s) { return (int)cudaStreamSynchronize((cudaStream_t)s); }
+XB_API void* xb_event_create(int timing) {
+  cudaEvent_t e;
+  if (cudaEventCreateWithFlags(&e, timing ? cudaEventDefault : cudaEventDisableTiming) != cudaSuccess) return nullptr;
+  return (void*)e;
+}
+XB_API int xb_event_record(void* e, void* s) { return (int)cudaEventRecord((cudaEvent_t)e, (cudaStream_t)s); }
+XB_API int xb_event_sync(void* e) { return (int)cudaEventSynchronize((cudaEvent_t)e); }
+XB_API int xb_stream_wait_event(void* s, void* e) { return (int)cudaStreamWaitEvent((cudaStream_t)s, (cudaEvent_t)e, 0); }
+XB_API float xb_event_elapsed_ms(void* a, void* b) { float ms = -1.f; cudaEventElapsedTime(&ms, (cudaEvent_t)a, (cudaEvent_t)b); return ms; }
+XB_API void* xb_pinned_alloc(long long bytes) { void* p = nullptr; if (cudaHostAlloc(&p, (size_t)bytes, cudaHostAllocPortable) != cudaSuccess) return nullptr; return p; }
+XB_API int xb_pinned_free(void* p) { return (int)cudaFreeHost(p); }
+XB_API void* xb_device_alloc(long long bytes) { void* p = nullptr; if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) return nullptr; cudaMemset(p, 0, (size_t)bytes); return p; }
+XB_API int xb_device_free(void* p) { return (int)cudaFree(p); }
+XB_API int xb_memcpy_h2d_async(void* d, const void* h, long long bytes, void* s) { return (int)cudaMemcpyAsync(d, h, (size_t)bytes, cudaMemcpyHostToDevice, (cudaStream_t)s); }
+XB_API int xb_memcpy_d2h_async(void* h, const void* d, long long bytes, void* s) { return (int)cudaMemcpyAsync(h, d, (size_t)bytes, cudaMemcpyDeviceToHost, (cudaStream_t)s); }
+XB_API int xb_memcpy_d2d_async(void* d, const void* s_, long long bytes, void* s) { return (int)cudaMemcpyAsync(d, s_, (size_t)bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)s); }
+XB_API int xb_device_sync() { return (int)cudaDeviceSynchronize(); }
+XB_API int xb_set_device(int d) { return (int)cudaSetDevice(d); }
+XB_API const char* xb_error_string(int e) { return cudaGetErrorString((cudaError_t)e); }
+XB_API int xb_last_error() { return (int)cudaGetLastError(); }
+
+// ---- peer memory (one process per GPU): export / import of cudaMalloc'd buffers --------------------------------------
+XB_API int xb_ipc_export(void* dptr, void* handle64) {
+  cudaIpcMemHandle_t h;
+  XB_CUDA_CHECK(cudaIpcGetMemHandle(&h, dptr));
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+XB_API void* xb_ipc_import(const void* handle64) {
+  cudaIpcMemHandle_t h; memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return nullptr;
+  return p;
+}
+XB_API int xb_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }

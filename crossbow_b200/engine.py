@@ -1,0 +1,325 @@
+"""Execution engines: what actually runs a task and a synchronisation step.
+
+``GpuEngine`` owns, for ONE GPU (= one process): the central average model ``z``, ``k`` learners (replica flat
+vectors + activation arena + CUDA stream + captured task graph each), the synchronisation stream and the fused
+synchroniser.  It is the counterpart of the reference's native execution context + model manager + streams
+(clib-multigpu/executioncontext.c, modelmanager.c, stream.c), restructured so that a replica, its stream and its
+buffers form one fixed unit ("learner") whose whole task is a single CUDA-graph launch.
+
+``CpuEngine`` runs the same protocol on the CPU oracle (``--gpu false``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from .conf import ModelConf, SolverConf, SystemConf
+from .graph import SubGraph
+from .model import Model
+from .oracle import (DeviceState, OracleExecutor, ReplicaState, local_update, sma_base_momentum, synchronise)
+from .types import MomentumMethod, Phase, Regularisation, UpdateModel
+
+
+def task_params(solver: SolverConf, task: int, seed: int, training: bool, bn_updates: int = 0):
+    from .ops import lib as L
+    p = L.XbTaskParams()
+    p.lr = solver.learning_rate(task) if training else 0.0
+    p.momentum = solver.momentum_at(task)
+    p.weight_decay = solver.weight_decay
+    p.bn_factor = 1.0 / (1.0 + bn_updates)
+    p.clip = solver.clip_gradient_threshold if solver.clip_gradient_threshold is not None else -1.0
+    p.alpha = solver.alpha
+    p.task_id = task & 0xFFFFFFFF
+    p.seed_lo, p.seed_hi = seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF
+    p.training = int(training)
+    p.l1 = int(solver.regularisation_type == Regularisation.L1)
+    p.nesterov = int(solver.momentum_method == MomentumMethod.NESTEROV)
+    return p
+
+
+class Learner:
+    """Replica + stream + arena + programs."""
+
+    def __init__(self, engine: "GpuEngine", index: int, init: torch.Tensor):
+        from .lower import Lowering, ReplicaBuffers
+        from .ops import lib as L
+        lib = engine.lib
+        self.engine, self.index = engine, index
+        self.rep = ReplicaBuffers(engine.model, engine.device, init)
+        self.params_dev = torch.zeros(16, dtype=torch.int32, device=engine.device)
+        self.low_train = self.low_test = None
+        self.handle = None
+        self.clock = 0
+        self.pending = None          # (task_id, phase) in flight
+        c, h, w = engine.input_chw
+        # the first lowering allocates the staging buffers the native learner copies into
+        self.handle_placeholder = None
+        self._create(L, lib)
+
+    def _create(self, L, lib):
+        from .lower import Lowering
+        e = self.engine
+        # native learner first (it owns the pinned parameter block and the result slot), staging set afterwards
+        self.handle = lib.xb_learner_create(0, 0, 0, 0, 0)
+        if not self.handle:
+            raise L.CudaError("could not create a learner stream")
+        params_host = C.cast(lib.xb_learner_params(self.handle), C.c_void_p).value
+        result_dev = lib.xb_learner_result_dev(self.handle)
+        self.low_train = Lowering(e.train_graph, e.model, e.batch, e.input_chw, e.device, self.rep.w, self.rep, e.shared,
+                                  self.params_dev, params_host, result_dev, update_model=e.update_model, training=True,
+                                  use_tc=e.use_tc, clip=e.solver.clip_gradient_threshold >= 0, lr_mult=e.lr_mult)
+        ops = self.low_train.op_array()
+        self.prog_train = lib.xb_program_create(ops, len(ops), int(e.use_tc), e.tc_status.data_ptr())
+        self.prog_test = None
+        if e.test_graph is not None:
+            # test tasks read the CENTRAL model (the reference checks with the master copy) and share the staging buffers
+            self.low_test = Lowering(e.test_graph, e.model, e.batch, e.input_chw, e.device, e.shared.z, None, e.shared,
+                                     self.params_dev, params_host, result_dev, update_model=e.update_model, training=False,
+                                     use_tc=e.use_tc)
+            tops = self.low_test.op_array()
+            self.prog_test = lib.xb_program_create(tops, len(tops), int(e.use_tc), e.tc_status.data_ptr())
+        lib.xb_learner_set_programs(self.handle, self.prog_train, self.prog_test)
+        self.stream = lib.xb_learner_stream(self.handle)
+        if e.use_graphs:
+            L.check(lib.xb_program_capture(self.prog_train, self.stream), "capture of the training program")
+            if self.prog_test:
+                L.check(lib.xb_program_capture(self.prog_test, self.stream), "capture of the test program")
+
+    def staging(self, phase):
+        low = self.low_train if phase == Phase.TRAIN else self.low_test
+        return low.examples, low.labels
+
+    def submit(self, examples: torch.Tensor, labels: torch.Tensor, params, phase=Phase.TRAIN):
+        from .ops import lib as L
+        lib = self.engine.lib
+        ex, lab = self.staging(phase)
+        s = self.stream
+        L.check(lib.xb_memcpy_h2d_async(ex.data_ptr(), examples.data_ptr(), examples.numel() * 4, s), "H2D examples")
+        L.check(lib.xb_memcpy_h2d_async(lab.data_ptr(), labels.data_ptr(), labels.numel() * 4, s), "H2D labels")
+        L.check(lib.xb_learner_submit(self.handle, None, None, C.byref(params), int(phase)), "task submit")
+        self.pending = (params.task_id, phase)
+
+    def wait(self):
+        from .ops import lib as L
+        loss, acc = C.c_float(), C.c_float()
+        L.check(self.engine.lib.xb_learner_wait(self.handle, C.byref(loss), C.byref(acc)), "task wait")
+        self.pending = None
+        return loss.value, acc.value
+
+    def destroy(self):
+        lib = self.engine.lib
+        if self.handle:
+            lib.xb_learner_destroy(self.handle)
+            self.handle = None
+        for p in (self.prog_train, self.prog_test):
+            if p:
+                lib.xb_program_destroy(p)
+        self.prog_train = self.prog_test = None
+
+
+class GpuEngine:
+    def __init__(self, train_graph: SubGraph, test_graph: Optional[SubGraph], model: Model, init_canonical: np.ndarray,
+                 batch: int, input_chw, solver: SolverConf, update_model: UpdateModel, replicas: int = 1, wpc: int = 1,
+                 rank: int = 0, world: int = 1, device_index: int = 0, use_tc: bool = True, use_graphs: bool = True,
+                 seed: int = 0, fused_sync: bool = True, two_shot: Optional[bool] = None, sync_timeout_s: float = 5.0):
+        from .ops import lib as L
+        from .parallel.sync import FusedSynchroniser, ReferenceSynchroniser
+        if not torch.cuda.is_available():
+            raise RuntimeError("GpuEngine needs a CUDA device")
+        self.lib = L.load()          # raises if the extension cannot be built / loaded: no fallback on the device path
+        torch.cuda.set_device(device_index)
+        self.device = torch.device("cuda", device_index)
+        self.train_graph, self.test_graph, self.model = train_graph, test_graph, model
+        self.batch, self.input_chw, self.solver, self.update_model = batch, tuple(input_chw), solver, update_model
+        self.rank, self.world, self.wpc, self.seed = rank, world, wpc, seed
+        self.use_tc, self.use_graphs = use_tc, use_graphs
+        self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        init = torch.from_numpy(model.to_device(init_canonical)).to(self.device)
+        from .lower import DeviceShared
+        self.shared = DeviceShared(model, self.device, init)
+        self.lr_mult = torch.from_numpy(model.to_device(model.lr_multipliers())).to(self.device) if model.has_lr_multipliers() else None
+        self.learners: List[Learner] = []
+        for i in range(replicas):
+            self.learners.append(Learner(self, i, init))
+        self.sync_stream = self.lib.xb_stream_create(-1)
+        self.sync_event = self.lib.xb_event_create(0)
+        n = model.device_elements
+        Sync = FusedSynchroniser if fused_sync else ReferenceSynchroniser
+        self.synchroniser = Sync(n, rank, world, two_shot, sync_timeout_s) if fused_sync else Sync(n, rank, world)
+        self.poly_count = 0
+        self.bn_updates = 0
+        torch.cuda.synchronize()
+
+    # ---- replicas ----
+    @property
+    def k(self):
+        return len(self.learners)
+
+    def add_learner(self) -> Learner:
+        """Auto-tuner: clone a new replica from an existing one (modelmanager.c:362-472)."""
+        torch.cuda.synchronize()
+        src = self.learners[0].rep.w
+        l = Learner(self, len(self.learners), src)
+        l.rep.last.copy_(self.learners[0].rep.last)
+        l.rep.prev.copy_(self.learners[0].rep.prev)
+        self.learners.append(l)
+        torch.cuda.synchronize()
+        return l
+
+    def remove_learner(self):
+        if len(self.learners) <= 1:
+            return
+        torch.cuda.synchronize()
+        self.learners.pop().destroy()
+
+    # ---- tasks ----
+    def params(self, task: int, training: bool):
+        return task_params(self.solver, task, self.seed, training, self.bn_updates)
+
+    def submit(self, learner: int, examples, labels, task: int, phase=Phase.TRAIN):
+        p = self.params(task, phase == Phase.TRAIN)
+        if phase == Phase.TRAIN:
+            self.bn_updates += 1
+        self.learners[learner].submit(examples, labels, p, phase)
+
+    def wait(self, learner: int):
+        return self.learners[learner].wait()
+
+    # ---- synchronisation ----
+    def synchronise(self, copy: bool = False, learners: Optional[List[int]] = None):
+        """Enqueue one synchronisation over the given (default: all) learners; returns immediately.
+
+        Ordering is on the device: the synchronisation stream waits for every participating learner's last task,
+        and those learners' next tasks wait for the synchronisation to finish."""
+        from .ops import lib as L
+        from .parallel import sync as S
+        lib, ss = self.lib, self.sync_stream
+        ls = [self.learners[i] for i in (learners if learners is not None else range(len(self.learners)))]
+        for l in ls:
+            L.check(lib.xb_stream_wait_learner(ss, l.handle), "sync waits for learner")
+        um, sv = self.update_model, self.solver
+        ws, prevs = [l.rep.w for l in ls], [l.rep.prev for l in ls]
+        sh = self.shared
+        if um in (UpdateModel.SMA, UpdateModel.SYNCHRONOUSEAMSGD):
+            self.synchroniser.synchronise(ss, S.ALGO_SMA, ws, prevs, sh.z, sh.zlast, None, alpha=sv.alpha,
+                                          mu=sma_base_momentum(sv), copy=copy, use_prev=True)
+        elif um == UpdateModel.EAMSGD:
+            self.synchroniser.synchronise(ss, S.ALGO_SMA, ws, prevs, sh.z, sh.zlast, None, alpha=sv.alpha,
+                                          mu=sv.base_model_momentum, copy=copy, use_prev=False)
+        elif um == UpdateModel.WORKER:
+            self.synchroniser.synchronise(ss, S.ALGO_SSGD, ws, None, sh.z, sh.zlast, sh.gacc, mu=sv.momentum, scale=1.0 / self.wpc)
+        elif um == UpdateModel.POLYAK_RUPPERT:
+            self.synchroniser.synchronise(ss, S.ALGO_POLYAK, ws, None, sh.z, sh.zlast, None, alpha=0.0,
+                                          scale=1.0 / (len(ls) * self.world), blend=1.0 / (self.poly_count + 1.0))
+            self.poly_count += 1
+        elif um == UpdateModel.DEFAULT:
+            arr = torch.tensor([w.data_ptr() for w in ws], dtype=torch.int64, device=self.device)
+            self._keep = arr
+            L.check(lib.xb_broadcast_model(sh.z.data_ptr(), arr.data_ptr(), len(ws), self.model.device_elements, ss), "broadcast")
+        else:
+            raise NotImplementedError(f"error: {um} is not supported (a stub in the reference as well)")
+        L.check(lib.xb_event_record(self.sync_event, ss), "record sync event")
+        for l in ls:
+            L.check(lib.xb_learner_wait_event(l.handle, self.sync_event), "learner waits for sync")
+
+    def finish(self):
+        torch.cuda.synchronize()
+        self.synchroniser.check()
+        s = self.tc_status.cpu()
+        if int(s[0]) != 0:
+            raise RuntimeError(f"a tensor-core kernel reported status {int(s[0])} (bounded wait expired)")
+
+    # ---- model access (canonical order, host) ----
+    def central_model(self) -> np.ndarray:
+        return self.model.to_canonical(self.shared.z.cpu().numpy())
+
+    def replica_model(self, i: int) -> np.ndarray:
+        return self.model.to_canonical(self.learners[i].rep.w.cpu().numpy())
+
+    def load_central(self, canonical: np.ndarray):
+        self.shared.z.copy_(torch.from_numpy(self.model.to_device(canonical)))
+
+    def load_replica(self, i: int, canonical: np.ndarray):
+        self.learners[i].rep.w.copy_(torch.from_numpy(self.model.to_device(canonical)))
+
+    def gpu_launches_per_task(self) -> int:
+        return self.lib.xb_program_launches(self.learners[0].prog_train)
+
+    def destroy(self):
+        torch.cuda.synchronize()
+        for l in self.learners:
+            l.destroy()
+        self.learners = []
+        self.synchroniser.close()
+        self.lib.xb_stream_destroy(self.sync_stream)
+
+
+class CpuEngine:
+    """Same protocol on the CPU oracle, with k replicas x G virtual devices in one process."""
+
+    def __init__(self, train_graph, test_graph, model: Model, init_canonical, batch, input_chw, solver: SolverConf,
+                 update_model: UpdateModel, replicas=1, wpc=1, devices=1, seed=0):
+        self.model, self.solver, self.update_model, self.wpc, self.seed = model, solver, update_model, wpc, seed
+        w = torch.from_numpy(np.asarray(init_canonical, dtype=np.float32))
+        self.devs = [DeviceState(w) for _ in range(devices)]
+        for d in self.devs:
+            d.replicas = [ReplicaState(w) for _ in range(replicas)]
+        self.train_exec = OracleExecutor(train_graph, model, seed)
+        self.test_exec = OracleExecutor(test_graph, model, seed) if test_graph is not None else None
+        self.results = {}
+        self.lr_mult = torch.from_numpy(model.lr_multipliers()) if model.has_lr_multipliers() else None
+
+    @property
+    def k(self):
+        return len(self.devs[0].replicas)
+
+    def _slot(self, learner):
+        return self.devs[learner // self.k], self.devs[learner // self.k].replicas[learner % self.k]
+
+    def submit(self, learner, examples, labels, task, phase=Phase.TRAIN):
+        dev, rep = self._slot(learner)
+        x, y = torch.as_tensor(examples, dtype=torch.float32), torch.as_tensor(labels)
+        if phase == Phase.TRAIN:
+            rep.g.zero_()
+            r = self.train_exec.run(rep.w, x, y, Phase.TRAIN, task, dev.op_state, rep.g)
+            local_update(rep, dev, self.solver, self.update_model, task, self.lr_mult)
+        else:
+            r = self.test_exec.run(dev.z, x, y, Phase.CHECK, task, dev.op_state)
+        self.results[learner] = (r["loss"] if r["loss"] is not None else 0.0, r["accuracy"] if r["accuracy"] is not None else 0.0)
+
+    def wait(self, learner):
+        return self.results.pop(learner)
+
+    def synchronise(self, copy=False, learners=None):
+        synchronise(self.update_model, self.devs, self.solver, self.wpc, copy)
+
+    def add_learner(self):
+        for d in self.devs:
+            d.replicas.append(d.replicas[0].clone())
+
+    def remove_learner(self):
+        for d in self.devs:
+            if len(d.replicas) > 1:
+                d.replicas.pop()
+
+    def finish(self):
+        pass
+
+    def central_model(self):
+        return self.devs[0].z.numpy().copy()
+
+    def replica_model(self, i):
+        return self._slot(i)[1].w.numpy().copy()
+
+    def load_central(self, canonical):
+        for d in self.devs:
+            d.z = torch.from_numpy(np.asarray(canonical, dtype=np.float32)).clone()
+
+    def load_replica(self, i, canonical):
+        self._slot(i)[1].w = torch.from_numpy(np.asarray(canonical, dtype=np.float32)).clone()
+
+    def destroy(self):
+        pass

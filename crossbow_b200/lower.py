@@ -1,0 +1,546 @@
+"""Lowers a dataflow graph to a device program (array of ``XbOp`` launches) for one learner.
+
+The reference registers every operator with the native side and then, per task, walks the operator list and
+calls one function per operator, gradient operators included (SubGraph.java:397-552; executioncontext.c:558-726).
+Here the forward nodes of the graph are compiled once into a fused launch list:
+
+* activations are channels-last; convolution / inner-product weights use the device element order of ``model.py``;
+* ``Conv -> BatchNorm``: the convolution epilogue produces the per-channel sum / sum of squares, so batch-norm is
+  one more pass; ``BatchNorm (-> Sum with a shortcut) -> ReLU`` is a single normalise kernel; ``Conv/InnerProduct
+  -> ReLU`` folds the activation into the GEMM epilogue; ``SoftMax -> {SoftMaxLoss, Accuracy}`` and the loss
+  gradient are one kernel that also writes loss/accuracy into the learner's host-mapped result slot;
+* the backward pass is derived from the same forward nodes in reverse topological order (the graph's explicit
+  gradient nodes define WHICH operators are differentiated; the CPU oracle executes them one by one), with
+  first-write / accumulate tracking for tensors that feed several consumers (the reference's "merge" operators);
+* weight gradients go straight into the replica's flat gradient vector, which the fused optimiser consumes
+  and clears.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .graph import SubGraph
+from .model import Model
+from .ops import lib as L
+from .types import (ActivationMode, BatchNormEstimatedMeanAndVarianceType, ElementWiseOpType, NormalisationMode,
+                    Phase, PoolMethod, UpdateModel)
+
+
+class Arena:
+    """Bump allocator over one CUDA allocation (activations, gradients of activations, scratch of one learner)."""
+
+    def __init__(self, device, nbytes: int = 0):
+        self.device = device
+        self.chunks: List[torch.Tensor] = []
+        self.total = 0
+
+    def alloc(self, numel: int, dtype=torch.float32, zero=False) -> torch.Tensor:
+        # separate torch allocations keep this simple; 256-byte alignment is guaranteed by the caching allocator
+        t = (torch.zeros if zero else torch.empty)(max(1, numel), dtype=dtype, device=self.device)
+        self.chunks.append(t)
+        self.total += t.numel() * t.element_size()
+        return t
+
+
+class T:
+    """A device tensor in the program: storage + logical channels-last shape."""
+    __slots__ = ("buf", "n", "h", "w", "c", "grad", "grad_written", "needs_grad", "name")
+
+    def __init__(self, buf, n, h, w, c, name=""):
+        self.buf, self.n, self.h, self.w, self.c = buf, n, h, w, c
+        self.grad: Optional[torch.Tensor] = None
+        self.grad_written = False
+        self.needs_grad = False
+        self.name = name
+
+    @property
+    def rows(self):
+        return self.n * self.h * self.w
+
+    @property
+    def numel(self):
+        return self.rows * self.c
+
+    def nhwc(self):
+        return self.buf[: self.numel].view(self.n, self.h, self.w, self.c)
+
+
+class ReplicaBuffers:
+    """Flat device vectors of one replica (device element order, padded)."""
+
+    def __init__(self, model: Model, device, init: Optional[torch.Tensor] = None):
+        n = model.device_elements
+        self.n = n
+        self.w = torch.zeros(n, device=device) if init is None else init.clone()
+        self.g = torch.zeros(n, device=device)
+        self.last = torch.zeros(n, device=device)
+        self.prev = self.w.clone()
+        self.wt = torch.zeros(max(1, n), device=device)      # transposed copies of convolution weights for dgrad
+
+
+class DeviceShared:
+    """State shared by all learners of one GPU: central model z, its momentum, S-SGD accumulator, BN running stats."""
+
+    def __init__(self, model: Model, device, init: torch.Tensor):
+        n = model.device_elements
+        self.z = init.clone()
+        self.zlast = torch.zeros(n, device=device)
+        self.gacc = torch.zeros(n, device=device)
+        self.run_mean: Dict[int, torch.Tensor] = {}
+        self.run_var: Dict[int, torch.Tensor] = {}
+        self.device = device
+
+    def running(self, op_uid: int, channels: int):
+        if op_uid not in self.run_mean:
+            self.run_mean[op_uid] = torch.zeros(channels, device=self.device)
+            self.run_var[op_uid] = torch.ones(channels, device=self.device)
+        return self.run_mean[op_uid], self.run_var[op_uid]
+
+
+def _op(kind, flags=0, ia=(), fa=(), la=(), p=()) -> L.XbOp:
+    o = L.XbOp()
+    o.kind, o.flags = kind, flags
+    for i, v in enumerate(ia):
+        o.ia[i] = int(v)
+    for i, v in enumerate(fa):
+        o.fa[i] = float(v)
+    for i, v in enumerate(la):
+        o.la[i] = int(v)
+    for i, v in enumerate(p):
+        o.p[i] = v if isinstance(v, int) else (0 if v is None else v.data_ptr())
+    return o
+
+
+class Lowering:
+    def __init__(self, graph: SubGraph, model: Model, batch: int, input_chw, device, weights: torch.Tensor,
+                 replica: Optional[ReplicaBuffers], shared: DeviceShared, params_dev: torch.Tensor, params_host_ptr: int,
+                 result_dev_ptr: int,
+                 update_model: UpdateModel = UpdateModel.SMA, training=True, use_tc=True, clip=False,
+                 lr_mult: Optional[torch.Tensor] = None, seed_stream_base=0):
+        self.g, self.model, self.batch, self.device = graph, model, batch, device
+        self.weights = weights              # flat vector the forward pass reads (replica weights, or z for tests)
+        self.replica, self.shared = replica, shared
+        self.params_dev, self.params_host_ptr, self.result_ptr = params_dev, params_host_ptr, result_dev_ptr
+        self.update_model, self.training, self.use_tc, self.clip = update_model, training, use_tc, clip
+        self.lr_mult = lr_mult
+        self.arena = Arena(device)
+        self.ops: List[L.XbOp] = []
+        self.keep = []                      # python objects that must outlive the program (descriptor tables ...)
+        c, h, w = input_chw
+        self.input_chw = (c, h, w)
+        self.examples = self.arena.alloc(batch * c * h * w)                 # NCHW staging buffer (H2D target)
+        self.labels = self.arena.alloc(batch, dtype=torch.int32)
+        self.tensors: Dict[int, T] = {}     # id(node) -> output tensor
+        bn_channels = sum(n.op.output_shape.dims[1] for n in graph.order if n.op.kernel.kind == "batchnorm")
+        self.zero_region = self.arena.alloc(4 * bn_channels + 64, zero=True)   # per-task accumulators, cleared by one memset
+        self.zero_used = 0
+        self.x_in: Optional[T] = None
+        self.node_info: Dict[int, dict] = {}
+        self.logits: Optional[T] = None
+        self.probs: Optional[T] = None
+        self._build()
+
+    # ---- helpers ----
+    def wptr(self, var, base: Optional[torch.Tensor] = None) -> int:
+        base = self.weights if base is None else base
+        return base.data_ptr() + 4 * var.doffset
+
+    def new_tensor(self, n, h, w, c, name="") -> T:
+        return T(self.arena.alloc(n * h * w * c), n, h, w, c, name)
+
+    def grad_of(self, t: T) -> torch.Tensor:
+        if t.grad is None:
+            t.grad = self.arena.alloc(t.numel)
+        return t.grad
+
+    def gout(self, t: T):
+        """(pointer, accumulate) for a backward op that contributes to t's gradient."""
+        g = self.grad_of(t)
+        acc = t.grad_written
+        t.grad_written = True
+        return g, int(acc)
+
+    def emit(self, op):
+        self.ops.append(op)
+
+    # ---- build ----
+    def _consumers(self, node):
+        return [m for m in node.next if not m.op.kernel.is_gradient and not m.op.kernel.is_optimiser
+                and not getattr(m.op.kernel, "is_gradient_merge", False)]
+
+    def _inputs(self, node):
+        return [p for p in node.prev if not p.op.kernel.is_gradient]
+
+    def _build(self):
+        fwd = [n for n in self.g.order if not n.op.kernel.is_gradient and not n.op.kernel.is_optimiser
+               and not getattr(n.op.kernel, "is_gradient_merge", False)]
+        self.fwd = fwd
+        has_grad = self.training and any(n.op.kernel.is_gradient for n in self.g.order)
+        self.has_backward = has_grad
+        differentiated = {n.op.peer.uid for n in self.g.order if n.op.kernel.is_gradient and n.op.peer is not None}
+        # task parameters first, then zero the per-task accumulators (filled in at the end, once sizes are known)
+        self.emit(_op(L.OP_UPLOAD, la=[C.sizeof(L.XbTaskParams)], p=[self.params_dev, self.params_host_ptr]))
+        zero_slot = len(self.ops)
+        self.emit(_op(L.OP_MEMSET, la=[4], p=[self.params_dev]))                              # placeholder, patched below
+        transpose_slot = None
+        if has_grad:
+            transpose_slot = len(self.ops)
+            self.emit(_op(L.OP_MEMSET, la=[0], p=[0]))                                        # placeholder
+        self._plan_fusion(fwd)
+        c, h, w = self.input_chw
+        x_in = None
+        if not fwd[0].op.kernel.is_data_transform:
+            x_in = self.new_tensor(self.batch, h, w, c, "input")
+            self.x_in = x_in
+            self.emit(_op(L.OP_TRANSFORM, ia=[self.batch, c, h, w, h, w, 0, 0, 0, 0], fa=[1.0],
+                          p=[self.examples, x_in.buf, 0, self.params_dev]))
+        for n in fwd:
+            self._forward(n, x_in)
+        if has_grad:
+            self._backward(fwd, differentiated)
+            self._finish_transposes(transpose_slot)
+            self._optimiser()
+        # one memset clears all per-task accumulators (BN sums, BN backward sums)
+        self.ops[zero_slot] = _op(L.OP_MEMSET, la=[4 * self.zero_used], p=[self.zero_region])
+
+    def scratch_zeroed(self, numel) -> torch.Tensor:
+        if self.zero_used + numel > self.zero_region.numel():
+            raise RuntimeError("per-task accumulator region is too small")
+        t = self.zero_region[self.zero_used:self.zero_used + numel]
+        self.zero_used += (numel + 3) // 4 * 4
+        return t
+
+    def _plan_fusion(self, fwd):
+        info = self.node_info
+        for n in fwd:
+            info[id(n)] = dict(fused_into=None, relu=None, stats_from=None, deferred=False, carrier=None, res=None)
+        for n in fwd:
+            k = n.op.kernel
+            cons = self._consumers(n)
+            if k.kind in ("conv", "innerproduct") and len(cons) == 1 and cons[0].op.kernel.kind == "relu" \
+                    and cons[0].op.kernel.conf.activation_mode == ActivationMode.RELU and cons[0].op.kernel.conf.negative_slope == 0:
+                info[id(n)]["relu"] = cons[0]
+                info[id(cons[0])]["fused_into"] = n
+            if k.kind == "batchnorm":
+                if len(cons) == 1 and cons[0].op.kernel.kind == "relu" and cons[0].op.kernel.conf.negative_slope == 0 \
+                        and cons[0].op.kernel.conf.activation_mode == ActivationMode.RELU:
+                    info[id(n)]["relu"] = cons[0]
+                    info[id(cons[0])]["fused_into"] = n
+                elif len(cons) == 1 and cons[0].op.kernel.kind == "elementwise" and len(self._inputs(cons[0])) == 2 \
+                        and cons[0].op.kernel.conf.type == ElementWiseOpType.SUM \
+                        and all(cons[0].op.kernel.conf.getCoefficient(i) == 1.0 for i in range(2)) \
+                        and info[id(cons[0])]["carrier"] is None and not getattr(cons[0].op.kernel, "is_gradient_merge", False):
+                    s = cons[0]
+                    info[id(n)]["deferred"] = True
+                    info[id(s)]["carrier"] = n
+                    sc = self._consumers(s)
+                    if len(sc) == 1 and sc[0].op.kernel.kind == "relu" and sc[0].op.kernel.conf.negative_slope == 0 \
+                            and sc[0].op.kernel.conf.activation_mode == ActivationMode.RELU:
+                        info[id(s)]["relu"] = sc[0]
+                        info[id(sc[0])]["fused_into"] = s
+        # conv epilogue statistics: producer (after optional fused relu) feeds exactly one BN, training mode
+        if self.training:
+            for n in fwd:
+                if n.op.kernel.kind != "batchnorm":
+                    continue
+                src = self._inputs(n)[0]
+                prod = info[id(src)]["fused_into"] or src
+                if prod.op.kernel.kind == "conv" and len(self._consumers(src)) == 1:
+                    info[id(n)]["stats_from"] = prod
+
+    def out_tensor(self, node) -> T:
+        return self.tensors[id(node)]
+
+    def _forward(self, n, x_in):
+        k, info = n.op.kernel, self.node_info[id(n)]
+        ins_nodes = self._inputs(n)
+        ins = [self.out_tensor(p) for p in ins_nodes] if ins_nodes else [x_in]
+        kind = k.kind
+        P = self.params_dev
+        if info["fused_into"] is not None:           # ReLU folded into its producer
+            self.tensors[id(n)] = self.out_tensor(info["fused_into"])
+            return
+        if kind == "datatransform":
+            c, h, w = self.input_chw
+            oh, ow = n.op.output_shape.dims[2], n.op.output_shape.dims[3]
+            out = self.new_tensor(self.batch, oh, ow, c, "transform")
+            conf = k.conf
+            mean, mode = None, 0
+            if conf.subtract_mean and conf.mean_pixel_values:
+                mean, mode = torch.tensor(conf.mean_pixel_values, dtype=torch.float32, device=self.device), 1
+            elif conf.subtract_mean and conf.mean_image_filename:
+                mean, mode = torch.from_numpy(np.fromfile(conf.mean_image_filename, dtype=np.float32)).to(self.device), 2
+            self.keep.append(mean)
+            self.emit(_op(L.OP_TRANSFORM, ia=[self.batch, c, h, w, oh, ow, int(bool(conf.mirror)), int(self.training), mode, n.op.uid],
+                          fa=[conf.scale_factor], p=[self.examples, out.buf, mean, P]))
+            self.tensors[id(n)] = out
+            return
+        x = ins[0]
+        if kind in ("conv", "innerproduct"):
+            if kind == "conv":
+                conf = k.conf
+                K = conf.number_of_outputs
+                geom = [x.n, x.h, x.w, x.c, K, conf.kernel_height, conf.kernel_width, n.op.output_shape.dims[2],
+                        n.op.output_shape.dims[3], conf.stride_height, conf.stride_width, conf.padding_height, conf.padding_width]
+                out = self.new_tensor(x.n, geom[7], geom[8], K, n.op.name)
+            else:
+                K = k.conf.number_of_outputs
+                geom = [x.n, 1, 1, x.h * x.w * x.c, K, 1, 1, 1, 1, 1, 1, 0, 0]
+                out = self.new_tensor(x.n, 1, 1, K, n.op.name)
+            out.needs_grad = True
+            wv = k.variables[0]
+            bias = self.wptr(k.variables[1]) if len(k.variables) > 1 else 0
+            flags = L.F_TC if self.use_tc else 0
+            if info["relu"] is not None:
+                flags |= L.F_RELU
+            stats = None
+            # does a BN take its statistics from this convolution?
+            for m in self.fwd:
+                if self.node_info[id(m)].get("stats_from") is n:
+                    stats = self.scratch_zeroed(2 * K)
+                    self.node_info[id(m)]["stats_buf"] = stats
+                    flags |= L.F_STATS
+            info["geom"] = geom
+            self.emit(_op(L.OP_CONV_FPROP, flags, ia=geom, p=[x.buf, self.wptr(wv), bias, out.buf, stats]))
+            self.tensors[id(n)] = out
+            return
+        if kind == "batchnorm":
+            if info["stats_from"] is None and self.training:
+                info["stats_buf"] = self.scratch_zeroed(2 * x.c)
+                self.emit(_op(L.OP_BN_STATS, ia=[x.rows, x.c], p=[x.buf, info["stats_buf"]]))
+            if info["deferred"]:
+                self.tensors[id(n)] = None   # materialised by the sum node
+                return
+            self._emit_bn(n, x, None, info["relu"] is not None)
+            return
+        if kind == "elementwise":
+            carrier = info["carrier"]
+            if carrier is not None:
+                other = [p for p in ins_nodes if p is not carrier][0]
+                bn_in = self.out_tensor(self._inputs(carrier)[0])
+                res = self.out_tensor(other)
+                info["res"] = other
+                out = self._emit_bn(carrier, bn_in, res, info["relu"] is not None, at=n)
+                return
+            out = self.new_tensor(x.n, x.h, x.w, x.c, n.op.name)
+            out.needs_grad = any(t.needs_grad for t in ins)
+            if k.conf.type != ElementWiseOpType.SUM:
+                raise NotImplementedError("error: only SUM element-wise operators run on the GPU (as in the reference)")
+            coefs = [k.conf.getCoefficient(i) for i in range(len(ins))]
+            for base in range(0, len(ins), 4):
+                part = ins[base:base + 4]
+                self.emit(_op(L.OP_SUM, ia=[len(part), int(base > 0)], fa=coefs[base:base + 4], la=[x.numel],
+                              p=[(part[i].buf if i < len(part) else None) for i in range(4)] + [out.buf]))
+            self.tensors[id(n)] = out
+            return
+        if kind == "relu":
+            out = self.new_tensor(x.n, x.h, x.w, x.c, n.op.name)
+            out.needs_grad = x.needs_grad
+            conf = k.conf
+            self.emit(_op(L.OP_ACT_FWD, ia=[int(conf.activation_mode)], fa=[conf.negative_slope, conf.ceiling], la=[x.numel], p=[x.buf, out.buf]))
+            self.tensors[id(n)] = out
+            return
+        if kind == "pool":
+            conf = k.conf
+            oh, ow = n.op.output_shape.dims[2], n.op.output_shape.dims[3]
+            out = self.new_tensor(x.n, oh, ow, x.c, n.op.name)
+            out.needs_grad = x.needs_grad
+            geom = [x.n, x.h, x.w, x.c, oh, ow, conf.kernel_height, conf.kernel_width, conf.stride_height, conf.stride_width,
+                    conf.padding_height, conf.padding_width]
+            info["geom"] = geom
+            self.emit(_op(L.OP_POOL_FWD, int(conf.method == PoolMethod.AVERAGE), ia=geom, p=[x.buf, out.buf]))
+            self.tensors[id(n)] = out
+            return
+        if kind == "dropout":
+            if not self.training:
+                self.tensors[id(n)] = x
+                return
+            out = self.new_tensor(x.n, x.h, x.w, x.c, n.op.name)
+            out.needs_grad = x.needs_grad
+            self.emit(_op(L.OP_DROPOUT, ia=[n.op.uid, 0], fa=[k.conf.ratio], la=[x.numel], p=[x.buf, out.buf, P]))
+            self.tensors[id(n)] = out
+            return
+        if kind == "concat":
+            ct = sum(t.c for t in ins)
+            out = self.new_tensor(x.n, x.h, x.w, ct, n.op.name)
+            out.needs_grad = any(t.needs_grad for t in ins)
+            off = 0
+            for t in ins:
+                self.emit(_op(L.OP_CONCAT, ia=[t.c, ct, off, 1, 0], la=[t.rows], p=[t.buf, out.buf]))
+                off += t.c
+            self.tensors[id(n)] = out
+            return
+        if kind == "lrn":
+            out = self.new_tensor(x.n, x.h, x.w, x.c, n.op.name)
+            out.needs_grad = x.needs_grad
+            info["scale"] = self.arena.alloc(x.numel)
+            c = k.conf
+            self.emit(_op(L.OP_LRN_FWD, ia=[x.c, c.local_size], fa=[c.alpha, c.beta, c.k], la=[x.rows], p=[x.buf, out.buf, info["scale"]]))
+            self.tensors[id(n)] = out
+            return
+        if kind == "softmax":
+            probs = self.new_tensor(x.n, 1, 1, x.numel // x.n, "probs")
+            self.logits, self.probs = x, probs
+            cons = self._consumers(n)
+            loss = next((m for m in cons if m.op.kernel.kind == "softmaxloss"), None)
+            want_grad = self.has_backward and loss is not None and x.needs_grad
+            dl = None
+            if want_grad:
+                dl, _ = self.gout(x)
+            lconf = loss.op.kernel.conf if loss is not None else None
+            mode = 0 if lconf is None or lconf.mode in (NormalisationMode.BATCH, NormalisationMode.FULL) else \
+                (1 if lconf.mode == NormalisationMode.VALID else 2)
+            ignore = lconf.ignored_label_value if lconf is not None else -1
+            self.emit(_op(L.OP_SOFTMAX_XENT, ia=[x.n, x.numel // x.n, ignore, mode], p=[x.buf, self.labels, probs.buf, dl, self.result_ptr]))
+            self.tensors[id(n)] = probs
+            return
+        if kind in ("softmaxloss", "accuracy"):
+            self.tensors[id(n)] = None
+            return
+        if kind == "classify":
+            out = self.new_tensor(x.n, 1, 1, 1, "classes")
+            self.emit(_op(L.OP_CLASSIFY, ia=[x.n, x.numel // x.n], p=[x.buf, out.buf]))
+            self.tensors[id(n)] = out
+            return
+        if kind == "noop":
+            self.tensors[id(n)] = x
+            return
+        raise NotImplementedError(f"error: operator kind {kind} has no device lowering")
+
+    def _emit_bn(self, bn_node, x: T, res: Optional[T], relu: bool, at=None) -> T:
+        k, info = bn_node.op.kernel, self.node_info[id(bn_node)]
+        conf = k.conf
+        out = self.new_tensor(x.n, x.h, x.w, x.c, bn_node.op.name)
+        out.needs_grad = True
+        rm, rv = self.shared.running(bn_node.op.uid, x.c)
+        sm = self.arena.alloc(x.c)
+        si = self.arena.alloc(x.c)
+        info.update(save_mean=sm, save_invstd=si, x=x, res=res, relu_fused=relu, out=out)
+        cma = int(conf.estimated_mean_and_variance_type == BatchNormEstimatedMeanAndVarianceType.CMA)
+        self.emit(_op(L.OP_BN_FWD, ia=[x.rows, x.c, int(relu), int(self.training), cma], fa=[k.epsilon(), 1.0 - float(conf.fraction)],
+                      p=[x.buf, res.buf if res is not None else None, out.buf, info.get("stats_buf"), self.wptr(k.variables[0]),
+                         self.wptr(k.variables[1]), rm, rv, sm, si, self.params_dev]))
+        self.tensors[id(at if at is not None else bn_node)] = out
+        if at is not None:
+            self.tensors[id(bn_node)] = None
+        return out
+
+    # ---- backward ----
+    def _backward(self, fwd, differentiated):
+        rep = self.replica
+        self.transposes = []
+        for n in reversed(fwd):
+            k, info = n.op.kernel, self.node_info[id(n)]
+            kind = k.kind
+            if info["fused_into"] is not None or kind in ("softmax", "softmaxloss", "accuracy", "classify", "datatransform", "noop"):
+                continue
+            if kind == "batchnorm" and info["deferred"]:
+                continue          # handled at its sum node
+            active = n.op.uid in differentiated or (kind == "elementwise" and info["carrier"] is not None
+                                                    and info["carrier"].op.uid in differentiated)
+            if not active:
+                continue
+            ins_nodes = self._inputs(n)
+            out = self.tensors.get(id(n))
+            if out is None or out.grad is None or not out.grad_written:
+                continue          # nothing flows back through this node
+            dy = out.grad
+            if kind in ("conv", "innerproduct"):
+                x = self.out_tensor(ins_nodes[0]) if ins_nodes else self.x_in
+                geom = info["geom"]
+                if info["relu"] is not None:   # mask by the fused ReLU, in place
+                    self.emit(_op(L.OP_ACT_BWD, ia=[1, 0], fa=[0.0, 0.0], la=[out.numel], p=[dy, out.buf, out.buf, dy]))
+                wv = k.variables[0]
+                tc = L.F_TC if self.use_tc else 0
+                self.emit(_op(L.OP_CONV_WGRAD, tc, ia=geom, p=[dy, x.buf, self.wptr(wv, rep.g)]))
+                if len(k.variables) > 1:
+                    self.emit(_op(L.OP_COLSUM, ia=[out.rows, out.c], p=[dy, self.wptr(k.variables[1], rep.g)]))
+                if x.needs_grad:
+                    gx, acc = self.gout(x)
+                    K, R, S, Cc = geom[4], geom[5], geom[6], geom[3]
+                    self.transposes.append((wv.doffset, K, R * S, Cc))
+                    self.emit(_op(L.OP_CONV_DGRAD, tc | acc, ia=geom, p=[dy, rep.wt.data_ptr() + 4 * wv.doffset, gx]))
+                continue
+            if kind == "batchnorm" or (kind == "elementwise" and info["carrier"] is not None):
+                bn = n if kind == "batchnorm" else info["carrier"]
+                bi = self.node_info[id(bn)]
+                bk = bn.op.kernel
+                x, res, relu = bi["x"], bi["res"], bi["relu_fused"]
+                dsums = self.scratch_zeroed(2 * x.c)
+                gx, accx = self.gout(x)
+                gres, accr = (None, 0)
+                if res is not None and res.needs_grad:
+                    gres, accr = self.gout(res)
+                self.emit(_op(L.OP_BN_BWD, ia=[x.rows, x.c, int(relu), accx, accr],
+                              p=[dy, x.buf, out.buf, bi["save_mean"], bi["save_invstd"], self.wptr(bk.variables[0]), dsums, gx, gres,
+                                 self.wptr(bk.variables[0], rep.g), self.wptr(bk.variables[1], rep.g)]))
+                continue
+            x = self.out_tensor(ins_nodes[0])
+            if kind == "elementwise":
+                for i, p in enumerate(ins_nodes):
+                    t = self.out_tensor(p)
+                    if not t.needs_grad:
+                        continue
+                    gx, acc = self.gout(t)
+                    self.emit(_op(L.OP_SUM, ia=[1, acc], fa=[k.conf.getCoefficient(i)], la=[t.numel], p=[dy, None, None, None, gx]))
+                continue
+            if not x.needs_grad:
+                continue
+            if kind == "relu":
+                gx, acc = self.gout(x)
+                conf = k.conf
+                self.emit(_op(L.OP_ACT_BWD, ia=[int(conf.activation_mode), acc], fa=[conf.negative_slope, conf.ceiling], la=[x.numel],
+                              p=[dy, x.buf, out.buf, gx]))
+            elif kind == "pool":
+                gx, acc = self.gout(x)
+                avg = int(k.conf.method == PoolMethod.AVERAGE)
+                self.emit(_op(L.OP_POOL_BWD, avg | (acc << 1), ia=info["geom"], p=[dy, x.buf, gx]))
+            elif kind == "dropout":
+                gx, acc = self.gout(x)
+                self.emit(_op(L.OP_DROPOUT, ia=[n.op.uid, acc], fa=[k.conf.ratio], la=[x.numel], p=[dy, gx, self.params_dev]))
+            elif kind == "concat":
+                off = 0
+                for p in ins_nodes:
+                    t = self.out_tensor(p)
+                    if t.needs_grad:
+                        gx, acc = self.gout(t)
+                        self.emit(_op(L.OP_CONCAT, ia=[t.c, out.c, off, 0, acc], la=[t.rows], p=[dy, gx]))
+                    off += t.c
+            elif kind == "lrn":
+                gx, acc = self.gout(x)
+                c = k.conf
+                self.emit(_op(L.OP_LRN_BWD, ia=[x.c, c.local_size, acc], fa=[c.alpha, c.beta], la=[x.rows], p=[dy, x.buf, out.buf, info["scale"], gx]))
+            else:
+                raise NotImplementedError(f"error: no backward lowering for {kind}")
+
+    def _finish_transposes(self, slot):
+        if not self.transposes:
+            self.ops[slot] = _op(L.OP_MEMSET, la=[0], p=[self.params_dev])
+            return
+        descs = (L.XbTransposeDesc * len(self.transposes))()
+        blocks = 0
+        for i, (off, K, RS, Cc) in enumerate(self.transposes):
+            descs[i].src_off, descs[i].dst_off, descs[i].K, descs[i].RS, descs[i].C = off, off, K, RS, Cc
+            descs[i].first_block = blocks
+            blocks += (K * RS * Cc + 255) // 256
+        raw = torch.frombuffer(bytearray(bytes(descs)), dtype=torch.uint8).to(self.device)
+        self.keep.append(raw)
+        self.ops[slot] = _op(L.OP_TRANSPOSE_W, ia=[len(self.transposes), blocks], p=[self.weights, self.replica.wt, raw])
+
+    def _optimiser(self):
+        rep, sh = self.replica, self.shared
+        mode = {UpdateModel.WORKER: 2, UpdateModel.DEFAULT: 1}.get(self.update_model, 0)
+        target = sh.gacc if mode == 2 else (sh.z if mode == 1 else None)
+        norm2 = None
+        if self.clip:
+            norm2 = self.arena.alloc(1, zero=True)
+            self.emit(_op(L.OP_GRAD_SUMSQ, la=[rep.n], p=[rep.g, norm2]))
+        self.emit(_op(L.OP_OPTIMISER, ia=[mode], la=[rep.n], p=[rep.w, rep.g, rep.last, rep.prev, target, self.lr_mult, norm2, self.params_dev]))
+
+    def op_array(self):
+        arr = (L.XbOp * len(self.ops))(*self.ops)
+        return arr

@@ -26,6 +26,9 @@ from .conf import InitialiserConf
 from .types import InitialiserType, VarianceNormalisation
 
 
+DEVICE_ALIGN = 64   # floats; keeps every variable 256-byte aligned for 16-byte vector loads and bulk copies
+
+
 class Shape:
     """N-d extent with the reference's accessor names (model/Shape.java)."""
 
@@ -107,7 +110,8 @@ class Variable:
         self.learnable = learnable
         self.initialiser: InitialiserConf = InitialiserConf()
         self.lr_multiplier = 1.0
-        self.offset = -1            # element offset in the flat vector
+        self.offset = -1            # element offset in the packed (canonical / checkpoint) flat vector
+        self.doffset = -1           # element offset in the device flat vector (every variable 256-byte aligned)
         self.op_id = -1
         self.order = 0              # 1 = weights, 2 = bias (Model.java linked-list order)
         # canonical -> device element order: reshape to view_shape, permute by device_perm, flatten
@@ -174,6 +178,7 @@ class Model:
         self.variables: List[Variable] = []
         self._final = False
         self.elements = 0
+        self.device_elements = 0
 
     def register(self, op_id: int, var: Variable, order: int):
         if self._final:
@@ -189,6 +194,11 @@ class Model:
             v.offset = off
             off += v.elements()
         self.elements = off
+        doff = 0
+        for v in self.variables:
+            v.doffset = doff
+            doff += (v.elements() + DEVICE_ALIGN - 1) // DEVICE_ALIGN * DEVICE_ALIGN
+        self.device_elements = doff
         self._final = True
         return self
 
@@ -216,19 +226,18 @@ class Model:
         return any(v.lr_multiplier != 1.0 for v in self.variables)
 
     def to_device(self, flat) -> np.ndarray:
+        """Packed canonical vector -> padded channels-last device vector (padding is zero and stays zero)."""
         flat = np.asarray(flat, dtype=np.float32)
-        out = np.empty_like(flat)
+        out = np.zeros(self.device_elements, dtype=np.float32)
         for v in self.variables:
-            s = slice(v.offset, v.offset + v.elements())
-            out[s] = v.to_device(flat[s])
+            out[v.doffset:v.doffset + v.elements()] = v.to_device(flat[v.offset:v.offset + v.elements()])
         return out
 
-    def to_canonical(self, flat) -> np.ndarray:
-        flat = np.asarray(flat, dtype=np.float32)
-        out = np.empty_like(flat)
+    def to_canonical(self, dflat) -> np.ndarray:
+        dflat = np.asarray(dflat, dtype=np.float32)
+        out = np.empty(self.elements, dtype=np.float32)
         for v in self.variables:
-            s = slice(v.offset, v.offset + v.elements())
-            out[s] = v.to_canonical(flat[s])
+            out[v.offset:v.offset + v.elements()] = v.to_canonical(dflat[v.doffset:v.doffset + v.elements()])
         return out
 
     def dump(self) -> str:

@@ -81,7 +81,7 @@ def resnet_imagenet(layers=50, solver_conf=None, classes=1000, size=224):
     n.conv("Conv", 64, 7, 2, 3)
     n.bn("BatchNorm")
     n.relu("ReLU")
-    x = n.pool("Pool", PoolMethod.MAX, 3, 2, 1)
+    x = n.pool("Pool", PoolMethod.MAX, 3, 2, 0)   # ceil-mode extent: 112 -> 56, as in the reference (ResNetv1.java:548-556)
     cin = 64
     for stage, (feat, count) in enumerate(zip((64, 128, 256, 512), units), 1):
         for unit in range(1, count + 1):

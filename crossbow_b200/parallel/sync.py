@@ -1,0 +1,143 @@
+"""Model synchronisation back ends.
+
+``FusedSynchroniser``     - the product: one persistent sm_100a kernel per GPU per clock (csrc/kernels/sync.cu) that
+                            reduces the replicas, exchanges partial sums through peer-mapped memory over NVLink,
+                            updates the central average model and corrects / overwrites the replicas.
+``ReferenceSynchroniser`` - the bar: the reference's sequence restated step by step - per-replica difference / axpy
+                            kernels, ``all_reduce`` (NCCL), central update, per-replica correction
+                            (clib-multigpu/synch/sma.c:13-231, synch/common.c:3-57, synch/synchronoussgd.c:13-110).
+Both implement ``synchronise(algo, ...)`` over the same flat device vectors and are interchangeable.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+
+from ..ops import lib as L
+from ..types import UpdateModel
+from .peer import PeerBuffer
+
+ALGO_SMA, ALGO_SSGD, ALGO_POLYAK = 0, 1, 2
+
+
+class SyncTimeout(RuntimeError):
+    """A bounded device-side wait on a peer expired (the peer is late, gone, or never joined)."""
+
+
+class FusedSynchroniser:
+    def __init__(self, n: int, rank: int = 0, world: int = 1, two_shot: Optional[bool] = None, timeout_s: float = 5.0,
+                 max_blocks: int = 0, group=None):
+        lib = L.load()
+        self.lib, self.n, self.rank, self.world = lib, n, rank, world
+        if n % 4:
+            raise ValueError("flat vector length must be a multiple of 4")
+        self.two_shot = bool(two_shot) if two_shot is not None else (n * 4 >= (8 << 20))
+        self.timeout_s, self.max_blocks = timeout_s, max_blocks
+        self.epoch = 0
+        self.args_dev = lib.xb_device_alloc(lib.xb_sync_args_size())
+        self.args_size = (lib.xb_sync_args_size() + 255) // 256 * 256
+        self.args_pinned = lib.xb_pinned_alloc(8 * self.args_size)    # ring: an upload may still be pending when the next is built
+        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.inbox = self.result = self.flags = None
+        if world > 1:
+            self.inbox = PeerBuffer(4 * lib.xb_sync_inbox_floats(n, world, int(self.two_shot)), rank, world, group)
+            self.result = PeerBuffer(4 * lib.xb_sync_result_floats(n) if self.two_shot else 256, rank, world, group)
+            self.flags = PeerBuffer(4 * lib.xb_sync_flag_words(n, world), rank, world, group)
+
+    def descriptor(self, algo, replicas_w, replicas_prev, z, zlast, gacc, alpha, mu, scale, blend, copy, use_prev) -> L.XbSyncDesc:
+        d = L.XbSyncDesc()
+        d.rank, d.G, d.k, d.algo, d.n = self.rank, self.world, len(replicas_w), algo, self.n
+        d.epoch = self.epoch
+        d.two_shot, d.copy_to_replicas, d.use_prev = int(self.two_shot), int(copy), int(use_prev)
+        d.alpha, d.mu, d.scale, d.blend = alpha, mu, scale, blend
+        for i, w in enumerate(replicas_w):
+            d.w[i] = w.data_ptr()
+            d.prev[i] = replicas_prev[i].data_ptr() if replicas_prev is not None else w.data_ptr()
+        d.z, d.zlast = z.data_ptr(), zlast.data_ptr()
+        d.gacc = gacc.data_ptr() if gacc is not None else 0
+        if self.world > 1:
+            for g in range(self.world):
+                d.inbox[g], d.result[g], d.flags[g] = self.inbox.ptrs[g], self.result.ptrs[g], self.flags.ptrs[g]
+        d.status = self.status.data_ptr()
+        d.timeout_s = self.timeout_s
+        return d
+
+    def synchronise(self, stream: int, algo: int, replicas_w: List[torch.Tensor], replicas_prev: Optional[List[torch.Tensor]],
+                    z, zlast, gacc=None, alpha=0.0, mu=0.0, scale=1.0, blend=0.0, copy=False, use_prev=True):
+        """Enqueue one synchronisation on ``stream`` (a raw cudaStream_t). Asynchronous; see ``check``."""
+        self.epoch += 1
+        d = self.descriptor(algo, replicas_w, replicas_prev, z, zlast, gacc, alpha, mu, scale, blend, copy, use_prev)
+        staging = self.args_pinned + (self.epoch % 8) * self.args_size
+        L.check(self.lib.xb_fused_sync(C.byref(d), self.args_dev, staging, self.max_blocks, stream), "fused sync")
+
+    def check(self):
+        """Host-side check of the device status word (call after the stream has been synchronised)."""
+        s = int(self.status.item())
+        if s != 0:
+            self.status.zero_()
+            raise SyncTimeout(f"fused synchronisation gave up waiting for a peer (status {s}, epoch {self.epoch})")
+
+    def close(self):
+        for b in (self.inbox, self.result, self.flags):
+            if b is not None:
+                b.close()
+        self.lib.xb_device_free(self.args_dev)
+        self.lib.xb_pinned_free(self.args_pinned)
+
+
+class ReferenceSynchroniser:
+    """Reference-style synchronisation with separate element-wise kernels (torch ops on the flat vectors) and a
+    library all-reduce.  Used as the measured baseline and as a second implementation in tests."""
+
+    def __init__(self, n: int, rank: int = 0, world: int = 1, group=None):
+        self.n, self.rank, self.world, self.group = n, rank, world, group
+        self.D = torch.zeros(n, device="cuda")
+        self.G = torch.zeros(n, device="cuda")
+
+    def _allreduce(self, t):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=self.group)
+
+    def synchronise(self, stream, algo, replicas_w, replicas_prev, z, zlast, gacc=None, alpha=0.0, mu=0.0, scale=1.0,
+                    blend=0.0, copy=False, use_prev=True):
+        s = torch.cuda.ExternalStream(stream) if isinstance(stream, int) and stream else torch.cuda.current_stream()
+        with torch.cuda.stream(s):
+            if algo == ALGO_SMA:
+                self.G.zero_()
+                for i, w in enumerate(replicas_w):
+                    src = replicas_prev[i] if use_prev else w
+                    torch.sub(src, z, out=self.D)            # D = r.diff - z
+                    w.add_(self.D, alpha=-alpha)             # r -= alpha*D
+                    self.G.add_(self.D, alpha=alpha)         # G += alpha*D
+                self._allreduce(self.G)
+                tot = self.G
+            elif algo == ALGO_SSGD:
+                self._allreduce(gacc)
+                tot = gacc.mul(scale)
+                gacc.zero_()
+            else:
+                self.G.zero_()
+                for w in replicas_w:
+                    self.G.add_(w)
+                self._allreduce(self.G)
+                z.add_(self.G.mul(scale).sub_(z), alpha=blend)
+                if alpha > 0:
+                    for w in replicas_w:
+                        w.sub_((w - z).mul_(alpha))
+                return
+            if mu > 0:
+                tot = tot.add(zlast, alpha=mu)
+                zlast.copy_(tot)
+            z.add_(tot)
+            if copy or algo == ALGO_SSGD:
+                for w in replicas_w:
+                    w.copy_(z)
+
+    def check(self):
+        pass
+
+    def close(self):
+        pass

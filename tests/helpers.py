@@ -1,0 +1,41 @@
+"""Shared helpers: build a model + engines with identical initial weights and data."""
+import numpy as np
+import torch
+
+from crossbow_b200 import Dataflow, Model, ModelConf, Phase, Shape, SolverConf, SystemConf, UpdateModel
+from crossbow_b200.models import build
+
+
+def make_solver(lr=0.05, momentum=0.9, wd=1e-4, alpha=0.1):
+    return SolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(lr).setMomentum(momentum) \
+        .setWeightDecay(wd).setAlpha(alpha)
+
+
+def build_model(name, batch, solver=None, **kw):
+    solver = solver or make_solver()
+    spec = build(name, solver_conf=solver, **kw)
+    m = Model()
+    ishape = Shape([batch] + spec.input_shape)
+    nid = spec.train.init(ishape, Shape([batch]), m)
+    m.finalise()
+    spec.test.init(ishape, Shape([batch]), m, nid)
+    return spec, m, solver
+
+
+def make_batches(spec, batch, n, seed=0):
+    g = np.random.default_rng(seed)
+    xs = [torch.from_numpy(g.standard_normal((batch, *spec.input_shape), dtype=np.float32)) for _ in range(n)]
+    ys = [torch.from_numpy(g.integers(0, spec.classes, size=batch, dtype=np.int32)) for _ in range(n)]
+    return xs, ys
+
+
+def engines(name, batch, k=1, update_model=UpdateModel.SMA, wpc=None, solver=None, use_graphs=True, use_tc=False, seed=7, **kw):
+    from crossbow_b200.engine import CpuEngine, GpuEngine
+    spec, m, solver = build_model(name, batch, solver, **kw)
+    init = m.initial_values(seed)
+    wpc = wpc or k
+    gpu = GpuEngine(spec.train, spec.test, m, init, batch, spec.input_shape, solver, update_model, replicas=k, wpc=wpc,
+                    use_graphs=use_graphs, use_tc=use_tc, seed=seed)
+    import copy
+    cpu = CpuEngine(spec.train, spec.test, m, init, batch, spec.input_shape, copy.deepcopy(solver), update_model, replicas=k, wpc=wpc, seed=seed)
+    return spec, m, gpu, cpu

@@ -1,0 +1,320 @@
+"""Host-only tests: configuration, CLI parsing, schedules, initialisers, graph construction, oracle, sync maths,
+checkpoint layout, clock / auto-tuner, counter-based RNG."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from crossbow_b200 import *  # noqa: F401,F403
+from crossbow_b200.autotune import AutoTuner
+from crossbow_b200.kernels import OpEnv, pool_output_size
+from crossbow_b200.models import build
+from crossbow_b200.oracle import (DeviceState, OracleExecutor, ReplicaState, local_update, synchronise_sma,
+                                  synchronise_ssgd, synchronise_polyak_ruppert, synchronise_eamsgd)
+from crossbow_b200.utils.philox import philox4x32, philox_uniform
+from crossbow_b200.workclock import WorkClock
+from helpers import build_model, make_batches, make_solver
+
+
+def test_philox_known_answers():
+    o = philox4x32([0], [0], [0], [0], 0, 0)
+    assert [int(x[0]) for x in o] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    o = philox4x32([0xFFFFFFFF] * 1, [0xFFFFFFFF], [0xFFFFFFFF], [0xFFFFFFFF], 0xFFFFFFFF, 0xFFFFFFFF)
+    assert [int(x[0]) for x in o] == [0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD]
+    u = philox_uniform(10001, 42, 3, 9)
+    assert u.min() >= 0 and u.max() < 1 and abs(u.mean() - 0.5) < 0.02
+    assert np.array_equal(u[:100], philox_uniform(100, 42, 3, 9))
+
+
+def test_system_and_model_conf_parse_all_flags():
+    s, m = SystemConf.reset(), ModelConf.reset()
+    flags = {"--gpu": "true", "--gpu-devices": "0,1,2,3", "--number-of-gpu-models": "4", "--synchronisation-model": "SSP",
+             "--autotune-models": "true", "--autotune-threshold": "0.2", "--task-queue-size": "64", "--random-seed": "7",
+             "--scheduling-policy": "FIFO", "--display-interval-unit": "epochs"}
+    for k, v in flags.items():
+        assert s.parse(k, v), k
+    assert s.gpu and s.gpu_devices == [0, 1, 2, 3] and s.number_of_gpu_models == 4
+    assert s.synchronisation_model == SynchronisationModel.SSP and s.autotune_threshold == 0.2
+    assert s.numberOfGPUs() == 4 and s.getNumberOfGpuModels() == 4
+    assert len(SystemConf.OPTIONS) >= 37
+    for k, v in {"--wpc": "8", "--slack": "1", "--batch-size": "64", "--update-model": "SMA", "--learning-rate": "0.1",
+                 "--momentum": "0.9", "--step-values": "80,120", "--learning-rate-decay-policy": "multistep", "--alpha": "0.1"}.items():
+        assert m.parse(k, v), k
+    assert m.wpc == 8 and m.update_model == UpdateModel.SMA and m.getSolverConf().step_values == [80, 120]
+    assert not m.parse("--no-such-flag", "1")
+
+
+def test_fluent_setters_match_reference_spelling():
+    c = ConvConf().setNumberOfOutputs(32).setKernelSize(2).setKernelHeight(5).setKernelWidth(5).setBias(False)
+    assert (c.number_of_outputs, c.kernel_height, c.kernel_width, c.bias) == (32, 5, 5, False)
+    p = PoolConf().setKernelSize(2).setStrideSize(2).setPaddingSize(0)
+    assert (p.kernel_height, p.stride_width) == (2, 2)
+    b = BatchNormConf().setEpsilon(1e-5).setMovingAverageFraction(0.9)
+    assert b.fraction == 0.9
+    i = InitialiserConf().setType(InitialiserType.GAUSSIAN).setStd(0.1).truncate(True)
+    assert i.type == InitialiserType.GAUSSIAN and i.truncated
+
+
+def test_learning_rate_schedules():
+    s = SolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.1)
+    assert s.learning_rate(5) == pytest.approx(0.1)
+    s = SolverConf().setLearningRateDecayPolicy("INV").setBaseLearningRate(0.1).setGamma(0.001).setPower(0.75)
+    assert s.learning_rate(9) == pytest.approx(0.1 * (1 + 0.001 * 10) ** -0.75)
+    s = SolverConf().setLearningRateDecayPolicy("STEP").setBaseLearningRate(1.0).setGamma(0.5).setStepSize(10)
+    assert s.learning_rate(8) == 1.0 and s.learning_rate(9) == 0.5 and s.learning_rate(19) == 0.25
+    s = SolverConf().setLearningRateDecayPolicy("EXP").setBaseLearningRate(1.0).setGamma(0.9)
+    assert s.learning_rate(1) == pytest.approx(0.81)
+    s = SolverConf().setLearningRateDecayPolicy("MULTISTEP").setBaseLearningRate(1.0).setGamma(0.1).setStepValues(3, 5)
+    rates = [s.learning_rate(t) for t in range(6)]
+    assert rates[:2] == [1.0, 1.0] and rates[2] == pytest.approx(0.1) and rates[4] == pytest.approx(0.01)
+    assert s.consume_copy_signal() and not s.consume_copy_signal()
+    s = SolverConf().setLearningRateDecayPolicy("LSR").setBaseLearningRate(1.0).setGamma(0.1).setStepValues(10).setWarmupSteps(4)
+    assert [s.learning_rate(t) for t in range(4)] == [0.0, 0.25, 0.5, 0.75] and s.learning_rate(4) == 1.0
+    s = SolverConf().setLearningRateDecayPolicy("MULTISTEP").setBaseLearningRate(1.0).setGamma(0.1).setStepValues(2)
+    s.step_unit = TrainingUnit.EPOCHS
+    s.set_tasks_per_epoch(10)
+    assert s.learning_rate(18) == 1.0 and s.learning_rate(19) == pytest.approx(0.1)
+
+
+def test_initialisers():
+    m = Model()
+    spec, m, _ = build_model("lenet", 4)
+    w = m.initial_values(123)
+    assert w.shape == (m.elements,) and np.isfinite(w).all()
+    conv = m.variables[0]
+    vals = w[conv.offset:conv.offset + conv.elements()]
+    assert abs(vals.std() - 0.1) < 0.03 and np.abs(vals).max() <= 0.2 + 1e-6        # truncated at 2 sigma
+    assert np.array_equal(w, m.initial_values(123)) and not np.array_equal(w, m.initial_values(124))
+    v = Variable("w", Shape([8, 4, 3, 3])).initialise(InitialiserConf().setType("XAVIER"))
+    from crossbow_b200.model import RandomGenerator
+    x = v.generate(RandomGenerator(1))
+    assert np.abs(x).max() <= math.sqrt(3.0 / 36) + 1e-6
+    v.initialise(InitialiserConf().setType("MSRA"))
+    assert abs(v.generate(RandomGenerator(1)).std() - math.sqrt(2.0 / 72)) < 0.03
+
+
+def test_device_layout_roundtrip():
+    spec, m, _ = build_model("lenet", 4)
+    w = m.initial_values(5)
+    d = m.to_device(w)
+    assert d.size == m.device_elements and m.device_elements % 64 == 0
+    assert all(v.doffset % 64 == 0 for v in m.variables)
+    assert np.array_equal(m.to_canonical(d), w)
+    conv = m.variables[0]
+    K, Cc, R, S = conv.shape.dims
+    a = w[conv.offset:conv.offset + conv.elements()].reshape(K, Cc, R, S)
+    b = d[conv.doffset:conv.doffset + conv.elements()].reshape(K, R, S, Cc)
+    assert np.array_equal(a.transpose(0, 2, 3, 1), b)
+
+
+def test_pool_ceil_mode_shapes():
+    assert pool_output_size(112, 3, 2, 0) == 56
+    assert pool_output_size(112, 3, 2, 1) == 57
+    assert pool_output_size(32, 2, 2, 0) == 16
+    assert pool_output_size(7, 3, 2, 1) == 4
+    assert pool_output_size(8, 7, 1, 0) == 2
+
+
+def test_graph_api_manual_gradient_chain():
+    """The reference's explicit style: forward chain, gradient nodes with peers, optimiser."""
+    ip = InnerProductConf().setNumberOfOutputs(10)
+    ip.setWeightInitialiser(InitialiserConf().setType("GAUSSIAN").setStd(0.1))
+    lc = LossConf()
+    n_ip = DataflowNode(Operator("InnerProduct", InnerProduct(ip)))
+    n_sm = DataflowNode(Operator("SoftMax", SoftMax(SoftMaxConf())))
+    n_loss = DataflowNode(Operator("Loss", SoftMaxLoss(lc)))
+    n_acc = DataflowNode(Operator("Accuracy", Accuracy(AccuracyConf())))
+    n_lg = DataflowNode(Operator("LossGradient", SoftMaxLossGradient(lc)).setPeer(n_loss.getOperator()))
+    n_ig = DataflowNode(Operator("InnerProductGradient", InnerProductGradient(ip)).setPeer(n_ip.getOperator()))
+    n_opt = DataflowNode(Operator("Optimiser", GradientDescentOptimiser(make_solver())))
+    n_ip.connectTo(n_sm).connectTo(n_loss)
+    n_sm.connectTo(n_acc)
+    n_loss.connectTo(n_lg).connectTo(n_ig).connectTo(n_opt)
+    g = SubGraph(n_ip)
+    m = Model()
+    g.init(Shape([4, 20, 1, 1]), Shape([4]), m)
+    m.finalise()
+    names = [n.op.name for n in g.order]
+    assert names.index("InnerProduct") < names.index("SoftMax") < names.index("Loss") < names.index("LossGradient") < names.index("Optimiser")
+    assert m.elements == 20 * 10 + 10
+    w = torch.from_numpy(m.initial_values(1))
+    x, y = torch.randn(4, 20, 1, 1), torch.tensor([1, 2, 3, 4], dtype=torch.int32)
+    grad = torch.zeros_like(w)
+    r = OracleExecutor(g, m).run(w, x, y, Phase.TRAIN, grad_out=grad)
+    wp = w.clone().requires_grad_(True)
+    logits = torch.nn.functional.linear(x.reshape(4, -1), wp[:200].reshape(10, 20), wp[200:])
+    loss = torch.nn.functional.cross_entropy(logits, y.long())
+    loss.backward()
+    assert r["loss"] == pytest.approx(float(loss), rel=1e-5)
+    assert torch.allclose(grad, wp.grad, atol=1e-6)
+    assert "digraph" in g.exportDot()
+    df = Dataflow(g).setPhase(Phase.TRAIN)
+    assert df.getPhase() == Phase.TRAIN and "InnerProduct" in df.dump()
+
+
+@pytest.mark.parametrize("name", ["resnet8", "mini-inception", "lenet-batchnorm"])
+def test_oracle_gradients_equal_monolithic_autograd(name):
+    spec, m, _ = build_model(name, 4)
+    w = torch.from_numpy(m.initial_values(1))
+    xs, ys = make_batches(spec, 4, 1)
+    grad = torch.zeros_like(w)
+    r = OracleExecutor(spec.train, m, seed=1).run(w, xs[0], ys[0], Phase.TRAIN, 0, {}, grad)
+    wp = w.clone().requires_grad_(True)
+    env = OpEnv(Phase.TRAIN, ys[0], 0, 1, {})
+    outs = {}
+    for node in spec.train.order:
+        k = node.op.kernel
+        if k.is_gradient or k.is_optimiser or getattr(k, "is_gradient_merge", False):
+            continue
+        ins = [outs[id(p)] for p in node.prev if not p.op.kernel.is_gradient] or [xs[0]]
+        params = [wp[v.offset:v.offset + v.elements()].reshape(v.shape.dims) for v in k.variables]
+        outs[id(node)] = k.forward(ins, params, env)
+        if k.is_loss:
+            loss = outs[id(node)]
+    loss.sum().backward()
+    assert r["loss"] == pytest.approx(float(loss.detach()), rel=1e-5)
+    assert torch.allclose(grad, wp.grad, atol=2e-6, rtol=1e-4)
+
+
+def test_test_graph_shares_operators_and_drops_dropout():
+    spec, m, _ = build_model("lenet", 4)
+    train_ops = {n.op.uid for n in spec.train.order}
+    assert all(n.op.uid in train_ops for n in spec.test.order)
+    assert not any(n.op.kernel.kind == "dropout" for n in spec.test.order)
+    assert any(n.op.kernel.kind == "accuracy" for n in spec.test.order)
+
+
+def _devs(G, k, n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    base = torch.randn(n, generator=g)
+    out = []
+    for _ in range(G):
+        d = DeviceState(base)
+        for _ in range(k):
+            r = ReplicaState(base + 0.1 * torch.randn(n, generator=g))
+            r.prev = r.w.clone()
+            d.replicas.append(r)
+        out.append(d)
+    return out
+
+
+def test_sma_keeps_devices_identical_and_moves_towards_mean():
+    devs = _devs(2, 2, 50)
+    mean_before = sum(r.w for d in devs for r in d.replicas) / 4
+    z_before = devs[0].z.clone()
+    synchronise_sma(devs, 0.25, 0.0)
+    assert torch.equal(devs[0].z, devs[1].z)
+    assert torch.allclose(devs[0].z, z_before + 0.25 * 4 * (mean_before - z_before), atol=1e-5)
+
+
+def test_sma_copy_on_rate_drop():
+    devs = _devs(1, 2, 10)
+    synchronise_sma(devs, 0.1, 0.9, copy=True)
+    assert all(torch.equal(r.w, devs[0].z) for r in devs[0].replicas)
+
+
+def test_ssgd_equals_large_batch_sgd():
+    n = 20
+    devs = _devs(2, 2, n)
+    s = make_solver(lr=0.1, momentum=0.0, wd=0.0)
+    grads = [torch.randn(n) for _ in range(4)]
+    z0 = devs[0].z.clone()
+    i = 0
+    for d in devs:
+        for r in d.replicas:
+            r.g = grads[i].clone()
+            local_update(r, d, s, UpdateModel.WORKER, 0)
+            i += 1
+    synchronise_ssgd(devs, 4, 0.0)
+    assert torch.allclose(devs[0].z, z0 - 0.1 * sum(grads) / 4, atol=1e-6)
+    assert all(torch.equal(r.w, d.z) for d in devs for r in d.replicas)
+
+
+def test_local_update_momentum_and_snapshot():
+    d = DeviceState(torch.ones(4))
+    r = ReplicaState(torch.ones(4))
+    s = make_solver(lr=0.5, momentum=0.9, wd=0.0)
+    r.g = torch.full((4,), 2.0)
+    local_update(r, d, s, UpdateModel.SMA, 0)
+    assert torch.allclose(r.prev, torch.ones(4)) and torch.allclose(r.w, torch.zeros(4)) and torch.allclose(r.last, -torch.ones(4))
+    r.g = torch.full((4,), 2.0)
+    local_update(r, d, s, UpdateModel.SMA, 1)
+    assert torch.allclose(r.w, torch.full((4,), -1.9))
+    s2 = make_solver(lr=1.0, momentum=0.0, wd=0.0).setClipGradientThreshold(1.0)
+    r2 = ReplicaState(torch.zeros(4))
+    r2.g = torch.full((4,), 3.0)
+    local_update(r2, d, s2, UpdateModel.SMA, 0)
+    assert torch.allclose(r2.w, torch.full((4,), -0.5))
+
+
+def test_polyak_and_eamsgd():
+    devs = _devs(1, 2, 8)
+    mean = sum(r.w for r in devs[0].replicas) / 2
+    synchronise_polyak_ruppert(devs)
+    assert torch.allclose(devs[0].z, mean)
+    devs = _devs(1, 2, 8)
+    w0 = [r.w.clone() for r in devs[0].replicas]
+    z0 = devs[0].z.clone()
+    synchronise_eamsgd(devs, 0.5)
+    assert torch.allclose(devs[0].replicas[0].w, w0[0] - 0.5 * (w0[0] - z0))
+
+
+def test_work_clock_and_autotuner():
+    c = WorkClock(3)
+    seen = []
+    for _ in range(7):
+        t = c.next_task()
+        if c.is_barrier():
+            c.tick()
+            seen.append(t)
+    assert seen == [2, 5] and c.clock == 2 and c.lower_bound(1) == 0
+    a = AutoTuner(0.1, 1)
+    assert a.decide([100.0]) == 1 and a.decide([100.0, 150.0]) == 1 and a.decide([150.0, 155.0]) == -1
+    assert a.decide([400.0]) == 0 and not a.active
+
+
+def test_cpu_context_trains_lenet_sma_and_checkpoints(tmp_path):
+    from crossbow_b200.context import ExecutionContext
+    from crossbow_b200.data import SyntheticDataset
+    SystemConf.reset().setNumberOfCpuModels(2).setDisplayInterval(0)
+    mc = ModelConf.reset()
+    sc = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.01).setMomentum(0.9).setAlpha(0.1)
+    mc.setBatchSize(16).setWpc(2).setUpdateModel("SMA")
+    ds = SyntheticDataset([1, 28, 28], 10, 16, batches=2, seed=1, distribution="uniform")
+    mc.setDataset(Phase.TRAIN, ds).setDataset(Phase.CHECK, ds)
+    spec = build("lenet-caffe", solver_conf=sc)
+    ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), Dataflow(spec.test).setPhase(Phase.CHECK)], quiet=True)
+    ctx.init()
+    ctx.train(16, "tasks")
+    losses = ctx.measurements.losses()
+    assert len(losses) == 16 and np.mean(losses[-4:]) < np.mean(losses[:4])
+    acc = ctx.test()
+    assert 0.0 <= acc <= 1.0
+    d = ctx.checkpoint(str(tmp_path))
+    files = sorted(os.listdir(d))
+    assert files == ["gpu-00-replica-000-data.dat", "gpu-00-replica-000-last.dat", "gpu-00-replica-001-data.dat",
+                     "gpu-00-replica-001-last.dat", "gpu-00-theModel-data.dat", "gpu-00-theModel-last.dat"]
+    assert os.path.getsize(os.path.join(d, files[4])) == 4 * ctx.model.elements
+    z = ctx.engine.central_model()
+    # resume into a fresh context
+    SystemConf.getInstance().setModelDirectory(str(tmp_path))
+    spec2 = build("lenet-caffe", solver_conf=sc)
+    ctx2 = ExecutionContext([Dataflow(spec2.train).setPhase(Phase.TRAIN), Dataflow(spec2.test).setPhase(Phase.CHECK)], quiet=True)
+    ctx2.init()
+    assert np.array_equal(ctx2.engine.central_model(), z)
+    assert np.array_equal(ctx2.engine.replica_model(1), ctx.engine.replica_model(1))
+
+
+def test_all_models_build_and_infer_shapes():
+    from crossbow_b200.models import REGISTRY
+    sizes = {"resnet18": 64, "resnet34": 64, "resnet50": 64, "resnet101": 64, "resnet152": 64, "alexnet": 224}
+    for name in REGISTRY:
+        kw = {"size": sizes[name]} if name in sizes else {}
+        spec, m, _ = build_model(name, 2, **kw)
+        assert m.elements > 0 and spec.train.getLossNode() is not None and spec.test.getAccuracyNode() is not None
+    spec, m, _ = build_model("resnet32", 2)
+    assert 460000 < m.elements < 470000
+    spec, m, _ = build_model("resnet50", 2, size=224)
+    assert 25.5e6 < m.elements < 25.7e6

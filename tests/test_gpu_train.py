@@ -1,0 +1,88 @@
+"""Device training against the CPU oracle, task by task: loss, accuracy, replica weights and the central model."""
+import numpy as np
+import pytest
+import torch
+
+from crossbow_b200 import Phase, UpdateModel
+from helpers import engines, make_batches
+
+pytestmark = pytest.mark.gpu
+
+
+def run_both(name, batch, k, tasks, update_model=UpdateModel.SMA, tol=2e-3, use_graphs=True, use_tc=False, **kw):
+    spec, m, gpu, cpu = engines(name, batch, k=k, update_model=update_model, use_graphs=use_graphs, use_tc=use_tc, **kw)
+    xs, ys = make_batches(spec, batch, tasks, seed=3)
+    pinned = [(x.pin_memory(), y.pin_memory()) for x, y in zip(xs, ys)]
+    try:
+        for t in range(tasks):
+            l = t % k
+            gpu.submit(l, pinned[t][0], pinned[t][1], t, Phase.TRAIN)
+            cpu.submit(l, xs[t], ys[t], t, Phase.TRAIN)
+            gl, ga = gpu.wait(l)
+            cl, ca = cpu.wait(l)
+            assert abs(gl - cl) <= tol * max(1.0, abs(cl)), f"task {t}: loss {gl} vs {cl}"
+            assert abs(ga - ca) <= 1.0 / batch + 1e-6, f"task {t}: accuracy {ga} vs {ca}"
+            if (t + 1) % k == 0:
+                gpu.synchronise()
+                cpu.synchronise()
+        gpu.finish()
+        for i in range(k):
+            a, b = gpu.replica_model(i), cpu.replica_model(i)
+            err = np.abs(a - b).max() / (np.abs(b).max() + 1e-12)
+            assert err < tol, f"replica {i}: rel err {err}"
+        a, b = gpu.central_model(), cpu.central_model()
+        assert np.abs(a - b).max() / (np.abs(b).max() + 1e-12) < tol
+        # test graph against the central model
+        gpu.submit(0, pinned[0][0], pinned[0][1], 0, Phase.CHECK)
+        cpu.submit(0, xs[0], ys[0], 0, Phase.CHECK)
+        assert abs(gpu.wait(0)[1] - cpu.wait(0)[1]) <= 1.0 / batch + 1e-6
+        gpu.finish()
+    finally:
+        gpu.destroy()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_lenet_sma(graphs):
+    run_both("lenet", 8, 2, 6, use_graphs=graphs)
+
+
+def test_lenet_caffe_default():
+    run_both("lenet-caffe", 16, 1, 3, update_model=UpdateModel.DEFAULT)
+
+
+def test_logistic_ssgd():
+    run_both("logistic-regression", 32, 2, 4, update_model=UpdateModel.WORKER)
+
+
+def test_resnet8_sma():
+    run_both("resnet8", 8, 2, 4)
+
+
+def test_resnet8_reference_pool():
+    run_both("resnet8", 4, 1, 2, reference_pool=True)
+
+
+def test_resnet20_transform():
+    run_both("resnet20", 4, 1, 2, transform=True)
+
+
+def test_mini_inception():
+    run_both("mini-inception", 4, 1, 2)
+
+
+def test_convnet_polyak():
+    run_both("convnet", 8, 2, 4, update_model=UpdateModel.POLYAK_RUPPERT)
+
+
+def test_lenet_batchnorm_eamsgd():
+    run_both("lenet-batchnorm", 8, 2, 4, update_model=UpdateModel.EAMSGD)
+
+
+def test_vgg_like_dropout():
+    # VGG-16 is the full Conv-ReLU-BN-Dropout pattern; two tasks are enough to cover every fused path
+    run_both("vgg16", 4, 1, 2, tol=5e-3)
+
+
+def test_bottleneck_resnet():
+    from crossbow_b200.models import REGISTRY
+    run_both("resnet50", 2, 1, 1, tol=5e-3, size=64, classes=10)
