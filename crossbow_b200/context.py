@@ -47,6 +47,7 @@ class ExecutionContext:
         self.test_accuracy = float("nan")
         self._next_learner = 0
         self._checkpoint_version = 0
+        self._native = self._native_test = None
 
     # ---- set-up ----
     def init(self):
@@ -94,7 +95,77 @@ class ExecutionContext:
         if sys.model_directory:
             from .checkpoint import load_checkpoint
             load_checkpoint(self, sys.model_directory)
+        self._native = self._native_test = None
+        if sys.gpu and sys.native_scheduler and sys.fused_sync and hasattr(ds, "examples"):
+            self._setup_native()
         return self
+
+    def _setup_native(self):
+        """Hand scheduling to the C++ runtime: dispatcher + handler threads call the CUDA executor directly."""
+        from .runtime import Runtime
+        sys, mc, e = self.sys, self.mc, self.engine
+        test_ds = mc.getDataset(Phase.CHECK) if self.dataflows[1] is not None else None
+        if test_ds is not None and not hasattr(test_ds, "examples"):
+            test_ds = None
+        ctx, sub, wait, sync, batch = e.native_executor(mc.getDataset(Phase.TRAIN), test_ds)
+        handlers = 0 if sys.direct_scheduling else max(0, sys.number_of_task_handlers - 1)
+        mk = lambda wpc: Runtime(learners=e.k, wpc=wpc, slack=mc.slack, sync_model=int(sys.synchronisation_model),
+                                 result_slots=sys.number_of_result_slots, task_handlers=handlers,
+                                 callback_handlers=max(1, sys.number_of_callback_handlers), task_timeout_s=sys.task_timeout)
+        self._native = mk(self.clock.wpc)
+        self._native.set_executor(sub, wait, sync, batch, ctx)
+        if test_ds is not None:
+            self._native_test = mk(1 << 30)          # test tasks never synchronise
+            self._native_test.set_executor(sub, wait, 0, batch, ctx)
+
+    def _train_native(self, ntasks: int) -> int:
+        rt, e = self._native, self.engine
+        chunk = ntasks
+        if self.autotuner is not None and self.autotuner.active:
+            chunk = max(self.clock.wpc, self.sys.autotune_interval * self.clock.wpc * 4)
+        done = 0
+        while done < ntasks:
+            n = min(chunk, ntasks - done)
+            t0 = time.perf_counter()
+            issued = rt.train(n, 0)
+            rt.drain(max(60.0, self.sys.task_timeout))
+            dt = time.perf_counter() - t0
+            done += issued
+            self.monitor.samples.append(issued * self.mc.batch_size / max(dt, 1e-9))
+            if issued < n:
+                break                                   # target loss reached
+            if self.autotuner is not None and self.autotuner.active:
+                delta = self.autotuner.decide(list(self.monitor.samples))
+                if delta > 0 and e.k < 16:
+                    e.add_learner()
+                    rt.add_learner()
+                    if self._native_test is not None:
+                        self._native_test.add_learner()
+                    if not self.quiet:
+                        print(f"[autotune] +1 replica -> {e.k}", flush=True)
+                elif delta < 0:
+                    rt.remove_learner()
+                    if self._native_test is not None:
+                        self._native_test.remove_learner()
+                    e.remove_learner()
+                    if not self.quiet:
+                        print(f"[autotune] -1 replica -> {e.k}; tuning stops", flush=True)
+            ci = self.sys.checkpoint_interval
+            if ci > 0 and self.sys.checkpoint_directory:
+                self.checkpoint()
+        hist = rt.history(min(max(done, 1), 65536))
+        for task, loss, acc in hist[-done:]:
+            self.measurements.add(task, loss, acc)
+            di = self.sys.display_interval
+            if not self.quiet and di > 0 and (task + 1) % di == 0:
+                print(f"[{task + 1:06d}] loss {loss:9.5f} accuracy {acc:7.4f} ({self.monitor.last_rate():9.1f} examples/s)", flush=True)
+        if hist:
+            self.last_loss, self.last_accuracy = hist[-1][1], hist[-1][2]
+        self.tasks_done += done
+        self.clock.clock = rt.clock()
+        self.clock.task = rt.tasks_issued() - 1
+        e.finish()
+        return done
 
     # ---- helpers ----
     def _learner_count(self):
@@ -121,6 +192,8 @@ class ExecutionContext:
             self._collect(l, inflight)
 
     def _train_tasks(self, ntasks: int):
+        if getattr(self, "_native", None) is not None:
+            return self._train_native(ntasks)
         e, mc, ds = self.engine, self.mc, self.mc.getDataset(Phase.TRAIN)
         inflight = {}
         solver = mc.getSolverConf()
@@ -171,6 +244,17 @@ class ExecutionContext:
         e, ds = self.engine, self.mc.getDataset(Phase.CHECK)
         if ds is None or self.dataflows[1] is None:
             raise ValueError("error: no test dataflow / data set")
+        if getattr(self, "_native_test", None) is not None:
+            rt = self._native_test
+            rt.totals(reset=True)
+            rt.train(ds.number_of_batches(), 1)
+            rt.drain(max(60.0, self.sys.task_timeout))
+            t = rt.totals()
+            e.finish()
+            self.test_accuracy = t["acc_sum"] / max(1, t["n"])
+            if not self.quiet:
+                print(f"[{self.clock.clock:06d}] Test accuracy is {self.test_accuracy:7.4f}", flush=True)
+            return self.test_accuracy
         accs, inflight = [], {}
         nl = self._learner_count()
         for t in range(ds.number_of_batches()):
@@ -236,6 +320,10 @@ class ExecutionContext:
         return save_checkpoint(self, directory or self.sys.checkpoint_directory)
 
     def destroy(self):
+        for rt in (getattr(self, "_native", None), getattr(self, "_native_test", None)):
+            if rt is not None:
+                rt.close()
+        self._native = self._native_test = None
         if self.engine is not None:
             self.engine.destroy()
             self.engine = None

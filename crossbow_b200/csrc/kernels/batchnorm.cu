@@ -234,8 +234,8 @@ __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
 
 inline int rows_per_block_for(int M, int C, int vec, int& blocks) {
   Tiling t = make_tiling(C, vec);
-  // aim for ~4 waves of 148 SMs at most, at least 8 row-steps per block
-  int min_rows = t.rows_per_iter * 8;
+  // aim for ~4 resident blocks per SM (592 blocks), at least 2 row-steps per block
+  int min_rows = t.rows_per_iter * 2;
   int rpb = xb_ceil_div(M, 592);
   if (rpb < min_rows) rpb = min_rows;
   rpb = xb_ceil_div(rpb, t.rows_per_iter) * t.rows_per_iter;

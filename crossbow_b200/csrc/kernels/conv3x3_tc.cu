@@ -1,0 +1,220 @@
+// 3x3 / stride 1 / pad 1 convolution (forward and data gradient) on tcgen05 without any im2col traffic.
+//
+// Idea: walk the output in a "padded position space" in which every image has one zero row on top (shared with the
+// image above: H+1 rows) and one zero column on each side (W+2 columns).  In that space the nine taps of a 3x3 filter
+// are nine CONSTANT shifts of one linear index: source = position + (r-1)*(W+2) + (s-1).  A CTA therefore stages one
+// contiguous slab of 128 + 2*(W+2) + 2 positions x C channels in shared memory ONCE, laid out as
+// [16-byte channel chunk][position][16 B], which is exactly the canonical K-major no-swizzle UMMA operand layout
+// (core matrix = 8 positions x 16 B).  The A operand of tap (r,s) is then the same slab with its descriptor start
+// address advanced by (r*(W+2)+s)*16 bytes: nine descriptors, one copy of the data, zero redundant global reads
+// (the gather formulation re-reads every input element nine times and spends ~700 instructions per thread per
+// reduction slice on address arithmetic).  The filter bank is staged once as [chunk][output channel][16 B].
+// One elected thread issues 9*C/8 tcgen05.mma (M128 x N x K8, tf32) into a TMEM accumulator and commits; the epilogue
+// drops the rows that fall on padding positions, adds bias / ReLU / accumulation, and produces the batch-norm sums.
+//
+// dgrad of such a convolution is the same computation over dY with the taps mirrored and the (C,R,S,K) weight copy.
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+using namespace tc;
+
+namespace {
+
+constexpr int BM = 128, NTHREADS = 128;
+constexpr int F_RELU = 1, F_ACCUM = 2, F_STATS = 4;
+
+struct SlabProblem {
+  int N, H, W, C, K;      // C = reduction channels, K = output channels (already swapped for dgrad)
+  int mirrored;           // 1: dgrad (tap (r,s) uses the weights of tap (2-r,2-s))
+  long long positions;    // N*(H+1)*(W+2)
+};
+
+template <int BN>
+__global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __restrict__ X, const float* __restrict__ Wb,
+                                                                const float* __restrict__ bias, float* __restrict__ Out,
+                                                                float* __restrict__ stats, SlabProblem g, int flags, int* status) {
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bar_done;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+  __shared__ float s_red[2 * BN];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int PW = g.W + 2, PR = g.H + 1;
+  const int S = BM + 2 * PW + 2;                      // slab length in positions
+  const int CQ = g.C >> 2;                            // 16-byte chunks per position
+  const uint32_t plane = (uint32_t)S * 16u;           // bytes per chunk plane of the slab
+  unsigned char* sSlab = smem;
+  unsigned char* sB = smem + (size_t)CQ * plane;      // [9*CQ chunks][BN rows][16 B]
+  const long long q0 = (long long)blockIdx.x * BM;
+  const long long qs = q0 - PW - 1;
+  const int n0 = blockIdx.y * BN;
+
+  if (tid == 0) {
+    mbar_init(&bar_done, 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);
+
+  // ---- stage the slab: one (position, chunk) = 16 bytes per copy, zero fill for padding positions ----
+  const uint32_t slab_u32 = smem_u32(sSlab);
+  for (int j = tid; j < S; j += NTHREADS) {
+    const long long p = qs + j;
+    const float* src = X;
+    uint32_t bytes = 0;
+    if (p >= 0 && p < g.positions) {
+      int xx = (int)(p % PW); long long t = p / PW; int yy = (int)(t % PR); int n = (int)(t / PR);
+      if (yy >= 1 && xx >= 1 && xx <= g.W) { src = X + (((long long)n * g.H + (yy - 1)) * g.W + (xx - 1)) * g.C; bytes = 16; }
+    }
+    for (int c = 0; c < CQ; ++c)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(slab_u32 + c * plane + j * 16), "l"(src + (bytes ? c * 4 : 0)), "r"(bytes) : "memory");
+  }
+  // ---- stage the filter bank: chunk index = tap*CQ + c ; row = output channel ----
+  const uint32_t b_u32 = smem_u32(sB);
+  const int KG = 9 * g.C;
+  for (int idx = tid; idx < 9 * CQ * BN; idx += NTHREADS) {
+    int row = idx % BN, chunk = idx / BN;
+    int tap = chunk / CQ, c = chunk - tap * CQ;
+    int wtap = g.mirrored ? (8 - tap) : tap;
+    int n = n0 + row;
+    const float* src = Wb;
+    uint32_t bytes = 0;
+    if (n < g.K) { src = Wb + (long long)n * KG + wtap * g.C + c * 4; bytes = 16; }
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(b_u32 + (chunk * BN + row) * 16), "l"(src), "r"(bytes) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+
+  if (tid == 0) {
+    const int k8s = g.C >> 3;
+    uint32_t acc = 0;
+    for (int tap = 0; tap < 9; ++tap) {
+      const int r = tap / 3, s = tap - 3 * r;
+      const uint32_t a_tap = slab_u32 + (uint32_t)(r * PW + s) * 16u;
+      for (int k8 = 0; k8 < k8s; ++k8) {
+        uint64_t ad = make_desc(a_tap + (uint32_t)(2 * k8) * plane, plane, 128);
+        uint64_t bd = make_desc(b_u32 + (uint32_t)((tap * CQ + 2 * k8) * BN) * 16u, BN * 16, 128);
+        umma_tf32(tmem, ad, bd, IDESC, acc);
+        acc = 1;
+      }
+    }
+    umma_commit(&bar_done);
+  }
+  if (!mbar_wait(&bar_done, 0)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
+  tc_fence_after();
+  if (flags & F_STATS) { for (int i = tid; i < 2 * BN; i += NTHREADS) s_red[i] = 0.f; }
+  __syncthreads();
+  const bool abort_all = s_abort != 0;
+
+  if (!abort_all) {
+    const long long q = q0 + warp * 32 + lane;
+    bool ok = false;
+    long long opix = 0;
+    if (q < g.positions) {
+      int xx = (int)(q % PW); long long t = q / PW; int yy = (int)(t % PR); int n = (int)(t / PR);
+      ok = yy >= 1 && xx >= 1 && xx <= g.W;
+      opix = ((long long)n * g.H + (yy - 1)) * g.W + (xx - 1);
+    }
+#pragma unroll
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+      float v[16];
+      tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+      float* orow = Out + opix * g.K + n0 + c0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        int n = n0 + c0 + j;
+        float x = v[j];
+        if (bias && n < g.K) x += bias[n];
+        if (flags & F_RELU) x = fmaxf(x, 0.f);
+        if ((flags & F_ACCUM) && ok && n < g.K) x += orow[j];
+        v[j] = (ok && n < g.K) ? x : 0.f;
+      }
+      if (ok) {
+        if (n0 + c0 + 16 <= g.K && ((g.K & 3) == 0)) {
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(orow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) if (n0 + c0 + j < g.K) orow[j] = v[j];
+        }
+      }
+      if (flags & F_STATS) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float sx = v[j], sq = v[j] * v[j];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) { sx += __shfl_xor_sync(0xffffffffu, sx, o); sq += __shfl_xor_sync(0xffffffffu, sq, o); }
+          if (lane == 0) { atomicAdd(&s_red[c0 + j], sx); atomicAdd(&s_red[BN + c0 + j], sq); }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if ((flags & F_STATS) && !abort_all) {
+    for (int i = tid; i < BN; i += NTHREADS) {
+      int n = n0 + i;
+      if (n < g.K) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.K + n], s_red[BN + i]); }
+    }
+  }
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+inline size_t slab_smem_bytes(int W, int C, int BN) {
+  size_t S = BM + 2 * (W + 2) + 2;
+  return (size_t)(C / 4) * S * 16 + (size_t)9 * (C / 4) * BN * 16;
+}
+constexpr size_t kSmemLimit = 200 * 1024;
+
+template <int BN>
+int launch_slab(const float* X, const float* Wb, const float* bias, float* Out, float* stats, const SlabProblem& g, int flags, int* status,
+                cudaStream_t st) {
+  size_t smem = slab_smem_bytes(g.W, g.C, BN);
+  dim3 grid((unsigned)((g.positions + BM - 1) / BM), (unsigned)((g.K + BN - 1) / BN));
+  conv3x3_slab_kernel<BN><<<grid, NTHREADS, smem, st>>>(X, Wb, bias, Out, stats, g, flags, status);
+  return (int)cudaGetLastError();
+}
+inline int pick_bn(int K) { return K <= 16 ? 16 : K <= 32 ? 32 : K <= 64 ? 64 : K <= 128 ? 128 : 256; }
+
+}  // namespace
+
+// 1 if the slab kernel covers this geometry in direction `which` (0 fprop, 1 dgrad)
+XB_API int xb_conv3x3_slab_supported(const XbConvGeom* g, int which) {
+  if (g->R != 3 || g->S != 3 || g->sh != 1 || g->sw != 1 || g->ph != 1 || g->pw != 1) return 0;
+  int Cred = which == 0 ? g->C : g->K, Kout = which == 0 ? g->K : g->C;
+  if (Cred % 8 || Kout % 4) return 0;
+  return slab_smem_bytes(g->W, Cred, pick_bn(Kout)) <= kSmemLimit ? 1 : 0;
+}
+XB_API int xb_conv3x3_slab_init() {
+  int e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  return 0;
+}
+// which: 0 fprop (In = X, Wb = weights (K,3,3,C)), 1 dgrad (In = dY, Wb = transposed copy (C,3,3,K), output dX)
+XB_API int xb_conv3x3_slab(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which,
+                           int flags, int* status, cudaStream_t st) {
+  SlabProblem g;
+  g.N = cg->N; g.H = cg->H; g.W = cg->W;
+  g.C = which == 0 ? cg->C : cg->K; g.K = which == 0 ? cg->K : cg->C;
+  g.mirrored = which;
+  g.positions = (long long)cg->N * (cg->H + 1) * (cg->W + 2);
+  switch (pick_bn(g.K)) {
+    case 16: return launch_slab<16>(In, Wb, bias, Out, stats, g, flags, status, st);
+    case 32: return launch_slab<32>(In, Wb, bias, Out, stats, g, flags, status, st);
+    case 64: return launch_slab<64>(In, Wb, bias, Out, stats, g, flags, status, st);
+    case 128: return launch_slab<128>(In, Wb, bias, Out, stats, g, flags, status, st);
+    default: return launch_slab<256>(In, Wb, bias, Out, stats, g, flags, status, st);
+  }
+}

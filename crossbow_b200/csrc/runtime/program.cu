@@ -320,3 +320,177 @@ XB_API void* xb_ipc_import(const void* handle64) {
   return p;
 }
 XB_API int xb_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+
+// ---- native executor: what the host runtime (libxbow_rt) drives through function pointers ----------------------------
+//
+// submit / wait / synchronise / batch have the exact signatures of the runtime's Executor table, so scheduler threads
+// call straight into this library without passing through Python.  The learning-rate schedule is evaluated here per
+// task (clib-multigpu/solverconfiguration.c:116-162 does the same natively), including the signal that makes the
+// next synchronisation overwrite the replicas with the central model when a multi-step boundary has been crossed.
+#include <atomic>
+#include <math.h>
+
+struct XbSolverState {
+  int policy;            // 0 FIXED 1 INV 2 STEP 3 MULTISTEP 4 LSR 5 EXP
+  float base_lr, gamma, power, momentum, weight_decay, clip, alpha;
+  long long step_size, warmup;
+  int nsteps; long long steps[32];
+  int l1, nesterov, cma;
+  int step_cursor; int copy_signal;
+};
+
+static float solver_lr(XbSolverState& s, unsigned long long task) {
+  double t1 = (double)task + 1.0;
+  switch (s.policy) {
+    case 0: return s.base_lr;
+    case 1: return s.base_lr * (float)pow(1.0 + s.gamma * t1, -s.power);
+    case 2: return s.base_lr * (float)pow((double)s.gamma, floor(t1 / (double)(s.step_size > 0 ? s.step_size : 1)));
+    case 4:
+      if (s.warmup > 0 && (long long)task < s.warmup) return s.base_lr * (float)task / (float)s.warmup;
+      // fall through
+    case 3:
+      if (s.step_cursor < s.nsteps && (long long)task + 1 >= s.steps[s.step_cursor]) { s.step_cursor++; s.copy_signal = 1; }
+      return s.base_lr * (float)pow((double)s.gamma, (double)s.step_cursor);
+    case 5: return s.base_lr * (float)pow((double)s.gamma, t1);
+  }
+  return s.base_lr;
+}
+
+// mirror of the descriptor in ../kernels/sync.cu (layout checked at start-up through xb_sync_desc_size)
+struct XbSyncDescMirror {
+  int rank, G, k, algo; long long n; unsigned int epoch; int two_shot, copy_to_replicas, use_prev;
+  float alpha, mu, scale, blend;
+  float* w[16]; const float* prev[16]; float* z; float* zlast; float* gacc;
+  float* inbox[8]; float* result[8]; unsigned int* flags[8]; int* status; double timeout_s;
+};
+XB_API int xb_fused_sync(const XbSyncDescMirror* d, void* args_dev, void* args_pinned, int max_blocks, cudaStream_t st);
+XB_API int xb_broadcast_model(const float* z, float* const* w_dev_array, int k, long long n, cudaStream_t st);
+XB_API int xb_sync_args_size();
+
+struct XbExec {
+  std::vector<XbLearner*> learners;
+  std::vector<float*> w, prev;
+  XbSolverState solver;
+  unsigned long long seed = 0;
+  XbSyncDescMirror tmpl;
+  int update_mode = 0;         // 0 averaging kernel, 1 broadcast z (DEFAULT)
+  void* args_dev = nullptr; char* args_pinned = nullptr; int args_stride = 0; int max_blocks = 0;
+  float** w_table_dev = nullptr;
+  cudaStream_t sync_stream = nullptr; cudaEvent_t sync_event = nullptr;
+  unsigned int epoch = 0;
+  std::atomic<unsigned long long> bn_updates{0};
+  // ring data set in pinned memory: [phase]
+  const char* ex_base[2] = {nullptr, nullptr}; const char* lab_base[2] = {nullptr, nullptr};
+  long long ex_bytes[2] = {0, 0}, lab_bytes[2] = {0, 0}, ring[2] = {0, 0}, stride_tasks = 1, offset_tasks = 0;
+  void* d_ex[2][64]; void* d_lab[2][64];
+};
+
+XB_API XbExec* xb_exec_create(const XbSolverState* solver, unsigned long long seed, void* sync_stream, int max_blocks) {
+  XbExec* e = new XbExec();
+  e->solver = *solver; e->seed = seed; e->max_blocks = max_blocks;
+  memset(&e->tmpl, 0, sizeof(e->tmpl));
+  e->sync_stream = (cudaStream_t)sync_stream;
+  cudaEventCreateWithFlags(&e->sync_event, cudaEventDisableTiming);
+  e->args_stride = (xb_sync_args_size() + 255) / 256 * 256;
+  cudaMalloc(&e->args_dev, e->args_stride);
+  cudaHostAlloc((void**)&e->args_pinned, 8 * e->args_stride, cudaHostAllocDefault);
+  cudaMalloc((void**)&e->w_table_dev, 16 * sizeof(float*));
+  memset(e->d_ex, 0, sizeof(e->d_ex)); memset(e->d_lab, 0, sizeof(e->d_lab));
+  return e;
+}
+XB_API void xb_exec_destroy(XbExec* e) {
+  if (!e) return;
+  cudaFree(e->args_dev); cudaFreeHost(e->args_pinned); cudaFree(e->w_table_dev); cudaEventDestroy(e->sync_event);
+  delete e;
+}
+XB_API int xb_exec_add_learner(XbExec* e, XbLearner* l, float* w, float* prev, void* d_ex_train, void* d_lab_train, void* d_ex_test, void* d_lab_test) {
+  int i = (int)e->learners.size();
+  if (i >= 64) return -1;
+  e->learners.push_back(l); e->w.push_back(w); e->prev.push_back(prev);
+  e->d_ex[0][i] = d_ex_train; e->d_lab[0][i] = d_lab_train; e->d_ex[1][i] = d_ex_test; e->d_lab[1][i] = d_lab_test;
+  return i;
+}
+XB_API void xb_exec_remove_learner(XbExec* e) { if (!e->learners.empty()) { e->learners.pop_back(); e->w.pop_back(); e->prev.pop_back(); } }
+XB_API void xb_exec_set_sync(XbExec* e, const XbSyncDescMirror* tmpl, int update_mode) { e->tmpl = *tmpl; e->update_mode = update_mode; }
+XB_API void xb_exec_set_data(XbExec* e, int phase, const void* examples, long long ex_bytes, const void* labels, long long lab_bytes, long long ring,
+                             long long stride_tasks, long long offset_tasks) {
+  e->ex_base[phase] = (const char*)examples; e->ex_bytes[phase] = ex_bytes; e->lab_base[phase] = (const char*)labels; e->lab_bytes[phase] = lab_bytes;
+  e->ring[phase] = ring; e->stride_tasks = stride_tasks; e->offset_tasks = offset_tasks;
+}
+XB_API int xb_sync_desc_size() { return (int)sizeof(XbSyncDescMirror); }
+XB_API int xb_exec_copy_signal(XbExec* e) { return e->solver.copy_signal; }
+
+XB_API int xb_exec_batch(void* ctx, unsigned long long task, int phase, const void** ex, const void** lab) {
+  XbExec* e = (XbExec*)ctx;
+  if (!e->ex_base[phase] || e->ring[phase] <= 0) { *ex = nullptr; *lab = nullptr; return 0; }
+  unsigned long long slot = (task * (unsigned long long)e->stride_tasks + (unsigned long long)e->offset_tasks) % (unsigned long long)e->ring[phase];
+  *ex = e->ex_base[phase] + slot * e->ex_bytes[phase];
+  *lab = e->lab_base[phase] + slot * e->lab_bytes[phase];
+  return 0;
+}
+XB_API int xb_exec_submit(void* ctx, int learner, const void* ex, const void* lab, unsigned long long task, int phase) {
+  XbExec* e = (XbExec*)ctx;
+  if (learner < 0 || learner >= (int)e->learners.size()) return -XB_BAD_ARG;
+  XbLearner* l = e->learners[learner];
+  XbTaskParams p; memset(&p, 0, sizeof(p));
+  const bool training = phase == 0;
+  p.lr = training ? solver_lr(e->solver, task) : 0.f;
+  p.momentum = e->solver.momentum; p.weight_decay = e->solver.weight_decay;
+  p.bn_factor = 1.0f / (1.0f + (float)(training ? e->bn_updates.fetch_add(1) : e->bn_updates.load()));
+  p.clip = e->solver.clip; p.alpha = e->solver.alpha;
+  p.task_id = (unsigned)task; p.seed_lo = (unsigned)(e->seed & 0xffffffffu); p.seed_hi = (unsigned)(e->seed >> 32);
+  p.training = training ? 1 : 0; p.l1 = e->solver.l1; p.nesterov = e->solver.nesterov;
+  if (ex) XB_CUDA_CHECK(cudaMemcpyAsync(e->d_ex[phase][learner], ex, (size_t)e->ex_bytes[phase], cudaMemcpyHostToDevice, l->stream));
+  if (lab) XB_CUDA_CHECK(cudaMemcpyAsync(e->d_lab[phase][learner], lab, (size_t)e->lab_bytes[phase], cudaMemcpyHostToDevice, l->stream));
+  return xb_learner_submit(l, nullptr, nullptr, &p, phase);
+}
+XB_API int xb_exec_wait(void* ctx, int learner, float* loss, float* acc) {
+  XbExec* e = (XbExec*)ctx;
+  if (learner < 0 || learner >= (int)e->learners.size()) return -XB_BAD_ARG;
+  return xb_learner_wait(e->learners[learner], loss, acc);
+}
+XB_API int xb_exec_synchronise(void* ctx, unsigned long long clock, const unsigned char* mask, int n, int copy) {
+  XbExec* e = (XbExec*)ctx;
+  (void)clock;
+  XbSyncDescMirror d = e->tmpl;
+  int k = 0;
+  for (int i = 0; i < n && i < (int)e->learners.size(); ++i) {
+    if (!mask[i]) continue;
+    if (k >= 16) return -XB_BAD_ARG;
+    XB_CUDA_CHECK(cudaStreamWaitEvent(e->sync_stream, e->learners[i]->done, 0));
+    d.w[k] = e->w[i]; d.prev[k] = e->prev[i]; ++k;
+  }
+  if (k == 0) return 0;
+  d.k = k;
+  if (e->update_mode == 1) {
+    XB_CUDA_CHECK(cudaMemcpyAsync(e->w_table_dev, d.w, sizeof(float*) * k, cudaMemcpyHostToDevice, e->sync_stream));
+    int r = xb_broadcast_model(d.z, e->w_table_dev, k, d.n, e->sync_stream);
+    if (r) return r;
+  } else {
+    d.epoch = ++e->epoch;
+    d.copy_to_replicas = (copy || e->solver.copy_signal) ? 1 : 0;
+    e->solver.copy_signal = 0;
+    if (d.algo == 2) { d.scale = 1.0f / (float)(k * d.G); d.blend = 1.0f / (float)d.epoch; }
+    int r = xb_fused_sync(&d, e->args_dev, e->args_pinned + (d.epoch % 8) * e->args_stride, e->max_blocks, e->sync_stream);
+    if (r) return r;
+  }
+  XB_CUDA_CHECK(cudaEventRecord(e->sync_event, e->sync_stream));
+  for (int i = 0; i < n && i < (int)e->learners.size(); ++i)
+    if (mask[i]) XB_CUDA_CHECK(cudaStreamWaitEvent(e->learners[i]->stream, e->sync_event, 0));
+  return 0;
+}
+XB_API unsigned int xb_exec_epoch(XbExec* e) { return e->epoch; }
+XB_API void xb_exec_set_epoch(XbExec* e, unsigned int epoch) { e->epoch = epoch; }
+
+// ---- page-locking of host memory owned by the data-set pipeline (mapped partition files, slot rings) -----------------
+// Signature int(void*, size_t) matches the registration hooks of the host runtime's data sets.
+XB_API int xb_host_register(void* p, size_t bytes) {
+  cudaError_t e = cudaHostRegister(p, bytes, cudaHostRegisterPortable);
+  if (e == cudaErrorHostMemoryAlreadyRegistered) { cudaGetLastError(); return 0; }
+  return (int)e;
+}
+XB_API int xb_host_unregister(void* p, size_t) {
+  cudaError_t e = cudaHostUnregister(p);
+  if (e == cudaErrorHostMemoryNotRegistered) { cudaGetLastError(); return 0; }
+  return (int)e;
+}

@@ -1,0 +1,173 @@
+// Lock-free building blocks of the host runtime.
+//
+//   ThetaQueue   fixed set of slots, each FREE / BUSY / SKIP(disabled), handed out round-robin; grows by one slot
+//                (auto-tuner adds a replica) and shrinks by disabling the last one.  Same role as
+//                clib-multigpu/thetaqueue.c:13-209, but every wait is bounded and reports failure instead of spinning
+//                for ever.
+//   SpscQueue    wait-free single-producer single-consumer ring (waitfreequeue.c:17-90).
+//   MpmcQueue    bounded multi-producer multi-consumer ring (Vyukov) used where the reference has a mutex-guarded
+//                queue (threadsafequeue.c).
+#pragma once
+#include <atomic>
+#include <chrono>
+#include <cstdint>
+#include <memory>
+#include <thread>
+#include <vector>
+
+namespace xb {
+
+inline void cpu_relax(unsigned spins) {
+  if (spins < 64) {
+#if defined(__x86_64__)
+    __builtin_ia32_pause();
+#endif
+  } else if (spins < 256) {
+    std::this_thread::yield();
+  } else {
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
+using Clock = std::chrono::steady_clock;
+inline double seconds_since(Clock::time_point t0) { return std::chrono::duration<double>(Clock::now() - t0).count(); }
+
+class ThetaQueue {
+ public:
+  enum State : int { FREE = 0, BUSY = 1, SKIP = 2 };
+  static constexpr int kMaxSlots = 256;
+
+  explicit ThetaQueue(int n) : size_(n), cursor_(0) {
+    for (int i = 0; i < kMaxSlots; ++i) slots_[i].state.store(i < n ? FREE : SKIP, std::memory_order_relaxed);
+  }
+  int size() const { return size_.load(std::memory_order_acquire); }
+  int enabled() const {
+    int c = 0;
+    for (int i = 0; i < size(); ++i) c += slots_[i].state.load(std::memory_order_acquire) != SKIP;
+    return c;
+  }
+  // Try to take slot i.
+  bool try_acquire(int i) {
+    int expect = FREE;
+    return slots_[i].state.compare_exchange_strong(expect, BUSY, std::memory_order_acq_rel);
+  }
+  // Next enabled slot in round-robin order for which accept(i) holds, waiting up to timeout_s for it to become free.
+  // Returns -1 on timeout.
+  template <class Accept>
+  int next(Accept accept, double timeout_s) {
+    auto t0 = Clock::now();
+    unsigned spins = 0;
+    for (;;) {
+      int n = size();
+      for (int probe = 0; probe < n; ++probe) {
+        int i = (int)(cursor_.load(std::memory_order_relaxed) % (uint64_t)n);
+        int st = slots_[i].state.load(std::memory_order_acquire);
+        if (st == SKIP || !accept(i)) { cursor_.fetch_add(1, std::memory_order_relaxed); continue; }
+        // strict round robin: wait for THIS slot rather than skipping ahead (keeps replicas evenly loaded)
+        if (try_acquire(i)) { cursor_.fetch_add(1, std::memory_order_relaxed); return i; }
+        break;
+      }
+      cpu_relax(++spins);
+      if ((spins & 63) == 0 && seconds_since(t0) > timeout_s) return -1;
+    }
+  }
+  void release(int i) { slots_[i].state.store(FREE, std::memory_order_release); }
+  int state(int i) const { return slots_[i].state.load(std::memory_order_acquire); }
+  // Grow by one slot, born BUSY (the caller releases it once the new replica is ready). Returns its index or -1.
+  int expand() {
+    int n = size();
+    if (n >= kMaxSlots) return -1;
+    slots_[n].state.store(BUSY, std::memory_order_release);
+    size_.store(n + 1, std::memory_order_release);
+    return n;
+  }
+  // Disable the last enabled slot (must be FREE or it is waited for). Returns its index or -1.
+  int shrink(double timeout_s) {
+    for (int i = size() - 1; i >= 0; --i) {
+      if (slots_[i].state.load(std::memory_order_acquire) == SKIP) continue;
+      auto t0 = Clock::now();
+      unsigned spins = 0;
+      for (;;) {
+        int expect = FREE;
+        if (slots_[i].state.compare_exchange_strong(expect, SKIP, std::memory_order_acq_rel)) return i;
+        cpu_relax(++spins);
+        if (seconds_since(t0) > timeout_s) return -1;
+      }
+    }
+    return -1;
+  }
+
+ private:
+  struct alignas(64) Slot { std::atomic<int> state; };
+  Slot slots_[kMaxSlots];
+  std::atomic<int> size_;
+  std::atomic<uint64_t> cursor_;
+};
+
+template <class T>
+class SpscQueue {
+ public:
+  explicit SpscQueue(size_t capacity_pow2 = 1024) : mask_(capacity_pow2 - 1), buf_(capacity_pow2), head_(0), tail_(0) {}
+  bool push(const T& v) {
+    size_t t = tail_.load(std::memory_order_relaxed);
+    if (t - head_.load(std::memory_order_acquire) > mask_) return false;
+    buf_[t & mask_] = v;
+    tail_.store(t + 1, std::memory_order_release);
+    return true;
+  }
+  bool pop(T& v) {
+    size_t h = head_.load(std::memory_order_relaxed);
+    if (h == tail_.load(std::memory_order_acquire)) return false;
+    v = buf_[h & mask_];
+    head_.store(h + 1, std::memory_order_release);
+    return true;
+  }
+  size_t size() const { return tail_.load(std::memory_order_acquire) - head_.load(std::memory_order_acquire); }
+
+ private:
+  size_t mask_;
+  std::vector<T> buf_;
+  alignas(64) std::atomic<size_t> head_;
+  alignas(64) std::atomic<size_t> tail_;
+};
+
+template <class T>
+class MpmcQueue {
+ public:
+  explicit MpmcQueue(size_t capacity_pow2 = 1024) : mask_(capacity_pow2 - 1), cells_(new Cell[capacity_pow2]), enq_(0), deq_(0) {
+    for (size_t i = 0; i <= mask_; ++i) cells_[i].seq.store(i, std::memory_order_relaxed);
+  }
+  bool push(const T& v) {
+    size_t pos = enq_.load(std::memory_order_relaxed);
+    for (;;) {
+      Cell& c = cells_[pos & mask_];
+      size_t seq = c.seq.load(std::memory_order_acquire);
+      intptr_t dif = (intptr_t)seq - (intptr_t)pos;
+      if (dif == 0) {
+        if (enq_.compare_exchange_weak(pos, pos + 1, std::memory_order_relaxed)) { c.value = v; c.seq.store(pos + 1, std::memory_order_release); return true; }
+      } else if (dif < 0) return false;
+      else pos = enq_.load(std::memory_order_relaxed);
+    }
+  }
+  bool pop(T& v) {
+    size_t pos = deq_.load(std::memory_order_relaxed);
+    for (;;) {
+      Cell& c = cells_[pos & mask_];
+      size_t seq = c.seq.load(std::memory_order_acquire);
+      intptr_t dif = (intptr_t)seq - (intptr_t)(pos + 1);
+      if (dif == 0) {
+        if (deq_.compare_exchange_weak(pos, pos + 1, std::memory_order_relaxed)) { v = c.value; c.seq.store(pos + mask_ + 1, std::memory_order_release); return true; }
+      } else if (dif < 0) return false;
+      else pos = deq_.load(std::memory_order_relaxed);
+    }
+  }
+
+ private:
+  struct Cell { std::atomic<size_t> seq; T value; };
+  size_t mask_;
+  std::unique_ptr<Cell[]> cells_;
+  alignas(64) std::atomic<size_t> enq_;
+  alignas(64) std::atomic<size_t> deq_;
+};
+
+}  // namespace xb

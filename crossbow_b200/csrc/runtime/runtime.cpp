@@ -1,0 +1,433 @@
+// Host runtime: work clock, replica pool, task scheduler, handler threads, result ring, collector, watchdog.
+//
+// The reference spreads this over a Java dispatcher, a lock-free Java task queue, native task-handler and
+// callback-handler thread pools, an off-heap result-slot ring and a Java result-collector thread
+// (ExecutionContext.java:257-283, dispatcher/TaskDispatcher.java, clib-multigpu/taskhandler.c, callbackhandler.c,
+// resulthandler.c:44-76, result/ResultCollector.java:40-70, modelmanager.c:147-245).  Here it is one C++ object driven
+// through a C ABI.  The device (or a fake) is reached only through four function pointers, so the very same code
+// runs against the CUDA learners, against the CPU oracle, and against a fake executor in host-only tests.
+//
+// Threads:   caller of rt_train  = dispatcher (numbers tasks, picks replicas, enqueues synchronisation)
+//            task handlers       (optional) issue the submission so the dispatcher can run ahead
+//            callback handlers   wait for a task's completion, publish its result slot, free the replica
+//            collector           drains result slots in task order, aggregates loss / accuracy, stops on target loss
+//            watchdog            aborts the run if a task does not complete within the deadline
+// Every wait is bounded; a failure is reported through rt_error instead of exit(1).
+#include <atomic>
+#include <cmath>
+#include <condition_variable>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+#include <pthread.h>
+#include <sched.h>
+
+#include "queues.hpp"
+
+#define RT_API extern "C" __attribute__((visibility("default")))
+
+namespace xb {
+
+struct Executor {
+  // enqueue one task on learner `learner`; must not block on the device
+  int (*submit)(void* ctx, int learner, const void* examples, const void* labels, uint64_t task, int phase);
+  // block until that learner's task is complete, return its loss / accuracy
+  int (*wait)(void* ctx, int learner, float* loss, float* accuracy);
+  // enqueue a synchronisation over the learners flagged in `mask[0..n)`
+  int (*synchronise)(void* ctx, uint64_t clock, const unsigned char* mask, int n, int copy);
+  // batch source: host addresses of task `task`'s examples and labels (may be null: executor has its own data)
+  int (*batch)(void* ctx, uint64_t task, int phase, const void** examples, const void** labels);
+  void* ctx;
+  // optional external batch source (data-set pipeline): returns a slot id >= 0 that is handed back through release
+  // once the task has completed, or < 0 on failure
+  int (*take)(void* dctx, uint64_t task, int phase, const void** examples, const void** labels);
+  void (*release)(void* dctx, int slot);
+  void* dctx;
+};
+
+// 64-byte result slot, same state machine as the reference's ring (0 free -> 1 being written -> 2 ready -> 3 consumed -> 0)
+struct alignas(64) ResultSlot {
+  std::atomic<int> state;
+  int learner;
+  uint64_t task;
+  float loss, accuracy;
+  int phase;
+  int status;
+  double t_submit, t_done;
+};
+
+struct TaskItem { uint64_t task; int learner; int phase; const void* ex; const void* lab; int slot; };
+
+enum SyncModel { BSP = 0, SSP = 1, ASP = 2 };
+
+class Runtime {
+ public:
+  Runtime(int learners, int wpc, int slack, int sync_model, int result_slots, int task_handlers, int callback_handlers,
+          double task_timeout_s)
+      : theta_(learners), wpc_(wpc), slack_(slack), sync_model_(sync_model), nslots_(result_slots), slots_(new ResultSlot[result_slots]),
+        n_task_handlers_(task_handlers), n_callback_handlers_(callback_handlers < 1 ? 1 : callback_handlers), timeout_(task_timeout_s),
+        task_q_(4096), cb_q_(4096) {
+    for (int i = 0; i < nslots_; ++i) slots_[i].state.store(0);
+    for (int i = 0; i < ThetaQueue::kMaxSlots; ++i) { replica_clock_[i].store(0); replica_updates_[i].store(0); busy_since_[i].store(0.0); }
+    memset(&exec_, 0, sizeof(exec_));
+    t_origin_ = Clock::now();
+    start_threads();
+  }
+  ~Runtime() { stop_threads(); delete[] slots_; }
+
+  void set_executor(const Executor& e) { auto t = exec_.take; auto r = exec_.release; auto d = exec_.dctx; exec_ = e; exec_.take = t; exec_.release = r; exec_.dctx = d; }
+  void set_data_source(decltype(Executor::take) take, decltype(Executor::release) release, void* dctx) { exec_.take = take; exec_.release = release; exec_.dctx = dctx; }
+  void set_target_loss(float t) { target_loss_ = t; }
+  void set_affinity(int first_core) { first_core_ = first_core; }
+
+  int learners() const { return theta_.enabled(); }
+  uint64_t clock() const { return clock_.load(); }
+  uint64_t tasks_issued() const { return next_task_.load(); }
+  uint64_t tasks_completed() const { return completed_.load(); }
+  const char* error() const { return error_.c_str(); }
+  bool failed() const { return failed_.load(); }
+
+  // ---- training loop (dispatcher) ----
+  // Issues `ntasks` training tasks; returns the number issued (less if stopped early), negative on failure.
+  long long train(long long ntasks, int phase) {
+    if (!exec_.submit) return fail("no executor set");
+    stop_.store(false);
+    long long issued = 0;
+    while (issued < ntasks && !stop_.load() && !failed_.load()) {
+      uint64_t task = next_task_.fetch_add(1);
+      const int64_t bound = (int64_t)clock_.load() - slack_ - 1;     // oldest model a task may use
+      int learner = theta_.next([&](int i) { return (int64_t)replica_clock_[i].load(std::memory_order_acquire) >= bound; }, timeout_);
+      if (learner < 0) return fail("no replica became free within the task deadline (a task or a synchronisation is stuck)");
+      busy_since_[learner].store(now());
+      const void *ex = nullptr, *lab = nullptr;
+      int slot = -1;
+      if (exec_.take) {
+        slot = exec_.take(exec_.dctx, task, phase, &ex, &lab);
+        if (slot < 0) return fail("data set could not provide a batch within the deadline");
+      } else if (exec_.batch && exec_.batch(exec_.ctx, task, phase, &ex, &lab) != 0) return fail("data set could not provide a batch");
+      TaskItem it{task, learner, phase, ex, lab, slot};
+      if (n_task_handlers_ > 0) {
+        if (!push_bounded(task_q_, it)) return fail("task queue stayed full");
+      } else {
+        if (!issue(it)) return -1;
+      }
+      ++issued;
+      if (phase == 0) {
+        if (++inner_ >= wpc_) {
+          inner_ = 0;
+          if (!synchronise()) return -1;
+        }
+      }
+    }
+    return issued;
+  }
+
+  // Wait until every issued task has been collected. Returns 0, or -1 on failure / timeout.
+  int drain(double timeout_s) {
+    auto t0 = Clock::now();
+    unsigned spins = 0;
+    while (collected_.load() < next_task_.load()) {
+      if (failed_.load()) return -1;
+      cpu_relax(++spins);
+      if (seconds_since(t0) > timeout_s) { fail("drain timed out"); return -1; }
+    }
+    return 0;
+  }
+
+  void request_stop() { stop_.store(true); }
+
+  // ---- replicas (auto-tuner) ----
+  int add_learner() {
+    int i = theta_.expand();
+    if (i < 0) return -1;
+    replica_clock_[i].store(clock_.load());
+    theta_.release(i);
+    return i;
+  }
+  int remove_learner() { return theta_.shrink(timeout_); }
+
+  // ---- results ----
+  struct Totals { double loss_sum, acc_sum; uint64_t n; float last_loss, last_acc; };
+  Totals totals(bool reset) {
+    std::lock_guard<std::mutex> g(tot_mu_);
+    Totals t = tot_;
+    if (reset) { tot_.loss_sum = tot_.acc_sum = 0; tot_.n = 0; }
+    return t;
+  }
+  // copy up to n most recent (task, loss, acc) records
+  int history(uint64_t* tasks, float* loss, float* acc, int n) {
+    std::lock_guard<std::mutex> g(tot_mu_);
+    int m = (int)hist_.size() < n ? (int)hist_.size() : n;
+    for (int i = 0; i < m; ++i) { const auto& h = hist_[hist_.size() - m + i]; tasks[i] = h.task; loss[i] = h.loss; acc[i] = h.acc; }
+    return m;
+  }
+
+ private:
+  double now() const { return seconds_since(t_origin_); }
+  long long fail(const char* why) {
+    bool expected = false;
+    if (failed_.compare_exchange_strong(expected, true)) error_ = why;
+    return -1;
+  }
+  template <class Q>
+  bool push_bounded(Q& q, const TaskItem& it) {
+    auto t0 = Clock::now();
+    unsigned spins = 0;
+    while (!q.push(it)) {
+      cpu_relax(++spins);
+      if (seconds_since(t0) > timeout_) return false;
+    }
+    return true;
+  }
+  bool issue(const TaskItem& it) {
+    int e = exec_.submit(exec_.ctx, it.learner, it.ex, it.lab, it.task, it.phase);
+    if (e != 0) { char b[96]; snprintf(b, sizeof b, "task submission failed with code %d", e); fail(b); return false; }
+    if (!push_bounded(cb_q_, it)) { fail("callback queue stayed full"); return false; }
+    return true;
+  }
+  // Called by the dispatcher after the wpc-th task of a clock has been handed over.
+  bool synchronise() {
+    if (n_task_handlers_ > 0) {          // submissions must be on the device queues before the synchronisation is
+      auto t0 = Clock::now(); unsigned spins = 0;
+      while (handed_.load() < next_task_.load()) { cpu_relax(++spins); if (failed_.load() || seconds_since(t0) > timeout_) { fail("task handlers stalled"); return false; } }
+    }
+    const int n = theta_.size();
+    std::vector<unsigned char> mask(n, 0);
+    int count = 0;
+    for (int i = 0; i < n; ++i) {
+      int st = theta_.state(i);
+      if (st == ThetaQueue::SKIP) continue;
+      // BSP: every replica takes part (ordering is enforced on the device by events, a replica that is still
+      // running simply makes the synchronisation wait there).  SSP / ASP: only replicas that are idle right now.
+      if (sync_model_ == BSP || st == ThetaQueue::FREE) { mask[i] = 1; ++count; }
+    }
+    uint64_t c = clock_.load() + 1;
+    if (count > 0 && exec_.synchronise) {
+      int e = exec_.synchronise(exec_.ctx, c, mask.data(), n, 0);
+      if (e != 0) { char b[96]; snprintf(b, sizeof b, "synchronisation failed with code %d", e); fail(b); return false; }
+    }
+    for (int i = 0; i < n; ++i) if (mask[i]) { replica_clock_[i].store(c, std::memory_order_release); replica_updates_[i].store(0); }
+    clock_.store(c);
+    return true;
+  }
+
+  void start_threads() {
+    running_.store(true);
+    for (int i = 0; i < n_task_handlers_; ++i) threads_.emplace_back([this, i] { pin(i + 1); task_loop(); });
+    for (int i = 0; i < n_callback_handlers_; ++i) threads_.emplace_back([this, i] { pin(n_task_handlers_ + i + 1); callback_loop(); });
+    threads_.emplace_back([this] { collector_loop(); });
+    threads_.emplace_back([this] { watchdog_loop(); });
+  }
+  void stop_threads() {
+    running_.store(false);
+    for (auto& t : threads_) if (t.joinable()) t.join();
+    threads_.clear();
+  }
+  void pin(int idx) {
+    if (first_core_ < 0) return;
+    cpu_set_t set; CPU_ZERO(&set);
+    int ncpu = (int)std::thread::hardware_concurrency();
+    if (ncpu <= 0) return;
+    CPU_SET((first_core_ + idx) % ncpu, &set);
+    pthread_setaffinity_np(pthread_self(), sizeof(set), &set);
+  }
+  void task_loop() {
+    unsigned spins = 0;
+    TaskItem it;
+    while (running_.load()) {
+      if (task_q_.pop(it)) { spins = 0; if (!failed_.load()) issue(it); handed_.fetch_add(1); }
+      else cpu_relax(++spins);
+    }
+  }
+  void callback_loop() {
+    unsigned spins = 0;
+    TaskItem it;
+    while (running_.load()) {
+      if (!cb_q_.pop(it)) { cpu_relax(++spins); continue; }
+      spins = 0;
+      if (n_task_handlers_ == 0) handed_.fetch_add(1);
+      float loss = NAN, acc = NAN;
+      int e = failed_.load() ? -1 : exec_.wait(exec_.ctx, it.learner, &loss, &acc);
+      if (e != 0 && !failed_.load()) { char b[96]; snprintf(b, sizeof b, "task %llu failed on learner %d with code %d", (unsigned long long)it.task, it.learner, e); fail(b); }
+      if (it.slot >= 0 && exec_.release) exec_.release(exec_.dctx, it.slot);      // the batch has been consumed
+      // publish the result slot: 0 -> 1, fill, 1 -> 2
+      ResultSlot& s = slots_[it.task % (uint64_t)nslots_];
+      unsigned sp = 0; int expect = 0;
+      auto t0 = Clock::now();
+      while (!s.state.compare_exchange_weak(expect, 1)) { expect = 0; cpu_relax(++sp); if (seconds_since(t0) > timeout_) { fail("result ring stayed full"); break; } }
+      s.learner = it.learner; s.task = it.task; s.loss = loss; s.accuracy = acc; s.phase = it.phase; s.status = e; s.t_done = now();
+      s.state.store(2, std::memory_order_release);
+      replica_updates_[it.learner].fetch_add(1);
+      busy_since_[it.learner].store(0.0);
+      theta_.release(it.learner);
+      completed_.fetch_add(1);
+    }
+  }
+  void collector_loop() {
+    unsigned spins = 0;
+    while (running_.load()) {
+      uint64_t next = collected_.load();
+      ResultSlot& s = slots_[next % (uint64_t)nslots_];
+      if (s.state.load(std::memory_order_acquire) != 2 || s.task != next) { cpu_relax(++spins); continue; }
+      spins = 0;
+      s.state.store(3);
+      {
+        std::lock_guard<std::mutex> g(tot_mu_);
+        if (s.phase == 0 && std::isfinite(s.loss)) { tot_.loss_sum += s.loss; tot_.acc_sum += s.accuracy; tot_.n += 1; tot_.last_loss = s.loss; tot_.last_acc = s.accuracy; }
+        else if (s.phase != 0 && std::isfinite(s.accuracy)) { tot_.loss_sum += s.loss; tot_.acc_sum += s.accuracy; tot_.n += 1; }
+        hist_.push_back({s.task, s.loss, s.accuracy});
+        if (hist_.size() > 65536) hist_.erase(hist_.begin(), hist_.begin() + 32768);
+      }
+      if (s.phase == 0 && target_loss_ > 0 && s.loss <= target_loss_) stop_.store(true);
+      s.state.store(0, std::memory_order_release);
+      collected_.fetch_add(1);
+    }
+  }
+  void watchdog_loop() {
+    while (running_.load()) {
+      std::this_thread::sleep_for(std::chrono::milliseconds(20));
+      double t = now();
+      for (int i = 0; i < theta_.size(); ++i) {
+        double b = busy_since_[i].load();
+        if (b > 0.0 && t - b > timeout_ && theta_.state(i) == ThetaQueue::BUSY) {
+          char msg[128]; snprintf(msg, sizeof msg, "watchdog: learner %d has been busy for %.1f s (deadline %.1f s)", i, t - b, timeout_);
+          fail(msg);
+        }
+      }
+    }
+  }
+
+  ThetaQueue theta_;
+  int wpc_, slack_, sync_model_;
+  int inner_ = 0;
+  int nslots_;
+  ResultSlot* slots_;
+  int n_task_handlers_, n_callback_handlers_;
+  double timeout_;
+  int first_core_ = -1;
+  Executor exec_;
+  MpmcQueue<TaskItem> task_q_, cb_q_;
+  std::atomic<uint64_t> next_task_{0}, completed_{0}, collected_{0}, handed_{0}, clock_{0};
+  std::atomic<uint64_t> replica_clock_[ThetaQueue::kMaxSlots];
+  std::atomic<uint64_t> replica_updates_[ThetaQueue::kMaxSlots];
+  std::atomic<double> busy_since_[ThetaQueue::kMaxSlots];
+  std::atomic<bool> running_{false}, stop_{false}, failed_{false};
+  std::string error_;
+  float target_loss_ = -1.f;
+  std::vector<std::thread> threads_;
+  std::mutex tot_mu_;
+  Totals tot_{0, 0, 0, NAN, NAN};
+  struct Hist { uint64_t task; float loss, acc; };
+  std::vector<Hist> hist_;
+  Clock::time_point t_origin_;
+};
+
+// ---- fake executor for host-only tests ------------------------------------------------------------------------------
+struct FakeExec {
+  int learners;
+  int task_us;
+  std::atomic<int> fail_task{-1};        // task id whose wait returns an error
+  std::atomic<int> hang_task{-1};        // task id whose wait never returns within the deadline
+  std::atomic<uint64_t> syncs{0}, submits{0};
+  std::vector<std::atomic<uint64_t>> current;
+  std::vector<unsigned char> last_mask;
+  std::mutex mu;
+  FakeExec(int n, int us) : learners(n), task_us(us), current(256) { for (auto& c : current) c.store(0); }
+};
+static int fake_submit(void* c, int learner, const void*, const void*, uint64_t task, int) {
+  auto* f = (FakeExec*)c; f->current[learner].store(task); f->submits.fetch_add(1); return 0;
+}
+static int fake_wait(void* c, int learner, float* loss, float* acc) {
+  auto* f = (FakeExec*)c;
+  uint64_t task = f->current[learner].load();
+  if ((int)task == f->hang_task.load()) { std::this_thread::sleep_for(std::chrono::milliseconds(1500)); }
+  else if (f->task_us > 0) std::this_thread::sleep_for(std::chrono::microseconds(f->task_us));
+  if ((int)task == f->fail_task.load()) return 77;
+  *loss = 1.0f / (1.0f + (float)task); *acc = (float)learner;
+  return 0;
+}
+static int fake_sync(void* c, uint64_t, const unsigned char* mask, int n, int) {
+  auto* f = (FakeExec*)c; f->syncs.fetch_add(1);
+  std::lock_guard<std::mutex> g(f->mu); f->last_mask.assign(mask, mask + n); return 0;
+}
+
+}  // namespace xb
+
+using namespace xb;
+
+RT_API void* rt_create(int learners, int wpc, int slack, int sync_model, int result_slots, int task_handlers, int callback_handlers, double task_timeout_s) {
+  if (learners < 1 || learners > ThetaQueue::kMaxSlots || wpc < 1 || result_slots < 2) return nullptr;
+  return new Runtime(learners, wpc, slack, sync_model, result_slots, task_handlers, callback_handlers, task_timeout_s);
+}
+RT_API void rt_destroy(void* r) { delete (Runtime*)r; }
+RT_API void rt_set_executor(void* r, void* submit, void* wait, void* synchronise, void* batch, void* ctx) {
+  Executor e; memset(&e, 0, sizeof(e));
+  e.submit = (decltype(e.submit))submit; e.wait = (decltype(e.wait))wait; e.synchronise = (decltype(e.synchronise))synchronise;
+  e.batch = (decltype(e.batch))batch; e.ctx = ctx;
+  ((Runtime*)r)->set_executor(e);
+}
+RT_API void rt_set_data_source(void* r, void* take, void* release, void* dctx) {
+  ((Runtime*)r)->set_data_source((decltype(Executor::take))take, (decltype(Executor::release))release, dctx);
+}
+RT_API void rt_set_target_loss(void* r, float t) { ((Runtime*)r)->set_target_loss(t); }
+RT_API void rt_set_affinity(void* r, int first_core) { ((Runtime*)r)->set_affinity(first_core); }
+RT_API long long rt_train(void* r, long long ntasks, int phase) { return ((Runtime*)r)->train(ntasks, phase); }
+RT_API int rt_drain(void* r, double timeout_s) { return ((Runtime*)r)->drain(timeout_s); }
+RT_API void rt_stop(void* r) { ((Runtime*)r)->request_stop(); }
+RT_API int rt_add_learner(void* r) { return ((Runtime*)r)->add_learner(); }
+RT_API int rt_remove_learner(void* r) { return ((Runtime*)r)->remove_learner(); }
+RT_API int rt_learners(void* r) { return ((Runtime*)r)->learners(); }
+RT_API unsigned long long rt_clock(void* r) { return ((Runtime*)r)->clock(); }
+RT_API unsigned long long rt_tasks_issued(void* r) { return ((Runtime*)r)->tasks_issued(); }
+RT_API unsigned long long rt_tasks_completed(void* r) { return ((Runtime*)r)->tasks_completed(); }
+RT_API int rt_failed(void* r) { return ((Runtime*)r)->failed() ? 1 : 0; }
+RT_API const char* rt_error(void* r) { return ((Runtime*)r)->error(); }
+RT_API void rt_totals(void* r, int reset, double* loss_sum, double* acc_sum, unsigned long long* n, float* last_loss, float* last_acc) {
+  auto t = ((Runtime*)r)->totals(reset != 0);
+  *loss_sum = t.loss_sum; *acc_sum = t.acc_sum; *n = t.n; *last_loss = t.last_loss; *last_acc = t.last_acc;
+}
+RT_API int rt_history(void* r, unsigned long long* tasks, float* loss, float* acc, int n) {
+  return ((Runtime*)r)->history((uint64_t*)tasks, loss, acc, n);
+}
+
+RT_API void* rt_fake_create(int learners, int task_us) { return new FakeExec(learners, task_us); }
+RT_API void rt_fake_destroy(void* f) { delete (FakeExec*)f; }
+RT_API void rt_fake_attach(void* r, void* f) {
+  Executor e; memset(&e, 0, sizeof(e)); e.submit = fake_submit; e.wait = fake_wait; e.synchronise = fake_sync; e.batch = nullptr; e.ctx = f;
+  ((Runtime*)r)->set_executor(e);
+}
+RT_API void rt_fake_inject(void* f, int fail_task, int hang_task) { ((FakeExec*)f)->fail_task.store(fail_task); ((FakeExec*)f)->hang_task.store(hang_task); }
+RT_API unsigned long long rt_fake_syncs(void* f) { return ((FakeExec*)f)->syncs.load(); }
+RT_API int rt_fake_last_mask(void* f, unsigned char* out, int n) {
+  auto* fe = (FakeExec*)f; std::lock_guard<std::mutex> g(fe->mu);
+  int m = (int)fe->last_mask.size() < n ? (int)fe->last_mask.size() : n;
+  memcpy(out, fe->last_mask.data(), m); return m;
+}
+
+// ---- theta queue, exposed for tests and for Python-side pools ---------------------------------------------------------
+RT_API void* rt_theta_create(int n) { return new ThetaQueue(n); }
+RT_API void rt_theta_destroy(void* q) { delete (ThetaQueue*)q; }
+RT_API int rt_theta_next(void* q, double timeout_s) { return ((ThetaQueue*)q)->next([](int) { return true; }, timeout_s); }
+RT_API void rt_theta_release(void* q, int i) { ((ThetaQueue*)q)->release(i); }
+RT_API int rt_theta_expand(void* q) { return ((ThetaQueue*)q)->expand(); }
+RT_API int rt_theta_shrink(void* q, double timeout_s) { return ((ThetaQueue*)q)->shrink(timeout_s); }
+RT_API int rt_theta_size(void* q) { return ((ThetaQueue*)q)->size(); }
+RT_API int rt_theta_enabled(void* q) { return ((ThetaQueue*)q)->enabled(); }
+
+// ---- CPU affinity (clib-multigpu/CPU.c:26-83) -------------------------------------------------------------------------
+RT_API int rt_cpu_bind(int core) {
+  cpu_set_t set; CPU_ZERO(&set); CPU_SET(core, &set);
+  return sched_setaffinity(0, sizeof(set), &set);
+}
+RT_API int rt_cpu_unbind() {
+  cpu_set_t set; CPU_ZERO(&set);
+  int n = (int)std::thread::hardware_concurrency();
+  for (int i = 0; i < n; ++i) CPU_SET(i, &set);
+  return sched_setaffinity(0, sizeof(set), &set);
+}
+RT_API int rt_cpu_id() { return sched_getcpu(); }
+RT_API int rt_cpu_count() { return (int)std::thread::hardware_concurrency(); }

@@ -129,8 +129,8 @@ class GpuEngine:
         from .parallel.sync import FusedSynchroniser, ReferenceSynchroniser
         if not torch.cuda.is_available():
             raise RuntimeError("GpuEngine needs a CUDA device")
-        self.lib = L.load()          # raises if the extension cannot be built / loaded: no fallback on the device path
         torch.cuda.set_device(device_index)
+        self.lib = L.init_device()   # raises if the extension cannot be built / loaded: no fallback on the device path
         self.device = torch.device("cuda", device_index)
         self.train_graph, self.test_graph, self.model = train_graph, test_graph, model
         self.batch, self.input_chw, self.solver, self.update_model = batch, tuple(input_chw), solver, update_model
@@ -151,6 +151,7 @@ class GpuEngine:
         self.synchroniser = Sync(n, rank, world, two_shot, sync_timeout_s) if fused_sync else Sync(n, rank, world)
         self.poly_count = 0
         self.bn_updates = 0
+        self._exec = None
         torch.cuda.synchronize()
 
     # ---- replicas ----
@@ -166,6 +167,8 @@ class GpuEngine:
         l.rep.last.copy_(self.learners[0].rep.last)
         l.rep.prev.copy_(self.learners[0].rep.prev)
         self.learners.append(l)
+        if self._exec:
+            self._exec_add(l)
         torch.cuda.synchronize()
         return l
 
@@ -173,6 +176,8 @@ class GpuEngine:
         if len(self.learners) <= 1:
             return
         torch.cuda.synchronize()
+        if self._exec:
+            self.lib.xb_exec_remove_learner(self._exec)
         self.learners.pop().destroy()
 
     # ---- tasks ----
@@ -225,6 +230,66 @@ class GpuEngine:
         for l in ls:
             L.check(lib.xb_learner_wait_event(l.handle, self.sync_event), "learner waits for sync")
 
+    # ---- native scheduling: hand the learners to the C++ runtime ----
+    def native_executor(self, train_ds=None, test_ds=None):
+        """Build the native executor (csrc/runtime/program.cu) for this engine and return
+        ``(ctx, submit, wait, synchronise, batch)`` as raw addresses for ``Runtime.set_executor``."""
+        from .ops import lib as L
+        from .parallel import sync as S
+        from .types import LearningRateDecayPolicy as P
+        lib, sv = self.lib, self.solver
+        if not hasattr(self.synchroniser, "descriptor"):
+            raise RuntimeError("the native scheduler needs the fused synchroniser")
+        st = L.XbSolverState()
+        st.policy = {P.FIXED: 0, P.INV: 1, P.STEP: 2, P.MULTISTEP: 3, P.LSR: 4, P.EXP: 5}.get(sv.learning_rate_decay_policy, 0)
+        st.base_lr, st.gamma, st.power, st.momentum = sv.base_learning_rate, sv.gamma, sv.power, sv.momentum
+        st.weight_decay, st.alpha = sv.weight_decay, sv.alpha
+        st.clip = sv.clip_gradient_threshold if sv.clip_gradient_threshold is not None else -1.0
+        st.step_size, st.warmup = sv._in_tasks(sv.step_size), sv._in_tasks(sv.warmup_steps)
+        steps = sv.steps_in_tasks()[:32]
+        st.nsteps = len(steps)
+        for i, v in enumerate(steps):
+            st.steps[i] = v
+        st.l1 = int(sv.regularisation_type == Regularisation.L1)
+        st.nesterov = int(sv.momentum_method == MomentumMethod.NESTEROV)
+        st.step_cursor, st.copy_signal = sv._step, 0
+        if self._exec:
+            lib.xb_exec_destroy(self._exec)
+        self._exec = lib.xb_exec_create(C.byref(st), self.seed, self.sync_stream, getattr(self.synchroniser, "max_blocks", 0))
+        for l in self.learners:
+            self._exec_add(l)
+        um, sh = self.update_model, self.shared
+        ws = [l.rep.w for l in self.learners]
+        prevs = [l.rep.prev for l in self.learners]
+        sy = self.synchroniser
+        if um in (UpdateModel.SMA, UpdateModel.SYNCHRONOUSEAMSGD):
+            d = sy.descriptor(S.ALGO_SMA, ws, prevs, sh.z, sh.zlast, None, sv.alpha, sma_base_momentum(sv), 1.0, 0.0, False, True)
+        elif um == UpdateModel.EAMSGD:
+            d = sy.descriptor(S.ALGO_SMA, ws, prevs, sh.z, sh.zlast, None, sv.alpha, sv.base_model_momentum, 1.0, 0.0, False, False)
+        elif um == UpdateModel.WORKER:
+            d = sy.descriptor(S.ALGO_SSGD, ws, None, sh.z, sh.zlast, sh.gacc, 0.0, sv.momentum, 1.0 / self.wpc, 0.0, False, True)
+        elif um == UpdateModel.POLYAK_RUPPERT:
+            d = sy.descriptor(S.ALGO_POLYAK, ws, None, sh.z, sh.zlast, None, 0.0, 0.0, 1.0, 1.0, False, True)
+        elif um == UpdateModel.DEFAULT:
+            d = sy.descriptor(S.ALGO_SMA, ws, prevs, sh.z, sh.zlast, None, 0.0, 0.0, 1.0, 0.0, False, True)
+        else:
+            raise NotImplementedError(f"error: {um} is not supported (a stub in the reference as well)")
+        lib.xb_exec_set_sync(self._exec, C.byref(d), int(um == UpdateModel.DEFAULT))
+        lib.xb_exec_set_epoch(self._exec, sy.epoch)
+        for phase, ds in ((0, train_ds), (1, test_ds)):
+            if ds is not None:
+                lib.xb_exec_set_data(self._exec, phase, ds.examples.data_ptr(), ds.examples[0].numel() * 4, ds.labels.data_ptr(),
+                                     ds.labels[0].numel() * 4, ds.examples.shape[0], self.world if phase == 0 else 1,
+                                     self.rank if phase == 0 else 0)
+        addr = lambda name: C.cast(getattr(lib, name), C.c_void_p).value
+        return self._exec, addr("xb_exec_submit"), addr("xb_exec_wait"), addr("xb_exec_synchronise"), addr("xb_exec_batch")
+
+    def _exec_add(self, l: Learner):
+        ext, lat = l.staging(Phase.TRAIN)
+        exs, las = l.staging(Phase.CHECK) if l.low_test is not None else (None, None)
+        p = lambda t: t.data_ptr() if t is not None else 0
+        self.lib.xb_exec_add_learner(self._exec, l.handle, l.rep.w.data_ptr(), l.rep.prev.data_ptr(), p(ext), p(lat), p(exs), p(las))
+
     def finish(self):
         torch.cuda.synchronize()
         self.synchroniser.check()
@@ -253,6 +318,9 @@ class GpuEngine:
         for l in self.learners:
             l.destroy()
         self.learners = []
+        if self._exec:
+            self.lib.xb_exec_destroy(self._exec)
+            self._exec = None
         self.synchroniser.close()
         self.lib.xb_stream_destroy(self.sync_stream)
 

@@ -44,6 +44,13 @@ class XbSyncDesc(C.Structure):
                 ("status", c_void_p), ("timeout_s", C.c_double)]
 
 
+class XbSolverState(C.Structure):
+    _fields_ = [("policy", c_int), ("base_lr", c_float), ("gamma", c_float), ("power", c_float), ("momentum", c_float),
+                ("weight_decay", c_float), ("clip", c_float), ("alpha", c_float), ("step_size", c_ll), ("warmup", c_ll),
+                ("nsteps", c_int), ("steps", c_ll * 32), ("l1", c_int), ("nesterov", c_int), ("cma", c_int),
+                ("step_cursor", c_int), ("copy_signal", c_int)]
+
+
 # op kinds (csrc/runtime/program.cu)
 (OP_MEMSET, OP_UPLOAD, OP_TRANSFORM, OP_CONV_FPROP, OP_CONV_DGRAD, OP_CONV_WGRAD, OP_COLSUM, OP_BN_STATS, OP_BN_FWD,
  OP_BN_BWD, OP_ACT_FWD, OP_ACT_BWD, OP_SUM, OP_DROPOUT, OP_CONCAT, OP_POOL_FWD, OP_POOL_BWD, OP_LRN_FWD, OP_LRN_BWD,
@@ -76,6 +83,9 @@ def load() -> C.CDLL:
     _sig(lib, "xb_conv_dgrad_tc", I, P, P, P, G, I, P, P)
     _sig(lib, "xb_conv_wgrad_tc", I, P, P, P, G, P, P)
     _sig(lib, "xb_tc_supported", I, G, I)
+    _sig(lib, "xb_tc_init", I)
+    _sig(lib, "xb_tc_set_slab", None, I)
+    _sig(lib, "xb_conv3x3_slab_supported", I, G, I)
     _sig(lib, "xb_transpose_weights", I, P, P, P, I, I, P)
     _sig(lib, "xb_bn_stats", I, P, P, I, I, P)
     _sig(lib, "xb_bn_forward", I, P, P, P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, F, P)
@@ -128,6 +138,18 @@ def load() -> C.CDLL:
     _sig(lib, "xb_learner_query", I, P)
     _sig(lib, "xb_stream_wait_learner", I, P, P)
     _sig(lib, "xb_learner_wait_event", I, P, P)
+    # native executor (function-pointer table for the host runtime)
+    _sig(lib, "xb_exec_create", P, C.POINTER(XbSolverState), C.c_ulonglong, P, I)
+    _sig(lib, "xb_exec_destroy", None, P)
+    _sig(lib, "xb_exec_add_learner", I, P, P, P, P, P, P, P, P)
+    _sig(lib, "xb_exec_remove_learner", None, P)
+    _sig(lib, "xb_exec_set_sync", None, P, C.POINTER(XbSyncDesc), I)
+    _sig(lib, "xb_exec_set_data", None, P, I, P, L, P, L, L, L, L)
+    _sig(lib, "xb_sync_desc_size", I)
+    _sig(lib, "xb_exec_copy_signal", I, P)
+    _sig(lib, "xb_exec_epoch", c_uint, P)
+    _sig(lib, "xb_exec_set_epoch", None, P, c_uint)
+    assert lib.xb_sync_desc_size() == C.sizeof(XbSyncDesc), (lib.xb_sync_desc_size(), C.sizeof(XbSyncDesc))
     # plumbing
     _sig(lib, "xb_stream_create", P, I)
     _sig(lib, "xb_stream_destroy", I, P)
@@ -153,6 +175,19 @@ def load() -> C.CDLL:
     _sig(lib, "xb_ipc_close", I, P)
     assert lib.xb_op_size() == C.sizeof(XbOp), (lib.xb_op_size(), C.sizeof(XbOp))
     _lib = lib
+    return lib
+
+
+_tc_ready = False
+
+
+def init_device():
+    """Per-process device set-up that must happen outside stream capture (shared-memory opt-in of the tcgen05 kernels)."""
+    global _tc_ready
+    lib = load()
+    if not _tc_ready:
+        check(lib.xb_tc_init(), "tensor-core kernel set-up")
+        _tc_ready = True
     return lib
 
 

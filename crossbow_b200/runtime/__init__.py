@@ -1,0 +1,231 @@
+"""ctypes binding of ``libxbow_rt.so``: the host-only C++ runtime (scheduler, replica pool, queues, result ring,
+watchdog, data-set pipeline, record reader).  It has no CUDA dependency, so it loads and is tested on machines without
+a GPU; the device is reached through executor function pointers exported by ``libxbow_cuda.so``."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+from ..ops import build as _build
+
+_lib: Optional[C.CDLL] = None
+
+
+def _sig(lib, name, restype, *argtypes):
+    f = getattr(lib, name)
+    f.restype, f.argtypes = restype, list(argtypes)
+    return f
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    lib = C.CDLL(str(_build.build_rt()))
+    P, I, D, L, U = C.c_void_p, C.c_int, C.c_double, C.c_longlong, C.c_ulonglong
+    _sig(lib, "rt_create", P, I, I, I, I, I, I, I, D)
+    _sig(lib, "rt_destroy", None, P)
+    _sig(lib, "rt_set_executor", None, P, P, P, P, P, P)
+    _sig(lib, "rt_set_target_loss", None, P, C.c_float)
+    _sig(lib, "rt_set_affinity", None, P, I)
+    _sig(lib, "rt_train", L, P, L, I)
+    _sig(lib, "rt_drain", I, P, D)
+    _sig(lib, "rt_stop", None, P)
+    _sig(lib, "rt_add_learner", I, P)
+    _sig(lib, "rt_remove_learner", I, P)
+    _sig(lib, "rt_learners", I, P)
+    _sig(lib, "rt_clock", U, P)
+    _sig(lib, "rt_tasks_issued", U, P)
+    _sig(lib, "rt_tasks_completed", U, P)
+    _sig(lib, "rt_failed", I, P)
+    _sig(lib, "rt_error", C.c_char_p, P)
+    _sig(lib, "rt_totals", None, P, I, C.POINTER(D), C.POINTER(D), C.POINTER(U), C.POINTER(C.c_float), C.POINTER(C.c_float))
+    _sig(lib, "rt_history", I, P, C.POINTER(U), C.POINTER(C.c_float), C.POINTER(C.c_float), I)
+    _sig(lib, "rt_fake_create", P, I, I)
+    _sig(lib, "rt_fake_destroy", None, P)
+    _sig(lib, "rt_fake_attach", None, P, P)
+    _sig(lib, "rt_fake_inject", None, P, I, I)
+    _sig(lib, "rt_fake_syncs", U, P)
+    _sig(lib, "rt_fake_last_mask", I, P, C.c_char_p, I)
+    _sig(lib, "rt_theta_create", P, I)
+    _sig(lib, "rt_theta_destroy", None, P)
+    _sig(lib, "rt_theta_next", I, P, D)
+    _sig(lib, "rt_theta_release", None, P, I)
+    _sig(lib, "rt_theta_expand", I, P)
+    _sig(lib, "rt_theta_shrink", I, P, D)
+    _sig(lib, "rt_theta_size", I, P)
+    _sig(lib, "rt_theta_enabled", I, P)
+    _sig(lib, "rt_set_data_source", None, P, P, P, P)
+    V = C.POINTER(C.c_void_p)
+    _sig(lib, "ds_meta_load", P, C.c_char_p)
+    _sig(lib, "ds_meta_free", None, P)
+    _sig(lib, "ds_meta_get", L, P, I)
+    _sig(lib, "ds_meta_shape", L, P, I)
+    _sig(lib, "ds_writer_create", P, C.c_char_p, C.c_char_p, C.c_char_p, L, C.POINTER(L), I, L, I)
+    _sig(lib, "ds_writer_append", I, P, P, P, L)
+    _sig(lib, "ds_writer_close", I, P)
+    _sig(lib, "ds_basic_open", P, C.c_char_p, I, P, P)
+    _sig(lib, "ds_basic_batch", I, P, L, V, V, D)
+    _sig(lib, "ds_basic_resident_bytes", L, P)
+    _sig(lib, "ds_basic_resident_partitions", I, P)
+    _sig(lib, "ds_basic_close", None, P)
+    _sig(lib, "ds_light_open", P, C.c_char_p, I, I)
+    _sig(lib, "ds_light_ring", P, P, I, C.POINTER(L))
+    _sig(lib, "ds_light_take", I, P, L, V, V, D)
+    _sig(lib, "ds_light_release", None, P, I)
+    _sig(lib, "ds_light_close", None, P)
+    _sig(lib, "ds_source_create", P, P, I, L, L, D)
+    _sig(lib, "ds_source_free", None, P)
+    _sig(lib, "rt_cpu_bind", I, I)
+    _sig(lib, "rt_cpu_unbind", I)
+    _sig(lib, "rt_cpu_id", I)
+    _sig(lib, "rt_cpu_count", I)
+    _lib = lib
+    return lib
+
+
+class RuntimeError_(RuntimeError):
+    """The native runtime stopped with an error (stuck task, failed submission, watchdog deadline ...)."""
+
+
+class ThetaQueue:
+    """Round-robin slot pool with FREE / BUSY / disabled states (clib-multigpu/thetaqueue.c)."""
+
+    def __init__(self, n: int):
+        self.lib = load()
+        self.h = self.lib.rt_theta_create(n)
+
+    def next(self, timeout_s: float = 1.0) -> int:
+        return self.lib.rt_theta_next(self.h, timeout_s)
+
+    def release(self, i: int):
+        self.lib.rt_theta_release(self.h, i)
+
+    def expand(self) -> int:
+        return self.lib.rt_theta_expand(self.h)
+
+    def shrink(self, timeout_s: float = 1.0) -> int:
+        return self.lib.rt_theta_shrink(self.h, timeout_s)
+
+    def size(self) -> int:
+        return self.lib.rt_theta_size(self.h)
+
+    def enabled(self) -> int:
+        return self.lib.rt_theta_enabled(self.h)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.rt_theta_destroy(self.h)
+            self.h = None
+
+
+class Runtime:
+    """Native scheduler. ``sync_model``: 0 BSP, 1 SSP, 2 ASP."""
+
+    def __init__(self, learners: int, wpc: int, slack: int = 0, sync_model: int = 0, result_slots: int = 2048,
+                 task_handlers: int = 0, callback_handlers: int = 1, task_timeout_s: float = 30.0):
+        self.lib = load()
+        self.h = self.lib.rt_create(learners, wpc, slack, sync_model, result_slots, task_handlers, callback_handlers, task_timeout_s)
+        if not self.h:
+            raise ValueError("invalid runtime configuration")
+        self._fake = None
+
+    def set_executor(self, submit: int, wait: int, synchronise: int, batch: int, ctx: int):
+        self.lib.rt_set_executor(self.h, submit, wait, synchronise, batch, ctx)
+
+    def set_data_source(self, source_handle: int):
+        """Batches come from a native data set (``crossbow_b200.data.native``) instead of the executor's own ring."""
+        addr = lambda name: C.cast(getattr(self.lib, name), C.c_void_p).value
+        self.lib.rt_set_data_source(self.h, addr("ds_source_take"), addr("ds_source_release"), source_handle)
+
+    def attach_fake(self, learners: int, task_us: int = 100):
+        self._fake = self.lib.rt_fake_create(learners, task_us)
+        self.lib.rt_fake_attach(self.h, self._fake)
+        return self._fake
+
+    def inject(self, fail_task: int = -1, hang_task: int = -1):
+        self.lib.rt_fake_inject(self._fake, fail_task, hang_task)
+
+    def fake_syncs(self) -> int:
+        return self.lib.rt_fake_syncs(self._fake)
+
+    def fake_last_mask(self):
+        buf = C.create_string_buffer(256)
+        n = self.lib.rt_fake_last_mask(self._fake, buf, 256)
+        return list(buf.raw[:n])
+
+    def train(self, ntasks: int, phase: int = 0) -> int:
+        n = self.lib.rt_train(self.h, ntasks, phase)
+        if n < 0:
+            raise RuntimeError_(self.error())
+        return n
+
+    def drain(self, timeout_s: float = 60.0):
+        if self.lib.rt_drain(self.h, timeout_s) != 0:
+            raise RuntimeError_(self.error())
+
+    def stop(self):
+        self.lib.rt_stop(self.h)
+
+    def set_target_loss(self, t: float):
+        self.lib.rt_set_target_loss(self.h, t)
+
+    def add_learner(self) -> int:
+        return self.lib.rt_add_learner(self.h)
+
+    def remove_learner(self) -> int:
+        return self.lib.rt_remove_learner(self.h)
+
+    def learners(self) -> int:
+        return self.lib.rt_learners(self.h)
+
+    def clock(self) -> int:
+        return self.lib.rt_clock(self.h)
+
+    def tasks_issued(self) -> int:
+        return self.lib.rt_tasks_issued(self.h)
+
+    def tasks_completed(self) -> int:
+        return self.lib.rt_tasks_completed(self.h)
+
+    def failed(self) -> bool:
+        return bool(self.lib.rt_failed(self.h))
+
+    def error(self) -> str:
+        return self.lib.rt_error(self.h).decode()
+
+    def totals(self, reset=False):
+        ls, as_, n, ll, la = C.c_double(), C.c_double(), C.c_ulonglong(), C.c_float(), C.c_float()
+        self.lib.rt_totals(self.h, int(reset), C.byref(ls), C.byref(as_), C.byref(n), C.byref(ll), C.byref(la))
+        return dict(loss_sum=ls.value, acc_sum=as_.value, n=n.value, last_loss=ll.value, last_acc=la.value)
+
+    def history(self, n: int = 1024):
+        t, l, a = (C.c_ulonglong * n)(), (C.c_float * n)(), (C.c_float * n)()
+        m = self.lib.rt_history(self.h, t, l, a, n)
+        return [(t[i], l[i], a[i]) for i in range(m)]
+
+    def close(self):
+        if self.h:
+            self.lib.rt_destroy(self.h)
+            self.h = None
+        if self._fake:
+            self.lib.rt_fake_destroy(self._fake)
+            self._fake = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def cpu_bind(core: int) -> int:
+    return load().rt_cpu_bind(core)
+
+
+def cpu_unbind() -> int:
+    return load().rt_cpu_unbind()
+
+
+def cpu_id() -> int:
+    return load().rt_cpu_id()

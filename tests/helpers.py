@@ -39,3 +39,51 @@ def engines(name, batch, k=1, update_model=UpdateModel.SMA, wpc=None, solver=Non
     import copy
     cpu = CpuEngine(spec.train, spec.test, m, init, batch, spec.input_shape, copy.deepcopy(solver), update_model, replicas=k, wpc=wpc, seed=seed)
     return spec, m, gpu, cpu
+
+
+def tiny_vgg(solver_conf=None):
+    """Conv-ReLU-BN-Dropout blocks + FC-ReLU-BN-Dropout head: every fused pattern of VGG-16 on a well-conditioned size."""
+    from crossbow_b200.models._builder import Net
+    from crossbow_b200.types import PoolMethod
+    n = Net()
+    for item in ((16, 0.3), (16, None), "M", (32, 0.4), (32, None), "M"):
+        if item == "M":
+            n.pool("Pool", PoolMethod.MAX, 2, 2)
+            continue
+        feat, drop = item
+        n.conv("Conv", feat, 3, 1, 1, bias=True)
+        n.relu("ReLU")
+        n.bn("BatchNorm")
+        if drop:
+            n.dropout("Dropout", drop)
+    n.dropout("Dropout", 0.5)
+    n.fc("InnerProduct", 64)
+    n.relu("ReLU")
+    n.bn("BatchNorm")
+    n.dropout("Dropout", 0.5)
+    n.fc("InnerProduct", 10)
+    n.classifier_tail()
+    return n.finish("tiny-vgg", [3, 16, 16], 10, solver_conf)
+
+
+def tiny_bottleneck(solver_conf=None):
+    """Two bottleneck units (identity-free: both have projection shortcuts, one strided)."""
+    from crossbow_b200.models._builder import Net
+    from crossbow_b200.models.resnet import _bottleneck
+    from crossbow_b200.types import PoolMethod
+    n = Net()
+    n.conv("Conv", 16, 3, 1, 1)
+    n.bn("BatchNorm")
+    x = n.relu("ReLU")
+    x = _bottleneck(n, x, "u1", 16, 8, 1)
+    x = _bottleneck(n, x, "u2", 32, 8, 1)
+    x = _bottleneck(n, x, "u3", 32, 16, 2)
+    n.pool("Pool", PoolMethod.AVERAGE, 1, 1, global_pooling=True)
+    n.fc("InnerProduct", 10)
+    n.classifier_tail()
+    return n.finish("tiny-bottleneck", [3, 16, 16], 10, solver_conf)
+
+
+from crossbow_b200.models import REGISTRY as _REG
+_REG.setdefault("tiny-vgg", tiny_vgg)
+_REG.setdefault("tiny-bottleneck", tiny_bottleneck)

@@ -1,0 +1,134 @@
+"""Native host runtime against a fake executor: scheduling order, clocks, synchronisation models, auto-tuner slots,
+result ring, failure detection (failed task, stuck task -> watchdog) - all injected on the host, no GPU involved."""
+import threading
+import time
+
+import pytest
+
+from crossbow_b200.runtime import Runtime, RuntimeError_, ThetaQueue, cpu_bind, cpu_id, cpu_unbind
+
+
+def test_theta_queue_round_robin_expand_shrink():
+    q = ThetaQueue(3)
+    got = [q.next() for _ in range(3)]
+    assert got == [0, 1, 2]
+    assert q.next(0.05) == -1            # all busy: bounded wait reports failure instead of spinning for ever
+    q.release(1)
+    # strict round robin: the cursor is at slot 0, which is still busy
+    assert q.next(0.05) == -1
+    q.release(0)
+    assert q.next() == 0 and q.next() == 1
+    i = q.expand()
+    assert i == 3 and q.size() == 4 and q.enabled() == 4
+    q.release(3)
+    q.release(2)
+    assert q.shrink() == 3 and q.enabled() == 3
+    q.release(0)
+    q.release(1)
+    assert sorted(q.next() for _ in range(3)) == [0, 1, 2]   # the disabled slot is skipped from now on
+    assert q.next(0.05) == -1
+
+
+@pytest.mark.parametrize("handlers", [0, 2])
+def test_tasks_results_and_clock(handlers):
+    rt = Runtime(learners=4, wpc=4, task_handlers=handlers, callback_handlers=2, task_timeout_s=5)
+    rt.attach_fake(4, task_us=200)
+    assert rt.train(40) == 40
+    rt.drain(10)
+    assert rt.tasks_completed() == 40 and rt.clock() == 10 and rt.fake_syncs() == 10
+    hist = rt.history(64)
+    assert [h[0] for h in hist] == list(range(40))           # collected strictly in task order
+    assert all(abs(h[1] - 1.0 / (1 + h[0])) < 1e-6 for h in hist)
+    assert sorted(set(int(h[2]) for h in hist)) == [0, 1, 2, 3]   # every learner took part, round robin
+    assert [int(h[2]) for h in hist[:8]] == [0, 1, 2, 3, 0, 1, 2, 3]
+    t = rt.totals()
+    assert t["n"] == 40 and abs(t["last_loss"] - 1.0 / 40) < 1e-6
+    rt.close()
+
+
+def test_bsp_masks_all_ssp_masks_idle_only():
+    rt = Runtime(learners=3, wpc=3, sync_model=0)
+    rt.attach_fake(3, task_us=2000)
+    rt.train(3)
+    assert rt.fake_last_mask() == [1, 1, 1]
+    rt.drain(5)
+    rt.close()
+    rt = Runtime(learners=3, wpc=3, slack=2, sync_model=1)
+    rt.attach_fake(3, task_us=20000)
+    rt.train(3)                           # the synchronisation is issued while all three tasks still run
+    assert rt.fake_syncs() == 0 and rt.clock() == 1      # nobody was idle: the clock ticks, nothing is synchronised
+    rt.drain(5)
+    rt.close()
+
+
+def test_staleness_bound_blocks_stale_replicas():
+    # SSP with slack 0: a replica that missed the synchronisation may not take a new task until it has been synchronised
+    rt = Runtime(learners=2, wpc=2, slack=0, sync_model=1, task_timeout_s=0.3)
+    rt.attach_fake(2, task_us=50000)
+    rt.train(2)                           # sync skipped both replicas (busy) -> their clocks stay at 0, global clock is 1
+    rt.drain(5)
+    assert rt.clock() == 1
+    # bound = clock - slack - 1 = 0 -> still allowed; after another clock the stale replicas are refused
+    rt.train(2)
+    rt.drain(5)
+    with pytest.raises(RuntimeError_):
+        rt.train(2)
+    assert "no replica became free" in rt.error()
+    rt.close()
+
+
+def test_auto_tuner_slots():
+    rt = Runtime(learners=1, wpc=1)
+    rt.attach_fake(8, task_us=100)
+    rt.train(4)
+    rt.drain(5)
+    assert rt.add_learner() == 1 and rt.learners() == 2
+    rt.train(6)
+    rt.drain(5)
+    assert sorted(set(int(h[2]) for h in rt.history(6))) == [0, 1]
+    assert rt.remove_learner() == 1 and rt.learners() == 1
+    rt.train(3)
+    rt.drain(5)
+    assert all(int(h[2]) == 0 for h in rt.history(3))
+    rt.close()
+
+
+def test_failed_task_is_reported_not_fatal():
+    rt = Runtime(learners=2, wpc=100, task_timeout_s=2)
+    rt.attach_fake(2, task_us=100)
+    rt.inject(fail_task=5)
+    with pytest.raises(RuntimeError_) as e:
+        rt.train(50)
+        rt.drain(5)
+    assert "task 5 failed on learner 1 with code 77" in str(e.value)
+    assert rt.failed()
+    rt.close()
+
+
+def test_watchdog_detects_stuck_task():
+    rt = Runtime(learners=2, wpc=100, task_timeout_s=0.3)
+    rt.attach_fake(2, task_us=100)
+    rt.inject(hang_task=3)                # its completion takes 1.5 s, far beyond the 0.3 s deadline
+    t0 = time.time()
+    with pytest.raises(RuntimeError_):
+        rt.train(20)
+        rt.drain(5)
+    assert time.time() - t0 < 3.0
+    assert "watchdog" in rt.error() or "no replica became free" in rt.error()
+    rt.close()
+
+
+def test_target_loss_stops_dispatch():
+    rt = Runtime(learners=2, wpc=2)
+    rt.attach_fake(2, task_us=1000)
+    rt.set_target_loss(0.1)               # fake loss = 1/(1+task) reaches 0.1 at task 9
+    n = rt.train(10000)
+    rt.drain(5)
+    assert 10 <= n < 200
+    rt.close()
+
+
+def test_cpu_affinity():
+    assert cpu_bind(0) == 0
+    assert cpu_id() == 0
+    assert cpu_unbind() == 0

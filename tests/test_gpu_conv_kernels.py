@@ -1,0 +1,120 @@
+"""Convolution / inner-product kernels in isolation against torch.nn.functional on the same device (fp32 reference,
+TF32 disabled), for the CUDA-core (exact fp32) and tensor-core (tf32 operands) implementations."""
+import ctypes as C
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    # N, H, W, C, K, R, S, stride, pad
+    (4, 32, 32, 16, 16, 3, 3, 1, 1),
+    (4, 32, 32, 16, 32, 3, 3, 2, 1),
+    (4, 16, 16, 32, 32, 3, 3, 1, 1),
+    (4, 16, 16, 16, 32, 1, 1, 2, 0),
+    (3, 9, 7, 8, 24, 3, 3, 1, 1),       # odd sizes, K not a multiple of 16
+    (2, 14, 14, 64, 256, 1, 1, 1, 0),
+    (2, 14, 14, 128, 320, 3, 3, 1, 1),  # more than 256 output channels (two N tiles)
+    (2, 12, 12, 4, 20, 5, 5, 1, 2),
+    (64, 1, 1, 256, 10, 1, 1, 1, 0),    # inner product
+    (5, 1, 1, 1000, 520, 1, 1, 1, 0),
+    (2, 23, 23, 12, 16, 7, 7, 2, 3),
+]
+
+
+def _geom(lib_mod, N, H, W, Cc, K, R, S, st, pad):
+    g = lib_mod.XbConvGeom()
+    P = (H + 2 * pad - R) // st + 1
+    Q = (W + 2 * pad - S) // st + 1
+    g.N, g.H, g.W, g.C, g.K, g.R, g.S, g.P, g.Q, g.sh, g.sw, g.ph, g.pw = N, H, W, Cc, K, R, S, P, Q, st, st, pad, pad
+    return g, P, Q
+
+
+@pytest.fixture(scope="module")
+def env():
+    from crossbow_b200.ops import lib as L
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return L, L.init_device()
+
+
+@pytest.mark.parametrize("impl", ["simt", "tc"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_fprop_dgrad_wgrad(env, impl, shape):
+    L, lib = env
+    N, H, W, Cc, K, R, S, st, pad = shape
+    g, P, Q = _geom(L, *shape)
+    if impl == "tc" and not lib.xb_tc_supported(C.byref(g), 0):
+        pytest.skip("shape not covered by the tensor-core path")
+    tol = 1e-4 if impl == "simt" else 4e-3
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(N, H, W, Cc, device=dev, generator=gen)
+    w = torch.randn(K, R, S, Cc, device=dev, generator=gen) * (1.0 / (R * S * Cc) ** 0.5)
+    b = torch.randn(K, device=dev, generator=gen)
+    dy = torch.randn(N, P, Q, K, device=dev, generator=gen)
+    xr = x.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    wr = w.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    yr = F.conv2d(xr, wr, b, stride=st, padding=pad)
+    yr.backward(dy.permute(0, 3, 1, 2))
+    y_ref = F.relu(yr.detach()).permute(0, 2, 3, 1)
+    s = torch.cuda.current_stream().cuda_stream
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    # forward with bias + ReLU + statistics
+    y = torch.full((N, P, Q, K), 7.0, device=dev)
+    stats = torch.zeros(2 * K, device=dev)
+    flags = 1 | 4
+    if impl == "simt":
+        L.check(lib.xb_conv_fprop_simt(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), stats.data_ptr(), C.byref(g), flags, s), "fprop")
+    else:
+        L.check(lib.xb_conv_fprop_tc(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), stats.data_ptr(), C.byref(g), flags, status.data_ptr(), s), "fprop")
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    scale = float(y_ref.abs().max()) + 1e-6
+    assert float((y - y_ref).abs().max()) / scale < tol
+    m = y_ref.reshape(-1, K)
+    assert torch.allclose(stats[:K], m.sum(0), rtol=tol * 10, atol=tol * 10 * m.shape[0] ** 0.5)
+    assert torch.allclose(stats[K:], (m * m).sum(0), rtol=tol * 10, atol=tol * 10 * m.shape[0] ** 0.5)
+
+    # data gradient (with and without accumulation) through the transposed weight copy
+    wt = w.permute(3, 1, 2, 0).contiguous()
+    dx_ref = xr.grad.permute(0, 2, 3, 1)
+    for accum in (0, 1):
+        dx = torch.full((N, H, W, Cc), 0.5, device=dev)
+        if impl == "simt" or not lib.xb_tc_supported(C.byref(g), 1):
+            L.check(lib.xb_conv_dgrad_simt(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), C.byref(g), accum, s), "dgrad")
+        else:
+            L.check(lib.xb_conv_dgrad_tc(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), C.byref(g), accum, status.data_ptr(), s), "dgrad")
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        ref = dx_ref + (0.5 if accum else 0.0)
+        assert float((dx - ref).abs().max()) / (float(dx_ref.abs().max()) + 1e-6) < tol
+
+    # weight gradient
+    dw = torch.zeros(K, R, S, Cc, device=dev)
+    if impl == "simt" or not lib.xb_tc_supported(C.byref(g), 2):
+        L.check(lib.xb_conv_wgrad_simt(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), s), "wgrad")
+    else:
+        L.check(lib.xb_conv_wgrad_tc(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), status.data_ptr(), s), "wgrad")
+    torch.cuda.synchronize()
+    dw_ref = wr.grad.permute(0, 2, 3, 1)
+    assert float((dw - dw_ref).abs().max()) / (float(dw_ref.abs().max()) + 1e-6) < (tol if impl == "tc" else 2e-4)
+
+
+def test_first_layer_three_channels(env):
+    """C=3 takes the scalar CUDA-core path in every direction."""
+    L, lib = env
+    shape = (4, 32, 32, 3, 16, 3, 3, 1, 1)
+    g, P, Q = _geom(L, *shape)
+    assert not lib.xb_tc_supported(C.byref(g), 0)
+    dev = torch.device("cuda")
+    x = torch.randn(4, 32, 32, 3, device=dev)
+    w = torch.randn(16, 3, 3, 3, device=dev)
+    y = torch.empty(4, P, Q, 16, device=dev)
+    s = torch.cuda.current_stream().cuda_stream
+    L.check(lib.xb_conv_fprop_simt(x.data_ptr(), w.data_ptr(), 0, y.data_ptr(), 0, C.byref(g), 0, s), "fprop")
+    ref = F.conv2d(x.permute(0, 3, 1, 2), w.permute(0, 3, 1, 2), padding=1).permute(0, 2, 3, 1)
+    assert torch.allclose(y, ref, rtol=1e-4, atol=1e-4)
