@@ -10,10 +10,17 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
-// bounded parity wait; false on expiry
+// Parity wait bounded by wall-clock time (1 s): mbarrier.try_wait may itself suspend the thread for an
+// implementation-defined while, so an iteration count alone does not bound the wait.  false on expiry.
+__device__ __forceinline__ unsigned long long tc_global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t a = smem_u32(bar);
-  for (int it = 0; it < (1 << 22); ++it) {
+  unsigned long long t0 = 0;
+  for (int it = 0;; ++it) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -21,9 +28,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(a), "r"(parity) : "memory");
     if (ok) return true;
-    if (it > 1024) __nanosleep(128);
+    if (it == 64) t0 = tc_global_ns();
+    if (it > 64) {
+      __nanosleep(64);
+      if (tc_global_ns() - t0 > 1000000000ull) return false;
+    }
   }
-  return false;
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }

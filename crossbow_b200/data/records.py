@@ -1,0 +1,136 @@
+"""Record files (JPEG + label + bounding boxes) and the double-buffered, multi-threaded decoding data set
+(csrc/data/record.cpp): the ImageNet path of the reference (RecordDataset.java:59-99, clib-multigpu/recorddataset.c,
+doublebuffer.c, image/*.c)."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..runtime import load as _load
+from .dataset import Dataset
+from .native import _tensor
+
+_ready = False
+
+
+def _lib():
+    global _ready
+    lib = _load()
+    if not _ready:
+        P, I, L, F = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+        V = C.POINTER(C.c_void_p)
+        lib.rec_jpeg_decode.restype, lib.rec_jpeg_decode.argtypes = I, [P, L, P, L, C.POINTER(I), C.POINTER(I)]
+        lib.rec_process.restype, lib.rec_process.argtypes = I, [P, L, C.POINTER(F), I, I, I, C.c_ulonglong, P]
+        lib.rec_writer_open.restype, lib.rec_writer_open.argtypes = P, [C.c_char_p]
+        lib.rec_writer_append.restype, lib.rec_writer_append.argtypes = I, [P, P, L, I, C.POINTER(F), I, I, I]
+        lib.rec_writer_close.restype, lib.rec_writer_close.argtypes = I, [P]
+        lib.rec_dataset_open.restype = P
+        lib.rec_dataset_open.argtypes = [C.POINTER(C.c_char_p), I, I, I, I, I, I, C.c_ulonglong]
+        lib.rec_dataset_buffer.restype, lib.rec_dataset_buffer.argtypes = P, [P, I, I, C.POINTER(L)]
+        lib.rec_dataset_take.restype, lib.rec_dataset_take.argtypes = I, [P, L, V, V, C.c_double]
+        lib.rec_dataset_release.restype, lib.rec_dataset_release.argtypes = None, [P, I]
+        for n in ("rec_dataset_examples", "rec_dataset_failures", "rec_dataset_images"):
+            getattr(lib, n).restype, getattr(lib, n).argtypes = L, [P]
+        lib.rec_dataset_close.restype, lib.rec_dataset_close.argtypes = None, [P]
+        lib.rec_source_create.restype, lib.rec_source_create.argtypes = P, [P, L, L, C.c_double]
+        _ready = True
+    return lib
+
+
+def decode_jpeg(data: bytes) -> np.ndarray:
+    """Baseline JPEG -> uint8 RGB array [H, W, 3]."""
+    lib = _lib()
+    w, h = C.c_int(), C.c_int()
+    out = np.zeros(1, dtype=np.uint8)
+    rc = lib.rec_jpeg_decode(data, len(data), out.ctypes.data, 0, C.byref(w), C.byref(h))
+    if rc not in (0, -3):
+        raise ValueError(f"JPEG decoder error {rc} ({'unsupported coding process' if rc == -2 else 'malformed stream'})")
+    out = np.zeros((h.value, w.value, 3), dtype=np.uint8)
+    rc = lib.rec_jpeg_decode(data, len(data), out.ctypes.data, out.size, C.byref(w), C.byref(h))
+    if rc != 0:
+        raise ValueError(f"JPEG decoder error {rc}")
+    return out
+
+
+def preprocess(data: bytes, boxes: Sequence[Sequence[float]] = (), training: bool = True, size: int = 224, seed: int = 0) -> np.ndarray:
+    """One record through the train / test pipeline -> float32 [3, size, size] in [-1, 1]."""
+    lib = _lib()
+    b = np.asarray(boxes, dtype=np.float32).reshape(-1, 4)
+    out = np.empty((3, size, size), dtype=np.float32)
+    rc = lib.rec_process(data, len(data), b.ctypes.data_as(C.POINTER(C.c_float)), b.shape[0], int(training), size, seed, out.ctypes.data)
+    if rc != 0:
+        raise ValueError(f"JPEG decoder error {rc}")
+    return out
+
+
+class RecordWriter:
+    def __init__(self, path: str):
+        self.lib = _lib()
+        self.h = self.lib.rec_writer_open(path.encode())
+        if not self.h:
+            raise IOError(f"cannot create {path}")
+
+    def append(self, jpeg: bytes, label: int, boxes: Sequence[Sequence[float]] = (), height: int = 0, width: int = 0):
+        b = np.asarray(boxes, dtype=np.float32).reshape(-1, 4)
+        self.lib.rec_writer_append(self.h, jpeg, len(jpeg), label, b.ctypes.data_as(C.POINTER(C.c_float)), b.shape[0], height, width)
+        return self
+
+    def close(self) -> int:
+        n = self.lib.rec_writer_close(self.h)
+        self.h = None
+        return n
+
+
+class RecordDataset(Dataset):
+    """Two page-locked halves of ``batches_per_half`` batches; ``workers`` threads decode + augment into the idle half."""
+
+    def __init__(self, paths: Sequence[str], batch_size: int, batches_per_half: int = 32, image_size: int = 224, workers: int = 4,
+                 training: bool = True, seed: int = 0, register_with_cuda: bool = False, timeout_s: float = 60.0):
+        self.lib = _lib()
+        arr = (C.c_char_p * len(paths))(*[p.encode() for p in paths])
+        self.h = self.lib.rec_dataset_open(arr, len(paths), batch_size, batches_per_half, image_size, workers, int(training), seed)
+        if not self.h:
+            raise IOError("cannot open the record files")
+        self.batch_size, self.example_shape, self.nb, self.timeout_s = batch_size, (3, image_size, image_size), batches_per_half, timeout_s
+        self._held = []
+        if register_with_cuda:
+            from ..ops import lib as L
+            cl = L.load()
+            for half in (0, 1):
+                for which in (0, 1):
+                    n = C.c_longlong()
+                    p = self.lib.rec_dataset_buffer(self.h, half, which, C.byref(n))
+                    L.check(cl.xb_host_register(p, n.value), "cudaHostRegister of the double buffer")
+
+    def number_of_examples(self):
+        n = self.lib.rec_dataset_examples(self.h)
+        return n // self.batch_size * self.batch_size
+
+    def batch(self, task: int):
+        """Batches must be requested in increasing order; earlier batches are released when the next half is entered."""
+        e, l = C.c_void_p(), C.c_void_p()
+        while self._held and self._held[0][0] // self.nb < task // self.nb:
+            self.lib.rec_dataset_release(self.h, self._held.pop(0)[1])
+        half = self.lib.rec_dataset_take(self.h, task, C.byref(e), C.byref(l), self.timeout_s)
+        if half < 0:
+            raise TimeoutError("the decoders did not refill the buffer in time")
+        self._held.append((task, half))
+        return _tensor(e.value, (self.batch_size,) + self.example_shape, torch.float32), _tensor(l.value, (self.batch_size,), torch.int32)
+
+    def decode_failures(self):
+        return self.lib.rec_dataset_failures(self.h)
+
+    def source(self, stride: int = 1, offset: int = 0, timeout_s: float = 60.0) -> int:
+        self._source = self.lib.rec_source_create(self.h, stride, offset, timeout_s)
+        return self._source
+
+    def close(self):
+        for _, half in self._held:
+            self.lib.rec_dataset_release(self.h, half)
+        self._held = []
+        if self.h:
+            self.lib.rec_dataset_close(self.h)
+            self.h = None
