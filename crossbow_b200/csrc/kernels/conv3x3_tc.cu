@@ -93,7 +93,11 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __r
   tc_fence_after();
   const uint32_t tmem = s_tmem;
 
-  if (tid == 0) {
+  // The whole of warp 0 takes this branch and re-converges at the __syncwarp below BEFORE any of its lanes starts to
+  // poll the completion barrier: lanes that spin in mbarrier.try_wait (which may suspend them) while a sibling lane of
+  // the same warp still has instructions to issue would starve that lane.
+  if (warp == 0) {
+   if (lane == 0) {
     const int k8s = g.C >> 3;
     uint32_t acc = 0;
     for (int tap = 0; tap < 9; ++tap) {
@@ -107,6 +111,8 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __r
       }
     }
     umma_commit(&bar_done);
+   }
+   __syncwarp();
   }
   if (!mbar_wait(&bar_done, 0)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
   tc_fence_after();

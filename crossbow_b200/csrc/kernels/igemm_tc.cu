@@ -133,7 +133,10 @@ __global__ void __launch_bounds__(NTHREADS) igemm_tc_kernel(const float* __restr
     asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");     // this thread's share of slice kt has landed
     fence_async_smem();
     __syncthreads();                                                         // ... and everybody else's
-    if (tid == 0 && alive) {
+    // warp 0 re-converges (__syncwarp) before any of its lanes goes on to poll a barrier: a lane that is suspended in
+    // mbarrier.try_wait must never share a warp with the lane that still has to issue the MMAs
+    if (warp == 0) {
+     if (lane == 0 && alive) {
       tc_fence_after();
       const uint32_t a0 = smem_u32(sA + s * A_STAGE), b0 = smem_u32(sB + s * B_STAGE);
 #pragma unroll
@@ -143,6 +146,8 @@ __global__ void __launch_bounds__(NTHREADS) igemm_tc_kernel(const float* __restr
         umma_tf32(tmem, ad, bd, IDESC, (kt > 0 || k4 > 0) ? 1u : 0u);
       }
       umma_commit(&bar_empty[s]);
+     }
+     __syncwarp();
     }
     // refill the stage that slice kt-1 used (its MMAs were committed one iteration ago)
     const int nt = kt + STAGES - 1;
@@ -156,7 +161,10 @@ __global__ void __launch_bounds__(NTHREADS) igemm_tc_kernel(const float* __restr
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
-  if (tid == 0 && alive) umma_commit(&bar_done);
+  if (warp == 0) {
+    if (lane == 0 && alive) umma_commit(&bar_done);
+    __syncwarp();
+  }
   if (alive && !mbar_wait(&bar_done, 0)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
   tc_fence_after();
   __syncthreads();

@@ -362,7 +362,19 @@ class CpuEngine:
         return self.results.pop(learner)
 
     def synchronise(self, copy=False, learners=None):
-        synchronise(self.update_model, self.devs, self.solver, self.wpc, copy)
+        """With ``torch.distributed`` initialised (gloo) every process holds one device group and the partial sums are
+        all-reduced across processes: the host-side twin of the multi-GPU path."""
+        import torch.distributed as dist
+        ar, world = None, 1
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            world = dist.get_world_size()
+
+            def ar(t):
+                t = t.clone()
+                dist.all_reduce(t)
+                return t
+        synchronise(self.update_model, self.devs, self.solver, self.wpc * world if self.update_model == UpdateModel.WORKER else self.wpc,
+                    copy, allreduce=ar, world=world)
 
     def add_learner(self):
         for d in self.devs:

@@ -227,8 +227,13 @@ def local_update(r: ReplicaState, dev: DeviceState, s: SolverConf, update_model:
 # Synchronisation algorithms (one call = one clock)
 # --------------------------------------------------------------------------------------------
 
+def _reduce(total: torch.Tensor, allreduce) -> torch.Tensor:
+    """Sum over the devices of THIS process is in ``total``; ``allreduce`` (if given) adds the other processes'."""
+    return allreduce(total) if allreduce is not None else total
+
+
 def synchronise_sma(devs: Sequence[DeviceState], alpha: float, base_momentum: float = 0.9, copy: bool = False,
-                    use_prev: bool = True):
+                    use_prev: bool = True, allreduce=None):
     """Synchronous model averaging over k replicas x G devices.
 
     Per device d: D_r = alpha*(prev_r - z_d); w_r -= D_r; G_d = sum_r D_r.  Then D = sum_d G_d (all-reduce);
@@ -243,7 +248,7 @@ def synchronise_sma(devs: Sequence[DeviceState], alpha: float, base_momentum: fl
             diff = alpha * (src - d.z)
             r.w -= diff
             d.G += diff
-    total = sum((d.G for d in devs[1:]), devs[0].G.clone())
+    total = _reduce(sum((d.G for d in devs[1:]), devs[0].G.clone()), allreduce)
     for d in devs:
         D = total.clone()
         if base_momentum > 0:
@@ -255,9 +260,9 @@ def synchronise_sma(devs: Sequence[DeviceState], alpha: float, base_momentum: fl
                 r.w = d.z.clone()
 
 
-def synchronise_ssgd(devs: Sequence[DeviceState], wpc: int, momentum: float):
+def synchronise_ssgd(devs: Sequence[DeviceState], wpc: int, momentum: float, allreduce=None):
     """S-SGD: all-reduce the accumulated -lr*(g+wd*w), scale by 1/wpc, momentum, apply to z, copy z to replicas."""
-    total = sum((d.G for d in devs[1:]), devs[0].G.clone())
+    total = _reduce(sum((d.G for d in devs[1:]), devs[0].G.clone()), allreduce)
     for d in devs:
         D = total / float(wpc)
         if momentum > 0:
@@ -276,7 +281,7 @@ def synchronise_default(devs: Sequence[DeviceState]):
             r.w = d.z.clone()
 
 
-def synchronise_eamsgd(devs: Sequence[DeviceState], alpha: float, base_momentum: float = 0.0):
+def synchronise_eamsgd(devs: Sequence[DeviceState], alpha: float, base_momentum: float = 0.0, allreduce=None):
     """Elastic averaging, synchronous variant: each replica is pulled towards z by alpha*(w_r - z) and z moves
     by the sum of the pulls (optionally with momentum on z).  Multi-device: pulls are summed across devices."""
     for d in devs:
@@ -285,7 +290,7 @@ def synchronise_eamsgd(devs: Sequence[DeviceState], alpha: float, base_momentum:
             diff = alpha * (r.w - d.z)
             r.w -= diff
             d.G += diff
-    total = sum((d.G for d in devs[1:]), devs[0].G.clone())
+    total = _reduce(sum((d.G for d in devs[1:]), devs[0].G.clone()), allreduce)
     for d in devs:
         D = total.clone()
         if base_momentum > 0:
@@ -294,11 +299,11 @@ def synchronise_eamsgd(devs: Sequence[DeviceState], alpha: float, base_momentum:
         d.z += D
 
 
-def synchronise_polyak_ruppert(devs: Sequence[DeviceState], alpha: float = 0.0):
+def synchronise_polyak_ruppert(devs: Sequence[DeviceState], alpha: float = 0.0, allreduce=None, world: int = 1):
     """z becomes the running average (factor 1/(count+1)) of the mean of all replicas; optional elastic pull of
     the replicas towards z with strength alpha (polyakruppert.c:5-138)."""
-    n = sum(len(d.replicas) for d in devs)
-    mean = sum((r.w for d in devs for r in d.replicas)) / float(n)
+    n = sum(len(d.replicas) for d in devs) * world
+    mean = _reduce(sum((r.w for d in devs for r in d.replicas)), allreduce) / float(n)
     for d in devs:
         f = 1.0 / (d.avg_count + 1.0)
         d.z = (1.0 - f) * d.z + f * mean
@@ -317,18 +322,20 @@ def sma_base_momentum(solver: SolverConf) -> float:
     return 0.9 if solver.momentum > 0 else 0.0
 
 
-def synchronise(update_model: UpdateModel, devs: Sequence[DeviceState], solver: SolverConf, wpc: int, copy=False):
-    """Dispatch as clib-multigpu/executioncontext.c:2262-2334 does."""
+def synchronise(update_model: UpdateModel, devs: Sequence[DeviceState], solver: SolverConf, wpc: int, copy=False,
+                allreduce=None, world: int = 1):
+    """Dispatch as clib-multigpu/executioncontext.c:2262-2334 does.  ``allreduce`` sums a tensor over processes
+    (one process per device group); ``world`` is the number of such processes."""
     if update_model in (UpdateModel.SMA, UpdateModel.SYNCHRONOUSEAMSGD):
-        synchronise_sma(devs, solver.alpha, sma_base_momentum(solver), copy)
+        synchronise_sma(devs, solver.alpha, sma_base_momentum(solver), copy, allreduce=allreduce)
     elif update_model == UpdateModel.WORKER:
-        synchronise_ssgd(devs, wpc, solver.momentum)
+        synchronise_ssgd(devs, wpc, solver.momentum, allreduce=allreduce)
     elif update_model == UpdateModel.DEFAULT:
         synchronise_default(devs)
     elif update_model == UpdateModel.EAMSGD:
-        synchronise_eamsgd(devs, solver.alpha, solver.base_model_momentum)
+        synchronise_eamsgd(devs, solver.alpha, solver.base_model_momentum, allreduce=allreduce)
     elif update_model == UpdateModel.POLYAK_RUPPERT:
-        synchronise_polyak_ruppert(devs, 0.0)
+        synchronise_polyak_ruppert(devs, 0.0, allreduce=allreduce, world=world)
     else:
         raise NotImplementedError(f"error: {update_model} is not supported (stub in the reference as well)")
     for d in devs:
