@@ -174,6 +174,130 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __r
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+
+// ---- weight gradient of a 3x3 / stride 1 / pad 1 convolution -------------------------------------------------------------
+// dW[k][tap][c] = sum over positions of dY[pos][k] * X[pos + shift(tap)][c].  The reduction runs over POSITIONS, and in the
+// slab layout [16-byte channel chunk][position][16 B] a group of 8 consecutive positions x 4 channels is one contiguous
+// 128-byte core matrix - exactly the canonical MN-major no-swizzle operand (MN = channel, K = position; stride between
+// channel chunks = SBO, between groups of 8 positions = LBO = 128 B).  So the SAME two slabs serve as operands again:
+//   A = dY tile   (M = output channels, padded to 128 by zero planes)      B = X slab shifted by the tap (N = input channels)
+// A persistent CTA walks position tiles, accumulating nine [128 x BN] products (one per tap) in 9*BN TMEM columns, and
+// adds its partial dW to global memory once at the end.
+template <int BN>
+__global__ void __launch_bounds__(NTHREADS) conv3x3_wgrad_slab_kernel(const float* __restrict__ dY, const float* __restrict__ X,
+                                                                      float* __restrict__ dW, SlabProblem g, int ntiles, int* status) {
+  constexpr uint32_t TMEM_COLS = 9 * BN <= 256 ? 256 : 512;
+  // M = 128, N = BN, both operands MN-major (bits 15 and 16)
+  constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bar_done;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int PW = g.W + 2, PR = g.H + 1;
+  const int S = BM + 2 * PW + 2;
+  const int KQ = g.K >> 2;                             // real 16-byte chunks of dY (output channels / 4)
+  const int c0 = blockIdx.y * BN;                      // first input channel of this CTA's N tile
+  constexpr uint32_t planeA = BM * 16u;                // dY tile: 32 planes x 128 positions x 16 B
+  const uint32_t planeB = (uint32_t)S * 16u;
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + 32 * planeA;              // [BN/4 planes][S positions][16 B]
+  const uint32_t a_u32 = smem_u32(sA), b_u32 = smem_u32(sB);
+
+  if (tid == 0) { mbar_init(&bar_done, 1); s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+  if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);
+  // planes of A beyond the real output channels stay zero for the whole kernel
+  for (int i = tid; i < (32 - KQ) * BM; i += NTHREADS) reinterpret_cast<float4*>(sA + (size_t)KQ * planeA)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+
+  uint32_t phase = 0;
+  bool first = true, alive = true;
+  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const long long q0 = (long long)tile * BM, qs = q0 - PW - 1;
+    if (!first) {                                       // the previous tile's MMAs must have consumed shared memory
+      if (alive && !mbar_wait(&bar_done, phase)) { alive = false; s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
+      phase ^= 1;
+      __syncthreads();
+    }
+    // dY tile: position m = tid, zero for padding positions
+    {
+      const long long p = q0 + tid;
+      const float* src = dY; uint32_t bytes = 0;
+      if (p < g.positions) {
+        int xx = (int)(p % PW); long long t = p / PW; int yy = (int)(t % PR); int n = (int)(t / PR);
+        if (yy >= 1 && xx >= 1 && xx <= g.W) { src = dY + (((long long)n * g.H + (yy - 1)) * g.W + (xx - 1)) * g.K; bytes = 16; }
+      }
+      for (int c = 0; c < KQ; ++c)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_u32 + c * planeA + tid * 16), "l"(src + (bytes ? c * 4 : 0)), "r"(bytes) : "memory");
+    }
+    // X slab (with halo), only this CTA's BN input channels
+    for (int j = tid; j < S; j += NTHREADS) {
+      const long long p = qs + j;
+      const float* src = X; uint32_t bytes = 0;
+      if (p >= 0 && p < g.positions) {
+        int xx = (int)(p % PW); long long t = p / PW; int yy = (int)(t % PR); int n = (int)(t / PR);
+        if (yy >= 1 && xx >= 1 && xx <= g.W) { src = X + (((long long)n * g.H + (yy - 1)) * g.W + (xx - 1)) * g.C + c0; bytes = 16; }
+      }
+      for (int c = 0; c < BN / 4; ++c) {
+        uint32_t b = (bytes && c0 + c * 4 < g.C) ? 16u : 0u;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(b_u32 + c * planeB + j * 16), "l"(src + (b ? c * 4 : 0)), "r"(b) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+      if (lane == 0 && alive) {
+        tc_fence_after();
+        for (int tap = 0; tap < 9; ++tap) {
+          const int r = tap / 3, s = tap - 3 * r;
+          const uint32_t shift = (uint32_t)(r * PW + s) * 16u;
+#pragma unroll 4
+          for (int j = 0; j < BM / 8; ++j) {             // 8 positions per MMA
+            uint64_t ad = make_desc(a_u32 + j * 128, 128, planeA);
+            uint64_t bd = make_desc(b_u32 + shift + j * 128, 128, planeB);
+            umma_tf32(tmem + tap * BN, ad, bd, IDESC, (first && j == 0) ? 0u : 1u);
+          }
+        }
+        umma_commit(&bar_done);
+      }
+      __syncwarp();
+    }
+    first = false;
+  }
+  if (!first && alive && !mbar_wait(&bar_done, phase)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
+  tc_fence_after();
+  __syncthreads();
+  if (!s_abort && !first) {
+    const int k = warp * 32 + lane;                      // output channel = TMEM lane
+    const bool warp_has_rows = warp * 32 < g.K;          // whole-warp condition: tcgen05.ld is warp-collective
+    if (warp_has_rows) {
+      for (int tap = 0; tap < 9; ++tap)
+#pragma unroll
+        for (int cc = 0; cc < BN; cc += 16) {
+          float v[16];
+          tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(tap * BN + cc), v);
+          if (k < g.K) {
+            float* o = dW + ((long long)k * 9 + tap) * g.C + c0 + cc;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (c0 + cc + j < g.C) atomicAdd(o + j, v[j]);
+          }
+        }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+inline size_t wgrad_smem_bytes(int W, int BN) { return (size_t)32 * BM * 16 + (size_t)(BN / 4) * (BM + 2 * (W + 2) + 2) * 16; }
+
 inline size_t slab_smem_bytes(int W, int C, int BN) {
   size_t S = BM + 2 * (W + 2) + 2;
   return (size_t)(C / 4) * S * 16 + (size_t)9 * (C / 4) * BN * 16;
@@ -195,6 +319,7 @@ inline int pick_bn(int K) { return K <= 16 ? 16 : K <= 32 ? 32 : K <= 64 ? 64 : 
 // 1 if the slab kernel covers this geometry in direction `which` (0 fprop, 1 dgrad)
 XB_API int xb_conv3x3_slab_supported(const XbConvGeom* g, int which) {
   if (g->R != 3 || g->S != 3 || g->sh != 1 || g->sw != 1 || g->ph != 1 || g->pw != 1) return 0;
+  if (which == 2) return (g->C % 16 == 0 && g->K % 4 == 0 && g->K <= 128 && wgrad_smem_bytes(g->W, 32) <= kSmemLimit) ? 1 : 0;
   int Cred = which == 0 ? g->C : g->K, Kout = which == 0 ? g->K : g->C;
   if (Cred % 8 || Kout % 4) return 0;
   return slab_smem_bytes(g->W, Cred, pick_bn(Kout)) <= kSmemLimit ? 1 : 0;
@@ -206,8 +331,24 @@ XB_API int xb_conv3x3_slab_init() {
   if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
   if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
   if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_wgrad_slab_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_wgrad_slab_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
   return 0;
 }
+// dW (K,3,3,C) must hold the value to accumulate onto (normally zero).
+XB_API int xb_conv3x3_wgrad_slab(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st) {
+  SlabProblem g;
+  g.N = cg->N; g.H = cg->H; g.W = cg->W; g.C = cg->C; g.K = cg->K; g.mirrored = 0;
+  g.positions = (long long)cg->N * (cg->H + 1) * (cg->W + 2);
+  const int ntiles = (int)((g.positions + BM - 1) / BM);
+  const int BN = cg->C <= 16 ? 16 : 32;
+  dim3 grid((unsigned)(ntiles < 148 ? ntiles : 148), (unsigned)((cg->C + BN - 1) / BN));
+  if (grid.y > 1 && grid.x * grid.y > 296) grid.x = 296 / grid.y;
+  if (BN == 16) conv3x3_wgrad_slab_kernel<16><<<grid, NTHREADS, wgrad_smem_bytes(g.W, 16), st>>>(dY, X, dW, g, ntiles, status);
+  else          conv3x3_wgrad_slab_kernel<32><<<grid, NTHREADS, wgrad_smem_bytes(g.W, 32), st>>>(dY, X, dW, g, ntiles, status);
+  return (int)cudaGetLastError();
+}
+
 // which: 0 fprop (In = X, Wb = weights (K,3,3,C)), 1 dgrad (In = dY, Wb = transposed copy (C,3,3,K), output dX)
 XB_API int xb_conv3x3_slab(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which,
                            int flags, int* status, cudaStream_t st) {

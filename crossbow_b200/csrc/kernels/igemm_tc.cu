@@ -252,9 +252,11 @@ XB_API int xb_conv3x3_slab_supported(const XbConvGeom* g, int which);
 XB_API int xb_conv3x3_slab_init();
 XB_API int xb_conv3x3_slab(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which,
                            int flags, int* status, cudaStream_t st);
-static int g_use_slab = 1;
-// 0 routes 3x3/stride-1 convolutions through the generic gather kernel as well (A/B comparisons)
-XB_API void xb_tc_set_slab(int on) { g_use_slab = on; }
+XB_API int xb_conv3x3_wgrad_slab(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st);
+static int g_use_slab = 1;   // the weight-gradient kernel (bit 1) is opt-in until validated
+// bit 0: 3x3/stride-1 fprop + dgrad use the slab kernel (else the generic gather kernel); bit 1: the tensor-core weight
+// gradient kernel is used where it applies (else CUDA cores).  For A/B comparisons.
+XB_API void xb_tc_set_slab(int mask) { g_use_slab = mask; }
 
 // Opt in to the large dynamic shared-memory carve-outs once per process, outside any stream capture.
 XB_API int xb_tc_init() {
@@ -273,13 +275,13 @@ XB_API int xb_tc_init() {
 XB_API int xb_tc_supported(const XbConvGeom* g, int which) {
   if (which == 0) return (g->C % 4 == 0) ? 1 : 0;
   if (which == 1) return (g->K % 4 == 0) ? 1 : 0;
-  return 0;
+  return (g_use_slab & 2) && xb_conv3x3_slab_supported(g, 2) ? 1 : 0;
 }
 
 XB_API int xb_conv_fprop_tc(const float* X, const float* W, const float* bias, float* Y, float* stats, const XbConvGeom* cg, int flags,
                             int* status, cudaStream_t st) {
   if (!aligned16(X) || !aligned16(W) || !aligned16(Y) || cg->C % 4) return -XB_BAD_ARG;
-  if (g_use_slab && xb_conv3x3_slab_supported(cg, 0)) return xb_conv3x3_slab(X, W, bias, Y, stats, cg, 0, flags, status, st);
+  if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 0)) return xb_conv3x3_slab(X, W, bias, Y, stats, cg, 0, flags, status, st);
   TcProblem g;
   g.M = cg->N * cg->P * cg->Q; g.OH = cg->P; g.OW = cg->Q; g.IH = cg->H; g.IW = cg->W; g.CR = cg->C; g.NG = cg->K;
   g.R = cg->R; g.S = cg->S; g.sh = cg->sh; g.sw = cg->sw; g.ph = cg->ph; g.pw = cg->pw; g.transposed = 0; g.KG = cg->R * cg->S * cg->C;
@@ -287,10 +289,13 @@ XB_API int xb_conv_fprop_tc(const float* X, const float* W, const float* bias, f
 }
 XB_API int xb_conv_dgrad_tc(const float* dY, const float* Wt, float* dX, const XbConvGeom* cg, int accumulate, int* status, cudaStream_t st) {
   if (!aligned16(dY) || !aligned16(Wt) || !aligned16(dX) || cg->K % 4) return -XB_BAD_ARG;
-  if (g_use_slab && xb_conv3x3_slab_supported(cg, 1)) return xb_conv3x3_slab(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);
+  if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 1)) return xb_conv3x3_slab(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);
   TcProblem g;
   g.M = cg->N * cg->H * cg->W; g.OH = cg->H; g.OW = cg->W; g.IH = cg->P; g.IW = cg->Q; g.CR = cg->K; g.NG = cg->C;
   g.R = cg->R; g.S = cg->S; g.sh = cg->sh; g.sw = cg->sw; g.ph = cg->ph; g.pw = cg->pw; g.transposed = 1; g.KG = cg->R * cg->S * cg->K;
   return dispatch_tc(dY, Wt, nullptr, dX, nullptr, g, accumulate ? F_ACCUM : 0, status, st);
 }
-XB_API int xb_conv_wgrad_tc(const float*, const float*, float*, const XbConvGeom*, int*, cudaStream_t) { return -XB_BAD_ARG; }
+XB_API int xb_conv_wgrad_tc(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st) {
+  if (!aligned16(dY) || !aligned16(X) || !xb_conv3x3_slab_supported(cg, 2)) return -XB_BAD_ARG;
+  return xb_conv3x3_wgrad_slab(dY, X, dW, cg, status, st);
+}

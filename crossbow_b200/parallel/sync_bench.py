@@ -1,0 +1,93 @@
+"""Synchronisation micro-benchmark: fused kernel vs the reference-style sequence, per model size and replica count.
+
+    python -m crossbow_b200.parallel.sync_bench                        # 1 GPU
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m crossbow_b200.parallel.sync_bench
+
+For flat fp32 vectors of 0.46 M (ResNet-32) and 25.6 M (ResNet-50) elements, values N(0, 0.01), k in {1, 2, 4}
+replicas per GPU: device time per synchronisation (CUDA events around ``--iters`` back-to-back calls after warm-up,
+maximum over ranks) of
+  fused      one persistent kernel per GPU: replica reduction + peer-memory all-reduce + central update + correction
+  reference  per-replica difference/axpy kernels + NCCL all_reduce + central update (the reference's sequence)
+and the fused kernel's fraction of its roofline = max(HBM bytes / measured copy bandwidth, NVLink bytes / 770 GB/s).
+Consecutive calls touch 4*n*(3k+4) bytes; for the small model that fits in L2, so the small-model rows are L2-resident
+numbers (as they are inside training); the large model exceeds L2 for every k.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--sizes", default="464154,25557032")
+    ap.add_argument("--replicas", default="1,2,4")
+    ap.add_argument("--two-shot", default="auto")
+    a = ap.parse_args()
+    import torch.distributed as dist
+    from ..ops import lib as L
+    from ..ops.kernel_bench import peaks
+    from .peer import init_process_group
+    from .sync import ALGO_SMA, FusedSynchroniser, ReferenceSynchroniser
+    world, rank, local = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    init_process_group("nccl")
+    lib = L.init_device()
+    bw, _, how = peaks()
+    nvlink = 770.0
+    stream = torch.cuda.Stream()
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(a.iters):
+            fn()
+        e1.record(stream)
+        e1.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / a.iters], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for n in [int(v) for v in a.sizes.split(",")]:
+        n = (n + 3) // 4 * 4
+        for k in [int(v) for v in a.replicas.split(",")]:
+            g = torch.Generator(device="cuda").manual_seed(1 + rank)
+            ws = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
+            ps = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
+            z, zl = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+            two = None if a.two_shot == "auto" else a.two_shot == "1"
+            fs = FusedSynchroniser(n, rank, world, two_shot=two)
+            rs = ReferenceSynchroniser(n, rank, world)
+            s = stream.cuda_stream
+            with torch.cuda.stream(stream):
+                t_f = timed(lambda: fs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9))
+                torch.cuda.synchronize()
+                fs.check()
+                t_r = timed(lambda: rs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9))
+            hbm = 4.0 * n * (3 * k + 4 + (2 * world if world > 1 and not fs.two_shot else (4 if world > 1 else 0)))
+            link = 4.0 * n * ((world - 1) if not fs.two_shot else 2.0 * (world - 1) / world) if world > 1 else 0.0
+            t_roof = max(hbm / (bw * 1e3), link / (nvlink * 1e3))            # microseconds
+            if rank == 0:
+                print(json.dumps({"op": "sma_sync", "n": n, "replicas": k, "gpus": world, "two_shot": fs.two_shot,
+                                  "fused_us": round(t_f, 2), "reference_us": round(t_r, 2), "speedup": round(t_r / t_f, 2),
+                                  "roofline_us": round(t_roof, 2), "fraction_of_roofline": round(t_roof / t_f, 3),
+                                  "hbm_bytes": hbm, "nvlink_bytes_per_gpu": link, "peaks": how}), flush=True)
+            fs.close()
+            del ws, ps, z, zl
+            torch.cuda.empty_cache()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,79 @@
+"""Launched by tests/test_gpu_multi.py with torch.distributed.run, one rank per GPU."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from crossbow_b200.parallel.peer import init_process_group
+    from crossbow_b200.parallel.sync import ALGO_SMA, ALGO_SSGD, FusedSynchroniser, ReferenceSynchroniser
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    init_process_group("nccl", timeout_s=120)
+    s = torch.cuda.current_stream().cuda_stream
+    for n, two_shot, k in ((4096 * 5 + 1024, False, 2), (4096 * 9, True, 3), (1 << 20, True, 1)):
+        g = torch.Generator(device="cuda").manual_seed(10 + rank)
+        ws = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
+        ps = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
+        z, zl = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+        ws2, ps2, z2, zl2 = [w.clone() for w in ws], [p.clone() for p in ps], z.clone(), zl.clone()
+        fs = FusedSynchroniser(n, rank, world, two_shot=two_shot, timeout_s=10.0)
+        rs = ReferenceSynchroniser(n, rank, world)
+        for it in range(3):
+            fs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9)
+            rs.synchronise(s, ALGO_SMA, ws2, ps2, z2, zl2, alpha=0.1, mu=0.9)
+            torch.cuda.synchronize()
+            fs.check()
+            assert torch.allclose(z, z2, rtol=1e-4, atol=1e-7), (n, two_shot, it, float((z - z2).abs().max()))
+            for a, b in zip(ws, ws2):
+                assert torch.allclose(a, b, rtol=1e-4, atol=1e-7)
+            # all ranks hold bit-identical central models
+            zs = [torch.empty_like(z) for _ in range(world)]
+            dist.all_gather(zs, z)
+            assert all(torch.equal(zs[0], t) for t in zs)
+        # S-SGD
+        gacc, gacc2 = torch.randn(n, device="cuda", generator=g) * 0.01, None
+        gacc2 = gacc.clone()
+        fs.synchronise(s, ALGO_SSGD, ws, None, z, zl, gacc, mu=0.9, scale=1.0 / (k * world))
+        rs.synchronise(s, ALGO_SSGD, ws2, None, z2, zl2, gacc2, mu=0.9, scale=1.0 / (k * world))
+        torch.cuda.synchronize()
+        fs.check()
+        assert torch.allclose(z, z2, rtol=1e-4, atol=1e-7)
+        assert float(gacc.abs().max()) == 0.0 and torch.equal(ws[0], z)
+        dist.barrier()
+        fs.close()
+    # end to end: two ranks train with SMA through the engine and stay in step
+    from crossbow_b200 import Phase, UpdateModel
+    from crossbow_b200.engine import GpuEngine
+    from helpers import build_model, make_batches
+    spec, m, solver = build_model("resnet8", 8)
+    eng = GpuEngine(spec.train, None, m, m.initial_values(7), 8, spec.input_shape, solver, UpdateModel.SMA, replicas=2, wpc=2,
+                    rank=rank, world=world, device_index=local, use_tc=True)
+    xs, ys = make_batches(spec, 8, 8, seed=100 + rank)
+    for t in range(8):
+        eng.submit(t % 2, xs[t].pin_memory(), ys[t].pin_memory(), t, Phase.TRAIN)
+        eng.wait(t % 2)
+        if t % 2 == 1:
+            eng.synchronise()
+    eng.finish()
+    zs = [torch.empty_like(eng.shared.z) for _ in range(world)]
+    dist.all_gather(zs, eng.shared.z)
+    assert all(torch.equal(zs[0], t) for t in zs), "central models diverged across ranks"
+    assert float(eng.shared.z.abs().sum()) > 0 and torch.isfinite(eng.shared.z).all()
+    eng.destroy()
+    dist.barrier()
+    if rank == 0:
+        print("MULTI_GPU_OK", world)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
