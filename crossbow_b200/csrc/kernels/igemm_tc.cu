@@ -200,13 +200,12 @@ __global__ void __launch_bounds__(NTHREADS) igemm_tc_kernel(const float* __restr
         }
       }
       if (flags & F_STATS) {
+        float sq[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float sx = v[j], sq = v[j] * v[j];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) { sx += __shfl_xor_sync(0xffffffffu, sx, o); sq += __shfl_xor_sync(0xffffffffu, sq, o); }
-          if (lane == 0) { atomicAdd(&s_red[c0 + j], sx); atomicAdd(&s_red[BN + c0 + j], sq); }
-        }
+        for (int j = 0; j < 16; ++j) sq[j] = v[j] * v[j];
+        int col;
+        float sx = warp_colsum16(v, lane, col), sqq = warp_colsum16(sq, lane, col);
+        if (lane < 16) { atomicAdd(&s_red[c0 + col], sx); atomicAdd(&s_red[BN + c0 + col], sqq); }
       }
     }
   }

@@ -23,7 +23,9 @@
 
 namespace {
 
-constexpr int CHUNK = 4096;          // floats per chunk (16 KB)
+constexpr int CHUNK_SMALL = 4096;    // floats per chunk: 16 KB for latency-bound (small) vectors,
+constexpr int CHUNK_LARGE = 16384;   // 64 KB for bandwidth-bound ones (fewer system fences and flag round trips)
+constexpr long long LARGE_N = 4LL << 20;
 constexpr int NT = 256;
 constexpr int MAXK = 16, MAXG = 8;
 
@@ -33,6 +35,7 @@ struct SyncArgs {
   int rank, G, k, algo;
   long long n;                 // elements (multiple of 4)
   int nchunks;
+  int chunk;                   // floats per chunk (multiple of 4*NT)
   unsigned int epoch;          // >= 1, increases by one per call
   int two_shot;
   int copy_to_replicas;        // overwrite replicas with z at the end
@@ -134,8 +137,16 @@ __device__ __forceinline__ void apply_total(const SyncArgs& a, long long i4, flo
 }
 
 __global__ void __launch_bounds__(NT) fused_sync_kernel(const SyncArgs* __restrict__ per_rank) {
-  const SyncArgs& a = per_rank[blockIdx.y];
+  // the argument block is read thousands of times (pointer tables): keep a copy in shared memory
+  __shared__ SyncArgs a;
   __shared__ int s_fail;
+  {
+    const int* src = reinterpret_cast<const int*>(per_rank + blockIdx.y);
+    int* dst = reinterpret_cast<int*>(&a);
+    for (int i = threadIdx.x; i < (int)(sizeof(SyncArgs) / sizeof(int)); i += NT) dst[i] = src[i];
+  }
+  __syncthreads();
+  const int CHUNK = a.chunk;
   const int tid = threadIdx.x, B = gridDim.x, G = a.G, me = a.rank;
   const long long n4 = a.n / 4;
   const int parity = a.epoch & 1;
@@ -242,14 +253,15 @@ __global__ void broadcast_z_kernel(const float* __restrict__ z, float* const* w,
 }  // namespace
 
 // Sizes (in floats / words) of the peer-visible buffers a GPU must allocate for vectors of n elements.
-XB_API long long xb_sync_chunk() { return CHUNK; }
-XB_API long long xb_sync_nchunks(long long n) { return (n + CHUNK - 1) / CHUNK; }
+static inline long long chunk_for(long long n) { return n >= LARGE_N ? CHUNK_LARGE : CHUNK_SMALL; }
+XB_API long long xb_sync_chunk(long long n) { return chunk_for(n); }
+XB_API long long xb_sync_nchunks(long long n) { return (n + chunk_for(n) - 1) / chunk_for(n); }
 XB_API long long xb_sync_inbox_floats(long long n, int G, int two_shot) {
   long long nc = xb_sync_nchunks(n);
   long long slots = two_shot ? (nc + G - 1) / G : nc;
-  return 2LL * G * slots * CHUNK;
+  return 2LL * G * slots * chunk_for(n);
 }
-XB_API long long xb_sync_result_floats(long long n) { return 2LL * xb_sync_nchunks(n) * CHUNK; }
+XB_API long long xb_sync_result_floats(long long n) { return 2LL * xb_sync_nchunks(n) * chunk_for(n); }
 XB_API long long xb_sync_flag_words(long long n, int G) { return (long long)(G + 1) * xb_sync_nchunks(n); }
 XB_API int xb_sync_args_size() { return (int)sizeof(SyncArgs); }
 
@@ -271,7 +283,7 @@ struct XbSyncDesc {
 
 static void fill_args(SyncArgs& a, const XbSyncDesc& d) {
   memset(&a, 0, sizeof(a));
-  a.rank = d.rank; a.G = d.G; a.k = d.k; a.algo = d.algo; a.n = d.n; a.nchunks = (int)xb_sync_nchunks(d.n);
+  a.rank = d.rank; a.G = d.G; a.k = d.k; a.algo = d.algo; a.n = d.n; a.nchunks = (int)xb_sync_nchunks(d.n); a.chunk = (int)chunk_for(d.n);
   a.epoch = d.epoch; a.two_shot = d.two_shot; a.copy_to_replicas = d.copy_to_replicas; a.use_prev = d.use_prev;
   a.alpha = d.alpha; a.mu = d.mu; a.scale = d.scale; a.blend = d.blend;
   for (int i = 0; i < MAXK; ++i) { a.w[i] = d.w[i]; a.prev[i] = d.prev[i]; }
@@ -297,7 +309,20 @@ XB_API int xb_fused_sync(const XbSyncDesc* d, void* args_dev, void* args_pinned,
   SyncArgs* h = reinterpret_cast<SyncArgs*>(args_pinned);
   fill_args(*h, *d);
   XB_CUDA_CHECK(cudaMemcpyAsync(args_dev, h, sizeof(SyncArgs), cudaMemcpyHostToDevice, st));
-  dim3 grid(sync_grid(h->nchunks, max_blocks > 0 ? max_blocks : 148), 1);
+  if (max_blocks <= 0) {
+    // half of what the device can hold at once: every block must be resident (blocks wait on other GPUs' blocks) and the
+    // learners' kernels run next to this one
+    static int cached = 0;
+    if (!cached) {
+      int dev = 0, sms = 148, per_sm = 1;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_sync_kernel, NT, 0);
+      cached = sms * (per_sm > 2 ? per_sm / 2 : 1);
+    }
+    max_blocks = cached;
+  }
+  dim3 grid(sync_grid(h->nchunks, max_blocks), 1);
   fused_sync_kernel<<<grid, NT, 0, st>>>(reinterpret_cast<const SyncArgs*>(args_dev));
   return (int)cudaGetLastError();
 }

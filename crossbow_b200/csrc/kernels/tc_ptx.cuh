@@ -78,6 +78,38 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 }
 
 
+// Column sums of a 32-lane x 16-value register tile in 16 shuffles (recursive halving): after the call lanes 0..15 hold
+// the sum over all 32 lanes of column `col` (returned through the reference), other lanes hold nothing useful.
+__device__ __forceinline__ float warp_colsum16(const float (&in)[16], int lane, int& col) {
+  float a[8];
+  {
+    const bool up = lane & 1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { float send = up ? in[i] : in[i + 8], keep = up ? in[i + 8] : in[i]; a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1); }
+  }
+  float b[4];
+  {
+    const bool up = lane & 2;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float send = up ? a[i] : a[i + 4], keep = up ? a[i + 4] : a[i]; b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2); }
+  }
+  float c[2];
+  {
+    const bool up = lane & 4;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) { float send = up ? b[i] : b[i + 2], keep = up ? b[i + 2] : b[i]; c[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4); }
+  }
+  float d;
+  {
+    const bool up = lane & 8;
+    float send = up ? c[0] : c[1], keep = up ? c[1] : c[0];
+    d = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+  d += __shfl_xor_sync(0xffffffffu, d, 16);
+  col = ((lane & 1) << 3) | ((lane & 2) << 1) | ((lane & 4) >> 1) | ((lane & 8) >> 3);
+  return d;
+}
+
 // shared-memory matrix descriptor with an explicit layout / major selection.
 //   K-major, no swizzle : element (row, k-chunk) at (row%8)*16 + (row/8)*SBO + chunk*LBO bytes
 //   MN-major, no swizzle: element (mn-group of 4, k) at (k%8)*16 + (k/8)*LBO + group*SBO bytes

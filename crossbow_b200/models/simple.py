@@ -94,3 +94,43 @@ def mini_inception(solver_conf=None, classes=10, size=32):
     n.fc("InnerProduct", classes)
     n.classifier_tail()
     return n.finish("mini-inception", [3, size, size], classes, solver_conf)
+
+
+def overfeat(solver_conf=None, classes=1000, size=231):
+    """OverFeat (fast) of the convnet-benchmarks suite (convnet/benchmarks/ModelBuilder.java)."""
+    n = Net()
+    n.conv("Conv", 96, 11, 4, 0, bias=True)
+    n.relu("ReLU")
+    n.pool("Pool", PoolMethod.MAX, 2, 2)
+    n.conv("Conv", 256, 5, 1, 0, bias=True)
+    n.relu("ReLU")
+    n.pool("Pool", PoolMethod.MAX, 2, 2)
+    for feat in (512, 1024, 1024):
+        n.conv("Conv", feat, 3, 1, 1, bias=True)
+        n.relu("ReLU")
+    n.pool("Pool", PoolMethod.MAX, 2, 2)
+    n.fc("InnerProduct", 3072)
+    n.relu("ReLU")
+    n.fc("InnerProduct", 4096)
+    n.relu("ReLU")
+    n.fc("InnerProduct", classes)
+    n.classifier_tail()
+    return n.finish("overfeat", [3, size, size], classes, solver_conf)
+
+
+def vgg_a(solver_conf=None, classes=1000, size=224):
+    """VGG model A (11 layers) of the convnet-benchmarks suite."""
+    n = Net()
+    for item in (64, "M", 128, "M", 256, 256, "M", 512, 512, "M", 512, 512, "M"):
+        if item == "M":
+            n.pool("Pool", PoolMethod.MAX, 2, 2)
+        else:
+            n.conv("Conv", item, 3, 1, 1, bias=True)
+            n.relu("ReLU")
+    n.fc("InnerProduct", 4096)
+    n.relu("ReLU")
+    n.fc("InnerProduct", 4096)
+    n.relu("ReLU")
+    n.fc("InnerProduct", classes)
+    n.classifier_tail()
+    return n.finish("vgg-a", [3, size, size], classes, solver_conf)

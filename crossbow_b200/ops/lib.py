@@ -107,7 +107,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_grad_sumsq", I, P, P, L, P)
     _sig(lib, "xb_fused_optimiser", I, P, P, P, P, P, P, P, P, L, I, P)
     # sync
-    _sig(lib, "xb_sync_chunk", L)
+    _sig(lib, "xb_sync_chunk", L, L)
     _sig(lib, "xb_sync_nchunks", L, L)
     _sig(lib, "xb_sync_inbox_floats", L, L, I, I)
     _sig(lib, "xb_sync_result_floats", L, L)

@@ -309,7 +309,8 @@ def test_cpu_context_trains_lenet_sma_and_checkpoints(tmp_path):
 
 def test_all_models_build_and_infer_shapes():
     from crossbow_b200.models import REGISTRY
-    sizes = {"resnet18": 64, "resnet34": 64, "resnet50": 64, "resnet101": 64, "resnet152": 64, "alexnet": 224}
+    sizes = {"resnet18": 64, "resnet34": 64, "resnet50": 64, "resnet101": 64, "resnet152": 64, "alexnet": 224, "overfeat": 231,
+             "vgg-a": 64}
     for name in REGISTRY:
         kw = {"size": sizes[name]} if name in sizes else {}
         spec, m, _ = build_model(name, 2, **kw)

@@ -118,3 +118,30 @@ def test_first_layer_three_channels(env):
     L.check(lib.xb_conv_fprop_simt(x.data_ptr(), w.data_ptr(), 0, y.data_ptr(), 0, C.byref(g), 0, s), "fprop")
     ref = F.conv2d(x.permute(0, 3, 1, 2), w.permute(0, 3, 1, 2), padding=1).permute(0, 2, 3, 1)
     assert torch.allclose(y, ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("shape", [(4, 32, 32, 16, 16, 3, 3, 1, 1), (4, 16, 16, 32, 32, 3, 3, 1, 1), (8, 8, 8, 64, 64, 3, 3, 1, 1),
+                                   (3, 9, 7, 16, 24, 3, 3, 1, 1), (2, 12, 12, 48, 20, 3, 3, 1, 1), (64, 32, 32, 16, 16, 3, 3, 1, 1)])
+def test_wgrad_tensor_core_slab(env, shape):
+    """Weight gradient on tcgen05 with MN-major operands taken straight from the position-major slabs."""
+    L, lib = env
+    g, P, Q = _geom(L, *shape)
+    lib.xb_tc_set_slab(3)
+    try:
+        assert lib.xb_tc_supported(C.byref(g), 2)
+        N, H, W, Cc, K, R, S, st, pad = shape
+        dev = torch.device("cuda")
+        gen = torch.Generator(device="cuda").manual_seed(2)
+        x = torch.randn(N, H, W, Cc, device=dev, generator=gen)
+        dy = torch.randn(N, P, Q, K, device=dev, generator=gen)
+        wr = torch.zeros(K, Cc, R, S, device=dev, requires_grad=True)
+        F.conv2d(x.permute(0, 3, 1, 2), wr, None, stride=st, padding=pad).backward(dy.permute(0, 3, 1, 2))
+        dw_ref = wr.grad.permute(0, 2, 3, 1)
+        dw = torch.zeros(K, R, S, Cc, device=dev)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        L.check(lib.xb_conv_wgrad_tc(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), status.data_ptr(), torch.cuda.current_stream().cuda_stream), "wgrad")
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        assert float((dw - dw_ref).abs().max()) / float(dw_ref.abs().max()) < 4e-3
+    finally:
+        lib.xb_tc_set_slab(1)
