@@ -279,3 +279,49 @@ XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const
   else    { bn_bwd_reduce_kernel<1><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a); }
   return (int)cudaGetLastError();
 }
+
+// ---- variant that allocates nothing: the scratch sums live in a fixed device array (see bn_backward_static.h) ----------
+#include "bn_backward_static.h"
+#include <stdio.h>
+
+// 2 * XB_BN_STATIC_MAX_CHANNELS floats = 32 KB per GPU, resident for the life of the process.  In host code this name is
+// only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_bn_static_sums[2 * XB_BN_STATIC_MAX_CHANNELS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_bn_static_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device, filled on first use
+}
+
+extern "C" __attribute__((visibility("default")))
+int xb_bn_backward_static(const float* dy, const float* x, const float* y, const float* save_mean, const float* save_invstd,
+                          const float* gamma, float* dx, float* dres, float* dgamma, float* dbeta, int M, int C, int relu,
+                          int accum_dx, int accum_dres, cudaStream_t stream) {
+  if (C > XB_BN_STATIC_MAX_CHANNELS) {
+    fprintf(stderr, "xb_bn_backward_static: %d channels exceed the built-in scratch of %d channels; use xb_bn_backward with your own scratch\n",
+            C, XB_BN_STATIC_MAX_CHANNELS);
+    return XB_BN_STATIC_TOO_MANY_CHANNELS;
+  }
+  if (M <= 0 || C <= 0 || !dy || !x || !dx || !dgamma || !dbeta || !save_mean || !save_invstd || !gamma || (relu && !y))
+    return XB_BN_STATIC_BAD_ARGUMENT;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return XB_BN_STATIC_BAD_ARGUMENT;
+  if (!g_bn_static_ptr[dev]) {
+    // once per device, with that device current: translate the symbol into the address the kernels can use
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_bn_static_sums);
+    if (e != cudaSuccess) return (int)e;
+    g_bn_static_ptr[dev] = p;
+  }
+  float* sums = g_bn_static_ptr[dev];
+  e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)C, stream);     // the sums accumulate from zero
+  if (e != cudaSuccess) return (int)e;
+  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, sums, dx, dres, dgamma, dbeta, M, C, relu, accum_dx, accum_dres, 0};
+  bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
+  int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
+  if (v4) { bn_bwd_reduce_kernel<4><<<blocks, NT, 0, stream>>>(a); bn_bwd_apply_kernel<4><<<blocks, NT, 0, stream>>>(a); }
+  else    { bn_bwd_reduce_kernel<1><<<blocks, NT, 0, stream>>>(a); bn_bwd_apply_kernel<1><<<blocks, NT, 0, stream>>>(a); }
+  return (int)cudaGetLastError();
+}
