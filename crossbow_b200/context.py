@@ -96,7 +96,7 @@ class ExecutionContext:
             from .checkpoint import load_checkpoint
             load_checkpoint(self, sys.model_directory)
         self._native = self._native_test = None
-        if sys.gpu and sys.native_scheduler and sys.fused_sync and hasattr(ds, "examples"):
+        if sys.gpu and sys.native_scheduler and sys.fused_sync and (hasattr(ds, "examples") or hasattr(ds, "source")):
             self._setup_native()
         return self
 
@@ -105,7 +105,7 @@ class ExecutionContext:
         from .runtime import Runtime
         sys, mc, e = self.sys, self.mc, self.engine
         test_ds = mc.getDataset(Phase.CHECK) if self.dataflows[1] is not None else None
-        if test_ds is not None and not hasattr(test_ds, "examples"):
+        if test_ds is not None and not (hasattr(test_ds, "examples") or hasattr(test_ds, "source")):
             test_ds = None
         ctx, sub, wait, sync, batch = e.native_executor(mc.getDataset(Phase.TRAIN), test_ds)
         handlers = 0 if sys.direct_scheduling else max(0, sys.number_of_task_handlers - 1)
@@ -114,9 +114,14 @@ class ExecutionContext:
                                  callback_handlers=max(1, sys.number_of_callback_handlers), task_timeout_s=sys.task_timeout)
         self._native = mk(self.clock.wpc)
         self._native.set_executor(sub, wait, sync, batch, ctx)
+        train_ds = mc.getDataset(Phase.TRAIN)
+        if hasattr(train_ds, "source"):              # C++ data set: batches go from its ring to the device without Python
+            self._native.set_data_source(train_ds.source(stride=self.world, offset=self.rank, timeout_s=sys.task_timeout))
         if test_ds is not None:
             self._native_test = mk(1 << 30)          # test tasks never synchronise
             self._native_test.set_executor(sub, wait, 0, batch, ctx)
+            if hasattr(test_ds, "source"):
+                self._native_test.set_data_source(test_ds.source(stride=1, offset=0, timeout_s=sys.task_timeout))
 
     def _train_native(self, ntasks: int) -> int:
         rt, e = self._native, self.engine

@@ -277,10 +277,15 @@ class GpuEngine:
         lib.xb_exec_set_sync(self._exec, C.byref(d), int(um == UpdateModel.DEFAULT))
         lib.xb_exec_set_epoch(self._exec, sy.epoch)
         for phase, ds in ((0, train_ds), (1, test_ds)):
-            if ds is not None:
+            if ds is None:
+                continue
+            if hasattr(ds, "examples"):      # contiguous pinned ring owned by Python: the executor indexes it itself
                 lib.xb_exec_set_data(self._exec, phase, ds.examples.data_ptr(), ds.examples[0].numel() * 4, ds.labels.data_ptr(),
                                      ds.labels[0].numel() * 4, ds.examples.shape[0], self.world if phase == 0 else 1,
                                      self.rank if phase == 0 else 0)
+            else:                            # native data source: the runtime asks it for addresses, sizes are all we need
+                n = int(np.prod(ds.example_shape)) * ds.batch_size
+                lib.xb_exec_set_data(self._exec, phase, 0, n * 4, 0, ds.batch_size * 4, 0, 1, 0)
         addr = lambda name: C.cast(getattr(lib, name), C.c_void_p).value
         return self._exec, addr("xb_exec_submit"), addr("xb_exec_wait"), addr("xb_exec_synchronise"), addr("xb_exec_batch")
 

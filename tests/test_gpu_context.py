@@ -1,0 +1,101 @@
+"""ExecutionContext on the GPU through the native scheduler: training, testing, auto-tuning, checkpoint / resume,
+binary data sets feeding the scheduler directly."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from crossbow_b200 import Dataflow, ModelConf, Phase, SystemConf, UpdateModel
+from crossbow_b200.context import ExecutionContext
+from crossbow_b200.data import SyntheticDataset
+from crossbow_b200.models import build
+
+pytestmark = pytest.mark.gpu
+
+
+def _context(model="lenet-caffe", shape=(1, 28, 28), k=2, batch=16, update="SMA", autotune=False, lr=0.01, batches=8, **sys_kw):
+    sysc, mc = SystemConf.reset(), ModelConf.reset()
+    sysc.setGPU(True).setCPU(False).setNumberOfGpuModels(k).setDisplayInterval(0)
+    sysc.autotune_models = autotune
+    for key, v in sys_kw.items():
+        setattr(sysc, key, v)
+    solver = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(lr).setMomentum(0.9).setAlpha(0.1)
+    mc.setBatchSize(batch).setWpc(k).setUpdateModel(update)
+    ds = SyntheticDataset(list(shape), 10, batch, batches=batches, seed=1, distribution="uniform")
+    mc.setDataset(Phase.TRAIN, ds).setDataset(Phase.CHECK, ds)
+    spec = build(model, solver_conf=solver)
+    ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), Dataflow(spec.test).setPhase(Phase.CHECK)], quiet=True)
+    ctx.init()
+    return ctx
+
+
+@pytest.mark.parametrize("native", [True, False])
+def test_train_test_and_loss_goes_down(native):
+    ctx = _context(native_scheduler=native)
+    assert (ctx._native is not None) == native
+    ctx.train(64, "tasks")
+    losses = ctx.measurements.losses()
+    assert len(losses) == 64 and np.isfinite(losses).all()
+    assert np.mean(losses[-8:]) < np.mean(losses[:8])          # 8 distinct batches, seen 8 times each
+    acc = ctx.test()
+    assert 0.0 <= acc <= 1.0
+    assert ctx.clock.clock == 32
+    ctx.destroy()
+
+
+def test_checkpoint_and_resume(tmp_path):
+    ctx = _context()
+    ctx.train(8, "tasks")
+    d = ctx.checkpoint(str(tmp_path))
+    z = ctx.engine.central_model()
+    r1 = ctx.engine.replica_model(1)
+    assert os.path.getsize(os.path.join(d, "gpu-00-theModel-data.dat")) == 4 * ctx.model.elements
+    assert os.path.exists(os.path.join(d, "gpu-00-replica-001-last.dat"))
+    ctx.destroy()
+    ctx2 = _context(model_directory=str(tmp_path))
+    assert np.array_equal(ctx2.engine.central_model(), z) and np.array_equal(ctx2.engine.replica_model(1), r1)
+    ctx2.train(4, "tasks")
+    ctx2.destroy()
+
+
+def test_batch_norm_statistics_are_checkpointed(tmp_path):
+    ctx = _context(model="resnet8", shape=(3, 32, 32), batch=8)
+    ctx.train(4, "tasks")
+    d = ctx.checkpoint(str(tmp_path))
+    assert any(f.startswith("gpu-00-bn-avg-") for f in os.listdir(d)) and any(f.startswith("gpu-00-bn-var-") for f in os.listdir(d))
+    ctx.destroy()
+
+
+def test_auto_tuner_adds_and_removes_replicas():
+    ctx = _context(k=1, autotune=True, autotune_threshold=-1.0)      # any throughput counts as an improvement -> keeps adding
+    ctx.train(24, "tasks")
+    assert ctx.engine.k > 1
+    k = ctx.engine.k
+    ctx.autotuner.threshold = 1e9                                   # nothing improves by that much -> remove one and stop
+    ctx.train(16, "tasks")
+    assert ctx.engine.k == k - 1 and not ctx.autotuner.active
+    assert np.isfinite(ctx.measurements.losses()).all()
+    ctx.destroy()
+
+
+def test_binary_dataset_feeds_the_scheduler(tmp_path):
+    from crossbow_b200.data.native import DatasetWriter, LightDataset
+    g = np.random.default_rng(0)
+    w = DatasetWriter(str(tmp_path), "toy", (1, 28, 28), 16)
+    w.append(g.random((64, 1, 28, 28), dtype=np.float32), g.integers(0, 10, 64))
+    meta = w.close()
+    sysc, mc = SystemConf.reset(), ModelConf.reset()
+    sysc.setGPU(True).setCPU(False).setNumberOfGpuModels(2).setDisplayInterval(0)
+    solver = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.01).setMomentum(0.9).setAlpha(0.1)
+    mc.setBatchSize(16).setWpc(2).setUpdateModel("SMA")
+    ds = LightDataset(meta, slots=4, copiers=1, register_with_cuda=True)
+    mc.setDataset(Phase.TRAIN, ds)
+    spec = build("lenet-caffe", solver_conf=solver)
+    ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), None], quiet=True)
+    ctx.init()
+    assert ctx._native is not None       # the C++ scheduler pulls batches straight from the C++ slot ring
+    ctx.train(12, "tasks")
+    assert len(ctx.measurements.losses()) == 12 and np.isfinite(ctx.measurements.losses()).all()
+    ctx.destroy()
+    ds.close()
