@@ -175,119 +175,154 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __r
 
 
 // ---- weight gradient of a 3x3 / stride 1 / pad 1 convolution -------------------------------------------------------------
-// dW[k][tap][c] = sum over positions of dY[pos][k] * X[pos + shift(tap)][c].  The reduction runs over POSITIONS, and in the
-// slab layout [16-byte channel chunk][position][16 B] a group of 8 consecutive positions x 4 channels is one contiguous
-// 128-byte core matrix - exactly the canonical MN-major no-swizzle operand (MN = channel, K = position; stride between
-// channel chunks = SBO, between groups of 8 positions = LBO = 128 B).  So the SAME two slabs serve as operands again:
-//   A = dY tile   (M = output channels, padded to 128 by zero planes)      B = X slab shifted by the tap (N = input channels)
-// A persistent CTA walks position tiles, accumulating nine [128 x BN] products (one per tap) in 9*BN TMEM columns, and
-// adds its partial dW to global memory once at the end.
-template <int BN>
-__global__ void __launch_bounds__(NTHREADS) conv3x3_wgrad_slab_kernel(const float* __restrict__ dY, const float* __restrict__ X,
-                                                                      float* __restrict__ dW, SlabProblem g, int ntiles, int* status) {
-  constexpr uint32_t TMEM_COLS = 9 * BN <= 256 ? 256 : 512;
-  // M = 128, N = BN, both operands MN-major (bits 15 and 16)
-  constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// dW[k][r][s][c] = sum over positions p of dY[p][k] * X[p + r*(W+2) + s][c]  (padded position space, slab index).
+// The reduction runs over POSITIONS while both tensors are stored position-major with the channels contiguous, i.e. both
+// operands are "MN-major".  For 32-bit operands tcgen05 accepts exactly one MN-major shared-memory layout: 128-byte rows
+// (32 channels of one position), four rows per 512-byte atom, the 32-byte chunks of a row XOR-ed with bits 7..8 of the
+// absolute address (layout type 1, "128-byte swizzle with 32-byte base"); SBO is the stride between groups of four rows,
+// LBO the stride between groups of 32 MN elements.  The swizzle works on absolute address bits, so a descriptor whose
+// start is advanced by whole rows still reads a consistently swizzled slab: measured on B200, and the basis of this
+// kernel.  Operands:
+//   A = the X slab.  M = 128 = 4 groups x 32 channels with LBO = ONE ROW (128 B): group g re-reads the slab one
+//       position further on, so the four groups are the taps s = 0, 1, 2 (and one unused) of filter row r.
+//   B = the dY tile, N = output channels, 32 per plane (LBO = plane stride).
+// One M128 x N x K8 MMA per filter row and 8 positions therefore covers three taps; 48 MMAs per 128-position tile.
+// The three accumulators (one per filter row) live in 3*N TMEM columns across all tiles a persistent CTA walks; a two-stage
+// cp.async ring overlaps the loads of tile i+1 with the MMAs of tile i.  At the end TMEM lane (s, c) adds its 3*N values to
+// dW - 32 consecutive lanes hit 32 consecutive floats.
+constexpr int WG_THREADS = 512;                        // many warps: the cp.async loads are latency-bound per warp
+template <int NK>
+__global__ void __launch_bounds__(WG_THREADS) conv3x3_wgrad_mn_kernel(const float* __restrict__ dY, const float* __restrict__ X,
+                                                                    float* __restrict__ dW, SlabProblem g, int ntiles, int* status) {
+  constexpr int NP = (NK + 31) / 32;                   // 32-channel planes of the dY tile
+  constexpr int YQ = NK / 4;                           // 16-byte chunks per dY position
+  constexpr uint32_t TMEM_COLS = 3 * NK <= 64 ? 64 : 3 * NK <= 128 ? 128 : 3 * NK <= 256 ? 256 : 512;
+  constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(NK >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  constexpr uint64_t LAYOUT = 1ull << 61;
+  constexpr uint32_t yplane = BM * 128u;
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bar_done;
+  __shared__ __align__(8) uint64_t bar_free[2];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int PW = g.W + 2, PR = g.H + 1;
-  const int S = BM + 2 * PW + 2;
-  const int KQ = g.K >> 2;                             // real 16-byte chunks of dY (output channels / 4)
-  const int c0 = blockIdx.y * BN;                      // first input channel of this CTA's N tile
-  constexpr uint32_t planeA = BM * 16u;                // dY tile: 32 planes x 128 positions x 16 B
-  const uint32_t planeB = (uint32_t)S * 16u;
-  unsigned char* sA = smem;
-  unsigned char* sB = smem + 32 * planeA;              // [BN/4 planes][S positions][16 B]
-  const uint32_t a_u32 = smem_u32(sA), b_u32 = smem_u32(sB);
-
-  if (tid == 0) { mbar_init(&bar_done, 1); s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+  const int S = (BM + 2 * PW + 4 + 3) & ~3;            // slab rows: the tile, two filter rows of halo, the group shift
+  const int c0 = blockIdx.y * 32, k0 = blockIdx.z * NK;
+  const int xq = (g.C - c0 >= 32 ? 32 : g.C - c0) >> 2;  // valid 16-byte chunks per slab row
+  const uint32_t xbytes = (uint32_t)S * 128u, stage_bytes = xbytes + NP * yplane;
+  const uint32_t base_u32 = smem_u32(smem);
+  if (tid == 0) { mbar_init(&bar_free[0], 1); mbar_init(&bar_free[1], 1); s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
   if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);
-  // planes of A beyond the real output channels stay zero for the whole kernel
-  for (int i = tid; i < (32 - KQ) * BM; i += NTHREADS) reinterpret_cast<float4*>(sA + (size_t)KQ * planeA)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem;
 
-  uint32_t phase = 0;
-  bool first = true, alive = true;
-  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-    const long long q0 = (long long)tile * BM, qs = q0 - PW - 1;
-    if (!first) {                                       // the previous tile's MMAs must have consumed shared memory
-      if (alive && !mbar_wait(&bar_done, phase)) { alive = false; s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
-      phase ^= 1;
-      __syncthreads();
-    }
-    // dY tile: position m = tid, zero for padding positions
-    {
-      const long long p = q0 + tid;
-      const float* src = dY; uint32_t bytes = 0;
-      if (p < g.positions) {
-        int xx = (int)(p % PW); long long t = p / PW; int yy = (int)(t % PR); int n = (int)(t / PR);
-        if (yy >= 1 && xx >= 1 && xx <= g.W) { src = dY + (((long long)n * g.H + (yy - 1)) * g.W + (xx - 1)) * g.K; bytes = 16; }
+  // Pixel index (n*H + y)*W + x of every slab row of a tile, -1 for padding: computed once per tile with 32-bit
+  // arithmetic so that the copy loops below carry no divisions.  Two tables, alternating with the stages.
+  int* s_pix = reinterpret_cast<int*>(smem + 2 * stage_bytes);
+  const int npos = (int)g.positions;
+  auto load_tile = [&](int tile, int stage) {
+    const uint32_t sbase = base_u32 + (uint32_t)stage * stage_bytes;
+    int* pix = s_pix + stage * S;
+    const int q0 = tile * BM, qs = q0 - PW - 1;
+    for (int j = tid; j < S; j += WG_THREADS) {
+      const int p = qs + j;
+      int v = -1;
+      if (p >= 0 && p < npos) {
+        const int t = p / PW, xx = p - t * PW, n = t / PR, yy = t - n * PR;
+        if (yy >= 1 && xx >= 1 && xx <= g.W) v = (n * g.H + (yy - 1)) * g.W + (xx - 1);
       }
-      for (int c = 0; c < KQ; ++c)
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_u32 + c * planeA + tid * 16), "l"(src + (bytes ? c * 4 : 0)), "r"(bytes) : "memory");
+      pix[j] = v;
     }
-    // X slab (with halo), only this CTA's BN input channels
-    for (int j = tid; j < S; j += NTHREADS) {
-      const long long p = qs + j;
-      const float* src = X; uint32_t bytes = 0;
-      if (p >= 0 && p < g.positions) {
-        int xx = (int)(p % PW); long long t = p / PW; int yy = (int)(t % PR); int n = (int)(t / PR);
-        if (yy >= 1 && xx >= 1 && xx <= g.W) { src = X + (((long long)n * g.H + (yy - 1)) * g.W + (xx - 1)) * g.C + c0; bytes = 16; }
+    __syncthreads();
+    {                                                    // X slab: eight threads per row, one 16-byte chunk each
+      const uint32_t q = (uint32_t)tid & 7u;
+      if ((int)q < xq) {
+        const float* xsrc = X + c0 + q * 4;
+        for (int j = tid >> 3; j < S; j += WG_THREADS / 8) {
+          const int v = pix[j];
+          const float* src = v >= 0 ? xsrc + (long long)v * g.C : X;
+          const uint32_t dst = sbase + (uint32_t)j * 128u + (((q >> 1) ^ ((uint32_t)j & 3u)) << 5) + (q & 1u) * 16u;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(v >= 0 ? 16u : 0u) : "memory");
+        }
       }
-      for (int c = 0; c < BN / 4; ++c) {
-        uint32_t b = (bytes && c0 + c * 4 < g.C) ? 16u : 0u;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(b_u32 + c * planeB + j * 16), "l"(src + (b ? c * 4 : 0)), "r"(b) : "memory");
+    }
+    {                                                    // dY tile: YQ threads per row
+      const uint32_t q = (uint32_t)tid % YQ, qq = q & 7u;
+      const bool kin = k0 + (int)q * 4 < g.K;
+      const float* ysrc = dY + k0 + q * 4;
+      const uint32_t ybase = sbase + xbytes + (q >> 3) * yplane;
+      for (int t = tid / YQ; t < BM; t += WG_THREADS / YQ) {
+        const int v = kin ? pix[t + PW + 1] : -1;
+        const float* src = v >= 0 ? ysrc + (long long)v * g.K : dY;
+        const uint32_t dst = ybase + (uint32_t)t * 128u + (((qq >> 1) ^ ((uint32_t)t & 3u)) << 5) + (qq & 1u) * 16u;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(v >= 0 ? 16u : 0u) : "memory");
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // Called by all threads after the loads of iteration `it` have landed (and a __syncthreads): one lane issues the MMAs.
+  auto issue_tile = [&](int it, bool alive) {
+    if (warp == 0) {
+      if (lane == 0 && alive) {
+        tc_fence_after();
+        const uint32_t sbase = base_u32 + (uint32_t)(it & 1) * stage_bytes;
+        for (int r = 0; r < 3; ++r) {
+          const uint32_t a0 = sbase + (uint32_t)(r * PW) * 128u;
+#pragma unroll 4
+          for (int j = 0; j < BM / 8; ++j) {
+            uint64_t ad = make_desc(a0 + (uint32_t)j * 1024u, 128, 512) | LAYOUT;
+            uint64_t bd = make_desc(sbase + xbytes + (uint32_t)j * 1024u, yplane, 512) | LAYOUT;
+            umma_tf32(tmem + (uint32_t)(r * NK), ad, bd, IDESC, (it == 0 && j == 0) ? 0u : 1u);
+          }
+        }
+        umma_commit(&bar_free[it & 1]);
+      }
+      __syncwarp();
+    }
+  };
+
+  const int my_tiles = blockIdx.x < ntiles ? (ntiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  bool alive = true;
+  for (int it = 0; it < my_tiles; ++it) {
+    if (it >= 2) {                                       // the MMAs of tile it-2 must have consumed this stage
+      if (alive && !mbar_wait(&bar_free[it & 1], (uint32_t)(((it >> 1) - 1) & 1))) { alive = false; s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
+    }
+    load_tile((int)blockIdx.x + it * (int)gridDim.x, it & 1);
+    if (it >= 1) {
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      issue_tile(it - 1, alive);
+    }
+  }
+  if (my_tiles > 0) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) {
-      if (lane == 0 && alive) {
-        tc_fence_after();
-        for (int tap = 0; tap < 9; ++tap) {
-          const int r = tap / 3, s = tap - 3 * r;
-          const uint32_t shift = (uint32_t)(r * PW + s) * 16u;
-#pragma unroll 4
-          for (int j = 0; j < BM / 8; ++j) {             // 8 positions per MMA
-            uint64_t ad = make_desc(a_u32 + j * 128, 128, planeA);
-            uint64_t bd = make_desc(b_u32 + shift + j * 128, 128, planeB);
-            umma_tf32(tmem + tap * BN, ad, bd, IDESC, (first && j == 0) ? 0u : 1u);
-          }
-        }
-        umma_commit(&bar_done);
-      }
-      __syncwarp();
-    }
-    first = false;
+    issue_tile(my_tiles - 1, alive);
+    const int last = my_tiles - 1;
+    if (alive && !mbar_wait(&bar_free[last & 1], (uint32_t)((last >> 1) & 1))) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
   }
-  if (!first && alive && !mbar_wait(&bar_done, phase)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
   tc_fence_after();
   __syncthreads();
-  if (!s_abort && !first) {
-    const int k = warp * 32 + lane;                      // output channel = TMEM lane
-    const bool warp_has_rows = warp * 32 < g.K;          // whole-warp condition: tcgen05.ld is warp-collective
-    if (warp_has_rows) {
-      for (int tap = 0; tap < 9; ++tap)
+  if (!s_abort && my_tiles > 0 && (warp & 3) < 3) {      // TMEM lane quadrant (warp & 3) = filter column s, lane = input channel
+    const int sx = warp & 3, c = c0 + lane;
+    for (int ch = warp >> 2; ch < 3 * NK / 16; ch += WG_THREADS / 128) {   // 16-column chunks, dealt to the warps of a quadrant
+      const int r = (ch * 16) / NK, n0 = (ch * 16) % NK;
+      float v[16];
+      tmem_ld16(tmem + ((uint32_t)(sx * 32) << 16) + (uint32_t)(ch * 16), v);
+      if (c < g.C) {
 #pragma unroll
-        for (int cc = 0; cc < BN; cc += 16) {
-          float v[16];
-          tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(tap * BN + cc), v);
-          if (k < g.K) {
-            float* o = dW + ((long long)k * 9 + tap) * g.C + c0 + cc;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) if (c0 + cc + j < g.C) atomicAdd(o + j, v[j]);
-          }
+        for (int j = 0; j < 16; ++j) {
+          const int kk = k0 + n0 + j;
+          if (kk < g.K) atomicAdd(dW + ((long long)kk * 9 + r * 3 + sx) * g.C + c, v[j]);
         }
+      }
     }
   }
   tc_fence_before();
@@ -295,7 +330,10 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_wgrad_slab_kernel(const floa
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
-inline size_t wgrad_smem_bytes(int W, int BN) { return (size_t)32 * BM * 16 + (size_t)(BN / 4) * (BM + 2 * (W + 2) + 2) * 16; }
+inline size_t wgrad_smem_bytes(int W, int NK) {
+  size_t S = (BM + 2 * (W + 2) + 4 + 3) & ~3;
+  return 2 * (S * 128 + (size_t)((NK + 31) / 32) * BM * 128) + 2 * S * sizeof(int);
+}
 
 inline size_t slab_smem_bytes(int W, int C, int BN) {
   size_t S = BM + 2 * (W + 2) + 2;
@@ -501,6 +539,13 @@ inline int choose_bn(long long positions, int W, int Cred, int Kout) {
   return bn;
 }
 
+// Output channels per CTA of the weight-gradient kernel: as many as fit in two shared-memory stages.
+inline int choose_wgrad_nk(int W, int K) {
+  int nk = K <= 16 ? 16 : K <= 32 ? 32 : K <= 64 ? 64 : 128;
+  while (nk > 16 && wgrad_smem_bytes(W, nk) > kSmemLimit) nk >>= 1;
+  return nk;
+}
+
 }  // namespace
 
 template <int BN>
@@ -522,7 +567,7 @@ inline int choose_pipe_bn(long long positions, int W, int Kout) {
 // 1 if the slab kernel covers this geometry in direction `which` (0 fprop, 1 dgrad)
 XB_API int xb_conv3x3_slab_supported(const XbConvGeom* g, int which) {
   if (g->R != 3 || g->S != 3 || g->sh != 1 || g->sw != 1 || g->ph != 1 || g->pw != 1) return 0;
-  if (which == 2) return (g->C % 16 == 0 && g->K % 4 == 0 && g->K <= 128 && wgrad_smem_bytes(g->W, 32) <= kSmemLimit) ? 1 : 0;
+  if (which == 2) return (g->C % 4 == 0 && g->K % 4 == 0 && (long long)g->N * (g->H + 1) * (g->W + 2) < (1ll << 30) && wgrad_smem_bytes(g->W, choose_wgrad_nk(g->W, g->K)) <= kSmemLimit) ? 1 : 0;
   int Cred = which == 0 ? g->C : g->K, Kout = which == 0 ? g->K : g->C;
   if (Cred % 8 || Kout % 4) return 0;
   const long long positions = (long long)g->N * (g->H + 1) * (g->W + 2);
@@ -541,21 +586,34 @@ XB_API int xb_conv3x3_slab_init() {
   if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_pipe_kernel<32, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
   if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_pipe_kernel<64, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
   if ((e = (int)cudaFuncSetAttribute(conv3x3_slab_pipe_kernel<128, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
-  if ((e = (int)cudaFuncSetAttribute(conv3x3_wgrad_slab_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
-  if ((e = (int)cudaFuncSetAttribute(conv3x3_wgrad_slab_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_wgrad_mn_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_wgrad_mn_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_wgrad_mn_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if ((e = (int)cudaFuncSetAttribute(conv3x3_wgrad_mn_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
   return 0;
 }
+// Upper bound on the CTAs of one weight-gradient launch (each adds a full partial dW to global memory at its end).
+static int g_wgrad_ctas = 2 * 148;
+XB_API void xb_conv3x3_wgrad_set_ctas(int n) { g_wgrad_ctas = n > 0 ? n : 2 * 148; }
 // dW (K,3,3,C) must hold the value to accumulate onto (normally zero).
 XB_API int xb_conv3x3_wgrad_slab(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st) {
   SlabProblem g;
   g.N = cg->N; g.H = cg->H; g.W = cg->W; g.C = cg->C; g.K = cg->K; g.mirrored = 0;
   g.positions = (long long)cg->N * (cg->H + 1) * (cg->W + 2);
   const int ntiles = (int)((g.positions + BM - 1) / BM);
-  const int BN = cg->C <= 16 ? 16 : 32;
-  dim3 grid((unsigned)(ntiles < 148 ? ntiles : 148), (unsigned)((cg->C + BN - 1) / BN));
-  if (grid.y > 1 && grid.x * grid.y > 296) grid.x = 296 / grid.y;
-  if (BN == 16) conv3x3_wgrad_slab_kernel<16><<<grid, NTHREADS, wgrad_smem_bytes(g.W, 16), st>>>(dY, X, dW, g, ntiles, status);
-  else          conv3x3_wgrad_slab_kernel<32><<<grid, NTHREADS, wgrad_smem_bytes(g.W, 32), st>>>(dY, X, dW, g, ntiles, status);
+  const int NK = choose_wgrad_nk(g.W, g.K);
+  const unsigned gy = (unsigned)((g.C + 31) / 32), gz = (unsigned)((g.K + NK - 1) / NK);
+  int gx = g_wgrad_ctas / (int)(gy * gz);
+  if (gx < 1) gx = 1;
+  if (gx > ntiles) gx = ntiles;
+  dim3 grid((unsigned)gx, gy, gz);
+  const size_t smem = wgrad_smem_bytes(g.W, NK);
+  switch (NK) {
+    case 16: conv3x3_wgrad_mn_kernel<16><<<grid, WG_THREADS, smem, st>>>(dY, X, dW, g, ntiles, status); break;
+    case 32: conv3x3_wgrad_mn_kernel<32><<<grid, WG_THREADS, smem, st>>>(dY, X, dW, g, ntiles, status); break;
+    case 64: conv3x3_wgrad_mn_kernel<64><<<grid, WG_THREADS, smem, st>>>(dY, X, dW, g, ntiles, status); break;
+    default: conv3x3_wgrad_mn_kernel<128><<<grid, WG_THREADS, smem, st>>>(dY, X, dW, g, ntiles, status); break;
+  }
   return (int)cudaGetLastError();
 }
 

@@ -252,7 +252,7 @@ XB_API int xb_conv3x3_slab_init();
 XB_API int xb_conv3x3_slab(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which,
                            int flags, int* status, cudaStream_t st);
 XB_API int xb_conv3x3_wgrad_slab(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st);
-static int g_use_slab = 1;   // the weight-gradient kernel (bit 1) is opt-in until validated
+static int g_use_slab = 3;
 // bit 0: 3x3/stride-1 fprop + dgrad use the slab kernel (else the generic gather kernel); bit 1: the tensor-core weight
 // gradient kernel is used where it applies (else CUDA cores).  For A/B comparisons.
 XB_API void xb_tc_set_slab(int mask) { g_use_slab = mask; }

@@ -141,7 +141,42 @@ __global__ void __launch_bounds__(256) fused_optimiser_kernel(OptArgs a) {
     }
   }
 }
+// Matrix factorisation (clib-multigpu/kernels/matfact.cu:6-61): one warp per (row, column, rating) example.
+//   pred = <U[row], V[col]> ; err = rating - pred
+//   loss = (sum err^2 + lambda * (sum |U[row]|^2 + sum |V[col]|^2)) / batch        -> result[0]
+//   dU[row] += (-2 err V[col] + 2 lambda U[row]) / batch ; dV[col] likewise (atomics: rows repeat within a batch)
+__global__ void matfact_kernel(const float* __restrict__ triples, int stride, const int* __restrict__ ratings_i, const float* __restrict__ U,
+                               const float* __restrict__ V, float* __restrict__ dU, float* __restrict__ dV, float* __restrict__ result,
+                               int batch, int latents, float lambda, int rows, int cols) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= batch) return;
+  const float* t = triples + (long long)warp * stride;
+  const int r = min(max((int)t[0], 0), rows - 1), c = min(max((int)t[1], 0), cols - 1);
+  const float rating = ratings_i ? (float)ratings_i[warp] : t[2];
+  const float* u = U + (long long)r * latents; const float* v = V + (long long)c * latents;
+  float dot = 0.f, nu = 0.f, nv = 0.f;
+  for (int k = lane; k < latents; k += 32) { float a = u[k], b = v[k]; dot += a * b; nu += a * a; nv += b * b; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { dot += __shfl_xor_sync(0xffffffffu, dot, o); nu += __shfl_xor_sync(0xffffffffu, nu, o); nv += __shfl_xor_sync(0xffffffffu, nv, o); }
+  const float err = rating - dot, inv = 1.f / (float)batch;
+  if (dU)
+    for (int k = lane; k < latents; k += 32) {
+      float a = u[k], b = v[k];
+      atomicAdd(&dU[(long long)r * latents + k], (-2.f * err * b + 2.f * lambda * a) * inv);
+      atomicAdd(&dV[(long long)c * latents + k], (-2.f * err * a + 2.f * lambda * b) * inv);
+    }
+  if (lane == 0) atomicAdd(&result[0], (err * err + lambda * (nu + nv)) * inv);
+}
 }  // namespace
+
+// result[0] must be zero on entry (it is accumulated); result[1] (accuracy) is set to 0.
+XB_API int xb_matfact(const float* triples, int stride, const int* ratings, const float* U, const float* V, float* dU, float* dV, float* result,
+                      int batch, int latents, float lambda, int rows, int cols, cudaStream_t st) {
+  XB_CUDA_CHECK(cudaMemsetAsync(result, 0, 2 * sizeof(float), st));
+  int threads = 256, blocks = xb_ceil_div((long long)batch * 32, threads);
+  matfact_kernel<<<blocks, threads, 0, st>>>(triples, stride, ratings, U, V, dU, dV, result, batch, latents, lambda, rows, cols);
+  return (int)cudaGetLastError();
+}
 
 XB_API int xb_softmax_xent(const float* logits, const int* labels, float* probs, float* dlogits, float* result, int rows, int classes,
                            int ignore_label, int mode, cudaStream_t st) {

@@ -40,13 +40,14 @@ XB_API int xb_colsum(const float*, float*, int, int, cudaStream_t);
 XB_API int xb_softmax_xent(const float*, const int*, float*, float*, float*, int, int, int, int, cudaStream_t);
 XB_API int xb_classify(const float*, float*, int, int, cudaStream_t);
 XB_API int xb_grad_sumsq(const float*, float*, long long, cudaStream_t);
+XB_API int xb_matfact(const float*, int, const int*, const float*, const float*, float*, float*, float*, int, int, float, int, int, cudaStream_t);
 XB_API int xb_fused_optimiser(float*, float*, float*, float*, float*, const float*, const float*, const XbTaskParams*, long long, int, cudaStream_t);
 
 enum XbOpKind : int {
   OP_MEMSET = 0, OP_UPLOAD = 1, OP_TRANSFORM = 2, OP_CONV_FPROP = 3, OP_CONV_DGRAD = 4, OP_CONV_WGRAD = 5, OP_COLSUM = 6,
   OP_BN_STATS = 7, OP_BN_FWD = 8, OP_BN_BWD = 9, OP_ACT_FWD = 10, OP_ACT_BWD = 11, OP_SUM = 12, OP_DROPOUT = 13,
   OP_CONCAT = 14, OP_POOL_FWD = 15, OP_POOL_BWD = 16, OP_LRN_FWD = 17, OP_LRN_BWD = 18, OP_SOFTMAX_XENT = 19,
-  OP_CLASSIFY = 20, OP_TRANSPOSE_W = 21, OP_GRAD_SUMSQ = 22, OP_OPTIMISER = 23, OP_COPY = 24,
+  OP_CLASSIFY = 20, OP_TRANSPOSE_W = 21, OP_GRAD_SUMSQ = 22, OP_OPTIMISER = 23, OP_COPY = 24, OP_MATFACT = 25,
 };
 
 // One launch. Field meaning depends on `kind` (documented where the Python lowering fills them).
@@ -129,6 +130,9 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
       return xb_softmax_xent((const float*)o.p[0], (const int*)o.p[1], (float*)o.p[2], (float*)o.p[3], (float*)o.p[4], o.ia[0], o.ia[1], o.ia[2], o.ia[3], st);
     case OP_CLASSIFY: return xb_classify((const float*)o.p[0], (float*)o.p[1], o.ia[0], o.ia[1], st);
     case OP_TRANSPOSE_W: return xb_transpose_weights((const float*)o.p[0], (float*)o.p[1], (const XbTransposeDesc*)o.p[2], o.ia[0], o.ia[1], st);
+    case OP_MATFACT:
+      return xb_matfact((const float*)o.p[0], o.ia[0], (const int*)o.p[1], (const float*)o.p[2], (const float*)o.p[3], (float*)o.p[4], (float*)o.p[5],
+                        (float*)o.p[6], o.ia[1], o.ia[2], o.fa[0], o.ia[3], o.ia[4], st);
     case OP_GRAD_SUMSQ: return xb_grad_sumsq((const float*)o.p[0], (float*)o.p[1], o.la[0], st);
     case OP_OPTIMISER:
       return xb_fused_optimiser((float*)o.p[0], (float*)o.p[1], (float*)o.p[2], (float*)o.p[3], (float*)o.p[4], (const float*)o.p[5],

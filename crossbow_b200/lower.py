@@ -406,6 +406,18 @@ class Lowering:
             self.emit(_op(L.OP_CLASSIFY, ia=[x.n, x.numel // x.n], p=[x.buf, out.buf]))
             self.tensors[id(n)] = out
             return
+        if kind == "matfact":
+            conf = k.conf
+            u, v = k.variables
+            train = self.has_backward and self.replica is not None
+            du = self.wptr(u, self.replica.g) if train else 0
+            dv = self.wptr(v, self.replica.g) if train else 0
+            # the input batch is [N, 3] (row, column, rating) in the public layout; ratings may also come as labels
+            src = self.x_in if self.x_in is not None else x
+            self.emit(_op(L.OP_MATFACT, ia=[src.numel // src.n, src.n, conf.number_of_latent_variables, conf.number_of_rows, conf.number_of_columns],
+                          fa=[conf.lambda_], p=[src.buf, None, self.wptr(u), self.wptr(v), du, dv, self.result_ptr]))
+            self.tensors[id(n)] = None
+            return
         if kind == "noop":
             self.tensors[id(n)] = x
             return
@@ -436,7 +448,7 @@ class Lowering:
         for n in reversed(fwd):
             k, info = n.op.kernel, self.node_info[id(n)]
             kind = k.kind
-            if info["fused_into"] is not None or kind in ("softmax", "softmaxloss", "accuracy", "classify", "datatransform", "noop"):
+            if info["fused_into"] is not None or kind in ("softmax", "softmaxloss", "accuracy", "classify", "datatransform", "noop", "matfact"):
                 continue
             if kind == "batchnorm" and info["deferred"]:
                 continue          # handled at its sum node

@@ -134,3 +134,18 @@ def vgg_a(solver_conf=None, classes=1000, size=224):
     n.fc("InnerProduct", classes)
     n.classifier_tail()
     return n.finish("vgg-a", [3, size, size], classes, solver_conf)
+
+
+def matrix_factorisation(solver_conf=None, rows=1000, columns=500, latents=16, lambda_=0.05):
+    """SGD matrix factorisation over (row, column, rating) triples (MatrixFactorisation.java); the input "image" is a
+    [3, 1, 1] example holding the two indices and the rating."""
+    from ..conf import MatFactConf, ModelConf
+    from ..graph import DataflowNode, Operator, SubGraph, append_gradients
+    from ..kernels import MatFact
+    from ._builder import ModelSpec
+    conf = MatFactConf().setNumberOfRows(rows).setNumberOfColumns(columns).setNumberOfLatentVariables(latents)
+    conf.lambda_ = lambda_
+    conf.model_variable_initialiser = InitialiserConf().setType(InitialiserType.GAUSSIAN).setStd(0.1)
+    head = DataflowNode(Operator("MatFact", MatFact(conf)))
+    append_gradients(head, solver_conf or ModelConf.getInstance().getSolverConf())
+    return ModelSpec("matrix-factorisation", SubGraph(head), None, [3, 1, 1], 1)

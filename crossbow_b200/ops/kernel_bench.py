@@ -207,6 +207,7 @@ def main():
     ap.add_argument("--suite", default=None, choices=[None, "resnet32", "resnet50"])
     a = ap.parse_args()
     lib = L.init_device()
+    lib.xb_tc_set_slab(3)
     timer = Timer(flush=not a.warm)
     if a.suite:
         shapes = RESNET32 if a.suite == "resnet32" else RESNET50

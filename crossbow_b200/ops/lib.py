@@ -54,7 +54,7 @@ class XbSolverState(C.Structure):
 # op kinds (csrc/runtime/program.cu)
 (OP_MEMSET, OP_UPLOAD, OP_TRANSFORM, OP_CONV_FPROP, OP_CONV_DGRAD, OP_CONV_WGRAD, OP_COLSUM, OP_BN_STATS, OP_BN_FWD,
  OP_BN_BWD, OP_ACT_FWD, OP_ACT_BWD, OP_SUM, OP_DROPOUT, OP_CONCAT, OP_POOL_FWD, OP_POOL_BWD, OP_LRN_FWD, OP_LRN_BWD,
- OP_SOFTMAX_XENT, OP_CLASSIFY, OP_TRANSPOSE_W, OP_GRAD_SUMSQ, OP_OPTIMISER, OP_COPY) = range(25)
+ OP_SOFTMAX_XENT, OP_CLASSIFY, OP_TRANSPOSE_W, OP_GRAD_SUMSQ, OP_OPTIMISER, OP_COPY, OP_MATFACT) = range(26)
 
 F_RELU, F_ACCUM, F_STATS, F_TC = 1, 2, 4, 0x100
 

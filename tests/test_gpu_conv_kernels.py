@@ -121,9 +121,10 @@ def test_first_layer_three_channels(env):
 
 
 @pytest.mark.parametrize("shape", [(4, 32, 32, 16, 16, 3, 3, 1, 1), (4, 16, 16, 32, 32, 3, 3, 1, 1), (8, 8, 8, 64, 64, 3, 3, 1, 1),
-                                   (3, 9, 7, 16, 24, 3, 3, 1, 1), (2, 12, 12, 48, 20, 3, 3, 1, 1), (64, 32, 32, 16, 16, 3, 3, 1, 1)])
+                                   (3, 9, 7, 16, 24, 3, 3, 1, 1), (2, 12, 12, 48, 20, 3, 3, 1, 1), (64, 32, 32, 16, 16, 3, 3, 1, 1),
+                                   (2, 8, 8, 128, 256, 3, 3, 1, 1), (2, 6, 10, 20, 12, 3, 3, 1, 1), (1, 56, 56, 64, 64, 3, 3, 1, 1)])
 def test_wgrad_tensor_core_slab(env, shape):
-    """Weight gradient on tcgen05 with MN-major operands taken straight from the position-major slabs."""
+    """Weight gradient on tcgen05 with swizzled MN-major operands taken straight from the position-major tensors."""
     L, lib = env
     g, P, Q = _geom(L, *shape)
     lib.xb_tc_set_slab(3)
@@ -144,4 +145,4 @@ def test_wgrad_tensor_core_slab(env, shape):
         assert int(status[0]) == 0
         assert float((dw - dw_ref).abs().max()) / float(dw_ref.abs().max()) < 4e-3
     finally:
-        lib.xb_tc_set_slab(1)
+        lib.xb_tc_set_slab(3)
