@@ -269,12 +269,14 @@ __global__ void __launch_bounds__(WG_THREADS) conv3x3_wgrad_mn_kernel(const floa
       if (lane == 0 && alive) {
         tc_fence_after();
         const uint32_t sbase = base_u32 + (uint32_t)(it & 1) * stage_bytes;
-        for (int r = 0; r < 3; ++r) {
-          const uint32_t a0 = sbase + (uint32_t)(r * PW) * 128u;
-#pragma unroll 4
-          for (int j = 0; j < BM / 8; ++j) {
-            uint64_t ad = make_desc(a0 + (uint32_t)j * 1024u, 128, 512) | LAYOUT;
-            uint64_t bd = make_desc(sbase + xbytes + (uint32_t)j * 1024u, yplane, 512) | LAYOUT;
+        // The three filter rows accumulate into three independent TMEM regions; issuing them round-robin keeps
+        // consecutive MMAs independent (back-to-back MMAs on ONE accumulator serialise on its read-modify-write).
+#pragma unroll 2
+        for (int j = 0; j < BM / 8; ++j) {
+          const uint64_t bd = make_desc(sbase + xbytes + (uint32_t)j * 1024u, yplane, 512) | LAYOUT;
+#pragma unroll
+          for (int r = 0; r < 3; ++r) {
+            const uint64_t ad = make_desc(sbase + (uint32_t)(r * PW) * 128u + (uint32_t)j * 1024u, 128, 512) | LAYOUT;
             umma_tf32(tmem + (uint32_t)(r * NK), ad, bd, IDESC, (it == 0 && j == 0) ? 0u : 1u);
           }
         }

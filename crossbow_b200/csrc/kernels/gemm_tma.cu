@@ -1,0 +1,337 @@
+// 1x1 convolutions (and any plain GEMM over position-major tensors) on TMA + tcgen05.
+//
+// A 1x1 convolution over NHWC data is a GEMM whose operands already sit in memory in the shape the tensor core wants, so
+// nothing is gathered: TMA (cp.async.bulk.tensor) drops swizzled operand tiles into shared memory, one elected thread
+// issues tcgen05.mma into a TMEM accumulator, and four epilogue warps drain it.  Warp roles in a 192-thread CTA:
+//   warp 0      producer: waits for a free stage, arms its mbarrier with the byte count, issues the TMA loads
+//   warp 1      tensor core: waits for a full stage, issues 4 x (M128 x BN x K8, tf32), tcgen05.commit frees the stage
+//   warps 2..5  epilogue: wait for the accumulator, tcgen05.ld, bias / ReLU / accumulate / batch-norm sums, store
+// Two operand forms:
+//   NT  D[m][n] = sum_k A[m][k] B[n][k]        (fprop: A = X, B = W (K,C);  dgrad: A = dY, B = W^T (C,K))
+//       both operands K-major, 128-byte swizzle, 32 floats of K per stage.  A is described by a 3-D tensor map
+//       (channel, column, row) so that a stride-2 convolution is the same kernel with doubled global strides.
+//   TN  D[m][n] += sum_p A[p][m] B[p][n]       (wgrad: A = dY, B = X, reduction over positions)
+//       both operands MN-major in the "128-byte swizzle, 32-byte atom" layout - the one layout tcgen05 reads 32-bit
+//       MN-major data from - written by TMA with the matching swizzle mode; 32 positions per stage; the position range is
+//       split over gridDim.z and every CTA adds its partial product to D with vector reductions.
+// Every wait is bounded; on expiry the CTA records XB_TIMEOUT_MBAR in *status, drains and exits.
+#include <cuda.h>
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+using namespace tc;
+
+namespace {
+
+constexpr int GT = 192;
+constexpr int MAX_STAGES = 6;
+constexpr int G_RELU = 1, G_ACCUM = 2, G_STATS = 4;
+constexpr uint32_t A_BYTES = 128 * 128;                 // 128 rows (or 4 planes x 32 positions) x 128 B
+
+struct GemmArgs {
+  int M, N;            // NT: real output rows / columns.  TN: output rows (filters) / columns (input channels)
+  int kblocks;         // NT: ceil(K / 32).  TN: ceil(positions / 32)
+  int mvalid;          // NT: rows of one tile that exist (box columns x box rows <= 128)
+  int c1_step, c2_step;  // NT: A coordinates of tile t are {k, t * c1_step, t * c2_step}
+  int a_bytes;         // NT: bytes one A box delivers
+  int ldd;             // floats between rows of D
+  int stages;
+  int kb_per_split;    // TN: position blocks per gridDim.z slice
+};
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                                                      float* __restrict__ D, const float* __restrict__ bias, float* __restrict__ stats,
+                                                      GemmArgs g, int flags, int* status) {
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
+  constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (MODE ? (3u << 15) : 0u) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], accum_bar;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+  __shared__ float s_red[2 * BN];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x, n0 = blockIdx.y * BN;
+  const int stages = g.stages;
+  const uint32_t base = smem_u32(smem);
+  int kb0 = 0, kb1 = g.kblocks;
+  if (MODE == 1) { kb0 = blockIdx.z * g.kb_per_split; kb1 = kb0 + g.kb_per_split < g.kblocks ? kb0 + g.kb_per_split : g.kblocks; }
+  const int nkb = kb1 - kb0;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&accum_bar, 1);
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) tmem_alloc(&s_tmem, TMEM_COLS);
+  for (int i = tid; i < 2 * BN; i += GT) s_red[i] = 0.f;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+
+  if (nkb > 0) {
+    if (warp == 0) {
+      if (lane == 0) {
+        for (int i = 0; i < nkb; ++i) {
+          const int s = i % stages, kb = kb0 + i;
+          if (i >= stages && !mbar_wait(&empty_bar[s], (uint32_t)((i / stages) - 1) & 1u)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); break; }
+          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + A_BYTES;
+          if (MODE == 0) {
+            mbar_expect_tx(&full_bar[s], (uint32_t)g.a_bytes + B_BYTES);
+            tma_load_3d(sa, &tmA, kb * 32, tile * g.c1_step, tile * g.c2_step, &full_bar[s]);
+            tma_load_2d(sb, &tmB, kb * 32, n0, &full_bar[s]);
+          } else {
+            mbar_expect_tx(&full_bar[s], STAGE);
+            tma_load_3d(sa, &tmA, 0, kb * 32, tile * 4, &full_bar[s]);
+            tma_load_3d(sb, &tmB, 0, kb * 32, n0 >> 5, &full_bar[s]);
+          }
+        }
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      if (lane == 0) {
+        for (int i = 0; i < nkb; ++i) {
+          const int s = i % stages;
+          if (!mbar_wait(&full_bar[s], (uint32_t)(i / stages) & 1u)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); break; }
+          tc_fence_after();
+          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            uint64_t ad, bd;
+            if (MODE == 0) {
+              ad = make_desc(sa + kk * 32, 16, 1024) | LAYOUT_SW128;
+              bd = make_desc(sb + kk * 32, 16, 1024) | LAYOUT_SW128;
+            } else {
+              ad = make_desc(sa + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
+              bd = make_desc(sb + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
+            }
+            umma_tf32(tmem, ad, bd, IDESC, (i | kk) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);
+        }
+        umma_commit(&accum_bar);                           // arrives once every MMA issued above has completed
+      }
+      __syncwarp();
+    } else {
+      // ---- epilogue: TMEM lane quadrant (warp & 3) ----
+      const bool done = mbar_wait(&accum_bar, 0);
+      if (!done) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
+      tc_fence_after();
+      const int q = warp & 3, row = q * 32 + lane;
+      if (done && !s_abort) {
+        if (MODE == 0) {
+          const long long m = (long long)tile * g.mvalid + row;
+          const bool ok = row < g.mvalid && m < g.M;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (n0 + c0 >= g.N) break;                     // whole-warp condition
+            float v[16];
+            tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+            float* orow = D + m * g.ldd + n0 + c0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int n = n0 + c0 + j;
+              float x = v[j];
+              if (bias && n < g.N) x += bias[n];
+              if (flags & G_RELU) x = fmaxf(x, 0.f);
+              if ((flags & G_ACCUM) && ok && n < g.N) x += orow[j];
+              v[j] = (ok && n < g.N) ? x : 0.f;
+            }
+            if (ok) {
+              if (n0 + c0 + 16 <= g.N) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(orow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) if (n0 + c0 + j < g.N) orow[j] = v[j];
+              }
+            }
+            if (flags & G_STATS) {
+              float sq[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) sq[j] = v[j] * v[j];
+              int col;
+              const float sx = warp_colsum16(v, lane, col), sqq = warp_colsum16(sq, lane, col);
+              if (lane < 16) { atomicAdd(&s_red[c0 + col], sx); atomicAdd(&s_red[BN + c0 + col], sqq); }
+            }
+          }
+        } else {
+          const int m = tile * 128 + row;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (n0 + c0 >= g.N) break;
+            float v[16];
+            tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+            if (m < g.M) {
+              float* orow = D + (long long)m * g.ldd + n0 + c0;
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) if (n0 + c0 + j < g.N) red_add_v4(orow + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (MODE == 0 && (flags & G_STATS) && !s_abort) {
+    for (int i = tid; i < BN; i += GT) {
+      const int n = n0 + i;
+      if (n < g.N) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.N + n], s_red[BN + i]); }
+    }
+  }
+  if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// ---- host side ----------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// rank-2 or rank-3 fp32 tensor map; strides[i] = bytes between consecutive indices of dimension i+1
+int make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -XB_BAD_ARG;
+  const cuuint32_t ones[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -XB_BAD_ARG;
+}
+
+constexpr size_t kSmemLimit = 200 * 1024;
+inline size_t stage_bytes(int BN) { return A_BYTES + (size_t)BN * 128; }
+
+template <int BN, int MODE>
+int launch(const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags, int* status,
+           cudaStream_t st) {
+  const size_t smem = (size_t)g.stages * stage_bytes(BN);
+  gemm_tma_kernel<BN, MODE><<<grid, GT, smem, st>>>(a, b, D, bias, stats, g, flags, status);
+  return (int)cudaGetLastError();
+}
+template <int MODE>
+int launch_bn(int BN, const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags,
+              int* status, cudaStream_t st) {
+  switch (BN) {
+    case 32: return launch<32, MODE>(a, b, D, bias, stats, g, grid, flags, status, st);
+    case 64: return launch<64, MODE>(a, b, D, bias, stats, g, grid, flags, status, st);
+    case 128: return launch<128, MODE>(a, b, D, bias, stats, g, grid, flags, status, st);
+    default: return launch<256, MODE>(a, b, D, bias, stats, g, grid, flags, status, st);
+  }
+}
+template <int BN, int MODE>
+int configure() { return (int)cudaFuncSetAttribute(gemm_tma_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit); }
+
+inline bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline bool is_1x1(const XbConvGeom* g) { return g->R == 1 && g->S == 1 && g->ph == 0 && g->pw == 0 && g->sh == g->sw && (g->sh == 1 || g->sh == 2); }
+
+}  // namespace
+
+XB_API int xb_gemm_tma_init() {
+  int e;
+  if (!encode_fn()) return 0;                            // no driver entry point: the callers keep to the gather kernels
+  if ((e = configure<32, 0>()) || (e = configure<64, 0>()) || (e = configure<128, 0>()) || (e = configure<256, 0>())) return e;
+  if ((e = configure<32, 1>()) || (e = configure<64, 1>()) || (e = configure<128, 1>()) || (e = configure<256, 1>())) return e;
+  return 0;
+}
+
+// which: 0 fprop (stride 1 or 2), 1 dgrad (stride 1), 2 wgrad (stride 1)
+XB_API int xb_conv1x1_tma_supported(const XbConvGeom* g, int which) {
+  if (!encode_fn() || !is_1x1(g)) return 0;
+  if (g->C % 4 || g->K % 4) return 0;
+  if ((long long)g->N * g->H * g->W >= (1ll << 31)) return 0;
+  if (which == 0) {
+    if (g->sh == 1) return 1;
+    return (g->H % 2 == 0 && g->W % 2 == 0 && g->Q <= 128) ? 1 : 0;
+  }
+  if (g->sh != 1) return 0;
+  if (which == 1) return 1;
+  return (g->C % 32 == 0 && g->K % 32 == 0) ? 1 : 0;
+}
+
+// which 0: In = X (N,H,W,C), Wb = weights (K,C), Out = Y (N,P,Q,K).  which 1: In = dY (N,P,Q,K), Wb = transposed weights (C,K), Out = dX.
+XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which, int flags,
+                          int* status, cudaStream_t st) {
+  if (!aligned16p(In) || !aligned16p(Wb) || !aligned16p(Out) || !xb_conv1x1_tma_supported(cg, which)) return -XB_BAD_ARG;
+  const int Kred = which == 0 ? cg->C : cg->K, Nout = which == 0 ? cg->K : cg->C;
+  GemmArgs g{};
+  CUtensorMap ta, tb;
+  int tiles_m;
+  if (cg->sh == 1) {
+    const long long P = (long long)cg->N * cg->H * cg->W;
+    const cuuint64_t dims[3] = {(cuuint64_t)Kred, (cuuint64_t)P, 1};
+    const cuuint64_t strides[2] = {(cuuint64_t)Kred * 4, (cuuint64_t)Kred * 4 * (cuuint64_t)P};
+    const cuuint32_t box[3] = {32, 128, 1};
+    if (make_map(&ta, In, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
+    g.M = (int)P; g.mvalid = 128; g.c1_step = 128; g.c2_step = 0; g.a_bytes = (int)A_BYTES;
+    tiles_m = (int)((P + 127) / 128);
+  } else {
+    // stride 2: output pixel (n, p, q) reads input pixel (n, 2p, 2q); with H even, row n*H + 2p = 2 * (n*P + p)
+    const int rows = cg->N * cg->P, bw = cg->Q, br = 128 / bw;
+    const cuuint64_t dims[3] = {(cuuint64_t)Kred, (cuuint64_t)bw, (cuuint64_t)rows};
+    const cuuint64_t strides[2] = {(cuuint64_t)Kred * 4 * 2, (cuuint64_t)Kred * 4 * 2 * (cuuint64_t)cg->W};
+    const cuuint32_t box[3] = {32, (cuuint32_t)bw, (cuuint32_t)br};
+    if (make_map(&ta, In, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
+    g.M = rows * bw; g.mvalid = bw * br; g.c1_step = 0; g.c2_step = br; g.a_bytes = bw * br * 128;
+    tiles_m = (rows + br - 1) / br;
+  }
+  int BN = Nout <= 32 ? 32 : Nout <= 64 ? 64 : Nout <= 128 ? 128 : 256;
+  while (BN > 64 && (long long)tiles_m * ((Nout + BN - 1) / BN) < 148) BN >>= 1;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)Kred, (cuuint64_t)Nout};
+    const cuuint64_t strides[1] = {(cuuint64_t)Kred * 4};
+    const cuuint32_t box[2] = {32, (cuuint32_t)BN};
+    if (make_map(&tb, Wb, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
+  }
+  g.N = Nout; g.kblocks = (Kred + 31) / 32; g.ldd = Nout;
+  g.stages = g.kblocks < 4 ? g.kblocks : 4;
+  while ((size_t)g.stages * stage_bytes(BN) > kSmemLimit) --g.stages;
+  dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
+  return launch_bn<0>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st);
+}
+
+// dW (K,C) += dY^T X over all positions; dW must hold the value to accumulate onto (normally zero).
+XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st) {
+  if (!aligned16p(dY) || !aligned16p(X) || !aligned16p(dW) || !xb_conv1x1_tma_supported(cg, 2)) return -XB_BAD_ARG;
+  const long long P = (long long)cg->N * cg->H * cg->W;
+  const int BN = cg->C <= 32 ? 32 : cg->C <= 64 ? 64 : cg->C <= 128 ? 128 : 256;
+  CUtensorMap ta, tb;
+  {
+    const cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(cg->K / 32)};
+    const cuuint64_t strides[2] = {(cuuint64_t)cg->K * 4, 128};
+    const cuuint32_t box[3] = {32, 32, 4};
+    if (make_map(&ta, dY, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
+  }
+  {
+    const cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(cg->C / 32)};
+    const cuuint64_t strides[2] = {(cuuint64_t)cg->C * 4, 128};
+    const cuuint32_t box[3] = {32, 32, (cuuint32_t)(BN / 32)};
+    if (make_map(&tb, X, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
+  }
+  GemmArgs g{};
+  g.M = cg->K; g.N = cg->C; g.ldd = cg->C;
+  g.kblocks = (int)((P + 31) / 32);
+  const int tiles = ((cg->K + 127) / 128) * ((cg->C + BN - 1) / BN);
+  int splits = (2 * 148 + tiles - 1) / tiles;
+  if (splits > g.kblocks) splits = g.kblocks;
+  g.kb_per_split = (g.kblocks + splits - 1) / splits;
+  splits = (g.kblocks + g.kb_per_split - 1) / g.kb_per_split;
+  g.stages = g.kb_per_split < 4 ? g.kb_per_split : 4;
+  while ((size_t)g.stages * stage_bytes(BN) > kSmemLimit) --g.stages;
+  dim3 grid((unsigned)((cg->K + 127) / 128), (unsigned)((cg->C + BN - 1) / BN), (unsigned)splits);
+  return launch_bn<1>(BN, ta, tb, dW, nullptr, nullptr, g, grid, 0, status, st);
+}

@@ -253,6 +253,15 @@ XB_API int xb_conv3x3_slab(const float* In, const float* Wb, const float* bias, 
                            int flags, int* status, cudaStream_t st);
 XB_API int xb_conv3x3_wgrad_slab(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st);
 static int g_use_slab = 3;
+static int g_use_tma = 1;
+XB_API int xb_gemm_tma_init();
+XB_API int xb_conv_wgrad_simt(const float*, const float*, float*, const XbConvGeom*, cudaStream_t);
+XB_API int xb_conv1x1_tma_supported(const XbConvGeom* g, int which);
+XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which, int flags,
+                          int* status, cudaStream_t st);
+XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st);
+// 1: 1x1 convolutions run on the TMA-fed GEMM kernel where it applies (else the gather kernel).  For A/B comparisons.
+XB_API void xb_tc_set_tma(int on) { g_use_tma = on; }
 // bit 0: 3x3/stride-1 fprop + dgrad use the slab kernel (else the generic gather kernel); bit 1: the tensor-core weight
 // gradient kernel is used where it applies (else CUDA cores).  For A/B comparisons.
 XB_API void xb_tc_set_slab(int mask) { g_use_slab = mask; }
@@ -261,6 +270,7 @@ XB_API void xb_tc_set_slab(int mask) { g_use_slab = mask; }
 XB_API int xb_tc_init() {
   int e;
   if ((e = xb_conv3x3_slab_init())) return e;
+  if ((e = xb_gemm_tma_init())) return e;
   if ((e = configure_tc<16, 4>())) return e;
   if ((e = configure_tc<32, 4>())) return e;
   if ((e = configure_tc<64, 4>())) return e;
@@ -274,6 +284,7 @@ XB_API int xb_tc_init() {
 XB_API int xb_tc_supported(const XbConvGeom* g, int which) {
   if (which == 0) return (g->C % 4 == 0) ? 1 : 0;
   if (which == 1) return (g->K % 4 == 0) ? 1 : 0;
+  if (g_use_tma && xb_conv1x1_tma_supported(g, 2)) return 1;
   return (g_use_slab & 2) && xb_conv3x3_slab_supported(g, 2) ? 1 : 0;
 }
 
@@ -281,6 +292,10 @@ XB_API int xb_conv_fprop_tc(const float* X, const float* W, const float* bias, f
                             int* status, cudaStream_t st) {
   if (!aligned16(X) || !aligned16(W) || !aligned16(Y) || cg->C % 4) return -XB_BAD_ARG;
   if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 0)) return xb_conv3x3_slab(X, W, bias, Y, stats, cg, 0, flags, status, st);
+  if (g_use_tma && xb_conv1x1_tma_supported(cg, 0)) {
+    const int r = xb_conv1x1_tma(X, W, bias, Y, stats, cg, 0, flags, status, st);
+    if (r != -XB_BAD_ARG) return r;                      // (tensor map refused: fall back to the gather kernel)
+  }
   TcProblem g;
   g.M = cg->N * cg->P * cg->Q; g.OH = cg->P; g.OW = cg->Q; g.IH = cg->H; g.IW = cg->W; g.CR = cg->C; g.NG = cg->K;
   g.R = cg->R; g.S = cg->S; g.sh = cg->sh; g.sw = cg->sw; g.ph = cg->ph; g.pw = cg->pw; g.transposed = 0; g.KG = cg->R * cg->S * cg->C;
@@ -289,12 +304,21 @@ XB_API int xb_conv_fprop_tc(const float* X, const float* W, const float* bias, f
 XB_API int xb_conv_dgrad_tc(const float* dY, const float* Wt, float* dX, const XbConvGeom* cg, int accumulate, int* status, cudaStream_t st) {
   if (!aligned16(dY) || !aligned16(Wt) || !aligned16(dX) || cg->K % 4) return -XB_BAD_ARG;
   if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 1)) return xb_conv3x3_slab(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);
+  if (g_use_tma && xb_conv1x1_tma_supported(cg, 1)) {
+    const int r = xb_conv1x1_tma(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);
+    if (r != -XB_BAD_ARG) return r;
+  }
   TcProblem g;
   g.M = cg->N * cg->H * cg->W; g.OH = cg->H; g.OW = cg->W; g.IH = cg->P; g.IW = cg->Q; g.CR = cg->K; g.NG = cg->C;
   g.R = cg->R; g.S = cg->S; g.sh = cg->sh; g.sw = cg->sw; g.ph = cg->ph; g.pw = cg->pw; g.transposed = 1; g.KG = cg->R * cg->S * cg->K;
   return dispatch_tc(dY, Wt, nullptr, dX, nullptr, g, accumulate ? F_ACCUM : 0, status, st);
 }
 XB_API int xb_conv_wgrad_tc(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st) {
-  if (!aligned16(dY) || !aligned16(X) || !xb_conv3x3_slab_supported(cg, 2)) return -XB_BAD_ARG;
+  if (!aligned16(dY) || !aligned16(X)) return -XB_BAD_ARG;
+  if (g_use_tma && xb_conv1x1_tma_supported(cg, 2)) {
+    const int r = xb_conv1x1_wgrad_tma(dY, X, dW, cg, status, st);
+    return r != -XB_BAD_ARG ? r : xb_conv_wgrad_simt(dY, X, dW, cg, st);
+  }
+  if (!xb_conv3x3_slab_supported(cg, 2)) return -XB_BAD_ARG;
   return xb_conv3x3_wgrad_slab(dY, X, dW, cg, status, st);
 }

@@ -110,11 +110,33 @@ __device__ __forceinline__ float warp_colsum16(const float (&in)[16], int lane, 
   return d;
 }
 
-// shared-memory matrix descriptor with an explicit layout / major selection.
-//   K-major, no swizzle : element (row, k-chunk) at (row%8)*16 + (row/8)*SBO + chunk*LBO bytes
-//   MN-major, no swizzle: element (mn-group of 4, k) at (k%8)*16 + (k/8)*LBO + group*SBO bytes
-__device__ __forceinline__ uint64_t make_desc_raw(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  return make_desc(saddr, lbo_bytes, sbo_bytes);
+// Layout-type field (bits 61..63) of a shared-memory matrix descriptor.
+//   LAYOUT_SW128        : 128-byte swizzle, 16-byte chunks XOR-ed with the row index mod 8 (8 rows x 128 B atoms; K-major
+//                         operands; SBO = 1024 B between 8-row groups; a K step inside the atom advances the start address).
+//   LAYOUT_SW128_BASE32 : 128-byte rows whose 32-byte chunks are XOR-ed with address bits 7..8 (4 rows x 128 B atoms).  The
+//                         only layout in which tcgen05 reads 32-bit MN-major operands: SBO = stride between groups of four
+//                         K rows, LBO = stride between groups of 32 MN elements.
+constexpr uint64_t LAYOUT_SW128_BASE32 = 1ull << 61;
+constexpr uint64_t LAYOUT_SW128 = 2ull << 61;
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Tiled TMA loads into this CTA's shared memory, completion signalled on an mbarrier of the same CTA.  The innermost
+// coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 }  // namespace tc

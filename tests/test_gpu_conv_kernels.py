@@ -21,6 +21,11 @@ SHAPES = [
     (64, 1, 1, 256, 10, 1, 1, 1, 0),    # inner product
     (5, 1, 1, 1000, 520, 1, 1, 1, 0),
     (2, 23, 23, 12, 16, 7, 7, 2, 3),
+    (8, 56, 56, 64, 256, 1, 1, 1, 0),   # 1x1 convolutions: TMA-fed GEMM
+    (2, 7, 7, 512, 2048, 1, 1, 1, 0),
+    (4, 28, 28, 256, 128, 1, 1, 2, 0),
+    (2, 8, 8, 48, 40, 1, 1, 1, 0),      # reduction tail, N tile wider than the layer
+    (3, 10, 10, 96, 64, 1, 1, 1, 0),
 ]
 
 
@@ -102,6 +107,14 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
     torch.cuda.synchronize()
     dw_ref = wr.grad.permute(0, 2, 3, 1)
     assert float((dw - dw_ref).abs().max()) / (float(dw_ref.abs().max()) + 1e-6) < (tol if impl == "tc" else 2e-4)
+
+
+def test_1x1_shapes_take_the_tma_path(env):
+    L, lib = env
+    for shape, which, want in [((8, 56, 56, 64, 256, 1, 1, 1, 0), 0, 1), ((8, 56, 56, 64, 256, 1, 1, 1, 0), 1, 1), ((8, 56, 56, 64, 256, 1, 1, 1, 0), 2, 1),
+                               ((4, 28, 28, 256, 128, 1, 1, 2, 0), 0, 1), ((2, 8, 8, 48, 40, 1, 1, 1, 0), 2, 0), ((4, 16, 16, 32, 32, 3, 3, 1, 1), 0, 0)]:
+        g, _, _ = _geom(L, *shape)
+        assert lib.xb_conv1x1_tma_supported(C.byref(g), which) == want
 
 
 def test_first_layer_three_channels(env):
