@@ -10,6 +10,10 @@
 //   NT  D[m][n] = sum_k A[m][k] B[n][k]        (fprop: A = X, B = W (K,C);  dgrad: A = dY, B = W^T (C,K))
 //       both operands K-major, 128-byte swizzle, 32 floats of K per stage.  A is described by a 3-D tensor map
 //       (channel, column, row) so that a stride-2 convolution is the same kernel with doubled global strides.
+//   CONV the NT form as an implicit GEMM for R x S / stride 1 / "same" convolutions: the reduction index is (tap, channel
+//       block); the A tile of a tap is ONE 4-D TMA box (channel, column, row, image) whose start coordinate is shifted by
+//       the tap - rows and columns outside the image arrive as zeros from the TMA unit, so padding costs nothing and no
+//       index arithmetic runs on the SM.  The data gradient is the same kernel over dY with the taps mirrored.
 //   TN  D[m][n] += sum_p A[p][m] B[p][n]       (wgrad: A = dY, B = X, reduction over positions)
 //       both operands MN-major in the "128-byte swizzle, 32-byte atom" layout - the one layout tcgen05 reads 32-bit
 //       MN-major data from - written by TMA with the matching swizzle mode; 32 positions per stage; the position range is
@@ -24,7 +28,7 @@ using namespace tc;
 namespace {
 
 constexpr int GT = 192;
-constexpr int MAX_STAGES = 6;
+constexpr int MAX_STAGES = 8;
 constexpr int G_RELU = 1, G_ACCUM = 2, G_STATS = 4;
 constexpr uint32_t A_BYTES = 128 * 128;                 // 128 rows (or 4 planes x 32 positions) x 128 B
 
@@ -37,6 +41,8 @@ struct GemmArgs {
   int ldd;             // floats between rows of D
   int stages;
   int kb_per_split;    // TN: position blocks per gridDim.z slice
+  // CONV: the A box is {32 channels, bw columns, bh rows, bn images}; tiles are numbered (image group, row group, column group)
+  int c32, R, S, ph, pw, H, W, NI, bw, bh, bn, tiles_w, tiles_h, mirrored, krow;
 };
 
 template <int BN, int MODE>
@@ -45,7 +51,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
                                                       GemmArgs g, int flags, int* status) {
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   constexpr uint32_t B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
-  constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (MODE ? (3u << 15) : 0u) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+  constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (MODE == 1 ? (3u << 15) : 0u) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], accum_bar;
   __shared__ uint32_t s_tmem;
@@ -86,6 +92,13 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
             mbar_expect_tx(&full_bar[s], (uint32_t)g.a_bytes + B_BYTES);
             tma_load_3d(sa, &tmA, kb * 32, tile * g.c1_step, tile * g.c2_step, &full_bar[s]);
             tma_load_2d(sb, &tmB, kb * 32, n0, &full_bar[s]);
+          } else if (MODE == 2) {
+            const int tap = kb / g.c32, cb = kb - tap * g.c32, r = tap / g.S, sx = tap - r * g.S;
+            const int wt = tile % g.tiles_w, t2 = tile / g.tiles_w, ht = t2 % g.tiles_h, nt = t2 / g.tiles_h;
+            const int btap = g.mirrored ? g.R * g.S - 1 - tap : tap;
+            mbar_expect_tx(&full_bar[s], (uint32_t)g.a_bytes + B_BYTES);
+            tma_load_4d(sa, &tmA, cb * 32, wt * g.bw + sx - g.pw, ht * g.bh + r - g.ph, nt * g.bn, &full_bar[s]);
+            tma_load_2d(sb, &tmB, btap * g.krow + cb * 32, n0, &full_bar[s]);
           } else {
             mbar_expect_tx(&full_bar[s], STAGE);
             tma_load_3d(sa, &tmA, 0, kb * 32, tile * 4, &full_bar[s]);
@@ -104,7 +117,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             uint64_t ad, bd;
-            if (MODE == 0) {
+            if (MODE != 1) {
               ad = make_desc(sa + kk * 32, 16, 1024) | LAYOUT_SW128;
               bd = make_desc(sb + kk * 32, 16, 1024) | LAYOUT_SW128;
             } else {
@@ -125,9 +138,19 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
       tc_fence_after();
       const int q = warp & 3, row = q * 32 + lane;
       if (done && !s_abort) {
-        if (MODE == 0) {
-          const long long m = (long long)tile * g.mvalid + row;
-          const bool ok = row < g.mvalid && m < g.M;
+        if (MODE != 1) {
+          long long m;
+          bool ok;
+          if (MODE == 0) {
+            m = (long long)tile * g.mvalid + row;
+            ok = row < g.mvalid && m < g.M;
+          } else {
+            const int wt = tile % g.tiles_w, t2 = tile / g.tiles_w, ht = t2 % g.tiles_h, nt = t2 / g.tiles_h;
+            const int wo = row % g.bw, t3 = row / g.bw, ho = t3 % g.bh, no = t3 / g.bh;
+            const int w = wt * g.bw + wo, h = ht * g.bh + ho, n = nt * g.bn + no;
+            ok = no < g.bn && w < g.W && h < g.H && n < g.NI;
+            m = ((long long)n * g.H + h) * g.W + w;
+          }
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 16) {
             if (n0 + c0 >= g.N) break;                     // whole-warp condition
@@ -180,7 +203,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
   }
   tc_fence_before();
   __syncthreads();
-  if (MODE == 0 && (flags & G_STATS) && !s_abort) {
+  if (MODE != 1 && (flags & G_STATS) && !s_abort) {
     for (int i = tid; i < BN; i += GT) {
       const int n = n0 + i;
       if (n < g.N) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.N + n], s_red[BN + i]); }
@@ -207,7 +230,7 @@ EncodeTiledFn encode_fn() {
 int make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle sw) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -XB_BAD_ARG;
-  const cuuint32_t ones[3] = {1, 1, 1};
+  const cuuint32_t ones[4] = {1, 1, 1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -XB_BAD_ARG;
@@ -215,6 +238,14 @@ int make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims,
 
 constexpr size_t kSmemLimit = 200 * 1024;
 inline size_t stage_bytes(int BN) { return A_BYTES + (size_t)BN * 128; }
+// Pipeline depth: as deep as the reduction, within a shared-memory budget that still lets two CTAs share an SM when the
+// grid has more CTAs than SMs (the second CTA's loads and MMAs then overlap the first one's epilogue).
+inline int pick_stages(int kblocks, int BN, long long ctas) {
+  const size_t budget = ctas > 148 ? 100 * 1024 : kSmemLimit;
+  int s = kblocks < MAX_STAGES ? kblocks : MAX_STAGES;
+  while (s > 2 && (size_t)s * stage_bytes(BN) > budget) --s;
+  return s;
+}
 
 template <int BN, int MODE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags, int* status,
@@ -245,6 +276,7 @@ XB_API int xb_gemm_tma_init() {
   int e;
   if (!encode_fn()) return 0;                            // no driver entry point: the callers keep to the gather kernels
   if ((e = configure<32, 0>()) || (e = configure<64, 0>()) || (e = configure<128, 0>()) || (e = configure<256, 0>())) return e;
+  if ((e = configure<32, 2>()) || (e = configure<64, 2>()) || (e = configure<128, 2>()) || (e = configure<256, 2>())) return e;
   if ((e = configure<32, 1>()) || (e = configure<64, 1>()) || (e = configure<128, 1>()) || (e = configure<256, 1>())) return e;
   return 0;
 }
@@ -298,9 +330,8 @@ XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, f
     if (make_map(&tb, Wb, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
   }
   g.N = Nout; g.kblocks = (Kred + 31) / 32; g.ldd = Nout;
-  g.stages = g.kblocks < 4 ? g.kblocks : 4;
-  while ((size_t)g.stages * stage_bytes(BN) > kSmemLimit) --g.stages;
   dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
+  g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y);
   return launch_bn<0>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st);
 }
 
@@ -330,8 +361,55 @@ XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, cons
   if (splits > g.kblocks) splits = g.kblocks;
   g.kb_per_split = (g.kblocks + splits - 1) / splits;
   splits = (g.kblocks + g.kb_per_split - 1) / g.kb_per_split;
-  g.stages = g.kb_per_split < 4 ? g.kb_per_split : 4;
-  while ((size_t)g.stages * stage_bytes(BN) > kSmemLimit) --g.stages;
   dim3 grid((unsigned)((cg->K + 127) / 128), (unsigned)((cg->C + BN - 1) / BN), (unsigned)splits);
+  g.stages = pick_stages(g.kb_per_split, BN, (long long)grid.x * grid.y * grid.z);
   return launch_bn<1>(BN, ta, tb, dW, nullptr, nullptr, g, grid, 0, status, st);
+}
+
+// which: 0 fprop (C % 32 == 0), 1 dgrad (K % 32 == 0).  R x S, stride 1, output extent = input extent.
+XB_API int xb_conv_tma_supported(const XbConvGeom* g, int which) {
+  if (!encode_fn()) return 0;
+  if (g->sh != 1 || g->sw != 1 || g->P != g->H || g->Q != g->W) return 0;
+  if (2 * g->ph != g->R - 1 || 2 * g->pw != g->S - 1) return 0;
+  const int Kred = which == 0 ? g->C : g->K, Nout = which == 0 ? g->K : g->C;
+  if (which > 1 || Kred % 32 || Nout % 4) return 0;
+  return 1;
+}
+
+// which 0: In = X, Wb = weights (K,R,S,C), Out = Y.  which 1: In = dY, Wb = transposed weights (C,R,S,K), Out = dX.
+XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which, int flags,
+                       int* status, cudaStream_t st) {
+  if (!aligned16p(In) || !aligned16p(Wb) || !aligned16p(Out) || !xb_conv_tma_supported(cg, which)) return -XB_BAD_ARG;
+  const int Kred = which == 0 ? cg->C : cg->K, Nout = which == 0 ? cg->K : cg->C;
+  GemmArgs g{};
+  g.H = cg->H; g.W = cg->W; g.NI = cg->N; g.R = cg->R; g.S = cg->S; g.ph = cg->ph; g.pw = cg->pw;
+  g.bw = cg->W < 128 ? cg->W : 128;
+  g.bh = 128 / g.bw < cg->H ? 128 / g.bw : cg->H;
+  if (g.bh < 1) g.bh = 1;
+  g.bn = 128 / (g.bw * g.bh) < cg->N ? 128 / (g.bw * g.bh) : cg->N;
+  if (g.bn < 1) g.bn = 1;
+  g.tiles_w = (cg->W + g.bw - 1) / g.bw; g.tiles_h = (cg->H + g.bh - 1) / g.bh;
+  const int tiles_m = g.tiles_w * g.tiles_h * ((cg->N + g.bn - 1) / g.bn);
+  g.c32 = Kred / 32; g.mirrored = which; g.krow = Kred;
+  g.a_bytes = g.bw * g.bh * g.bn * 128;
+  g.M = cg->N * cg->H * cg->W; g.N = Nout; g.ldd = Nout;
+  g.kblocks = cg->R * cg->S * g.c32;
+  CUtensorMap ta, tb;
+  {
+    const cuuint64_t dims[4] = {(cuuint64_t)Kred, (cuuint64_t)cg->W, (cuuint64_t)cg->H, (cuuint64_t)cg->N};
+    const cuuint64_t strides[3] = {(cuuint64_t)Kred * 4, (cuuint64_t)Kred * 4 * cg->W, (cuuint64_t)Kred * 4 * cg->W * cg->H};
+    const cuuint32_t box[4] = {32, (cuuint32_t)g.bw, (cuuint32_t)g.bh, (cuuint32_t)g.bn};
+    if (make_map(&ta, In, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
+  }
+  int BN = Nout <= 32 ? 32 : Nout <= 64 ? 64 : Nout <= 128 ? 128 : 256;
+  while (BN > 64 && (long long)tiles_m * ((Nout + BN - 1) / BN) < 120) BN >>= 1;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)cg->R * cg->S * Kred, (cuuint64_t)Nout};
+    const cuuint64_t strides[1] = {(cuuint64_t)cg->R * cg->S * Kred * 4};
+    const cuuint32_t box[2] = {32, (cuuint32_t)BN};
+    if (make_map(&tb, Wb, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
+  }
+  dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
+  g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y);
+  return launch_bn<2>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st);
 }

@@ -262,6 +262,13 @@ XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, f
 XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st);
 // 1: 1x1 convolutions run on the TMA-fed GEMM kernel where it applies (else the gather kernel).  For A/B comparisons.
 XB_API void xb_tc_set_tma(int on) { g_use_tma = on; }
+XB_API int xb_conv_tma_supported(const XbConvGeom* g, int which);
+XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which, int flags,
+                       int* status, cudaStream_t st);
+// R x S stride-1 convolutions with at least this many reduction channels run as a TMA implicit GEMM, narrower ones on the
+// slab kernel (one staged copy of the input serves all taps, which wins while the filter bank is small).
+static int g_tma_conv_min = 64;
+XB_API void xb_tc_set_tma_conv_min(int c) { g_tma_conv_min = c; }
 // bit 0: 3x3/stride-1 fprop + dgrad use the slab kernel (else the generic gather kernel); bit 1: the tensor-core weight
 // gradient kernel is used where it applies (else CUDA cores).  For A/B comparisons.
 XB_API void xb_tc_set_slab(int mask) { g_use_slab = mask; }
@@ -291,6 +298,10 @@ XB_API int xb_tc_supported(const XbConvGeom* g, int which) {
 XB_API int xb_conv_fprop_tc(const float* X, const float* W, const float* bias, float* Y, float* stats, const XbConvGeom* cg, int flags,
                             int* status, cudaStream_t st) {
   if (!aligned16(X) || !aligned16(W) || !aligned16(Y) || cg->C % 4) return -XB_BAD_ARG;
+  if (g_use_tma && (cg->R > 1 || cg->S > 1) && cg->C >= g_tma_conv_min && xb_conv_tma_supported(cg, 0)) {
+    const int r = xb_conv_tma(X, W, bias, Y, stats, cg, 0, flags, status, st);
+    if (r != -XB_BAD_ARG) return r;
+  }
   if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 0)) return xb_conv3x3_slab(X, W, bias, Y, stats, cg, 0, flags, status, st);
   if (g_use_tma && xb_conv1x1_tma_supported(cg, 0)) {
     const int r = xb_conv1x1_tma(X, W, bias, Y, stats, cg, 0, flags, status, st);
@@ -303,6 +314,10 @@ XB_API int xb_conv_fprop_tc(const float* X, const float* W, const float* bias, f
 }
 XB_API int xb_conv_dgrad_tc(const float* dY, const float* Wt, float* dX, const XbConvGeom* cg, int accumulate, int* status, cudaStream_t st) {
   if (!aligned16(dY) || !aligned16(Wt) || !aligned16(dX) || cg->K % 4) return -XB_BAD_ARG;
+  if (g_use_tma && (cg->R > 1 || cg->S > 1) && cg->K >= g_tma_conv_min && xb_conv_tma_supported(cg, 1)) {
+    const int r = xb_conv_tma(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);
+    if (r != -XB_BAD_ARG) return r;
+  }
   if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 1)) return xb_conv3x3_slab(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);
   if (g_use_tma && xb_conv1x1_tma_supported(cg, 1)) {
     const int r = xb_conv1x1_tma(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);

@@ -86,6 +86,8 @@ def load() -> C.CDLL:
     _sig(lib, "xb_tc_init", I)
     _sig(lib, "xb_tc_set_slab", None, I)
     _sig(lib, "xb_tc_set_tma", None, I)
+    _sig(lib, "xb_tc_set_tma_conv_min", None, I)
+    _sig(lib, "xb_conv_tma_supported", I, G, I)
     _sig(lib, "xb_conv1x1_tma_supported", I, G, I)
     _sig(lib, "xb_conv3x3_slab_supported", I, G, I)
     _sig(lib, "xb_transpose_weights", I, P, P, P, I, I, P)

@@ -26,6 +26,11 @@ SHAPES = [
     (4, 28, 28, 256, 128, 1, 1, 2, 0),
     (2, 8, 8, 48, 40, 1, 1, 1, 0),      # reduction tail, N tile wider than the layer
     (3, 10, 10, 96, 64, 1, 1, 1, 0),
+    (2, 56, 56, 64, 64, 3, 3, 1, 1),    # wide 3x3: implicit GEMM over 4-D TMA boxes
+    (3, 14, 14, 256, 256, 3, 3, 1, 1),
+    (5, 7, 7, 512, 96, 3, 3, 1, 1),     # two images per tile
+    (1, 6, 150, 64, 32, 3, 3, 1, 1),    # rows wider than a tile
+    (2, 9, 11, 64, 96, 5, 5, 1, 2),
 ]
 
 
@@ -53,7 +58,7 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
     g, P, Q = _geom(L, *shape)
     if impl == "tc" and not lib.xb_tc_supported(C.byref(g), 0):
         pytest.skip("shape not covered by the tensor-core path")
-    tol = 1e-4 if impl == "simt" else 4e-3
+    tol = 1e-4 if impl == "simt" else (4e-3 if R * S * Cc <= 1152 else 8e-3)   # tf32 operands: error grows with the reduction length
     dev = torch.device("cuda")
     gen = torch.Generator(device="cuda").manual_seed(1)
     x = torch.randn(N, H, W, Cc, device=dev, generator=gen)
