@@ -43,6 +43,12 @@ struct GemmArgs {
   int kb_per_split;    // TN: position blocks per gridDim.z slice
   // CONV: the A box is {32 channels, bw columns, bh rows, bn images}; tiles are numbered (image group, row group, column group)
   int c32, R, S, ph, pw, H, W, NI, bw, bh, bn, tiles_w, tiles_h, mirrored, krow;
+  // NT with a strided output (data gradient of a stride-2 1x1 convolution): row m = (n, p, q) of the GEMM is written to
+  // pixel (n, 2p, 2q) of an (oH, oW) image.  0 = rows are written where they are.
+  int oP, oQ, oH, oW;
+  // TN over a sub-sampled B (weight gradient of a stride-2 1x1 convolution): one reduction block = rpb output rows of Q
+  // positions (ppb = rpb * Q <= 32); rows ppb..31 of every stage stay zero.  0 = 32 consecutive positions per block.
+  int rpb, ppb;
 };
 
 template <int BN, int MODE>
@@ -76,6 +82,11 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
   }
   if (warp == 1) tmem_alloc(&s_tmem, TMEM_COLS);
   for (int i = tid; i < 2 * BN; i += GT) s_red[i] = 0.f;
+  if (MODE == 1 && g.rpb) {                              // rows the boxes never write must read as zero
+    const int words = stages * (int)(STAGE / 16);
+    for (int i = tid; i < words; i += GT) reinterpret_cast<float4*>(smem)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    fence_async_smem();
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -99,10 +110,15 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
             mbar_expect_tx(&full_bar[s], (uint32_t)g.a_bytes + B_BYTES);
             tma_load_4d(sa, &tmA, cb * 32, wt * g.bw + sx - g.pw, ht * g.bh + r - g.ph, nt * g.bn, &full_bar[s]);
             tma_load_2d(sb, &tmB, btap * g.krow + cb * 32, n0, &full_bar[s]);
-          } else {
+          } else if (g.rpb == 0) {
             mbar_expect_tx(&full_bar[s], STAGE);
             tma_load_3d(sa, &tmA, 0, kb * 32, tile * 4, &full_bar[s]);
             tma_load_3d(sb, &tmB, 0, kb * 32, n0 >> 5, &full_bar[s]);
+          } else {
+            // one box per 32-channel plane, so that the planes keep their 4096-byte pitch although a box has fewer than 32 rows
+            mbar_expect_tx(&full_bar[s], (uint32_t)g.ppb * 128u * (4u + BN / 32u));
+            for (int pl = 0; pl < 4; ++pl) tma_load_3d(sa + pl * 4096, &tmA, 0, kb * g.ppb, tile * 4 + pl, &full_bar[s]);
+            for (int pl = 0; pl < BN / 32; ++pl) tma_load_4d(sb + pl * 4096, &tmB, 0, 0, kb * g.rpb, (n0 >> 5) + pl, &full_bar[s]);
           }
         }
       }
@@ -144,6 +160,10 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
           if (MODE == 0) {
             m = (long long)tile * g.mvalid + row;
             ok = row < g.mvalid && m < g.M;
+            if (g.oQ && ok) {
+              const int q = (int)(m % g.oQ); const long long t = m / g.oQ; const int pp = (int)(t % g.oP); const long long n = t / g.oP;
+              m = (n * g.oH + 2 * pp) * g.oW + 2 * q;
+            }
           } else {
             const int wt = tile % g.tiles_w, t2 = tile / g.tiles_w, ht = t2 % g.tiles_h, nt = t2 / g.tiles_h;
             const int wo = row % g.bw, t3 = row / g.bw, ho = t3 % g.bh, no = t3 / g.bh;
@@ -281,7 +301,7 @@ XB_API int xb_gemm_tma_init() {
   return 0;
 }
 
-// which: 0 fprop (stride 1 or 2), 1 dgrad (stride 1), 2 wgrad (stride 1)
+// which: 0 fprop, 1 dgrad, 2 wgrad; stride 1 or 2
 XB_API int xb_conv1x1_tma_supported(const XbConvGeom* g, int which) {
   if (!encode_fn() || !is_1x1(g)) return 0;
   if (g->C % 4 || g->K % 4) return 0;
@@ -290,9 +310,10 @@ XB_API int xb_conv1x1_tma_supported(const XbConvGeom* g, int which) {
     if (g->sh == 1) return 1;
     return (g->H % 2 == 0 && g->W % 2 == 0 && g->Q <= 128) ? 1 : 0;
   }
-  if (g->sh != 1) return 0;
+  if (g->sh != 1 && (g->H % 2 || g->W % 2)) return 0;
   if (which == 1) return 1;
-  return (g->C % 32 == 0 && g->K % 32 == 0) ? 1 : 0;
+  if (g->C % 32 || g->K % 32) return 0;
+  return (g->sh == 1 || g->Q <= 32) ? 1 : 0;
 }
 
 // which 0: In = X (N,H,W,C), Wb = weights (K,C), Out = Y (N,P,Q,K).  which 1: In = dY (N,P,Q,K), Wb = transposed weights (C,K), Out = dX.
@@ -303,14 +324,23 @@ XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, f
   GemmArgs g{};
   CUtensorMap ta, tb;
   int tiles_m;
-  if (cg->sh == 1) {
-    const long long P = (long long)cg->N * cg->H * cg->W;
+  if (cg->sh == 1 || which == 1) {
+    // rows of the GEMM = consecutive pixels of In (for the data gradient of a stride-2 layer: of dY, the small image)
+    const long long P = which == 1 ? (long long)cg->N * cg->P * cg->Q : (long long)cg->N * cg->H * cg->W;
     const cuuint64_t dims[3] = {(cuuint64_t)Kred, (cuuint64_t)P, 1};
     const cuuint64_t strides[2] = {(cuuint64_t)Kred * 4, (cuuint64_t)Kred * 4 * (cuuint64_t)P};
     const cuuint32_t box[3] = {32, 128, 1};
     if (make_map(&ta, In, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
     g.M = (int)P; g.mvalid = 128; g.c1_step = 128; g.c2_step = 0; g.a_bytes = (int)A_BYTES;
     tiles_m = (int)((P + 127) / 128);
+    if (cg->sh == 2) {
+      g.oP = cg->P; g.oQ = cg->Q; g.oH = cg->H; g.oW = cg->W;
+      // pixels no output maps to receive no gradient: clear them unless the caller accumulates
+      if (!(flags & G_ACCUM)) {
+        cudaError_t e = cudaMemsetAsync(Out, 0, (size_t)cg->N * cg->H * cg->W * Nout * sizeof(float), st);
+        if (e != cudaSuccess) return (int)e;
+      }
+    }
   } else {
     // stride 2: output pixel (n, p, q) reads input pixel (n, 2p, 2q); with H even, row n*H + 2p = 2 * (n*P + p)
     const int rows = cg->N * cg->P, bw = cg->Q, br = 128 / bw;
@@ -338,24 +368,31 @@ XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, f
 // dW (K,C) += dY^T X over all positions; dW must hold the value to accumulate onto (normally zero).
 XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st) {
   if (!aligned16p(dY) || !aligned16p(X) || !aligned16p(dW) || !xb_conv1x1_tma_supported(cg, 2)) return -XB_BAD_ARG;
-  const long long P = (long long)cg->N * cg->H * cg->W;
+  const long long P = (long long)cg->N * cg->P * cg->Q;   // positions of dY
   const int BN = cg->C <= 32 ? 32 : cg->C <= 64 ? 64 : cg->C <= 128 ? 128 : 256;
+  const int rpb = cg->sh == 1 ? 0 : (32 / cg->Q < cg->N * cg->P ? 32 / cg->Q : cg->N * cg->P), ppb = rpb * cg->Q;
   CUtensorMap ta, tb;
   {
     const cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(cg->K / 32)};
     const cuuint64_t strides[2] = {(cuuint64_t)cg->K * 4, 128};
-    const cuuint32_t box[3] = {32, 32, 4};
+    const cuuint32_t box[3] = {32, (cuuint32_t)(rpb ? ppb : 32), (cuuint32_t)(rpb ? 1 : 4)};
     if (make_map(&ta, dY, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
   }
-  {
+  if (rpb == 0) {
     const cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(cg->C / 32)};
     const cuuint64_t strides[2] = {(cuuint64_t)cg->C * 4, 128};
     const cuuint32_t box[3] = {32, 32, (cuuint32_t)(BN / 32)};
     if (make_map(&tb, X, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
+  } else {
+    // every second pixel of every second row: (channel in plane, q, n*P + p, plane)
+    const cuuint64_t dims[4] = {32, (cuuint64_t)cg->Q, (cuuint64_t)cg->N * cg->P, (cuuint64_t)(cg->C / 32)};
+    const cuuint64_t strides[3] = {(cuuint64_t)cg->C * 4 * 2, (cuuint64_t)cg->C * 4 * 2 * cg->W, 128};
+    const cuuint32_t box[4] = {32, (cuuint32_t)cg->Q, (cuuint32_t)rpb, 1};
+    if (make_map(&tb, X, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
   }
   GemmArgs g{};
-  g.M = cg->K; g.N = cg->C; g.ldd = cg->C;
-  g.kblocks = (int)((P + 31) / 32);
+  g.M = cg->K; g.N = cg->C; g.ldd = cg->C; g.rpb = rpb; g.ppb = ppb;
+  g.kblocks = rpb ? (cg->N * cg->P + rpb - 1) / rpb : (int)((P + 31) / 32);
   const int tiles = ((cg->K + 127) / 128) * ((cg->C + BN - 1) / BN);
   int splits = (2 * 148 + tiles - 1) / tiles;
   if (splits > g.kblocks) splits = g.kblocks;

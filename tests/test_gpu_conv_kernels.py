@@ -24,6 +24,8 @@ SHAPES = [
     (8, 56, 56, 64, 256, 1, 1, 1, 0),   # 1x1 convolutions: TMA-fed GEMM
     (2, 7, 7, 512, 2048, 1, 1, 1, 0),
     (4, 28, 28, 256, 128, 1, 1, 2, 0),
+    (2, 56, 56, 64, 96, 1, 1, 2, 0),
+    (3, 14, 14, 64, 128, 1, 1, 2, 0),   # stride 2: reduction blocks of whole output rows, last block partial
     (2, 8, 8, 48, 40, 1, 1, 1, 0),      # reduction tail, N tile wider than the layer
     (3, 10, 10, 96, 64, 1, 1, 1, 0),
     (2, 56, 56, 64, 64, 3, 3, 1, 1),    # wide 3x3: implicit GEMM over 4-D TMA boxes
