@@ -63,6 +63,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ float s_red[2 * BN];
+  __shared__ long long s_rowoff[4][32];                  // float offset of every tile row in D, -1 for rows that do not exist
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, n0 = blockIdx.y * BN;
@@ -171,38 +172,62 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
             ok = no < g.bn && w < g.W && h < g.H && n < g.NI;
             m = ((long long)n * g.H + h) * g.W + w;
           }
+          // Thread = row after tcgen05.ld, but a row-per-thread store touches 32 lines per instruction.  So every warp
+          // transposes 32 x 32 blocks through shared memory: afterwards eight lanes cover the 128 contiguous bytes of one
+          // row, an instruction writes four full lines, and the batch-norm sums need two shuffles per column group.
+          // (the pipeline stages are idle by now - every load has landed and every MMA has completed - and serve as the buffer)
+          float (*tb)[33] = reinterpret_cast<float (*)[33]>(smem + (size_t)q * 32 * 33 * sizeof(float));
+          s_rowoff[q][lane] = ok ? m * g.ldd : -1ll;
+          __syncwarp();
+          const int cq = (lane & 7) * 4, rsub = lane >> 3;
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) {
+          for (int c0 = 0; c0 < BN; c0 += 32) {
             if (n0 + c0 >= g.N) break;                     // whole-warp condition
-            float v[16];
-            tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-            float* orow = D + m * g.ldd + n0 + c0;
+            {
+              float v[16];
+              tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int n = n0 + c0 + j;
-              float x = v[j];
-              if (bias && n < g.N) x += bias[n];
-              if (flags & G_RELU) x = fmaxf(x, 0.f);
-              if ((flags & G_ACCUM) && ok && n < g.N) x += orow[j];
-              v[j] = (ok && n < g.N) ? x : 0.f;
+              for (int j = 0; j < 16; ++j) tb[lane][j] = v[j];
+              tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(c0 + 16), v);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) tb[lane][16 + j] = v[j];
             }
-            if (ok) {
-              if (n0 + c0 + 16 <= g.N) {
+            __syncwarp();
+            const int n = n0 + c0 + cq;                    // first of this lane's four columns
+            const bool ncol = n < g.N;                     // (N is a multiple of 4)
+            float b4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (bias && ncol) { b4[0] = bias[n]; b4[1] = bias[n + 1]; b4[2] = bias[n + 2]; b4[3] = bias[n + 3]; }
+            float sx[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(orow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-              } else {
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + rsub;
+              const long long off = s_rowoff[q][r];
+              if (off >= 0 && ncol) {
+                float x[4];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) if (n0 + c0 + j < g.N) orow[j] = v[j];
+                for (int k = 0; k < 4; ++k) {
+                  x[k] = tb[r][cq + k] + b4[k];
+                  if (flags & G_RELU) x[k] = fmaxf(x[k], 0.f);
+                }
+                float4* o = reinterpret_cast<float4*>(D + off + n);
+                if (flags & G_ACCUM) { const float4 old = *o; x[0] += old.x; x[1] += old.y; x[2] += old.z; x[3] += old.w; }
+                *o = make_float4(x[0], x[1], x[2], x[3]);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { sx[k] += x[k]; sq[k] += x[k] * x[k]; }
               }
             }
             if (flags & G_STATS) {
-              float sq[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) sq[j] = v[j] * v[j];
-              int col;
-              const float sx = warp_colsum16(v, lane, col), sqq = warp_colsum16(sq, lane, col);
-              if (lane < 16) { atomicAdd(&s_red[c0 + col], sx); atomicAdd(&s_red[BN + c0 + col], sqq); }
+              for (int k = 0; k < 4; ++k) {
+                sx[k] += __shfl_xor_sync(0xffffffffu, sx[k], 8);  sq[k] += __shfl_xor_sync(0xffffffffu, sq[k], 8);
+                sx[k] += __shfl_xor_sync(0xffffffffu, sx[k], 16); sq[k] += __shfl_xor_sync(0xffffffffu, sq[k], 16);
+              }
+              if (lane < 8 && ncol) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { atomicAdd(&s_red[c0 + cq + k], sx[k]); atomicAdd(&s_red[BN + c0 + cq + k], sq[k]); }
+              }
             }
+            __syncwarp();
           }
         } else {
           const int m = tile * 128 + row;
@@ -261,7 +286,7 @@ inline size_t stage_bytes(int BN) { return A_BYTES + (size_t)BN * 128; }
 // Pipeline depth: as deep as the reduction, within a shared-memory budget that still lets two CTAs share an SM when the
 // grid has more CTAs than SMs (the second CTA's loads and MMAs then overlap the first one's epilogue).
 inline int pick_stages(int kblocks, int BN, long long ctas) {
-  const size_t budget = ctas > 148 ? 100 * 1024 : kSmemLimit;
+  const size_t budget = ctas > 148 ? 108 * 1024 : kSmemLimit;
   int s = kblocks < MAX_STAGES ? kblocks : MAX_STAGES;
   while (s > 2 && (size_t)s * stage_bytes(BN) > budget) --s;
   return s;
