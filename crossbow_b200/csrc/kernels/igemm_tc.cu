@@ -273,6 +273,26 @@ XB_API void xb_tc_set_tma_conv_min(int c) { g_tma_conv_min = c; }
 // gradient kernel is used where it applies (else CUDA cores).  For A/B comparisons.
 XB_API void xb_tc_set_slab(int mask) { g_use_slab = mask; }
 
+XB_API long long xb_conv_im2col_scratch(const XbConvGeom* g, int which);
+// Bytes of scratch if the forward pass (which 0) or the weight gradient (which 2) of this layer should run as patch
+// matrix + GEMM: that is, when no direct tensor-core kernel covers it.  0 otherwise.
+XB_API long long xb_conv_im2col_wanted(const XbConvGeom* g, int which) {
+  if (!g_use_tma) return 0;
+  if (which == 0) {
+    if ((g_use_slab & 1) && xb_conv3x3_slab_supported(g, 0)) return 0;
+    if (xb_conv1x1_tma_supported(g, 0)) return 0;
+    if ((g->R > 1 || g->S > 1) && g->C >= g_tma_conv_min && xb_conv_tma_supported(g, 0)) return 0;
+  } else if (which == 2) {
+    if (xb_conv1x1_tma_supported(g, 2)) return 0;
+    if ((g_use_slab & 2) && xb_conv3x3_slab_supported(g, 2)) return 0;
+  } else {
+    return 0;
+  }
+  if (g->P == 1 && g->Q == 1 && g->H == 1 && g->W == 1) return 0;   // inner products keep to the GEMM-shaped kernels
+  const long long b = xb_conv_im2col_scratch(g, which);
+  return b <= (1ll << 30) ? b : 0;
+}
+
 // Opt in to the large dynamic shared-memory carve-outs once per process, outside any stream capture.
 XB_API int xb_tc_init() {
   int e;

@@ -19,6 +19,8 @@ XB_API int xb_conv_wgrad_simt(const float*, const float*, float*, const XbConvGe
 XB_API int xb_conv_fprop_tc(const float*, const float*, const float*, float*, float*, const XbConvGeom*, int, int*, cudaStream_t);
 XB_API int xb_conv_dgrad_tc(const float*, const float*, float*, const XbConvGeom*, int, int*, cudaStream_t);
 XB_API int xb_conv_wgrad_tc(const float*, const float*, float*, const XbConvGeom*, int*, cudaStream_t);
+XB_API int xb_conv_fprop_im2col(const float*, const float*, const float*, float*, float*, const XbConvGeom*, int, float*, int*, cudaStream_t);
+XB_API int xb_conv_wgrad_im2col(const float*, const float*, float*, const XbConvGeom*, float*, int*, cudaStream_t);
 XB_API int xb_tc_supported(const XbConvGeom*, int which);
 XB_API int xb_transpose_weights(const float*, float*, const XbTransposeDesc*, int, int, cudaStream_t);
 XB_API int xb_bn_stats(const float*, float*, int, int, cudaStream_t);
@@ -85,6 +87,9 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
                           o.ia[6], o.ia[7], o.fa[0], o.ia[8], (unsigned)o.ia[9], (const XbTaskParams*)o.p[3], st);
     case OP_CONV_FPROP: {
       XbConvGeom g = geom_of(o);
+      if (pr->use_tc && (o.flags & 0x100) && o.p[5])       // patch matrix + GEMM, scratch provided by the lowering
+        return xb_conv_fprop_im2col((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (float*)o.p[3], (float*)o.p[4], &g, o.flags & 0xff,
+                                    (float*)o.p[5], pr->tc_status, st);
       if (pr->use_tc && (o.flags & 0x100) && xb_tc_supported(&g, 0))
         return xb_conv_fprop_tc((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (float*)o.p[3], (float*)o.p[4], &g, o.flags & 0xff, pr->tc_status, st);
       return xb_conv_fprop_simt((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (float*)o.p[3], (float*)o.p[4], &g, o.flags & 0xff, st);
@@ -97,6 +102,8 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
     }
     case OP_CONV_WGRAD: {
       XbConvGeom g = geom_of(o);
+      if (pr->use_tc && (o.flags & 0x100) && o.p[3])
+        return xb_conv_wgrad_im2col((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, (float*)o.p[3], pr->tc_status, st);
       if (pr->use_tc && (o.flags & 0x100) && xb_tc_supported(&g, 2))
         return xb_conv_wgrad_tc((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, pr->tc_status, st);
       return xb_conv_wgrad_simt((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, st);

@@ -305,7 +305,10 @@ class Lowering:
                     self.node_info[id(m)]["stats_buf"] = stats
                     flags |= L.F_STATS
             info["geom"] = geom
-            self.emit(_op(L.OP_CONV_FPROP, flags, ia=geom, p=[x.buf, self.wptr(wv), bias, out.buf, stats]))
+            # layers no direct tensor-core kernel covers are lowered to a patch matrix + GEMM and need scratch for it
+            info["im2col"] = self._im2col_scratch(geom) if self.use_tc else None
+            self.emit(_op(L.OP_CONV_FPROP, flags, ia=geom, p=[x.buf, self.wptr(wv), bias, out.buf, stats,
+                                                              info["im2col"] if L.load().xb_conv_im2col_wanted(self._geom_struct(geom), 0) else None]))
             self.tensors[id(n)] = out
             return
         if kind == "batchnorm":
@@ -441,6 +444,16 @@ class Lowering:
             self.tensors[id(bn_node)] = None
         return out
 
+    def _geom_struct(self, geom):
+        g = L.XbConvGeom()
+        (g.N, g.H, g.W, g.C, g.K, g.R, g.S, g.P, g.Q, g.sh, g.sw, g.ph, g.pw) = [int(v) for v in geom]
+        return C.byref(g)
+
+    def _im2col_scratch(self, geom):
+        """Scratch for the patch-matrix path of one layer (shared by its forward and weight-gradient operators)."""
+        need = max(L.load().xb_conv_im2col_wanted(self._geom_struct(geom), 0), L.load().xb_conv_im2col_wanted(self._geom_struct(geom), 2))
+        return self.arena.alloc((need + 3) // 4) if need > 0 else None
+
     # ---- backward ----
     def _backward(self, fwd, differentiated):
         rep = self.replica
@@ -468,7 +481,8 @@ class Lowering:
                     self.emit(_op(L.OP_ACT_BWD, ia=[1, 0], fa=[0.0, 0.0], la=[out.numel], p=[dy, out.buf, out.buf, dy]))
                 wv = k.variables[0]
                 tc = L.F_TC if self.use_tc else 0
-                self.emit(_op(L.OP_CONV_WGRAD, tc, ia=geom, p=[dy, x.buf, self.wptr(wv, rep.g)]))
+                scratch = info.get("im2col") if (tc and L.load().xb_conv_im2col_wanted(self._geom_struct(geom), 2)) else None
+                self.emit(_op(L.OP_CONV_WGRAD, tc, ia=geom, p=[dy, x.buf, self.wptr(wv, rep.g), scratch]))
                 if len(k.variables) > 1:
                     self.emit(_op(L.OP_COLSUM, ia=[out.rows, out.c], p=[dy, self.wptr(k.variables[1], rep.g)]))
                 if x.needs_grad:

@@ -67,11 +67,12 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
     w = torch.randn(K, R, S, Cc, device=dev, generator=gen) * (1.0 / (R * S * Cc) ** 0.5)
     b = torch.randn(K, device=dev, generator=gen)
     dy = torch.randn(N, P, Q, K, device=dev, generator=gen)
-    xr = x.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
-    wr = w.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
-    yr = F.conv2d(xr, wr, b, stride=st, padding=pad)
-    yr.backward(dy.permute(0, 3, 1, 2))
-    y_ref = F.relu(yr.detach()).permute(0, 2, 3, 1)
+    # float64 reference: the library's fp32 convolution may itself pick a transform-domain algorithm with ~1e-3 error
+    xr = x.double().permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    wr = w.double().permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    yr = F.conv2d(xr, wr, b.double(), stride=st, padding=pad)
+    yr.backward(dy.double().permute(0, 3, 1, 2))
+    y_ref = F.relu(yr.detach()).permute(0, 2, 3, 1).float()
     s = torch.cuda.current_stream().cuda_stream
     status = torch.zeros(4, dtype=torch.int32, device=dev)
 
@@ -93,7 +94,7 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
 
     # data gradient (with and without accumulation) through the transposed weight copy
     wt = w.permute(3, 1, 2, 0).contiguous()
-    dx_ref = xr.grad.permute(0, 2, 3, 1)
+    dx_ref = xr.grad.permute(0, 2, 3, 1).float()
     for accum in (0, 1):
         dx = torch.full((N, H, W, Cc), 0.5, device=dev)
         if impl == "simt" or not lib.xb_tc_supported(C.byref(g), 1):
@@ -112,7 +113,7 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
     else:
         L.check(lib.xb_conv_wgrad_tc(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), status.data_ptr(), s), "wgrad")
     torch.cuda.synchronize()
-    dw_ref = wr.grad.permute(0, 2, 3, 1)
+    dw_ref = wr.grad.permute(0, 2, 3, 1).float()
     assert float((dw - dw_ref).abs().max()) / (float(dw_ref.abs().max()) + 1e-6) < (tol if impl == "tc" else 2e-4)
 
 
@@ -122,6 +123,46 @@ def test_1x1_shapes_take_the_tma_path(env):
                                ((4, 28, 28, 256, 128, 1, 1, 2, 0), 0, 1), ((2, 8, 8, 48, 40, 1, 1, 1, 0), 2, 0), ((4, 16, 16, 32, 32, 3, 3, 1, 1), 0, 0)]:
         g, _, _ = _geom(L, *shape)
         assert lib.xb_conv1x1_tma_supported(C.byref(g), which) == want
+
+
+@pytest.mark.parametrize("shape", [(2, 64, 64, 3, 64, 7, 7, 2, 3), (4, 32, 32, 16, 32, 3, 3, 2, 1), (2, 12, 12, 4, 32, 5, 5, 1, 2),
+                                   (3, 28, 28, 1, 20, 5, 5, 1, 0), (8, 32, 32, 3, 64, 3, 3, 1, 1)])
+def test_patch_matrix_gemm_path(env, shape):
+    """Layers without a direct tensor-core kernel: gather to a patch matrix, then the TMA GEMM (forward, weight gradient)."""
+    L, lib = env
+    N, H, W, Cc, K, R, S, st, pad = shape
+    g, P, Q = _geom(L, *shape)
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(N, H, W, Cc, device=dev, generator=gen)
+    w = torch.randn(K, R, S, Cc, device=dev, generator=gen) * (1.0 / (R * S * Cc) ** 0.5)
+    b = torch.randn(K, device=dev, generator=gen)
+    dy = torch.randn(N, P, Q, K, device=dev, generator=gen)
+    wr = w.permute(0, 3, 1, 2).contiguous().requires_grad_(True)
+    yr = F.conv2d(x.permute(0, 3, 1, 2), wr, b, stride=st, padding=pad)
+    yr.backward(dy.permute(0, 3, 1, 2))
+    y_ref = F.relu(yr.detach()).permute(0, 2, 3, 1)
+    need = lib.xb_conv_im2col_scratch(C.byref(g), 0)
+    assert need > 0 and lib.xb_conv_im2col_wanted(C.byref(g), 0) == need
+    scratch = torch.empty(need // 4, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    s = torch.cuda.current_stream().cuda_stream
+    y = torch.full((N, P, Q, K), 7.0, device=dev)
+    stats = torch.zeros(2 * K, device=dev)
+    L.check(lib.xb_conv_fprop_im2col(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), stats.data_ptr(), C.byref(g), 1 | 4, scratch.data_ptr(),
+                                     status.data_ptr(), s), "fprop")
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    assert float((y - y_ref).abs().max()) / float(y_ref.abs().max()) < 4e-3
+    m = y_ref.reshape(-1, K)
+    assert torch.allclose(stats[:K], m.sum(0), rtol=4e-2, atol=4e-2 * m.shape[0] ** 0.5)
+    if K % 32 == 0:
+        dw = torch.zeros(K, R, S, Cc, device=dev)
+        L.check(lib.xb_conv_wgrad_im2col(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), scratch.data_ptr(), status.data_ptr(), s), "wgrad")
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        dw_ref = wr.grad.permute(0, 2, 3, 1)
+        assert float((dw - dw_ref).abs().max()) / float(dw_ref.abs().max()) < 4e-3
 
 
 def test_first_layer_three_channels(env):

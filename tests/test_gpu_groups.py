@@ -126,10 +126,16 @@ def check_model(name, batch, use_tc, tol_f=2e-4, tol_b=1e-3, **kw):
             # a ReLU folded into a GEMM epilogue: the device has already masked this group's upstream gradient in
             # place with ITS OWN output sign, so differentiate the GEMM alone (a CPU-side mask could differ by
             # rounding for pre-activations that are almost zero)
-            target = head if (head.op.kernel.kind in ("conv", "innerproduct") and info[id(head)]["relu"] is not None) else v
+            relu_fused = info[id(head)]["relu"] is not None
+            target = head if relu_fused else v
             with torch.enable_grad():
                 out = eval_node(target, leaves, all_values - {vid}, True)
             gy = grad_nchw(t).reshape(out.shape)
+            if relu_fused and head.op.kernel.kind not in ("conv", "innerproduct"):
+                # normalisation (+ residual sum) + ReLU in one kernel: apply the DEVICE's mask to the upstream gradient and
+                # differentiate the part in front of the ReLU, for the same reason (an output within rounding of zero
+                # would otherwise flip one element of the reference now and then)
+                gy = gy * (nchw(t).reshape(out.shape) > 0)
             leaf_items = [(k, x) for k, x in leaves.items() if k != "input" and x.requires_grad]
             group_params = [(nid, ps) for nid, ps in params_cache.items()]
             wrt = [x for _, x in leaf_items] + [p_ for _, ps in group_params for p_ in ps]
@@ -159,7 +165,12 @@ def check_model(name, batch, use_tc, tol_f=2e-4, tol_b=1e-3, **kw):
                 ref = ref * (nchw(t).reshape(ref.shape) > 0)
             err = float((dev - ref).abs().max()) / (float(ref.abs().max()) + 1e-9)
             worst_b = max(worst_b, err)
-            assert err < tol_b, f"{name}: gradient w.r.t. output of {node_by_id[vid].op} off by {err:.3e}"
+            if err >= tol_b:          # say where: which images / channels / how many elements
+                bad = ((dev - ref).abs() > tol_b * float(ref.abs().max())).nonzero()
+                where = {d: sorted(set(bad[:, d].tolist()))[:12] for d in range(bad.shape[1])}
+                i0 = tuple(bad[0].tolist())
+                raise AssertionError(f"{name}: gradient w.r.t. output of {node_by_id[vid].op} off by {err:.3e}; {bad.shape[0]} of {dev.numel()} "
+                                     f"elements, index sets per dim {where}, first {i0}: dev {float(dev[i0]):.4e} ref {float(ref[i0]):.4e}")
         for var in m.variables:
             s = slice(var.offset, var.offset + var.elements())
             ref, dev = expected_dw[s], g_dev[s]
