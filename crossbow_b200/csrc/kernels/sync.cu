@@ -35,7 +35,7 @@ struct SyncArgs {
   int rank, G, k, algo;
   long long n;                 // elements (multiple of 4)
   int nchunks;
-  int chunk;                   // floats per chunk (multiple of 4*NT)
+  int chunk;                   // floats per chunk (multiple of 4*U*NT)
   unsigned int epoch;          // >= 1, increases by one per call
   int two_shot;
   int copy_to_replicas;        // overwrite replicas with z at the end
@@ -85,55 +85,100 @@ __device__ __forceinline__ float4 f4axpy(float s, float4 a, float4 b) { return m
 __device__ __forceinline__ float4 f4sub(float4 a, float4 b) { return make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w); }
 __device__ __forceinline__ float4 f4scale(float s, float4 a) { return make_float4(s * a.x, s * a.y, s * a.z, s * a.w); }
 
-// local reduction of one float4 lane + in-place replica correction
-__device__ __forceinline__ float4 local_part(const SyncArgs& a, long long i4) {
-  float4 acc = make_float4(0, 0, 0, 0);
+// The element loops below handle U float4 lanes per thread and iteration (lanes j, j+NT, ...): all loads of a step are
+// issued before the first dependent store, so every thread keeps 2U..3U 16-byte loads in flight - a plain one-lane loop
+// leaves the memory system half idle because the compiler may not move loads across the stores to possibly aliasing
+// pointers.
+constexpr int U = 4;
+
+// local reduction of U float4 lanes + in-place replica correction; lanes with ok[u] == false are skipped
+__device__ __forceinline__ void local_part(const SyncArgs& a, const long long (&i4)[U], const bool (&ok)[U], float4 (&acc)[U]) {
+#pragma unroll
+  for (int u = 0; u < U; ++u) acc[u] = make_float4(0, 0, 0, 0);
   if (a.algo == ALGO_SMA) {
-    const float4 z = reinterpret_cast<const float4*>(a.z)[i4];
+    float4 z[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (ok[u]) z[u] = reinterpret_cast<const float4*>(a.z)[i4[u]];
     for (int r = 0; r < a.k; ++r) {
-      float4* wp = reinterpret_cast<float4*>(a.w[r]) + i4;
-      float4 w = *wp;
-      float4 src = a.use_prev ? reinterpret_cast<const float4*>(a.prev[r])[i4] : w;
-      float4 d = f4scale(a.alpha, f4sub(src, z));
-      *wp = f4sub(w, d);
-      acc = f4add(acc, d);
+      float4* wp = reinterpret_cast<float4*>(a.w[r]);
+      const float4* pp = reinterpret_cast<const float4*>(a.prev[r]);
+      float4 w[U], src[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (ok[u]) w[u] = wp[i4[u]];
+      if (a.use_prev) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) if (ok[u]) src[u] = pp[i4[u]];
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) src[u] = w[u];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (ok[u]) {
+        const float4 d = f4scale(a.alpha, f4sub(src[u], z[u]));
+        wp[i4[u]] = f4sub(w[u], d);
+        acc[u] = f4add(acc[u], d);
+      }
     }
   } else if (a.algo == ALGO_SSGD) {
-    float4* gp = reinterpret_cast<float4*>(a.gacc) + i4;
-    acc = *gp;
-    *gp = make_float4(0, 0, 0, 0);
+    float4* gp = reinterpret_cast<float4*>(a.gacc);
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (ok[u]) acc[u] = gp[i4[u]];
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (ok[u]) gp[i4[u]] = make_float4(0, 0, 0, 0);
   } else {  // ALGO_POLYAK: sum of replicas
-    for (int r = 0; r < a.k; ++r) acc = f4add(acc, reinterpret_cast<const float4*>(a.w[r])[i4]);
+    for (int r = 0; r < a.k; ++r) {
+      const float4* wp = reinterpret_cast<const float4*>(a.w[r]);
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (ok[u]) acc[u] = f4add(acc[u], wp[i4[u]]);
+    }
   }
-  return acc;
 }
 
-// apply the all-reduced value D to z (and replicas)
-__device__ __forceinline__ void apply_total(const SyncArgs& a, long long i4, float4 D) {
-  float4* zp = reinterpret_cast<float4*>(a.z) + i4;
-  float4 z = *zp;
+// apply the all-reduced values D to z (and replicas)
+__device__ __forceinline__ void apply_total(const SyncArgs& a, const long long (&i4)[U], const bool (&ok)[U], float4 (&D)[U]) {
+  float4* zp = reinterpret_cast<float4*>(a.z);
+  float4 z[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) if (ok[u]) z[u] = zp[i4[u]];
   if (a.algo == ALGO_POLYAK) {
-    float4 mean = f4scale(a.scale, D);
-    z = make_float4(z.x + a.blend * (mean.x - z.x), z.y + a.blend * (mean.y - z.y), z.z + a.blend * (mean.z - z.z), z.w + a.blend * (mean.w - z.w));
-    *zp = z;
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (ok[u]) {
+      const float4 mean = f4scale(a.scale, D[u]);
+      z[u] = make_float4(z[u].x + a.blend * (mean.x - z[u].x), z[u].y + a.blend * (mean.y - z[u].y), z[u].z + a.blend * (mean.z - z[u].z),
+                         z[u].w + a.blend * (mean.w - z[u].w));
+      zp[i4[u]] = z[u];
+    }
     if (a.alpha > 0.f)
       for (int r = 0; r < a.k; ++r) {
-        float4* wp = reinterpret_cast<float4*>(a.w[r]) + i4;
-        float4 w = *wp;
-        *wp = f4sub(w, f4scale(a.alpha, f4sub(w, z)));
+        float4* wp = reinterpret_cast<float4*>(a.w[r]);
+        float4 w[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) if (ok[u]) w[u] = wp[i4[u]];
+#pragma unroll
+        for (int u = 0; u < U; ++u) if (ok[u]) wp[i4[u]] = f4sub(w[u], f4scale(a.alpha, f4sub(w[u], z[u])));
       }
     return;
   }
-  if (a.algo == ALGO_SSGD) D = f4scale(a.scale, D);
-  if (a.mu > 0.f) {
-    float4* lp = reinterpret_cast<float4*>(a.zlast) + i4;
-    D = f4axpy(a.mu, *lp, D);
-    *lp = D;
+  if (a.algo == ALGO_SSGD) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) D[u] = f4scale(a.scale, D[u]);
   }
-  z = f4add(z, D);
-  *zp = z;
+  if (a.mu > 0.f) {
+    float4* lp = reinterpret_cast<float4*>(a.zlast);
+    float4 l[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (ok[u]) l[u] = lp[i4[u]];
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (ok[u]) { D[u] = f4axpy(a.mu, l[u], D[u]); lp[i4[u]] = D[u]; }
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) if (ok[u]) { z[u] = f4add(z[u], D[u]); zp[i4[u]] = z[u]; }
   if (a.copy_to_replicas || a.algo == ALGO_SSGD)
-    for (int r = 0; r < a.k; ++r) reinterpret_cast<float4*>(a.w[r])[i4] = z;
+    for (int r = 0; r < a.k; ++r) {
+      float4* wp = reinterpret_cast<float4*>(a.w[r]);
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (ok[u]) wp[i4[u]] = z[u];
+    }
 }
 
 __global__ void __launch_bounds__(NT) fused_sync_kernel(const SyncArgs* __restrict__ per_rank) {
@@ -153,9 +198,12 @@ __global__ void __launch_bounds__(NT) fused_sync_kernel(const SyncArgs* __restri
 
   if (G == 1) {   // no exchange: one pass
     for (int c = blockIdx.x; c < a.nchunks; c += B)
-      for (int j = tid; j < CHUNK / 4; j += NT) {
-        long long i4 = (long long)c * (CHUNK / 4) + j;
-        if (i4 < n4) apply_total(a, i4, local_part(a, i4));
+      for (int j0 = tid; j0 < CHUNK / 4; j0 += U * NT) {
+        long long i4[U]; bool ok[U]; float4 acc[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) { i4[u] = (long long)c * (CHUNK / 4) + j0 + u * NT; ok[u] = i4[u] < n4; }
+        local_part(a, i4, ok, acc);
+        apply_total(a, i4, ok, acc);
       }
     return;
   }
@@ -168,13 +216,19 @@ __global__ void __launch_bounds__(NT) fused_sync_kernel(const SyncArgs* __restri
     const int owner = c % G;
     const long long dst_chunk = a.two_shot ? (c / G) : c;
     const long long off4 = (((long long)parity * G + me) * slot_elems + dst_chunk * CHUNK) / 4;
-    for (int j = tid; j < CHUNK / 4; j += NT) {
-      long long i4 = (long long)c * (CHUNK / 4) + j;
-      float4 acc = (i4 < n4) ? local_part(a, i4) : make_float4(0, 0, 0, 0);
+    for (int j0 = tid; j0 < CHUNK / 4; j0 += U * NT) {
+      long long i4[U]; bool ok[U]; float4 acc[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) { i4[u] = (long long)c * (CHUNK / 4) + j0 + u * NT; ok[u] = i4[u] < n4; }
+      local_part(a, i4, ok, acc);                         // (lanes past the end contribute zeros)
       if (a.two_shot) {
-        reinterpret_cast<float4*>(a.inbox[owner])[off4 + j] = acc;
+#pragma unroll
+        for (int u = 0; u < U; ++u) reinterpret_cast<float4*>(a.inbox[owner])[off4 + j0 + u * NT] = acc[u];
       } else {
-        for (int g = 0; g < G; ++g) reinterpret_cast<float4*>(a.inbox[g])[off4 + j] = acc;
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) reinterpret_cast<float4*>(a.inbox[g])[off4 + j0 + u * NT] = acc[u];
+        }
       }
     }
     __syncthreads();
@@ -197,13 +251,22 @@ __global__ void __launch_bounds__(NT) fused_sync_kernel(const SyncArgs* __restri
       __syncthreads();
       const bool ok = !s_fail;
       const long long res4 = ((long long)parity * a.nchunks + c) * (CHUNK / 4);
-      for (int j = tid; j < CHUNK / 4 && ok; j += NT) {
-        float4 t = make_float4(0, 0, 0, 0);
-        for (int src = 0; src < G; ++src) {
-          long long o4 = (((long long)parity * G + src) * slot_elems + (long long)(c / G) * CHUNK) / 4 + j;
-          t = f4add(t, __ldcg(reinterpret_cast<const float4*>(a.inbox[me]) + o4));
+      for (int j0 = tid; j0 < CHUNK / 4 && ok; j0 += U * NT) {
+        float4 t[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) t[u] = make_float4(0, 0, 0, 0);
+        for (int src = 0; src < G; ++src) {               // rank order: every owner adds in the same order
+          const long long o4 = (((long long)parity * G + src) * slot_elems + (long long)(c / G) * CHUNK) / 4 + j0;
+          float4 v[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) v[u] = __ldcg(reinterpret_cast<const float4*>(a.inbox[me]) + o4 + u * NT);
+#pragma unroll
+          for (int u = 0; u < U; ++u) t[u] = f4add(t[u], v[u]);
         }
-        for (int g = 0; g < G; ++g) reinterpret_cast<float4*>(a.result[g])[res4 + j] = t;
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) reinterpret_cast<float4*>(a.result[g])[res4 + j0 + u * NT] = t[u];
+        }
       }
       __syncthreads();
       if (ok && tid < G) { __threadfence_system(); st_release_sys(a.ready2[tid] + c, a.epoch); }
@@ -223,20 +286,25 @@ __global__ void __launch_bounds__(NT) fused_sync_kernel(const SyncArgs* __restri
     const bool fail = s_fail != 0;
     __syncthreads();            // everyone has read s_fail before thread 0 may reset it in the next iteration
     if (fail) continue;
-    for (int j = tid; j < CHUNK / 4; j += NT) {
-      long long i4 = (long long)c * (CHUNK / 4) + j;
-      if (i4 >= n4) break;
-      float4 D;
+    for (int j0 = tid; j0 < CHUNK / 4; j0 += U * NT) {
+      long long i4[U]; bool ok[U]; float4 D[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) { i4[u] = (long long)c * (CHUNK / 4) + j0 + u * NT; ok[u] = i4[u] < n4; D[u] = make_float4(0, 0, 0, 0); }
       if (a.two_shot) {
-        D = __ldcg(reinterpret_cast<const float4*>(a.result[me]) + ((long long)parity * a.nchunks + c) * (CHUNK / 4) + j);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (ok[u]) D[u] = __ldcg(reinterpret_cast<const float4*>(a.result[me]) + ((long long)parity * a.nchunks + c) * (CHUNK / 4) + j0 + u * NT);
       } else {
-        D = make_float4(0, 0, 0, 0);
         for (int src = 0; src < G; ++src) {
-          long long o4 = (((long long)parity * G + src) * slot_elems + (long long)c * CHUNK) / 4 + j;
-          D = f4add(D, __ldcg(reinterpret_cast<const float4*>(a.inbox[me]) + o4));
+          const long long o4 = (((long long)parity * G + src) * slot_elems + (long long)c * CHUNK) / 4 + j0;
+          float4 v[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) if (ok[u]) v[u] = __ldcg(reinterpret_cast<const float4*>(a.inbox[me]) + o4 + u * NT);
+#pragma unroll
+          for (int u = 0; u < U; ++u) if (ok[u]) D[u] = f4add(D[u], v[u]);
         }
       }
-      apply_total(a, i4, D);
+      apply_total(a, i4, ok, D);
     }
     __syncthreads();
   }
