@@ -42,7 +42,7 @@ def save_checkpoint(ctx, directory: str) -> str:
     _write(os.path.join(d, f"gpu-{dev:02d}-theModel-data.dat"), e.central_model())
     if gpu:
         m = ctx.model
-        _write(os.path.join(d, f"gpu-{dev:02d}-theModel-last.dat"), m.to_canonical(e.shared.zlast.cpu().numpy()))
+        _write(os.path.join(d, f"gpu-{dev:02d}-theModel-last.dat"), m.to_canonical(e.central_momentum().cpu().numpy()))
         for i, l in enumerate(e.learners):
             _write(os.path.join(d, f"gpu-{dev:02d}-replica-{i:03d}-data.dat"), e.replica_model(i))
             _write(os.path.join(d, f"gpu-{dev:02d}-replica-{i:03d}-last.dat"), m.to_canonical(l.rep.last.cpu().numpy()))

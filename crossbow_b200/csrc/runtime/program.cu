@@ -373,6 +373,7 @@ struct XbSyncDescMirror {
   float alpha, mu, scale, blend;
   float* w[16]; const float* prev[16]; float* z; float* zlast; float* gacc;
   float* inbox[8]; float* result[8]; unsigned int* flags[8]; int* status; double timeout_s;
+  float* zpeer[8];
 };
 XB_API int xb_fused_sync(const XbSyncDescMirror* d, void* args_dev, void* args_pinned, int max_blocks, cudaStream_t st);
 XB_API int xb_broadcast_model(const float* z, float* const* w_dev_array, int k, long long n, cudaStream_t st);

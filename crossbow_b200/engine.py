@@ -139,16 +139,18 @@ class GpuEngine:
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.device)
         init = torch.from_numpy(model.to_device(init_canonical)).to(self.device)
         from .lower import DeviceShared
-        self.shared = DeviceShared(model, self.device, init)
+        n = model.device_elements
+        Sync = FusedSynchroniser if fused_sync else ReferenceSynchroniser
+        # (created first: with several GPUs and a large model it provides the peer-visible home of the central model)
+        self.synchroniser = Sync(n, rank, world, two_shot, sync_timeout_s) if fused_sync else Sync(n, rank, world)
+        z_storage = self.synchroniser.central_storage() if hasattr(self.synchroniser, "central_storage") else None
+        self.shared = DeviceShared(model, self.device, init, z_storage)
         self.lr_mult = torch.from_numpy(model.to_device(model.lr_multipliers())).to(self.device) if model.has_lr_multipliers() else None
         self.learners: List[Learner] = []
         for i in range(replicas):
             self.learners.append(Learner(self, i, init))
         self.sync_stream = self.lib.xb_stream_create(-1)
         self.sync_event = self.lib.xb_event_create(0)
-        n = model.device_elements
-        Sync = FusedSynchroniser if fused_sync else ReferenceSynchroniser
-        self.synchroniser = Sync(n, rank, world, two_shot, sync_timeout_s) if fused_sync else Sync(n, rank, world)
         self.poly_count = 0
         self.bn_updates = 0
         self._exec = None
@@ -303,6 +305,12 @@ class GpuEngine:
             raise RuntimeError(f"a tensor-core kernel reported status {int(s[0])} (bounded wait expired)")
 
     # ---- model access (canonical order, host) ----
+    def central_momentum(self) -> torch.Tensor:
+        """Momentum vector of the central model (device order).  Collective when the chunk owners keep it in shares."""
+        self.finish()
+        sy = self.synchroniser
+        return sy.gather_momentum(self.shared.zlast) if getattr(sy, "owner_apply", False) else self.shared.zlast
+
     def central_model(self) -> np.ndarray:
         return self.model.to_canonical(self.shared.z.cpu().numpy())
 

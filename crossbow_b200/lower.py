@@ -85,9 +85,13 @@ class ReplicaBuffers:
 class DeviceShared:
     """State shared by all learners of one GPU: central model z, its momentum, S-SGD accumulator, BN running stats."""
 
-    def __init__(self, model: Model, device, init: torch.Tensor):
+    def __init__(self, model: Model, device, init: torch.Tensor, z_storage: Optional[torch.Tensor] = None):
         n = model.device_elements
-        self.z = init.clone()
+        if z_storage is not None:            # peer-visible memory provided by the synchroniser
+            self.z = z_storage
+            self.z.copy_(init)
+        else:
+            self.z = init.clone()
         self.zlast = torch.zeros(n, device=device)
         self.gacc = torch.zeros(n, device=device)
         self.run_mean: Dict[int, torch.Tensor] = {}

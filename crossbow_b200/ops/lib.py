@@ -41,7 +41,7 @@ class XbSyncDesc(C.Structure):
                 ("alpha", c_float), ("mu", c_float), ("scale", c_float), ("blend", c_float),
                 ("w", c_void_p * MAXK), ("prev", c_void_p * MAXK), ("z", c_void_p), ("zlast", c_void_p), ("gacc", c_void_p),
                 ("inbox", c_void_p * MAXG), ("result", c_void_p * MAXG), ("flags", c_void_p * MAXG),
-                ("status", c_void_p), ("timeout_s", C.c_double)]
+                ("status", c_void_p), ("timeout_s", C.c_double), ("zpeer", c_void_p * MAXG)]
 
 
 class XbSolverState(C.Structure):

@@ -70,6 +70,15 @@ class PeerBuffer:
                 self.ptrs[g] = p
                 self._imported.append(p)
 
+    def as_tensor(self, numel: int, device=None) -> torch.Tensor:
+        """This rank's buffer as a float32 tensor (no copy; the buffer must outlive the tensor)."""
+        class _Raw:
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (int(numel),), "typestr": "<f4", "data": (int(self.local), False), "version": 2}
+        self._keep = raw
+        return torch.as_tensor(raw, device=device if device is not None else torch.device("cuda", torch.cuda.current_device()))
+
     def close(self):
         for p in self._imported:
             self.lib.xb_ipc_close(p)

@@ -40,11 +40,34 @@ class FusedSynchroniser:
         self.args_size = (lib.xb_sync_args_size() + 255) // 256 * 256
         self.args_pinned = lib.xb_pinned_alloc(8 * self.args_size)    # ring: an upload may still be pending when the next is built
         self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
-        self.inbox = self.result = self.flags = None
+        self.inbox = self.result = self.flags = self.zbuf = None
         if world > 1:
             self.inbox = PeerBuffer(4 * lib.xb_sync_inbox_floats(n, world, int(self.two_shot)), rank, world, group)
             self.result = PeerBuffer(4 * lib.xb_sync_result_floats(n) if self.two_shot else 256, rank, world, group)
             self.flags = PeerBuffer(4 * lib.xb_sync_flag_words(n, world), rank, world, group)
+            if self.two_shot:
+                # peer-visible home for the central model: chunk owners then store the updated model straight into it
+                self.zbuf = PeerBuffer(4 * n, rank, world, group)
+
+    def central_storage(self) -> Optional[torch.Tensor]:
+        """Peer-visible tensor to keep the central model in (None when the exchange does not use one)."""
+        return self.zbuf.as_tensor(self.n) if self.zbuf is not None else None
+
+    @property
+    def owner_apply(self) -> bool:
+        return self.zbuf is not None
+
+    def gather_momentum(self, zlast: torch.Tensor) -> torch.Tensor:
+        """The central model's momentum vector in full.  With owner-apply every rank only maintains the chunks it owns
+        (chunk c belongs to rank c mod world); this call is collective."""
+        if not self.owner_apply:
+            return zlast
+        import torch.distributed as dist
+        chunk = int(self.lib.xb_sync_chunk(self.n))
+        owner = (torch.arange(self.n, device=zlast.device) // chunk) % self.world
+        full = torch.where(owner == self.rank, zlast, torch.zeros_like(zlast))
+        dist.all_reduce(full)
+        return full
 
     def descriptor(self, algo, replicas_w, replicas_prev, z, zlast, gacc, alpha, mu, scale, blend, copy, use_prev) -> L.XbSyncDesc:
         d = L.XbSyncDesc()
@@ -60,6 +83,9 @@ class FusedSynchroniser:
         if self.world > 1:
             for g in range(self.world):
                 d.inbox[g], d.result[g], d.flags[g] = self.inbox.ptrs[g], self.result.ptrs[g], self.flags.ptrs[g]
+            if self.zbuf is not None and z.data_ptr() == self.zbuf.local:
+                for g in range(self.world):
+                    d.zpeer[g] = self.zbuf.ptrs[g]
         d.status = self.status.data_ptr()
         d.timeout_s = self.timeout_s
         return d
@@ -80,7 +106,7 @@ class FusedSynchroniser:
             raise SyncTimeout(f"fused synchronisation gave up waiting for a peer (status {s}, epoch {self.epoch})")
 
     def close(self):
-        for b in (self.inbox, self.result, self.flags):
+        for b in (self.inbox, self.result, self.flags, self.zbuf):
             if b is not None:
                 b.close()
         self.lib.xb_device_free(self.args_dev)

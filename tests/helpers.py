@@ -18,7 +18,8 @@ def build_model(name, batch, solver=None, **kw):
     ishape = Shape([batch] + spec.input_shape)
     nid = spec.train.init(ishape, Shape([batch]), m)
     m.finalise()
-    spec.test.init(ishape, Shape([batch]), m, nid)
+    if spec.test is not None:
+        spec.test.init(ishape, Shape([batch]), m, nid)
     return spec, m, solver
 
 

@@ -314,7 +314,8 @@ def test_all_models_build_and_infer_shapes():
     for name in REGISTRY:
         kw = {"size": sizes[name]} if name in sizes else {}
         spec, m, _ = build_model(name, 2, **kw)
-        assert m.elements > 0 and spec.train.getLossNode() is not None and spec.test.getAccuracyNode() is not None
+        assert m.elements > 0 and spec.train.getLossNode() is not None
+        assert spec.test is None or spec.test.getAccuracyNode() is not None      # (matrix factorisation has no test graph)
     spec, m, _ = build_model("resnet32", 2)
     assert 460000 < m.elements < 470000
     spec, m, _ = build_model("resnet50", 2, size=224)

@@ -100,7 +100,8 @@ def test_failed_task_is_reported_not_fatal():
     with pytest.raises(RuntimeError_) as e:
         rt.train(50)
         rt.drain(5)
-    assert "task 5 failed on learner 1 with code 77" in str(e.value)
+    import re
+    assert re.search(r"task 5 failed on learner \d+ with code 77", str(e.value))      # (which learner took it depends on timing)
     assert rt.failed()
     rt.close()
 

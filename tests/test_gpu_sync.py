@@ -57,6 +57,7 @@ def _run_emulated(devs, n, algo, two_shot, epochs=3, **kw):
             d.z, d.zlast, d.gacc = Z[g].data_ptr(), ZL[g].data_ptr(), GA[g].data_ptr()
             for j in range(G):
                 d.inbox[j], d.result[j], d.flags[j] = inbox[j].data_ptr(), result[j].data_ptr(), flags[j].data_ptr()
+                d.zpeer[j] = Z[j].data_ptr() if kw.get("owner_apply", False) else None
             d.status, d.timeout_s = status.data_ptr(), 2.0
         L.check(lib.xb_fused_sync_emulated(descs, G, args.data_ptr(), 8, torch.cuda.current_stream().cuda_stream), "emulated sync")
         torch.cuda.synchronize()
@@ -76,6 +77,38 @@ def test_sma_matches_oracle(G, k, two_shot):
             for i in range(k):
                 assert torch.allclose(W[g][i].cpu(), devs[g].replicas[i].w, rtol=1e-5, atol=1e-6)
         # all GPUs hold bit-identical central models
+        for g in range(1, G):
+            assert torch.equal(Z[g], Z[0])
+
+
+def _owned(n, G, g):
+    """Mask of the elements whose chunk belongs to rank g (chunk c -> rank c mod G)."""
+    from crossbow_b200.ops import lib as L
+    chunk = int(L.load().xb_sync_chunk(n))
+    return ((torch.arange(n) // chunk) % G) == g
+
+
+@pytest.mark.parametrize("G,k,algo", [(2, 2, 0), (4, 1, 0), (8, 2, 0), (4, 2, 1), (4, 2, 2)])
+def test_owner_apply_matches_oracle(G, k, algo):
+    """Two-shot exchange in which the owner of a chunk updates the central model and stores it on every GPU; the
+    momentum of the central model is then kept by the owners only."""
+    n = 4096 * 9 + 2048
+    devs = _state(G, k, n, seed=7)
+    kw = {0: dict(alpha=0.1, mu=0.9), 1: dict(mu=0.9, scale=1.0 / (G * k)), 2: dict(alpha=0.05, scale=1.0 / (G * k), blend=1.0, epochs=1)}[algo]
+    for e, W, Z, ZL, GA in _run_emulated(devs, n, algo, True, owner_apply=True, **kw):
+        if algo == 0:
+            synchronise_sma(devs, 0.1, 0.9)
+        elif algo == 1:
+            synchronise_ssgd(devs, G * k, 0.9)
+        else:
+            synchronise_polyak_ruppert(devs, 0.05)
+        for g in range(G):
+            assert torch.allclose(Z[g].cpu(), devs[g].z, rtol=1e-5, atol=1e-6), f"epoch {e} z[{g}]"
+            if algo != 2:
+                own = _owned(n, G, g)
+                assert torch.allclose(ZL[g].cpu()[own], devs[g].z_last[own], rtol=1e-5, atol=1e-6)
+            for i in range(k):
+                assert torch.allclose(W[g][i].cpu(), devs[g].replicas[i].w, rtol=1e-5, atol=1e-6)
         for g in range(1, G):
             assert torch.equal(Z[g], Z[0])
 
