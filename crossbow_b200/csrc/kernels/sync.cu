@@ -187,7 +187,7 @@ __device__ __forceinline__ void apply_total(const SyncArgs& a, const long long (
     }
 }
 
-__global__ void __launch_bounds__(NT) fused_sync_kernel(const SyncArgs* __restrict__ per_rank) {
+__global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __restrict__ per_rank) {
   // the argument block is read thousands of times (pointer tables): keep a copy in shared memory
   __shared__ SyncArgs a;
   __shared__ int s_fail;
@@ -450,15 +450,15 @@ XB_API int xb_fused_sync(const XbSyncDesc* d, void* args_dev, void* args_pinned,
   fill_args(*h, *d);
   XB_CUDA_CHECK(cudaMemcpyAsync(args_dev, h, sizeof(SyncArgs), cudaMemcpyHostToDevice, st));
   if (max_blocks <= 0) {
-    // half of what the device can hold at once: every block must be resident (blocks wait on other GPUs' blocks) and the
-    // learners' kernels run next to this one
+    // two blocks per SM (one covers the other's fences and flag waits); every block must become resident, because blocks
+    // wait on other GPUs' blocks - the learners' kernels running next to this one never wait on it, so they drain
     static int cached = 0;
     if (!cached) {
       int dev = 0, sms = 148, per_sm = 1;
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_sync_kernel, NT, 0);
-      cached = sms * (per_sm > 2 ? per_sm / 2 : 1);
+      cached = sms * (per_sm >= 2 ? 2 : 1);
     }
     max_blocks = cached;
   }

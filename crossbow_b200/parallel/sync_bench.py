@@ -64,9 +64,12 @@ def main():
             g = torch.Generator(device="cuda").manual_seed(1 + rank)
             ws = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
             ps = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
-            z, zl = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
             two = None if a.two_shot == "auto" else a.two_shot == "1"
             fs = FusedSynchroniser(n, rank, world, two_shot=two)
+            # the central model lives where the synchroniser wants it (peer-visible memory when chunk owners store into it)
+            z = fs.central_storage()
+            z = z.zero_() if z is not None else torch.zeros(n, device="cuda")
+            zl = torch.zeros(n, device="cuda")
             rs = ReferenceSynchroniser(n, rank, world)
             s = stream.cuda_stream
             with torch.cuda.stream(stream):
@@ -74,11 +77,14 @@ def main():
                 torch.cuda.synchronize()
                 fs.check()
                 t_r = timed(lambda: rs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9))
-            hbm = 4.0 * n * (3 * k + 4 + (2 * world if world > 1 and not fs.two_shot else (4 if world > 1 else 0)))
+            # bytes this implementation moves through one GPU's HBM: replicas 3k, central model and its momentum 4, plus the
+            # exchange (one-shot: G partials written and read; two-shot with owner-apply: partials once in, once out, 3/G)
+            extra = 0.0 if world == 1 else (2.0 * world if not fs.two_shot else (3.0 / world if fs.owner_apply else 4.0))
+            hbm = 4.0 * n * (3 * k + 4 + extra)
             link = 4.0 * n * ((world - 1) if not fs.two_shot else 2.0 * (world - 1) / world) if world > 1 else 0.0
             t_roof = max(hbm / (bw * 1e3), link / (nvlink * 1e3))            # microseconds
             if rank == 0:
-                print(json.dumps({"op": "sma_sync", "n": n, "replicas": k, "gpus": world, "two_shot": fs.two_shot,
+                print(json.dumps({"op": "sma_sync", "n": n, "replicas": k, "gpus": world, "two_shot": fs.two_shot, "owner_apply": bool(fs.owner_apply and world > 1),
                                   "fused_us": round(t_f, 2), "reference_us": round(t_r, 2), "speedup": round(t_r / t_f, 2),
                                   "roofline_us": round(t_roof, 2), "fraction_of_roofline": round(t_roof / t_f, 3),
                                   "hbm_bytes": hbm, "nvlink_bytes_per_gpu": link, "peaks": how}), flush=True)
