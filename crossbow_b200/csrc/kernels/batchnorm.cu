@@ -118,7 +118,31 @@ __global__ void __launch_bounds__(NT) bn_fwd_kernel(BnArgs a) {
       sc[e] = a.gamma[c] * invstd;
       sh[e] = a.beta[c] - mean * sc[e];
     }
-    for (int r = r_begin + rsub; r < r_end; r += t.rows_per_iter) {
+    constexpr int RU = 4;                                // rows per step: all loads first, then the stores
+    const long long step = (long long)t.rows_per_iter * a.C;
+    int r = r_begin + rsub;
+    for (; r + (RU - 1) * t.rows_per_iter < r_end; r += RU * t.rows_per_iter) {
+      const long long off = (long long)r * a.C + cg * VEC;
+      float v[RU][VEC], rr[RU][VEC];
+#pragma unroll
+      for (int u = 0; u < RU; ++u) ld<VEC>(a.x + off + u * step, v[u]);
+      if (a.res) {
+#pragma unroll
+        for (int u = 0; u < RU; ++u) ld<VEC>(a.res + off + u * step, rr[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float o = fmaf(v[u][e], sc[e], sh[e]);
+          if (a.res) o += rr[u][e];
+          if (a.relu) o = fmaxf(o, 0.f);
+          v[u][e] = o;
+        }
+        st<VEC>(a.y + off + u * step, v[u]);
+      }
+    }
+    for (; r < r_end; r += t.rows_per_iter) {
       long long off = (long long)r * a.C + cg * VEC;
       float v[VEC]; ld<VEC>(a.x + off, v);
       float rr[VEC];
@@ -158,7 +182,28 @@ __global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
     if (active) {
 #pragma unroll
       for (int e = 0; e < VEC; ++e) { mean[e] = a.save_mean[cg * VEC + e]; istd[e] = a.save_invstd[cg * VEC + e]; }
-      for (int r = r_begin + rsub; r < r_end; r += t.rows_per_iter) {
+      // four rows per step: twelve 16-byte loads in flight per thread before the first use
+      constexpr int RU = 4;
+      const long long step = (long long)t.rows_per_iter * a.C;
+      int r = r_begin + rsub;
+      for (; r + (RU - 1) * t.rows_per_iter < r_end; r += RU * t.rows_per_iter) {
+        const long long off = (long long)r * a.C + cg * VEC;
+        float g[RU][VEC], xv[RU][VEC], yv[RU][VEC];
+#pragma unroll
+        for (int u = 0; u < RU; ++u) { ld<VEC>(a.dy + off + u * step, g[u]); ld<VEC>(a.x + off + u * step, xv[u]); }
+        if (a.relu) {
+#pragma unroll
+          for (int u = 0; u < RU; ++u) ld<VEC>(a.y + off + u * step, yv[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < RU; ++u)
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            float dz = (a.relu && !(yv[u][e] > 0.f)) ? 0.f : g[u][e];
+            s1[e] += dz; s2[e] += dz * (xv[u][e] - mean[e]) * istd[e];
+          }
+      }
+      for (; r < r_end; r += t.rows_per_iter) {
         long long off = (long long)r * a.C + cg * VEC;
         float g[VEC], xv[VEC], yv[VEC];
         ld<VEC>(a.dy + off, g); ld<VEC>(a.x + off, xv);
