@@ -83,11 +83,12 @@ class ExecutionContext:
                                     replicas=sys.number_of_gpu_models, wpc=wpc, rank=self.rank, world=self.world,
                                     device_index=local, use_graphs=sys.use_cuda_graphs, seed=sys.random_seed,
                                     use_tc=sys.use_tensor_cores, fused_sync=sys.fused_sync,
-                                    sync_timeout_s=sys.sync_timeout)
+                                    sync_timeout_s=sys.sync_timeout, splits=mc.splits)
         else:
             from .engine import CpuEngine
             self.engine = CpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,
-                                    replicas=sys.number_of_cpu_models, wpc=wpc, devices=1, seed=sys.random_seed)
+                                    replicas=sys.number_of_cpu_models, wpc=wpc, devices=1, seed=sys.random_seed,
+                                    splits=mc.splits)
         self.clock = WorkClock(wpc)
         self.monitor = PerformanceMonitor(batch, ds.batch_bytes() if ds is not None else 0, sys.monitor_interval / 1000.0)
         if sys.autotune_models:

@@ -643,3 +643,46 @@ XB_API int xb_conv3x3_slab(const float* In, const float* Wb, const float* bias, 
     default: return launch_slab<256>(In, Wb, bias, Out, stats, g, flags, status, st);
   }
 }
+
+// ---- data gradient of a 3x3 / stride 2 / pad 1 convolution ---------------------------------------------------------------
+// dX[h] = sum_r dY_up[h + 1 - r] w[r] with dY_up[2p] = dY[p] and zeros in between: exactly the stride-1 data gradient over the
+// zero-inserted output gradient.  A small kernel writes dY_up (input resolution, K channels) into caller-provided scratch and
+// the slab kernel above does the rest on the tensor core.
+namespace {
+__global__ void upsample2_zero_kernel(const float* __restrict__ dY, float* __restrict__ up, int N, int P, int Q, int H, int W, int K4) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)N * H * W * K4;
+  if (idx >= total) return;
+  const int k4 = (int)(idx % K4); long long t = idx / K4;
+  const int w = (int)(t % W); t /= W;
+  const int h = (int)(t % H); const int n = (int)(t / H);
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!(h & 1) && !(w & 1) && (h >> 1) < P && (w >> 1) < Q)
+    v = reinterpret_cast<const float4*>(dY)[(((long long)n * P + (h >> 1)) * Q + (w >> 1)) * K4 + k4];
+  reinterpret_cast<float4*>(up)[idx] = v;
+}
+inline XbConvGeom stride1_of(const XbConvGeom* g) {
+  XbConvGeom s = *g;
+  s.sh = 1; s.sw = 1; s.P = g->H; s.Q = g->W;
+  return s;
+}
+}  // namespace
+
+// bytes of scratch if this layer's data gradient can run this way, else 0
+XB_API long long xb_conv3x3_s2_dgrad_scratch(const XbConvGeom* g) {
+  if (g->R != 3 || g->S != 3 || g->sh != 2 || g->sw != 2 || g->ph != 1 || g->pw != 1) return 0;
+  if ((g->H & 1) || (g->W & 1) || g->P != g->H / 2 || g->Q != g->W / 2 || (g->K & 3)) return 0;
+  XbConvGeom s = stride1_of(g);
+  if (!xb_conv3x3_slab_supported(&s, 1)) return 0;
+  return (long long)g->N * g->H * g->W * g->K * 4;
+}
+XB_API int xb_conv3x3_s2_dgrad(const float* dY, const float* Wt, float* dX, const XbConvGeom* cg, int accumulate, float* scratch, int* status,
+                               cudaStream_t st) {
+  if (!scratch || !xb_conv3x3_s2_dgrad_scratch(cg)) return -XB_BAD_ARG;
+  const long long total = (long long)cg->N * cg->H * cg->W * (cg->K / 4);
+  upsample2_zero_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(dY, scratch, cg->N, cg->P, cg->Q, cg->H, cg->W, cg->K / 4);
+  int e = (int)cudaGetLastError();
+  if (e) return e;
+  XbConvGeom s = stride1_of(cg);
+  return xb_conv3x3_slab(scratch, Wt, nullptr, dX, nullptr, &s, 1, accumulate ? F_ACCUM : 0, status, st);
+}

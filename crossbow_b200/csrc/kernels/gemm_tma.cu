@@ -464,7 +464,7 @@ XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, floa
     if (make_map(&ta, In, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
   }
   int BN = Nout <= 32 ? 32 : Nout <= 64 ? 64 : Nout <= 128 ? 128 : 256;
-  while (BN > 64 && (long long)tiles_m * ((Nout + BN - 1) / BN) < 120) BN >>= 1;
+  while (BN > 32 && (long long)tiles_m * ((Nout + BN - 1) / BN) < 120) BN >>= 1;
   {
     const cuuint64_t dims[2] = {(cuuint64_t)cg->R * cg->S * Kred, (cuuint64_t)Nout};
     const cuuint64_t strides[1] = {(cuuint64_t)cg->R * cg->S * Kred * 4};

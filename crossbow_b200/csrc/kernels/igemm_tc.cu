@@ -267,7 +267,7 @@ XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, floa
                        int* status, cudaStream_t st);
 // R x S stride-1 convolutions with at least this many reduction channels run as a TMA implicit GEMM, narrower ones on the
 // slab kernel (one staged copy of the input serves all taps, which wins while the filter bank is small).
-static int g_tma_conv_min = 64;
+static int g_tma_conv_min = 32;
 XB_API void xb_tc_set_tma_conv_min(int c) { g_tma_conv_min = c; }
 // bit 0: 3x3/stride-1 fprop + dgrad use the slab kernel (else the generic gather kernel); bit 1: the tensor-core weight
 // gradient kernel is used where it applies (else CUDA cores).  For A/B comparisons.

@@ -16,7 +16,7 @@ namespace {
 __global__ void __launch_bounds__(1024) softmax_xent_kernel(const float* __restrict__ logits, const int* __restrict__ labels,
                                                             float* __restrict__ probs, float* __restrict__ dlogits,
                                                             float* __restrict__ result /* [0]=loss [1]=accuracy */,
-                                                            int rows, int classes, int ignore_label, int mode) {
+                                                            int rows, int classes, int ignore_label, int mode, int part, int parts) {
   __shared__ float s_loss[32], s_acc[32], s_valid[32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   float loss_sum = 0.f, acc_sum = 0.f, valid_sum = 0.f;
@@ -61,8 +61,10 @@ __global__ void __launch_bounds__(1024) softmax_xent_kernel(const float* __restr
   if (threadIdx.x == 0) {
     float l = 0.f, a = 0.f;
     for (int w = 0; w < nwarps; ++w) { l += s_loss[w]; a += s_acc[w]; }
-    result[0] = l / denom;
-    result[1] = a / (float)rows;
+    // part p of `parts` sub-batches of one task: the slot ends up holding the mean over the parts
+    const float wgt = 1.f / (float)parts;
+    result[0] = (part ? result[0] : 0.f) + wgt * l / denom;
+    result[1] = (part ? result[1] : 0.f) + wgt * a / (float)rows;
   }
   if (dlogits) {
     __syncthreads();
@@ -179,9 +181,9 @@ XB_API int xb_matfact(const float* triples, int stride, const int* ratings, cons
 }
 
 XB_API int xb_softmax_xent(const float* logits, const int* labels, float* probs, float* dlogits, float* result, int rows, int classes,
-                           int ignore_label, int mode, cudaStream_t st) {
+                           int ignore_label, int mode, int part, int parts, cudaStream_t st) {
   int threads = rows * 32; if (threads > 1024) threads = 1024; if (threads < 32) threads = 32;
-  softmax_xent_kernel<<<1, threads, 0, st>>>(logits, labels, probs, dlogits, result, rows, classes, ignore_label, mode);
+  softmax_xent_kernel<<<1, threads, 0, st>>>(logits, labels, probs, dlogits, result, rows, classes, ignore_label, mode, part, parts > 0 ? parts : 1);
   return (int)cudaGetLastError();
 }
 XB_API int xb_classify(const float* x, float* out, int rows, int classes, cudaStream_t st) {

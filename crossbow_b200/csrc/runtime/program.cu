@@ -20,6 +20,7 @@ XB_API int xb_conv_fprop_tc(const float*, const float*, const float*, float*, fl
 XB_API int xb_conv_dgrad_tc(const float*, const float*, float*, const XbConvGeom*, int, int*, cudaStream_t);
 XB_API int xb_conv_wgrad_tc(const float*, const float*, float*, const XbConvGeom*, int*, cudaStream_t);
 XB_API int xb_conv_fprop_im2col(const float*, const float*, const float*, float*, float*, const XbConvGeom*, int, float*, int*, cudaStream_t);
+XB_API int xb_conv3x3_s2_dgrad(const float*, const float*, float*, const XbConvGeom*, int, float*, int*, cudaStream_t);
 XB_API int xb_conv_wgrad_im2col(const float*, const float*, float*, const XbConvGeom*, float*, int*, cudaStream_t);
 XB_API int xb_tc_supported(const XbConvGeom*, int which);
 XB_API int xb_transpose_weights(const float*, float*, const XbTransposeDesc*, int, int, cudaStream_t);
@@ -39,7 +40,7 @@ XB_API int xb_lrn_forward(const float*, float*, float*, long long, int, int, flo
 XB_API int xb_lrn_backward(const float*, const float*, const float*, const float*, float*, long long, int, int, float, float, int, cudaStream_t);
 XB_API int xb_transform(const float*, float*, const float*, int, int, int, int, int, int, int, int, float, int, unsigned, const XbTaskParams*, cudaStream_t);
 XB_API int xb_colsum(const float*, float*, int, int, cudaStream_t);
-XB_API int xb_softmax_xent(const float*, const int*, float*, float*, float*, int, int, int, int, cudaStream_t);
+XB_API int xb_softmax_xent(const float*, const int*, float*, float*, float*, int, int, int, int, int, int, cudaStream_t);
 XB_API int xb_classify(const float*, float*, int, int, cudaStream_t);
 XB_API int xb_grad_sumsq(const float*, float*, long long, cudaStream_t);
 XB_API int xb_matfact(const float*, int, const int*, const float*, const float*, float*, float*, float*, int, int, float, int, int, cudaStream_t);
@@ -96,6 +97,8 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
     }
     case OP_CONV_DGRAD: {
       XbConvGeom g = geom_of(o);
+      if (pr->use_tc && (o.flags & 0x100) && o.p[3])       // stride-2 3x3: zero-inserted gradient + stride-1 slab kernel
+        return xb_conv3x3_s2_dgrad((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, (float*)o.p[3], pr->tc_status, st);
       if (pr->use_tc && (o.flags & 0x100) && xb_tc_supported(&g, 1))
         return xb_conv_dgrad_tc((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, pr->tc_status, st);
       return xb_conv_dgrad_simt((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, st);
@@ -134,7 +137,7 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
       return xb_lrn_backward((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (const float*)o.p[3], (float*)o.p[4], o.la[0], o.ia[0],
                              o.ia[1], o.fa[0], o.fa[1], o.ia[2], st);
     case OP_SOFTMAX_XENT:
-      return xb_softmax_xent((const float*)o.p[0], (const int*)o.p[1], (float*)o.p[2], (float*)o.p[3], (float*)o.p[4], o.ia[0], o.ia[1], o.ia[2], o.ia[3], st);
+      return xb_softmax_xent((const float*)o.p[0], (const int*)o.p[1], (float*)o.p[2], (float*)o.p[3], (float*)o.p[4], o.ia[0], o.ia[1], o.ia[2], o.ia[3], o.ia[4], o.ia[5], st);
     case OP_CLASSIFY: return xb_classify((const float*)o.p[0], (float*)o.p[1], o.ia[0], o.ia[1], st);
     case OP_TRANSPOSE_W: return xb_transpose_weights((const float*)o.p[0], (float*)o.p[1], (const XbTransposeDesc*)o.p[2], o.ia[0], o.ia[1], st);
     case OP_MATFACT:

@@ -70,7 +70,7 @@ class Learner:
         result_dev = lib.xb_learner_result_dev(self.handle)
         self.low_train = Lowering(e.train_graph, e.model, e.batch, e.input_chw, e.device, self.rep.w, self.rep, e.shared,
                                   self.params_dev, params_host, result_dev, update_model=e.update_model, training=True,
-                                  use_tc=e.use_tc, clip=e.solver.clip_gradient_threshold >= 0, lr_mult=e.lr_mult)
+                                  use_tc=e.use_tc, clip=e.solver.clip_gradient_threshold >= 0, lr_mult=e.lr_mult, splits=e.splits)
         ops = self.low_train.op_array()
         self.prog_train = lib.xb_program_create(ops, len(ops), int(e.use_tc), e.tc_status.data_ptr())
         self.prog_test = None
@@ -124,7 +124,8 @@ class GpuEngine:
     def __init__(self, train_graph: SubGraph, test_graph: Optional[SubGraph], model: Model, init_canonical: np.ndarray,
                  batch: int, input_chw, solver: SolverConf, update_model: UpdateModel, replicas: int = 1, wpc: int = 1,
                  rank: int = 0, world: int = 1, device_index: int = 0, use_tc: bool = True, use_graphs: bool = True,
-                 seed: int = 0, fused_sync: bool = True, two_shot: Optional[bool] = None, sync_timeout_s: float = 5.0):
+                 seed: int = 0, fused_sync: bool = True, two_shot: Optional[bool] = None, sync_timeout_s: float = 5.0,
+                 splits: int = 1):
         from .ops import lib as L
         from .parallel.sync import FusedSynchroniser, ReferenceSynchroniser
         if not torch.cuda.is_available():
@@ -134,6 +135,7 @@ class GpuEngine:
         self.device = torch.device("cuda", device_index)
         self.train_graph, self.test_graph, self.model = train_graph, test_graph, model
         self.batch, self.input_chw, self.solver, self.update_model = batch, tuple(input_chw), solver, update_model
+        self.splits = max(1, int(splits))
         self.rank, self.world, self.wpc, self.seed = rank, world, wpc, seed
         self.use_tc, self.use_graphs = use_tc, use_graphs
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -342,8 +344,9 @@ class CpuEngine:
     """Same protocol on the CPU oracle, with k replicas x G virtual devices in one process."""
 
     def __init__(self, train_graph, test_graph, model: Model, init_canonical, batch, input_chw, solver: SolverConf,
-                 update_model: UpdateModel, replicas=1, wpc=1, devices=1, seed=0):
+                 update_model: UpdateModel, replicas=1, wpc=1, devices=1, seed=0, splits=1):
         self.model, self.solver, self.update_model, self.wpc, self.seed = model, solver, update_model, wpc, seed
+        self.splits = max(1, int(splits))
         w = torch.from_numpy(np.asarray(init_canonical, dtype=np.float32))
         self.devs = [DeviceState(w) for _ in range(devices)]
         for d in self.devs:
@@ -364,9 +367,14 @@ class CpuEngine:
         dev, rep = self._slot(learner)
         x, y = torch.as_tensor(examples, dtype=torch.float32), torch.as_tensor(labels)
         if phase == Phase.TRAIN:
-            rep.g.zero_()
-            r = self.train_exec.run(rep.w, x, y, Phase.TRAIN, task, dev.op_state, rep.g)
-            local_update(rep, dev, self.solver, self.update_model, task, self.lr_mult)
+            # `--splits`: the graph (optimiser included) runs once per sub-batch; the task reports the mean loss / accuracy
+            sub = x.shape[0] // self.splits
+            parts = []
+            for s in range(self.splits):
+                rep.g.zero_()
+                parts.append(self.train_exec.run(rep.w, x[s * sub:(s + 1) * sub], y[s * sub:(s + 1) * sub], Phase.TRAIN, task, dev.op_state, rep.g))
+                local_update(rep, dev, self.solver, self.update_model, task, self.lr_mult)
+            r = {k_: (None if parts[0][k_] is None else float(sum(p_[k_] for p_ in parts)) / self.splits) for k_ in ("loss", "accuracy")}
         else:
             r = self.test_exec.run(dev.z, x, y, Phase.CHECK, task, dev.op_state)
         self.results[learner] = (r["loss"] if r["loss"] is not None else 0.0, r["accuracy"] if r["accuracy"] is not None else 0.0)

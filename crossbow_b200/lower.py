@@ -124,7 +124,13 @@ class Lowering:
                  replica: Optional[ReplicaBuffers], shared: DeviceShared, params_dev: torch.Tensor, params_host_ptr: int,
                  result_dev_ptr: int,
                  update_model: UpdateModel = UpdateModel.SMA, training=True, use_tc=True, clip=False,
-                 lr_mult: Optional[torch.Tensor] = None, seed_stream_base=0):
+                 lr_mult: Optional[torch.Tensor] = None, seed_stream_base=0, splits: int = 1):
+        if splits < 1 or batch % splits:
+            raise ValueError("error: the batch size must be a multiple of the number of splits")
+        # `--splits` (taskhandler.c:65-114): one task runs the whole graph `splits` times over consecutive sub-batches of
+        # the staged batch.  The program is lowered for ONE sub-batch and its operator list repeated with shifted inputs.
+        self.splits, full_batch = splits, batch
+        batch = batch // splits
         self.g, self.model, self.batch, self.device = graph, model, batch, device
         self.weights = weights              # flat vector the forward pass reads (replica weights, or z for tests)
         self.replica, self.shared = replica, shared
@@ -136,8 +142,8 @@ class Lowering:
         self.keep = []                      # python objects that must outlive the program (descriptor tables ...)
         c, h, w = input_chw
         self.input_chw = (c, h, w)
-        self.examples = self.arena.alloc(batch * c * h * w)                 # NCHW staging buffer (H2D target)
-        self.labels = self.arena.alloc(batch, dtype=torch.int32)
+        self.examples = self.arena.alloc(full_batch * c * h * w)            # NCHW staging buffer (H2D target), whole batch
+        self.labels = self.arena.alloc(full_batch, dtype=torch.int32)
         self.tensors: Dict[int, T] = {}     # id(node) -> output tensor
         bn_channels = sum(n.op.output_shape.dims[1] for n in graph.order if n.op.kernel.kind == "batchnorm")
         self.zero_region = self.arena.alloc(4 * bn_channels + 64, zero=True)   # per-task accumulators, cleared by one memset
@@ -210,6 +216,30 @@ class Lowering:
             self._optimiser()
         # one memset clears all per-task accumulators (BN sums, BN backward sums)
         self.ops[zero_slot] = _op(L.OP_MEMSET, la=[4 * self.zero_used], p=[self.zero_region])
+        if self.splits > 1:
+            self._repeat_for_splits()
+
+    def _repeat_for_splits(self):
+        """Operator list of one sub-batch -> `splits` copies reading consecutive windows of the staged batch.  The loss and
+        accuracy slot receives the mean over the sub-batches."""
+        c, h, w = self.input_chw
+        ex0, lab0 = self.examples.data_ptr(), self.labels.data_ptr()
+        ex_step, lab_step = 4 * self.batch * c * h * w, 4 * self.batch
+        head, body = self.ops[:1], self.ops[1:]          # (the task parameters are uploaded once)
+        out = list(head)
+        for s in range(self.splits):
+            for o in body:
+                q = L.XbOp()
+                C.memmove(C.byref(q), C.byref(o), C.sizeof(L.XbOp))
+                for i in range(len(q.p)):
+                    if q.p[i] == ex0:
+                        q.p[i] = ex0 + s * ex_step
+                    elif q.p[i] == lab0:
+                        q.p[i] = lab0 + s * lab_step
+                if q.kind == L.OP_SOFTMAX_XENT:
+                    q.ia[4], q.ia[5] = s, self.splits
+                out.append(q)
+        self.ops = out
 
     def scratch_zeroed(self, numel) -> torch.Tensor:
         if self.zero_used + numel > self.zero_region.numel():
@@ -493,7 +523,11 @@ class Lowering:
                     gx, acc = self.gout(x)
                     K, R, S, Cc = geom[4], geom[5], geom[6], geom[3]
                     self.transposes.append((wv.doffset, K, R * S, Cc))
-                    self.emit(_op(L.OP_CONV_DGRAD, tc | acc, ia=geom, p=[dy, rep.wt.data_ptr() + 4 * wv.doffset, gx]))
+                    up = None
+                    if tc:
+                        need = L.load().xb_conv3x3_s2_dgrad_scratch(self._geom_struct(geom))
+                        up = self.arena.alloc(need // 4) if need > 0 else None      # zero-inserted output gradient
+                    self.emit(_op(L.OP_CONV_DGRAD, tc | acc, ia=geom, p=[dy, rep.wt.data_ptr() + 4 * wv.doffset, gx, up]))
                 continue
             if kind == "batchnorm" or (kind == "elementwise" and info["carrier"] is not None):
                 bn = n if kind == "batchnorm" else info["carrier"]

@@ -89,6 +89,8 @@ def load() -> C.CDLL:
     _sig(lib, "xb_tc_set_tma_conv_min", None, I)
     _sig(lib, "xb_conv_tma_supported", I, G, I)
     _sig(lib, "xb_conv_im2col_wanted", C.c_longlong, G, I)
+    _sig(lib, "xb_conv3x3_s2_dgrad_scratch", C.c_longlong, G)
+    _sig(lib, "xb_conv3x3_s2_dgrad", I, P, P, P, G, I, P, P, P)
     _sig(lib, "xb_conv_im2col_scratch", C.c_longlong, G, I)
     _sig(lib, "xb_conv_fprop_im2col", I, P, P, P, P, P, G, I, P, P, P)
     _sig(lib, "xb_conv_wgrad_im2col", I, P, P, P, G, P, P, P)
@@ -110,7 +112,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_transform", I, P, P, P, I, I, I, I, I, I, I, I, F, I, c_uint, P, P)
     _sig(lib, "xb_nhwc_to_nchw", I, P, P, I, I, I, I, P)
     _sig(lib, "xb_colsum", I, P, P, I, I, P)
-    _sig(lib, "xb_softmax_xent", I, P, P, P, P, P, I, I, I, I, P)
+    _sig(lib, "xb_softmax_xent", I, P, P, P, P, P, I, I, I, I, I, I, P)
     _sig(lib, "xb_classify", I, P, P, I, I, P)
     _sig(lib, "xb_grad_sumsq", I, P, P, L, P)
     _sig(lib, "xb_fused_optimiser", I, P, P, P, P, P, P, P, P, L, I, P)

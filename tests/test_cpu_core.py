@@ -320,3 +320,23 @@ def test_all_models_build_and_infer_shapes():
     assert 460000 < m.elements < 470000
     spec, m, _ = build_model("resnet50", 2, size=224)
     assert 25.5e6 < m.elements < 25.7e6
+
+
+def test_batch_splits_equal_consecutive_sub_batch_tasks():
+    """A task of 8 examples with 2 splits = two updates on its halves (taskhandler.c:65-114 slides the input window)."""
+    from crossbow_b200.engine import CpuEngine
+    import copy
+    spec, m, solver = build_model("mlp", 8)
+    init = m.initial_values(3)
+    xs, ys = make_batches(spec, 8, 2, seed=4)
+    a = CpuEngine(spec.train, spec.test, m, init, 8, spec.input_shape, copy.deepcopy(solver), UpdateModel.DEFAULT, splits=2)
+    b = CpuEngine(spec.train, spec.test, m, init, 4, spec.input_shape, copy.deepcopy(solver), UpdateModel.DEFAULT)
+    for t in range(2):
+        a.submit(0, xs[t], ys[t], t)
+        la, _ = a.wait(0)
+        lb = []
+        for s in range(2):
+            b.submit(0, xs[t][4 * s:4 * s + 4], ys[t][4 * s:4 * s + 4], t)
+            lb.append(b.wait(0)[0])
+        assert la == pytest.approx(sum(lb) / 2, rel=1e-6)
+    assert np.allclose(a.replica_model(0), b.replica_model(0), rtol=1e-6, atol=1e-7)

@@ -165,6 +165,33 @@ def test_patch_matrix_gemm_path(env, shape):
         assert float((dw - dw_ref).abs().max()) / float(dw_ref.abs().max()) < 4e-3
 
 
+@pytest.mark.parametrize("shape", [(4, 32, 32, 16, 32, 3, 3, 2, 1), (3, 16, 16, 32, 64, 3, 3, 2, 1), (2, 8, 12, 8, 24, 3, 3, 2, 1)])
+def test_stride2_dgrad_by_zero_insertion(env, shape):
+    L, lib = env
+    N, H, W, Cc, K, R, S, st, pad = shape
+    g, P, Q = _geom(L, *shape)
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    w = torch.randn(K, R, S, Cc, device=dev, generator=gen) * 0.1
+    dy = torch.randn(N, P, Q, K, device=dev, generator=gen)
+    xr = torch.zeros(N, Cc, H, W, device=dev, dtype=torch.float64, requires_grad=True)
+    F.conv2d(xr, w.double().permute(0, 3, 1, 2), None, stride=2, padding=1).backward(dy.double().permute(0, 3, 1, 2))
+    dx_ref = xr.grad.permute(0, 2, 3, 1).float()
+    need = lib.xb_conv3x3_s2_dgrad_scratch(C.byref(g))
+    assert need == N * H * W * K * 4
+    scratch = torch.empty(need // 4, device=dev)
+    wt = w.permute(3, 1, 2, 0).contiguous()
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    for accum in (0, 1):
+        dx = torch.full((N, H, W, Cc), 0.25, device=dev)
+        L.check(lib.xb_conv3x3_s2_dgrad(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), C.byref(g), accum, scratch.data_ptr(), status.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream), "dgrad")
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        ref = dx_ref + (0.25 if accum else 0.0)
+        assert float((dx - ref).abs().max()) / float(dx_ref.abs().max()) < 4e-3
+
+
 def test_first_layer_three_channels(env):
     """C=3 takes the scalar CUDA-core path in every direction."""
     L, lib = env

@@ -80,6 +80,12 @@ def test_lenet_batchnorm_eamsgd():
     run_both("lenet-batchnorm", 8, 2, 4, update_model=UpdateModel.EAMSGD)
 
 
+def test_batch_splits():
+    """--splits 2: every task runs the graph (optimiser included) over two consecutive sub-batches."""
+    run_both("convnet", 8, 2, 4, splits=2)
+    run_both("lenet-batchnorm", 16, 1, 3, splits=2)
+
+
 def test_bottleneck_resnet():
     run_both("tiny-bottleneck", 16, 1, 2, tol=5e-3)
 
