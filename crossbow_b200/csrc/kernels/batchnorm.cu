@@ -325,6 +325,18 @@ XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const
   return (int)cudaGetLastError();
 }
 
+// Second half only: `dsums` already holds the sums (produced by the epilogue of the kernel that completed dy).
+XB_API int xb_bn_backward_apply(const float* dy, const float* x, const float* y, const float* save_mean, const float* save_invstd,
+                                const float* gamma, const float* dsums, float* dx, float* dres, float* dgamma, float* dbeta,
+                                int M, int C, int relu, int accum_dx, int accum_dres, cudaStream_t st) {
+  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, const_cast<float*>(dsums), dx, dres, dgamma, dbeta, M, C, relu, accum_dx, accum_dres, 0};
+  bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
+  int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
+  if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a);
+  else    bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
 // ---- variant that allocates nothing: the scratch sums live in a fixed device array (see bn_backward_static.h) ----------
 #include "bn_backward_static.h"
 #include <stdio.h>

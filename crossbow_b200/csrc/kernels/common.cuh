@@ -14,6 +14,15 @@ struct XbConvGeom {
   int sh, sw, ph, pw;  // stride / padding
 };
 
+// Batch-norm backward sums produced by the epilogue of the kernel that writes the gradient dy of a normalisation layer
+// (the data gradient of the next convolution): sums[c] += dz, sums[C + c] += dz * (x - mean[c]) * istd[c] with
+// dz = dy masked by the layer's fused ReLU (y > 0).  x = the layer's input, y = its output; all of dy's shape.
+struct XbBnFuse {
+  const float* x; const float* y; const float* mean; const float* istd;
+  float* sums;
+  int relu;
+};
+
 // Values that change from task to task.  They live in device memory (one block per learner) and are refreshed
 // by a host-to-device copy in front of the task's kernels, so a captured CUDA graph never bakes them in.
 struct XbTaskParams {

@@ -21,7 +21,7 @@ using namespace tc;
 namespace {
 
 constexpr int BM = 128, NTHREADS = 128;
-constexpr int F_RELU = 1, F_ACCUM = 2, F_STATS = 4;
+constexpr int F_RELU = 1, F_ACCUM = 2, F_STATS = 4, F_BNBWD = 8;   // F_BNBWD: `stats` receives batch-norm backward sums (XbBnFuse)
 
 struct SlabProblem {
   int N, H, W, C, K;      // C = reduction channels, K = output channels (already swapped for dgrad)
@@ -32,7 +32,7 @@ struct SlabProblem {
 template <int BN>
 __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __restrict__ X, const float* __restrict__ Wb,
                                                                 const float* __restrict__ bias, float* __restrict__ Out,
-                                                                float* __restrict__ stats, SlabProblem g, int flags, int* status) {
+                                                                float* __restrict__ stats, SlabProblem g, int flags, int* status, XbBnFuse bn) {
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __r
   }
   if (!mbar_wait(&bar_done, 0)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
   tc_fence_after();
-  if (flags & F_STATS) { for (int i = tid; i < 2 * BN; i += NTHREADS) s_red[i] = 0.f; }
+  if (flags & (F_STATS | F_BNBWD)) { for (int i = tid; i < 2 * BN; i += NTHREADS) s_red[i] = 0.f; }
   __syncthreads();
   const bool abort_all = s_abort != 0;
 
@@ -152,10 +152,24 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __r
           for (int j = 0; j < 16; ++j) if (n0 + c0 + j < g.K) orow[j] = v[j];
         }
       }
-      if (flags & F_STATS) {
+      if (flags & (F_STATS | F_BNBWD)) {
         float sq[16];
+        if (flags & F_BNBWD) {                             // v = final dy of a normalisation layer: its backward sums
+          const long long off = opix * g.K + n0 + c0;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sq[j] = v[j] * v[j];
+          for (int j = 0; j < 16; ++j) {
+            const int n = n0 + c0 + j;
+            float dz = 0.f, t = 0.f;
+            if (ok && n < g.K) {
+              dz = (bn.relu && !(bn.y[off + j] > 0.f)) ? 0.f : v[j];
+              t = dz * (bn.x[off + j] - bn.mean[n]) * bn.istd[n];
+            }
+            v[j] = dz; sq[j] = t;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sq[j] = v[j] * v[j];
+        }
         int col;
         float sx = warp_colsum16(v, lane, col), sqq = warp_colsum16(sq, lane, col);
         if (lane < 16) { atomicAdd(&s_red[c0 + col], sx); atomicAdd(&s_red[BN + c0 + col], sqq); }
@@ -164,7 +178,7 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __r
   }
   tc_fence_before();
   __syncthreads();
-  if ((flags & F_STATS) && !abort_all) {
+  if ((flags & (F_STATS | F_BNBWD)) && !abort_all) {
     for (int i = tid; i < BN; i += NTHREADS) {
       int n = n0 + i;
       if (n < g.K) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.K + n], s_red[BN + i]); }
@@ -351,7 +365,7 @@ constexpr size_t kSmemLimit = 200 * 1024;
 template <int BN, int CC>
 __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_pipe_kernel(const float* __restrict__ X, const float* __restrict__ Wb,
                                                                      const float* __restrict__ bias, float* __restrict__ Out,
-                                                                     float* __restrict__ stats, SlabProblem g, int flags, int* status) {
+                                                                     float* __restrict__ stats, SlabProblem g, int flags, int* status, XbBnFuse bn) {
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   constexpr int CQ = CC / 4;
@@ -459,7 +473,7 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_pipe_kernel(const float
   }
   if (alive && !mbar_wait(&bar_done, 0)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
   tc_fence_after();
-  if (flags & F_STATS) { for (int i = tid; i < 2 * BN; i += NTHREADS) s_red[i] = 0.f; }
+  if (flags & (F_STATS | F_BNBWD)) { for (int i = tid; i < 2 * BN; i += NTHREADS) s_red[i] = 0.f; }
   __syncthreads();
   const bool abort_all = s_abort != 0;
 
@@ -495,10 +509,24 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_pipe_kernel(const float
           for (int j = 0; j < 16; ++j) if (n0 + c0 + j < g.K) orow[j] = v[j];
         }
       }
-      if (flags & F_STATS) {
+      if (flags & (F_STATS | F_BNBWD)) {
         float sq[16];
+        if (flags & F_BNBWD) {                             // v = final dy of a normalisation layer: its backward sums
+          const long long off = opix * g.K + n0 + c0;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sq[j] = v[j] * v[j];
+          for (int j = 0; j < 16; ++j) {
+            const int n = n0 + c0 + j;
+            float dz = 0.f, t = 0.f;
+            if (ok && n < g.K) {
+              dz = (bn.relu && !(bn.y[off + j] > 0.f)) ? 0.f : v[j];
+              t = dz * (bn.x[off + j] - bn.mean[n]) * bn.istd[n];
+            }
+            v[j] = dz; sq[j] = t;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sq[j] = v[j] * v[j];
+        }
         int col;
         float sx = warp_colsum16(v, lane, col), sqq = warp_colsum16(sq, lane, col);
         if (lane < 16) { atomicAdd(&s_red[c0 + col], sx); atomicAdd(&s_red[BN + c0 + col], sqq); }
@@ -507,7 +535,7 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_pipe_kernel(const float
   }
   tc_fence_before();
   __syncthreads();
-  if ((flags & F_STATS) && !abort_all) {
+  if ((flags & (F_STATS | F_BNBWD)) && !abort_all) {
     for (int i = tid; i < BN; i += NTHREADS) {
       int n = n0 + i;
       if (n < g.K) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.K + n], s_red[BN + i]); }
@@ -524,10 +552,10 @@ inline size_t pipe_smem_bytes(int W, int CC, int BN) {
 
 template <int BN>
 int launch_slab(const float* X, const float* Wb, const float* bias, float* Out, float* stats, const SlabProblem& g, int flags, int* status,
-                cudaStream_t st) {
+                cudaStream_t st, const XbBnFuse& bn) {
   size_t smem = slab_smem_bytes(g.W, g.C, BN);
   dim3 grid((unsigned)((g.positions + BM - 1) / BM), (unsigned)((g.K + BN - 1) / BN));
-  conv3x3_slab_kernel<BN><<<grid, NTHREADS, smem, st>>>(X, Wb, bias, Out, stats, g, flags, status);
+  conv3x3_slab_kernel<BN><<<grid, NTHREADS, smem, st>>>(X, Wb, bias, Out, stats, g, flags, status, bn);
   return (int)cudaGetLastError();
 }
 inline int pick_bn(int K) { return K <= 16 ? 16 : K <= 32 ? 32 : K <= 64 ? 64 : K <= 128 ? 128 : 256; }
@@ -552,10 +580,10 @@ inline int choose_wgrad_nk(int W, int K) {
 
 template <int BN>
 int launch_pipe(const float* X, const float* Wb, const float* bias, float* Out, float* stats, const SlabProblem& g, int flags, int* status,
-                cudaStream_t st) {
+                cudaStream_t st, const XbBnFuse& bn) {
   size_t smem = pipe_smem_bytes(g.W, 16, BN);
   dim3 grid((unsigned)((g.positions + BM - 1) / BM), (unsigned)((g.K + BN - 1) / BN));
-  conv3x3_slab_pipe_kernel<BN, 16><<<grid, NTHREADS, smem, st>>>(X, Wb, bias, Out, stats, g, flags, status);
+  conv3x3_slab_pipe_kernel<BN, 16><<<grid, NTHREADS, smem, st>>>(X, Wb, bias, Out, stats, g, flags, status, bn);
   return (int)cudaGetLastError();
 }
 inline int choose_pipe_bn(long long positions, int W, int Kout) {
@@ -621,7 +649,9 @@ XB_API int xb_conv3x3_wgrad_slab(const float* dY, const float* X, float* dW, con
 
 // which: 0 fprop (In = X, Wb = weights (K,3,3,C)), 1 dgrad (In = dY, Wb = transposed copy (C,3,3,K), output dX)
 XB_API int xb_conv3x3_slab(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which,
-                           int flags, int* status, cudaStream_t st) {
+                           int flags, int* status, cudaStream_t st, const XbBnFuse* bnf) {
+  XbBnFuse bn{};
+  if (bnf && bnf->sums) { bn = *bnf; stats = bnf->sums; flags = (flags & ~F_STATS) | F_BNBWD; }
   SlabProblem g;
   g.N = cg->N; g.H = cg->H; g.W = cg->W;
   g.C = which == 0 ? cg->C : cg->K; g.K = which == 0 ? cg->K : cg->C;
@@ -629,18 +659,18 @@ XB_API int xb_conv3x3_slab(const float* In, const float* Wb, const float* bias, 
   g.positions = (long long)cg->N * (cg->H + 1) * (cg->W + 2);
   if (slab_smem_bytes(g.W, g.C, choose_bn(g.positions, g.W, g.C, g.K)) > kSmemLimit) {
     switch (choose_pipe_bn(g.positions, g.W, g.K)) {
-      case 16: return launch_pipe<16>(In, Wb, bias, Out, stats, g, flags, status, st);
-      case 32: return launch_pipe<32>(In, Wb, bias, Out, stats, g, flags, status, st);
-      case 64: return launch_pipe<64>(In, Wb, bias, Out, stats, g, flags, status, st);
-      default: return launch_pipe<128>(In, Wb, bias, Out, stats, g, flags, status, st);
+      case 16: return launch_pipe<16>(In, Wb, bias, Out, stats, g, flags, status, st, bn);
+      case 32: return launch_pipe<32>(In, Wb, bias, Out, stats, g, flags, status, st, bn);
+      case 64: return launch_pipe<64>(In, Wb, bias, Out, stats, g, flags, status, st, bn);
+      default: return launch_pipe<128>(In, Wb, bias, Out, stats, g, flags, status, st, bn);
     }
   }
   switch (choose_bn(g.positions, g.W, g.C, g.K)) {
-    case 16: return launch_slab<16>(In, Wb, bias, Out, stats, g, flags, status, st);
-    case 32: return launch_slab<32>(In, Wb, bias, Out, stats, g, flags, status, st);
-    case 64: return launch_slab<64>(In, Wb, bias, Out, stats, g, flags, status, st);
-    case 128: return launch_slab<128>(In, Wb, bias, Out, stats, g, flags, status, st);
-    default: return launch_slab<256>(In, Wb, bias, Out, stats, g, flags, status, st);
+    case 16: return launch_slab<16>(In, Wb, bias, Out, stats, g, flags, status, st, bn);
+    case 32: return launch_slab<32>(In, Wb, bias, Out, stats, g, flags, status, st, bn);
+    case 64: return launch_slab<64>(In, Wb, bias, Out, stats, g, flags, status, st, bn);
+    case 128: return launch_slab<128>(In, Wb, bias, Out, stats, g, flags, status, st, bn);
+    default: return launch_slab<256>(In, Wb, bias, Out, stats, g, flags, status, st, bn);
   }
 }
 
@@ -677,12 +707,12 @@ XB_API long long xb_conv3x3_s2_dgrad_scratch(const XbConvGeom* g) {
   return (long long)g->N * g->H * g->W * g->K * 4;
 }
 XB_API int xb_conv3x3_s2_dgrad(const float* dY, const float* Wt, float* dX, const XbConvGeom* cg, int accumulate, float* scratch, int* status,
-                               cudaStream_t st) {
+                               cudaStream_t st, const XbBnFuse* bnf) {
   if (!scratch || !xb_conv3x3_s2_dgrad_scratch(cg)) return -XB_BAD_ARG;
   const long long total = (long long)cg->N * cg->H * cg->W * (cg->K / 4);
   upsample2_zero_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(dY, scratch, cg->N, cg->P, cg->Q, cg->H, cg->W, cg->K / 4);
   int e = (int)cudaGetLastError();
   if (e) return e;
   XbConvGeom s = stride1_of(cg);
-  return xb_conv3x3_slab(scratch, Wt, nullptr, dX, nullptr, &s, 1, accumulate ? F_ACCUM : 0, status, st);
+  return xb_conv3x3_slab(scratch, Wt, nullptr, dX, nullptr, &s, 1, accumulate ? F_ACCUM : 0, status, st, bnf);
 }

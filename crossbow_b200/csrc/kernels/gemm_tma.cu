@@ -29,7 +29,7 @@ namespace {
 
 constexpr int GT = 192;
 constexpr int MAX_STAGES = 8;
-constexpr int G_RELU = 1, G_ACCUM = 2, G_STATS = 4;
+constexpr int G_RELU = 1, G_ACCUM = 2, G_STATS = 4, G_BNBWD = 8;   // G_BNBWD: `stats` receives batch-norm backward sums (XbBnFuse)
 constexpr uint32_t A_BYTES = 128 * 128;                 // 128 rows (or 4 planes x 32 positions) x 128 B
 
 struct GemmArgs {
@@ -54,7 +54,7 @@ struct GemmArgs {
 template <int BN, int MODE>
 __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                                       float* __restrict__ D, const float* __restrict__ bias, float* __restrict__ stats,
-                                                      GemmArgs g, int flags, int* status) {
+                                                      GemmArgs g, int flags, int* status, XbBnFuse bn) {
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   constexpr uint32_t B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
   constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (MODE == 1 ? (3u << 15) : 0u) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -212,11 +212,23 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
                 float4* o = reinterpret_cast<float4*>(D + off + n);
                 if (flags & G_ACCUM) { const float4 old = *o; x[0] += old.x; x[1] += old.y; x[2] += old.z; x[3] += old.w; }
                 *o = make_float4(x[0], x[1], x[2], x[3]);
+                if (flags & G_BNBWD) {                     // x = final dy of a normalisation layer: its backward sums
+                  const float4 bx = *reinterpret_cast<const float4*>(bn.x + off + n);
+                  float4 by = make_float4(1.f, 1.f, 1.f, 1.f);
+                  if (bn.relu) by = *reinterpret_cast<const float4*>(bn.y + off + n);
+                  const float xv[4] = {bx.x, bx.y, bx.z, bx.w}, yv[4] = {by.x, by.y, by.z, by.w};
 #pragma unroll
-                for (int k = 0; k < 4; ++k) { sx[k] += x[k]; sq[k] += x[k] * x[k]; }
+                  for (int k = 0; k < 4; ++k) {
+                    const float dz = yv[k] > 0.f ? x[k] : 0.f;
+                    sx[k] += dz; sq[k] += dz * (xv[k] - bn.mean[n + k]) * bn.istd[n + k];
+                  }
+                } else {
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) { sx[k] += x[k]; sq[k] += x[k] * x[k]; }
+                }
               }
             }
-            if (flags & G_STATS) {
+            if (flags & (G_STATS | G_BNBWD)) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
                 sx[k] += __shfl_xor_sync(0xffffffffu, sx[k], 8);  sq[k] += __shfl_xor_sync(0xffffffffu, sq[k], 8);
@@ -248,7 +260,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
   }
   tc_fence_before();
   __syncthreads();
-  if (MODE != 1 && (flags & G_STATS) && !s_abort) {
+  if (MODE != 1 && (flags & (G_STATS | G_BNBWD)) && !s_abort) {
     for (int i = tid; i < BN; i += GT) {
       const int n = n0 + i;
       if (n < g.N) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.N + n], s_red[BN + i]); }
@@ -294,19 +306,19 @@ inline int pick_stages(int kblocks, int BN, long long ctas) {
 
 template <int BN, int MODE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags, int* status,
-           cudaStream_t st) {
+           cudaStream_t st, const XbBnFuse& bn) {
   const size_t smem = (size_t)g.stages * stage_bytes(BN);
-  gemm_tma_kernel<BN, MODE><<<grid, GT, smem, st>>>(a, b, D, bias, stats, g, flags, status);
+  gemm_tma_kernel<BN, MODE><<<grid, GT, smem, st>>>(a, b, D, bias, stats, g, flags, status, bn);
   return (int)cudaGetLastError();
 }
 template <int MODE>
 int launch_bn(int BN, const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags,
-              int* status, cudaStream_t st) {
+              int* status, cudaStream_t st, const XbBnFuse& bn = XbBnFuse{}) {
   switch (BN) {
-    case 32: return launch<32, MODE>(a, b, D, bias, stats, g, grid, flags, status, st);
-    case 64: return launch<64, MODE>(a, b, D, bias, stats, g, grid, flags, status, st);
-    case 128: return launch<128, MODE>(a, b, D, bias, stats, g, grid, flags, status, st);
-    default: return launch<256, MODE>(a, b, D, bias, stats, g, grid, flags, status, st);
+    case 32: return launch<32, MODE>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
+    case 64: return launch<64, MODE>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
+    case 128: return launch<128, MODE>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
+    default: return launch<256, MODE>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
   }
 }
 template <int BN, int MODE>
@@ -343,7 +355,9 @@ XB_API int xb_conv1x1_tma_supported(const XbConvGeom* g, int which) {
 
 // which 0: In = X (N,H,W,C), Wb = weights (K,C), Out = Y (N,P,Q,K).  which 1: In = dY (N,P,Q,K), Wb = transposed weights (C,K), Out = dX.
 XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which, int flags,
-                          int* status, cudaStream_t st) {
+                          int* status, cudaStream_t st, const XbBnFuse* bnf) {
+  XbBnFuse bn{};
+  if (bnf && bnf->sums) { bn = *bnf; stats = bnf->sums; flags = (flags & ~G_STATS) | G_BNBWD; }
   if (!aligned16p(In) || !aligned16p(Wb) || !aligned16p(Out) || !xb_conv1x1_tma_supported(cg, which)) return -XB_BAD_ARG;
   const int Kred = which == 0 ? cg->C : cg->K, Nout = which == 0 ? cg->K : cg->C;
   GemmArgs g{};
@@ -387,7 +401,7 @@ XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, f
   g.N = Nout; g.kblocks = (Kred + 31) / 32; g.ldd = Nout;
   dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
   g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y);
-  return launch_bn<0>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st);
+  return launch_bn<0>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st, bn);
 }
 
 // dW (K,C) += dY^T X over all positions; dW must hold the value to accumulate onto (normally zero).
@@ -440,7 +454,9 @@ XB_API int xb_conv_tma_supported(const XbConvGeom* g, int which) {
 
 // which 0: In = X, Wb = weights (K,R,S,C), Out = Y.  which 1: In = dY, Wb = transposed weights (C,R,S,K), Out = dX.
 XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which, int flags,
-                       int* status, cudaStream_t st) {
+                       int* status, cudaStream_t st, const XbBnFuse* bnf) {
+  XbBnFuse bn{};
+  if (bnf && bnf->sums) { bn = *bnf; stats = bnf->sums; flags = (flags & ~G_STATS) | G_BNBWD; }
   if (!aligned16p(In) || !aligned16p(Wb) || !aligned16p(Out) || !xb_conv_tma_supported(cg, which)) return -XB_BAD_ARG;
   const int Kred = which == 0 ? cg->C : cg->K, Nout = which == 0 ? cg->K : cg->C;
   GemmArgs g{};
@@ -473,5 +489,5 @@ XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, floa
   }
   dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
   g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y);
-  return launch_bn<2>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st);
+  return launch_bn<2>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st, bn);
 }

@@ -250,7 +250,7 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 XB_API int xb_conv3x3_slab_supported(const XbConvGeom* g, int which);
 XB_API int xb_conv3x3_slab_init();
 XB_API int xb_conv3x3_slab(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which,
-                           int flags, int* status, cudaStream_t st);
+                           int flags, int* status, cudaStream_t st, const XbBnFuse* bnf);
 XB_API int xb_conv3x3_wgrad_slab(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st);
 static int g_use_slab = 3;
 static int g_use_tma = 1;
@@ -258,13 +258,13 @@ XB_API int xb_gemm_tma_init();
 XB_API int xb_conv_wgrad_simt(const float*, const float*, float*, const XbConvGeom*, cudaStream_t);
 XB_API int xb_conv1x1_tma_supported(const XbConvGeom* g, int which);
 XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which, int flags,
-                          int* status, cudaStream_t st);
+                          int* status, cudaStream_t st, const XbBnFuse* bnf);
 XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st);
 // 1: 1x1 convolutions run on the TMA-fed GEMM kernel where it applies (else the gather kernel).  For A/B comparisons.
 XB_API void xb_tc_set_tma(int on) { g_use_tma = on; }
 XB_API int xb_conv_tma_supported(const XbConvGeom* g, int which);
 XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which, int flags,
-                       int* status, cudaStream_t st);
+                       int* status, cudaStream_t st, const XbBnFuse* bnf);
 // R x S stride-1 convolutions with at least this many reduction channels run as a TMA implicit GEMM, narrower ones on the
 // slab kernel (one staged copy of the input serves all taps, which wins while the filter bank is small).
 static int g_tma_conv_min = 32;
@@ -319,12 +319,12 @@ XB_API int xb_conv_fprop_tc(const float* X, const float* W, const float* bias, f
                             int* status, cudaStream_t st) {
   if (!aligned16(X) || !aligned16(W) || !aligned16(Y) || cg->C % 4) return -XB_BAD_ARG;
   if (g_use_tma && (cg->R > 1 || cg->S > 1) && cg->C >= g_tma_conv_min && xb_conv_tma_supported(cg, 0)) {
-    const int r = xb_conv_tma(X, W, bias, Y, stats, cg, 0, flags, status, st);
+    const int r = xb_conv_tma(X, W, bias, Y, stats, cg, 0, flags, status, st, nullptr);
     if (r != -XB_BAD_ARG) return r;
   }
-  if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 0)) return xb_conv3x3_slab(X, W, bias, Y, stats, cg, 0, flags, status, st);
+  if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 0)) return xb_conv3x3_slab(X, W, bias, Y, stats, cg, 0, flags, status, st, nullptr);
   if (g_use_tma && xb_conv1x1_tma_supported(cg, 0)) {
-    const int r = xb_conv1x1_tma(X, W, bias, Y, stats, cg, 0, flags, status, st);
+    const int r = xb_conv1x1_tma(X, W, bias, Y, stats, cg, 0, flags, status, st, nullptr);
     if (r != -XB_BAD_ARG) return r;                      // (tensor map refused: fall back to the gather kernel)
   }
   TcProblem g;
@@ -332,15 +332,26 @@ XB_API int xb_conv_fprop_tc(const float* X, const float* W, const float* bias, f
   g.R = cg->R; g.S = cg->S; g.sh = cg->sh; g.sw = cg->sw; g.ph = cg->ph; g.pw = cg->pw; g.transposed = 0; g.KG = cg->R * cg->S * cg->C;
   return dispatch_tc(X, W, bias, Y, stats, g, flags, status, st);
 }
-XB_API int xb_conv_dgrad_tc(const float* dY, const float* Wt, float* dX, const XbConvGeom* cg, int accumulate, int* status, cudaStream_t st) {
+// 1 if the kernel that xb_conv_dgrad_tc picks for this layer can also produce the batch-norm backward sums of the layer
+// that owns dX (XbBnFuse).  It must visit every element of dX, which rules out the strided 1x1 form.
+XB_API int xb_conv_dgrad_fuses_bn(const XbConvGeom* cg) {
+  if (cg->K % 4 || cg->C % 4) return 0;
+  if (g_use_tma && (cg->R > 1 || cg->S > 1) && cg->K >= g_tma_conv_min && xb_conv_tma_supported(cg, 1)) return 1;
+  if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 1)) return 1;
+  if (g_use_tma && cg->sh == 1 && xb_conv1x1_tma_supported(cg, 1)) return 1;
+  return 0;
+}
+XB_API int xb_conv_dgrad_tc(const float* dY, const float* Wt, float* dX, const XbConvGeom* cg, int accumulate, int* status, cudaStream_t st,
+                            const XbBnFuse* bnf) {
+  if (bnf && bnf->sums && !xb_conv_dgrad_fuses_bn(cg)) return -XB_BAD_ARG;
   if (!aligned16(dY) || !aligned16(Wt) || !aligned16(dX) || cg->K % 4) return -XB_BAD_ARG;
   if (g_use_tma && (cg->R > 1 || cg->S > 1) && cg->K >= g_tma_conv_min && xb_conv_tma_supported(cg, 1)) {
-    const int r = xb_conv_tma(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);
+    const int r = xb_conv_tma(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st, bnf);
     if (r != -XB_BAD_ARG) return r;
   }
-  if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 1)) return xb_conv3x3_slab(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);
+  if ((g_use_slab & 1) && xb_conv3x3_slab_supported(cg, 1)) return xb_conv3x3_slab(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st, bnf);
   if (g_use_tma && xb_conv1x1_tma_supported(cg, 1)) {
-    const int r = xb_conv1x1_tma(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st);
+    const int r = xb_conv1x1_tma(dY, Wt, nullptr, dX, nullptr, cg, 1, accumulate ? F_ACCUM : 0, status, st, bnf);
     if (r != -XB_BAD_ARG) return r;
   }
   TcProblem g;

@@ -9,7 +9,7 @@
 
 XB_API int xb_conv1x1_tma_supported(const XbConvGeom* g, int which);
 XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, float* Out, float* stats, const XbConvGeom* cg, int which, int flags,
-                          int* status, cudaStream_t st);
+                          int* status, cudaStream_t st, const XbBnFuse* bnf);
 XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, const XbConvGeom* cg, int* status, cudaStream_t st);
 
 namespace {
@@ -105,7 +105,7 @@ XB_API int xb_conv_fprop_im2col(const float* X, const float* W, const float* bia
   pad_rows_kernel<<<(g->K * Kp + 255) / 256, 256, 0, st>>>(W, Wp, g->K, KR, Kp);
   if ((e = (int)cudaGetLastError())) return e;
   XbConvGeom f = as_gemm(g, Kp, M);
-  return xb_conv1x1_tma(A, Wp, bias, Y, stats, &f, 0, flags, status, st);
+  return xb_conv1x1_tma(A, Wp, bias, Y, stats, &f, 0, flags, status, st, nullptr);
 }
 
 // dW (K,R,S,C) += dY^T A; dW must hold the value to accumulate onto (normally zero).

@@ -104,42 +104,62 @@ __global__ void __launch_bounds__(256) fused_optimiser_kernel(OptArgs a) {
   const XbTaskParams tp = *a.tp;
   float gscale = 1.f;
   if (tp.clip >= 0.f && a.norm2) { float l2 = sqrtf(*a.norm2); if (l2 > tp.clip) gscale = tp.clip / l2; }
-  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < a.n4; i += (long long)gridDim.x * 256) {
-    float4 w = reinterpret_cast<float4*>(a.w)[i];
-    float4 g = reinterpret_cast<float4*>(a.g)[i];
-    reinterpret_cast<float4*>(a.g)[i] = make_float4(0, 0, 0, 0);     // the next task's wgrad accumulates from zero
-    float wv[4] = {w.x, w.y, w.z, w.w}, gv[4] = {g.x, g.y, g.z, g.w}, lm[4] = {1.f, 1.f, 1.f, 1.f};
-    if (a.lr_mult) { float4 m = reinterpret_cast<const float4*>(a.lr_mult)[i]; lm[0] = m.x; lm[1] = m.y; lm[2] = m.z; lm[3] = m.w; }
-    float step[4];
+  // Four float4 lanes per thread and step, all loads ahead of the first store: the compiler may not hoist loads above
+  // stores to pointers that could alias, and a one-lane loop leaves most of the memory pipeline idle.
+  constexpr int U = 4;
+  const long long stride = (long long)gridDim.x * 256;
+  for (long long i0 = blockIdx.x * 256LL + threadIdx.x; i0 < a.n4; i0 += U * stride) {
+    float4 w[U], g[U], l[U], m[U];
+    bool ok[U];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float gg = gv[e] * gscale;
-      if (tp.weight_decay > 0.f) gg += tp.weight_decay * (tp.l1 ? (wv[e] > 0.f ? 1.f : (wv[e] < 0.f ? -1.f : 0.f)) : wv[e]);
-      step[e] = -tp.lr * lm[e] * gg;
-    }
-    if (a.update_mode == 2) {
-      float* acc = a.z_or_gacc + i * 4;
+    for (int u = 0; u < U; ++u) ok[u] = i0 + u * stride < a.n4;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) atomicAdd(acc + e, step[e]);       // several replicas of the device accumulate concurrently
-      continue;
+    for (int u = 0; u < U; ++u) if (ok[u]) { w[u] = reinterpret_cast<float4*>(a.w)[i0 + u * stride]; g[u] = reinterpret_cast<float4*>(a.g)[i0 + u * stride]; }
+    if (a.update_mode != 2 && tp.momentum > 0.f) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (ok[u]) l[u] = reinterpret_cast<float4*>(a.last)[i0 + u * stride];
     }
-    reinterpret_cast<float4*>(a.prev)[i] = w;                         // snapshot BEFORE the step
-    if (tp.momentum > 0.f) {
-      float4 l = reinterpret_cast<float4*>(a.last)[i];
-      float lv[4] = {l.x, l.y, l.z, l.w};
+    if (a.lr_mult) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (ok[u]) m[u] = reinterpret_cast<const float4*>(a.lr_mult)[i0 + u * stride];
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!ok[u]) continue;
+      const long long i = i0 + u * stride;
+      reinterpret_cast<float4*>(a.g)[i] = make_float4(0, 0, 0, 0);     // the next task's wgrad accumulates from zero
+      float wv[4] = {w[u].x, w[u].y, w[u].z, w[u].w}, gv[4] = {g[u].x, g[u].y, g[u].z, g[u].w}, lm[4] = {1.f, 1.f, 1.f, 1.f};
+      if (a.lr_mult) { lm[0] = m[u].x; lm[1] = m[u].y; lm[2] = m[u].z; lm[3] = m[u].w; }
+      float step[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float s = step[e] + tp.momentum * lv[e];
-        lv[e] = s;
-        step[e] = tp.nesterov ? (step[e] + tp.momentum * s) : s;
+        float gg = gv[e] * gscale;
+        if (tp.weight_decay > 0.f) gg += tp.weight_decay * (tp.l1 ? (wv[e] > 0.f ? 1.f : (wv[e] < 0.f ? -1.f : 0.f)) : wv[e]);
+        step[e] = -tp.lr * lm[e] * gg;
       }
-      reinterpret_cast<float4*>(a.last)[i] = make_float4(lv[0], lv[1], lv[2], lv[3]);
-    }
-    reinterpret_cast<float4*>(a.w)[i] = make_float4(wv[0] + step[0], wv[1] + step[1], wv[2] + step[2], wv[3] + step[3]);
-    if (a.update_mode == 1) {
-      float* z = a.z_or_gacc + i * 4;
+      if (a.update_mode == 2) {
+        float* acc = a.z_or_gacc + i * 4;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) atomicAdd(z + e, step[e]);
+        for (int e = 0; e < 4; ++e) atomicAdd(acc + e, step[e]);       // several replicas of the device accumulate concurrently
+        continue;
+      }
+      reinterpret_cast<float4*>(a.prev)[i] = w[u];                      // snapshot BEFORE the step
+      if (tp.momentum > 0.f) {
+        float lv[4] = {l[u].x, l[u].y, l[u].z, l[u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float s = step[e] + tp.momentum * lv[e];
+          lv[e] = s;
+          step[e] = tp.nesterov ? (step[e] + tp.momentum * s) : s;
+        }
+        reinterpret_cast<float4*>(a.last)[i] = make_float4(lv[0], lv[1], lv[2], lv[3]);
+      }
+      reinterpret_cast<float4*>(a.w)[i] = make_float4(wv[0] + step[0], wv[1] + step[1], wv[2] + step[2], wv[3] + step[3]);
+      if (a.update_mode == 1) {
+        float* z = a.z_or_gacc + i * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) atomicAdd(z + e, step[e]);
+      }
     }
   }
 }

@@ -17,16 +17,18 @@ XB_API int xb_conv_fprop_simt(const float*, const float*, const float*, float*, 
 XB_API int xb_conv_dgrad_simt(const float*, const float*, float*, const XbConvGeom*, int, cudaStream_t);
 XB_API int xb_conv_wgrad_simt(const float*, const float*, float*, const XbConvGeom*, cudaStream_t);
 XB_API int xb_conv_fprop_tc(const float*, const float*, const float*, float*, float*, const XbConvGeom*, int, int*, cudaStream_t);
-XB_API int xb_conv_dgrad_tc(const float*, const float*, float*, const XbConvGeom*, int, int*, cudaStream_t);
+XB_API int xb_conv_dgrad_tc(const float*, const float*, float*, const XbConvGeom*, int, int*, cudaStream_t, const XbBnFuse*);
 XB_API int xb_conv_wgrad_tc(const float*, const float*, float*, const XbConvGeom*, int*, cudaStream_t);
 XB_API int xb_conv_fprop_im2col(const float*, const float*, const float*, float*, float*, const XbConvGeom*, int, float*, int*, cudaStream_t);
-XB_API int xb_conv3x3_s2_dgrad(const float*, const float*, float*, const XbConvGeom*, int, float*, int*, cudaStream_t);
+XB_API int xb_conv3x3_s2_dgrad(const float*, const float*, float*, const XbConvGeom*, int, float*, int*, cudaStream_t, const XbBnFuse*);
 XB_API int xb_conv_wgrad_im2col(const float*, const float*, float*, const XbConvGeom*, float*, int*, cudaStream_t);
 XB_API int xb_tc_supported(const XbConvGeom*, int which);
 XB_API int xb_transpose_weights(const float*, float*, const XbTransposeDesc*, int, int, cudaStream_t);
 XB_API int xb_bn_stats(const float*, float*, int, int, cudaStream_t);
 XB_API int xb_bn_forward(const float*, const float*, float*, const float*, const float*, const float*, float*, float*, float*, float*,
                          const XbTaskParams*, int, int, float, int, int, int, float, cudaStream_t);
+XB_API int xb_bn_backward_apply(const float*, const float*, const float*, const float*, const float*, const float*, const float*, float*, float*, float*,
+                                float*, int, int, int, int, int, cudaStream_t);
 XB_API int xb_bn_backward(const float*, const float*, const float*, const float*, const float*, const float*, float*, float*, float*, float*,
                           float*, int, int, int, int, int, cudaStream_t);
 XB_API int xb_act_forward(const float*, float*, long long, int, float, float, cudaStream_t);
@@ -97,10 +99,14 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
     }
     case OP_CONV_DGRAD: {
       XbConvGeom g = geom_of(o);
+      // p[4..8]: batch-norm backward sums of the layer that owns dX, produced by this kernel's epilogue (flags 0x8; 0x10 = ReLU mask)
+      XbBnFuse bn{(const float*)o.p[4], (const float*)o.p[5], (const float*)o.p[6], (const float*)o.p[7], (float*)o.p[8], (o.flags & 0x10) ? 1 : 0};
+      const XbBnFuse* bnp = (o.flags & 0x8) ? &bn : nullptr;
       if (pr->use_tc && (o.flags & 0x100) && o.p[3])       // stride-2 3x3: zero-inserted gradient + stride-1 slab kernel
-        return xb_conv3x3_s2_dgrad((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, (float*)o.p[3], pr->tc_status, st);
+        return xb_conv3x3_s2_dgrad((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, (float*)o.p[3], pr->tc_status, st, bnp);
       if (pr->use_tc && (o.flags & 0x100) && xb_tc_supported(&g, 1))
-        return xb_conv_dgrad_tc((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, pr->tc_status, st);
+        return xb_conv_dgrad_tc((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, pr->tc_status, st, bnp);
+      if (bnp) return -XB_BAD_ARG;
       return xb_conv_dgrad_simt((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, o.flags & 1, st);
     }
     case OP_CONV_WGRAD: {
@@ -118,6 +124,10 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
                            (const float*)o.p[5], (float*)o.p[6], (float*)o.p[7], (float*)o.p[8], (float*)o.p[9], (const XbTaskParams*)o.p[10],
                            o.ia[0], o.ia[1], o.fa[0], o.ia[2], o.ia[3], o.ia[4], o.fa[1], st);
     case OP_BN_BWD:
+      if (o.ia[5])     // the sums were produced by the operator that completed dy
+        return xb_bn_backward_apply((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (const float*)o.p[3], (const float*)o.p[4],
+                                    (const float*)o.p[5], (const float*)o.p[6], (float*)o.p[7], (float*)o.p[8], (float*)o.p[9], (float*)o.p[10],
+                                    o.ia[0], o.ia[1], o.ia[2], o.ia[3], o.ia[4], st);
       return xb_bn_backward((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (const float*)o.p[3], (const float*)o.p[4],
                             (const float*)o.p[5], (float*)o.p[6], (float*)o.p[7], (float*)o.p[8], (float*)o.p[9], (float*)o.p[10],
                             o.ia[0], o.ia[1], o.ia[2], o.ia[3], o.ia[4], st);

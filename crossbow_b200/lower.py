@@ -30,6 +30,13 @@ from .types import (ActivationMode, BatchNormEstimatedMeanAndVarianceType, Eleme
                     Phase, PoolMethod, UpdateModel)
 
 
+# Let the data-gradient kernel that completes dy of a normalisation layer also produce that layer's backward sums (and skip
+# the layer's own reduction kernel).  Measured on B200: ResNet-32 -6 %, ResNet-50 -4 % images/s - the extra loads and
+# column sums lengthen the epilogue of CTAs that hold tensor memory and a full operand pipeline, which costs more than the
+# lean stand-alone reduction it saves.  Off; the kernels keep the capability (tests/test_gpu_conv_kernels.py).
+FUSE_BN_BACKWARD_SUMS = False
+
+
 class Arena:
     """Bump allocator over one CUDA allocation (activations, gradients of activations, scratch of one learner)."""
 
@@ -48,7 +55,7 @@ class Arena:
 
 class T:
     """A device tensor in the program: storage + logical channels-last shape."""
-    __slots__ = ("buf", "n", "h", "w", "c", "grad", "grad_written", "needs_grad", "name")
+    __slots__ = ("buf", "n", "h", "w", "c", "grad", "grad_written", "needs_grad", "name", "bn_info")
 
     def __init__(self, buf, n, h, w, c, name=""):
         self.buf, self.n, self.h, self.w, self.c = buf, n, h, w, c
@@ -56,6 +63,7 @@ class T:
         self.grad_written = False
         self.needs_grad = False
         self.name = name
+        self.bn_info = None          # node_info of the normalisation group that produced this tensor, if any
 
     @property
     def rows(self):
@@ -138,6 +146,7 @@ class Lowering:
         self.update_model, self.training, self.use_tc, self.clip = update_model, training, use_tc, clip
         self.lr_mult = lr_mult
         self.arena = Arena(device)
+        self._count_pass, self._gout_count, self._gout_total = False, {}, {}
         self.ops: List[L.XbOp] = []
         self.keep = []                      # python objects that must outlive the program (descriptor tables ...)
         c, h, w = input_chw
@@ -172,7 +181,12 @@ class Lowering:
         g = self.grad_of(t)
         acc = t.grad_written
         t.grad_written = True
+        self._gout_count[id(t)] = self._gout_count.get(id(t), 0) + 1
         return g, int(acc)
+
+    def _last_contribution(self, t: T) -> bool:
+        """True (in the emitting pass) when the gout() just issued for t was the final one: t's gradient is complete after it."""
+        return (not self._count_pass) and self._gout_total.get(id(t), -1) == self._gout_count.get(id(t), 0)
 
     def emit(self, op):
         self.ops.append(op)
@@ -211,6 +225,20 @@ class Lowering:
         for n in fwd:
             self._forward(n, x_in)
         if has_grad:
+            # Pass 1 only counts the contributions every activation gradient receives, so that pass 2 knows which operator
+            # completes a gradient (that operator's epilogue can then produce the batch-norm backward sums of its owner).
+            mark_ops, mark_zero = len(self.ops), self.zero_used
+            written = {id(t): t.grad_written for t in self.tensors.values() if t is not None}
+            self._count_pass, self._gout_count, self._gout_total = True, {}, {}
+            self._backward(fwd, differentiated)
+            del self.ops[mark_ops:]
+            self.zero_used = mark_zero
+            for t in self.tensors.values():
+                if t is not None:
+                    t.grad_written = written.get(id(t), False)
+            if self.x_in is not None:
+                self.x_in.grad_written = False
+            self._count_pass, self._gout_total, self._gout_count = False, self._gout_count, {}
             self._backward(fwd, differentiated)
             self._finish_transposes(transpose_slot)
             self._optimiser()
@@ -469,6 +497,7 @@ class Lowering:
         sm = self.arena.alloc(x.c)
         si = self.arena.alloc(x.c)
         info.update(save_mean=sm, save_invstd=si, x=x, res=res, relu_fused=relu, out=out)
+        out.bn_info = info
         cma = int(conf.estimated_mean_and_variance_type == BatchNormEstimatedMeanAndVarianceType.CMA)
         self.emit(_op(L.OP_BN_FWD, ia=[x.rows, x.c, int(relu), int(self.training), cma], fa=[k.epsilon(), 1.0 - float(conf.fraction)],
                       p=[x.buf, res.buf if res is not None else None, out.buf, info.get("stats_buf"), self.wptr(k.variables[0]),
@@ -525,21 +554,33 @@ class Lowering:
                     self.transposes.append((wv.doffset, K, R * S, Cc))
                     up = None
                     if tc:
-                        need = L.load().xb_conv3x3_s2_dgrad_scratch(self._geom_struct(geom))
-                        up = self.arena.alloc(need // 4) if need > 0 else None      # zero-inserted output gradient
-                    self.emit(_op(L.OP_CONV_DGRAD, tc | acc, ia=geom, p=[dy, rep.wt.data_ptr() + 4 * wv.doffset, gx, up]))
+                        if "s2up" not in info:
+                            need = L.load().xb_conv3x3_s2_dgrad_scratch(self._geom_struct(geom))
+                            info["s2up"] = self.arena.alloc(need // 4) if need > 0 else None   # zero-inserted output gradient
+                        up = info["s2up"]
+                    bnp, bflags = [None] * 5, 0
+                    bi = x.bn_info
+                    if (FUSE_BN_BACKWARD_SUMS and tc and bi is not None and self._last_contribution(x)
+                            and (up is not None or L.load().xb_conv_dgrad_fuses_bn(self._geom_struct(geom)))):
+                        # this operator completes the gradient of a normalisation layer's output: its epilogue also produces
+                        # that layer's backward sums, and the layer's own reduction kernel is skipped
+                        bi["dsums_fused"] = self.scratch_zeroed(2 * x.c)
+                        bnp = [bi["x"].buf, x.buf, bi["save_mean"], bi["save_invstd"], bi["dsums_fused"]]
+                        bflags = 0x8 | (0x10 if bi["relu_fused"] else 0)
+                    self.emit(_op(L.OP_CONV_DGRAD, tc | acc | bflags, ia=geom, p=[dy, rep.wt.data_ptr() + 4 * wv.doffset, gx, up] + bnp))
                 continue
             if kind == "batchnorm" or (kind == "elementwise" and info["carrier"] is not None):
                 bn = n if kind == "batchnorm" else info["carrier"]
                 bi = self.node_info[id(bn)]
                 bk = bn.op.kernel
                 x, res, relu = bi["x"], bi["res"], bi["relu_fused"]
-                dsums = self.scratch_zeroed(2 * x.c)
+                fused = bi.pop("dsums_fused", None)        # sums already produced by the operator that completed dy
+                dsums = fused if fused is not None else self.scratch_zeroed(2 * x.c)
                 gx, accx = self.gout(x)
                 gres, accr = (None, 0)
                 if res is not None and res.needs_grad:
                     gres, accr = self.gout(res)
-                self.emit(_op(L.OP_BN_BWD, ia=[x.rows, x.c, int(relu), accx, accr],
+                self.emit(_op(L.OP_BN_BWD, ia=[x.rows, x.c, int(relu), accx, accr, int(fused is not None)],
                               p=[dy, x.buf, out.buf, bi["save_mean"], bi["save_invstd"], self.wptr(bk.variables[0]), dsums, gx, gres,
                                  self.wptr(bk.variables[0], rep.g), self.wptr(bk.variables[1], rep.g)]))
                 continue

@@ -97,7 +97,7 @@ def bench_conv(lib, timer, op, impl, shape, iters, flags=0):
         bytes_ = 4 * (x.numel() + w.numel() + y.numel())
     elif op == "conv_dgrad":
         if impl == "tc":
-            fn = lambda: lib.xb_conv_dgrad_tc(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), gp, 0, status.data_ptr(), s)
+            fn = lambda: lib.xb_conv_dgrad_tc(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), gp, 0, status.data_ptr(), s, None)
         else:
             fn = lambda: lib.xb_conv_dgrad_simt(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), gp, 0, s)
         bytes_ = 4 * (dy.numel() + w.numel() + dx.numel())

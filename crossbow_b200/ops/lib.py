@@ -44,6 +44,10 @@ class XbSyncDesc(C.Structure):
                 ("status", c_void_p), ("timeout_s", C.c_double), ("zpeer", c_void_p * MAXG)]
 
 
+class XbBnFuse(C.Structure):
+    _fields_ = [("x", c_void_p), ("y", c_void_p), ("mean", c_void_p), ("istd", c_void_p), ("sums", c_void_p), ("relu", c_int)]
+
+
 class XbSolverState(C.Structure):
     _fields_ = [("policy", c_int), ("base_lr", c_float), ("gamma", c_float), ("power", c_float), ("momentum", c_float),
                 ("weight_decay", c_float), ("clip", c_float), ("alpha", c_float), ("step_size", c_ll), ("warmup", c_ll),
@@ -80,7 +84,8 @@ def load() -> C.CDLL:
     _sig(lib, "xb_conv_dgrad_simt", I, P, P, P, G, I, P)
     _sig(lib, "xb_conv_wgrad_simt", I, P, P, P, G, P)
     _sig(lib, "xb_conv_fprop_tc", I, P, P, P, P, P, G, I, P, P)
-    _sig(lib, "xb_conv_dgrad_tc", I, P, P, P, G, I, P, P)
+    _sig(lib, "xb_conv_dgrad_tc", I, P, P, P, G, I, P, P, P)
+    _sig(lib, "xb_conv_dgrad_fuses_bn", I, G)
     _sig(lib, "xb_conv_wgrad_tc", I, P, P, P, G, P, P)
     _sig(lib, "xb_tc_supported", I, G, I)
     _sig(lib, "xb_tc_init", I)
@@ -90,7 +95,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_conv_tma_supported", I, G, I)
     _sig(lib, "xb_conv_im2col_wanted", C.c_longlong, G, I)
     _sig(lib, "xb_conv3x3_s2_dgrad_scratch", C.c_longlong, G)
-    _sig(lib, "xb_conv3x3_s2_dgrad", I, P, P, P, G, I, P, P, P)
+    _sig(lib, "xb_conv3x3_s2_dgrad", I, P, P, P, G, I, P, P, P, P)
     _sig(lib, "xb_conv_im2col_scratch", C.c_longlong, G, I)
     _sig(lib, "xb_conv_fprop_im2col", I, P, P, P, P, P, G, I, P, P, P)
     _sig(lib, "xb_conv_wgrad_im2col", I, P, P, P, G, P, P, P)

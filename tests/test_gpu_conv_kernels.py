@@ -100,7 +100,7 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
         if impl == "simt" or not lib.xb_tc_supported(C.byref(g), 1):
             L.check(lib.xb_conv_dgrad_simt(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), C.byref(g), accum, s), "dgrad")
         else:
-            L.check(lib.xb_conv_dgrad_tc(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), C.byref(g), accum, status.data_ptr(), s), "dgrad")
+            L.check(lib.xb_conv_dgrad_tc(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), C.byref(g), accum, status.data_ptr(), s, None), "dgrad")
         torch.cuda.synchronize()
         assert int(status[0]) == 0
         ref = dx_ref + (0.5 if accum else 0.0)
@@ -185,11 +185,52 @@ def test_stride2_dgrad_by_zero_insertion(env, shape):
     for accum in (0, 1):
         dx = torch.full((N, H, W, Cc), 0.25, device=dev)
         L.check(lib.xb_conv3x3_s2_dgrad(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), C.byref(g), accum, scratch.data_ptr(), status.data_ptr(),
-                                        torch.cuda.current_stream().cuda_stream), "dgrad")
+                                        torch.cuda.current_stream().cuda_stream, None), "dgrad")
         torch.cuda.synchronize()
         assert int(status[0]) == 0
         ref = dx_ref + (0.25 if accum else 0.0)
         assert float((dx - ref).abs().max()) / float(dx_ref.abs().max()) < 4e-3
+
+
+@pytest.mark.parametrize("shape", [(4, 32, 32, 16, 16, 3, 3, 1, 1), (4, 16, 16, 32, 32, 3, 3, 1, 1), (2, 14, 14, 64, 256, 1, 1, 1, 0),
+                                   (2, 28, 28, 128, 128, 3, 3, 1, 1), (3, 8, 8, 64, 64, 3, 3, 1, 1)])
+@pytest.mark.parametrize("relu,accum", [(1, 0), (0, 1)])
+def test_dgrad_epilogue_produces_bn_backward_sums(env, shape, relu, accum):
+    """The data-gradient kernel that completes dy of a normalisation layer also returns that layer's backward sums:
+    sum dz and sum dz * xhat with dz = dy masked by the layer's ReLU."""
+    L, lib = env
+    N, H, W, Cc, K, R, S, st, pad = shape
+    g, P, Q = _geom(L, *shape)
+    assert lib.xb_conv_dgrad_fuses_bn(C.byref(g))
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    w = torch.randn(K, R, S, Cc, device=dev, generator=gen) * (1.0 / (R * S * K) ** 0.5)
+    dyo = torch.randn(N, P, Q, K, device=dev, generator=gen)              # gradient w.r.t. the convolution's output
+    bn_x = torch.randn(N, H, W, Cc, device=dev, generator=gen)            # input of the normalisation layer in front of the convolution
+    bn_y = torch.randn(N, H, W, Cc, device=dev, generator=gen)            # its output (sign = ReLU mask)
+    mean = torch.randn(Cc, device=dev, generator=gen) * 0.1
+    istd = torch.rand(Cc, device=dev, generator=gen) + 0.5
+    base = torch.randn(N, H, W, Cc, device=dev, generator=gen) if accum else torch.zeros(N, H, W, Cc, device=dev)
+    xr = torch.zeros(N, Cc, H, W, device=dev, dtype=torch.float64, requires_grad=True)
+    F.conv2d(xr, w.double().permute(0, 3, 1, 2), None, stride=st, padding=pad).backward(dyo.double().permute(0, 3, 1, 2))
+    dx_ref = xr.grad.permute(0, 2, 3, 1) + base.double()
+    dz = dx_ref * (bn_y > 0) if relu else dx_ref
+    s1 = dz.reshape(-1, Cc).sum(0)
+    s2 = (dz * (bn_x.double() - mean.double()) * istd.double()).reshape(-1, Cc).sum(0)
+    sums = torch.zeros(2 * Cc, device=dev)
+    fuse = L.XbBnFuse()
+    fuse.x, fuse.y, fuse.mean, fuse.istd, fuse.sums, fuse.relu = bn_x.data_ptr(), bn_y.data_ptr(), mean.data_ptr(), istd.data_ptr(), sums.data_ptr(), relu
+    dx = base.clone()
+    wt = w.permute(3, 1, 2, 0).contiguous()
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    L.check(lib.xb_conv_dgrad_tc(dyo.data_ptr(), wt.data_ptr(), dx.data_ptr(), C.byref(g), accum, status.data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream, C.byref(fuse)), "dgrad")
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    assert float((dx.double() - dx_ref).abs().max()) / float(dx_ref.abs().max()) < 4e-3
+    scale = float(dz.abs().sum(dim=(0, 1, 2)).max())
+    assert float((sums[:Cc].double() - s1).abs().max()) / scale < 4e-3
+    assert float((sums[Cc:].double() - s2).abs().max()) / (scale * 3) < 4e-3
 
 
 def test_first_layer_three_channels(env):
