@@ -477,10 +477,10 @@ class Lowering:
             train = self.has_backward and self.replica is not None
             du = self.wptr(u, self.replica.g) if train else 0
             dv = self.wptr(v, self.replica.g) if train else 0
-            # the input batch is [N, 3] (row, column, rating) in the public layout; ratings may also come as labels
+            # examples are (row, column[, rating]) rows; the ratings are the task's labels, as in the reference (matfact.cu:26-29)
             src = self.x_in if self.x_in is not None else x
             self.emit(_op(L.OP_MATFACT, ia=[src.numel // src.n, src.n, conf.number_of_latent_variables, conf.number_of_rows, conf.number_of_columns],
-                          fa=[conf.lambda_], p=[src.buf, None, self.wptr(u), self.wptr(v), du, dv, self.result_ptr]))
+                          fa=[conf.lambda_], p=[src.buf, self.labels, self.wptr(u), self.wptr(v), du, dv, self.result_ptr]))
             self.tensors[id(n)] = None
             return
         if kind == "noop":

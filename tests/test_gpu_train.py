@@ -86,6 +86,40 @@ def test_batch_splits():
     run_both("lenet-batchnorm", 16, 1, 3, splits=2)
 
 
+def test_matrix_factorisation():
+    """(row, column, rating) triples: loss, factor gradients and the SMA step agree with the CPU definition."""
+    from helpers import build_model
+    from crossbow_b200.engine import CpuEngine, GpuEngine
+    import copy
+    batch, k = 32, 2
+    spec, m, solver = build_model("matrix-factorisation", batch)
+    init = m.initial_values(5)
+    gpu = GpuEngine(spec.train, None, m, init, batch, spec.input_shape, solver, UpdateModel.SMA, replicas=k, wpc=k, seed=5)
+    cpu = CpuEngine(spec.train, None, m, init, batch, spec.input_shape, copy.deepcopy(solver), UpdateModel.SMA, replicas=k, wpc=k, seed=5)
+    g = torch.Generator().manual_seed(8)
+    try:
+        for t in range(6):
+            x = torch.stack([torch.randint(0, 1000, (batch,), generator=g).float(), torch.randint(0, 500, (batch,), generator=g).float(),
+                             torch.rand(batch, generator=g) * 5.0], 1).reshape(batch, 3, 1, 1).contiguous()
+            y = torch.randint(0, 6, (batch,), generator=g).to(torch.int32)      # ratings travel as labels
+            l = t % k
+            gpu.submit(l, x.pin_memory(), y.pin_memory(), t, Phase.TRAIN)
+            cpu.submit(l, x, y, t, Phase.TRAIN)
+            gl, cl = gpu.wait(l)[0], cpu.wait(l)[0]
+            assert abs(gl - cl) <= 1e-4 * max(1.0, abs(cl)), f"task {t}: loss {gl} vs {cl}"
+            if (t + 1) % k == 0:
+                gpu.synchronise()
+                cpu.synchronise()
+        gpu.finish()
+        a, b = gpu.central_model(), cpu.central_model()
+        assert np.abs(a - b).max() / np.abs(b).max() < 1e-4
+        for i in range(k):
+            a, b = gpu.replica_model(i), cpu.replica_model(i)
+            assert np.abs(a - b).max() / np.abs(b).max() < 1e-4
+    finally:
+        gpu.destroy()
+
+
 def test_bottleneck_resnet():
     run_both("tiny-bottleneck", 16, 1, 2, tol=5e-3)
 
