@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Headline benchmark: small-batch SMA training throughput (images/s) of a CIFAR ResNet-32 / ImageNet ResNet-50.
 
-    python bench.py --gpus N --steps K --warmup W [--model resnet32|resnet50] [--replicas k] [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--model resnet32|resnet50] [--replicas k] [--impl reference|cudnn]
 
 One STEP = one synchronisation clock: every one of the k replicas of every GPU runs one task (forward, backward,
 local momentum-SGD update on a batch of 64 / 32 images) and then the fused SMA synchronisation runs across all
@@ -97,6 +97,10 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "cudnn":
+        # library baseline (stock PyTorch operators: cuDNN / cuBLAS / NCCL), same workload; none of this repository's kernels
+        from baseline.cudnn_arm import run
+        return run(args, CONFIGS[args.model], json.dumps)
     if args.warmup < 3:
         args.warmup = 3
 

@@ -115,8 +115,9 @@ __global__ void __launch_bounds__(NT) bn_fwd_kernel(BnArgs a) {
         mean = a.run_mean[c];
         invstd = rsqrtf(a.run_var[c] + a.eps);
       }
+      // explicit fused multiply-adds: the backward pass re-derives the ReLU mask from x with the same two expressions
       sc[e] = a.gamma[c] * invstd;
-      sh[e] = a.beta[c] - mean * sc[e];
+      sh[e] = __fmaf_rn(-mean, sc[e], a.beta[c]);
     }
     constexpr int RU = 4;                                // rows per step: all loads first, then the stores
     const long long step = (long long)t.rows_per_iter * a.C;
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(NT) bn_fwd_kernel(BnArgs a) {
       for (int u = 0; u < RU; ++u) {
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          float o = fmaf(v[u][e], sc[e], sh[e]);
+          float o = __fmaf_rn(v[u][e], sc[e], sh[e]);
           if (a.res) o += rr[u][e];
           if (a.relu) o = fmaxf(o, 0.f);
           v[u][e] = o;
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(NT) bn_fwd_kernel(BnArgs a) {
       if (a.res) ld<VEC>(a.res + off, rr);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        float o = fmaf(v[e], sc[e], sh[e]);
+        float o = __fmaf_rn(v[e], sc[e], sh[e]);
         if (a.res) o += rr[e];
         if (a.relu) o = fmaxf(o, 0.f);
         v[e] = o;
@@ -165,6 +166,7 @@ struct BnBwdArgs {
   float* dsums;                                      // [2C]: sum dz, sum dz*xhat
   float* dx; float* dres; float* dgamma; float* dbeta;
   int M, C; int relu; int accum_dx; int accum_dres; int rows_per_block;
+  const float* beta;   // relu == 2: the mask is re-derived from x (fma(x, gamma*istd, beta - mean*gamma*istd) > 0) and y is not read
 };
 
 template <int VEC>
@@ -176,12 +178,16 @@ __global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
     int cg = (t.col_passes == 1) ? (threadIdx.x % t.cv) : (pass * NT + threadIdx.x);
     int rsub = (t.col_passes == 1) ? (threadIdx.x / t.cv) : 0;
     bool active = cg < t.cv && rsub < t.rows_per_iter;
-    float s1[VEC], s2[VEC], mean[VEC], istd[VEC];
+    float s1[VEC], s2[VEC], mean[VEC], istd[VEC], msc[VEC], msh[VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) { s1[e] = 0.f; s2[e] = 0.f; mean[e] = 0.f; istd[e] = 0.f; }
+    for (int e = 0; e < VEC; ++e) { s1[e] = 0.f; s2[e] = 0.f; mean[e] = 0.f; istd[e] = 0.f; msc[e] = 0.f; msh[e] = 0.f; }
+    const bool from_y = a.relu == 1, from_x = a.relu == 2;
     if (active) {
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) { mean[e] = a.save_mean[cg * VEC + e]; istd[e] = a.save_invstd[cg * VEC + e]; }
+      for (int e = 0; e < VEC; ++e) {
+        mean[e] = a.save_mean[cg * VEC + e]; istd[e] = a.save_invstd[cg * VEC + e];
+        if (from_x) { msc[e] = a.gamma[cg * VEC + e] * istd[e]; msh[e] = __fmaf_rn(-mean[e], msc[e], a.beta[cg * VEC + e]); }
+      }
       // four rows per step: twelve 16-byte loads in flight per thread before the first use
       constexpr int RU = 4;
       const long long step = (long long)t.rows_per_iter * a.C;
@@ -191,7 +197,7 @@ __global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
         float g[RU][VEC], xv[RU][VEC], yv[RU][VEC];
 #pragma unroll
         for (int u = 0; u < RU; ++u) { ld<VEC>(a.dy + off + u * step, g[u]); ld<VEC>(a.x + off + u * step, xv[u]); }
-        if (a.relu) {
+        if (from_y) {
 #pragma unroll
           for (int u = 0; u < RU; ++u) ld<VEC>(a.y + off + u * step, yv[u]);
         }
@@ -199,7 +205,8 @@ __global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
         for (int u = 0; u < RU; ++u)
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
-            float dz = (a.relu && !(yv[u][e] > 0.f)) ? 0.f : g[u][e];
+            const bool off_ = from_y ? !(yv[u][e] > 0.f) : (from_x && !(__fmaf_rn(xv[u][e], msc[e], msh[e]) > 0.f));
+            float dz = off_ ? 0.f : g[u][e];
             s1[e] += dz; s2[e] += dz * (xv[u][e] - mean[e]) * istd[e];
           }
       }
@@ -207,10 +214,11 @@ __global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
         long long off = (long long)r * a.C + cg * VEC;
         float g[VEC], xv[VEC], yv[VEC];
         ld<VEC>(a.dy + off, g); ld<VEC>(a.x + off, xv);
-        if (a.relu) ld<VEC>(a.y + off, yv);
+        if (from_y) ld<VEC>(a.y + off, yv);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          float dz = (a.relu && !(yv[e] > 0.f)) ? 0.f : g[e];
+          const bool off_ = from_y ? !(yv[e] > 0.f) : (from_x && !(__fmaf_rn(xv[e], msc[e], msh[e]) > 0.f));
+          float dz = off_ ? 0.f : g[e];
           s1[e] += dz; s2[e] += dz * (xv[e] - mean[e]) * istd[e];
         }
       }
@@ -240,13 +248,15 @@ __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
     int cg = (t.col_passes == 1) ? (threadIdx.x % t.cv) : (pass * NT + threadIdx.x);
     int rsub = (t.col_passes == 1) ? (threadIdx.x / t.cv) : 0;
     if (cg >= t.cv || rsub >= t.rows_per_iter) continue;
-    float mean[VEC], istd[VEC], k0[VEC], k1[VEC], k2[VEC];
+    float mean[VEC], istd[VEC], k0[VEC], k1[VEC], k2[VEC], msh[VEC];
+    const bool from_y = a.relu == 1, from_x = a.relu == 2;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
       int c = cg * VEC + e;
       mean[e] = a.save_mean[c]; istd[e] = a.save_invstd[c];
       float s1 = a.dsums[c], s2 = a.dsums[a.C + c];
       float gi = a.gamma[c] * istd[e];
+      msh[e] = from_x ? __fmaf_rn(-mean[e], gi, a.beta[c]) : 0.f;       // (gi = gamma * istd is the forward pass's scale)
       k0[e] = gi; k1[e] = gi * s1 * invM; k2[e] = gi * s2 * invM;
       if (blockIdx.x == 0 && rsub == 0) { atomicAdd(&a.dgamma[c], s2); atomicAdd(&a.dbeta[c], s1); }
     }
@@ -254,11 +264,12 @@ __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
       long long off = (long long)r * a.C + cg * VEC;
       float g[VEC], xv[VEC], yv[VEC], o[VEC], old[VEC];
       ld<VEC>(a.dy + off, g); ld<VEC>(a.x + off, xv);
-      if (a.relu) ld<VEC>(a.y + off, yv);
+      if (from_y) ld<VEC>(a.y + off, yv);
       if (a.accum_dx) ld<VEC>(a.dx + off, old);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        float dz = (a.relu && !(yv[e] > 0.f)) ? 0.f : g[e];
+        const bool off_ = from_y ? !(yv[e] > 0.f) : (from_x && !(__fmaf_rn(xv[e], k0[e], msh[e]) > 0.f));
+        float dz = off_ ? 0.f : g[e];
         g[e] = dz;
         float xhat = (xv[e] - mean[e]) * istd[e];
         o[e] = k0[e] * dz - k1[e] - k2[e] * xhat;
@@ -317,8 +328,22 @@ XB_API int xb_bn_forward(const float* x, const float* res, float* y, const float
 XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const float* save_mean, const float* save_invstd,
                           const float* gamma, float* dsums, float* dx, float* dres, float* dgamma, float* dbeta,
                           int M, int C, int relu, int accum_dx, int accum_dres, cudaStream_t st) {
-  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, dsums, dx, dres, dgamma, dbeta, M, C, relu, accum_dx, accum_dres, 0};
+  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, dsums, dx, dres, dgamma, dbeta, M, C, relu ? 1 : 0, accum_dx, accum_dres, 0, nullptr};
   bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
+  int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
+  if (v4) { bn_bwd_reduce_kernel<4><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); }
+  else    { bn_bwd_reduce_kernel<1><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a); }
+  return (int)cudaGetLastError();
+}
+
+// As xb_bn_backward, for a layer whose fused ReLU has no residual input: the mask is re-derived from x, gamma, beta and the
+// saved statistics with the forward pass's own expressions (bit-identical), so the layer's output is not read at all -
+// five passes over the tensor instead of seven.
+XB_API int xb_bn_backward_remask(const float* dy, const float* x, const float* save_mean, const float* save_invstd, const float* gamma,
+                                 const float* beta, float* dsums, float* dx, float* dgamma, float* dbeta, int M, int C, int accum_dx,
+                                 cudaStream_t st) {
+  BnBwdArgs a{dy, x, nullptr, save_mean, save_invstd, gamma, dsums, dx, nullptr, dgamma, dbeta, M, C, 2, accum_dx, 0, 0, beta};
+  bool v4 = can_vec4(C, dy, x, nullptr, dx);
   int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
   if (v4) { bn_bwd_reduce_kernel<4><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); }
   else    { bn_bwd_reduce_kernel<1><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a); }
@@ -329,7 +354,7 @@ XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const
 XB_API int xb_bn_backward_apply(const float* dy, const float* x, const float* y, const float* save_mean, const float* save_invstd,
                                 const float* gamma, const float* dsums, float* dx, float* dres, float* dgamma, float* dbeta,
                                 int M, int C, int relu, int accum_dx, int accum_dres, cudaStream_t st) {
-  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, const_cast<float*>(dsums), dx, dres, dgamma, dbeta, M, C, relu, accum_dx, accum_dres, 0};
+  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, const_cast<float*>(dsums), dx, dres, dgamma, dbeta, M, C, relu ? 1 : 0, accum_dx, accum_dres, 0, nullptr};
   bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
   int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
   if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a);
@@ -375,7 +400,7 @@ int xb_bn_backward_static(const float* dy, const float* x, const float* y, const
   float* sums = g_bn_static_ptr[dev];
   e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)C, stream);     // the sums accumulate from zero
   if (e != cudaSuccess) return (int)e;
-  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, sums, dx, dres, dgamma, dbeta, M, C, relu, accum_dx, accum_dres, 0};
+  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, sums, dx, dres, dgamma, dbeta, M, C, relu ? 1 : 0, accum_dx, accum_dres, 0, nullptr};
   bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
   int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
   if (v4) { bn_bwd_reduce_kernel<4><<<blocks, NT, 0, stream>>>(a); bn_bwd_apply_kernel<4><<<blocks, NT, 0, stream>>>(a); }

@@ -2,10 +2,11 @@
 //
 // A 1x1 convolution over NHWC data is a GEMM whose operands already sit in memory in the shape the tensor core wants, so
 // nothing is gathered: TMA (cp.async.bulk.tensor) drops swizzled operand tiles into shared memory, one elected thread
-// issues tcgen05.mma into a TMEM accumulator, and four epilogue warps drain it.  Warp roles in a 192-thread CTA:
+// issues tcgen05.mma into a TMEM accumulator, and eight epilogue warps drain it.  Warp roles in a 320-thread CTA:
 //   warp 0      producer: waits for a free stage, arms its mbarrier with the byte count, issues the TMA loads
 //   warp 1      tensor core: waits for a full stage, issues 4 x (M128 x BN x K8, tf32), tcgen05.commit frees the stage
-//   warps 2..5  epilogue: wait for the accumulator, tcgen05.ld, bias / ReLU / accumulate / batch-norm sums, store
+//   warps 2..9  epilogue: wait for the accumulator, tcgen05.ld, bias / ReLU / accumulate / batch-norm sums, store; the two
+//               warps of a TMEM lane quadrant take alternate 32-column blocks
 // Two operand forms:
 //   NT  D[m][n] = sum_k A[m][k] B[n][k]        (fprop: A = X, B = W (K,C);  dgrad: A = dY, B = W^T (C,K))
 //       both operands K-major, 128-byte swizzle, 32 floats of K per stage.  A is described by a 3-D tensor map
@@ -27,7 +28,8 @@ using namespace tc;
 
 namespace {
 
-constexpr int GT = 192;
+constexpr int GT = 320;                                 // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two per TMEM lane quadrant)
+constexpr int EPI_BYTES = 8 * 32 * 33 * 4;              // one 32 x 32 transpose block per epilogue warp
 constexpr int MAX_STAGES = 8;
 constexpr int G_RELU = 1, G_ACCUM = 2, G_STATS = 4, G_BNBWD = 8;   // G_BNBWD: `stats` receives batch-norm backward sums (XbBnFuse)
 constexpr uint32_t A_BYTES = 128 * 128;                 // 128 rows (or 4 planes x 32 positions) x 128 B
@@ -153,7 +155,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
       const bool done = mbar_wait(&accum_bar, 0);
       if (!done) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); }
       tc_fence_after();
-      const int q = warp & 3, row = q * 32 + lane;
+      const int q = warp & 3, half = (warp - 2) >> 2, row = q * 32 + lane;
       if (done && !s_abort) {
         if (MODE != 1) {
           long long m;
@@ -176,12 +178,12 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
           // transposes 32 x 32 blocks through shared memory: afterwards eight lanes cover the 128 contiguous bytes of one
           // row, an instruction writes four full lines, and the batch-norm sums need two shuffles per column group.
           // (the pipeline stages are idle by now - every load has landed and every MMA has completed - and serve as the buffer)
-          float (*tb)[33] = reinterpret_cast<float (*)[33]>(smem + (size_t)q * 32 * 33 * sizeof(float));
+          float (*tb)[33] = reinterpret_cast<float (*)[33]>(smem + (size_t)(warp - 2) * 32 * 33 * sizeof(float));
           s_rowoff[q][lane] = ok ? m * g.ldd : -1ll;
           __syncwarp();
           const int cq = (lane & 7) * 4, rsub = lane >> 3;
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 32) {
+          for (int c0 = half * 32; c0 < BN; c0 += 64) {
             if (n0 + c0 >= g.N) break;                     // whole-warp condition
             {
               float v[16];
@@ -244,7 +246,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
         } else {
           const int m = tile * 128 + row;
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) {
+          for (int c0 = half * 16; c0 < BN; c0 += 32) {
             if (n0 + c0 >= g.N) break;
             float v[16];
             tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
@@ -307,7 +309,8 @@ inline int pick_stages(int kblocks, int BN, long long ctas) {
 template <int BN, int MODE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags, int* status,
            cudaStream_t st, const XbBnFuse& bn) {
-  const size_t smem = (size_t)g.stages * stage_bytes(BN);
+  size_t smem = (size_t)g.stages * stage_bytes(BN);
+  if (smem < (size_t)EPI_BYTES) smem = EPI_BYTES;          // the idle stages double as the epilogue's transpose blocks
   gemm_tma_kernel<BN, MODE><<<grid, GT, smem, st>>>(a, b, D, bias, stats, g, flags, status, bn);
   return (int)cudaGetLastError();
 }

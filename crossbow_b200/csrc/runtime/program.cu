@@ -27,6 +27,8 @@ XB_API int xb_transpose_weights(const float*, float*, const XbTransposeDesc*, in
 XB_API int xb_bn_stats(const float*, float*, int, int, cudaStream_t);
 XB_API int xb_bn_forward(const float*, const float*, float*, const float*, const float*, const float*, float*, float*, float*, float*,
                          const XbTaskParams*, int, int, float, int, int, int, float, cudaStream_t);
+XB_API int xb_bn_backward_remask(const float*, const float*, const float*, const float*, const float*, const float*, float*, float*, float*, float*, int, int,
+                                 int, cudaStream_t);
 XB_API int xb_bn_backward_apply(const float*, const float*, const float*, const float*, const float*, const float*, const float*, float*, float*, float*,
                                 float*, int, int, int, int, int, cudaStream_t);
 XB_API int xb_bn_backward(const float*, const float*, const float*, const float*, const float*, const float*, float*, float*, float*, float*,
@@ -124,6 +126,9 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
                            (const float*)o.p[5], (float*)o.p[6], (float*)o.p[7], (float*)o.p[8], (float*)o.p[9], (const XbTaskParams*)o.p[10],
                            o.ia[0], o.ia[1], o.fa[0], o.ia[2], o.ia[3], o.ia[4], o.fa[1], st);
     case OP_BN_BWD:
+      if (o.p[11] && !o.ia[5])   // ReLU without residual: mask re-derived from x, the layer's output is not read
+        return xb_bn_backward_remask((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[3], (const float*)o.p[4], (const float*)o.p[5],
+                                     (const float*)o.p[11], (float*)o.p[6], (float*)o.p[7], (float*)o.p[9], (float*)o.p[10], o.ia[0], o.ia[1], o.ia[3], st);
       if (o.ia[5])     // the sums were produced by the operator that completed dy
         return xb_bn_backward_apply((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[2], (const float*)o.p[3], (const float*)o.p[4],
                                     (const float*)o.p[5], (const float*)o.p[6], (float*)o.p[7], (float*)o.p[8], (float*)o.p[9], (float*)o.p[10],

@@ -580,9 +580,11 @@ class Lowering:
                 gres, accr = (None, 0)
                 if res is not None and res.needs_grad:
                     gres, accr = self.gout(res)
+                # ReLU fused, no residual: the kernels re-derive the mask from x and never read the layer's output
+                remask = self.wptr(bk.variables[1]) if (relu and res is None and fused is None) else None
                 self.emit(_op(L.OP_BN_BWD, ia=[x.rows, x.c, int(relu), accx, accr, int(fused is not None)],
                               p=[dy, x.buf, out.buf, bi["save_mean"], bi["save_invstd"], self.wptr(bk.variables[0]), dsums, gx, gres,
-                                 self.wptr(bk.variables[0], rep.g), self.wptr(bk.variables[1], rep.g)]))
+                                 self.wptr(bk.variables[0], rep.g), self.wptr(bk.variables[1], rep.g), remask]))
                 continue
             x = self.out_tensor(ins_nodes[0])
             if kind == "elementwise":
