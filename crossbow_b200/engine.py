@@ -70,7 +70,7 @@ class Learner:
         result_dev = lib.xb_learner_result_dev(self.handle)
         self.low_train = Lowering(e.train_graph, e.model, e.batch, e.input_chw, e.device, self.rep.w, self.rep, e.shared,
                                   self.params_dev, params_host, result_dev, update_model=e.update_model, training=True,
-                                  use_tc=e.use_tc, clip=e.solver.clip_gradient_threshold >= 0, lr_mult=e.lr_mult, splits=e.splits)
+                                  use_tc=e.use_tc, clip=e.solver.clip_gradient_threshold >= 0, lr_mult=e.lr_mult, splits=e.splits, reuse_memory=e.reuse_memory)
         ops = self.low_train.op_array()
         self.prog_train = lib.xb_program_create(ops, len(ops), int(e.use_tc), e.tc_status.data_ptr())
         self.prog_test = None
@@ -78,7 +78,7 @@ class Learner:
             # test tasks read the CENTRAL model (the reference checks with the master copy) and share the staging buffers
             self.low_test = Lowering(e.test_graph, e.model, e.batch, e.input_chw, e.device, e.shared.z, None, e.shared,
                                      self.params_dev, params_host, result_dev, update_model=e.update_model, training=False,
-                                     use_tc=e.use_tc)
+                                     use_tc=e.use_tc, reuse_memory=e.reuse_memory)
             tops = self.low_test.op_array()
             self.prog_test = lib.xb_program_create(tops, len(tops), int(e.use_tc), e.tc_status.data_ptr())
         lib.xb_learner_set_programs(self.handle, self.prog_train, self.prog_test)
@@ -125,7 +125,7 @@ class GpuEngine:
                  batch: int, input_chw, solver: SolverConf, update_model: UpdateModel, replicas: int = 1, wpc: int = 1,
                  rank: int = 0, world: int = 1, device_index: int = 0, use_tc: bool = True, use_graphs: bool = True,
                  seed: int = 0, fused_sync: bool = True, two_shot: Optional[bool] = None, sync_timeout_s: float = 5.0,
-                 splits: int = 1):
+                 splits: int = 1, reuse_memory: bool = False):
         from .ops import lib as L
         from .parallel.sync import FusedSynchroniser, ReferenceSynchroniser
         if not torch.cuda.is_available():
@@ -136,6 +136,7 @@ class GpuEngine:
         self.train_graph, self.test_graph, self.model = train_graph, test_graph, model
         self.batch, self.input_chw, self.solver, self.update_model = batch, tuple(input_chw), solver, update_model
         self.splits = max(1, int(splits))
+        self.reuse_memory = bool(reuse_memory)
         self.rank, self.world, self.wpc, self.seed = rank, world, wpc, seed
         self.use_tc, self.use_graphs = use_tc, use_graphs
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.device)

@@ -132,7 +132,7 @@ class Lowering:
                  replica: Optional[ReplicaBuffers], shared: DeviceShared, params_dev: torch.Tensor, params_host_ptr: int,
                  result_dev_ptr: int,
                  update_model: UpdateModel = UpdateModel.SMA, training=True, use_tc=True, clip=False,
-                 lr_mult: Optional[torch.Tensor] = None, seed_stream_base=0, splits: int = 1):
+                 lr_mult: Optional[torch.Tensor] = None, seed_stream_base=0, splits: int = 1, reuse_memory: bool = False):
         if splits < 1 or batch % splits:
             raise ValueError("error: the batch size must be a multiple of the number of splits")
         # `--splits` (taskhandler.c:65-114): one task runs the whole graph `splits` times over consecutive sub-batches of
@@ -147,6 +147,9 @@ class Lowering:
         self.lr_mult = lr_mult
         self.arena = Arena(device)
         self._count_pass, self._gout_count, self._gout_total = False, {}, {}
+        self.all_tensors: List[T] = []
+        self.reuse_memory = reuse_memory
+        self.bytes_before_reuse = 0
         self.ops: List[L.XbOp] = []
         self.keep = []                      # python objects that must outlive the program (descriptor tables ...)
         c, h, w = input_chw
@@ -169,7 +172,9 @@ class Lowering:
         return base.data_ptr() + 4 * var.doffset
 
     def new_tensor(self, n, h, w, c, name="") -> T:
-        return T(self.arena.alloc(n * h * w * c), n, h, w, c, name)
+        t = T(self.arena.alloc(n * h * w * c), n, h, w, c, name)
+        self.all_tensors.append(t)
+        return t
 
     def grad_of(self, t: T) -> torch.Tensor:
         if t.grad is None:
@@ -246,6 +251,55 @@ class Lowering:
         self.ops[zero_slot] = _op(L.OP_MEMSET, la=[4 * self.zero_used], p=[self.zero_region])
         if self.splits > 1:
             self._repeat_for_splits()
+        if self.reuse_memory:
+            self._reuse_buffers()
+
+    def _reuse_buffers(self):
+        """`--reuse-memory` (MemoryPlannerV2.java:117-296): activations and activation gradients whose lifetimes do not overlap
+        share storage.  Lifetimes are read off the finished operator list (first and last operator that names a buffer), a
+        best-fit scan assigns buffers to slots, and the operators' pointers are patched; a learner's operators run in
+        stream order, so the aliasing is safe.  Inspecting intermediate tensors after a run is meaningless with this on."""
+        cands = {}
+        for t in self.all_tensors:
+            for b in (t.buf, t.grad):
+                if b is not None:
+                    cands[b.data_ptr()] = b
+        first, last = {}, {}
+        for i, o in enumerate(self.ops):
+            for j in range(len(o.p)):
+                p = o.p[j]
+                if p in cands:
+                    first.setdefault(p, i)
+                    last[p] = i
+        slots = []                                           # [capacity in elements, last operator that uses it, members]
+        home = {}
+        for p in sorted(first, key=first.get):
+            need = cands[p].numel()
+            best = None
+            for sl in slots:
+                if sl[1] < first[p] and sl[0] >= need and (best is None or sl[0] < best[0]):
+                    best = sl
+            if best is None:
+                best = [need, -1, []]
+                slots.append(best)
+            best[1] = last[p]
+            best[2].append(p)
+            home[p] = best
+        self.bytes_before_reuse = self.arena.total
+        storage = {id(sl): torch.empty(sl[0], device=self.device) for sl in slots}
+        new_ptr = {p: storage[id(sl)].data_ptr() for p, sl in home.items()}
+        for o in self.ops:
+            for j in range(len(o.p)):
+                if o.p[j] in new_ptr:
+                    o.p[j] = new_ptr[o.p[j]]
+        for t in self.all_tensors:
+            if t.buf is not None and t.buf.data_ptr() in home:
+                t.buf = storage[id(home[t.buf.data_ptr()])][: t.buf.numel()]
+            if t.grad is not None and t.grad.data_ptr() in home:
+                t.grad = storage[id(home[t.grad.data_ptr()])][: t.grad.numel()]
+        dropped = set(home)
+        self.arena.chunks = [c for c in self.arena.chunks if c.data_ptr() not in dropped] + list(storage.values())
+        self.arena.total = sum(c.numel() * c.element_size() for c in self.arena.chunks)
 
     def _repeat_for_splits(self):
         """Operator list of one sub-batch -> `splits` copies reading consecutive windows of the staged batch.  The loss and

@@ -80,6 +80,19 @@ def test_lenet_batchnorm_eamsgd():
     run_both("lenet-batchnorm", 8, 2, 4, update_model=UpdateModel.EAMSGD)
 
 
+def test_reuse_memory_same_results_less_memory():
+    """--reuse-memory: buffers with disjoint lifetimes share storage; training results are unchanged."""
+    run_both("resnet8", 8, 2, 4, reuse_memory=True)
+    run_both("convnet", 8, 1, 3, reuse_memory=True)
+    from helpers import engines
+    sizes = []
+    for reuse in (False, True):
+        spec, m, gpu, _ = engines("resnet20", 16, k=1, reuse_memory=reuse)
+        sizes.append(gpu.learners[0].low_train.arena.total)
+        gpu.destroy()
+    assert sizes[1] < 0.8 * sizes[0], sizes
+
+
 def test_batch_splits():
     """--splits 2: every task runs the graph (optimiser included) over two consecutive sub-batches."""
     run_both("convnet", 8, 2, 4, splits=2)
