@@ -288,11 +288,13 @@ __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
   }
 }
 
-inline int rows_per_block_for(int M, int C, int vec, int& blocks) {
+// Reductions end in 2C same-address atomics per block, which serialise in L2: they get fewer, longer blocks.
+static int g_bn_reduce_blocks = 296;
+inline int rows_per_block_for(int M, int C, int vec, int& blocks, int target = 592, int min_steps = 2) {
   Tiling t = make_tiling(C, vec);
   // aim for ~4 resident blocks per SM (592 blocks), at least 2 row-steps per block
-  int min_rows = t.rows_per_iter * 2;
-  int rpb = xb_ceil_div(M, 592);
+  int min_rows = t.rows_per_iter * min_steps;
+  int rpb = xb_ceil_div(M, target);
   if (rpb < min_rows) rpb = min_rows;
   rpb = xb_ceil_div(rpb, t.rows_per_iter) * t.rows_per_iter;
   blocks = xb_ceil_div(M, rpb);
@@ -330,11 +332,13 @@ XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const
                           int M, int C, int relu, int accum_dx, int accum_dres, cudaStream_t st) {
   BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, dsums, dx, dres, dgamma, dbeta, M, C, relu ? 1 : 0, accum_dx, accum_dres, 0, nullptr};
   bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
-  int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
-  if (v4) { bn_bwd_reduce_kernel<4><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); }
-  else    { bn_bwd_reduce_kernel<1><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a); }
+  int blocks, rblocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, rblocks, g_bn_reduce_blocks, 8);
+  if (v4) bn_bwd_reduce_kernel<4><<<rblocks, NT, 0, st>>>(a); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, st>>>(a);
+  a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
+  if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); else bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
+XB_API void xb_bn_set_reduce_blocks(int n) { g_bn_reduce_blocks = n > 0 ? n : 296; }
 
 // As xb_bn_backward, for a layer whose fused ReLU has no residual input: the mask is re-derived from x, gamma, beta and the
 // saved statistics with the forward pass's own expressions (bit-identical), so the layer's output is not read at all -
@@ -344,9 +348,10 @@ XB_API int xb_bn_backward_remask(const float* dy, const float* x, const float* s
                                  cudaStream_t st) {
   BnBwdArgs a{dy, x, nullptr, save_mean, save_invstd, gamma, dsums, dx, nullptr, dgamma, dbeta, M, C, 2, accum_dx, 0, 0, beta};
   bool v4 = can_vec4(C, dy, x, nullptr, dx);
-  int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
-  if (v4) { bn_bwd_reduce_kernel<4><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); }
-  else    { bn_bwd_reduce_kernel<1><<<blocks, NT, 0, st>>>(a); bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a); }
+  int blocks, rblocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, rblocks, g_bn_reduce_blocks, 8);
+  if (v4) bn_bwd_reduce_kernel<4><<<rblocks, NT, 0, st>>>(a); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, st>>>(a);
+  a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
+  if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); else bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
 

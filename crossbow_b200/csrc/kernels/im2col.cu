@@ -17,38 +17,41 @@ namespace {
 inline int padded_k(const XbConvGeom* g) { return (g->R * g->S * g->C + 31) / 32 * 32; }
 inline size_t align256(size_t b) { return (b + 255) / 256 * 256; }
 
-// One thread = four consecutive reduction indices of one output position.
-__global__ void im2col_kernel(const float* __restrict__ X, float* __restrict__ A, XbConvGeom g, int Kp, long long M) {
+// A thread keeps four consecutive reduction indices (their tap / channel decomposition is computed once) and walks the
+// output positions of its block's slice; the Kp/4 threads of a position write one contiguous row of the patch matrix.
+__global__ void __launch_bounds__(256) im2col_kernel(const float* __restrict__ X, float* __restrict__ A, XbConvGeom g, int Kp, long long M, int rows_per_block) {
   const int k4n = Kp >> 2;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= M * k4n) return;
-  const long long m = idx / k4n;
-  const int k0 = (int)(idx - m * k4n) * 4;
-  const int q = (int)(m % g.Q); const long long t = m / g.Q; const int p = (int)(t % g.P); const int n = (int)(t / g.P);
-  const int KR = g.R * g.S * g.C;
-  float v[4];
-  if ((g.C & 3) == 0) {                                    // four channels of one tap: one 16-byte load
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (k0 < KR) {
-      const int tap = k0 / g.C, c = k0 - tap * g.C, r = tap / g.S, s = tap - r * g.S;
-      const int h = p * g.sh - g.ph + r, w = q * g.sw - g.pw + s;
-      if (h >= 0 && h < g.H && w >= 0 && w < g.W) x = *reinterpret_cast<const float4*>(X + (((long long)n * g.H + h) * g.W + w) * g.C + c);
-    }
-    *reinterpret_cast<float4*>(A + m * Kp + k0) = x;
-    return;
-  }
+  const int per = 256 / k4n;                               // positions handled side by side by one block (>= 1 for Kp <= 1024)
+  const int lane_k = threadIdx.x % k4n, sub = threadIdx.x / k4n;
+  if (sub >= per) return;
+  const int k0 = lane_k * 4, KR = g.R * g.S * g.C;
+  int rr[4], ss[4], cc[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const int k = k0 + j;
-    float x = 0.f;
-    if (k < KR) {
-      const int tap = k / g.C, c = k - tap * g.C, r = tap / g.S, s = tap - r * g.S;
-      const int h = p * g.sh - g.ph + r, w = q * g.sw - g.pw + s;
-      if (h >= 0 && h < g.H && w >= 0 && w < g.W) x = __ldg(X + (((long long)n * g.H + h) * g.W + w) * g.C + c);
-    }
-    v[j] = x;
+    const int k = k0 + j, tap = k / g.C;
+    cc[j] = k - tap * g.C; rr[j] = tap / g.S; ss[j] = tap - rr[j] * g.S;
+    if (k >= KR) rr[j] = -1000000;                         // padding column: always out of range -> zero
   }
-  *reinterpret_cast<float4*>(A + m * Kp + k0) = make_float4(v[0], v[1], v[2], v[3]);
+  const bool vec = (g.C & 3) == 0;
+  const long long m0 = (long long)blockIdx.x * rows_per_block, m1 = m0 + rows_per_block < M ? m0 + rows_per_block : M;
+  for (long long m = m0 + sub; m < m1; m += per) {
+    const int q = (int)(m % g.Q); const long long t = m / g.Q; const int p = (int)(t % g.P); const int n = (int)(t / g.P);
+    const int hb = p * g.sh - g.ph, wb = q * g.sw - g.pw;
+    float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (vec) {                                             // four channels of one tap: one 16-byte load
+      const int h = hb + rr[0], w = wb + ss[0];
+      if (h >= 0 && h < g.H && w >= 0 && w < g.W) out = *reinterpret_cast<const float4*>(X + (((long long)n * g.H + h) * g.W + w) * g.C + cc[0]);
+    } else {
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int h = hb + rr[j], w = wb + ss[j];
+        v[j] = (h >= 0 && h < g.H && w >= 0 && w < g.W) ? __ldg(X + (((long long)n * g.H + h) * g.W + w) * g.C + cc[j]) : 0.f;
+      }
+      out = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    *reinterpret_cast<float4*>(A + m * Kp + k0) = out;
+  }
 }
 
 // dst[row][0..Kp) = src[row][0..KR) followed by zeros
@@ -74,8 +77,13 @@ XbConvGeom as_gemm(const XbConvGeom* g, int Kp, long long M) {
 }
 
 int run_im2col(const float* X, float* A, const XbConvGeom* g, int Kp, long long M, cudaStream_t st) {
-  const long long total = M * (Kp >> 2);
-  im2col_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(X, A, *g, Kp, M);
+  if ((Kp >> 2) > 256) return -XB_BAD_ARG;
+  const int per = 256 / (Kp >> 2);
+  long long blocks = (M + (long long)per * 8 - 1) / ((long long)per * 8);      // ~8 positions per thread
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const int rows_per_block = (int)((M + blocks - 1) / blocks);
+  blocks = (M + rows_per_block - 1) / rows_per_block;
+  im2col_kernel<<<(unsigned)blocks, 256, 0, st>>>(X, A, *g, Kp, M, rows_per_block);
   return (int)cudaGetLastError();
 }
 
@@ -86,7 +94,7 @@ XB_API long long xb_conv_im2col_scratch(const XbConvGeom* g, int which) {
   if (which != 0 && which != 2) return 0;
   const long long M = (long long)g->N * g->P * g->Q;
   const int Kp = padded_k(g);
-  if (M * Kp >= (1ll << 31) || M >= (1ll << 31) || g->K % 4) return 0;
+  if (M * Kp >= (1ll << 31) || M >= (1ll << 31) || g->K % 4 || Kp > 1024) return 0;
   if (which == 2 && g->K % 32) return 0;
   XbConvGeom f = as_gemm(g, Kp, M);
   if (!xb_conv1x1_tma_supported(&f, which)) return 0;
@@ -109,14 +117,16 @@ XB_API int xb_conv_fprop_im2col(const float* X, const float* W, const float* bia
 }
 
 // dW (K,R,S,C) += dY^T A; dW must hold the value to accumulate onto (normally zero).
-XB_API int xb_conv_wgrad_im2col(const float* dY, const float* X, float* dW, const XbConvGeom* g, float* scratch, int* status, cudaStream_t st) {
+// `reuse_patches` != 0: the scratch still holds this layer's patch matrix from the forward pass of the same task.
+XB_API int xb_conv_wgrad_im2col(const float* dY, const float* X, float* dW, const XbConvGeom* g, float* scratch, int reuse_patches, int* status,
+                                cudaStream_t st) {
   if (!scratch || !xb_conv_im2col_scratch(g, 2)) return -XB_BAD_ARG;
   const long long M = (long long)g->N * g->P * g->Q;
   const int Kp = padded_k(g), KR = g->R * g->S * g->C;
   float* A = scratch;
   float* dWp = scratch + align256((size_t)M * Kp * 4) / 4;
   int e;
-  if ((e = run_im2col(X, A, g, Kp, M, st))) return e;
+  if (!reuse_patches && (e = run_im2col(X, A, g, Kp, M, st))) return e;
   if ((e = (int)cudaMemsetAsync(dWp, 0, (size_t)g->K * Kp * 4, st))) return e;
   XbConvGeom f = as_gemm(g, Kp, M);
   if ((e = xb_conv1x1_wgrad_tma(dY, A, dWp, &f, status, st))) return e;

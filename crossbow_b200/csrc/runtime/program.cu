@@ -21,7 +21,7 @@ XB_API int xb_conv_dgrad_tc(const float*, const float*, float*, const XbConvGeom
 XB_API int xb_conv_wgrad_tc(const float*, const float*, float*, const XbConvGeom*, int*, cudaStream_t);
 XB_API int xb_conv_fprop_im2col(const float*, const float*, const float*, float*, float*, const XbConvGeom*, int, float*, int*, cudaStream_t);
 XB_API int xb_conv3x3_s2_dgrad(const float*, const float*, float*, const XbConvGeom*, int, float*, int*, cudaStream_t, const XbBnFuse*);
-XB_API int xb_conv_wgrad_im2col(const float*, const float*, float*, const XbConvGeom*, float*, int*, cudaStream_t);
+XB_API int xb_conv_wgrad_im2col(const float*, const float*, float*, const XbConvGeom*, float*, int, int*, cudaStream_t);
 XB_API int xb_tc_supported(const XbConvGeom*, int which);
 XB_API int xb_transpose_weights(const float*, float*, const XbTransposeDesc*, int, int, cudaStream_t);
 XB_API int xb_bn_stats(const float*, float*, int, int, cudaStream_t);
@@ -114,7 +114,7 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
     case OP_CONV_WGRAD: {
       XbConvGeom g = geom_of(o);
       if (pr->use_tc && (o.flags & 0x100) && o.p[3])
-        return xb_conv_wgrad_im2col((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, (float*)o.p[3], pr->tc_status, st);
+        return xb_conv_wgrad_im2col((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, (float*)o.p[3], o.flags & 0x20, pr->tc_status, st);
       if (pr->use_tc && (o.flags & 0x100) && xb_tc_supported(&g, 2))
         return xb_conv_wgrad_tc((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, pr->tc_status, st);
       return xb_conv_wgrad_simt((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], &g, st);

@@ -599,7 +599,9 @@ class Lowering:
                 wv = k.variables[0]
                 tc = L.F_TC if self.use_tc else 0
                 scratch = info.get("im2col") if (tc and L.load().xb_conv_im2col_wanted(self._geom_struct(geom), 2)) else None
-                self.emit(_op(L.OP_CONV_WGRAD, tc, ia=geom, p=[dy, x.buf, self.wptr(wv, rep.g), scratch]))
+                # 0x20: the layer's forward pass went through the same patch matrix and left it in the scratch
+                keep = 0x20 if (scratch is not None and L.load().xb_conv_im2col_wanted(self._geom_struct(geom), 0)) else 0
+                self.emit(_op(L.OP_CONV_WGRAD, tc | keep, ia=geom, p=[dy, x.buf, self.wptr(wv, rep.g), scratch]))
                 if len(k.variables) > 1:
                     self.emit(_op(L.OP_COLSUM, ia=[out.rows, out.c], p=[dy, self.wptr(k.variables[1], rep.g)]))
                 if x.needs_grad:

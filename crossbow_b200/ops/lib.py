@@ -98,7 +98,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_conv3x3_s2_dgrad", I, P, P, P, G, I, P, P, P, P)
     _sig(lib, "xb_conv_im2col_scratch", C.c_longlong, G, I)
     _sig(lib, "xb_conv_fprop_im2col", I, P, P, P, P, P, G, I, P, P, P)
-    _sig(lib, "xb_conv_wgrad_im2col", I, P, P, P, G, P, P, P)
+    _sig(lib, "xb_conv_wgrad_im2col", I, P, P, P, G, P, I, P, P)
     _sig(lib, "xb_conv1x1_tma_supported", I, G, I)
     _sig(lib, "xb_conv3x3_slab_supported", I, G, I)
     _sig(lib, "xb_transpose_weights", I, P, P, P, I, I, P)

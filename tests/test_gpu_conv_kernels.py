@@ -158,7 +158,9 @@ def test_patch_matrix_gemm_path(env, shape):
     assert torch.allclose(stats[:K], m.sum(0), rtol=4e-2, atol=4e-2 * m.shape[0] ** 0.5)
     if K % 32 == 0:
         dw = torch.zeros(K, R, S, Cc, device=dev)
-        L.check(lib.xb_conv_wgrad_im2col(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), scratch.data_ptr(), status.data_ptr(), s), "wgrad")
+        for reuse in (0, 1):          # 1: the patch matrix written by the forward call above is still in the scratch
+            dw.zero_()
+            L.check(lib.xb_conv_wgrad_im2col(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), scratch.data_ptr(), reuse, status.data_ptr(), s), "wgrad")
         torch.cuda.synchronize()
         assert int(status[0]) == 0
         dw_ref = wr.grad.permute(0, 2, 3, 1)
