@@ -265,7 +265,8 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
   if (MODE != 1 && (flags & (G_STATS | G_BNBWD)) && !s_abort) {
     for (int i = tid; i < BN; i += GT) {
       const int n = n0 + i;
-      if (n < g.N) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.N + n], s_red[BN + i]); }
+      float* dst = (flags & G_BNBWD) ? stats : stats + (size_t)(blockIdx.x % XB_STATS_COPIES) * 2 * g.N;
+      if (n < g.N) { atomicAdd(&dst[n], s_red[i]); atomicAdd(&dst[g.N + n], s_red[BN + i]); }
     }
   }
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);

@@ -78,7 +78,8 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
 
     # forward with bias + ReLU + statistics
     y = torch.full((N, P, Q, K), 7.0, device=dev)
-    stats = torch.zeros(2 * K, device=dev)
+    copies = lib.xb_stats_copies()          # the sums are spread over several copies of the [2K] vector
+    stats = torch.zeros(2 * K * copies, device=dev)
     flags = 1 | 4
     if impl == "simt":
         L.check(lib.xb_conv_fprop_simt(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), stats.data_ptr(), C.byref(g), flags, s), "fprop")
@@ -89,6 +90,7 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
     scale = float(y_ref.abs().max()) + 1e-6
     assert float((y - y_ref).abs().max()) / scale < tol
     m = y_ref.reshape(-1, K)
+    stats = stats.view(copies, 2 * K).sum(0)
     assert torch.allclose(stats[:K], m.sum(0), rtol=tol * 10, atol=tol * 10 * m.shape[0] ** 0.5)
     assert torch.allclose(stats[K:], (m * m).sum(0), rtol=tol * 10, atol=tol * 10 * m.shape[0] ** 0.5)
 
@@ -148,13 +150,14 @@ def test_patch_matrix_gemm_path(env, shape):
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     s = torch.cuda.current_stream().cuda_stream
     y = torch.full((N, P, Q, K), 7.0, device=dev)
-    stats = torch.zeros(2 * K, device=dev)
+    stats = torch.zeros(2 * K * lib.xb_stats_copies(), device=dev)
     L.check(lib.xb_conv_fprop_im2col(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), stats.data_ptr(), C.byref(g), 1 | 4, scratch.data_ptr(),
                                      status.data_ptr(), s), "fprop")
     torch.cuda.synchronize()
     assert int(status[0]) == 0
     assert float((y - y_ref).abs().max()) / float(y_ref.abs().max()) < 4e-3
     m = y_ref.reshape(-1, K)
+    stats = stats.view(lib.xb_stats_copies(), 2 * K).sum(0)
     assert torch.allclose(stats[:K], m.sum(0), rtol=4e-2, atol=4e-2 * m.shape[0] ** 0.5)
     if K % 32 == 0:
         dw = torch.zeros(K, R, S, Cc, device=dev)
