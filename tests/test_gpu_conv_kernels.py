@@ -119,6 +119,18 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
     assert float((dw - dw_ref).abs().max()) / (float(dw_ref.abs().max()) + 1e-6) < (tol if impl == "tc" else 2e-4)
 
 
+@pytest.mark.parametrize("shape", [(2, 14, 14, 64, 256, 1, 1, 1, 0), (3, 14, 14, 256, 256, 3, 3, 1, 1), (5, 7, 7, 512, 96, 3, 3, 1, 1),
+                                   (2, 56, 56, 64, 64, 3, 3, 1, 1), (4, 28, 28, 256, 128, 1, 1, 2, 0), (3, 10, 10, 96, 64, 1, 1, 1, 0)])
+def test_two_m_tiles_per_cta(env, shape):
+    """The GEMM kernels with two M tiles per CTA forced (odd tile counts included)."""
+    L, lib = env
+    lib.xb_gemm_set_mt(2)
+    try:
+        test_fprop_dgrad_wgrad(env, "tc", shape)
+    finally:
+        lib.xb_gemm_set_mt(0)
+
+
 def test_1x1_shapes_take_the_tma_path(env):
     L, lib = env
     for shape, which, want in [((8, 56, 56, 64, 256, 1, 1, 1, 0), 0, 1), ((8, 56, 56, 64, 256, 1, 1, 1, 0), 1, 1), ((8, 56, 56, 64, 256, 1, 1, 1, 0), 2, 1),
