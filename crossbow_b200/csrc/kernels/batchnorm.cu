@@ -38,7 +38,7 @@ __host__ __device__ inline Tiling make_tiling(int C, int vec) {
   return t;
 }
 
-// sums[0..C) += sum_x, sums[C..2C) += sum_x^2 (copy 0 of the XB_STATS_COPIES copies a statistics buffer has)
+// sums[0..C) += sum_x, sums[C..2C) += sum_x^2 ; optionally of a*(mask) for backward
 template <int VEC>
 __global__ void __launch_bounds__(NT) bn_stats_kernel(const float* __restrict__ x, float* __restrict__ sums, int M, int C, int rows_per_block) {
   const Tiling t = make_tiling(C, VEC);
@@ -100,11 +100,8 @@ __global__ void __launch_bounds__(NT) bn_fwd_kernel(BnArgs a) {
       int c = cg * VEC + e;
       float mean, invstd;
       if (a.training) {
-        float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-        for (int k = 0; k < XB_STATS_COPIES; ++k) { s1 += a.sums[k * 2 * a.C + c]; s2 += a.sums[k * 2 * a.C + a.C + c]; }
-        mean = s1 * invM;
-        float var = fmaxf(s2 * invM - mean * mean, 0.f);
+        mean = a.sums[c] * invM;
+        float var = fmaxf(a.sums[a.C + c] * invM - mean * mean, 0.f);
         invstd = rsqrtf(var + a.eps);
         if (blockIdx.x == 0 && rsub == 0) {
           a.save_mean[c] = mean; a.save_invstd[c] = invstd;
@@ -341,7 +338,6 @@ XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const
   if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); else bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
-XB_API int xb_stats_copies() { return XB_STATS_COPIES; }
 XB_API void xb_bn_set_reduce_blocks(int n) { g_bn_reduce_blocks = n > 0 ? n : 296; }
 
 // As xb_bn_backward, for a layer whose fused ReLU has no residual input: the mask is re-derived from x, gamma, beta and the

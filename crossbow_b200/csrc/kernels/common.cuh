@@ -14,11 +14,6 @@ struct XbConvGeom {
   int sh, sw, ph, pw;  // stride / padding
 };
 
-// Batch-norm FORWARD sums arrive from hundreds of CTAs (convolution epilogues); 2C same-address atomics per CTA serialise in
-// L2, so the sums are spread over XB_STATS_COPIES copies of the [2C] vector (copy = CTA index mod copies) and the
-// normalisation kernel adds the copies up.  A statistics buffer is therefore XB_STATS_COPIES * 2C floats, zero on entry.
-#define XB_STATS_COPIES 1
-
 // Batch-norm backward sums produced by the epilogue of the kernel that writes the gradient dy of a normalisation layer
 // (the data gradient of the next convolution): sums[c] += dz, sums[C + c] += dz * (x - mean[c]) * istd[c] with
 // dz = dy masked by the layer's fused ReLU (y > 0).  x = the layer's input, y = its output; all of dy's shape.

@@ -181,8 +181,7 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __r
   if ((flags & (F_STATS | F_BNBWD)) && !abort_all) {
     for (int i = tid; i < BN; i += NTHREADS) {
       int n = n0 + i;
-      float* dst = (flags & F_BNBWD) ? stats : stats + (size_t)(blockIdx.x % XB_STATS_COPIES) * 2 * g.K;
-      if (n < g.K) { atomicAdd(&dst[n], s_red[i]); atomicAdd(&dst[g.K + n], s_red[BN + i]); }
+      if (n < g.K) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.K + n], s_red[BN + i]); }
     }
   }
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
@@ -539,8 +538,7 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_pipe_kernel(const float
   if ((flags & (F_STATS | F_BNBWD)) && !abort_all) {
     for (int i = tid; i < BN; i += NTHREADS) {
       int n = n0 + i;
-      float* dst = (flags & F_BNBWD) ? stats : stats + (size_t)(blockIdx.x % XB_STATS_COPIES) * 2 * g.K;
-      if (n < g.K) { atomicAdd(&dst[n], s_red[i]); atomicAdd(&dst[g.K + n], s_red[BN + i]); }
+      if (n < g.K) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.K + n], s_red[BN + i]); }
     }
   }
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);

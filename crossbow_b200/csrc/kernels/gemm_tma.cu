@@ -51,28 +51,24 @@ struct GemmArgs {
   // TN over a sub-sampled B (weight gradient of a stride-2 1x1 convolution): one reduction block = rpb output rows of Q
   // positions (ppb = rpb * Q <= 32); rows ppb..31 of every stage stay zero.  0 = 32 consecutive positions per block.
   int rpb, ppb;
-  // NT / CONV: a CTA computes `mt` (1 or 2) consecutive M tiles against the same B tile, halving the weight traffic per
-  // output; `tiles` = number of M tiles, `tmem_cols` = power of two >= mt * BN
-  int mt, tiles, tmem_cols;
 };
 
 template <int BN, int MODE>
 __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                                       float* __restrict__ D, const float* __restrict__ bias, float* __restrict__ stats,
                                                       GemmArgs g, int flags, int* status, XbBnFuse bn) {
-  constexpr uint32_t B_BYTES = BN * 128;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
   constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (MODE == 1 ? (3u << 15) : 0u) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], accum_bar;
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ float s_red[2 * BN];
-  __shared__ long long s_rowoff[8][32];                  // per epilogue warp: float offset of every tile row in D, -1 for rows that do not exist
+  __shared__ long long s_rowoff[4][32];                  // float offset of every tile row in D, -1 for rows that do not exist
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mt = MODE == 1 ? 1 : g.mt;
-  const int tile = blockIdx.x * mt, n0 = blockIdx.y * BN;     // first M tile of this CTA
-  const uint32_t STAGE = (uint32_t)mt * A_BYTES + B_BYTES, TMEM_COLS = (uint32_t)g.tmem_cols;
+  const int tile = blockIdx.x, n0 = blockIdx.y * BN;
   const int stages = g.stages;
   const uint32_t base = smem_u32(smem);
   int kb0 = 0, kb1 = g.kblocks;
@@ -105,20 +101,17 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
         for (int i = 0; i < nkb; ++i) {
           const int s = i % stages, kb = kb0 + i;
           if (i >= stages && !mbar_wait(&empty_bar[s], (uint32_t)((i / stages) - 1) & 1u)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); break; }
-          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + (uint32_t)mt * A_BYTES;
+          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + A_BYTES;
           if (MODE == 0) {
-            mbar_expect_tx(&full_bar[s], (uint32_t)(mt * g.a_bytes) + B_BYTES);
-            for (int t = 0; t < mt; ++t)                       // (tiles past the end read zeros)
-              tma_load_3d(sa + t * A_BYTES, &tmA, kb * 32, (tile + t) * g.c1_step, (tile + t) * g.c2_step, &full_bar[s]);
+            mbar_expect_tx(&full_bar[s], (uint32_t)g.a_bytes + B_BYTES);
+            tma_load_3d(sa, &tmA, kb * 32, tile * g.c1_step, tile * g.c2_step, &full_bar[s]);
             tma_load_2d(sb, &tmB, kb * 32, n0, &full_bar[s]);
           } else if (MODE == 2) {
             const int tap = kb / g.c32, cb = kb - tap * g.c32, r = tap / g.S, sx = tap - r * g.S;
+            const int wt = tile % g.tiles_w, t2 = tile / g.tiles_w, ht = t2 % g.tiles_h, nt = t2 / g.tiles_h;
             const int btap = g.mirrored ? g.R * g.S - 1 - tap : tap;
-            mbar_expect_tx(&full_bar[s], (uint32_t)(mt * g.a_bytes) + B_BYTES);
-            for (int t = 0; t < mt; ++t) {
-              const int tl = tile + t, wt = tl % g.tiles_w, t2 = tl / g.tiles_w, ht = t2 % g.tiles_h, nt = t2 / g.tiles_h;
-              tma_load_4d(sa + t * A_BYTES, &tmA, cb * 32, wt * g.bw + sx - g.pw, ht * g.bh + r - g.ph, nt * g.bn, &full_bar[s]);
-            }
+            mbar_expect_tx(&full_bar[s], (uint32_t)g.a_bytes + B_BYTES);
+            tma_load_4d(sa, &tmA, cb * 32, wt * g.bw + sx - g.pw, ht * g.bh + r - g.ph, nt * g.bn, &full_bar[s]);
             tma_load_2d(sb, &tmB, btap * g.krow + cb * 32, n0, &full_bar[s]);
           } else if (g.rpb == 0) {
             mbar_expect_tx(&full_bar[s], STAGE);
@@ -139,20 +132,18 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
           const int s = i % stages;
           if (!mbar_wait(&full_bar[s], (uint32_t)(i / stages) & 1u)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); break; }
           tc_fence_after();
-          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + (uint32_t)mt * A_BYTES;
+          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + A_BYTES;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
+            uint64_t ad, bd;
             if (MODE != 1) {
-              const uint64_t bd = make_desc(sb + kk * 32, 16, 1024) | LAYOUT_SW128;
-              for (int t = 0; t < mt; ++t) {
-                const uint64_t ad = make_desc(sa + t * A_BYTES + kk * 32, 16, 1024) | LAYOUT_SW128;
-                umma_tf32(tmem + (uint32_t)(t * BN), ad, bd, IDESC, (i | kk) ? 1u : 0u);
-              }
+              ad = make_desc(sa + kk * 32, 16, 1024) | LAYOUT_SW128;
+              bd = make_desc(sb + kk * 32, 16, 1024) | LAYOUT_SW128;
             } else {
-              const uint64_t ad = make_desc(sa + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
-              const uint64_t bd = make_desc(sb + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
-              umma_tf32(tmem, ad, bd, IDESC, (i | kk) ? 1u : 0u);
+              ad = make_desc(sa + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
+              bd = make_desc(sb + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
             }
+            umma_tf32(tmem, ad, bd, IDESC, (i | kk) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);
         }
@@ -167,20 +158,17 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
       const int q = warp & 3, half = (warp - 2) >> 2, row = q * 32 + lane;
       if (done && !s_abort) {
         if (MODE != 1) {
-         for (int t = 0; t < mt; ++t) {
-          const int tl = tile + t;
-          if (tl >= g.tiles) break;                        // (same for the whole CTA)
           long long m;
           bool ok;
           if (MODE == 0) {
-            m = (long long)tl * g.mvalid + row;
+            m = (long long)tile * g.mvalid + row;
             ok = row < g.mvalid && m < g.M;
             if (g.oQ && ok) {
               const int q = (int)(m % g.oQ); const long long t = m / g.oQ; const int pp = (int)(t % g.oP); const long long n = t / g.oP;
               m = (n * g.oH + 2 * pp) * g.oW + 2 * q;
             }
           } else {
-            const int wt = tl % g.tiles_w, t2 = tl / g.tiles_w, ht = t2 % g.tiles_h, nt = t2 / g.tiles_h;
+            const int wt = tile % g.tiles_w, t2 = tile / g.tiles_w, ht = t2 % g.tiles_h, nt = t2 / g.tiles_h;
             const int wo = row % g.bw, t3 = row / g.bw, ho = t3 % g.bh, no = t3 / g.bh;
             const int w = wt * g.bw + wo, h = ht * g.bh + ho, n = nt * g.bn + no;
             ok = no < g.bn && w < g.W && h < g.H && n < g.NI;
@@ -191,8 +179,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
           // row, an instruction writes four full lines, and the batch-norm sums need two shuffles per column group.
           // (the pipeline stages are idle by now - every load has landed and every MMA has completed - and serve as the buffer)
           float (*tb)[33] = reinterpret_cast<float (*)[33]>(smem + (size_t)(warp - 2) * 32 * 33 * sizeof(float));
-          long long* rowoff = s_rowoff[warp - 2];
-          rowoff[lane] = ok ? m * g.ldd : -1ll;
+          s_rowoff[q][lane] = ok ? m * g.ldd : -1ll;
           __syncwarp();
           const int cq = (lane & 7) * 4, rsub = lane >> 3;
 #pragma unroll 1
@@ -200,10 +187,10 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
             if (n0 + c0 >= g.N) break;                     // whole-warp condition
             {
               float v[16];
-              tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * BN + c0), v);
+              tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
               for (int j = 0; j < 16; ++j) tb[lane][j] = v[j];
-              tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * BN + c0 + 16), v);
+              tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(c0 + 16), v);
 #pragma unroll
               for (int j = 0; j < 16; ++j) tb[lane][16 + j] = v[j];
             }
@@ -216,7 +203,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int r = i * 4 + rsub;
-              const long long off = rowoff[r];
+              const long long off = s_rowoff[q][r];
               if (off >= 0 && ncol) {
                 float x[4];
 #pragma unroll
@@ -256,7 +243,6 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
             }
             __syncwarp();
           }
-         }
         } else {
           const int m = tile * 128 + row;
 #pragma unroll 1
@@ -279,8 +265,7 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
   if (MODE != 1 && (flags & (G_STATS | G_BNBWD)) && !s_abort) {
     for (int i = tid; i < BN; i += GT) {
       const int n = n0 + i;
-      float* dst = (flags & G_BNBWD) ? stats : stats + (size_t)(blockIdx.x % XB_STATS_COPIES) * 2 * g.N;
-      if (n < g.N) { atomicAdd(&dst[n], s_red[i]); atomicAdd(&dst[g.N + n], s_red[BN + i]); }
+      if (n < g.N) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.N + n], s_red[BN + i]); }
     }
   }
   if (warp == 1) tmem_dealloc(tmem, TMEM_COLS);
@@ -311,21 +296,20 @@ int make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims,
 }
 
 constexpr size_t kSmemLimit = 200 * 1024;
-inline size_t stage_bytes(int BN, int mt = 1) { return (size_t)mt * A_BYTES + (size_t)BN * 128; }
+inline size_t stage_bytes(int BN) { return A_BYTES + (size_t)BN * 128; }
 // Pipeline depth: as deep as the reduction, within a shared-memory budget that still lets two CTAs share an SM when the
 // grid has more CTAs than SMs (the second CTA's loads and MMAs then overlap the first one's epilogue).
-inline int pick_stages(int kblocks, int BN, long long ctas, int mt = 1) {
+inline int pick_stages(int kblocks, int BN, long long ctas) {
   const size_t budget = ctas > 148 ? 108 * 1024 : kSmemLimit;
   int s = kblocks < MAX_STAGES ? kblocks : MAX_STAGES;
-  while (s > 2 && (size_t)s * stage_bytes(BN, mt) > budget) --s;
-  while (s > 1 && (size_t)s * stage_bytes(BN, mt) > kSmemLimit) --s;
+  while (s > 2 && (size_t)s * stage_bytes(BN) > budget) --s;
   return s;
 }
 
 template <int BN, int MODE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags, int* status,
            cudaStream_t st, const XbBnFuse& bn) {
-  size_t smem = (size_t)g.stages * stage_bytes(BN, MODE == 1 ? 1 : g.mt);
+  size_t smem = (size_t)g.stages * stage_bytes(BN);
   if (smem < (size_t)EPI_BYTES) smem = EPI_BYTES;          // the idle stages double as the epilogue's transpose blocks
   gemm_tma_kernel<BN, MODE><<<grid, GT, smem, st>>>(a, b, D, bias, stats, g, flags, status, bn);
   return (int)cudaGetLastError();
@@ -340,15 +324,6 @@ int launch_bn(int BN, const CUtensorMap& a, const CUtensorMap& b, float* D, cons
     default: return launch<256, MODE>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
   }
 }
-// M tiles per CTA: two when the reduction is long enough for the mainloop to matter and enough CTAs remain to fill the GPU.
-static int g_gemm_mt = 0;                                // 0 = choose, 1 / 2 = forced (A/B comparisons)
-inline int choose_mt(int tiles_m, int tiles_n, int kblocks, int BN) {
-  if (g_gemm_mt) return (g_gemm_mt == 2 && 2 * BN <= 512 && tiles_m >= 2) ? 2 : 1;
-  if (2 * BN > 512 || tiles_m < 2 || kblocks < 8) return 1;
-  return ((long long)((tiles_m + 1) / 2) * tiles_n >= 96) ? 2 : 1;
-}
-inline int tmem_cols_for(int n) { int c = 32; while (c < n) c <<= 1; return c; }
-
 template <int BN, int MODE>
 int configure() { return (int)cudaFuncSetAttribute(gemm_tma_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit); }
 
@@ -357,7 +332,6 @@ inline bool is_1x1(const XbConvGeom* g) { return g->R == 1 && g->S == 1 && g->ph
 
 }  // namespace
 
-XB_API void xb_gemm_set_mt(int mt) { g_gemm_mt = mt; }
 XB_API int xb_gemm_tma_init() {
   int e;
   if (!encode_fn()) return 0;                            // no driver entry point: the callers keep to the gather kernels
@@ -428,12 +402,8 @@ XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, f
     if (make_map(&tb, Wb, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
   }
   g.N = Nout; g.kblocks = (Kred + 31) / 32; g.ldd = Nout;
-  const int tiles_n = (Nout + BN - 1) / BN;
-  g.tiles = tiles_m;
-  g.mt = choose_mt(tiles_m, tiles_n, g.kblocks, BN);
-  g.tmem_cols = tmem_cols_for(g.mt * BN);
-  dim3 grid((unsigned)((tiles_m + g.mt - 1) / g.mt), (unsigned)tiles_n, 1);
-  g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y, g.mt);
+  dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
+  g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y);
   return launch_bn<0>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st, bn);
 }
 
@@ -472,7 +442,6 @@ XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, cons
   splits = (g.kblocks + g.kb_per_split - 1) / g.kb_per_split;
   dim3 grid((unsigned)((cg->K + 127) / 128), (unsigned)((cg->C + BN - 1) / BN), (unsigned)splits);
   g.stages = pick_stages(g.kb_per_split, BN, (long long)grid.x * grid.y * grid.z);
-  g.mt = 1; g.tiles = (int)grid.x; g.tmem_cols = tmem_cols_for(BN);
   return launch_bn<1>(BN, ta, tb, dW, nullptr, nullptr, g, grid, 0, status, st);
 }
 
@@ -521,11 +490,7 @@ XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, floa
     const cuuint32_t box[2] = {32, (cuuint32_t)BN};
     if (make_map(&tb, Wb, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
   }
-  const int tiles_n = (Nout + BN - 1) / BN;
-  g.tiles = tiles_m;
-  g.mt = choose_mt(tiles_m, tiles_n, g.kblocks, BN);
-  g.tmem_cols = tmem_cols_for(g.mt * BN);
-  dim3 grid((unsigned)((tiles_m + g.mt - 1) / g.mt), (unsigned)tiles_n, 1);
-  g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y, g.mt);
+  dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
+  g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y);
   return launch_bn<2>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st, bn);
 }

@@ -220,9 +220,8 @@ igemm_gather_kernel(const float* __restrict__ A, const float* __restrict__ Bw, c
     for (int i = tid; i < BN; i += NT) {
       int n = n0 + i;
       if (n < g.NG) {
-        float* dst = stats + (size_t)(blockIdx.x % XB_STATS_COPIES) * 2 * g.NG;
-        atomicAdd(&dst[n], red[i]);
-        atomicAdd(&dst[g.NG + n], red[BN + i]);
+        atomicAdd(&stats[n], red[i]);
+        atomicAdd(&stats[g.NG + n], red[BN + i]);
       }
     }
   }

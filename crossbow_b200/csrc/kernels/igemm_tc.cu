@@ -214,8 +214,7 @@ __global__ void __launch_bounds__(NTHREADS) igemm_tc_kernel(const float* __restr
   if ((flags & F_STATS) && !abort_all) {
     for (int i = tid; i < BN; i += NTHREADS) {
       int n = n0 + i;
-      float* dst = stats + (size_t)(blockIdx.x % XB_STATS_COPIES) * 2 * g.NG;
-      if (n < g.NG) { atomicAdd(&dst[n], s_red[i]); atomicAdd(&dst[g.NG + n], s_red[BN + i]); }
+      if (n < g.NG) { atomicAdd(&stats[n], s_red[i]); atomicAdd(&stats[g.NG + n], s_red[BN + i]); }
     }
   }
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);

@@ -158,8 +158,7 @@ class Lowering:
         self.labels = self.arena.alloc(full_batch, dtype=torch.int32)
         self.tensors: Dict[int, T] = {}     # id(node) -> output tensor
         bn_channels = sum(n.op.output_shape.dims[1] for n in graph.order if n.op.kernel.kind == "batchnorm")
-        self.stats_copies = int(L.load().xb_stats_copies())                  # forward sums are spread over this many copies
-        self.zero_region = self.arena.alloc((2 * self.stats_copies + 2) * bn_channels + 64, zero=True)   # per-task accumulators, one memset
+        self.zero_region = self.arena.alloc(4 * bn_channels + 64, zero=True)   # per-task accumulators, cleared by one memset
         self.zero_used = 0
         self.x_in: Optional[T] = None
         self.node_info: Dict[int, dict] = {}
@@ -418,7 +417,7 @@ class Lowering:
             # does a BN take its statistics from this convolution?
             for m in self.fwd:
                 if self.node_info[id(m)].get("stats_from") is n:
-                    stats = self.scratch_zeroed(2 * K * self.stats_copies)
+                    stats = self.scratch_zeroed(2 * K)
                     self.node_info[id(m)]["stats_buf"] = stats
                     flags |= L.F_STATS
             info["geom"] = geom
@@ -430,7 +429,7 @@ class Lowering:
             return
         if kind == "batchnorm":
             if info["stats_from"] is None and self.training:
-                info["stats_buf"] = self.scratch_zeroed(2 * x.c * self.stats_copies)
+                info["stats_buf"] = self.scratch_zeroed(2 * x.c)
                 self.emit(_op(L.OP_BN_STATS, ia=[x.rows, x.c], p=[x.buf, info["stats_buf"]]))
             if info["deferred"]:
                 self.tensors[id(n)] = None   # materialised by the sum node

@@ -85,7 +85,7 @@ def bench_conv(lib, timer, op, impl, shape, iters, flags=0):
     dy = torch.randn(N, P, Q, K, device=dev)
     dx = torch.empty_like(x)
     dw = torch.zeros_like(w)
-    stats = torch.zeros(2 * K * lib.xb_stats_copies(), device=dev)
+    stats = torch.zeros(2 * K, device=dev)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     s = torch.cuda.current_stream().cuda_stream
     gp = C.byref(g)
@@ -120,7 +120,7 @@ def bench_conv(lib, timer, op, impl, shape, iters, flags=0):
 def bench_bn(lib, timer, op, M, Cc, iters):
     dev = "cuda"
     x, y, dy, dx = (torch.randn(M, Cc, device=dev) for _ in range(4))
-    sums, dsums = torch.zeros(2 * Cc * lib.xb_stats_copies(), device=dev), torch.zeros(2 * Cc, device=dev)
+    sums, dsums = torch.zeros(2 * Cc, device=dev), torch.zeros(2 * Cc, device=dev)
     gamma, beta, rm, rv, sm, si = torch.ones(Cc, device=dev), torch.zeros(Cc, device=dev), torch.zeros(Cc, device=dev), \
         torch.ones(Cc, device=dev), torch.zeros(Cc, device=dev), torch.ones(Cc, device=dev)
     dg, db = torch.zeros(Cc, device=dev), torch.zeros(Cc, device=dev)
