@@ -74,7 +74,7 @@ class ClockSampler(threading.Thread):
 
 
 def reference_arm(args):
-    # The reference is a Java/Maven + CUDA 8 / cuDNN 6 project: `pip install /root/reference` finds neither setup.py
+    # The reference is a Java/Maven + CUDA 8 / cuDNN 6 project: `pip install <reference tree>` finds neither setup.py
     # nor pyproject.toml, there is no JVM on the image and its native code uses cuDNN APIs removed in cuDNN 8.
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a Java/Maven project (no setup.py/pyproject.toml; pip install fails), no JVM on the "
