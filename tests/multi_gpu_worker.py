@@ -27,6 +27,11 @@ def main():
         ws2, ps2, z2, zl2 = [w.clone() for w in ws], [p.clone() for p in ps], z.clone(), zl.clone()
         fs = FusedSynchroniser(n, rank, world, two_shot=two_shot, timeout_s=10.0)
         rs = ReferenceSynchroniser(n, rank, world)
+        if fs.owner_apply and n != 4096 * 9:
+            # owner-apply: the central model lives in the synchroniser's peer-visible buffer, chunk owners store the new
+            # model into every rank's copy and keep the momentum of their chunks
+            z = fs.central_storage()
+            z.zero_()
         for it in range(3):
             fs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9)
             rs.synchronise(s, ALGO_SMA, ws2, ps2, z2, zl2, alpha=0.1, mu=0.9)
@@ -37,8 +42,9 @@ def main():
                 assert torch.allclose(a, b, rtol=1e-4, atol=1e-7)
             # all ranks hold bit-identical central models
             zs = [torch.empty_like(z) for _ in range(world)]
-            dist.all_gather(zs, z)
+            dist.all_gather(zs, z.clone())
             assert all(torch.equal(zs[0], t) for t in zs)
+            assert torch.allclose(fs.gather_momentum(zl), zl2, rtol=1e-4, atol=1e-7)
         # S-SGD
         gacc, gacc2 = torch.randn(n, device="cuda", generator=g) * 0.01, None
         gacc2 = gacc.clone()
