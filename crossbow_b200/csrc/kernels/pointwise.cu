@@ -307,3 +307,18 @@ XB_API int xb_colsum(const float* a, float* out, int M, int C, cudaStream_t st) 
   colsum_kernel<<<xb_ceil_div(M, rpb), NT, 0, st>>>(a, out, M, C, rpb);
   return (int)cudaGetLastError();
 }
+
+// ---- busy-wait for a number of SM clock cycles (kernels/sleep.cu:4-23; used to measure a pipeline's makespan) --------------
+// Bounded: at most 2^31 cycles (about a second), so a wrong argument cannot park a GPU.
+namespace {
+__global__ void sleep_kernel(long long cycles) {
+  const long long t0 = clock64();
+  while (clock64() - t0 < cycles) { }
+}
+}  // namespace
+XB_API int xb_sleep(long long cycles, cudaStream_t st) {
+  if (cycles < 0) return -XB_BAD_ARG;
+  if (cycles > (1ll << 31)) cycles = 1ll << 31;
+  sleep_kernel<<<1, 1, 0, st>>>(cycles);
+  return (int)cudaGetLastError();
+}

@@ -156,6 +156,18 @@ class InnerProduct(Kernel):
         return F.linear(x, params[0], params[1] if self.conf.bias else None)
 
 
+class MatMul(InnerProduct):
+    """Product of the input with one model variable, no bias (the reference's test kernel, matmul.cu:3-35): an inner
+    product whose configuration has the bias switched off."""
+
+    def setup(self, ins, model, label_shape):
+        self.conf.bias = False
+        return super().setup(ins, model, label_shape)
+
+
+class MatMulGradient(GradientKernel): pass
+
+
 def pool_output_size(size, k, s, p):
     """Caffe ceil-mode extent with the clip that keeps the last window inside image+padding (Pool.java:159-175)."""
     o = int(math.ceil((size + 2 * p - k) / s)) + 1

@@ -91,6 +91,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_tc_init", I)
     _sig(lib, "xb_tc_set_slab", None, I)
     _sig(lib, "xb_tc_set_tma", None, I)
+    _sig(lib, "xb_sleep", I, C.c_longlong, P)
     _sig(lib, "xb_tc_set_tma_conv_min", None, I)
     _sig(lib, "xb_conv_tma_supported", I, G, I)
     _sig(lib, "xb_conv_im2col_wanted", C.c_longlong, G, I)

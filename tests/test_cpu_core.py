@@ -340,3 +340,18 @@ def test_batch_splits_equal_consecutive_sub_batch_tasks():
             lb.append(b.wait(0)[0])
         assert la == pytest.approx(sum(lb) / 2, rel=1e-6)
     assert np.allclose(a.replica_model(0), b.replica_model(0), rtol=1e-6, atol=1e-7)
+
+
+def test_matmul_is_an_inner_product_without_bias():
+    from crossbow_b200.conf import InnerProductConf
+    from crossbow_b200.kernels import MatMul
+    m = Model()
+    k = MatMul(InnerProductConf().setNumberOfOutputs(5))
+    node = DataflowNode(Operator("MatMul", k))
+    g = SubGraph(node)
+    g.init(Shape([3, 7]), Shape([3]), m)
+    m.finalise()
+    assert [v.name for v in k.variables] == ["weights"] and m.elements == 35
+    w = torch.from_numpy(m.initial_values(1)).reshape(5, 7)
+    x = torch.randn(3, 7)
+    assert torch.allclose(k.forward([x], [w], None), x @ w.t())

@@ -93,6 +93,21 @@ def test_reuse_memory_same_results_less_memory():
     assert sizes[1] < 0.8 * sizes[0], sizes
 
 
+def test_sleep_kernel_waits_roughly_the_requested_cycles():
+    from crossbow_b200.ops import lib as L
+    lib = L.init_device()
+    s = torch.cuda.current_stream()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    L.check(lib.xb_sleep(1000, s.cuda_stream), "sleep")
+    torch.cuda.synchronize()
+    a.record(s)
+    L.check(lib.xb_sleep(2_000_000, s.cuda_stream), "sleep")      # ~1 ms at ~2 GHz
+    b.record(s)
+    b.synchronize()
+    assert 0.5 < a.elapsed_time(b) < 5.0
+    assert lib.xb_sleep(-1, s.cuda_stream) != 0
+
+
 def test_batch_splits():
     """--splits 2: every task runs the graph (optimiser included) over two consecutive sub-batches."""
     run_both("convnet", 8, 2, 4, splits=2)
