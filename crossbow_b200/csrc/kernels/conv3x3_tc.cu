@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(WG_THREADS) conv3x3_wgrad_mn_kernel(const floa
   const int xq = (g.C - c0 >= 32 ? 32 : g.C - c0) >> 2;  // valid 16-byte chunks per slab row
   const uint32_t xbytes = (uint32_t)S * 128u, stage_bytes = xbytes + NP * yplane;
   const uint32_t base_u32 = smem_u32(smem);
-  if (tid == 0) { mbar_init(&bar_free[0], 1); mbar_init(&bar_free[1], 1); s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+  if (tid == 0) { mbar_init(&bar_free[0], 3); mbar_init(&bar_free[1], 3); s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
   if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -279,20 +279,20 @@ __global__ void __launch_bounds__(WG_THREADS) conv3x3_wgrad_mn_kernel(const floa
   };
   // Called by all threads after the loads of iteration `it` have landed (and a __syncthreads): one lane issues the MMAs.
   auto issue_tile = [&](int it, bool alive) {
-    if (warp == 0) {
+    // The three filter rows accumulate into three independent TMEM regions, and THREE threads (lane 0 of warps 0..2) issue
+    // them: one thread sustains only about one tcgen05.mma per 70 cycles, far below what the tensor pipe needs for these
+    // small-N products, and issue streams of different threads overlap.  Each thread commits its own MMAs; the stage
+    // barrier counts three arrivals.
+    if (warp < 3) {
       if (lane == 0 && alive) {
         tc_fence_after();
         const uint32_t sbase = base_u32 + (uint32_t)(it & 1) * stage_bytes;
-        // The three filter rows accumulate into three independent TMEM regions; issuing them round-robin keeps
-        // consecutive MMAs independent (back-to-back MMAs on ONE accumulator serialise on its read-modify-write).
-#pragma unroll 2
+        const int r = warp;
+#pragma unroll 4
         for (int j = 0; j < BM / 8; ++j) {
           const uint64_t bd = make_desc(sbase + xbytes + (uint32_t)j * 1024u, yplane, 512) | LAYOUT;
-#pragma unroll
-          for (int r = 0; r < 3; ++r) {
-            const uint64_t ad = make_desc(sbase + (uint32_t)(r * PW) * 128u + (uint32_t)j * 1024u, 128, 512) | LAYOUT;
-            umma_tf32(tmem + (uint32_t)(r * NK), ad, bd, IDESC, (it == 0 && j == 0) ? 0u : 1u);
-          }
+          const uint64_t ad = make_desc(sbase + (uint32_t)(r * PW) * 128u + (uint32_t)j * 1024u, 128, 512) | LAYOUT;
+          umma_tf32(tmem + (uint32_t)(r * NK), ad, bd, IDESC, (it == 0 && j == 0) ? 0u : 1u);
         }
         umma_commit(&bar_free[it & 1]);
       }
