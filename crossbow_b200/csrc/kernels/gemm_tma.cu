@@ -19,6 +19,8 @@
 //       both operands MN-major in the "128-byte swizzle, 32-byte atom" layout - the one layout tcgen05 reads 32-bit
 //       MN-major data from - written by TMA with the matching swizzle mode; 32 positions per stage; the position range is
 //       split over gridDim.z and every CTA adds its partial product to D with vector reductions.
+// A pipeline stage holds KC (1, 2 or 4) consecutive 32-float reduction blocks: the issuing thread pays a fixed ~500 cycles per
+// stage for the barrier round trip (wait full, commit empty) whatever the tile, so narrow tiles want many MMAs per stage.
 // Every wait is bounded; on expiry the CTA records XB_TIMEOUT_MBAR in *status, drains and exits.
 #include <cuda.h>
 #include "common.cuh"
@@ -51,14 +53,15 @@ struct GemmArgs {
   // TN over a sub-sampled B (weight gradient of a stride-2 1x1 convolution): one reduction block = rpb output rows of Q
   // positions (ppb = rpb * Q <= 32); rows ppb..31 of every stage stay zero.  0 = 32 consecutive positions per block.
   int rpb, ppb;
+  int kc;              // NT / CONV: 32-float reduction blocks per pipeline stage (1, 2 or 4); kblocks counts stages' worth
 };
 
-template <int BN, int MODE>
+template <int BN, int MODE, int KC>
 __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                                       float* __restrict__ D, const float* __restrict__ bias, float* __restrict__ stats,
                                                       GemmArgs g, int flags, int* status, XbBnFuse bn) {
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
-  constexpr uint32_t B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
+  constexpr uint32_t B_BYTES = BN * 128, STAGE = KC * (A_BYTES + B_BYTES);   // stage = [A sub-blocks][B sub-blocks]
   constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (MODE == 1 ? (3u << 15) : 0u) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], accum_bar;
@@ -101,18 +104,25 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
         for (int i = 0; i < nkb; ++i) {
           const int s = i % stages, kb = kb0 + i;
           if (i >= stages && !mbar_wait(&empty_bar[s], (uint32_t)((i / stages) - 1) & 1u)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); break; }
-          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + A_BYTES;
+          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + KC * A_BYTES;
           if (MODE == 0) {
-            mbar_expect_tx(&full_bar[s], (uint32_t)g.a_bytes + B_BYTES);
-            tma_load_3d(sa, &tmA, kb * 32, tile * g.c1_step, tile * g.c2_step, &full_bar[s]);
-            tma_load_2d(sb, &tmB, kb * 32, n0, &full_bar[s]);
+            mbar_expect_tx(&full_bar[s], KC * ((uint32_t)g.a_bytes + B_BYTES));
+#pragma unroll
+            for (int u = 0; u < KC; ++u) {
+              tma_load_3d(sa + u * A_BYTES, &tmA, (kb * KC + u) * 32, tile * g.c1_step, tile * g.c2_step, &full_bar[s]);
+              tma_load_2d(sb + u * B_BYTES, &tmB, (kb * KC + u) * 32, n0, &full_bar[s]);
+            }
           } else if (MODE == 2) {
-            const int tap = kb / g.c32, cb = kb - tap * g.c32, r = tap / g.S, sx = tap - r * g.S;
+            // step kb covers KC consecutive channel blocks of one tap (KC divides the channel blocks per tap)
+            const int per_tap = g.c32 / KC, tap = kb / per_tap, cb0 = (kb - tap * per_tap) * KC, r = tap / g.S, sx = tap - r * g.S;
             const int wt = tile % g.tiles_w, t2 = tile / g.tiles_w, ht = t2 % g.tiles_h, nt = t2 / g.tiles_h;
             const int btap = g.mirrored ? g.R * g.S - 1 - tap : tap;
-            mbar_expect_tx(&full_bar[s], (uint32_t)g.a_bytes + B_BYTES);
-            tma_load_4d(sa, &tmA, cb * 32, wt * g.bw + sx - g.pw, ht * g.bh + r - g.ph, nt * g.bn, &full_bar[s]);
-            tma_load_2d(sb, &tmB, btap * g.krow + cb * 32, n0, &full_bar[s]);
+            mbar_expect_tx(&full_bar[s], KC * ((uint32_t)g.a_bytes + B_BYTES));
+#pragma unroll
+            for (int u = 0; u < KC; ++u) {
+              tma_load_4d(sa + u * A_BYTES, &tmA, (cb0 + u) * 32, wt * g.bw + sx - g.pw, ht * g.bh + r - g.ph, nt * g.bn, &full_bar[s]);
+              tma_load_2d(sb + u * B_BYTES, &tmB, btap * g.krow + (cb0 + u) * 32, n0, &full_bar[s]);
+            }
           } else if (g.rpb == 0) {
             mbar_expect_tx(&full_bar[s], STAGE);
             tma_load_3d(sa, &tmA, 0, kb * 32, tile * 4, &full_bar[s]);
@@ -132,18 +142,23 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
           const int s = i % stages;
           if (!mbar_wait(&full_bar[s], (uint32_t)(i / stages) & 1u)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); break; }
           tc_fence_after();
-          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + A_BYTES;
+          const uint32_t sa = base + (uint32_t)s * STAGE, sb = sa + KC * A_BYTES;
+          if (MODE != 1) {
+            // descriptors differ only in their 14-bit start-address field (bytes >> 4): one add per MMA
+            const uint64_t ad0 = make_desc(sa, 16, 1024) | LAYOUT_SW128, bd0 = make_desc(sb, 16, 1024) | LAYOUT_SW128;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            uint64_t ad, bd;
-            if (MODE != 1) {
-              ad = make_desc(sa + kk * 32, 16, 1024) | LAYOUT_SW128;
-              bd = make_desc(sb + kk * 32, 16, 1024) | LAYOUT_SW128;
-            } else {
-              ad = make_desc(sa + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
-              bd = make_desc(sb + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
+            for (int u = 0; u < KC; ++u)
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                umma_tf32(tmem, ad0 + (uint64_t)((u * A_BYTES + kk * 32) >> 4), bd0 + (uint64_t)((u * B_BYTES + kk * 32) >> 4), IDESC,
+                          (i | u | kk) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const uint64_t ad = make_desc(sa + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
+              const uint64_t bd = make_desc(sb + kk * 1024, 4096, 512) | LAYOUT_SW128_BASE32;
+              umma_tf32(tmem, ad, bd, IDESC, (i | kk) ? 1u : 0u);
             }
-            umma_tf32(tmem, ad, bd, IDESC, (i | kk) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);
         }
@@ -296,23 +311,38 @@ int make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims,
 }
 
 constexpr size_t kSmemLimit = 200 * 1024;
-inline size_t stage_bytes(int BN) { return A_BYTES + (size_t)BN * 128; }
+inline size_t stage_bytes(int BN, int kc = 1) { return (size_t)kc * (A_BYTES + (size_t)BN * 128); }
 // Pipeline depth: as deep as the reduction, within a shared-memory budget that still lets two CTAs share an SM when the
 // grid has more CTAs than SMs (the second CTA's loads and MMAs then overlap the first one's epilogue).
-inline int pick_stages(int kblocks, int BN, long long ctas) {
+inline int pick_stages(int steps, int BN, long long ctas, int kc = 1) {
   const size_t budget = ctas > 148 ? 108 * 1024 : kSmemLimit;
-  int s = kblocks < MAX_STAGES ? kblocks : MAX_STAGES;
-  while (s > 2 && (size_t)s * stage_bytes(BN) > budget) --s;
+  int s = steps < MAX_STAGES ? steps : MAX_STAGES;
+  while (s > 2 && (size_t)s * stage_bytes(BN, kc) > budget) --s;
   return s;
 }
+// Reduction blocks per stage: as many as divide `blocks` (channel blocks per tap, or k-blocks of a plain GEMM) while at
+// least two stages still fit; wide tiles keep one (their MMAs are long enough to hide the per-stage overhead).
+inline int pick_kc(int blocks, int BN, long long ctas) {
+  const size_t budget = ctas > 148 ? 108 * 1024 : kSmemLimit;     // (same budget as pick_stages: keep two CTAs per SM)
+  for (int kc = 4; kc > 1; kc >>= 1)
+    if (blocks % kc == 0 && 2 * stage_bytes(BN, kc) <= budget && (BN <= 64 || kc <= 2)) return kc;
+  return 1;
+}
 
+template <int BN, int MODE, int KC>
+int launch_kc(const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags, int* status,
+              cudaStream_t st, const XbBnFuse& bn) {
+  size_t smem = (size_t)g.stages * stage_bytes(BN, KC);
+  if (smem < (size_t)EPI_BYTES) smem = EPI_BYTES;          // the idle stages double as the epilogue's transpose blocks
+  gemm_tma_kernel<BN, MODE, KC><<<grid, GT, smem, st>>>(a, b, D, bias, stats, g, flags, status, bn);
+  return (int)cudaGetLastError();
+}
 template <int BN, int MODE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags, int* status,
            cudaStream_t st, const XbBnFuse& bn) {
-  size_t smem = (size_t)g.stages * stage_bytes(BN);
-  if (smem < (size_t)EPI_BYTES) smem = EPI_BYTES;          // the idle stages double as the epilogue's transpose blocks
-  gemm_tma_kernel<BN, MODE><<<grid, GT, smem, st>>>(a, b, D, bias, stats, g, flags, status, bn);
-  return (int)cudaGetLastError();
+  if (MODE != 1 && g.kc == 4) return launch_kc<BN, MODE == 1 ? 0 : MODE, (MODE == 1 || BN > 64) ? 1 : 4>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
+  if (MODE != 1 && g.kc == 2) return launch_kc<BN, MODE == 1 ? 0 : MODE, MODE == 1 ? 1 : 2>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
+  return launch_kc<BN, MODE, 1>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
 }
 template <int MODE>
 int launch_bn(int BN, const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags,
@@ -325,7 +355,15 @@ int launch_bn(int BN, const CUtensorMap& a, const CUtensorMap& b, float* D, cons
   }
 }
 template <int BN, int MODE>
-int configure() { return (int)cudaFuncSetAttribute(gemm_tma_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit); }
+int configure() {
+  int e;
+  if ((e = (int)cudaFuncSetAttribute(gemm_tma_kernel<BN, MODE, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  if (MODE != 1) {
+    if ((e = (int)cudaFuncSetAttribute(gemm_tma_kernel<BN, MODE == 1 ? 0 : MODE, MODE == 1 ? 1 : 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+    if (BN <= 64 && (e = (int)cudaFuncSetAttribute(gemm_tma_kernel<BN, MODE == 1 ? 0 : MODE, (MODE == 1 || BN > 64) ? 1 : 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+  }
+  return 0;
+}
 
 inline bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline bool is_1x1(const XbConvGeom* g) { return g->R == 1 && g->S == 1 && g->ph == 0 && g->pw == 0 && g->sh == g->sw && (g->sh == 1 || g->sh == 2); }
@@ -433,7 +471,7 @@ XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, cons
     if (make_map(&tb, X, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
   }
   GemmArgs g{};
-  g.M = cg->K; g.N = cg->C; g.ldd = cg->C; g.rpb = rpb; g.ppb = ppb;
+  g.M = cg->K; g.N = cg->C; g.ldd = cg->C; g.rpb = rpb; g.ppb = ppb; g.kc = 1;
   g.kblocks = rpb ? (cg->N * cg->P + rpb - 1) / rpb : (int)((P + 31) / 32);
   const int tiles = ((cg->K + 127) / 128) * ((cg->C + BN - 1) / BN);
   int splits = (2 * 148 + tiles - 1) / tiles;
@@ -474,7 +512,6 @@ XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, floa
   g.c32 = Kred / 32; g.mirrored = which; g.krow = Kred;
   g.a_bytes = g.bw * g.bh * g.bn * 128;
   g.M = cg->N * cg->H * cg->W; g.N = Nout; g.ldd = Nout;
-  g.kblocks = cg->R * cg->S * g.c32;
   CUtensorMap ta, tb;
   {
     const cuuint64_t dims[4] = {(cuuint64_t)Kred, (cuuint64_t)cg->W, (cuuint64_t)cg->H, (cuuint64_t)cg->N};
@@ -491,6 +528,8 @@ XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, floa
     if (make_map(&tb, Wb, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
   }
   dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
-  g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y);
+  g.kc = pick_kc(g.c32, BN, (long long)grid.x * grid.y);
+  g.kblocks = cg->R * cg->S * g.c32 / g.kc;              // pipeline steps: (tap, group of kc channel blocks)
+  g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y, g.kc);
   return launch_bn<2>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st, bn);
 }
