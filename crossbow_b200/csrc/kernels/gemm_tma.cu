@@ -201,13 +201,10 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
           for (int c0 = half * 32; c0 < BN; c0 += 64) {
             if (n0 + c0 >= g.N) break;                     // whole-warp condition
             {
-              float v[16];
-              tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+              float v[32];                                 // one 32-column load: one wait instead of two
+              tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
-              for (int j = 0; j < 16; ++j) tb[lane][j] = v[j];
-              tmem_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(c0 + 16), v);
-#pragma unroll
-              for (int j = 0; j < 16; ++j) tb[lane][16 + j] = v[j];
+              for (int j = 0; j < 32; ++j) tb[lane][j] = v[j];
             }
             __syncwarp();
             const int n = n0 + c0 + cq;                    // first of this lane's four columns
