@@ -34,7 +34,7 @@ CONFIGS = {
 class ClockSampler(threading.Thread):
     """Samples SM clock, max clock and throttle reasons through NVML (read-only) while the timed region runs."""
 
-    def __init__(self, index, period=0.1):
+    def __init__(self, index, period=0.02):
         super().__init__(daemon=True)
         self.index, self.period = index, period
         self.samples, self.reasons, self.max_mhz = [], set(), None

@@ -101,6 +101,9 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
   if (nkb > 0) {
     if (warp == 0) {
       if (lane == 0) {
+        // CONV: position of the tile and a running (filter row, filter column, channel block) counter - no divisions in the loop
+        int wt = 0, ht = 0, nt = 0, cr = 0, cs = 0, ccb = 0;
+        if (MODE == 2) { wt = tile % g.tiles_w; const int t2 = tile / g.tiles_w; ht = t2 % g.tiles_h; nt = t2 / g.tiles_h; }
         for (int i = 0; i < nkb; ++i) {
           const int s = i % stages, kb = kb0 + i;
           if (i >= stages && !mbar_wait(&empty_bar[s], (uint32_t)((i / stages) - 1) & 1u)) { s_abort = 1; atomicExch(status, XB_TIMEOUT_MBAR); break; }
@@ -113,15 +116,14 @@ __global__ void __launch_bounds__(GT) gemm_tma_kernel(const __grid_constant__ CU
               tma_load_2d(sb + u * B_BYTES, &tmB, (kb * KC + u) * 32, n0, &full_bar[s]);
             }
           } else if (MODE == 2) {
-            // step kb covers KC consecutive channel blocks of one tap (KC divides the channel blocks per tap)
-            const int per_tap = g.c32 / KC, tap = kb / per_tap, cb0 = (kb - tap * per_tap) * KC, r = tap / g.S, sx = tap - r * g.S;
-            const int wt = tile % g.tiles_w, t2 = tile / g.tiles_w, ht = t2 % g.tiles_h, nt = t2 / g.tiles_h;
-            const int btap = g.mirrored ? g.R * g.S - 1 - tap : tap;
+            // step kb covers KC consecutive (tap, channel block) pairs of the reduction, in tap-major order
             mbar_expect_tx(&full_bar[s], KC * ((uint32_t)g.a_bytes + B_BYTES));
 #pragma unroll
             for (int u = 0; u < KC; ++u) {
-              tma_load_4d(sa + u * A_BYTES, &tmA, (cb0 + u) * 32, wt * g.bw + sx - g.pw, ht * g.bh + r - g.ph, nt * g.bn, &full_bar[s]);
-              tma_load_2d(sb + u * B_BYTES, &tmB, btap * g.krow + (cb0 + u) * 32, n0, &full_bar[s]);
+              const int tap = cr * g.S + cs, btap = g.mirrored ? g.R * g.S - 1 - tap : tap;
+              tma_load_4d(sa + u * A_BYTES, &tmA, ccb * 32, wt * g.bw + cs - g.pw, ht * g.bh + cr - g.ph, nt * g.bn, &full_bar[s]);
+              tma_load_2d(sb + u * B_BYTES, &tmB, btap * g.krow + ccb * 32, n0, &full_bar[s]);
+              if (++ccb == g.c32) { ccb = 0; if (++cs == g.S) { cs = 0; ++cr; } }
             }
           } else if (g.rpb == 0) {
             mbar_expect_tx(&full_bar[s], STAGE);
@@ -321,7 +323,8 @@ inline int pick_stages(int steps, int BN, long long ctas, int kc = 1) {
 // least two stages still fit; wide tiles keep one (their MMAs are long enough to hide the per-stage overhead).
 inline int pick_kc(int blocks, int BN, long long ctas) {
   const size_t budget = ctas > 148 ? 108 * 1024 : kSmemLimit;     // (same budget as pick_stages: keep two CTAs per SM)
-  for (int kc = 4; kc > 1; kc >>= 1)
+  const int order[3] = {4, 2, 3};                        // (3 only where neither 4 nor 2 divides: nine taps of a 32-channel layer)
+  for (int kc : order)
     if (blocks % kc == 0 && 2 * stage_bytes(BN, kc) <= budget && (BN <= 64 || kc <= 2)) return kc;
   return 1;
 }
@@ -338,6 +341,7 @@ template <int BN, int MODE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags, int* status,
            cudaStream_t st, const XbBnFuse& bn) {
   if (MODE != 1 && g.kc == 4) return launch_kc<BN, MODE == 1 ? 0 : MODE, (MODE == 1 || BN > 64) ? 1 : 4>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
+  if (MODE != 1 && g.kc == 3) return launch_kc<BN, MODE == 1 ? 0 : MODE, (MODE == 1 || BN > 64) ? 1 : 3>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
   if (MODE != 1 && g.kc == 2) return launch_kc<BN, MODE == 1 ? 0 : MODE, MODE == 1 ? 1 : 2>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
   return launch_kc<BN, MODE, 1>(a, b, D, bias, stats, g, grid, flags, status, st, bn);
 }
@@ -358,6 +362,7 @@ int configure() {
   if (MODE != 1) {
     if ((e = (int)cudaFuncSetAttribute(gemm_tma_kernel<BN, MODE == 1 ? 0 : MODE, MODE == 1 ? 1 : 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
     if (BN <= 64 && (e = (int)cudaFuncSetAttribute(gemm_tma_kernel<BN, MODE == 1 ? 0 : MODE, (MODE == 1 || BN > 64) ? 1 : 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
+    if (BN <= 64 && (e = (int)cudaFuncSetAttribute(gemm_tma_kernel<BN, MODE == 1 ? 0 : MODE, (MODE == 1 || BN > 64) ? 1 : 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit))) return e;
   }
   return 0;
 }
@@ -525,7 +530,7 @@ XB_API int xb_conv_tma(const float* In, const float* Wb, const float* bias, floa
     if (make_map(&tb, Wb, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -XB_BAD_ARG;
   }
   dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
-  g.kc = pick_kc(g.c32, BN, (long long)grid.x * grid.y);
+  g.kc = pick_kc(cg->R * cg->S * g.c32, BN, (long long)grid.x * grid.y);
   g.kblocks = cg->R * cg->S * g.c32 / g.kc;              // pipeline steps: (tap, group of kc channel blocks)
   g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y, g.kc);
   return launch_bn<2>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st, bn);
