@@ -94,6 +94,8 @@ def main():
     ap.add_argument("--no-tc", action="store_true", help="CUDA-core convolution kernels only")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--sync", default="fused", choices=["fused", "reference"])
+    ap.add_argument("--bn-blocks", type=int, default=0, help="tuning: blocks of the batch-norm normalise / apply kernels")
+    ap.add_argument("--bn-reduce-blocks", type=int, default=0, help="tuning: blocks of the batch-norm reduction kernels")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -137,6 +139,13 @@ def main():
     ds = SyntheticDataset(cfg["shape"], cfg["classes"], batch, batches=ring * world, seed=1234)
     mc.setDataset(Phase.TRAIN, ds)
     spec = build(cfg["build"], solver_conf=solver)
+    if args.bn_blocks or args.bn_reduce_blocks:              # (launch shapes are baked into the task graphs at init)
+        from crossbow_b200.ops import lib as _L
+        _lib = _L.init_device()
+        if args.bn_blocks:
+            _lib.xb_bn_set_stream_blocks(args.bn_blocks)
+        if args.bn_reduce_blocks:
+            _lib.xb_bn_set_reduce_blocks(args.bn_reduce_blocks)
     ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), None], quiet=True)
     ctx.init()
     eng = ctx.engine

@@ -290,7 +290,10 @@ __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
 
 // Reductions end in 2C same-address atomics per block, which serialise in L2: they get fewer, longer blocks.
 static int g_bn_reduce_blocks = 296;
-inline int rows_per_block_for(int M, int C, int vec, int& blocks, int target = 592, int min_steps = 2) {
+static int g_bn_stream_blocks = 592;                   // normalise / apply passes (no atomics): ~4 resident blocks per SM
+inline int rows_per_block_for(int M, int C, int vec, int& blocks, int target = 0, int min_steps = 2) {
+  // small tensors (<= 8 MB) are latency-bound and run better with half as many, longer blocks
+  if (target <= 0) target = ((long long)M * C <= (2ll << 20)) ? g_bn_stream_blocks / 2 : g_bn_stream_blocks;
   Tiling t = make_tiling(C, vec);
   // aim for ~4 resident blocks per SM (592 blocks), at least 2 row-steps per block
   int min_rows = t.rows_per_iter * min_steps;
@@ -339,6 +342,7 @@ XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const
   return (int)cudaGetLastError();
 }
 XB_API void xb_bn_set_reduce_blocks(int n) { g_bn_reduce_blocks = n > 0 ? n : 296; }
+XB_API void xb_bn_set_stream_blocks(int n) { g_bn_stream_blocks = n > 0 ? n : 592; }
 
 // As xb_bn_backward, for a layer whose fused ReLU has no residual input: the mask is re-derived from x, gamma, beta and the
 // saved statistics with the forward pass's own expressions (bit-identical), so the layer's output is not read at all -

@@ -32,7 +32,8 @@ namespace {
 
 constexpr int GT = 320;                                 // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue (two per TMEM lane quadrant)
 // 32-column tiles have one 32-column epilogue block per TMEM lane quadrant: four epilogue warps, not eight
-__host__ __device__ constexpr int gemm_threads(int BN) { return BN <= 32 ? 192 : GT; }
+// (the weight-gradient form deals 16-column blocks to the two warps of a quadrant and always needs both)
+__host__ __device__ constexpr int gemm_threads(int BN, int MODE) { return (BN <= 32 && MODE != 1) ? 192 : GT; }
 constexpr int EPI_BYTES = 8 * 32 * 33 * 4;              // one 32 x 32 transpose block per epilogue warp
 constexpr int MAX_STAGES = 8;
 constexpr int G_RELU = 1, G_ACCUM = 2, G_STATS = 4, G_BNBWD = 8;   // G_BNBWD: `stats` receives batch-norm backward sums (XbBnFuse)
@@ -59,10 +60,10 @@ struct GemmArgs {
 };
 
 template <int BN, int MODE, int KC>
-__global__ void __launch_bounds__(gemm_threads(BN)) gemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+__global__ void __launch_bounds__(gemm_threads(BN, MODE)) gemm_tma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                                       float* __restrict__ D, const float* __restrict__ bias, float* __restrict__ stats,
                                                       GemmArgs g, int flags, int* status, XbBnFuse bn) {
-  constexpr int NTH = gemm_threads(BN);
+  constexpr int NTH = gemm_threads(BN, MODE);
   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
   constexpr uint32_t B_BYTES = BN * 128, STAGE = KC * (A_BYTES + B_BYTES);   // stage = [A sub-blocks][B sub-blocks]
   constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (MODE == 1 ? (3u << 15) : 0u) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -337,7 +338,7 @@ int launch_kc(const CUtensorMap& a, const CUtensorMap& b, float* D, const float*
               cudaStream_t st, const XbBnFuse& bn) {
   size_t smem = (size_t)g.stages * stage_bytes(BN, KC);
   if (smem < (size_t)EPI_BYTES) smem = EPI_BYTES;          // the idle stages double as the epilogue's transpose blocks
-  gemm_tma_kernel<BN, MODE, KC><<<grid, gemm_threads(BN), smem, st>>>(a, b, D, bias, stats, g, flags, status, bn);
+  gemm_tma_kernel<BN, MODE, KC><<<grid, gemm_threads(BN, MODE), smem, st>>>(a, b, D, bias, stats, g, flags, status, bn);
   return (int)cudaGetLastError();
 }
 template <int BN, int MODE>
