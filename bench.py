@@ -96,6 +96,7 @@ def main():
     ap.add_argument("--sync", default="fused", choices=["fused", "reference"])
     ap.add_argument("--bn-blocks", type=int, default=0, help="tuning: blocks of the batch-norm normalise / apply kernels")
     ap.add_argument("--bn-reduce-blocks", type=int, default=0, help="tuning: blocks of the batch-norm reduction kernels")
+    ap.add_argument("--wgrad-ctas", type=int, default=0, help="tuning: CTAs of the 3x3 weight-gradient kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -139,13 +140,15 @@ def main():
     ds = SyntheticDataset(cfg["shape"], cfg["classes"], batch, batches=ring * world, seed=1234)
     mc.setDataset(Phase.TRAIN, ds)
     spec = build(cfg["build"], solver_conf=solver)
-    if args.bn_blocks or args.bn_reduce_blocks:              # (launch shapes are baked into the task graphs at init)
+    if args.bn_blocks or args.bn_reduce_blocks or args.wgrad_ctas:   # (launch shapes are baked into the task graphs at init)
         from crossbow_b200.ops import lib as _L
         _lib = _L.init_device()
         if args.bn_blocks:
             _lib.xb_bn_set_stream_blocks(args.bn_blocks)
         if args.bn_reduce_blocks:
             _lib.xb_bn_set_reduce_blocks(args.bn_reduce_blocks)
+        if args.wgrad_ctas:
+            _lib.xb_conv3x3_wgrad_set_ctas(args.wgrad_ctas)
     ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), None], quiet=True)
     ctx.init()
     eng = ctx.engine
