@@ -97,6 +97,7 @@ def main():
     ap.add_argument("--bn-blocks", type=int, default=0, help="tuning: blocks of the batch-norm normalise / apply kernels")
     ap.add_argument("--bn-reduce-blocks", type=int, default=0, help="tuning: blocks of the batch-norm reduction kernels")
     ap.add_argument("--wgrad-ctas", type=int, default=0, help="tuning: CTAs of the 3x3 weight-gradient kernel")
+    ap.add_argument("--tn-ctas", type=int, default=0, help="tuning: CTAs of the 1x1 weight-gradient GEMM")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -140,7 +141,7 @@ def main():
     ds = SyntheticDataset(cfg["shape"], cfg["classes"], batch, batches=ring * world, seed=1234)
     mc.setDataset(Phase.TRAIN, ds)
     spec = build(cfg["build"], solver_conf=solver)
-    if args.bn_blocks or args.bn_reduce_blocks or args.wgrad_ctas:   # (launch shapes are baked into the task graphs at init)
+    if args.bn_blocks or args.bn_reduce_blocks or args.wgrad_ctas or args.tn_ctas:   # (launch shapes are baked into the task graphs at init)
         from crossbow_b200.ops import lib as _L
         _lib = _L.init_device()
         if args.bn_blocks:
@@ -149,6 +150,8 @@ def main():
             _lib.xb_bn_set_reduce_blocks(args.bn_reduce_blocks)
         if args.wgrad_ctas:
             _lib.xb_conv3x3_wgrad_set_ctas(args.wgrad_ctas)
+        if args.tn_ctas:
+            _lib.xb_gemm_set_tn_ctas(args.tn_ctas)
     ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), None], quiet=True)
     ctx.init()
     eng = ctx.engine

@@ -371,11 +371,13 @@ int configure() {
   return 0;
 }
 
+static int g_tn_ctas = 111;                              // CTAs of a weight-gradient GEMM (output tiles x position slices)
 inline bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 inline bool is_1x1(const XbConvGeom* g) { return g->R == 1 && g->S == 1 && g->ph == 0 && g->pw == 0 && g->sh == g->sw && (g->sh == 1 || g->sh == 2); }
 
 }  // namespace
 
+XB_API void xb_gemm_set_tn_ctas(int n) { g_tn_ctas = n > 0 ? n : 111; }
 XB_API int xb_gemm_tma_init() {
   int e;
   if (!encode_fn()) return 0;                            // no driver entry point: the callers keep to the gather kernels
@@ -480,7 +482,7 @@ XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, cons
   g.M = cg->K; g.N = cg->C; g.ldd = cg->C; g.rpb = rpb; g.ppb = ppb; g.kc = 1;
   g.kblocks = rpb ? (cg->N * cg->P + rpb - 1) / rpb : (int)((P + 31) / 32);
   const int tiles = ((cg->K + 127) / 128) * ((cg->C + BN - 1) / BN);
-  int splits = (2 * 148 + tiles - 1) / tiles;
+  int splits = (g_tn_ctas + tiles - 1) / tiles;
   if (splits > g.kblocks) splits = g.kblocks;
   g.kb_per_split = (g.kblocks + splits - 1) / splits;
   splits = (g.kblocks + g.kb_per_split - 1) / g.kb_per_split;
