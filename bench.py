@@ -94,6 +94,8 @@ def main():
     ap.add_argument("--no-tc", action="store_true", help="CUDA-core convolution kernels only")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--sync", default="fused", choices=["fused", "reference"])
+    ap.add_argument("--update-model", default="sma", choices=["sma", "ssgd"], help="sma (headline) or synchronous SGD")
+    ap.add_argument("--gradient-buckets", type=int, default=0, help="synchronous SGD: buckets overlapping the backward pass (0 = automatic)")
     ap.add_argument("--bn-blocks", type=int, default=0, help="tuning: blocks of the batch-norm normalise / apply kernels")
     ap.add_argument("--bn-reduce-blocks", type=int, default=0, help="tuning: blocks of the batch-norm reduction kernels")
     ap.add_argument("--wgrad-ctas", type=int, default=0, help="tuning: CTAs of the 3x3 weight-gradient kernel")
@@ -136,7 +138,8 @@ def main():
     sysc.fused_sync = args.sync == "fused"
     solver = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.1).setMomentum(0.9) \
         .setWeightDecay(1e-4).setAlpha(0.1)
-    mc.setBatchSize(batch).setWpc(k).setUpdateModel(UpdateModel.SMA)
+    mc.setBatchSize(batch).setWpc(k).setUpdateModel(UpdateModel.SMA if args.update_model == "sma" else UpdateModel.WORKER)
+    sysc.gradient_buckets = args.gradient_buckets
     ring = max(2 * k, 8)
     ds = SyntheticDataset(cfg["shape"], cfg["classes"], batch, batches=ring * world, seed=1234)
     mc.setDataset(Phase.TRAIN, ds)
@@ -220,15 +223,18 @@ def main():
     e2e = images_per_step * args.steps / e2e_s
     launches_per_task = eng.gpu_launches_per_task()
     arena_mb = sum(l.low_train.arena.total for l in eng.learners) / 1e6
+    algo = "SMA" if args.update_model == "sma" else "S-SGD"
+    syncs_per_step = max(1, len(eng.bucket_syncs))
     if rank == 0:
         out = {
-            "metric": f"{args.model} SMA training throughput", "value": round(value, 1), "unit": "images/s",
+            "metric": f"{args.model} {algo} training throughput", "value": round(value, 1), "unit": "images/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms / args.steps, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "tf32 tensor-core tiles, fp32 storage/accumulate" if eng.use_tc else "fp32", "data": "synthetic",
             "impl": "ours",
             "config": {"model": args.model, "global_batch": images_per_step, "batch_per_replica": batch, "replicas_per_gpu": k,
-                       "input": cfg["shape"], "parallelism": f"dp{world} x {k} replicas/GPU, SMA alpha 0.1, wpc = k*G",
+                       "input": cfg["shape"], "parallelism": f"dp{world} x {k} replicas/GPU, " + ("SMA alpha 0.1" if algo == "SMA" else f"synchronous SGD, {syncs_per_step} gradient bucket(s)")
+                                      + ", wpc = k*G",
                        "optimizer": "momentum 0.9, wd 1e-4, lr 0.1", "sync": args.sync,
                        "l2": f"no explicit flush: per-step working set {arena_mb:.0f} MB of activations/gradients exceeds the 126 MB L2"
                              if arena_mb > 252 else f"working set {arena_mb:.0f} MB",
@@ -236,7 +242,7 @@ def main():
             "e2e": {"value": round(e2e, 1), "unit": "images/s", "ms_per_step": round(e2e_s * 1e3 / args.steps, 4),
                     "h2d_bytes_per_step": k * ds.batch_bytes(), "d2h_bytes_per_step": k * 8,
                     "timing": "host wall clock around ExecutionContext.train, synchronised on both sides, max over ranks"},
-            "gpu_launches": args.steps * (k * launches_per_task + 1),
+            "gpu_launches": args.steps * (k * launches_per_task + syncs_per_step),
             "launches_per_task": launches_per_task,
             "clocks": sampler.summary(),
             "final_loss": ctx.last_loss,

@@ -83,7 +83,8 @@ class ExecutionContext:
                                     replicas=sys.number_of_gpu_models, wpc=wpc, rank=self.rank, world=self.world,
                                     device_index=local, use_graphs=sys.use_cuda_graphs, seed=sys.random_seed,
                                     use_tc=sys.use_tensor_cores, fused_sync=sys.fused_sync,
-                                    sync_timeout_s=sys.sync_timeout, splits=mc.splits, reuse_memory=sys.reuse_memory)
+                                    sync_timeout_s=sys.sync_timeout, splits=mc.splits, reuse_memory=sys.reuse_memory,
+                                    gradient_buckets=sys.gradient_buckets)
         else:
             from .engine import CpuEngine
             self.engine = CpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,
@@ -126,6 +127,7 @@ class ExecutionContext:
 
     def _train_native(self, ntasks: int) -> int:
         rt, e = self._native, self.engine
+        e.epoch_to_native()
         chunk = ntasks
         if self.autotuner is not None and self.autotuner.active:
             chunk = max(self.clock.wpc, self.sys.autotune_interval * self.clock.wpc * 4)
@@ -170,6 +172,7 @@ class ExecutionContext:
         self.tasks_done += done
         self.clock.clock = rt.clock()
         self.clock.task = rt.tasks_issued() - 1
+        e.epoch_from_native()
         e.finish()
         return done
 

@@ -55,6 +55,7 @@ enum XbOpKind : int {
   OP_BN_STATS = 7, OP_BN_FWD = 8, OP_BN_BWD = 9, OP_ACT_FWD = 10, OP_ACT_BWD = 11, OP_SUM = 12, OP_DROPOUT = 13,
   OP_CONCAT = 14, OP_POOL_FWD = 15, OP_POOL_BWD = 16, OP_LRN_FWD = 17, OP_LRN_BWD = 18, OP_SOFTMAX_XENT = 19,
   OP_CLASSIFY = 20, OP_TRANSPOSE_W = 21, OP_GRAD_SUMSQ = 22, OP_OPTIMISER = 23, OP_COPY = 24, OP_MATFACT = 25,
+  OP_MARK = 26,   // no launch: end of gradient bucket ia[0] - the learner records that bucket's event here
 };
 
 // One launch. Field meaning depends on `kind` (documented where the Python lowering fills them).
@@ -67,10 +68,17 @@ struct XbOp {
   void* p[12];
 };
 
+constexpr int XB_MAX_BUCKETS = 8;
+
 struct XbProgram {
   std::vector<XbOp> ops;
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
+  // A program with OP_MARK ops is cut there: one graph per segment, so the caller can record an ordinary stream event
+  // between two segments (segs[i] covers ops [seg_first[i], seg_first[i+1]) and ends in mark seg_mark[i], or -1).
+  std::vector<cudaGraphExec_t> segs;
+  std::vector<int> seg_first, seg_mark;
+  int marks = 0;
   int launches = 0;       // kernel launches issued by one replay (for accounting)
   int use_tc = 1;         // allow tensor-core convolution kernels
   int* tc_status = nullptr;
@@ -158,6 +166,7 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
     case OP_MATFACT:
       return xb_matfact((const float*)o.p[0], o.ia[0], (const int*)o.p[1], (const float*)o.p[2], (const float*)o.p[3], (float*)o.p[4], (float*)o.p[5],
                         (float*)o.p[6], o.ia[1], o.ia[2], o.fa[0], o.ia[3], o.ia[4], st);
+    case OP_MARK: return 0;
     case OP_GRAD_SUMSQ: return xb_grad_sumsq((const float*)o.p[0], (float*)o.p[1], o.la[0], st);
     case OP_OPTIMISER:
       return xb_fused_optimiser((float*)o.p[0], (float*)o.p[1], (float*)o.p[2], (float*)o.p[3], (float*)o.p[4], (const float*)o.p[5],
@@ -176,14 +185,20 @@ XB_API XbProgram* xb_program_create(const XbOp* ops, int n, int use_tc, int* tc_
   int l = 0;
   for (int i = 0; i < n; ++i) {
     int k = ops[i].kind;
+    if (k == OP_MARK) { p->marks++; continue; }
     if (k == OP_MEMSET || k == OP_UPLOAD || k == OP_COPY) continue;
     l += (k == OP_BN_BWD) ? 2 : 1;
   }
   p->launches = l;
   return p;
 }
+static void drop_segments(XbProgram* p) {
+  for (cudaGraphExec_t g : p->segs) if (g) cudaGraphExecDestroy(g);
+  p->segs.clear(); p->seg_first.clear(); p->seg_mark.clear();
+}
 XB_API void xb_program_destroy(XbProgram* p) {
   if (!p) return;
+  drop_segments(p);
   if (p->exec) cudaGraphExecDestroy(p->exec);
   if (p->graph) cudaGraphDestroy(p->graph);
   delete p;
@@ -209,7 +224,9 @@ XB_API int xb_program_run_range(XbProgram* p, int first, int last, cudaStream_t 
 }
 
 // Record the program into a CUDA graph (the stream must not be the legacy default stream).
+XB_API int xb_program_capture_segments(XbProgram* p, cudaStream_t st);
 XB_API int xb_program_capture(XbProgram* p, cudaStream_t st) {
+  if (p->marks > 0) return xb_program_capture_segments(p, st);
   if (p->exec) { cudaGraphExecDestroy(p->exec); p->exec = nullptr; }
   if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
   XB_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
@@ -222,15 +239,59 @@ XB_API int xb_program_capture(XbProgram* p, cudaStream_t st) {
   XB_CUDA_CHECK(cudaGraphInstantiate(&p->exec, g, 0));
   return 0;
 }
-XB_API int xb_program_launch(XbProgram* p, cudaStream_t st) {
-  if (p->exec) return (int)cudaGraphLaunch(p->exec, st);
-  return xb_program_run(p, st);
+// The same, cut at the marks: one graph per segment (see XbProgram::segs).
+XB_API int xb_program_capture_segments(XbProgram* p, cudaStream_t st) {
+  drop_segments(p);
+  const int n = (int)p->ops.size();
+  int first = 0;
+  while (first < n) {
+    int last = first, mark = -1;
+    while (last < n && p->ops[last].kind != OP_MARK) ++last;
+    if (last < n) { mark = p->ops[last].ia[0]; ++last; }          // the mark closes the segment
+    XB_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    int e = xb_program_run_range(p, first, last, st);
+    cudaGraph_t g = nullptr;
+    cudaError_t ce = cudaStreamEndCapture(st, &g);
+    if (e != 0 || ce != cudaSuccess) { if (g) cudaGraphDestroy(g); drop_segments(p); return e != 0 ? e : (int)ce; }
+    cudaGraphExec_t ex = nullptr;
+    ce = cudaGraphInstantiate(&ex, g, 0);
+    cudaGraphDestroy(g);
+    if (ce != cudaSuccess) { drop_segments(p); return (int)ce; }
+    p->segs.push_back(ex); p->seg_first.push_back(first); p->seg_mark.push_back(mark);
+    first = last;
+  }
+  return 0;
 }
+XB_API int xb_program_marks(XbProgram* p) { return p->marks; }
+// Replay; `marks[b]` (may be null) is recorded on `st` right after the ops that precede mark b.
+XB_API int xb_program_launch_marked(XbProgram* p, cudaStream_t st, cudaEvent_t* marks, int nmarks) {
+  if (!p->segs.empty()) {
+    for (size_t i = 0; i < p->segs.size(); ++i) {
+      XB_CUDA_CHECK(cudaGraphLaunch(p->segs[i], st));
+      const int m = p->seg_mark[i];
+      if (m >= 0 && m < nmarks && marks && marks[m]) XB_CUDA_CHECK(cudaEventRecord(marks[m], st));
+    }
+    return 0;
+  }
+  if (p->exec && p->marks == 0) return (int)cudaGraphLaunch(p->exec, st);
+  for (size_t i = 0; i < p->ops.size(); ++i) {
+    const XbOp& o = p->ops[i];
+    if (o.kind == OP_MARK) {
+      if (o.ia[0] >= 0 && o.ia[0] < nmarks && marks && marks[o.ia[0]]) XB_CUDA_CHECK(cudaEventRecord(marks[o.ia[0]], st));
+      continue;
+    }
+    int e = run_op(p, o, st);
+    if (e != 0) return (int)(1000 * (i + 1) + (e < 0 ? -e : e));
+  }
+  return 0;
+}
+XB_API int xb_program_launch(XbProgram* p, cudaStream_t st) { return xb_program_launch_marked(p, st, nullptr, 0); }
 
 // ---- learner: stream + staging buffers + programs ------------------------------------------------------------------
 struct XbLearner {
   cudaStream_t stream = nullptr;
   cudaEvent_t done = nullptr, start = nullptr;
+  cudaEvent_t bucket[XB_MAX_BUCKETS] = {};   // gradient bucket b of the last training task is complete (created on demand)
   XbProgram* train = nullptr;
   XbProgram* test = nullptr;
   void* d_examples = nullptr; size_t examples_bytes = 0;
@@ -262,6 +323,7 @@ XB_API void xb_learner_destroy(XbLearner* l) {
   if (!l) return;
   cudaStreamSynchronize(l->stream);
   cudaEventDestroy(l->done); cudaEventDestroy(l->start);
+  for (cudaEvent_t ev : l->bucket) if (ev) cudaEventDestroy(ev);
   cudaFreeHost(l->h_params); cudaFreeHost(l->h_result);
   cudaStreamDestroy(l->stream);
   delete l;
@@ -280,7 +342,10 @@ XB_API int xb_learner_submit(XbLearner* l, const void* h_examples, const void* h
   *l->h_params = *params;
   if (h_examples) XB_CUDA_CHECK(cudaMemcpyAsync(l->d_examples, h_examples, l->examples_bytes, cudaMemcpyHostToDevice, l->stream));
   if (h_labels) XB_CUDA_CHECK(cudaMemcpyAsync(l->d_labels, h_labels, l->labels_bytes, cudaMemcpyHostToDevice, l->stream));
-  int e = xb_program_launch(p, l->stream);
+  if (p->marks > 0)
+    for (int b = 0; b < XB_MAX_BUCKETS && b < p->marks; ++b)
+      if (!l->bucket[b]) XB_CUDA_CHECK(cudaEventCreateWithFlags(&l->bucket[b], cudaEventDisableTiming));
+  int e = xb_program_launch_marked(p, l->stream, l->bucket, XB_MAX_BUCKETS);
   if (e) return e;
   XB_CUDA_CHECK(cudaEventRecord(l->done, l->stream));
   l->busy = 1;
@@ -302,6 +367,12 @@ XB_API int xb_learner_query(XbLearner* l) {
 }
 // Make stream `st` wait for this learner's last task (used by the synchroniser) and vice versa.
 XB_API int xb_stream_wait_learner(cudaStream_t st, XbLearner* l) { return (int)cudaStreamWaitEvent(st, l->done, 0); }
+// `st` waits until gradient bucket b of the learner's last submitted training task is complete (the whole task if the
+// program has no such mark)
+XB_API int xb_stream_wait_learner_bucket(cudaStream_t st, XbLearner* l, int b) {
+  cudaEvent_t ev = (b >= 0 && b < XB_MAX_BUCKETS && l->bucket[b]) ? l->bucket[b] : l->done;
+  return (int)cudaStreamWaitEvent(st, ev, 0);
+}
 XB_API int xb_learner_wait_event(XbLearner* l, cudaEvent_t ev) { return (int)cudaStreamWaitEvent(l->stream, ev, 0); }
 
 // ---- small CUDA plumbing used from Python (keeps torch out of the hot path) -----------------------------------------
@@ -403,6 +474,11 @@ struct XbExec {
   XbSolverState solver;
   unsigned long long seed = 0;
   XbSyncDescMirror tmpl;
+  // Bucketed synchronous SGD: one descriptor per gradient bucket (its own exchange buffers and flags, vector pointers
+  // already moved to the bucket's first element); replica pointers are moved by bucket_off[b] floats.
+  std::vector<XbSyncDescMirror> buckets;
+  std::vector<long long> bucket_off;
+  unsigned int launches = 0;   // picks the pinned staging slot of a launch
   int update_mode = 0;         // 0 averaging kernel, 1 broadcast z (DEFAULT)
   void* args_dev = nullptr; char* args_pinned = nullptr; int args_stride = 0; int max_blocks = 0;
   float** w_table_dev = nullptr;
@@ -423,7 +499,7 @@ XB_API XbExec* xb_exec_create(const XbSolverState* solver, unsigned long long se
   cudaEventCreateWithFlags(&e->sync_event, cudaEventDisableTiming);
   e->args_stride = (xb_sync_args_size() + 255) / 256 * 256;
   cudaMalloc(&e->args_dev, e->args_stride);
-  cudaHostAlloc((void**)&e->args_pinned, 8 * e->args_stride, cudaHostAllocDefault);
+  cudaHostAlloc((void**)&e->args_pinned, 32 * e->args_stride, cudaHostAllocDefault);
   cudaMalloc((void**)&e->w_table_dev, 16 * sizeof(float*));
   memset(e->d_ex, 0, sizeof(e->d_ex)); memset(e->d_lab, 0, sizeof(e->d_lab));
   return e;
@@ -441,7 +517,15 @@ XB_API int xb_exec_add_learner(XbExec* e, XbLearner* l, float* w, float* prev, v
   return i;
 }
 XB_API void xb_exec_remove_learner(XbExec* e) { if (!e->learners.empty()) { e->learners.pop_back(); e->w.pop_back(); e->prev.pop_back(); } }
-XB_API void xb_exec_set_sync(XbExec* e, const XbSyncDescMirror* tmpl, int update_mode) { e->tmpl = *tmpl; e->update_mode = update_mode; }
+XB_API void xb_exec_set_sync(XbExec* e, const XbSyncDescMirror* tmpl, int update_mode) {
+  e->tmpl = *tmpl; e->update_mode = update_mode; e->buckets.clear(); e->bucket_off.clear();
+}
+// Buckets in the order in which the backward pass completes them; `offset` in floats from the start of the flat vectors.
+XB_API int xb_exec_add_bucket(XbExec* e, const XbSyncDescMirror* tmpl, long long offset) {
+  if ((int)e->buckets.size() >= XB_MAX_BUCKETS) return -XB_BAD_ARG;
+  e->buckets.push_back(*tmpl); e->bucket_off.push_back(offset);
+  return (int)e->buckets.size() - 1;
+}
 XB_API void xb_exec_set_data(XbExec* e, int phase, const void* examples, long long ex_bytes, const void* labels, long long lab_bytes, long long ring,
                              long long stride_tasks, long long offset_tasks) {
   e->ex_base[phase] = (const char*)examples; e->ex_bytes[phase] = ex_bytes; e->lab_base[phase] = (const char*)labels; e->lab_bytes[phase] = lab_bytes;
@@ -484,15 +568,36 @@ XB_API int xb_exec_synchronise(void* ctx, unsigned long long clock, const unsign
   (void)clock;
   XbSyncDescMirror d = e->tmpl;
   int k = 0;
+  const bool bucketed = !e->buckets.empty() && e->update_mode == 0;
   for (int i = 0; i < n && i < (int)e->learners.size(); ++i) {
     if (!mask[i]) continue;
     if (k >= 16) return -XB_BAD_ARG;
-    XB_CUDA_CHECK(cudaStreamWaitEvent(e->sync_stream, e->learners[i]->done, 0));
+    if (!bucketed) XB_CUDA_CHECK(cudaStreamWaitEvent(e->sync_stream, e->learners[i]->done, 0));
     d.w[k] = e->w[i]; d.prev[k] = e->prev[i]; ++k;
   }
   if (k == 0) return 0;
   d.k = k;
-  if (e->update_mode == 1) {
+  if (bucketed) {
+    // each bucket's exchange starts as soon as every participating learner has produced that bucket's gradients, while
+    // the learners are still in the backward pass of the earlier layers
+    const unsigned int epoch = ++e->epoch;
+    const int copy_now = (copy || e->solver.copy_signal) ? 1 : 0;
+    e->solver.copy_signal = 0;
+    for (size_t b = 0; b < e->buckets.size(); ++b) {
+      XbSyncDescMirror db = e->buckets[b];
+      int kk = 0;
+      for (int i = 0; i < n && i < (int)e->learners.size(); ++i) {
+        if (!mask[i]) continue;
+        { int r = xb_stream_wait_learner_bucket(e->sync_stream, e->learners[i], (int)b); if (r) return r; }
+        db.w[kk] = e->w[i] + e->bucket_off[b]; db.prev[kk] = e->prev[i] + e->bucket_off[b]; ++kk;
+      }
+      db.k = kk; db.epoch = epoch; db.copy_to_replicas = copy_now;
+      int r = xb_fused_sync(&db, e->args_dev, e->args_pinned + (e->launches++ % 32) * e->args_stride, e->max_blocks, e->sync_stream);
+      if (r) return r;
+    }
+    for (int i = 0; i < n && i < (int)e->learners.size(); ++i)       // (a learner whose program has no marks)
+      if (mask[i]) XB_CUDA_CHECK(cudaStreamWaitEvent(e->sync_stream, e->learners[i]->done, 0));
+  } else if (e->update_mode == 1) {
     XB_CUDA_CHECK(cudaMemcpyAsync(e->w_table_dev, d.w, sizeof(float*) * k, cudaMemcpyHostToDevice, e->sync_stream));
     int r = xb_broadcast_model(d.z, e->w_table_dev, k, d.n, e->sync_stream);
     if (r) return r;
@@ -501,7 +606,7 @@ XB_API int xb_exec_synchronise(void* ctx, unsigned long long clock, const unsign
     d.copy_to_replicas = (copy || e->solver.copy_signal) ? 1 : 0;
     e->solver.copy_signal = 0;
     if (d.algo == 2) { d.scale = 1.0f / (float)(k * d.G); d.blend = 1.0f / (float)d.epoch; }
-    int r = xb_fused_sync(&d, e->args_dev, e->args_pinned + (d.epoch % 8) * e->args_stride, e->max_blocks, e->sync_stream);
+    int r = xb_fused_sync(&d, e->args_dev, e->args_pinned + (e->launches++ % 32) * e->args_stride, e->max_blocks, e->sync_stream);
     if (r) return r;
   }
   XB_CUDA_CHECK(cudaEventRecord(e->sync_event, e->sync_stream));

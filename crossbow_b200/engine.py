@@ -70,7 +70,8 @@ class Learner:
         result_dev = lib.xb_learner_result_dev(self.handle)
         self.low_train = Lowering(e.train_graph, e.model, e.batch, e.input_chw, e.device, self.rep.w, self.rep, e.shared,
                                   self.params_dev, params_host, result_dev, update_model=e.update_model, training=True,
-                                  use_tc=e.use_tc, clip=e.solver.clip_gradient_threshold >= 0, lr_mult=e.lr_mult, splits=e.splits, reuse_memory=e.reuse_memory)
+                                  use_tc=e.use_tc, clip=e.solver.clip_gradient_threshold >= 0, lr_mult=e.lr_mult, splits=e.splits, reuse_memory=e.reuse_memory,
+                                  gradient_buckets=e.gradient_buckets)
         ops = self.low_train.op_array()
         self.prog_train = lib.xb_program_create(ops, len(ops), int(e.use_tc), e.tc_status.data_ptr())
         self.prog_test = None
@@ -125,7 +126,9 @@ class GpuEngine:
                  batch: int, input_chw, solver: SolverConf, update_model: UpdateModel, replicas: int = 1, wpc: int = 1,
                  rank: int = 0, world: int = 1, device_index: int = 0, use_tc: bool = True, use_graphs: bool = True,
                  seed: int = 0, fused_sync: bool = True, two_shot: Optional[bool] = None, sync_timeout_s: float = 5.0,
-                 splits: int = 1, reuse_memory: bool = False):
+                 splits: int = 1, reuse_memory: bool = False, gradient_buckets: int = 0):
+        """`gradient_buckets`: synchronous SGD only - number of gradient buckets whose all-reduce + update overlaps the
+        backward pass (0 = 4 for models of at least 32 MB, otherwise 1; 1 = one synchronisation after the task)."""
         from .ops import lib as L
         from .parallel.sync import FusedSynchroniser, ReferenceSynchroniser
         if not torch.cuda.is_available():
@@ -137,6 +140,9 @@ class GpuEngine:
         self.batch, self.input_chw, self.solver, self.update_model = batch, tuple(input_chw), solver, update_model
         self.splits = max(1, int(splits))
         self.reuse_memory = bool(reuse_memory)
+        nb = int(gradient_buckets) if gradient_buckets else (4 if model.device_elements * 4 >= (32 << 20) else 1)
+        self.gradient_buckets = min(8, nb) if (fused_sync and update_model == UpdateModel.WORKER) else 1
+        self.bucket_syncs = []
         self.rank, self.world, self.wpc, self.seed = rank, world, wpc, seed
         self.use_tc, self.use_graphs = use_tc, use_graphs
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -152,6 +158,9 @@ class GpuEngine:
         self.learners: List[Learner] = []
         for i in range(replicas):
             self.learners.append(Learner(self, i, init))
+        ranges = self.learners[0].low_train.buckets if self.learners else []
+        if len(ranges) > 1:
+            self.bucket_syncs = self.synchroniser.make_buckets(ranges)
         self.sync_stream = self.lib.xb_stream_create(-1)
         self.sync_event = self.lib.xb_event_create(0)
         self.poly_count = 0
@@ -208,9 +217,11 @@ class GpuEngine:
         from .parallel import sync as S
         lib, ss = self.lib, self.sync_stream
         ls = [self.learners[i] for i in (learners if learners is not None else range(len(self.learners)))]
-        for l in ls:
-            L.check(lib.xb_stream_wait_learner(ss, l.handle), "sync waits for learner")
         um, sv = self.update_model, self.solver
+        bucketed = bool(self.bucket_syncs) and um == UpdateModel.WORKER
+        if not bucketed:
+            for l in ls:
+                L.check(lib.xb_stream_wait_learner(ss, l.handle), "sync waits for learner")
         ws, prevs = [l.rep.w for l in ls], [l.rep.prev for l in ls]
         sh = self.shared
         if um in (UpdateModel.SMA, UpdateModel.SYNCHRONOUSEAMSGD):
@@ -219,6 +230,19 @@ class GpuEngine:
         elif um == UpdateModel.EAMSGD:
             self.synchroniser.synchronise(ss, S.ALGO_SMA, ws, prevs, sh.z, sh.zlast, None, alpha=sv.alpha,
                                           mu=sv.base_model_momentum, copy=copy, use_prev=False)
+        elif bucketed:
+            # bucket b starts as soon as every learner has accumulated that bucket's gradients (the learners are then still
+            # in the backward pass of the earlier layers)
+            self.synchroniser.epoch += 1
+            for b, c in enumerate(self.bucket_syncs):
+                for l in ls:
+                    L.check(lib.xb_stream_wait_learner_bucket(ss, l.handle, b), "sync waits for a gradient bucket")
+                sl = slice(c.offset, c.offset + c.n)
+                c.epoch = self.synchroniser.epoch - 1
+                c.synchronise(ss, S.ALGO_SSGD, [w[sl] for w in ws], None, sh.z[sl], sh.zlast[sl], sh.gacc[sl], mu=sv.momentum,
+                              scale=1.0 / self.wpc)
+            for l in ls:
+                L.check(lib.xb_stream_wait_learner(ss, l.handle), "sync waits for learner")
         elif um == UpdateModel.WORKER:
             self.synchroniser.synchronise(ss, S.ALGO_SSGD, ws, None, sh.z, sh.zlast, sh.gacc, mu=sv.momentum, scale=1.0 / self.wpc)
         elif um == UpdateModel.POLYAK_RUPPERT:
@@ -280,6 +304,12 @@ class GpuEngine:
         else:
             raise NotImplementedError(f"error: {um} is not supported (a stub in the reference as well)")
         lib.xb_exec_set_sync(self._exec, C.byref(d), int(um == UpdateModel.DEFAULT))
+        if um == UpdateModel.WORKER:
+            for c in self.bucket_syncs:
+                sl = slice(c.offset, c.offset + c.n)
+                db = c.descriptor(S.ALGO_SSGD, [w[sl] for w in ws], None, sh.z[sl], sh.zlast[sl], sh.gacc[sl], 0.0, sv.momentum,
+                                  1.0 / self.wpc, 0.0, False, True)
+                L.check(min(0, lib.xb_exec_add_bucket(self._exec, C.byref(db), c.offset)), "gradient bucket")
         lib.xb_exec_set_epoch(self._exec, sy.epoch)
         for phase, ds in ((0, train_ds), (1, test_ds)):
             if ds is None:
@@ -293,6 +323,16 @@ class GpuEngine:
                 lib.xb_exec_set_data(self._exec, phase, 0, n * 4, 0, ds.batch_size * 4, 0, 1, 0)
         addr = lambda name: C.cast(getattr(lib, name), C.c_void_p).value
         return self._exec, addr("xb_exec_submit"), addr("xb_exec_wait"), addr("xb_exec_synchronise"), addr("xb_exec_batch")
+
+    def epoch_to_native(self):
+        """The synchronisation epoch is one counter whichever side enqueues the kernels: the flags in peer memory hold the
+        epochs already used, so the native executor must continue after the last one enqueued from Python."""
+        if self._exec and hasattr(self.synchroniser, "epoch"):
+            self.lib.xb_exec_set_epoch(self._exec, max(int(self.lib.xb_exec_epoch(self._exec)), int(self.synchroniser.epoch)))
+
+    def epoch_from_native(self):
+        if self._exec and hasattr(self.synchroniser, "epoch"):
+            self.synchroniser.epoch = max(int(self.synchroniser.epoch), int(self.lib.xb_exec_epoch(self._exec)))
 
     def _exec_add(self, l: Learner):
         ext, lat = l.staging(Phase.TRAIN)

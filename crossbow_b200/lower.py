@@ -132,7 +132,8 @@ class Lowering:
                  replica: Optional[ReplicaBuffers], shared: DeviceShared, params_dev: torch.Tensor, params_host_ptr: int,
                  result_dev_ptr: int,
                  update_model: UpdateModel = UpdateModel.SMA, training=True, use_tc=True, clip=False,
-                 lr_mult: Optional[torch.Tensor] = None, seed_stream_base=0, splits: int = 1, reuse_memory: bool = False):
+                 lr_mult: Optional[torch.Tensor] = None, seed_stream_base=0, splits: int = 1, reuse_memory: bool = False,
+                 gradient_buckets: int = 1):
         if splits < 1 or batch % splits:
             raise ValueError("error: the batch size must be a multiple of the number of splits")
         # `--splits` (taskhandler.c:65-114): one task runs the whole graph `splits` times over consecutive sub-batches of
@@ -149,6 +150,8 @@ class Lowering:
         self._count_pass, self._gout_count, self._gout_total = False, {}, {}
         self.all_tensors: List[T] = []
         self.reuse_memory = reuse_memory
+        self.gradient_buckets = gradient_buckets
+        self.buckets: List[tuple] = []      # (offset, elements) of each gradient bucket, in the order the backward pass completes them
         self.bytes_before_reuse = 0
         self.ops: List[L.XbOp] = []
         self.keep = []                      # python objects that must outlive the program (descriptor tables ...)
@@ -249,6 +252,9 @@ class Lowering:
             self._optimiser()
         # one memset clears all per-task accumulators (BN sums, BN backward sums)
         self.ops[zero_slot] = _op(L.OP_MEMSET, la=[4 * self.zero_used], p=[self.zero_region])
+        if (self.gradient_buckets > 1 and self.update_model == UpdateModel.WORKER and not self.clip and self.splits == 1
+                and self.ops and self.ops[-1].kind == L.OP_OPTIMISER):
+            self._bucket_gradients(self.gradient_buckets)
         if self.splits > 1:
             self._repeat_for_splits()
         if self.reuse_memory:
@@ -703,6 +709,59 @@ class Lowering:
             norm2 = self.arena.alloc(1, zero=True)
             self.emit(_op(L.OP_GRAD_SUMSQ, la=[rep.n], p=[rep.g, norm2]))
         self.emit(_op(L.OP_OPTIMISER, ia=[mode], la=[rep.n], p=[rep.w, rep.g, rep.last, rep.prev, target, self.lr_mult, norm2, self.params_dev]))
+
+    def _bucket_gradients(self, nb: int):
+        """Synchronous SGD overlapped with the backward pass: the flat vector is cut into up to `nb` contiguous buckets
+        of whole variables, from the last layer backwards.  The accumulate step of a bucket (the optimiser operator over
+        that range) is issued right after the last operator that writes a gradient of the bucket, followed by a mark at
+        which the learner records an event; the synchronisation of that bucket (gradient all-reduce fused with the
+        momentum update, what synch/synchronoussgd.c:13-110 does once for the whole vector) waits for that event only,
+        and so runs next to the backward pass of the earlier layers."""
+        import bisect
+        rep = self.replica
+        opt = self.ops.pop()
+        assert opt.kind == L.OP_OPTIMISER
+        g0, n = rep.g.data_ptr(), rep.n
+        vs = sorted(self.model.variables, key=lambda v: v.doffset)
+        starts = [v.doffset for v in vs]
+        # last operator that names an address inside the variable's slice of the gradient vector - or of the weight vector:
+        # the synchronisation overwrites the replica's weights of the bucket, so their last reader must have been issued
+        w0 = rep.w.data_ptr()
+        last = [-1] * len(vs)
+        for i, o in enumerate(self.ops):
+            for j in range(12):
+                a = o.p[j]
+                for base in (g0, w0):
+                    if a and base <= a < base + 4 * n:
+                        last[bisect.bisect_right(starts, (a - base) // 4) - 1] = i
+        # cut from the tail: a bucket closes once it holds its share of the vector
+        share, cuts, hi, ready = (n + nb - 1) // nb, [], n, -1
+        for vi in range(len(vs) - 1, -1, -1):
+            ready = max(ready, last[vi])
+            if hi - starts[vi] >= share or vi == 0:
+                cuts.append((starts[vi] if vi else 0, hi, ready))
+                hi = starts[vi]
+        merged = []                            # buckets that complete at the same operator are one bucket
+        for lo, hi, ready in cuts:
+            if merged and merged[-1][2] >= ready:
+                merged[-1] = (lo, merged[-1][1], merged[-1][2])
+            else:
+                merged.append((lo, hi, ready))
+        if len(merged) < 2:
+            self.ops.append(opt)
+            return
+        after: Dict[int, list] = {}
+        for b, (lo, hi, ready) in enumerate(merged):
+            sl = lambda t: (t.data_ptr() + 4 * lo) if t is not None else None
+            o = _op(L.OP_OPTIMISER, ia=[2], la=[hi - lo],
+                    p=[sl(rep.w), sl(rep.g), sl(rep.last), sl(rep.prev), sl(self.shared.gacc), sl(self.lr_mult), None, self.params_dev])
+            after.setdefault(ready, []).extend([o, _op(L.OP_MARK, ia=[b])])
+            self.buckets.append((lo, hi - lo))
+        ops = list(after.get(-1, []))
+        for i, o in enumerate(self.ops):
+            ops.append(o)
+            ops.extend(after.get(i, []))
+        self.ops = ops
 
     def op_array(self):
         arr = (L.XbOp * len(self.ops))(*self.ops)

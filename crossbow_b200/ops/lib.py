@@ -58,7 +58,7 @@ class XbSolverState(C.Structure):
 # op kinds (csrc/runtime/program.cu)
 (OP_MEMSET, OP_UPLOAD, OP_TRANSFORM, OP_CONV_FPROP, OP_CONV_DGRAD, OP_CONV_WGRAD, OP_COLSUM, OP_BN_STATS, OP_BN_FWD,
  OP_BN_BWD, OP_ACT_FWD, OP_ACT_BWD, OP_SUM, OP_DROPOUT, OP_CONCAT, OP_POOL_FWD, OP_POOL_BWD, OP_LRN_FWD, OP_LRN_BWD,
- OP_SOFTMAX_XENT, OP_CLASSIFY, OP_TRANSPOSE_W, OP_GRAD_SUMSQ, OP_OPTIMISER, OP_COPY, OP_MATFACT) = range(26)
+ OP_SOFTMAX_XENT, OP_CLASSIFY, OP_TRANSPOSE_W, OP_GRAD_SUMSQ, OP_OPTIMISER, OP_COPY, OP_MATFACT, OP_MARK) = range(27)
 
 F_RELU, F_ACCUM, F_STATS, F_TC = 1, 2, 4, 0x100
 
@@ -145,6 +145,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_program_run", I, P, P)
     _sig(lib, "xb_program_run_range", I, P, I, I, P)
     _sig(lib, "xb_program_capture", I, P, P)
+    _sig(lib, "xb_program_marks", I, P)
     _sig(lib, "xb_program_launch", I, P, P)
     _sig(lib, "xb_learner_create", P, I, P, L, P, L)
     _sig(lib, "xb_learner_destroy", None, P)
@@ -157,6 +158,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_learner_wait", I, P, C.POINTER(c_float), C.POINTER(c_float))
     _sig(lib, "xb_learner_query", I, P)
     _sig(lib, "xb_stream_wait_learner", I, P, P)
+    _sig(lib, "xb_stream_wait_learner_bucket", I, P, P, I)
     _sig(lib, "xb_learner_wait_event", I, P, P)
     # native executor (function-pointer table for the host runtime)
     _sig(lib, "xb_exec_create", P, C.POINTER(XbSolverState), C.c_ulonglong, P, I)
@@ -164,6 +166,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_exec_add_learner", I, P, P, P, P, P, P, P, P)
     _sig(lib, "xb_exec_remove_learner", None, P)
     _sig(lib, "xb_exec_set_sync", None, P, C.POINTER(XbSyncDesc), I)
+    _sig(lib, "xb_exec_add_bucket", I, P, C.POINTER(XbSyncDesc), C.c_longlong)
     _sig(lib, "xb_exec_set_data", None, P, I, P, L, P, L, L, L, L)
     _sig(lib, "xb_sync_desc_size", I)
     _sig(lib, "xb_exec_copy_signal", I, P)

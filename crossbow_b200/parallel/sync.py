@@ -26,9 +26,23 @@ class SyncTimeout(RuntimeError):
     """A bounded device-side wait on a peer expired (the peer is late, gone, or never joined)."""
 
 
+class _PeerView:
+    """A window of another PeerBuffer (same mapping, moved by `offset_bytes`); owns nothing."""
+
+    def __init__(self, buf: PeerBuffer, offset_bytes: int):
+        self.ptrs = [p + offset_bytes for p in buf.ptrs]
+        self.local = buf.local + offset_bytes
+
+    def close(self):
+        pass
+
+
 class FusedSynchroniser:
     def __init__(self, n: int, rank: int = 0, world: int = 1, two_shot: Optional[bool] = None, timeout_s: float = 5.0,
-                 max_blocks: int = 0, group=None):
+                 max_blocks: int = 0, group=None, parent: Optional["FusedSynchroniser"] = None, offset: int = 0):
+        """`parent` / `offset`: this synchroniser covers elements [offset, offset + n) of the parent's vectors (a gradient
+        bucket).  It has exchange buffers and flags of its own, so buckets of different sizes never share a flag slot or
+        an inbox region, and it shares the parent's status word and central-model storage."""
         lib = L.load()
         self.lib, self.n, self.rank, self.world = lib, n, rank, world
         if n % 4:
@@ -39,15 +53,28 @@ class FusedSynchroniser:
         self.args_dev = lib.xb_device_alloc(lib.xb_sync_args_size())
         self.args_size = (lib.xb_sync_args_size() + 255) // 256 * 256
         self.args_pinned = lib.xb_pinned_alloc(8 * self.args_size)    # ring: an upload may still be pending when the next is built
-        self.status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.status = parent.status if parent is not None else torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.parent, self.offset, self.group = parent, offset, group
+        self.children: List["FusedSynchroniser"] = []
         self.inbox = self.result = self.flags = self.zbuf = None
         if world > 1:
             self.inbox = PeerBuffer(4 * lib.xb_sync_inbox_floats(n, world, int(self.two_shot)), rank, world, group)
             self.result = PeerBuffer(4 * lib.xb_sync_result_floats(n) if self.two_shot else 256, rank, world, group)
             self.flags = PeerBuffer(4 * lib.xb_sync_flag_words(n, world), rank, world, group)
-            if self.two_shot:
+            if self.two_shot and parent is not None:
+                self.zbuf = _PeerView(parent.zbuf, 4 * offset) if parent.zbuf is not None else None
+            elif self.two_shot:
                 # peer-visible home for the central model: chunk owners then store the updated model straight into it
                 self.zbuf = PeerBuffer(4 * n, rank, world, group)
+
+    def make_buckets(self, ranges) -> List["FusedSynchroniser"]:
+        """One child synchroniser per (offset, elements) range, in the given order (collective: every rank must pass the
+        same ranges).  The children replace this synchroniser for the algorithm that is run bucket by bucket."""
+        for c in self.children:
+            c.close()
+        self.children = [FusedSynchroniser(ln, self.rank, self.world, self.two_shot, self.timeout_s, self.max_blocks, self.group,
+                                           parent=self, offset=off) for off, ln in ranges]
+        return self.children
 
     def central_storage(self) -> Optional[torch.Tensor]:
         """Peer-visible tensor to keep the central model in (None when the exchange does not use one)."""
@@ -63,8 +90,14 @@ class FusedSynchroniser:
         if not self.owner_apply:
             return zlast
         import torch.distributed as dist
-        chunk = int(self.lib.xb_sync_chunk(self.n))
-        owner = (torch.arange(self.n, device=zlast.device) // chunk) % self.world
+        if self.children:                     # bucket by bucket: ownership follows each bucket's own chunking
+            owner = torch.empty(self.n, dtype=torch.int64, device=zlast.device)
+            for c in self.children:
+                chunk = int(self.lib.xb_sync_chunk(c.n))
+                owner[c.offset:c.offset + c.n] = (torch.arange(c.n, device=zlast.device) // chunk) % self.world
+        else:
+            chunk = int(self.lib.xb_sync_chunk(self.n))
+            owner = (torch.arange(self.n, device=zlast.device) // chunk) % self.world
         full = torch.where(owner == self.rank, zlast, torch.zeros_like(zlast))
         dist.all_reduce(full)
         return full
@@ -95,7 +128,8 @@ class FusedSynchroniser:
         """Enqueue one synchronisation on ``stream`` (a raw cudaStream_t). Asynchronous; see ``check``."""
         self.epoch += 1
         d = self.descriptor(algo, replicas_w, replicas_prev, z, zlast, gacc, alpha, mu, scale, blend, copy, use_prev)
-        staging = self.args_pinned + (self.epoch % 8) * self.args_size
+        self.launches = getattr(self, "launches", 0) + 1
+        staging = self.args_pinned + (self.launches % 8) * self.args_size
         L.check(self.lib.xb_fused_sync(C.byref(d), self.args_dev, staging, self.max_blocks, stream), "fused sync")
 
     def check(self):
@@ -106,6 +140,9 @@ class FusedSynchroniser:
             raise SyncTimeout(f"fused synchronisation gave up waiting for a peer (status {s}, epoch {self.epoch})")
 
     def close(self):
+        for c in self.children:
+            c.close()
+        self.children = []
         for b in (self.inbox, self.result, self.flags, self.zbuf):
             if b is not None:
                 b.close()

@@ -30,13 +30,15 @@ def make_batches(spec, batch, n, seed=0):
     return xs, ys
 
 
-def engines(name, batch, k=1, update_model=UpdateModel.SMA, wpc=None, solver=None, use_graphs=True, use_tc=False, seed=7, splits=1, reuse_memory=False, **kw):
+def engines(name, batch, k=1, update_model=UpdateModel.SMA, wpc=None, solver=None, use_graphs=True, use_tc=False, seed=7, splits=1, reuse_memory=False,
+            gradient_buckets=0, **kw):
     from crossbow_b200.engine import CpuEngine, GpuEngine
     spec, m, solver = build_model(name, batch, solver, **kw)
     init = m.initial_values(seed)
     wpc = wpc or k
     gpu = GpuEngine(spec.train, spec.test, m, init, batch, spec.input_shape, solver, update_model, replicas=k, wpc=wpc,
-                    use_graphs=use_graphs, use_tc=use_tc, seed=seed, splits=splits, reuse_memory=reuse_memory)
+                    use_graphs=use_graphs, use_tc=use_tc, seed=seed, splits=splits, reuse_memory=reuse_memory,
+                    gradient_buckets=gradient_buckets)
     import copy
     cpu = CpuEngine(spec.train, spec.test, m, init, batch, spec.input_shape, copy.deepcopy(solver), update_model, replicas=k, wpc=wpc, seed=seed,
                     splits=splits)

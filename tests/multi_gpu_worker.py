@@ -76,6 +76,30 @@ def main():
     assert float(eng.shared.z.abs().sum()) > 0 and torch.isfinite(eng.shared.z).all()
     eng.destroy()
     dist.barrier()
+    # synchronous SGD with gradient buckets (owner-apply exchange per bucket, overlapping the backward pass) against one
+    # synchronisation per clock; both learners of a rank run concurrently
+    import copy
+    outs = []
+    spec, m, solver = build_model("lenet-caffe", 8)          # well conditioned: rounding noise is not amplified
+    xs, ys = make_batches(spec, 8, 8, seed=100 + rank)
+    for nb in (1, 3):
+        eng = GpuEngine(spec.train, None, m, m.initial_values(7), 8, spec.input_shape, copy.deepcopy(solver), UpdateModel.WORKER, replicas=2,
+                        wpc=2 * world, rank=rank, world=world, device_index=local, use_tc=True, two_shot=True, gradient_buckets=nb)
+        assert (len(eng.bucket_syncs) > 1) == (nb > 1)
+        for t in range(0, 8, 2):
+            eng.submit(0, xs[t].pin_memory(), ys[t].pin_memory(), t, Phase.TRAIN)
+            eng.submit(1, xs[t + 1].pin_memory(), ys[t + 1].pin_memory(), t + 1, Phase.TRAIN)
+            eng.synchronise()
+        eng.wait(0), eng.wait(1)
+        eng.finish()
+        zs = [torch.empty_like(eng.shared.z) for _ in range(world)]
+        dist.all_gather(zs, eng.shared.z.clone())
+        assert all(torch.equal(zs[0], t) for t in zs), "central models diverged across ranks (bucketed S-SGD)"
+        outs.append((eng.shared.z.clone(), eng.central_momentum().clone(), eng.learners[1].rep.w.clone()))
+        eng.destroy()
+        dist.barrier()
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.isfinite(a).all() and float((a - b).abs().max()) <= 3e-4 * float(a.abs().max()) + 1e-9, float((a - b).abs().max())
     if rank == 0:
         print("MULTI_GPU_OK", world)
     dist.destroy_process_group()

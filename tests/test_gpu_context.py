@@ -44,6 +44,21 @@ def test_train_test_and_loss_goes_down(native):
     ctx.destroy()
 
 
+def test_synchronous_sgd_with_gradient_buckets_through_the_native_scheduler():
+    ref = _context(update="WORKER", gradient_buckets=1)
+    ref.train(16, "tasks")
+    z1 = ref.engine.central_model()
+    ref.destroy()
+    ctx = _context(update="WORKER", gradient_buckets=3)
+    assert ctx._native is not None and len(ctx.engine.bucket_syncs) >= 2
+    ctx.train(16, "tasks")
+    z2 = ctx.engine.central_model()
+    losses = ctx.measurements.losses()
+    ctx.destroy()
+    assert np.isfinite(losses).all()
+    assert np.abs(z1 - z2).max() <= 1e-4 * np.abs(z1).max()
+
+
 def test_checkpoint_and_resume(tmp_path):
     ctx = _context()
     ctx.train(8, "tasks")

@@ -56,6 +56,46 @@ def test_logistic_ssgd():
     run_both("logistic-regression", 32, 2, 4, update_model=UpdateModel.WORKER)
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_ssgd_gradient_buckets_against_oracle(graphs):
+    # the accumulate step and the synchronisation run bucket by bucket (marks in the program, one event per bucket)
+    spec, m, gpu, cpu = engines("lenet-caffe", 8, k=2, update_model=UpdateModel.WORKER, gradient_buckets=3, use_graphs=graphs)
+    try:
+        assert len(gpu.bucket_syncs) >= 2 and gpu.lib.xb_program_marks(gpu.learners[0].prog_train) == len(gpu.bucket_syncs)
+        assert sum(c.n for c in gpu.bucket_syncs) == m.device_elements
+    finally:
+        gpu.destroy()
+    run_both("lenet-caffe", 8, 2, 6, update_model=UpdateModel.WORKER, gradient_buckets=3, use_graphs=graphs)
+
+
+def test_ssgd_gradient_buckets_match_one_synchronisation_with_concurrent_learners():
+    from crossbow_b200.engine import GpuEngine
+    from helpers import build_model
+    # (a well-conditioned model: the replicas' atomic accumulation order differs from run to run, and a deep batch-norm
+    # network at batch 8 amplifies that rounding noise to 1e-3 within a few steps)
+    spec, m, solver = build_model("lenet-caffe", 8)
+    init = m.initial_values(5)
+    xs, ys = make_batches(spec, 8, 8, seed=11)
+    pinned = [(x.pin_memory(), y.pin_memory()) for x, y in zip(xs, ys)]
+    out = []
+    for nb in (1, 4):
+        import copy
+        eng = GpuEngine(spec.train, None, m, init, 8, spec.input_shape, copy.deepcopy(solver), UpdateModel.WORKER, replicas=2, wpc=2,
+                        use_tc=True, gradient_buckets=nb)
+        assert (len(eng.bucket_syncs) > 1) == (nb > 1)
+        for t in range(0, 8, 2):
+            eng.submit(0, *pinned[t], t, Phase.TRAIN)
+            eng.submit(1, *pinned[t + 1], t + 1, Phase.TRAIN)
+            eng.synchronise()                      # enqueued while both learners are still running
+        for l in range(2):
+            eng.wait(l)
+        eng.finish()
+        out.append((eng.central_model(), eng.replica_model(1), eng.central_momentum().cpu().numpy()))
+        eng.destroy()
+    for a, b in zip(out[0], out[1]):
+        assert np.isfinite(a).all() and np.abs(a - b).max() <= 2e-4 * (np.abs(a).max() + 1e-12), np.abs(a - b).max() / np.abs(a).max()
+
+
 def test_resnet8_sma():
     run_both("resnet8", 8, 2, 4)
 
