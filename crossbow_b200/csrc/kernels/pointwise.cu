@@ -39,6 +39,39 @@ __global__ void act_bwd_kernel(const float* __restrict__ dy, const float* __rest
   }
 }
 
+__device__ __forceinline__ float act_one(float v, int mode, float slope, float ceiling) {
+  if (mode == 1) return v > 0.f ? v : v * slope;
+  if (mode == 0) return 1.f / (1.f + __expf(-v));
+  if (mode == 2) return tanhf(v);
+  return fminf(fmaxf(v, 0.f), ceiling);
+}
+__device__ __forceinline__ float act_grad_one(float g, float x, float y, int mode, float slope, float ceiling) {
+  if (mode == 1) return y > 0.f ? g : g * slope;
+  if (mode == 0) return g * y * (1.f - y);
+  if (mode == 2) return g * (1.f - y * y);
+  return (x > 0.f && x < ceiling) ? g : 0.f;
+}
+// 16-byte forms of the two kernels above (n4 = elements / 4, all pointers 16-byte aligned)
+__global__ void act_fwd_v4_kernel(const float4* __restrict__ x, float4* __restrict__ y, long long n4, int mode, float slope, float ceiling) {
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n4; i += (long long)gridDim.x * NT) {
+    const float4 v = x[i];
+    y[i] = make_float4(act_one(v.x, mode, slope, ceiling), act_one(v.y, mode, slope, ceiling), act_one(v.z, mode, slope, ceiling),
+                       act_one(v.w, mode, slope, ceiling));
+  }
+}
+__global__ void act_bwd_v4_kernel(const float4* __restrict__ dy, const float4* __restrict__ x, const float4* __restrict__ y,
+                                  float4* __restrict__ dx, long long n4, int mode, float slope, float ceiling, int accum) {
+  const bool need_x = mode == 3;
+  for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n4; i += (long long)gridDim.x * NT) {
+    const float4 g = dy[i], yy = y[i];
+    const float4 xx = need_x ? x[i] : yy;
+    float4 o = make_float4(act_grad_one(g.x, xx.x, yy.x, mode, slope, ceiling), act_grad_one(g.y, xx.y, yy.y, mode, slope, ceiling),
+                           act_grad_one(g.z, xx.z, yy.z, mode, slope, ceiling), act_grad_one(g.w, xx.w, yy.w, mode, slope, ceiling));
+    if (accum) { const float4 d = dx[i]; o.x += d.x; o.y += d.y; o.z += d.z; o.w += d.w; }
+    dx[i] = o;
+  }
+}
+
 // y = (accum ? y : 0) + sum_i coef[i]*x[i]
 struct SumArgs { const float* x[4]; float coef[4]; int n_in; };
 __global__ void weighted_sum_kernel(SumArgs a, float* __restrict__ y, long long n4, long long n, int accum) {
@@ -62,13 +95,21 @@ __global__ void weighted_sum_kernel(SumArgs a, float* __restrict__ y, long long 
 
 // Inverted dropout. Element i uses lane i%4 of Philox(counter = i/4, task, stream); keep iff u >= ratio.
 __global__ void dropout_kernel(const float* __restrict__ x, float* __restrict__ y, long long n, float ratio, unsigned stream,
-                               const XbTaskParams* __restrict__ tp, int accum) {
+                               const XbTaskParams* __restrict__ tp, int accum, bool vec) {
   const float scale = 1.f / (1.f - ratio);
   const unsigned task = tp->task_id, k0 = tp->seed_lo, k1 = tp->seed_hi;
   long long groups = (n + 3) / 4;
   for (long long gidx = blockIdx.x * (long long)NT + threadIdx.x; gidx < groups; gidx += (long long)gridDim.x * NT) {
     uint4 r = xb_philox4x32((uint32_t)gidx, task, stream, 0u, k0, k1);
     uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+    if (vec && gidx * 4 + 3 < n) {          // one 16-byte load and store per group
+      const float4 v = reinterpret_cast<const float4*>(x)[gidx];
+      float4 o = make_float4((xb_u24(rr[0]) >= ratio) ? v.x * scale : 0.f, (xb_u24(rr[1]) >= ratio) ? v.y * scale : 0.f,
+                             (xb_u24(rr[2]) >= ratio) ? v.z * scale : 0.f, (xb_u24(rr[3]) >= ratio) ? v.w * scale : 0.f);
+      if (accum) { const float4 d = reinterpret_cast<const float4*>(y)[gidx]; o.x += d.x; o.y += d.y; o.z += d.z; o.w += d.w; }
+      reinterpret_cast<float4*>(y)[gidx] = o;
+      continue;
+    }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       long long i = gidx * 4 + e;
@@ -128,6 +169,75 @@ __global__ void maxpool_bwd_kernel(const float* __restrict__ dy, const float* __
     if (arg >= 0) atomicAdd(&dx[arg], dy[i]);
   }
 }
+// ---- 16-byte forms (C % 4 == 0, fewer than 2^31 groups): one thread = four channels of one output position -----------
+template <bool AVG>
+__global__ void __launch_bounds__(NT) pool_fwd_v4_kernel(const float4* __restrict__ x, float4* __restrict__ y, PoolGeom g) {
+  const unsigned C4 = (unsigned)g.C >> 2, n = (unsigned)g.N * g.P * g.Q * C4;
+  const float inv = 1.f / (float)(g.kh * g.kw);
+  for (unsigned i = blockIdx.x * NT + threadIdx.x; i < n; i += gridDim.x * NT) {
+    const unsigned c = i % C4; unsigned t = i / C4; const int q = t % g.Q; t /= g.Q; const int p = t % g.P, b = t / g.P;
+    const int y0 = p * g.sh - g.ph, x0 = q * g.sw - g.pw;
+    float4 a = AVG ? make_float4(0, 0, 0, 0) : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+    for (int r = 0; r < g.kh; ++r) {
+      const int iy = y0 + r; if (iy < 0 || iy >= g.H) continue;
+      const float4* row = x + ((long long)b * g.H + iy) * g.W * C4 + c;
+      for (int s = 0; s < g.kw; ++s) {
+        const int ix = x0 + s; if (ix < 0 || ix >= g.W) continue;
+        const float4 v = row[(long long)ix * C4];
+        if (AVG) { a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w; }
+        else { if (v.x > a.x) a.x = v.x; if (v.y > a.y) a.y = v.y; if (v.z > a.z) a.z = v.z; if (v.w > a.w) a.w = v.w; }
+      }
+    }
+    y[i] = AVG ? make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv) : a;
+  }
+}
+// DIRECT (windows do not overlap): every window position is written with a plain store - dy at the first maximum, zero
+// elsewhere; otherwise dy is added at the first maximum with an atomic (dx zeroed by the caller).
+template <bool DIRECT>
+__global__ void __launch_bounds__(NT) maxpool_bwd_v4_kernel(const float4* __restrict__ dy, const float4* __restrict__ x, float* __restrict__ dx,
+                                                            PoolGeom g, int accum) {
+  const unsigned C4 = (unsigned)g.C >> 2, n = (unsigned)g.N * g.P * g.Q * C4;
+  for (unsigned i = blockIdx.x * NT + threadIdx.x; i < n; i += gridDim.x * NT) {
+    const unsigned c = i % C4; unsigned t = i / C4; const int q = t % g.Q; t /= g.Q; const int p = t % g.P, b = t / g.P;
+    const int y0 = p * g.sh - g.ph, x0 = q * g.sw - g.pw;
+    float best[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};
+    int arg[4] = {-1, -1, -1, -1};
+    for (int r = 0; r < g.kh; ++r) {
+      const int iy = y0 + r; if (iy < 0 || iy >= g.H) continue;
+      const float4* row = x + ((long long)b * g.H + iy) * g.W * C4 + c;
+      for (int s = 0; s < g.kw; ++s) {
+        const int ix = x0 + s; if (ix < 0 || ix >= g.W) continue;
+        const float4 v = row[(long long)ix * C4];
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) if (vv[e] > best[e]) { best[e] = vv[e]; arg[e] = r * g.kw + s; }
+      }
+    }
+    const float4 g4 = dy[i];
+    const float gg[4] = {g4.x, g4.y, g4.z, g4.w};
+    if (DIRECT) {
+      for (int r = 0; r < g.kh; ++r) {
+        const int iy = y0 + r; if (iy < 0 || iy >= g.H) continue;
+        for (int s = 0; s < g.kw; ++s) {
+          const int ix = x0 + s; if (ix < 0 || ix >= g.W) continue;
+          float4* d = reinterpret_cast<float4*>(dx) + (((long long)b * g.H + iy) * g.W + ix) * C4 + c;
+          const int tap = r * g.kw + s;
+          float4 o = make_float4(arg[0] == tap ? gg[0] : 0.f, arg[1] == tap ? gg[1] : 0.f, arg[2] == tap ? gg[2] : 0.f, arg[3] == tap ? gg[3] : 0.f);
+          if (accum) { const float4 old = *d; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+          *d = o;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (arg[e] >= 0) {
+          const int r = arg[e] / g.kw, s = arg[e] - r * g.kw;
+          atomicAdd(dx + ((((long long)b * g.H + y0 + r) * g.W + x0 + s) * C4 + c) * 4 + e, gg[e]);
+        }
+    }
+  }
+}
+
 // average pooling, divisor = kh*kw always (padding counted)
 __global__ void avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, PoolGeom g) {
   long long n = (long long)g.N * g.P * g.Q * g.C;
@@ -238,12 +348,19 @@ __global__ void colsum_kernel(const float* __restrict__ a, float* __restrict__ o
 }  // namespace
 
 XB_API int xb_act_forward(const float* x, float* y, long long n, int mode, float slope, float ceiling, cudaStream_t st) {
-  act_fwd_kernel<<<grid_for(n, 4), NT, 0, st>>>(x, y, n, mode, slope, ceiling);
+  if (n % 4 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0)
+    act_fwd_v4_kernel<<<grid_for(n / 4, 2), NT, 0, st>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), n / 4, mode, slope, ceiling);
+  else
+    act_fwd_kernel<<<grid_for(n, 4), NT, 0, st>>>(x, y, n, mode, slope, ceiling);
   return (int)cudaGetLastError();
 }
 XB_API int xb_act_backward(const float* dy, const float* x, const float* y, float* dx, long long n, int mode, float slope, float ceiling,
                            int accum, cudaStream_t st) {
-  act_bwd_kernel<<<grid_for(n, 4), NT, 0, st>>>(dy, x, y, dx, n, mode, slope, ceiling, accum);
+  if (n % 4 == 0 && ((uintptr_t)dy % 16) == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)dx % 16) == 0)
+    act_bwd_v4_kernel<<<grid_for(n / 4, 2), NT, 0, st>>>(reinterpret_cast<const float4*>(dy), reinterpret_cast<const float4*>(x), reinterpret_cast<const float4*>(y),
+                                                        reinterpret_cast<float4*>(dx), n / 4, mode, slope, ceiling, accum);
+  else
+    act_bwd_kernel<<<grid_for(n, 4), NT, 0, st>>>(dy, x, y, dx, n, mode, slope, ceiling, accum);
   return (int)cudaGetLastError();
 }
 XB_API int xb_weighted_sum(const float* const* xs, const float* coef, int n_in, float* y, long long n, int accum, cudaStream_t st) {
@@ -258,17 +375,25 @@ XB_API int xb_weighted_sum(const float* const* xs, const float* coef, int n_in, 
   return (int)cudaGetLastError();
 }
 XB_API int xb_dropout(const float* x, float* y, long long n, float ratio, unsigned stream, const XbTaskParams* tp, int accum, cudaStream_t st) {
-  dropout_kernel<<<grid_for((n + 3) / 4), NT, 0, st>>>(x, y, n, ratio, stream, tp, accum);
+  const bool vec = ((uintptr_t)x % 16) == 0 && ((uintptr_t)y % 16) == 0;
+  dropout_kernel<<<grid_for((n + 3) / 4, 2), NT, 0, st>>>(x, y, n, ratio, stream, tp, accum, vec);
   return (int)cudaGetLastError();
 }
 XB_API int xb_concat_copy(const float* src, float* dst, long long M, int Cs, int Ct, int coff, int to_wide, int accum, cudaStream_t st) {
   concat_copy_kernel<<<grid_for(M * Cs, 2), NT, 0, st>>>(src, dst, M, Cs, Ct, coff, to_wide, accum);
   return (int)cudaGetLastError();
 }
+static inline bool pool_vec_ok(const PoolGeom& g, const void* a, const void* b) {
+  return (g.C % 4) == 0 && ((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0 && (long long)g.N * g.P * g.Q * (g.C / 4) < (1ll << 31) &&
+         (long long)g.N * g.H * g.W < (1ll << 31);
+}
 XB_API int xb_pool_forward(const float* x, float* y, const int* geom12, int average, cudaStream_t st) {
   PoolGeom g; memcpy(&g, geom12, sizeof(g));
   long long n = (long long)g.N * g.P * g.Q * g.C;
-  if (average) avgpool_fwd_kernel<<<grid_for(n), NT, 0, st>>>(x, y, g);
+  if (pool_vec_ok(g, x, y)) {
+    if (average) pool_fwd_v4_kernel<true><<<grid_for(n / 4), NT, 0, st>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), g);
+    else pool_fwd_v4_kernel<false><<<grid_for(n / 4), NT, 0, st>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), g);
+  } else if (average) avgpool_fwd_kernel<<<grid_for(n), NT, 0, st>>>(x, y, g);
   else maxpool_fwd_kernel<<<grid_for(n), NT, 0, st>>>(x, y, g);
   return (int)cudaGetLastError();
 }
@@ -278,8 +403,17 @@ XB_API int xb_pool_backward(const float* dy, const float* x, float* dx, const in
   if (average) {
     avgpool_bwd_kernel<<<grid_for((long long)g.N * g.H * g.W * g.C), NT, 0, st>>>(dy, dx, g, accum);
   } else {
-    if (!accum) { cudaError_t e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.N * g.H * g.W * g.C, st); if (e != cudaSuccess) return (int)e; }
-    maxpool_bwd_kernel<<<grid_for((long long)g.N * g.P * g.Q * g.C), NT, 0, st>>>(dy, x, dx, g);
+    const long long n = (long long)g.N * g.P * g.Q * g.C;
+    const bool vec = pool_vec_ok(g, x, dy) && ((uintptr_t)dx % 16) == 0;
+    const bool disjoint = g.kh <= g.sh && g.kw <= g.sw;                       // a position belongs to at most one window
+    const bool covered = disjoint && g.kh == g.sh && g.kw == g.sw && g.ph == 0 && g.pw == 0 && (long long)g.P * g.sh >= g.H && (long long)g.Q * g.sw >= g.W;
+    if (!accum && !(vec && covered)) { cudaError_t e = cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)g.N * g.H * g.W * g.C, st); if (e != cudaSuccess) return (int)e; }
+    if (vec && disjoint)
+      maxpool_bwd_v4_kernel<true><<<grid_for(n / 4), NT, 0, st>>>(reinterpret_cast<const float4*>(dy), reinterpret_cast<const float4*>(x), dx, g, accum);
+    else if (vec)
+      maxpool_bwd_v4_kernel<false><<<grid_for(n / 4), NT, 0, st>>>(reinterpret_cast<const float4*>(dy), reinterpret_cast<const float4*>(x), dx, g, accum);
+    else
+      maxpool_bwd_kernel<<<grid_for(n), NT, 0, st>>>(dy, x, dx, g);
   }
   return (int)cudaGetLastError();
 }

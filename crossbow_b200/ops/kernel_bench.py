@@ -173,6 +173,55 @@ def bench_optimiser(lib, timer, n, iters):
     return dict(op="fused_optimiser", n=n, us=round(med, 2), best_us=round(best, 2), bytes=4 * n * 7, flops=0)
 
 
+def bench_pointwise(lib, timer, op, iters):
+    """Element-wise / pooling / loss kernels on the shapes they have in ResNet-50 (batch 32) and VGG-16 (batch 128)."""
+    dev = "cuda"
+    s = torch.cuda.current_stream().cuda_stream
+    tp = L.XbTaskParams()
+    tp.training, tp.task_id, tp.seed_lo = 1, 3, 17
+    tpd = torch.frombuffer(bytearray(bytes(tp)), dtype=torch.uint8).to(dev)
+    if op in ("relu_fwd", "relu_bwd", "dropout"):
+        n = 32 * 56 * 56 * 256 if op != "dropout" else 128 * 32 * 32 * 64
+        x, y, dy, dx = (torch.randn(n, device=dev) for _ in range(4))
+        if op == "relu_fwd":
+            fn, bytes_ = (lambda: lib.xb_act_forward(x.data_ptr(), y.data_ptr(), n, 0, 0.0, 0.0, s)), 8 * n
+        elif op == "relu_bwd":
+            fn, bytes_ = (lambda: lib.xb_act_backward(dy.data_ptr(), x.data_ptr(), y.data_ptr(), dx.data_ptr(), n, 0, 0.0, 0.0, 0, s)), 12 * n
+        else:
+            fn, bytes_ = (lambda: lib.xb_dropout(x.data_ptr(), y.data_ptr(), n, 0.3, 5, tpd.data_ptr(), 0, s)), 8 * n
+        shape = [n]
+    elif op in ("maxpool_fwd", "maxpool_bwd", "avgpool_fwd"):
+        if op == "avgpool_fwd":
+            N, H, W, Cc, R, st = 32, 7, 7, 2048, 7, 1
+        else:
+            N, H, W, Cc, R, st = 32, 112, 112, 64, 3, 2
+        P = -(-(H - R) // st) + 1                      # ceil mode, no padding (the reference's ResNet-50 pooling)
+        geo = (C.c_int * 12)(N, H, W, Cc, P, P, R, R, st, st, 0, 0)
+        x, dx = torch.randn(N * H * W * Cc, device=dev), torch.empty(N * H * W * Cc, device=dev)
+        y, dy = torch.empty(N * P * P * Cc, device=dev), torch.randn(N * P * P * Cc, device=dev)
+        if op == "maxpool_bwd":
+            fn, bytes_ = (lambda: lib.xb_pool_backward(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), geo, 0, 0, s)), 4 * (dy.numel() + 3 * x.numel())
+        else:
+            fn, bytes_ = (lambda: lib.xb_pool_forward(x.data_ptr(), y.data_ptr(), geo, int(op == "avgpool_fwd"), s)), 4 * (x.numel() + y.numel())
+        shape = [N, H, W, Cc, R, st]
+    elif op == "softmax_xent":
+        rows, classes = 32, 1000
+        logits, probs, dl = torch.randn(rows, classes, device=dev), torch.empty(rows, classes, device=dev), torch.empty(rows, classes, device=dev)
+        labels, res = torch.randint(0, classes, (rows,), dtype=torch.int32, device=dev), torch.zeros(2, device=dev)
+        fn = lambda: lib.xb_softmax_xent(logits.data_ptr(), labels.data_ptr(), probs.data_ptr(), dl.data_ptr(), res.data_ptr(), rows, classes, -1, 0, 0, 1, s)
+        bytes_, shape = 12 * rows * classes, [rows, classes]
+    else:
+        raise SystemExit(f"unknown op {op}")
+    L.check(fn(), op)
+    med, best = timer.run(fn, iters)
+    return dict(op=op, shape=shape, us=round(med, 2), best_us=round(best, 2), bytes=bytes_, flops=0)
+
+
+POINTWISE = ("relu_fwd", "relu_bwd", "dropout", "maxpool_fwd", "maxpool_bwd", "avgpool_fwd", "softmax_xent")
+# inner-product layers as the GEMM sees them (rows = batch): VGG-16 512 -> 512 at batch 128, ResNet-50 2048 -> 1000 at batch 32
+FC_SHAPES = [(128, 1, 1, 512, 512, 1, 1, 1, 0), (32, 1, 1, 2048, 1000, 1, 1, 1, 0)]
+
+
 def report(r):
     bw, tf, how = peaks()
     us = r["us"]
@@ -204,11 +253,20 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", action="store_true", help="do not flush L2 between launches")
     ap.add_argument("--stats", action="store_true", help="convolution epilogue also produces batch-norm sums")
-    ap.add_argument("--suite", default=None, choices=[None, "resnet32", "resnet50"])
+    ap.add_argument("--suite", default=None, choices=[None, "resnet32", "resnet50", "pointwise"])
     a = ap.parse_args()
     lib = L.init_device()
     lib.xb_tc_set_slab(3)
     timer = Timer(flush=not a.warm)
+    if a.suite == "pointwise":
+        for op in POINTWISE:
+            report(bench_pointwise(lib, timer, op, a.iters))
+        for sh in FC_SHAPES:
+            for op in ("conv_fprop", "conv_dgrad", "conv_wgrad"):
+                g, _, _ = geom(*sh)
+                impl = "tc" if lib.xb_tc_supported(C.byref(g), {"conv_fprop": 0, "conv_dgrad": 1, "conv_wgrad": 2}[op]) else "simt"
+                report(bench_conv(lib, timer, op, impl, sh, a.iters))
+        return
     if a.suite:
         shapes = RESNET32 if a.suite == "resnet32" else RESNET50
         for sh in shapes:
@@ -235,6 +293,8 @@ def main():
         report(bench_sync(lib, timer, a.n, a.replicas, a.iters))
     elif a.op == "optimiser":
         report(bench_optimiser(lib, timer, a.n, a.iters))
+    elif a.op in POINTWISE:
+        report(bench_pointwise(lib, timer, a.op, a.iters))
     else:
         raise SystemExit(f"unknown op {a.op}")
 
