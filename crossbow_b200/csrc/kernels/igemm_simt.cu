@@ -442,17 +442,36 @@ XB_API int xb_conv_wgrad_simt(const float* dY, const float* X, float* dW, const 
 // ---- batched weight transpose (K,R,S,C) -> (C,R,S,K) for every convolution of a model, ONE launch -------
 struct XbTransposeDesc { long long src_off, dst_off; int K, RS, C; int first_block; };
 
-__global__ void transpose_weights_kernel(const float* __restrict__ w, float* __restrict__ wt, const XbTransposeDesc* __restrict__ d, int nd) {
+// One block = one 32 (k) x 32 (c) tile of one filter tap, moved through shared memory so that both the loads (along c) and
+// the stores (along k) are coalesced.
+__global__ void __launch_bounds__(256) transpose_weights_kernel(const float* __restrict__ w, float* __restrict__ wt, const XbTransposeDesc* __restrict__ d, int nd) {
+  __shared__ float tile[32][33];
   // find the descriptor this block belongs to (descriptors are sorted by first_block)
   int lo = 0, hi = nd - 1;
   while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (d[mid].first_block <= (int)blockIdx.x) lo = mid; else hi = mid - 1; }
   const XbTransposeDesc e = d[lo];
-  long long total = (long long)e.K * e.RS * e.C;
-  long long i = (long long)(blockIdx.x - e.first_block) * blockDim.x + threadIdx.x;   // index in destination order (c, rs, k)
-  if (i >= total) return;
-  int k = (int)(i % e.K); long long t = i / e.K; int rs = (int)(t % e.RS); int c = (int)(t / e.RS);
-  wt[e.dst_off + i] = w[e.src_off + ((long long)k * e.RS + rs) * e.C + c];
+  const int kt = (e.K + 31) >> 5, ct = (e.C + 31) >> 5;
+  int b = (int)blockIdx.x - e.first_block;
+  const int c0 = (b % ct) << 5; b /= ct;
+  const int k0 = (b % kt) << 5; const int rs = b / kt;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const float* src = w + e.src_off;
+  float* dst = wt + e.dst_off;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int k = k0 + ty + j, c = c0 + tx;
+    tile[ty + j][tx] = (k < e.K && c < e.C) ? src[((long long)k * e.RS + rs) * e.C + c] : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int c = c0 + ty + j, k = k0 + tx;
+    if (c < e.C && k < e.K) dst[((long long)c * e.RS + rs) * e.K + k] = tile[tx][ty + j];
+  }
 }
+
+// blocks the kernel above needs for one (K, RS, C) filter bank - the caller lays out first_block with this
+XB_API int xb_transpose_blocks(int K, int RS, int C) { return ((K + 31) / 32) * ((C + 31) / 32) * RS; }
 
 XB_API int xb_transpose_weights(const float* w, float* wt, const XbTransposeDesc* descs_dev, int nd, int total_blocks, cudaStream_t st) {
   if (nd == 0) return 0;

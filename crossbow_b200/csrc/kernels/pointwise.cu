@@ -273,6 +273,27 @@ __global__ void avgpool_bwd_kernel(const float* __restrict__ dy, float* __restri
   }
 }
 
+// 16-byte form of the kernel above (C % 4 == 0): one thread = four channels of one input position
+__global__ void __launch_bounds__(NT) avgpool_bwd_v4_kernel(const float4* __restrict__ dy, float4* __restrict__ dx, PoolGeom g, int accum) {
+  const unsigned C4 = (unsigned)g.C >> 2, n = (unsigned)g.N * g.H * g.W * C4;
+  const float inv = 1.f / (float)(g.kh * g.kw);
+  for (unsigned i = blockIdx.x * NT + threadIdx.x; i < n; i += gridDim.x * NT) {
+    const unsigned c = i % C4; unsigned t = i / C4; const int ix = t % g.W; t /= g.W; const int iy = t % g.H, b = t / g.H;
+    float4 s = make_float4(0, 0, 0, 0);
+    for (int r = 0; r < g.kh; ++r) {
+      const int ty = iy + g.ph - r; if (ty < 0 || ty % g.sh) continue; const int p = ty / g.sh; if (p >= g.P) continue;
+      for (int ss = 0; ss < g.kw; ++ss) {
+        const int tx = ix + g.pw - ss; if (tx < 0 || tx % g.sw) continue; const int q = tx / g.sw; if (q >= g.Q) continue;
+        const float4 v = dy[(((long long)b * g.P + p) * g.Q + q) * C4 + c];
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
+    }
+    float4 o = make_float4(s.x * inv, s.y * inv, s.z * inv, s.w * inv);
+    if (accum) { const float4 d = dx[i]; o.x += d.x; o.y += d.y; o.z += d.z; o.w += d.w; }
+    dx[i] = o;
+  }
+}
+
 // across-channel LRN (Caffe): y = x * (k + alpha/size * sum_{window} x^2)^-beta
 __global__ void lrn_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ scale, long long M, int C, int size, float alpha, float beta, float k) {
   long long n = M * C; int half = size / 2;
@@ -345,6 +366,29 @@ __global__ void colsum_kernel(const float* __restrict__ a, float* __restrict__ o
     atomicAdd(&out[c], s);
   }
 }
+// the same for C % 4 == 0, C <= 1024: the block's 256 threads form (256 / C4) row lanes x C4 column groups, every thread
+// adds 16-byte loads of its rows four at a time, the row lanes are folded through shared memory, one atomic per column
+__global__ void __launch_bounds__(NT) colsum_v4_kernel(const float4* __restrict__ a, float* __restrict__ out, int M, int C4, int rows_per_block) {
+  __shared__ float4 red[NT];
+  const int lanes = NT / C4, cg = threadIdx.x % C4, lane = threadIdx.x / C4;
+  const int r0 = blockIdx.x * rows_per_block, r1 = min(M, r0 + rows_per_block);
+  float4 s = make_float4(0, 0, 0, 0);
+  if (lane < lanes) {
+    int r = r0 + lane;
+    for (; r + 3 * lanes < r1; r += 4 * lanes) {
+      const float4 v0 = a[(long long)r * C4 + cg], v1 = a[(long long)(r + lanes) * C4 + cg], v2 = a[(long long)(r + 2 * lanes) * C4 + cg],
+                   v3 = a[(long long)(r + 3 * lanes) * C4 + cg];
+      s.x += (v0.x + v1.x) + (v2.x + v3.x); s.y += (v0.y + v1.y) + (v2.y + v3.y); s.z += (v0.z + v1.z) + (v2.z + v3.z); s.w += (v0.w + v1.w) + (v2.w + v3.w);
+    }
+    for (; r < r1; r += lanes) { const float4 v = a[(long long)r * C4 + cg]; s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w; }
+  }
+  red[threadIdx.x] = s;
+  __syncthreads();
+  if (lane == 0) {
+    for (int l = 1; l < lanes; ++l) { const float4 v = red[l * C4 + cg]; s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w; }
+    atomicAdd(out + 4 * cg, s.x); atomicAdd(out + 4 * cg + 1, s.y); atomicAdd(out + 4 * cg + 2, s.z); atomicAdd(out + 4 * cg + 3, s.w);
+  }
+}
 }  // namespace
 
 XB_API int xb_act_forward(const float* x, float* y, long long n, int mode, float slope, float ceiling, cudaStream_t st) {
@@ -401,7 +445,10 @@ XB_API int xb_pool_forward(const float* x, float* y, const int* geom12, int aver
 XB_API int xb_pool_backward(const float* dy, const float* x, float* dx, const int* geom12, int average, int accum, cudaStream_t st) {
   PoolGeom g; memcpy(&g, geom12, sizeof(g));
   if (average) {
-    avgpool_bwd_kernel<<<grid_for((long long)g.N * g.H * g.W * g.C), NT, 0, st>>>(dy, dx, g, accum);
+    if (pool_vec_ok(g, dy, dx) && (long long)g.N * g.H * g.W * (g.C / 4) < (1ll << 31))
+      avgpool_bwd_v4_kernel<<<grid_for((long long)g.N * g.H * g.W * (g.C / 4)), NT, 0, st>>>(reinterpret_cast<const float4*>(dy), reinterpret_cast<float4*>(dx), g, accum);
+    else
+      avgpool_bwd_kernel<<<grid_for((long long)g.N * g.H * g.W * g.C), NT, 0, st>>>(dy, dx, g, accum);
   } else {
     const long long n = (long long)g.N * g.P * g.Q * g.C;
     const bool vec = pool_vec_ok(g, x, dy) && ((uintptr_t)dx % 16) == 0;
@@ -437,6 +484,12 @@ XB_API int xb_nhwc_to_nchw(const float* src, float* dst, int N, int C, int H, in
   return (int)cudaGetLastError();
 }
 XB_API int xb_colsum(const float* a, float* out, int M, int C, cudaStream_t st) {
+  if (C % 4 == 0 && C <= 4 * NT && ((uintptr_t)a % 16) == 0 && M >= 64) {
+    const int C4 = C / 4, lanes = NT / C4;
+    int rpb = xb_ceil_div(M, 296); if (rpb < lanes * 8) rpb = lanes * 8;
+    colsum_v4_kernel<<<xb_ceil_div(M, rpb), NT, 0, st>>>(reinterpret_cast<const float4*>(a), out, M, C4, rpb);
+    return (int)cudaGetLastError();
+  }
   int rpb = xb_ceil_div(M, 148); if (rpb < 32) rpb = 32;
   colsum_kernel<<<xb_ceil_div(M, rpb), NT, 0, st>>>(a, out, M, C, rpb);
   return (int)cudaGetLastError();

@@ -695,7 +695,7 @@ class Lowering:
         for i, (off, K, RS, Cc) in enumerate(self.transposes):
             descs[i].src_off, descs[i].dst_off, descs[i].K, descs[i].RS, descs[i].C = off, off, K, RS, Cc
             descs[i].first_block = blocks
-            blocks += (K * RS * Cc + 255) // 256
+            blocks += L.load().xb_transpose_blocks(K, RS, Cc)
         raw = torch.frombuffer(bytearray(bytes(descs)), dtype=torch.uint8).to(self.device)
         self.keep.append(raw)
         self.ops[slot] = _op(L.OP_TRANSPOSE_W, ia=[len(self.transposes), blocks], p=[self.weights, self.replica.wt, raw])

@@ -107,6 +107,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_conv1x1_tma_supported", I, G, I)
     _sig(lib, "xb_conv3x3_slab_supported", I, G, I)
     _sig(lib, "xb_transpose_weights", I, P, P, P, I, I, P)
+    _sig(lib, "xb_transpose_blocks", I, I, I, I)
     _sig(lib, "xb_bn_stats", I, P, P, I, I, P)
     _sig(lib, "xb_bn_forward", I, P, P, P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, F, P)
     _sig(lib, "xb_bn_backward", I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P)
