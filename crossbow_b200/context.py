@@ -116,6 +116,9 @@ class ExecutionContext:
                                  callback_handlers=max(1, sys.number_of_callback_handlers), task_timeout_s=sys.task_timeout)
         self._native = mk(self.clock.wpc)
         self._native.set_executor(sub, wait, sync, batch, ctx)
+        if sys.run_ahead > 1:
+            # the next task of a replica is handed to the device while the previous one is still running
+            self._native.set_run_ahead(sys.run_ahead, e.native_wait_task())
         train_ds = mc.getDataset(Phase.TRAIN)
         if hasattr(train_ds, "source"):              # C++ data set: batches go from its ring to the device without Python
             self._native.set_data_source(train_ds.source(stride=self.world, offset=self.rank, timeout_s=sys.task_timeout))

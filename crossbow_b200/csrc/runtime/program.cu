@@ -287,6 +287,10 @@ XB_API int xb_program_launch_marked(XbProgram* p, cudaStream_t st, cudaEvent_t* 
 }
 XB_API int xb_program_launch(XbProgram* p, cudaStream_t st) { return xb_program_launch_marked(p, st, nullptr, 0); }
 
+__global__ void copy_result_kernel(const float* __restrict__ src, float* __restrict__ dst) {
+  if (threadIdx.x < 2) dst[threadIdx.x] = src[threadIdx.x];
+}
+
 // ---- learner: stream + staging buffers + programs ------------------------------------------------------------------
 struct XbLearner {
   cudaStream_t stream = nullptr;
@@ -299,6 +303,14 @@ struct XbLearner {
   XbTaskParams* h_params = nullptr;   // pinned; uploaded by the program's first node
   float* h_result = nullptr;          // pinned + mapped: [loss, accuracy] written by the loss kernel
   float* d_result = nullptr;          // device alias of h_result
+  // Run-ahead: a learner may hold several tasks in flight.  After each task a one-thread kernel copies the live result pair
+  // into the ring slot of that task (floats [4 + 2 s, 4 + 2 s + 2) of the same mapped allocation) and an event of its own
+  // is recorded, so the host can wait for and read one particular task.
+  static constexpr int RING = 4;
+  cudaEvent_t ring_done[RING] = {};
+  unsigned long long ring_task[RING] = {};
+  int ring_phase[RING] = {};
+  unsigned long long submitted = 0;
   int busy = 0;
 };
 
@@ -312,6 +324,7 @@ XB_API XbLearner* xb_learner_create(int priority, void* d_examples, long long ex
   cudaEventCreate(&l->start);
   cudaHostAlloc((void**)&l->h_params, sizeof(XbTaskParams), cudaHostAllocDefault);
   cudaHostAlloc((void**)&l->h_result, 64, cudaHostAllocMapped);
+  for (int i = 0; i < XbLearner::RING; ++i) { cudaEventCreateWithFlags(&l->ring_done[i], cudaEventDisableTiming); l->ring_task[i] = ~0ull; }
   memset(l->h_params, 0, sizeof(XbTaskParams));
   memset(l->h_result, 0, 64);
   cudaHostGetDevicePointer((void**)&l->d_result, l->h_result, 0);
@@ -324,6 +337,7 @@ XB_API void xb_learner_destroy(XbLearner* l) {
   cudaStreamSynchronize(l->stream);
   cudaEventDestroy(l->done); cudaEventDestroy(l->start);
   for (cudaEvent_t ev : l->bucket) if (ev) cudaEventDestroy(ev);
+  for (cudaEvent_t ev : l->ring_done) if (ev) cudaEventDestroy(ev);
   cudaFreeHost(l->h_params); cudaFreeHost(l->h_result);
   cudaStreamDestroy(l->stream);
   delete l;
@@ -347,9 +361,29 @@ XB_API int xb_learner_submit(XbLearner* l, const void* h_examples, const void* h
       if (!l->bucket[b]) XB_CUDA_CHECK(cudaEventCreateWithFlags(&l->bucket[b], cudaEventDisableTiming));
   int e = xb_program_launch_marked(p, l->stream, l->bucket, XB_MAX_BUCKETS);
   if (e) return e;
+  {
+    const int slot = (int)(l->submitted++ % XbLearner::RING);
+    l->ring_task[slot] = params->task_id; l->ring_phase[slot] = phase;
+    copy_result_kernel<<<1, 32, 0, l->stream>>>(l->d_result, l->d_result + 4 + 2 * slot);
+    XB_CUDA_CHECK(cudaGetLastError());
+    XB_CUDA_CHECK(cudaEventRecord(l->ring_done[slot], l->stream));
+  }
   XB_CUDA_CHECK(cudaEventRecord(l->done, l->stream));
   l->busy = 1;
   return 0;
+}
+// Block until task `task` (the most recent submission with that id; of that phase unless phase < 0) has finished and
+// return ITS loss / accuracy.
+XB_API int xb_learner_wait_task(XbLearner* l, unsigned long long task, int phase, float* loss, float* accuracy) {
+  for (unsigned long long back = 0; back < (unsigned long long)XbLearner::RING && back < l->submitted; ++back) {
+    const int slot = (int)((l->submitted - 1 - back) % XbLearner::RING);
+    if (l->ring_task[slot] != (task & 0xffffffffull) || (phase >= 0 && l->ring_phase[slot] != phase)) continue;
+    XB_CUDA_CHECK(cudaEventSynchronize(l->ring_done[slot]));
+    if (loss) *loss = l->h_result[4 + 2 * slot];
+    if (accuracy) *accuracy = l->h_result[4 + 2 * slot + 1];
+    return 0;
+  }
+  return -XB_BAD_ARG;
 }
 // Block until the learner's last task has finished; loss/accuracy are then valid in the result slot.
 XB_API int xb_learner_wait(XbLearner* l, float* loss, float* accuracy) {
@@ -562,6 +596,11 @@ XB_API int xb_exec_wait(void* ctx, int learner, float* loss, float* acc) {
   XbExec* e = (XbExec*)ctx;
   if (learner < 0 || learner >= (int)e->learners.size()) return -XB_BAD_ARG;
   return xb_learner_wait(e->learners[learner], loss, acc);
+}
+XB_API int xb_exec_wait_task(void* ctx, int learner, unsigned long long task, float* loss, float* acc) {
+  XbExec* e = (XbExec*)ctx;
+  if (learner < 0 || learner >= (int)e->learners.size()) return -XB_BAD_ARG;
+  return xb_learner_wait_task(e->learners[learner], task, -1, loss, acc);
 }
 XB_API int xb_exec_synchronise(void* ctx, unsigned long long clock, const unsigned char* mask, int n, int copy) {
   XbExec* e = (XbExec*)ctx;

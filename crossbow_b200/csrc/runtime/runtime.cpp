@@ -47,6 +47,9 @@ struct Executor {
   int (*take)(void* dctx, uint64_t task, int phase, const void** examples, const void** labels);
   void (*release)(void* dctx, int slot);
   void* dctx;
+  // optional (run-ahead): block until task `task` of that learner is complete.  A learner may then hold several tasks in
+  // flight, so "the learner's task" of `wait` is no longer unique.
+  int (*wait_task)(void* ctx, int learner, uint64_t task, float* loss, float* accuracy);
 };
 
 // 64-byte result slot, same state machine as the reference's ring (0 free -> 1 being written -> 2 ready -> 3 consumed -> 0)
@@ -72,14 +75,25 @@ class Runtime {
         n_task_handlers_(task_handlers), n_callback_handlers_(callback_handlers < 1 ? 1 : callback_handlers), timeout_(task_timeout_s),
         task_q_(4096), cb_q_(4096) {
     for (int i = 0; i < nslots_; ++i) slots_[i].state.store(0);
-    for (int i = 0; i < ThetaQueue::kMaxSlots; ++i) { replica_clock_[i].store(0); replica_updates_[i].store(0); busy_since_[i].store(0.0); }
+    for (int i = 0; i < ThetaQueue::kMaxSlots; ++i) { replica_clock_[i].store(0); replica_updates_[i].store(0); busy_since_[i].store(0.0); inflight_[i].store(0); }
     memset(&exec_, 0, sizeof(exec_));
     t_origin_ = Clock::now();
     start_threads();
   }
   ~Runtime() { stop_threads(); delete[] slots_; }
 
-  void set_executor(const Executor& e) { auto t = exec_.take; auto r = exec_.release; auto d = exec_.dctx; exec_ = e; exec_.take = t; exec_.release = r; exec_.dctx = d; }
+  void set_executor(const Executor& e) {
+    auto t = exec_.take; auto r = exec_.release; auto d = exec_.dctx; auto w = exec_.wait_task;
+    exec_ = e; exec_.take = t; exec_.release = r; exec_.dctx = d;
+    if (!exec_.wait_task) exec_.wait_task = w;
+  }
+  // Run-ahead: a replica goes back to the free list as soon as its task has been handed to the device, until `depth` of
+  // its tasks are in flight.  The device orders them (one stream per learner; a learner's next task waits for the
+  // synchronisation event), so the host no longer sits between the end of one task and the start of the next.
+  void set_run_ahead(int depth, decltype(Executor::wait_task) wait_task) {
+    depth_ = (depth > 1 && wait_task) ? (depth > 4 ? 4 : depth) : 1;
+    exec_.wait_task = wait_task;
+  }
   void set_data_source(decltype(Executor::take) take, decltype(Executor::release) release, void* dctx) { exec_.take = take; exec_.release = release; exec_.dctx = dctx; }
   void set_target_loss(float t) { target_loss_ = t; }
   void set_affinity(int first_core) { first_core_ = first_core; }
@@ -187,6 +201,7 @@ class Runtime {
     int e = exec_.submit(exec_.ctx, it.learner, it.ex, it.lab, it.task, it.phase);
     if (e != 0) { char b[96]; snprintf(b, sizeof b, "task submission failed with code %d", e); fail(b); return false; }
     if (!push_bounded(cb_q_, it)) { fail("callback queue stayed full"); return false; }
+    if (depth_ > 1 && inflight_[it.learner].fetch_add(1) + 1 < depth_) theta_.release(it.learner);
     return true;
   }
   // Called by the dispatcher after the wpc-th task of a clock has been handed over.
@@ -251,7 +266,8 @@ class Runtime {
       spins = 0;
       if (n_task_handlers_ == 0) handed_.fetch_add(1);
       float loss = NAN, acc = NAN;
-      int e = failed_.load() ? -1 : exec_.wait(exec_.ctx, it.learner, &loss, &acc);
+      int e = failed_.load() ? -1
+              : (depth_ > 1 ? exec_.wait_task(exec_.ctx, it.learner, it.task, &loss, &acc) : exec_.wait(exec_.ctx, it.learner, &loss, &acc));
       if (e != 0 && !failed_.load()) { char b[96]; snprintf(b, sizeof b, "task %llu failed on learner %d with code %d", (unsigned long long)it.task, it.learner, e); fail(b); }
       if (it.slot >= 0 && exec_.release) exec_.release(exec_.dctx, it.slot);      // the batch has been consumed
       // publish the result slot: 0 -> 1, fill, 1 -> 2
@@ -263,7 +279,8 @@ class Runtime {
       s.state.store(2, std::memory_order_release);
       replica_updates_[it.learner].fetch_add(1);
       busy_since_[it.learner].store(0.0);
-      theta_.release(it.learner);
+      // (run-ahead: the replica was already released at submission unless it was then at its in-flight limit)
+      if (depth_ <= 1 || inflight_[it.learner].fetch_sub(1) - 1 == depth_ - 1) theta_.release(it.learner);
       completed_.fetch_add(1);
     }
   }
@@ -315,6 +332,8 @@ class Runtime {
   std::atomic<uint64_t> replica_clock_[ThetaQueue::kMaxSlots];
   std::atomic<uint64_t> replica_updates_[ThetaQueue::kMaxSlots];
   std::atomic<double> busy_since_[ThetaQueue::kMaxSlots];
+  std::atomic<int> inflight_[ThetaQueue::kMaxSlots];
+  int depth_ = 1;
   std::atomic<bool> running_{false}, stop_{false}, failed_{false};
   std::string error_;
   float target_loss_ = -1.f;
@@ -350,6 +369,14 @@ static int fake_wait(void* c, int learner, float* loss, float* acc) {
   *loss = 1.0f / (1.0f + (float)task); *acc = (float)learner;
   return 0;
 }
+static int fake_wait_task(void* c, int learner, uint64_t task, float* loss, float* acc) {
+  auto* f = (FakeExec*)c;
+  if ((int)task == f->hang_task.load()) { std::this_thread::sleep_for(std::chrono::milliseconds(1500)); }
+  else if (f->task_us > 0) std::this_thread::sleep_for(std::chrono::microseconds(f->task_us));
+  if ((int)task == f->fail_task.load()) return 77;
+  *loss = 1.0f / (1.0f + (float)task); *acc = (float)learner;
+  return 0;
+}
 static int fake_sync(void* c, uint64_t, const unsigned char* mask, int n, int) {
   auto* f = (FakeExec*)c; f->syncs.fetch_add(1);
   std::lock_guard<std::mutex> g(f->mu); f->last_mask.assign(mask, mask + n); return 0;
@@ -373,6 +400,8 @@ RT_API void rt_set_executor(void* r, void* submit, void* wait, void* synchronise
 RT_API void rt_set_data_source(void* r, void* take, void* release, void* dctx) {
   ((Runtime*)r)->set_data_source((decltype(Executor::take))take, (decltype(Executor::release))release, dctx);
 }
+RT_API void rt_set_run_ahead(void* r, int depth, void* wait_task) { ((Runtime*)r)->set_run_ahead(depth, (decltype(Executor::wait_task))wait_task); }
+RT_API void rt_fake_run_ahead(void* r, int depth) { ((Runtime*)r)->set_run_ahead(depth, fake_wait_task); }
 RT_API void rt_set_target_loss(void* r, float t) { ((Runtime*)r)->set_target_loss(t); }
 RT_API void rt_set_affinity(void* r, int first_core) { ((Runtime*)r)->set_affinity(first_core); }
 RT_API long long rt_train(void* r, long long ntasks, int phase) { return ((Runtime*)r)->train(ntasks, phase); }

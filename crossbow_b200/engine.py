@@ -324,6 +324,10 @@ class GpuEngine:
         addr = lambda name: C.cast(getattr(lib, name), C.c_void_p).value
         return self._exec, addr("xb_exec_submit"), addr("xb_exec_wait"), addr("xb_exec_synchronise"), addr("xb_exec_batch")
 
+    def native_wait_task(self) -> int:
+        """Address of the executor's per-task wait (run-ahead scheduling)."""
+        return C.cast(self.lib.xb_exec_wait_task, C.c_void_p).value
+
     def epoch_to_native(self):
         """The synchronisation epoch is one counter whichever side enqueues the kernels: the flags in peer memory hold the
         epochs already used, so the native executor must continue after the last one enqueued from Python."""

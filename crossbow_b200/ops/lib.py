@@ -172,6 +172,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_sync_desc_size", I)
     _sig(lib, "xb_exec_copy_signal", I, P)
     _sig(lib, "xb_exec_epoch", c_uint, P)
+    _sig(lib, "xb_learner_wait_task", I, P, C.c_ulonglong, I, C.POINTER(c_float), C.POINTER(c_float))
     _sig(lib, "xb_exec_set_epoch", None, P, c_uint)
     assert lib.xb_sync_desc_size() == C.sizeof(XbSyncDesc), (lib.xb_sync_desc_size(), C.sizeof(XbSyncDesc))
     # plumbing

@@ -27,6 +27,8 @@ def load() -> C.CDLL:
     _sig(lib, "rt_destroy", None, P)
     _sig(lib, "rt_set_executor", None, P, P, P, P, P, P)
     _sig(lib, "rt_set_target_loss", None, P, C.c_float)
+    _sig(lib, "rt_set_run_ahead", None, P, I, P)
+    _sig(lib, "rt_fake_run_ahead", None, P, I)
     _sig(lib, "rt_set_affinity", None, P, I)
     _sig(lib, "rt_train", L, P, L, I)
     _sig(lib, "rt_drain", I, P, D)
@@ -132,6 +134,14 @@ class Runtime:
 
     def set_executor(self, submit: int, wait: int, synchronise: int, batch: int, ctx: int):
         self.lib.rt_set_executor(self.h, submit, wait, synchronise, batch, ctx)
+
+    def set_run_ahead(self, depth: int, wait_task: int = 0):
+        """Let every replica hold up to ``depth`` tasks in flight (``wait_task``: address of the executor's per-task wait;
+        0 with an attached fake executor uses the fake's)."""
+        if wait_task:
+            self.lib.rt_set_run_ahead(self.h, depth, wait_task)
+        else:
+            self.lib.rt_fake_run_ahead(self.h, depth)
 
     def set_data_source(self, source_handle: int):
         """Batches come from a native data set (``crossbow_b200.data.native``) instead of the executor's own ring."""

@@ -46,6 +46,31 @@ def test_tasks_results_and_clock(handlers):
     rt.close()
 
 
+@pytest.mark.parametrize("handlers", [0, 2])
+def test_run_ahead_keeps_two_tasks_per_replica_in_flight(handlers):
+    # every replica is released at submission until two of its tasks are in flight; results are still attributed per task
+    rt = Runtime(learners=4, wpc=4, task_handlers=handlers, callback_handlers=2, task_timeout_s=5)
+    rt.attach_fake(4, task_us=2000)
+    rt.set_run_ahead(2)
+    t0 = time.perf_counter()
+    assert rt.train(8) == 8                                   # two rounds are handed over without waiting for a completion
+    assert rt.tasks_completed() < 8                           # (each fake task takes 2 ms)
+    assert rt.train(32) == 32
+    rt.drain(10)
+    assert rt.tasks_completed() == 40 and rt.clock() == 10 and rt.fake_syncs() == 10
+    hist = rt.history(64)
+    assert [h[0] for h in hist] == list(range(40))
+    assert all(abs(h[1] - 1.0 / (1.0 + h[0])) < 1e-6 for h in hist)          # the loss of task t, not of a later task
+    assert all(int(h[2]) == h[0] % 4 for h in hist)                          # round robin over the four replicas
+    # a failed task is still reported with run-ahead on
+    rt.inject(fail_task=43)
+    with pytest.raises(RuntimeError_):
+        rt.train(8)
+        rt.drain(5)
+    assert rt.failed()
+    rt.close()
+
+
 def test_bsp_masks_all_ssp_masks_idle_only():
     rt = Runtime(learners=3, wpc=3, sync_model=0)
     rt.attach_fake(3, task_us=2000)
