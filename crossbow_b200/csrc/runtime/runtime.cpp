@@ -183,8 +183,9 @@ class Runtime {
  private:
   double now() const { return seconds_since(t_origin_); }
   long long fail(const char* why) {
-    bool expected = false;
-    if (failed_.compare_exchange_strong(expected, true)) error_ = why;
+    // the message is in place before anyone can see the flag (a reader of failed() may ask for error() at once)
+    std::lock_guard<std::mutex> g(err_mu_);
+    if (!failed_.load()) { error_ = why; failed_.store(true); }
     return -1;
   }
   template <class Q>
@@ -336,6 +337,7 @@ class Runtime {
   int depth_ = 1;
   std::atomic<bool> running_{false}, stop_{false}, failed_{false};
   std::string error_;
+  std::mutex err_mu_;
   float target_loss_ = -1.f;
   std::vector<std::thread> threads_;
   std::mutex tot_mu_;

@@ -3,6 +3,7 @@ from ._builder import ModelSpec, Net
 from .lenet import lenet, lenet_caffe
 from .resnet import resnet_cifar, resnet_imagenet
 from .vgg import vgg16_cifar
+from .inception import googlenet_v1, inception_v3
 from .simple import (alexnet_v2, convnet_cifar, lenet_batchnorm, logistic_regression, matrix_factorisation, mini_inception, mlp,
                      overfeat, vgg_a)
 
@@ -10,6 +11,7 @@ REGISTRY = {
     "lenet": lenet, "lenet-caffe": lenet_caffe, "vgg16": vgg16_cifar, "logistic-regression": logistic_regression,
     "mlp": mlp, "convnet": convnet_cifar, "lenet-batchnorm": lenet_batchnorm, "alexnet": alexnet_v2,
     "mini-inception": mini_inception, "overfeat": overfeat, "vgg-a": vgg_a, "matrix-factorisation": matrix_factorisation,
+    "inception-v3": inception_v3, "googlenet": googlenet_v1,
     **{f"resnet{d}": (lambda d=d, **kw: resnet_cifar(d, **kw)) for d in (8, 20, 32, 44, 56, 110)},
     **{f"resnet{d}": (lambda d=d, **kw: resnet_imagenet(d, **kw)) for d in (18, 34, 50, 101, 152)},
 }

@@ -48,8 +48,11 @@ class Net:
         return InitialiserConf().setType(self.init_type)
 
     def conv(self, name, outputs, k, stride=1, pad=0, bias=False, inputs=None, winit=None, binit=None):
-        c = ConvConf().setNumberOfOutputs(outputs).setKernelSize(2, k, k).setStrideSize(2, stride, stride) \
-            .setPaddingSize(2, pad, pad).setBias(bias)
+        """`k`, `stride`, `pad`: one number, or (height, width)."""
+        hw = lambda v: tuple(v) if isinstance(v, (tuple, list)) else (v, v)
+        (kh, kw), (sh, sw), (ph, pw) = hw(k), hw(stride), hw(pad)
+        c = ConvConf().setNumberOfOutputs(outputs).setKernelSize(2, kh, kw).setStrideSize(2, sh, sw) \
+            .setPaddingSize(2, ph, pw).setBias(bias)
         c.setWeightInitialiser(winit or self.winit())
         if binit is not None:
             c.setBiasInitialiser(binit)

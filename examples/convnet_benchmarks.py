@@ -14,7 +14,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--model", default="alexnet", choices=["alexnet", "overfeat", "vgg-a", "mini-inception"])
+    ap.add_argument("--model", default="alexnet", choices=["alexnet", "overfeat", "vgg-a", "googlenet", "mini-inception", "inception-v3"])
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()

@@ -200,6 +200,8 @@ CASES = [
     ("resnet50", 2, dict(size=64, classes=10)),
     ("mini-inception", 4, {}),
     ("alexnet", 2, dict(size=96, classes=10)),
+    ("inception-v3", 2, dict(size=139, width=0.25, classes=10)),        # rectangular 1x7 / 7x1 / 1x3 / 3x1 filters, six-way concat
+    ("googlenet", 2, dict(size=64, width=0.5, classes=10)),
 ]
 
 
