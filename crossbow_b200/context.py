@@ -79,6 +79,9 @@ class ExecutionContext:
             from .parallel.peer import dist_info
             from .engine import GpuEngine
             self.rank, self.world, local = dist_info()
+            if sys.trace_level > 0:                      # before the task programs are captured (operator ranges)
+                from .utils import trace
+                trace.enable(sys.trace_level)
             self.engine = GpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,
                                     replicas=sys.number_of_gpu_models, wpc=wpc, rank=self.rank, world=self.world,
                                     device_index=local, use_graphs=sys.use_cuda_graphs, seed=sys.random_seed,
@@ -337,6 +340,13 @@ class ExecutionContext:
                 rt.close()
         self._native = self._native_test = None
         if self.engine is not None:
+            if self.sys.gpu and self.sys.trace_level > 0:
+                from .utils import trace
+                self.trace_summary = trace.summary(clear=True)
+                if not self.quiet:                       # what the reference prints per callback handler at shutdown
+                    for name, st in self.trace_summary.items():
+                        print(f"[TRACE] {name}: " + " ".join(f"{k}={v:.3f}" if isinstance(v, float) else f"{k}={v}" for k, v in st.items()), flush=True)
+                trace.enable(0)
             self.engine.destroy()
             self.engine = None
         if self.sys.queue_measurements and not self.quiet:

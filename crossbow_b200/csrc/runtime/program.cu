@@ -6,6 +6,9 @@
 // pointers and shapes resolved; a learner replays it either directly or, normally, as a captured CUDA graph, so a
 // task costs one graph launch on the host.  Values that differ between tasks (learning rate, task id, ...) live in a
 // per-learner XbTaskParams block that is uploaded by the first node of the program.
+#include <nvtx3/nvToolsExt.h>
+#include <chrono>
+#include <mutex>
 #include "../kernels/common.cuh"
 #include <vector>
 #include <string.h>
@@ -207,9 +210,45 @@ XB_API int xb_program_launches(XbProgram* p) { return p->launches; }
 XB_API int xb_program_num_ops(XbProgram* p) { return (int)p->ops.size(); }
 
 // Issue every op on `st`. Returns 0 or (1000*op_index + error) so the caller can name the failing op.
+// ---- tracing (utils.h:13-16 __NVPROF_MARK_TASK / __NVPROF_MARK_OPERATOR, INTRA_ / INTER_TASK_MEASUREMENTS of the reference) ----
+// level 0: off.  1: an NVTX range around every task submission, device time of every task (two timing events per task) and
+// host inter-arrival time of submissions.  2: also an NVTX range per operator while a program is issued or captured.
+static int g_trace = 0;
+XB_API void xb_trace_set(int level) { g_trace = level; }
+XB_API int xb_trace_level() { return g_trace; }
+static const char* op_name(int kind) {
+  static const char* names[] = {"memset", "upload", "transform", "conv-fprop", "conv-dgrad", "conv-wgrad", "colsum", "bn-stats", "bn-fwd", "bn-bwd",
+                                "act-fwd", "act-bwd", "sum", "dropout", "concat", "pool-fwd", "pool-bwd", "lrn-fwd", "lrn-bwd", "softmax-xent",
+                                "classify", "transpose-w", "grad-sumsq", "optimiser", "copy", "matfact", "mark"};
+  return (kind >= 0 && kind < (int)(sizeof(names) / sizeof(names[0]))) ? names[kind] : "op";
+}
+struct TaskTrace {
+  std::mutex mu;
+  std::vector<float> device_ms;        // per finished task
+  std::vector<float> arrival_us;       // host time between consecutive submissions
+  std::chrono::steady_clock::time_point last_submit; bool have_last = false;
+};
+static TaskTrace g_tt;
+// copies up to n values (most recent last) into out; which: 0 device time per task (ms), 1 inter-arrival (us). Returns the count.
+XB_API int xb_trace_read(int which, float* out, int n, int clear) {
+  std::lock_guard<std::mutex> g(g_tt.mu);
+  std::vector<float>& v = which == 0 ? g_tt.device_ms : g_tt.arrival_us;
+  int m = (int)v.size() < n ? (int)v.size() : n;
+  for (int i = 0; i < m; ++i) out[i] = v[v.size() - m + i];
+  if (clear) v.clear();
+  return m;
+}
+
+static inline int run_op_traced(XbProgram* p, const XbOp& o, cudaStream_t st) {
+  if (g_trace < 2) return run_op(p, o, st);
+  nvtxRangePushA(op_name(o.kind));
+  int e = run_op(p, o, st);
+  nvtxRangePop();
+  return e;
+}
 XB_API int xb_program_run(XbProgram* p, cudaStream_t st) {
   for (size_t i = 0; i < p->ops.size(); ++i) {
-    int e = run_op(p, p->ops[i], st);
+    int e = run_op_traced(p, p->ops[i], st);
     if (e != 0) return (int)(1000 * (i + 1) + (e < 0 ? -e : e));
   }
   return 0;
@@ -217,7 +256,7 @@ XB_API int xb_program_run(XbProgram* p, cudaStream_t st) {
 // Run a sub-range [first, last) - used by tests that inspect intermediate tensors.
 XB_API int xb_program_run_range(XbProgram* p, int first, int last, cudaStream_t st) {
   for (int i = first; i < last && i < (int)p->ops.size(); ++i) {
-    int e = run_op(p, p->ops[i], st);
+    int e = run_op_traced(p, p->ops[i], st);
     if (e != 0) return 1000 * (i + 1) + (e < 0 ? -e : e);
   }
   return 0;
@@ -280,7 +319,7 @@ XB_API int xb_program_launch_marked(XbProgram* p, cudaStream_t st, cudaEvent_t* 
       if (o.ia[0] >= 0 && o.ia[0] < nmarks && marks && marks[o.ia[0]]) XB_CUDA_CHECK(cudaEventRecord(marks[o.ia[0]], st));
       continue;
     }
-    int e = run_op(p, o, st);
+    int e = run_op_traced(p, o, st);
     if (e != 0) return (int)(1000 * (i + 1) + (e < 0 ? -e : e));
   }
   return 0;
@@ -308,6 +347,8 @@ struct XbLearner {
   // is recorded, so the host can wait for and read one particular task.
   static constexpr int RING = 4;
   cudaEvent_t ring_done[RING] = {};
+  cudaEvent_t ring_t0[RING] = {}, ring_t1[RING] = {};   // tracing: timing events around the task (created on demand)
+  bool ring_timed[RING] = {};
   unsigned long long ring_task[RING] = {};
   int ring_phase[RING] = {};
   unsigned long long submitted = 0;
@@ -338,6 +379,7 @@ XB_API void xb_learner_destroy(XbLearner* l) {
   cudaEventDestroy(l->done); cudaEventDestroy(l->start);
   for (cudaEvent_t ev : l->bucket) if (ev) cudaEventDestroy(ev);
   for (cudaEvent_t ev : l->ring_done) if (ev) cudaEventDestroy(ev);
+  for (int i = 0; i < XbLearner::RING; ++i) { if (l->ring_t0[i]) cudaEventDestroy(l->ring_t0[i]); if (l->ring_t1[i]) cudaEventDestroy(l->ring_t1[i]); }
   cudaFreeHost(l->h_params); cudaFreeHost(l->h_result);
   cudaStreamDestroy(l->stream);
   delete l;
@@ -359,15 +401,26 @@ XB_API int xb_learner_submit(XbLearner* l, const void* h_examples, const void* h
   if (p->marks > 0)
     for (int b = 0; b < XB_MAX_BUCKETS && b < p->marks; ++b)
       if (!l->bucket[b]) XB_CUDA_CHECK(cudaEventCreateWithFlags(&l->bucket[b], cudaEventDisableTiming));
-  int e = xb_program_launch_marked(p, l->stream, l->bucket, XB_MAX_BUCKETS);
-  if (e) return e;
-  {
-    const int slot = (int)(l->submitted++ % XbLearner::RING);
-    l->ring_task[slot] = params->task_id; l->ring_phase[slot] = phase;
-    copy_result_kernel<<<1, 32, 0, l->stream>>>(l->d_result, l->d_result + 4 + 2 * slot);
-    XB_CUDA_CHECK(cudaGetLastError());
-    XB_CUDA_CHECK(cudaEventRecord(l->ring_done[slot], l->stream));
+  const int slot = (int)(l->submitted++ % XbLearner::RING);
+  const bool timed = g_trace >= 1;
+  if (timed) {
+    char label[48]; snprintf(label, sizeof label, "%s task %u", phase == 0 ? "train" : "test", params->task_id);
+    nvtxRangePushA(label);
+    if (!l->ring_t0[slot]) { XB_CUDA_CHECK(cudaEventCreate(&l->ring_t0[slot])); XB_CUDA_CHECK(cudaEventCreate(&l->ring_t1[slot])); }
+    XB_CUDA_CHECK(cudaEventRecord(l->ring_t0[slot], l->stream));
+    auto now = std::chrono::steady_clock::now();
+    std::lock_guard<std::mutex> g(g_tt.mu);
+    if (g_tt.have_last) g_tt.arrival_us.push_back(std::chrono::duration<float, std::micro>(now - g_tt.last_submit).count());
+    g_tt.last_submit = now; g_tt.have_last = true;
   }
+  l->ring_timed[slot] = timed;
+  int e = xb_program_launch_marked(p, l->stream, l->bucket, XB_MAX_BUCKETS);
+  if (timed) { if (!e) e = (int)cudaEventRecord(l->ring_t1[slot], l->stream); nvtxRangePop(); }
+  if (e) return e;
+  l->ring_task[slot] = params->task_id; l->ring_phase[slot] = phase;
+  copy_result_kernel<<<1, 32, 0, l->stream>>>(l->d_result, l->d_result + 4 + 2 * slot);
+  XB_CUDA_CHECK(cudaGetLastError());
+  XB_CUDA_CHECK(cudaEventRecord(l->ring_done[slot], l->stream));
   XB_CUDA_CHECK(cudaEventRecord(l->done, l->stream));
   l->busy = 1;
   return 0;
@@ -379,6 +432,11 @@ XB_API int xb_learner_wait_task(XbLearner* l, unsigned long long task, int phase
     const int slot = (int)((l->submitted - 1 - back) % XbLearner::RING);
     if (l->ring_task[slot] != (task & 0xffffffffull) || (phase >= 0 && l->ring_phase[slot] != phase)) continue;
     XB_CUDA_CHECK(cudaEventSynchronize(l->ring_done[slot]));
+    if (l->ring_timed[slot]) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, l->ring_t0[slot], l->ring_t1[slot]) == cudaSuccess) { std::lock_guard<std::mutex> g(g_tt.mu); g_tt.device_ms.push_back(ms); }
+      l->ring_timed[slot] = false;
+    }
     if (loss) *loss = l->h_result[4 + 2 * slot];
     if (accuracy) *accuracy = l->h_result[4 + 2 * slot + 1];
     return 0;
@@ -424,6 +482,7 @@ XB_API void* xb_event_create(int timing) {
   if (cudaEventCreateWithFlags(&e, timing ? cudaEventDefault : cudaEventDisableTiming) != cudaSuccess) return nullptr;
   return (void*)e;
 }
+XB_API int xb_event_destroy(void* e) { return (int)cudaEventDestroy((cudaEvent_t)e); }
 XB_API int xb_event_record(void* e, void* s) { return (int)cudaEventRecord((cudaEvent_t)e, (cudaStream_t)s); }
 XB_API int xb_event_sync(void* e) { return (int)cudaEventSynchronize((cudaEvent_t)e); }
 XB_API int xb_stream_wait_event(void* s, void* e) { return (int)cudaStreamWaitEvent((cudaStream_t)s, (cudaEvent_t)e, 0); }

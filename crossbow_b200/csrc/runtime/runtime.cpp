@@ -149,7 +149,7 @@ class Runtime {
       cpu_relax(++spins);
       if (seconds_since(t0) > timeout_s) { fail("drain timed out"); return -1; }
     }
-    return 0;
+    return failed_.load() ? -1 : 0;      // (a failure whose task was collected before this call is still a failure)
   }
 
   void request_stop() { stop_.store(true); }

@@ -71,7 +71,7 @@ def build_cuda(force=False, verbose=False) -> Path:
             if verbose:
                 print(out)
     objs = [str(OBJDIR / (s.stem + ".o")) for s in srcs]
-    _run([_nvcc(), "-shared", "-o", str(lib), *objs, "-lcudart", "-lcuda"], OBJDIR / "link_cuda.log")
+    _run([_nvcc(), "-shared", "-o", str(lib), *objs, "-lcudart", "-lcuda", "-ldl"], OBJDIR / "link_cuda.log")
     return lib
 
 

@@ -172,6 +172,9 @@ def load() -> C.CDLL:
     _sig(lib, "xb_sync_desc_size", I)
     _sig(lib, "xb_exec_copy_signal", I, P)
     _sig(lib, "xb_exec_epoch", c_uint, P)
+    _sig(lib, "xb_trace_set", None, I)
+    _sig(lib, "xb_trace_level", I)
+    _sig(lib, "xb_trace_read", I, I, C.POINTER(c_float), I, I)
     _sig(lib, "xb_learner_wait_task", I, P, C.c_ulonglong, I, C.POINTER(c_float), C.POINTER(c_float))
     _sig(lib, "xb_exec_set_epoch", None, P, c_uint)
     assert lib.xb_sync_desc_size() == C.sizeof(XbSyncDesc), (lib.xb_sync_desc_size(), C.sizeof(XbSyncDesc))
@@ -180,6 +183,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_stream_destroy", I, P)
     _sig(lib, "xb_stream_sync", I, P)
     _sig(lib, "xb_event_create", P, I)
+    _sig(lib, "xb_event_destroy", I, P)
     _sig(lib, "xb_event_record", I, P, P)
     _sig(lib, "xb_event_sync", I, P)
     _sig(lib, "xb_stream_wait_event", I, P, P)

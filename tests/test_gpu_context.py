@@ -59,6 +59,24 @@ def test_synchronous_sgd_with_gradient_buckets_through_the_native_scheduler():
     assert np.abs(z1 - z2).max() <= 1e-4 * np.abs(z1).max()
 
 
+def test_tracing_collects_task_times_and_makespan():
+    from crossbow_b200.utils import trace
+    ctx = _context(trace_level=2, use_cuda_graphs=False)           # per-operator NVTX ranges are issued with every eager launch
+    try:
+        assert trace.level() == 2
+        ctx.train(16, "tasks")
+        dev, gaps = trace.task_device_ms(), trace.inter_arrival_us()
+        assert len(dev) == 16 and (dev > 0).all() and len(gaps) == 15 and (gaps > 0).all()
+        st = trace.summary()
+        assert st["task_device_ms"]["p50"] <= st["task_device_ms"]["max"]
+        ms = trace.makespan_ms(ctx.engine, tasks_per_learner=3, park_ms=5.0)
+        # the tasks were all queued behind the sleep kernels: the makespan covers at least one task's device time
+        assert ms >= float(dev.min()) * 0.5 and ms < 5000
+    finally:
+        ctx.destroy()
+    assert trace.level() == 0 and ctx.trace_summary["task_device_ms"]["n"] >= 16
+
+
 def test_checkpoint_and_resume(tmp_path):
     ctx = _context()
     ctx.train(8, "tasks")
