@@ -87,7 +87,7 @@ class ExecutionContext:
                                     device_index=local, use_graphs=sys.use_cuda_graphs, seed=sys.random_seed,
                                     use_tc=sys.use_tensor_cores, fused_sync=sys.fused_sync,
                                     sync_timeout_s=sys.sync_timeout, splits=mc.splits, reuse_memory=sys.reuse_memory,
-                                    gradient_buckets=sys.gradient_buckets)
+                                    gradient_buckets=sys.gradient_buckets, debug_canaries=sys.debug_canaries)
         else:
             from .engine import CpuEngine
             self.engine = CpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,

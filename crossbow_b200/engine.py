@@ -71,7 +71,7 @@ class Learner:
         self.low_train = Lowering(e.train_graph, e.model, e.batch, e.input_chw, e.device, self.rep.w, self.rep, e.shared,
                                   self.params_dev, params_host, result_dev, update_model=e.update_model, training=True,
                                   use_tc=e.use_tc, clip=e.solver.clip_gradient_threshold >= 0, lr_mult=e.lr_mult, splits=e.splits, reuse_memory=e.reuse_memory,
-                                  gradient_buckets=e.gradient_buckets)
+                                  gradient_buckets=e.gradient_buckets, canaries=e.debug_canaries)
         ops = self.low_train.op_array()
         self.prog_train = lib.xb_program_create(ops, len(ops), int(e.use_tc), e.tc_status.data_ptr())
         self.prog_test = None
@@ -79,7 +79,7 @@ class Learner:
             # test tasks read the CENTRAL model (the reference checks with the master copy) and share the staging buffers
             self.low_test = Lowering(e.test_graph, e.model, e.batch, e.input_chw, e.device, e.shared.z, None, e.shared,
                                      self.params_dev, params_host, result_dev, update_model=e.update_model, training=False,
-                                     use_tc=e.use_tc, reuse_memory=e.reuse_memory)
+                                     use_tc=e.use_tc, reuse_memory=e.reuse_memory, canaries=e.debug_canaries)
             tops = self.low_test.op_array()
             self.prog_test = lib.xb_program_create(tops, len(tops), int(e.use_tc), e.tc_status.data_ptr())
         lib.xb_learner_set_programs(self.handle, self.prog_train, self.prog_test)
@@ -126,7 +126,8 @@ class GpuEngine:
                  batch: int, input_chw, solver: SolverConf, update_model: UpdateModel, replicas: int = 1, wpc: int = 1,
                  rank: int = 0, world: int = 1, device_index: int = 0, use_tc: bool = True, use_graphs: bool = True,
                  seed: int = 0, fused_sync: bool = True, two_shot: Optional[bool] = None, sync_timeout_s: float = 5.0,
-                 splits: int = 1, reuse_memory: bool = False, gradient_buckets: int = 0):
+                 splits: int = 1, reuse_memory: bool = False, gradient_buckets: int = 0,
+                 debug_canaries: bool = False):
         """`gradient_buckets`: synchronous SGD only - number of gradient buckets whose all-reduce + update overlaps the
         backward pass (0 = 4 for models of at least 32 MB, otherwise 1; 1 = one synchronisation after the task)."""
         from .ops import lib as L
@@ -140,6 +141,7 @@ class GpuEngine:
         self.batch, self.input_chw, self.solver, self.update_model = batch, tuple(input_chw), solver, update_model
         self.splits = max(1, int(splits))
         self.reuse_memory = bool(reuse_memory)
+        self.debug_canaries = bool(debug_canaries)      # guard words behind every activation buffer, checked in finish()
         nb = int(gradient_buckets) if gradient_buckets else (4 if model.device_elements * 4 >= (32 << 20) else 1)
         self.gradient_buckets = min(8, nb) if (fused_sync and update_model == UpdateModel.WORKER) else 1
         self.bucket_syncs = []
@@ -350,6 +352,12 @@ class GpuEngine:
         s = self.tc_status.cpu()
         if int(s[0]) != 0:
             raise RuntimeError(f"a tensor-core kernel reported status {int(s[0])} (bounded wait expired)")
+        if self.debug_canaries:
+            for l in self.learners:
+                for low in (l.low_train, l.low_test):
+                    bad = low.arena.check_canaries() if low is not None else 0
+                    if bad:
+                        raise RuntimeError(f"learner {l.index}: {bad} activation buffer(s) were written past their end (guard words changed)")
 
     # ---- model access (canonical order, host) ----
     def central_momentum(self) -> torch.Tensor:

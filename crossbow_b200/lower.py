@@ -40,17 +40,39 @@ FUSE_BN_BACKWARD_SUMS = False
 class Arena:
     """Bump allocator over one CUDA allocation (activations, gradients of activations, scratch of one learner)."""
 
-    def __init__(self, device, nbytes: int = 0):
+    GUARD_WORDS = 64                     # canary words behind every allocation (debug option)
+    GUARD_PATTERN = 0x5AC0FFEE
+
+    def __init__(self, device, nbytes: int = 0, canaries: bool = False):
         self.device = device
         self.chunks: List[torch.Tensor] = []
         self.total = 0
+        self.canaries = canaries
+        self.guards: List[torch.Tensor] = []
 
     def alloc(self, numel: int, dtype=torch.float32, zero=False) -> torch.Tensor:
         # separate torch allocations keep this simple; 256-byte alignment is guaranteed by the caching allocator
-        t = (torch.zeros if zero else torch.empty)(max(1, numel), dtype=dtype, device=self.device)
-        self.chunks.append(t)
-        self.total += t.numel() * t.element_size()
-        return t
+        numel = max(1, numel)
+        if not self.canaries:
+            t = (torch.zeros if zero else torch.empty)(numel, dtype=dtype, device=self.device)
+            self.chunks.append(t)
+            self.total += t.numel() * t.element_size()
+            return t
+        # debug: a guard of known words follows the tensor; a kernel that writes past the end of its output changes it
+        full = (torch.zeros if zero else torch.empty)(numel + self.GUARD_WORDS, dtype=dtype, device=self.device)
+        guard = full[numel:].view(torch.int32)
+        guard.fill_(self.GUARD_PATTERN)
+        self.chunks.append(full)
+        self.guards.append(guard)
+        self.total += full.numel() * full.element_size()
+        return full[:numel]
+
+    def check_canaries(self) -> int:
+        """Number of guards that no longer hold the pattern (0 when intact or when the option is off)."""
+        if not self.guards:
+            return 0
+        bad = torch.stack([(g != self.GUARD_PATTERN).any() for g in self.guards])
+        return int(bad.sum().item())
 
 
 class T:
@@ -133,7 +155,7 @@ class Lowering:
                  result_dev_ptr: int,
                  update_model: UpdateModel = UpdateModel.SMA, training=True, use_tc=True, clip=False,
                  lr_mult: Optional[torch.Tensor] = None, seed_stream_base=0, splits: int = 1, reuse_memory: bool = False,
-                 gradient_buckets: int = 1):
+                 gradient_buckets: int = 1, canaries: bool = False):
         if splits < 1 or batch % splits:
             raise ValueError("error: the batch size must be a multiple of the number of splits")
         # `--splits` (taskhandler.c:65-114): one task runs the whole graph `splits` times over consecutive sub-batches of
@@ -146,7 +168,7 @@ class Lowering:
         self.params_dev, self.params_host_ptr, self.result_ptr = params_dev, params_host_ptr, result_dev_ptr
         self.update_model, self.training, self.use_tc, self.clip = update_model, training, use_tc, clip
         self.lr_mult = lr_mult
-        self.arena = Arena(device)
+        self.arena = Arena(device, canaries=canaries)
         self._count_pass, self._gout_count, self._gout_total = False, {}, {}
         self.all_tensors: List[T] = []
         self.reuse_memory = reuse_memory

@@ -75,6 +75,18 @@ def build_cuda(force=False, verbose=False) -> Path:
     return lib
 
 
+def build_rt_selftest(sanitize: str = "thread") -> Path:
+    """Stand-alone self-test of the host runtime (csrc/selftest/rt_selftest.cpp) built with -fsanitize=<thread|address>."""
+    exe = LIBDIR / f"rt_selftest_{sanitize}"
+    srcs = rt_sources() + [CSRC / "selftest" / "rt_selftest.cpp"]
+    if _stale(exe, srcs + _headers()):
+        LIBDIR.mkdir(parents=True, exist_ok=True)
+        OBJDIR.mkdir(parents=True, exist_ok=True)
+        _run(["g++", "-O1", "-g", "-std=c++17", "-pthread", f"-fsanitize={sanitize}", "-fno-omit-frame-pointer", "-o", str(exe),
+              *map(str, srcs), "-lpthread", "-ldl"], OBJDIR / f"rt_selftest_{sanitize}.log")
+    return exe
+
+
 def build_rt(force=False) -> Path:
     lib = LIBDIR / "libxbow_rt.so"
     srcs, hdrs = rt_sources(), _headers()

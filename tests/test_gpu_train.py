@@ -96,6 +96,31 @@ def test_ssgd_gradient_buckets_match_one_synchronisation_with_concurrent_learner
         assert np.isfinite(a).all() and np.abs(a - b).max() <= 2e-4 * (np.abs(a).max() + 1e-12), np.abs(a - b).max() / np.abs(a).max()
 
 
+def test_debug_canaries_stay_intact_and_catch_an_overrun():
+    from crossbow_b200.engine import GpuEngine
+    from helpers import build_model
+    spec, m, solver = build_model("resnet8", 8)
+    eng = GpuEngine(spec.train, spec.test, m, m.initial_values(5), 8, spec.input_shape, solver, UpdateModel.SMA, replicas=2, wpc=2,
+                    use_tc=True, debug_canaries=True)
+    try:
+        xs, ys = make_batches(spec, 8, 4, seed=2)
+        for t in range(4):
+            eng.submit(t % 2, xs[t].pin_memory(), ys[t].pin_memory(), t, Phase.TRAIN)
+            eng.wait(t % 2)
+            if t % 2:
+                eng.synchronise()
+        eng.submit(0, xs[0].pin_memory(), ys[0].pin_memory(), 0, Phase.CHECK)
+        eng.wait(0)
+        eng.finish()                                           # every kernel stayed inside its buffers
+        arena = eng.learners[1].low_train.arena
+        assert len(arena.guards) > 20 and arena.check_canaries() == 0
+        arena.guards[7][3] = 0                                 # what an overrun by four words would leave behind (written from the host)
+        with pytest.raises(RuntimeError, match="written past their end"):
+            eng.finish()
+    finally:
+        eng.destroy()
+
+
 def test_resnet8_sma():
     run_both("resnet8", 8, 2, 4)
 
