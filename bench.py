@@ -242,7 +242,7 @@ def main():
             "e2e": {"value": round(e2e, 1), "unit": "images/s", "ms_per_step": round(e2e_s * 1e3 / args.steps, 4),
                     "h2d_bytes_per_step": k * ds.batch_bytes(), "d2h_bytes_per_step": k * 8,
                     "timing": "host wall clock around ExecutionContext.train, synchronised on both sides, max over ranks"},
-            "gpu_launches": args.steps * (k * launches_per_task + syncs_per_step),
+            "gpu_launches": args.steps * (k * (launches_per_task + 1) + syncs_per_step),   # + the per-task result copy
             "launches_per_task": launches_per_task,
             "clocks": sampler.summary(),
             "final_loss": ctx.last_loss,
