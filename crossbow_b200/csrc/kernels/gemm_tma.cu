@@ -199,7 +199,10 @@ __global__ void __launch_bounds__(gemm_threads(BN, MODE)) gemm_tma_kernel(const 
           // transposes 32 x 32 blocks through shared memory: afterwards eight lanes cover the 128 contiguous bytes of one
           // row, an instruction writes four full lines, and the batch-norm sums need two shuffles per column group.
           // (the pipeline stages are idle by now - every load has landed and every MMA has completed - and serve as the buffer)
-          float (*tb)[33] = reinterpret_cast<float (*)[33]>(smem + (size_t)(warp - 2) * 32 * 33 * sizeof(float));
+          // The block is kept as 32 rows of eight 16-byte chunks, chunk j of row r at position j ^ (r & 7): the eight lanes
+          // of a quarter-warp then hit all 32 banks both when a lane writes chunk j of ITS row and when eight lanes read the
+          // eight chunks of ONE row, so the whole transpose is 8 + 8 conflict-free 16-byte accesses per lane.
+          float4* tb4 = reinterpret_cast<float4*>(smem + (size_t)(warp - 2) * 32 * 32 * sizeof(float));
           s_rowoff[q][lane] = ok ? m * g.ldd : -1ll;
           __syncwarp();
           const int cq = (lane & 7) * 4, rsub = lane >> 3;
@@ -210,7 +213,7 @@ __global__ void __launch_bounds__(gemm_threads(BN, MODE)) gemm_tma_kernel(const 
               float v[32];                                 // one 32-column load: one wait instead of two
               tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) tb[lane][j] = v[j];
+              for (int j = 0; j < 8; ++j) tb4[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             }
             __syncwarp();
             const int n = n0 + c0 + cq;                    // first of this lane's four columns
@@ -223,11 +226,11 @@ __global__ void __launch_bounds__(gemm_threads(BN, MODE)) gemm_tma_kernel(const 
               const int r = i * 4 + rsub;
               const long long off = s_rowoff[q][r];
               if (off >= 0 && ncol) {
-                float x[4];
+                const float4 t4 = tb4[r * 8 + ((lane & 7) ^ (r & 7))];
+                float x[4] = {t4.x + b4[0], t4.y + b4[1], t4.z + b4[2], t4.w + b4[3]};
+                if (flags & G_RELU) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  x[k] = tb[r][cq + k] + b4[k];
-                  if (flags & G_RELU) x[k] = fmaxf(x[k], 0.f);
+                  for (int k = 0; k < 4; ++k) x[k] = fmaxf(x[k], 0.f);
                 }
                 float4* o = reinterpret_cast<float4*>(D + off + n);
                 if (flags & G_ACCUM) { const float4 old = *o; x[0] += old.x; x[1] += old.y; x[2] += old.z; x[3] += old.w; }

@@ -84,7 +84,7 @@ def main():
     xs, ys = make_batches(spec, 8, 8, seed=100 + rank)
     for nb in (1, 3):
         eng = GpuEngine(spec.train, None, m, m.initial_values(7), 8, spec.input_shape, copy.deepcopy(solver), UpdateModel.WORKER, replicas=2,
-                        wpc=2 * world, rank=rank, world=world, device_index=local, use_tc=True, two_shot=True, gradient_buckets=nb)
+                        wpc=2 * world, rank=rank, world=world, device_index=local, use_tc=False, two_shot=True, gradient_buckets=nb)
         assert (len(eng.bucket_syncs) > 1) == (nb > 1)
         for t in range(0, 8, 2):
             eng.submit(0, xs[t].pin_memory(), ys[t].pin_memory(), t, Phase.TRAIN)

@@ -80,8 +80,9 @@ def test_ssgd_gradient_buckets_match_one_synchronisation_with_concurrent_learner
     out = []
     for nb in (1, 4):
         import copy
+        # (fp32 kernels: with tf32 tiles the run-to-run noise of the atomic accumulation order is itself ~1e-3 here)
         eng = GpuEngine(spec.train, None, m, init, 8, spec.input_shape, copy.deepcopy(solver), UpdateModel.WORKER, replicas=2, wpc=2,
-                        use_tc=True, gradient_buckets=nb)
+                        use_tc=False, gradient_buckets=nb)
         assert (len(eng.bucket_syncs) > 1) == (nb > 1)
         for t in range(0, 8, 2):
             eng.submit(0, *pinned[t], t, Phase.TRAIN)
