@@ -172,6 +172,8 @@ def load() -> C.CDLL:
     _sig(lib, "xb_sync_desc_size", I)
     _sig(lib, "xb_exec_copy_signal", I, P)
     _sig(lib, "xb_exec_epoch", c_uint, P)
+    _sig(lib, "xb_exec_submit", I, P, I, P, P, C.c_ulonglong, I)
+    _sig(lib, "xb_exec_synchronise", I, P, C.c_ulonglong, P, I, I)
     _sig(lib, "xb_trace_set", None, I)
     _sig(lib, "xb_trace_level", I)
     _sig(lib, "xb_trace_read", I, I, C.POINTER(c_float), I, I)
