@@ -174,6 +174,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_exec_epoch", c_uint, P)
     _sig(lib, "xb_exec_submit", I, P, I, P, P, C.c_ulonglong, I)
     _sig(lib, "xb_exec_synchronise", I, P, C.c_ulonglong, P, I, I)
+    _sig(lib, "xb_optimiser_set_blocks", None, I)
     _sig(lib, "xb_trace_set", None, I)
     _sig(lib, "xb_trace_level", I)
     _sig(lib, "xb_trace_read", I, I, C.POINTER(c_float), I, I)
