@@ -191,6 +191,27 @@ __global__ void __launch_bounds__(NT) pool_fwd_v4_kernel(const float4* __restric
     y[i] = AVG ? make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv) : a;
   }
 }
+// Global average pooling (one window = the whole image): a block takes one image and up to 32 channel groups; its 256
+// threads are (position lanes) x (channel-group lanes), so a step reads whole contiguous rows of the image and every thread
+// has only H*W / (position lanes) loads in a row; the position lanes are folded through shared memory.
+__global__ void __launch_bounds__(NT) global_avgpool_v4_kernel(const float4* __restrict__ x, float4* __restrict__ y, int HW, int C4, int CL) {
+  __shared__ float4 red[NT];
+  const int PL = NT / CL, cl = threadIdx.x % CL, pl = threadIdx.x / CL;
+  const int n = blockIdx.y, c = blockIdx.x * CL + cl;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (pl < PL && c < C4) {
+    const float4* src = x + (long long)n * HW * C4 + c;
+#pragma unroll 4
+    for (int p = pl; p < HW; p += PL) { const float4 v = src[(long long)p * C4]; a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w; }
+  }
+  red[threadIdx.x] = a;
+  __syncthreads();
+  if (pl == 0 && c < C4) {
+    for (int l = 1; l < PL; ++l) { const float4 v = red[l * CL + cl]; a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w; }
+    const float inv = 1.f / (float)HW;
+    y[(long long)n * C4 + c] = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+  }
+}
 // DIRECT (windows do not overlap): every window position is written with a plain store - dy at the first maximum, zero
 // elsewhere; otherwise dy is added at the first maximum with an atomic (dx zeroed by the caller).
 template <bool DIRECT>
@@ -434,6 +455,13 @@ static inline bool pool_vec_ok(const PoolGeom& g, const void* a, const void* b) 
 XB_API int xb_pool_forward(const float* x, float* y, const int* geom12, int average, cudaStream_t st) {
   PoolGeom g; memcpy(&g, geom12, sizeof(g));
   long long n = (long long)g.N * g.P * g.Q * g.C;
+  if (average && pool_vec_ok(g, x, y) && g.P == 1 && g.Q == 1 && g.kh == g.H && g.kw == g.W && g.ph == 0 && g.pw == 0) {
+    const int C4 = g.C / 4;
+    int CL = 1; while (CL < 32 && CL < C4) CL <<= 1;         // channel-group lanes: a power of two <= 32
+    dim3 grid((unsigned)((C4 + CL - 1) / CL), (unsigned)g.N);
+    global_avgpool_v4_kernel<<<grid, NT, 0, st>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), g.H * g.W, C4, CL);
+    return (int)cudaGetLastError();
+  }
   if (pool_vec_ok(g, x, y)) {
     if (average) pool_fwd_v4_kernel<true><<<grid_for(n / 4), NT, 0, st>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), g);
     else pool_fwd_v4_kernel<false><<<grid_for(n / 4), NT, 0, st>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(y), g);
