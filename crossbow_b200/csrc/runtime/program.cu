@@ -7,6 +7,7 @@
 // task costs one graph launch on the host.  Values that differ between tasks (learning rate, task id, ...) live in a
 // per-learner XbTaskParams block that is uploaded by the first node of the program.
 #include <nvtx3/nvToolsExt.h>
+#include <atomic>
 #include <chrono>
 #include <mutex>
 #include "../kernels/common.cuh"
@@ -351,7 +352,7 @@ struct XbLearner {
   bool ring_timed[RING] = {};
   unsigned long long ring_task[RING] = {};
   int ring_phase[RING] = {};
-  unsigned long long submitted = 0;
+  std::atomic<unsigned long long> submitted{0};   // written by the submitting thread, read by the thread that waits for a task
   int busy = 0;
 };
 
@@ -401,7 +402,7 @@ XB_API int xb_learner_submit(XbLearner* l, const void* h_examples, const void* h
   if (p->marks > 0)
     for (int b = 0; b < XB_MAX_BUCKETS && b < p->marks; ++b)
       if (!l->bucket[b]) XB_CUDA_CHECK(cudaEventCreateWithFlags(&l->bucket[b], cudaEventDisableTiming));
-  const int slot = (int)(l->submitted++ % XbLearner::RING);
+  const int slot = (int)(l->submitted.fetch_add(1) % XbLearner::RING);
   const bool timed = g_trace >= 1;
   if (timed) {
     char label[48]; snprintf(label, sizeof label, "%s task %u", phase == 0 ? "train" : "test", params->task_id);
@@ -428,8 +429,9 @@ XB_API int xb_learner_submit(XbLearner* l, const void* h_examples, const void* h
 // Block until task `task` (the most recent submission with that id; of that phase unless phase < 0) has finished and
 // return ITS loss / accuracy.
 XB_API int xb_learner_wait_task(XbLearner* l, unsigned long long task, int phase, float* loss, float* accuracy) {
-  for (unsigned long long back = 0; back < (unsigned long long)XbLearner::RING && back < l->submitted; ++back) {
-    const int slot = (int)((l->submitted - 1 - back) % XbLearner::RING);
+  const unsigned long long submitted = l->submitted.load();
+  for (unsigned long long back = 0; back < (unsigned long long)XbLearner::RING && back < submitted; ++back) {
+    const int slot = (int)((submitted - 1 - back) % XbLearner::RING);
     if (l->ring_task[slot] != (task & 0xffffffffull) || (phase >= 0 && l->ring_phase[slot] != phase)) continue;
     XB_CUDA_CHECK(cudaEventSynchronize(l->ring_done[slot]));
     if (l->ring_timed[slot]) {
@@ -520,7 +522,6 @@ XB_API int xb_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 // call straight into this library without passing through Python.  The learning-rate schedule is evaluated here per
 // task (clib-multigpu/solverconfiguration.c:116-162 does the same natively), including the signal that makes the
 // next synchronisation overwrite the replicas with the central model when a multi-step boundary has been crossed.
-#include <atomic>
 #include <math.h>
 
 struct XbSolverState {
