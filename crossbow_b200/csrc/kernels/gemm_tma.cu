@@ -401,7 +401,9 @@ XB_API int xb_conv1x1_tma_supported(const XbConvGeom* g, int which) {
   }
   if (g->sh != 1 && (g->H % 2 || g->W % 2)) return 0;
   if (which == 1) return 1;
-  if (g->C % 32 || g->K % 32) return 0;
+  // K below 32 (first layers): one partial 32-channel plane of dY; the loads read the fill value (zero) for the missing
+  // channels and the epilogue only writes rows below K
+  if (g->C % 32 || (g->K % 32 && !(g->K < 32 && g->sh == 1))) return 0;
   return (g->sh == 1 || g->Q <= 32) ? 1 : 0;
 }
 
@@ -464,7 +466,7 @@ XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, cons
   const int rpb = cg->sh == 1 ? 0 : (32 / cg->Q < cg->N * cg->P ? 32 / cg->Q : cg->N * cg->P), ppb = rpb * cg->Q;
   CUtensorMap ta, tb;
   {
-    const cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(cg->K / 32)};
+    const cuuint64_t dims[3] = {(cuuint64_t)(cg->K < 32 ? cg->K : 32), (cuuint64_t)P, (cuuint64_t)((cg->K + 31) / 32)};
     const cuuint64_t strides[2] = {(cuuint64_t)cg->K * 4, 128};
     const cuuint32_t box[3] = {32, (cuuint32_t)(rpb ? ppb : 32), (cuuint32_t)(rpb ? 1 : 4)};
     if (make_map(&ta, dY, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
