@@ -147,6 +147,7 @@ def main():
     if args.bn_blocks or args.bn_reduce_blocks or args.wgrad_ctas or args.tn_ctas:   # (launch shapes are baked into the task graphs at init)
         from crossbow_b200.ops import lib as _L
         _lib = _L.init_device()
+        _L.launch_shapes_pinned = True               # the engine keeps its hands off the launch shapes set here
         if args.bn_blocks:
             _lib.xb_bn_set_stream_blocks(args.bn_blocks)
         if args.bn_reduce_blocks:
