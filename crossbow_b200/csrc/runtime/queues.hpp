@@ -9,6 +9,8 @@
 //                queue (threadsafequeue.c).
 #pragma once
 #include <atomic>
+#include <mutex>
+#include <deque>
 #include <chrono>
 #include <cstdint>
 #include <memory>
@@ -168,6 +170,51 @@ class MpmcQueue {
   std::unique_ptr<Cell[]> cells_;
   alignas(64) std::atomic<size_t> enq_;
   alignas(64) std::atomic<size_t> deq_;
+};
+
+// Task queue with a scheduling policy (task/TaskQueue.java:42-76, task/TaskWindow.java:185-227).
+//   FIFO: a processor takes the oldest task.
+//   HLS (hybrid latency scheduling): processor p (0 = CPU, 1 = GPU) walks the queue in order and takes the first task whose
+//        graph it runs at least as fast as the other processor (throughput matrix[p][graph] >= matrix[other][graph]), or
+//        any task once the work it has skipped would have kept the OTHER processor busy for longer than this task takes
+//        here: skip cost = sum over skipped tasks of 1 / matrix[other][graph] >= 1 / matrix[p][graph].
+//   NONE: never hands out a task (the reference's NULL policy).
+// Tasks may carry the replica they are bound to and the oldest clock they accept (-1 / 0 = any), the reference's
+// select() filter.  Not on a hot path here (the native scheduler hands tasks straight to learners): a mutex is enough.
+class PolicyTaskQueue {
+ public:
+  enum Policy { HLS = 0, FIFO = 1, NONE = 2 };
+  struct Task { long long id; int graph; int replica; long long clock; };
+  explicit PolicyTaskQueue(int policy) : policy_(policy) {}
+  void push(long long id, int graph, int replica, long long clock) {
+    std::lock_guard<std::mutex> g(mu_);
+    q_.push_back(Task{id, graph, replica, clock});
+  }
+  // matrix: [2][graphs] tasks per second; returns the task id or -1
+  long long poll(int p, const int* matrix, int graphs, int replica, long long clock) {
+    if (policy_ == NONE) return -1;
+    std::lock_guard<std::mutex> g(mu_);
+    const int other = (p + 1) % 2;
+    double skip_cost = 0.0;
+    for (auto it = q_.begin(); it != q_.end(); ++it) {
+      const bool selectable = (it->replica < 0 || replica < 0 || it->replica == replica) && it->clock <= clock;
+      const int gid = (it->graph >= 0 && it->graph < graphs) ? it->graph : 0;
+      const double mine = matrix ? (double)matrix[p * graphs + gid] : 1.0, theirs = matrix ? (double)matrix[other * graphs + gid] : 1.0;
+      if (selectable && (policy_ == FIFO || mine >= theirs || (mine > 0 && skip_cost >= 1.0 / mine))) {
+        long long id = it->id;
+        q_.erase(it);
+        return id;
+      }
+      if (policy_ == HLS && theirs > 0) skip_cost += 1.0 / theirs;
+    }
+    return -1;
+  }
+  int size() { std::lock_guard<std::mutex> g(mu_); return (int)q_.size(); }
+
+ private:
+  int policy_;
+  std::mutex mu_;
+  std::deque<Task> q_;
 };
 
 }  // namespace xb

@@ -440,6 +440,13 @@ RT_API int rt_fake_last_mask(void* f, unsigned char* out, int n) {
 }
 
 // ---- theta queue, exposed for tests and for Python-side pools ---------------------------------------------------------
+RT_API void* rt_taskq_create(int policy) { return new PolicyTaskQueue(policy); }
+RT_API void rt_taskq_destroy(void* q) { delete (PolicyTaskQueue*)q; }
+RT_API void rt_taskq_push(void* q, long long id, int graph, int replica, long long clock) { ((PolicyTaskQueue*)q)->push(id, graph, replica, clock); }
+RT_API long long rt_taskq_poll(void* q, int p, const int* matrix, int graphs, int replica, long long clock) {
+  return ((PolicyTaskQueue*)q)->poll(p, matrix, graphs, replica, clock);
+}
+RT_API int rt_taskq_size(void* q) { return ((PolicyTaskQueue*)q)->size(); }
 RT_API void* rt_theta_create(int n) { return new ThetaQueue(n); }
 RT_API void rt_theta_destroy(void* q) { delete (ThetaQueue*)q; }
 RT_API int rt_theta_next(void* q, double timeout_s) { return ((ThetaQueue*)q)->next([](int) { return true; }, timeout_s); }

@@ -49,6 +49,11 @@ def load() -> C.CDLL:
     _sig(lib, "rt_fake_inject", None, P, I, I)
     _sig(lib, "rt_fake_syncs", U, P)
     _sig(lib, "rt_fake_last_mask", I, P, C.c_char_p, I)
+    _sig(lib, "rt_taskq_create", P, I)
+    _sig(lib, "rt_taskq_destroy", None, P)
+    _sig(lib, "rt_taskq_push", None, P, L, I, I, L)
+    _sig(lib, "rt_taskq_poll", L, P, I, C.POINTER(I), I, I, L)
+    _sig(lib, "rt_taskq_size", I, P)
     _sig(lib, "rt_theta_create", P, I)
     _sig(lib, "rt_theta_destroy", None, P)
     _sig(lib, "rt_theta_next", I, P, D)
@@ -118,6 +123,37 @@ class ThetaQueue:
     def __del__(self):
         if getattr(self, "h", None):
             self.lib.rt_theta_destroy(self.h)
+            self.h = None
+
+
+class TaskQueue:
+    """Ordered task queue with the reference's scheduling policies (task/TaskQueue.java, task/TaskWindow.java:185-227):
+    ``FIFO``, ``HLS`` (hybrid latency scheduling between two processors, 0 = CPU and 1 = GPU, driven by a throughput
+    matrix ``[2][graphs]`` in tasks per second) and ``NULL`` (never hands out a task)."""
+
+    def __init__(self, policy="FIFO"):
+        from ..types import SchedulingPolicy
+        self.lib = load()
+        self.policy = SchedulingPolicy.from_string(policy) if isinstance(policy, str) else policy
+        self.h = self.lib.rt_taskq_create(int(self.policy))
+
+    def push(self, task: int, graph: int = 0, replica: int = -1, clock: int = 0):
+        self.lib.rt_taskq_push(self.h, task, graph, replica, clock)
+
+    def poll(self, processor: int, matrix=None, replica: int = -1, clock: int = 1 << 62) -> int:
+        """Next task for ``processor`` (or -1).  ``matrix``: two rows of per-graph throughputs."""
+        if matrix is None:
+            return int(self.lib.rt_taskq_poll(self.h, processor, None, 1, replica, clock))
+        graphs = len(matrix[0])
+        flat = (C.c_int * (2 * graphs))(*[int(v) for row in matrix for v in row])
+        return int(self.lib.rt_taskq_poll(self.h, processor, flat, graphs, replica, clock))
+
+    def __len__(self):
+        return int(self.lib.rt_taskq_size(self.h))
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.rt_taskq_destroy(self.h)
             self.h = None
 
 

@@ -71,6 +71,60 @@ def test_run_ahead_keeps_two_tasks_per_replica_in_flight(handlers):
     rt.close()
 
 
+def _hls_model(queue, p, matrix):
+    """The reference's rule (task/TaskWindow.java:185-227) restated: index of the task processor p takes, or None."""
+    other, skip = (p + 1) % 2, 0.0
+    for i, g in enumerate(queue):
+        if matrix[p][g] >= matrix[other][g] or skip >= 1.0 / matrix[p][g]:
+            return i
+        skip += 1.0 / matrix[other][g]
+    return None
+
+
+def test_task_queue_policies_fifo_hls_null():
+    import random
+    from crossbow_b200.runtime import TaskQueue
+    q = TaskQueue("FIFO")
+    for t in range(4):
+        q.push(t, graph=t % 2)
+    assert [q.poll(0), q.poll(1), q.poll(0)] == [0, 1, 2] and len(q) == 1
+    assert TaskQueue("NULL").poll(0) == -1
+    # replica / clock filter (the reference's select()): a task bound to replica 1 at clock 3
+    q = TaskQueue("FIFO")
+    q.push(7, replica=1, clock=3)
+    assert q.poll(0, replica=0, clock=5) == -1 and q.poll(0, replica=1, clock=2) == -1 and q.poll(0, replica=1, clock=3) == 7
+    # HLS: graph 0 is ten times faster on the GPU (processor 1), graph 1 twice as fast on the CPU
+    matrix = [[10, 40], [100, 20]]
+    q = TaskQueue("HLS")
+    for t, g in enumerate([0, 0, 1, 0]):
+        q.push(t, graph=g)
+    assert q.poll(1, matrix) == 0          # the GPU takes its own kind first
+    assert q.poll(0, matrix) == 2          # the CPU skips the two GPU-friendly tasks (cost 2/100 < 1/10) and takes graph 1
+    assert q.poll(0, matrix) == -1         # ... and leaves the rest to the GPU: 2/100 has not reached 1/10
+    assert q.poll(1, matrix) == 1 and q.poll(1, matrix) == 3
+    # against the restated rule on random queues
+    rng = random.Random(5)
+    for _ in range(50):
+        graphs = [rng.randrange(3) for _ in range(rng.randrange(1, 12))]
+        matrix = [[rng.randrange(1, 50) for _ in range(3)] for _ in range(2)]
+        q, model = TaskQueue("HLS"), list(graphs)
+        ids = list(range(len(graphs)))
+        for t, g in zip(ids, graphs):
+            q.push(t, graph=g)
+        while True:
+            p = rng.randrange(2)
+            want = _hls_model(model, p, matrix)
+            got = q.poll(p, matrix)
+            assert got == (-1 if want is None else ids[want])
+            if want is None:
+                if _hls_model(model, 1 - p, matrix) is None:
+                    break
+                continue
+            del model[want], ids[want]
+            if not model:
+                break
+
+
 def test_bsp_masks_all_ssp_masks_idle_only():
     rt = Runtime(learners=3, wpc=3, sync_model=0)
     rt.attach_fake(3, task_us=2000)
