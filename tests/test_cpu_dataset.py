@@ -70,3 +70,52 @@ def test_scheduler_pulls_from_ring(tmp_path):
     assert rt.tasks_completed() == 40
     rt.close()
     ds.close()
+
+
+def test_converters_mnist_cifar_ratings_random(tmp_path):
+    import gzip
+    import struct
+    from crossbow_b200.data import convert
+    g = np.random.default_rng(3)
+    # MNIST: IDX files, big-endian headers, pixels scaled by 1/256
+    px = g.integers(0, 256, (20, 28, 28), dtype=np.uint8)
+    lab = g.integers(0, 10, 20, dtype=np.uint8)
+    with gzip.open(tmp_path / "img.gz", "wb") as f:
+        f.write(struct.pack(">iiii", 2051, 20, 28, 28) + px.tobytes())
+    (tmp_path / "lab").write_bytes(struct.pack(">ii", 2049, 20) + lab.tobytes())
+    meta = convert.convert_mnist(str(tmp_path / "img.gz"), str(tmp_path / "lab"), str(tmp_path / "m"), "mnist-train", 8)
+    ds = BasicDataset(meta)
+    ex, lb = ds.batch(1)
+    assert ds.example_shape == (1, 28, 28) and np.array_equal(lb.numpy(), lab[8:16].astype(np.int32))
+    assert np.array_equal(ex.numpy(), px[8:16, None].astype(np.float32) / 256.0)
+    ds.close()
+    with pytest.raises(ValueError, match="magic"):
+        convert.convert_mnist(str(tmp_path / "lab"), str(tmp_path / "lab"), str(tmp_path / "bad"), "x", 8)
+    # CIFAR-10 / CIFAR-100 records, pixels to [-1, 1], mean image beside the partitions
+    rec = np.concatenate([g.integers(0, 10, (16, 1), dtype=np.uint8), g.integers(0, 256, (16, 3072), dtype=np.uint8)], axis=1)
+    (tmp_path / "b1.bin").write_bytes(rec[:8].tobytes())
+    (tmp_path / "b2.bin").write_bytes(rec[8:].tobytes())
+    meta = convert.main(["cifar10", "--input", str(tmp_path / "b1.bin"), str(tmp_path / "b2.bin"), "-o", str(tmp_path / "c"), "--name", "cifar-train", "-b", "8"])
+    ds = BasicDataset(str(tmp_path / "c" / "cifar-train.metadata"))
+    ex, lb = ds.batch(1)
+    want = rec[8:, 1:].reshape(8, 3, 32, 32).astype(np.float32) / 127.5 - 1.0
+    assert np.allclose(ex.numpy(), want, atol=1e-6) and np.array_equal(lb.numpy(), rec[8:, 0].astype(np.int32))
+    mean = np.fromfile(tmp_path / "c" / "cifar-train.mean", dtype=np.float32).reshape(3, 32, 32)
+    assert np.allclose(mean, (rec[:, 1:].reshape(16, 3, 32, 32).astype(np.float32) / 127.5 - 1.0).mean(0), atol=1e-5)
+    ds.close()
+    rec100 = np.concatenate([g.integers(0, 20, (8, 1), dtype=np.uint8), g.integers(0, 100, (8, 1), dtype=np.uint8),
+                             g.integers(0, 256, (8, 3072), dtype=np.uint8)], axis=1)
+    (tmp_path / "c100.bin").write_bytes(rec100.tobytes())
+    ds = BasicDataset(convert.convert_cifar100([str(tmp_path / "c100.bin")], str(tmp_path / "c100"), "c100", 8))
+    assert np.array_equal(ds.batch(0)[1].numpy(), rec100[:, 1].astype(np.int32))          # fine labels
+    ds.close()
+    # ratings: "row column rating" lines
+    (tmp_path / "r.txt").write_text("".join(f"{i} {2 * i} {i % 5 + 1}\n" for i in range(8)))
+    ds = BasicDataset(convert.convert_ratings(str(tmp_path / "r.txt"), str(tmp_path / "r"), "ratings", 4))
+    ex, lb = ds.batch(1)
+    assert np.array_equal(ex.numpy(), np.array([[4, 8], [5, 10], [6, 12], [7, 14]], dtype=np.float32)) and list(lb.numpy()) == [5, 1, 2, 3]
+    ds.close()
+    # random
+    ds = BasicDataset(convert.convert_random([3, 8, 8], 10, 32, str(tmp_path / "rnd"), "random-train", 16, seed=1))
+    assert ds.number_of_examples() == 32 and ds.example_shape == (3, 8, 8)
+    ds.close()
