@@ -440,6 +440,48 @@ RT_API int rt_fake_last_mask(void* f, unsigned char* out, int n) {
 }
 
 // ---- theta queue, exposed for tests and for Python-side pools ---------------------------------------------------------
+// ---- micro-benchmarks of the queues (src/test/java/.../microbenchmarks/{queues,slots}) -------------------------------------
+// Million items per second through one bounded MPMC queue with the given number of producer and consumer threads.
+RT_API double rt_bench_mpmc(int producers, int consumers, long long items) {
+  if (producers < 1 || consumers < 1 || items < 1) return 0.0;
+  MpmcQueue<TaskItem> q(4096);
+  std::atomic<long long> produced{0}, consumed{0};
+  auto t0 = Clock::now();
+  std::vector<std::thread> th;
+  for (int p = 0; p < producers; ++p)
+    th.emplace_back([&] {
+      unsigned spins = 0;
+      for (;;) {
+        long long i = produced.fetch_add(1);
+        if (i >= items) break;
+        TaskItem it{(uint64_t)i, 0, 0, nullptr, nullptr, -1};
+        while (!q.push(it)) cpu_relax(++spins);
+      }
+    });
+  for (int c = 0; c < consumers; ++c)
+    th.emplace_back([&] {
+      unsigned spins = 0;
+      TaskItem it;
+      while (consumed.load() < items) {
+        if (q.pop(it)) consumed.fetch_add(1);
+        else cpu_relax(++spins);
+      }
+    });
+  for (auto& t : th) t.join();
+  return (double)items / seconds_since(t0) / 1e6;
+}
+// Million next() + release() pairs per second on a replica pool of `slots` entries (one thread).
+RT_API double rt_bench_theta(int slots, long long rounds) {
+  if (slots < 1 || slots > ThetaQueue::kMaxSlots || rounds < 1) return 0.0;
+  ThetaQueue q(slots);
+  auto t0 = Clock::now();
+  for (long long i = 0; i < rounds; ++i) {
+    int s = q.next([](int) { return true; }, 1.0);
+    if (s < 0) return 0.0;
+    q.release(s);
+  }
+  return (double)rounds / seconds_since(t0) / 1e6;
+}
 RT_API void* rt_taskq_create(int policy) { return new PolicyTaskQueue(policy); }
 RT_API void rt_taskq_destroy(void* q) { delete (PolicyTaskQueue*)q; }
 RT_API void rt_taskq_push(void* q, long long id, int graph, int replica, long long clock) { ((PolicyTaskQueue*)q)->push(id, graph, replica, clock); }

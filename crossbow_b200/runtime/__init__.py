@@ -49,6 +49,8 @@ def load() -> C.CDLL:
     _sig(lib, "rt_fake_inject", None, P, I, I)
     _sig(lib, "rt_fake_syncs", U, P)
     _sig(lib, "rt_fake_last_mask", I, P, C.c_char_p, I)
+    _sig(lib, "rt_bench_mpmc", D, I, I, L)
+    _sig(lib, "rt_bench_theta", D, I, L)
     _sig(lib, "rt_taskq_create", P, I)
     _sig(lib, "rt_taskq_destroy", None, P)
     _sig(lib, "rt_taskq_push", None, P, L, I, I, L)
