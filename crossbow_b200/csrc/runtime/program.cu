@@ -583,6 +583,12 @@ struct XbExec {
   const char* ex_base[2] = {nullptr, nullptr}; const char* lab_base[2] = {nullptr, nullptr};
   long long ex_bytes[2] = {0, 0}, lab_bytes[2] = {0, 0}, ring[2] = {0, 0}, stride_tasks = 1, offset_tasks = 0;
   void* d_ex[2][64]; void* d_lab[2][64];
+  // Input prefetch: the host-to-device copy of a task's examples runs on a copy stream of its own into a second device
+  // buffer, so with two tasks of a replica in flight it overlaps the replica's running task; the learner's stream then
+  // only does a device-to-device copy into the staging buffer its task graph reads.
+  struct Prefetch { cudaStream_t copy = nullptr; void* next = nullptr; cudaEvent_t copied = nullptr, consumed = nullptr; bool used = false; };
+  Prefetch pf[2][64];
+  int prefetch = 1;
 };
 
 XB_API XbExec* xb_exec_create(const XbSolverState* solver, unsigned long long seed, void* sync_stream, int max_blocks) {
@@ -601,6 +607,13 @@ XB_API XbExec* xb_exec_create(const XbSolverState* solver, unsigned long long se
 XB_API void xb_exec_destroy(XbExec* e) {
   if (!e) return;
   cudaFree(e->args_dev); cudaFreeHost(e->args_pinned); cudaFree(e->w_table_dev); cudaEventDestroy(e->sync_event);
+  for (auto& row : e->pf)
+    for (auto& pf : row) {
+      if (pf.copy) { cudaStreamSynchronize(pf.copy); cudaStreamDestroy(pf.copy); }
+      if (pf.next) cudaFree(pf.next);
+      if (pf.copied) cudaEventDestroy(pf.copied);
+      if (pf.consumed) cudaEventDestroy(pf.consumed);
+    }
   delete e;
 }
 XB_API int xb_exec_add_learner(XbExec* e, XbLearner* l, float* w, float* prev, void* d_ex_train, void* d_lab_train, void* d_ex_test, void* d_lab_test) {
@@ -648,10 +661,29 @@ XB_API int xb_exec_submit(void* ctx, int learner, const void* ex, const void* la
   p.clip = e->solver.clip; p.alpha = e->solver.alpha;
   p.task_id = (unsigned)task; p.seed_lo = (unsigned)(e->seed & 0xffffffffu); p.seed_hi = (unsigned)(e->seed >> 32);
   p.training = training ? 1 : 0; p.l1 = e->solver.l1; p.nesterov = e->solver.nesterov;
-  if (ex) XB_CUDA_CHECK(cudaMemcpyAsync(e->d_ex[phase][learner], ex, (size_t)e->ex_bytes[phase], cudaMemcpyHostToDevice, l->stream));
+  if (ex && e->prefetch && learner < 64) {
+    XbExec::Prefetch& pf = e->pf[phase][learner];
+    const size_t bytes = (size_t)e->ex_bytes[phase];
+    if (!pf.copy) {
+      XB_CUDA_CHECK(cudaStreamCreateWithFlags(&pf.copy, cudaStreamNonBlocking));
+      XB_CUDA_CHECK(cudaMalloc(&pf.next, bytes));
+      XB_CUDA_CHECK(cudaEventCreateWithFlags(&pf.copied, cudaEventDisableTiming));
+      XB_CUDA_CHECK(cudaEventCreateWithFlags(&pf.consumed, cudaEventDisableTiming));
+    }
+    if (pf.used) XB_CUDA_CHECK(cudaStreamWaitEvent(pf.copy, pf.consumed, 0));       // the previous task has taken its batch out of `next`
+    XB_CUDA_CHECK(cudaMemcpyAsync(pf.next, ex, bytes, cudaMemcpyHostToDevice, pf.copy));
+    XB_CUDA_CHECK(cudaEventRecord(pf.copied, pf.copy));
+    XB_CUDA_CHECK(cudaStreamWaitEvent(l->stream, pf.copied, 0));
+    XB_CUDA_CHECK(cudaMemcpyAsync(e->d_ex[phase][learner], pf.next, bytes, cudaMemcpyDeviceToDevice, l->stream));
+    XB_CUDA_CHECK(cudaEventRecord(pf.consumed, l->stream));
+    pf.used = true;
+  } else if (ex) {
+    XB_CUDA_CHECK(cudaMemcpyAsync(e->d_ex[phase][learner], ex, (size_t)e->ex_bytes[phase], cudaMemcpyHostToDevice, l->stream));
+  }
   if (lab) XB_CUDA_CHECK(cudaMemcpyAsync(e->d_lab[phase][learner], lab, (size_t)e->lab_bytes[phase], cudaMemcpyHostToDevice, l->stream));
   return xb_learner_submit(l, nullptr, nullptr, &p, phase);
 }
+XB_API void xb_exec_set_prefetch(XbExec* e, int on) { e->prefetch = on ? 1 : 0; }
 XB_API int xb_exec_wait(void* ctx, int learner, float* loss, float* acc) {
   XbExec* e = (XbExec*)ctx;
   if (learner < 0 || learner >= (int)e->learners.size()) return -XB_BAD_ARG;
