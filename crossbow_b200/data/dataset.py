@@ -7,7 +7,7 @@ is copied on the way to the device except the DMA itself.
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence, Tuple
+from typing import Sequence, Tuple
 
 import numpy as np
 import torch

@@ -4,7 +4,7 @@ doublebuffer.c, image/*.c)."""
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Sequence
+from typing import Sequence
 
 import numpy as np
 import torch

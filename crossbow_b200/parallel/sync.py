@@ -16,7 +16,6 @@ from typing import List, Optional
 import torch
 
 from ..ops import lib as L
-from ..types import UpdateModel
 from .peer import PeerBuffer
 
 ALGO_SMA, ALGO_SSGD, ALGO_POLYAK = 0, 1, 2

@@ -14,7 +14,7 @@ What the reference compiles in with macros is a run-time level here (``--trace-l
 from __future__ import annotations
 
 import ctypes as C
-from typing import Dict, List
+from typing import Dict
 
 import numpy as np
 
