@@ -37,7 +37,9 @@ class ExecutionContext:
         self.engine = None
         self.clock: Optional[WorkClock] = None
         self.quiet = quiet
-        self.measurements = MeasurementQueue()
+        self.measurements = MeasurementQueue()          # every training result
+        self.displayed = MeasurementQueue()             # what `--queue-measurements` keeps: one record per display interval
+        self._disp_n, self._disp_loss, self._disp_acc = 0, 0.0, 0.0
         self.monitor: Optional[PerformanceMonitor] = None
         self.autotuner: Optional[AutoTuner] = None
         self.rank, self.world = 0, 1
@@ -170,9 +172,7 @@ class ExecutionContext:
         hist = rt.history(min(max(done, 1), 65536))
         for task, loss, acc in hist[-done:]:
             self.measurements.add(task, loss, acc)
-            di = self.sys.display_interval
-            if not self.quiet and di > 0 and (task + 1) % di == 0:
-                print(f"[{task + 1:06d}] loss {loss:9.5f} accuracy {acc:7.4f} ({self.monitor.last_rate():9.1f} examples/s)", flush=True)
+            self._display(task, loss, acc)
         if hist:
             self.last_loss, self.last_accuracy = hist[-1][1], hist[-1][2]
         self.tasks_done += done
@@ -196,9 +196,7 @@ class ExecutionContext:
                 self.measurements.add(task, loss, acc)
                 self.monitor.task_done()
                 self.tasks_done += 1
-                di = self.sys.display_interval
-                if not self.quiet and di > 0 and (task + 1) % di == 0:
-                    print(f"[{task + 1:06d}] loss {loss:9.5f} accuracy {acc:7.4f} ({self.monitor.last_rate():9.1f} examples/s)", flush=True)
+                self._display(task, loss, acc)
             return loss, acc
         return None
 
@@ -245,6 +243,34 @@ class ExecutionContext:
         self._drain(inflight)
         e.finish()
         return done
+
+    def _display(self, task: int, loss: float, acc: float):
+        """One training result (result/TrainingResultHandler.java:231-317): every `--display-interval` tasks a line is
+        printed - the last task's values, or with `--display-accumulated-loss` the mean over the interval with the last
+        value in parentheses.  With `--queue-measurements` the displayed pair goes to a queue that is dumped at shutdown
+        and the line is only printed if `--tee-measurements` is set."""
+        di = self.sys.display_interval
+        if di <= 0:
+            return
+        self._disp_n += 1
+        self._disp_loss += loss
+        self._disp_acc += acc
+        if (task + 1) % di:
+            return
+        n = max(1, self._disp_n)
+        if self.sys.display_accumulated_loss:
+            shown_loss, shown_acc = self._disp_loss / n, self._disp_acc / n
+            text = f"[{task + 1:06d}] loss {shown_loss:9.5f} ({loss:9.5f}) accuracy {shown_acc:7.4f} ({acc:7.4f})"
+        else:
+            shown_loss, shown_acc = loss, acc
+            text = f"[{task + 1:06d}] loss {loss:9.5f} accuracy {acc:7.4f}"
+        self._disp_n, self._disp_loss, self._disp_acc = 0, 0.0, 0.0
+        if self.sys.queue_measurements:
+            self.displayed.add(task, shown_loss, shown_acc)
+            if not self.sys.tee_measurements:
+                return
+        if not self.quiet:
+            print(f"{text} ({self.monitor.last_rate():9.1f} examples/s)", flush=True)
 
     def _tasks_of(self, n: int, unit) -> int:
         unit = TrainingUnit.from_string(unit)
@@ -350,7 +376,7 @@ class ExecutionContext:
             self.engine.destroy()
             self.engine = None
         if self.sys.queue_measurements and not self.quiet:
-            print(self.measurements.dump())
+            print(self.displayed.dump())
 
     # snake_case aliases
     train_and_test = trainAndTest

@@ -355,3 +355,27 @@ def test_matmul_is_an_inner_product_without_bias():
     w = torch.from_numpy(m.initial_values(1)).reshape(5, 7)
     x = torch.randn(3, 7)
     assert torch.allclose(k.forward([x], [w], None), x @ w.t())
+
+
+def test_display_interval_accumulated_loss_queue_and_tee(capsys):
+    """Display semantics of the training result handler: interval, accumulated mean, queued records, tee."""
+    from crossbow_b200.context import ExecutionContext
+    ctx = ExecutionContext.__new__(ExecutionContext)
+    from crossbow_b200.utils.measure import MeasurementQueue, PerformanceMonitor
+    sysc = SystemConf.reset()
+    ctx.sys, ctx.quiet = sysc, False
+    ctx.displayed, ctx.monitor = MeasurementQueue(), PerformanceMonitor(8, 0)
+    ctx._disp_n, ctx._disp_loss, ctx._disp_acc = 0, 0.0, 0.0
+    sysc.display_interval, sysc.display_accumulated_loss = 2, True
+    for t, (l, a) in enumerate([(4.0, 0.0), (2.0, 1.0), (1.0, 0.5), (3.0, 0.5)]):
+        ctx._display(t, l, a)
+    out = capsys.readouterr().out.splitlines()
+    assert len(out) == 2 and "loss   3.00000 (  2.00000)" in out[0] and "accuracy  0.5000 ( 1.0000)" in out[0] and "[000004]" in out[1]
+    sysc.display_accumulated_loss, sysc.queue_measurements, sysc.tee_measurements = False, True, False
+    ctx._display(4, 9.0, 0.0)
+    ctx._display(5, 7.0, 0.25)
+    assert capsys.readouterr().out == "" and len(ctx.displayed) == 1 and ctx.displayed.losses() == [7.0]
+    sysc.tee_measurements = True
+    ctx._display(6, 1.0, 0.0)
+    ctx._display(7, 0.5, 1.0)
+    assert "loss   0.50000 accuracy  1.0000" in capsys.readouterr().out and len(ctx.displayed) == 2
