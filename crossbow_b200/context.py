@@ -81,6 +81,11 @@ class ExecutionContext:
             from .parallel.peer import dist_info
             from .engine import GpuEngine
             self.rank, self.world, local = dist_info()
+            if sys.number_of_gpu_streams not in (1, sys.number_of_gpu_models) and not self.quiet:
+                # (the reference warns when the two differ, executioncontext.c:1724-1725; here a learner IS a replica bound to
+                # its own stream, so the replica count decides)
+                print(f"warning: --number-of-gpu-streams {sys.number_of_gpu_streams} is ignored: every one of the "
+                      f"{sys.number_of_gpu_models} replicas has its own stream", flush=True)
             if sys.trace_level > 0:                      # before the task programs are captured (operator ranges)
                 from .utils import trace
                 trace.enable(sys.trace_level)
@@ -250,6 +255,8 @@ class ExecutionContext:
         value in parentheses.  With `--queue-measurements` the displayed pair goes to a queue that is dumped at shutdown
         and the line is only printed if `--tee-measurements` is set."""
         di = self.sys.display_interval
+        if di > 0 and TrainingUnit.from_string(self.sys.display_interval_unit) == TrainingUnit.EPOCHS and getattr(self, "mc", None) is not None:
+            di *= max(1, self.mc.numberOfTasksPerEpoch(Phase.TRAIN))           # `--display-interval-unit epochs`
         if di <= 0:
             return
         self._disp_n += 1

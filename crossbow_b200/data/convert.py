@@ -28,7 +28,7 @@ def _open(path):
     return gzip.open(path, "rb") if str(path).endswith(".gz") else open(path, "rb")
 
 
-def _write(directory, name, shape, batch, examples: np.ndarray, labels: np.ndarray, partition_bytes=1 << 30) -> str:
+def _write(directory, name, shape, batch, examples: np.ndarray, labels: np.ndarray, partition_bytes=None) -> str:
     n = len(examples)
     w = DatasetWriter(directory, name, shape, batch, partition_bytes=partition_bytes)
     step = max(batch, (4096 // batch) * batch)

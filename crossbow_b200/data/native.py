@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import ctypes as C
 import os
-from typing import Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 import torch
@@ -30,7 +30,11 @@ def _tensor(ptr: int, shape, dtype):
 
 class DatasetWriter:
     def __init__(self, directory: str, name: str, example_shape: Sequence[int], batch_size: int,
-                 partition_bytes: int = 1 << 30, pad_to_page: bool = True):
+                 partition_bytes: Optional[int] = None, pad_to_page: bool = True):
+        """`partition_bytes`: size limit of one partition file (default: `--file-partition-size`)."""
+        if partition_bytes is None:
+            from ..conf import SystemConf
+            partition_bytes = SystemConf.getInstance().file_partition_size
         self.lib = _load()
         os.makedirs(directory, exist_ok=True)
         self.meta_path = os.path.join(directory, f"{name}.metadata")
@@ -82,7 +86,11 @@ class _NativeDataset(Dataset):
 class BasicDataset(_NativeDataset):
     kind = 0
 
-    def __init__(self, metadata_path: str, window: int = 4, register_with_cuda: bool = False, timeout_s: float = 30.0):
+    def __init__(self, metadata_path: str, window: Optional[int] = None, register_with_cuda: bool = False, timeout_s: float = 30.0):
+        """`window`: partitions kept mapped at a time (default: `--mapped-partitions-window`)."""
+        if window is None:
+            from ..conf import SystemConf
+            window = SystemConf.getInstance().mapped_partitions_window
         self.lib = _load()
         self._read_meta(metadata_path)
         reg = unreg = None
@@ -114,7 +122,12 @@ class BasicDataset(_NativeDataset):
 class LightDataset(_NativeDataset):
     kind = 1
 
-    def __init__(self, metadata_path: str, slots: int = 8, copiers: int = 1, register_with_cuda: bool = False, timeout_s: float = 30.0):
+    def __init__(self, metadata_path: str, slots: int = 8, copiers: Optional[int] = None, register_with_cuda: bool = False,
+                 timeout_s: float = 30.0):
+        """`copiers`: threads that fill the slot ring from the partition files (default: `--number-of-file-handlers`)."""
+        if copiers is None:
+            from ..conf import SystemConf
+            copiers = max(1, SystemConf.getInstance().number_of_file_handlers)
         self.lib = _load()
         self._read_meta(metadata_path)
         self.h = self.lib.ds_light_open(metadata_path.encode(), slots, copiers)
