@@ -379,3 +379,10 @@ def test_display_interval_accumulated_loss_queue_and_tee(capsys):
     ctx._display(6, 1.0, 0.0)
     ctx._display(7, 0.5, 1.0)
     assert "loss   0.50000 accuracy  1.0000" in capsys.readouterr().out and len(ctx.displayed) == 2
+
+
+def test_trace_percentiles_and_gpu_sampler_summary():
+    from crossbow_b200.utils.trace import percentiles
+    st = percentiles(np.arange(1, 101, dtype=np.float32))
+    assert st["n"] == 100 and st["min"] == 1 and st["max"] == 100 and abs(st["p50"] - 50.5) < 1e-3 and abs(st["p99"] - 99.01) < 1e-2
+    assert percentiles(np.array([])) == {"n": 0}

@@ -70,3 +70,29 @@ def test_splits_repeat_the_operator_list_and_reuse_memory_shrinks_the_arena():
     assert sum(1 for o in two.ops if o.kind == L.OP_OPTIMISER) == 2      # the whole graph, optimiser included, once per sub-batch
     _, _, _, shared = _lower(update_model=UpdateModel.SMA, reuse_memory=True)
     assert shared.arena.total < 0.8 * one.arena.total and shared.bytes_before_reuse == one.arena.total
+
+
+def test_rectangular_filters_reach_the_kernels_with_their_geometry():
+    """Inception-v3's 1x7 / 7x1 / 1x3 / 3x1 convolutions: (R, S) and (pad_h, pad_w) of the lowered launches."""
+    from crossbow_b200.lower import DeviceShared, Lowering, ReplicaBuffers
+    from crossbow_b200.ops import lib as L
+    try:
+        L.load()
+    except Exception as e:                           # pragma: no cover
+        pytest.skip(f"native library not loadable here: {e}")
+    spec, m, solver = build_model("inception-v3", 2, size=139, width=0.25, classes=10)
+    dev = torch.device("cpu")
+    init = torch.from_numpy(m.to_device(m.initial_values(3)))
+    rep, sh = ReplicaBuffers(m, dev, init), DeviceShared(m, dev, init)
+    low = Lowering(spec.train, m, 2, spec.input_shape, dev, rep.w, rep, sh, torch.zeros(16, dtype=torch.int32), 0, 0,
+                   update_model=UpdateModel.SMA, training=True, use_tc=True)
+    shapes = set()
+    for o in low.ops:
+        if o.kind == L.OP_CONV_FPROP:
+            g = L.XbConvGeom.from_buffer_copy(bytes(o.ia)[: 13 * 4])
+            shapes.add((g.R, g.S, g.ph, g.pw, g.sh))
+            assert g.P == (g.H + 2 * g.ph - g.R) // g.sh + 1 and g.Q == (g.W + 2 * g.pw - g.S) // g.sw + 1
+    assert {(7, 1, 3, 0, 1), (1, 7, 0, 3, 1), (3, 1, 1, 0, 1), (1, 3, 0, 1, 1), (3, 3, 0, 0, 2), (5, 5, 2, 2, 1), (1, 1, 0, 0, 1)} <= shapes
+    # every convolution has its three launches (the stem has no data gradient)
+    n_f = sum(o.kind == L.OP_CONV_FPROP for o in low.ops)
+    assert sum(o.kind == L.OP_CONV_WGRAD for o in low.ops) == n_f and sum(o.kind == L.OP_CONV_DGRAD for o in low.ops) == n_f - 1
