@@ -50,11 +50,10 @@ def test_tasks_results_and_clock(handlers):
 def test_run_ahead_keeps_two_tasks_per_replica_in_flight(handlers):
     # every replica is released at submission until two of its tasks are in flight; results are still attributed per task
     rt = Runtime(learners=4, wpc=4, task_handlers=handlers, callback_handlers=2, task_timeout_s=5)
-    rt.attach_fake(4, task_us=2000)
+    rt.attach_fake(4, task_us=10000)
     rt.set_run_ahead(2)
-    t0 = time.perf_counter()
     assert rt.train(8) == 8                                   # two rounds are handed over without waiting for a completion
-    assert rt.tasks_completed() < 8                           # (each fake task takes 2 ms)
+    assert rt.tasks_completed() < 8                           # (each fake task takes 10 ms, two at a time: 40 ms for eight)
     assert rt.train(32) == 32
     rt.drain(10)
     assert rt.tasks_completed() == 40 and rt.clock() == 10 and rt.fake_syncs() == 10
