@@ -385,6 +385,35 @@ class ExecutionContext:
         if self.sys.queue_measurements and not self.quiet:
             print(self.displayed.dump())
 
+    # ---- accessors of the reference's ExecutionContext (ExecutionContext.java:51-90) ----
+    def getDataflows(self):
+        return list(self.dataflows)
+
+    def getDataflow(self, phase):
+        return self.dataflows[int(Phase.from_string(phase))]
+
+    def getModel(self):
+        return self.model
+
+    def getModelManager(self):
+        """The engine owns what the reference's ModelManager does: replicas, the central model, synchronisation."""
+        return self.engine
+
+    def getWorkClock(self):
+        return self.clock
+
+    def getThroughputMatrix(self):
+        """[processor][dataflow] tasks per second as the hybrid scheduler reads it (row 0 CPU, row 1 GPU); only the row of
+        the processor this context runs on is measured."""
+        rate = int(self.monitor.last_rate() / max(1, self.mc.batch_size)) if getattr(self, "monitor", None) is not None else 0
+        row = [rate, 0]
+        return [[0, 0], row] if self.sys.gpu else [row, [0, 0]]
+
+    def getExecutorQueueSize(self) -> int:
+        """Tasks handed to the scheduler that have not completed yet."""
+        rt = getattr(self, "_native", None)
+        return int(rt.tasks_issued() - rt.tasks_completed()) if rt is not None else 0
+
     # snake_case aliases
     train_and_test = trainAndTest
     train_for_duration = trainForDuration

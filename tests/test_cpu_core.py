@@ -386,3 +386,24 @@ def test_trace_percentiles_and_gpu_sampler_summary():
     st = percentiles(np.arange(1, 101, dtype=np.float32))
     assert st["n"] == 100 and st["min"] == 1 and st["max"] == 100 and abs(st["p50"] - 50.5) < 1e-3 and abs(st["p99"] - 99.01) < 1e-2
     assert percentiles(np.array([])) == {"n": 0}
+
+
+def test_execution_context_accessors():
+    from crossbow_b200.context import ExecutionContext
+    from crossbow_b200.data import SyntheticDataset
+    from crossbow_b200.models import build
+    sysc, mc = SystemConf.reset(), ModelConf.reset()
+    sysc.setCPU(True).setGPU(False).setDisplayInterval(0)
+    solver = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.01)
+    mc.setBatchSize(8).setWpc(1).setUpdateModel("SMA")
+    mc.setDataset(Phase.TRAIN, SyntheticDataset([1, 28, 28], 10, 8, batches=4, seed=1, distribution="uniform"))
+    spec = build("logistic-regression", solver_conf=solver)
+    ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), None], quiet=True)
+    ctx.init()
+    ctx.train(4, "tasks")
+    assert len(ctx.getDataflows()) == 2 and ctx.getDataflow("TRAIN") is ctx.dataflows[0] and ctx.getDataflow(Phase.CHECK) is None
+    assert ctx.getModel().elements == 7850 and ctx.getWorkClock().clock == 4 and ctx.getExecutorQueueSize() == 0
+    m = ctx.getThroughputMatrix()
+    assert len(m) == 2 and len(m[0]) == 2 and m[1] == [0, 0]           # CPU row measured, GPU row empty
+    assert ctx.getModelManager() is ctx.engine
+    ctx.destroy()
