@@ -16,7 +16,7 @@ from .types import (ActivationMode, BatchNormEstimatedMeanAndVarianceType, Eleme
                     InitialiserType, LearningRateDecayPolicy, MomentumMethod, NormalisationMode,
                     NormalisationRegion, PoolMethod, Regularisation, ReplicationModel,
                     SchedulingPolicy, SynchronisationModel, TrainingUnit, UpdateModel,
-                    VarianceNormalisation, DurationUnit)
+                    VarianceNormalisation, DurationUnit, Phase)
 
 
 def _camel_to_snake(name: str) -> str:
@@ -315,6 +315,15 @@ class SolverConf(Fluent):
         c, self._copy = self._copy, False
         return c
 
+    def setCurrentStep(self, step: int):
+        """Position in the multi-step schedule (SolverConf.java:209-212), e.g. after a resume."""
+        self._step = int(step)
+        return self
+
+    def setModelConf(self, parent):
+        self.parent = parent
+        return self
+
     def learning_rate(self, task: int) -> float:
         """Learning rate used by task number ``task`` (0-based). Stateful for MULTISTEP/LSR like the reference."""
         p = self.learning_rate_decay_policy
@@ -495,6 +504,27 @@ class SystemConf(_OptionHolder):
     def numberOfGPUs(self):
         return len(self.gpu_devices)
 
+    # ---- the reference's setter names that differ from the generated set<Field> ones (SystemConf.java:237-780) ----
+    def _set(self, field, value):
+        setattr(self, field, value)
+        return self
+
+    def setNumberOfWorkerThreads(self, n): return self._set("number_of_workers", int(n))
+    def setNumberOfCPUModelReplicas(self, n): return self._set("number_of_cpu_models", int(n))
+    def setNumberOfGPUModelReplicas(self, n): return self._set("number_of_gpu_models", int(n))
+    def setNumberOfReadersPerModel(self, n): return self._set("readers_per_model", int(n))
+    def setNumberOfGPUCallbackHandlers(self, n): return self._set("number_of_callback_handlers", int(n))
+    def setNumberOfGPUTaskHandlers(self, n): return self._set("number_of_task_handlers", int(n))
+    def setPerformanceMonitorInterval(self, ms): return self._set("monitor_interval", int(ms))
+    def setTaskQueueSizeLimit(self, n): return self._set("task_queue_size", int(n))
+    def setVariableBufferSize(self, nbytes): return self._set("data_buffer_size", int(nbytes))
+    def setMaxNumberOfMappedPartitions(self, n): return self._set("mapped_partitions_window", int(n))
+    def allowMemoryReuse(self, flag): return self._set("reuse_memory", bool(flag))
+    def autotuneModels(self, flag): return self._set("autotune_models", bool(flag))
+    def displayAccumulatedLossValue(self, flag): return self._set("display_accumulated_loss", bool(flag))
+    def queueMeasurements(self, flag): return self._set("queue_measurements", bool(flag))
+    def useDirectBuffers(self, flag): return self._set("use_direct_buffers", bool(flag))
+
     def isHybrid(self):
         return self.cpu and self.gpu
 
@@ -553,6 +583,17 @@ class ModelConf(_OptionHolder):
 
     def getDataset(self, phase):
         return self.datasets[int(phase)]
+
+    # reference names (ModelConf.java:150-214)
+    def setTrainingDataset(self, dataset):
+        return self.setDataset(Phase.TRAIN, dataset)
+
+    def setValidationDataset(self, dataset):
+        return self.setDataset(Phase.CHECK, dataset)
+
+    def setNumberOfSplits(self, n):
+        self.splits = int(n)
+        return self
 
     def setBatchSize(self, n):
         self.batch_size = int(n)

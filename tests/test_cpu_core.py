@@ -407,3 +407,17 @@ def test_execution_context_accessors():
     assert len(m) == 2 and len(m[0]) == 2 and m[1] == [0, 0]           # CPU row measured, GPU row empty
     assert ctx.getModelManager() is ctx.engine
     ctx.destroy()
+
+
+def test_reference_setter_names_exist():
+    """A program written against the reference's configuration API keeps working (SystemConf.java, ModelConf.java, SolverConf.java)."""
+    s = SystemConf.reset().setCPU(False).setGPU(True).setGPUDevices(0, 1).setNumberOfWorkerThreads(1).setNumberOfCPUModelReplicas(1) \
+        .setNumberOfReadersPerModel(1).setNumberOfGPUModelReplicas(3).setNumberOfGPUStreams(3).setNumberOfGPUCallbackHandlers(8) \
+        .setNumberOfGPUTaskHandlers(2).setDisplayInterval(100).displayAccumulatedLossValue(True).queueMeasurements(True) \
+        .setTaskQueueSizeLimit(32).setPerformanceMonitorInterval(2000).setNumberOfResultSlots(128).allowMemoryReuse(True) \
+        .autotuneModels(False).useDirectBuffers(True).setMaxNumberOfMappedPartitions(2).setVariableBufferSize(1 << 20)
+    assert (s.number_of_gpu_models, s.number_of_callback_handlers, s.number_of_task_handlers, s.monitor_interval) == (3, 8, 2, 2000)
+    assert s.display_accumulated_loss and s.queue_measurements and s.reuse_memory and s.mapped_partitions_window == 2 and s.gpu_devices == [0, 1]
+    m = ModelConf.reset().setBatchSize(64).setWpc(4).setSlack(0).setNumberOfSplits(2).setTrainingDataset("train").setValidationDataset("test")
+    assert m.splits == 2 and m.getDataset(Phase.TRAIN) == "train" and m.getDataset(Phase.CHECK) == "test"
+    assert m.getSolverConf().setCurrentStep(1)._step == 1
