@@ -126,6 +126,53 @@ class ConvConf(Fluent):
     def hasBias(self):
         return self.bias
 
+    # indexed access as in ConvConf.java:117-221 (index 0 = height, 1 = width)
+    def setKernel(self, ndx, val):
+        setattr(self, ("kernel_height", "kernel_width")[ndx], int(val))
+        return self
+
+    def getKernel(self, ndx):
+        return (self.kernel_height, self.kernel_width)[ndx]
+
+    def setStride(self, ndx, val):
+        setattr(self, ("stride_height", "stride_width")[ndx], int(val))
+        return self
+
+    def getStride(self, ndx):
+        return (self.stride_height, self.stride_width)[ndx]
+
+    def setPadding(self, ndx, val):
+        setattr(self, ("padding_height", "padding_width")[ndx], int(val))
+        return self
+
+    def getPadding(self, ndx):
+        return (self.padding_height, self.padding_width)[ndx]
+
+    def numberOfOutputs(self):
+        return self.number_of_outputs
+
+    def setNumberOfGroup(self, groups):
+        self.groups = int(groups)
+        return self
+
+    def numberOfGroups(self):
+        return self.groups
+
+    # learning-rate multipliers under the reference's names
+    def setWeightsLearningRateMultiplier(self, v):
+        self.weights_lr_multiplier = float(v)
+        return self
+
+    def setBiasLearningRateMultiplier(self, v):
+        self.bias_lr_multiplier = float(v)
+        return self
+
+    def getWeightsLearningRateMultiplier(self):
+        return self.weights_lr_multiplier
+
+    def getBiasLearningRateMultiplier(self):
+        return self.bias_lr_multiplier
+
 
 class PoolConf(Fluent):
     """kernel/conf/PoolConf.java:20-33. Scalar setters apply to both spatial dims."""
@@ -148,6 +195,22 @@ class PoolConf(Fluent):
         self.method = PoolMethod.from_string(m)
         return self
 
+    def getKernelSize(self):
+        return self.kernel_height
+
+    def getStrideSize(self):
+        return self.stride_height
+
+    def getPaddingSize(self):
+        return self.padding_height
+
+    def setGlobal(self, flag):
+        self.global_pooling = bool(flag)
+        return self
+
+    def isGlobal(self):
+        return self.global_pooling
+
 
 class BatchNormConf(Fluent):
     """kernel/conf/BatchNormConf.java:24-39."""
@@ -161,6 +224,28 @@ class BatchNormConf(Fluent):
         super().__init__(**kw)
         self.weight_initialiser = self.weight_initialiser or InitialiserConf(value=1.0)
         self.bias_initialiser = self.bias_initialiser or InitialiserConf(value=0.0)
+
+    def setBias(self, flag):
+        """Accepted for the reference's API; the shift term is always a model variable here (as in its kernels)."""
+        return self
+
+    def hasBias(self):
+        return True
+
+    # learning-rate multipliers under the reference's names
+    def setWeightsLearningRateMultiplier(self, v):
+        self.weights_lr_multiplier = float(v)
+        return self
+
+    def setBiasLearningRateMultiplier(self, v):
+        self.bias_lr_multiplier = float(v)
+        return self
+
+    def getWeightsLearningRateMultiplier(self):
+        return self.weights_lr_multiplier
+
+    def getBiasLearningRateMultiplier(self):
+        return self.bias_lr_multiplier
 
 
 class InnerProductConf(Fluent):
@@ -181,6 +266,24 @@ class InnerProductConf(Fluent):
     def hasBias(self):
         return self.bias
 
+    def numberOfOutputs(self):
+        return self.number_of_outputs
+
+    # learning-rate multipliers under the reference's names
+    def setWeightsLearningRateMultiplier(self, v):
+        self.weights_lr_multiplier = float(v)
+        return self
+
+    def setBiasLearningRateMultiplier(self, v):
+        self.bias_lr_multiplier = float(v)
+        return self
+
+    def getWeightsLearningRateMultiplier(self):
+        return self.weights_lr_multiplier
+
+    def getBiasLearningRateMultiplier(self):
+        return self.bias_lr_multiplier
+
 
 class DropoutConf(Fluent):
     """kernel/conf/DropoutConf.java:8 — ratio = probability of dropping a unit."""
@@ -190,6 +293,13 @@ class DropoutConf(Fluent):
 class ReLUConf(Fluent):
     """kernel/conf/ReLUConf.java:17-20."""
     FIELDS = dict(negative_slope=0.0, activation_mode=ActivationMode.RELU, ceiling=0.0)
+
+    def setReLUCeiling(self, ceiling):
+        self.ceiling = float(ceiling)
+        return self
+
+    def getReLUCeiling(self):
+        return self.ceiling
 
 
 class SoftMaxConf(Fluent):
@@ -217,6 +327,14 @@ class ElementWiseOpConf(Fluent):
     def getCoefficient(self, i):
         return 1.0 if not self.coefficients else float(self.coefficients[i])
 
+    def numberOfCoefficients(self):
+        return 0 if self.coefficients is None else len(self.coefficients)
+
+    def resizeCoefficients(self, length):
+        """Grow the coefficient list to `length` entries, new ones 1 (ElementWiseOpConf.java:39-60)."""
+        cur = list(self.coefficients or [])
+        self.coefficients = cur[:length] + [1.0] * max(0, length - len(cur))
+
 
 class ConcatConf(Fluent):
     """kernel/conf/ConcatConf.java:13-14."""
@@ -239,10 +357,37 @@ class DataTransformConf(Fluent):
         self.subtract_mean = True
         return self
 
+    def hasMeanPixel(self):
+        return self.mean_pixel_values is not None
+
+    def subtractMean(self):
+        return self.mean_image_filename is not None or self.mean_pixel_values is not None
+
 
 class LRNConf(Fluent):
     """kernel/conf/LRNConf.java:34-39."""
     FIELDS = dict(local_size=5, alpha=1.0, beta=0.75, k=1.0, region=NormalisationRegion.ACROSS_CHANNELS)
+
+    def setSize(self, size):
+        self.local_size = int(size)
+        return self
+
+    def getSize(self):
+        return self.local_size
+
+    def setKappa(self, kappa):
+        self.k = float(kappa)
+        return self
+
+    def getKappa(self):
+        return self.k
+
+    def setNormalisationRegion(self, region):
+        self.region = NormalisationRegion.from_string(region)
+        return self
+
+    def getNormalisationRegion(self):
+        return self.region
 
 
 class MatFactConf(Fluent):
@@ -250,6 +395,15 @@ class MatFactConf(Fluent):
     FIELDS = dict(number_of_latent_variables=10, number_of_rows=0, number_of_columns=0, learning_rate_eta0=0.001,
                   lambda_=0.05, model_variable_initialiser=None)
     ALIASES = {"lambda": "lambda_"}
+
+    def numberOfLatentVariables(self):
+        return self.number_of_latent_variables
+
+    def numberOfRows(self):
+        return self.number_of_rows
+
+    def numberOfColumns(self):
+        return self.number_of_columns
 
 
 class NoopConf(Fluent):
@@ -319,6 +473,21 @@ class SolverConf(Fluent):
         """Position in the multi-step schedule (SolverConf.java:209-212), e.g. after a resume."""
         self._step = int(step)
         return self
+
+    def getCurrentStep(self):
+        return self._step
+
+    def getStepValuesToString(self):
+        v = self.steps_in_tasks() if hasattr(self, "steps_in_tasks") else []
+        return None if not v else ",".join(str(int(x)) for x in v)
+
+    def GPURegister(self):
+        """The reference pushes the solver's constants to its native library here; the device reads them from the task
+        parameter block, so there is nothing to register."""
+        return None
+
+    def toString(self):
+        return self.dump() if hasattr(self, "dump") else repr(self)
 
     def setModelConf(self, parent):
         self.parent = parent

@@ -421,3 +421,24 @@ def test_reference_setter_names_exist():
     m = ModelConf.reset().setBatchSize(64).setWpc(4).setSlack(0).setNumberOfSplits(2).setTrainingDataset("train").setValidationDataset("test")
     assert m.splits == 2 and m.getDataset(Phase.TRAIN) == "train" and m.getDataset(Phase.CHECK) == "test"
     assert m.getSolverConf().setCurrentStep(1)._step == 1
+
+
+def test_operator_conf_reference_method_names():
+    """Indexed kernel / stride / padding access, learning-rate multipliers, pool / LRN / ReLU / element-wise helpers under the
+    reference's names (kernel/conf/*.java)."""
+    from crossbow_b200.conf import BatchNormConf, DataTransformConf, LRNConf, MatFactConf
+    c = ConvConf().setNumberOfOutputs(8).setKernelSize(2).setKernel(0, 7).setKernel(1, 1).setStride(0, 1).setStride(1, 1) \
+        .setPadding(0, 3).setPadding(1, 0).setNumberOfGroup(1).setWeightsLearningRateMultiplier(2.0)
+    assert (c.kernel_height, c.kernel_width, c.getPadding(0), c.getPadding(1), c.numberOfOutputs(), c.numberOfGroups()) == (7, 1, 3, 0, 8, 1)
+    assert c.getWeightsLearningRateMultiplier() == 2.0 and c.getBiasLearningRateMultiplier() == 1.0
+    p = PoolConf().setKernelSize(3).setStrideSize(2).setGlobal(True)
+    assert p.isGlobal() and p.getKernelSize() == 3 and p.getStrideSize() == 2 and p.getPaddingSize() == 0
+    assert LRNConf().setSize(7).setKappa(2.0).getSize() == 7 and ReLUConf().setReLUCeiling(6).getReLUCeiling() == 6.0
+    e = ElementWiseOpConf()
+    assert e.numberOfCoefficients() == 0
+    e.resizeCoefficients(2)
+    assert e.coefficients == [1.0, 1.0]
+    d = DataTransformConf()
+    assert not d.subtractMean() and d.setMeanPixelValues(1.0, 2.0, 3.0).hasMeanPixel() and d.subtractMean()
+    assert BatchNormConf().setBiasLearningRateMultiplier(0.5).getBiasLearningRateMultiplier() == 0.5
+    assert MatFactConf().numberOfLatentVariables() == 10
