@@ -694,6 +694,43 @@ class SystemConf(_OptionHolder):
     def queueMeasurements(self, flag): return self._set("queue_measurements", bool(flag))
     def useDirectBuffers(self, flag): return self._set("use_direct_buffers", bool(flag))
 
+    # ---- and its getter names (SystemConf.java) ----
+    def numberOfWorkerThreads(self): return self.number_of_workers
+    def numberOfCPUModelReplicas(self): return self.number_of_cpu_models
+    def numberOfGPUModelReplicas(self): return self.number_of_gpu_models
+    def numberOfGPUStreams(self): return self.number_of_gpu_streams
+    def numberOfGPUCallbackHandlers(self): return self.number_of_callback_handlers
+    def numberOfGPUTaskHandlers(self): return self.number_of_task_handlers
+    def numberOfReadersPerModel(self): return self.readers_per_model
+    def numberOfResultSlots(self): return self.number_of_result_slots
+    def numberOfBuffers(self): return self.number_of_buffers
+    def numberOfFileHandlers(self): return self.number_of_file_handlers
+    def maxNumberOfMappedPartitions(self): return self.mapped_partitions_window
+    def getPerformanceMonitorInterval(self): return self.monitor_interval
+    def getTaskQueueSizeLimit(self): return self.task_queue_size
+    def getVariableBufferSize(self): return self.data_buffer_size
+    def teeMeasurements(self): return self.tee_measurements
+    def tryReuseMemory(self): return self.reuse_memory
+    def getExecutionMode(self): return self.executionMode()
+    def getOptions(self): return dict(self.OPTIONS)
+
+    def getPageSize(self):
+        import mmap
+        return mmap.PAGESIZE
+
+    def getHomeDirectory(self):
+        """`CROSSBOW_HOME` in the reference (mandatory there); here the directory of the package unless set."""
+        import os
+        return getattr(self, "_home", None) or os.environ.get("CROSSBOW_HOME") or os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def setHomeDirectory(self, d):
+        self._home = d
+        return self
+
+    def getCoreMapper(self):
+        from .utils.coremap import CoreMapper
+        return CoreMapper()
+
     def isHybrid(self):
         return self.cpu and self.gpu
 
@@ -762,6 +799,41 @@ class ModelConf(_OptionHolder):
 
     def setNumberOfSplits(self, n):
         self.splits = int(n)
+        return self
+
+    def numberOfSplits(self):
+        return self.splits
+
+    def getTrainingDataset(self):
+        return self.getDataset(Phase.TRAIN)
+
+    def getValidationDataset(self):
+        return self.getDataset(Phase.CHECK)
+
+    def getOptions(self):
+        return dict(self.OPTIONS)
+
+    def getInputShape(self, phase=Phase.TRAIN):
+        ds = self.getDataset(phase)
+        return None if ds is None else [self.batch_size] + list(ds.example_shape)
+
+    def getTaskSize(self, phase=Phase.TRAIN):
+        """Bytes of one task's examples."""
+        ds = self.getDataset(phase)
+        return 0 if ds is None else int(ds.batch_bytes())
+
+    def numberOfTestTasks(self):
+        return self.numberOfTasksPerEpoch(Phase.CHECK) if self.getDataset(Phase.CHECK) is not None else 0
+
+    def getDatasetType(self, phase=Phase.TRAIN):
+        ds = self.getDataset(phase)
+        return None if ds is None else type(ds).__name__
+
+    def isLightWeight(self, phase=Phase.TRAIN):
+        return self.getDatasetType(phase) == "LightDataset"
+
+    def init(self):
+        """The reference opens its data sets here; data sets open themselves when constructed."""
         return self
 
     def setBatchSize(self, n):

@@ -15,3 +15,22 @@ def plan(task_handlers: int, file_handlers: int, callback_handlers: int, offset:
         return out
 
     return {"dispatcher": [0], "worker": [offset % n], "task": take(task_handlers), "file": take(file_handlers), "callback": take(callback_handlers)}
+
+
+class CoreMapper:
+    """The plan for the current system configuration (what `SystemConf.getCoreMapper()` hands out in the reference)."""
+
+    def __init__(self, conf=None):
+        if conf is None:
+            from ..conf import SystemConf
+            conf = SystemConf.getInstance()
+        self.cores = plan(max(0, conf.number_of_task_handlers), max(0, conf.number_of_file_handlers),
+                          max(1, conf.number_of_callback_handlers), conf.core_mapper_offset)
+
+    def get(self, role: str, index: int = 0) -> int:
+        """Core of the index-th thread of a role: dispatcher, worker, task, file, callback."""
+        ids = self.cores[role]
+        return ids[index % len(ids)] if ids else 0
+
+    def dump(self) -> str:
+        return "\n".join(f"{k:<10s} {v}" for k, v in self.cores.items())
