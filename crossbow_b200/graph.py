@@ -105,6 +105,30 @@ class DataflowNode:
     def isMostDownstream(self):
         return not self.next
 
+    # accessors under the reference's names (DataflowNode.java)
+    def getNextList(self):
+        return list(self.next)
+
+    def getPreviousList(self):
+        return list(self.prev)
+
+    def getNextOperators(self):
+        return [n.op for n in self.next]
+
+    def getPreviousOperators(self):
+        return [n.op for n in self.prev]
+
+    def getLabel(self):
+        return self.label
+
+    def setLabel(self, label):
+        self.label = int(label)
+        return self
+
+    def getOrder(self):
+        """Position in the topological order of the sub-graph that owns the node (-1 before it is part of one)."""
+        return getattr(self, "order_index", -1)
+
     def __repr__(self):
         return f"Node({self.op})"
 
@@ -144,6 +168,7 @@ class SubGraph:
     def connectTo(self, g: "SubGraph"):
         """Chain sub-graphs: the output batch of this graph feeds ``g`` on the same replica (SubGraph.java:230-234)."""
         self.next_graph = g
+        g.prev_graph = self
         return g
 
     def nodes(self):
@@ -155,9 +180,53 @@ class SubGraph:
     def numberOfOperators(self):
         return len(self.order)
 
+    cardinality = numberOfOperators
+
+    # accessors under the reference's names (SubGraph.java)
+    def getId(self):
+        return self.id
+
+    def getName(self):
+        return f"SubGraph #{self.id}"
+
+    def getDataflowNode(self):
+        return self.head
+
+    def getNext(self):
+        return self.next_graph
+
+    def getPrevious(self):
+        return getattr(self, "prev_graph", None)
+
+    def setPrevious(self, g):
+        self.prev_graph = g
+        return self
+
+    def isMostUpstream(self):
+        return self.getPrevious() is None
+
+    def getBranchFactor(self):
+        return 1                      # the reference's labelling pass is disabled: one stream branch per learner
+
+    def getInputShape(self):
+        return getattr(self, "input_shape", None)
+
+    def getOutputShape(self):
+        last = [n for n in self.forward_nodes() if n.op.getOutputShape() is not None]
+        return last[-1].op.getOutputShape() if last else None
+
+    def dump(self) -> str:
+        return f"=== [{self.getName()}: {self.numberOfOperators()} operators] ===\n" + " -> ".join(str(n.op) for n in self.order)
+
+    def export(self) -> str:
+        return self.exportDot()
+
     def init(self, input_shape: Shape, label_shape: Shape, model: Model, first_id=0):
         """Assign operator ids, propagate shapes and register model variables (once per operator)."""
         self.model = model
+        self.input_shape = input_shape
+        for i, n in enumerate(self.order):
+            n.order_index = i
         next_id = first_id
         for n in self.order:
             op = n.op
@@ -260,6 +329,34 @@ class Dataflow:
 
     def isTest(self):
         return self.phase == Phase.CHECK
+
+    # accessors under the reference's names (Dataflow.java)
+    def getId(self):
+        return self.id
+
+    def numberOfSubGraphs(self):
+        return len(self.subgraphs())
+
+    def numberOfOperators(self):
+        return self.graph.numberOfOperators()
+
+    def totalNumberOfOperators(self):
+        return sum(g.numberOfOperators() for g in self.subgraphs())
+
+    cardinality = totalNumberOfOperators
+
+    def exportDot(self) -> str:
+        return self.export()
+
+    def dumpMemoryRequirements(self) -> str:
+        return "\n".join(g.dumpMemoryRequirements() for g in self.subgraphs())
+
+    def init(self, input_shape, label_shape, model, first_id=0):
+        """Initialise every sub-graph of the chain; returns the next free operator id."""
+        nid = first_id
+        for g in self.subgraphs():
+            nid = g.init(input_shape, label_shape, model, nid)
+        return nid
 
     def export(self) -> str:
         return "\n".join(g.exportDot() for g in self.subgraphs())
