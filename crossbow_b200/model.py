@@ -71,6 +71,32 @@ class Shape:
     def tuple(self):
         return tuple(self.dims)
 
+    # remaining names of model/Shape.java
+    def push(self, value):
+        self.dims.append(int(value))
+
+    def countElements(self, start, end=None):
+        return self.countAllElements(start, end)
+
+    def offset(self, n, c):
+        """Element offset of (example n, channel c) in a contiguous N x C x H x W tensor."""
+        return ((n * self.numberOfChannels() + c) * self.height()) * self.width()
+
+    def array(self):
+        return self.dims
+
+    def getNCHW(self, out=None):
+        v = [self.numberOfExamples(), self.numberOfChannels(), self.height(), self.width()]
+        if out is not None:
+            out[:4] = v
+        return v
+
+    def equals(self, other):
+        return self == other
+
+    def toString(self):
+        return repr(self)
+
     def __eq__(self, o):
         return isinstance(o, Shape) and self.dims == o.dims
 
@@ -124,6 +150,27 @@ class Variable:
     def setLearningRateMultiplier(self, m):
         self.lr_multiplier = float(m)
         return self
+
+    # accessors of model/Variable.java
+    def getLearningRateMultiplier(self):
+        return self.lr_multiplier
+
+    def getName(self):
+        return self.name
+
+    def getShape(self):
+        return self.shape
+
+    def getOrder(self):
+        return self.order
+
+    def setOrder(self, order):
+        self.order = int(order)
+        return self
+
+    def capacity(self):
+        """Bytes of the variable."""
+        return 4 * self.elements()
 
     def initialise(self, conf: InitialiserConf):
         self.initialiser = conf
@@ -179,6 +226,26 @@ class Model:
         self._final = False
         self.elements = 0
         self.device_elements = 0
+
+    # accessors of model/Model.java
+    def getVariables(self):
+        return list(self.variables)
+
+    def getVariable(self, op_id: int, order: int = 1):
+        """Variable `order` (1 = weights, 2 = bias) of an operator, or None."""
+        for v in self.variables:
+            if v.op_id == op_id and v.order == order:
+                return v
+        return None
+
+    def getSize(self):
+        return len(self.variables)
+
+    def capacity(self):
+        return self.bytes()
+
+    def toString(self):
+        return self.dump()
 
     def register(self, op_id: int, var: Variable, order: int):
         if self._final:
