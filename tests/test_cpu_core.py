@@ -442,3 +442,26 @@ def test_operator_conf_reference_method_names():
     assert not d.subtractMean() and d.setMeanPixelValues(1.0, 2.0, 3.0).hasMeanPixel() and d.subtractMean()
     assert BatchNormConf().setBiasLearningRateMultiplier(0.5).getBiasLearningRateMultiplier() == 0.5
     assert MatFactConf().numberOfLatentVariables() == 10
+
+
+def test_graph_and_model_accessors_under_reference_names():
+    from crossbow_b200.models import build
+    spec = build("lenet-caffe", solver_conf=SolverConf())
+    m = Model()
+    df = Dataflow(spec.train)
+    nid = df.init(Shape([8, 1, 28, 28]), Shape([8]), m)
+    m.finalise()
+    g = df.getSubGraph()
+    assert nid == df.totalNumberOfOperators() == g.cardinality() and df.numberOfSubGraphs() == 1 and df.getId() == 0
+    assert g.getInputShape().array() == [8, 1, 28, 28] and g.isMostUpstream() and g.getNext() is None and g.getBranchFactor() == 1
+    assert g.getDataflowNode() is g.head and g.head.getOrder() == 0 and g.head.getNextList()[0].getPreviousList() == [g.head]
+    assert "digraph" in df.exportDot() and "operators" in g.dump() and df.dumpMemoryRequirements()
+    w = m.getVariable(0, 1)
+    assert m.getSize() == len(m.getVariables()) == 8 and m.capacity() == 4 * m.elements and w.getName() == "weights"
+    assert w.getShape().array() == [20, 1, 5, 5] and w.capacity() == 2000 and w.getLearningRateMultiplier() == 1.0 and m.getVariable(99) is None
+    s = Shape([2, 3, 4, 5])
+    assert s.offset(1, 2) == 100 and s.getNCHW() == [2, 3, 4, 5] and s.countElements(2) == 20 and s.equals(Shape([2, 3, 4, 5])) and s.toString() == "[2, 3, 4, 5]"
+    s.push(6)
+    assert s.dimensions() == 5
+    g2 = SubGraph(DataflowNode(Operator("x", ReLU(ReLUConf()))))
+    assert g.connectTo(g2) is g2 and g2.getPrevious() is g and not g2.isMostUpstream()
