@@ -15,9 +15,8 @@ class _NamedEnum(enum.IntEnum):
         if isinstance(s, cls):
             return s
         key = str(s).strip().upper().replace("-", "_")
-        for m in cls:
-            if m.name == key:
-                return m
+        if key in cls.__members__:              # (includes aliases)
+            return cls.__members__[key]
         raise ValueError(f"error: invalid {cls.__name__}: {s}")
 
     fromString = from_string
@@ -155,6 +154,19 @@ class NormalisationMode(_NamedEnum):
 class NormalisationRegion(_NamedEnum):
     ACROSS_CHANNELS = 0
     WITHIN_CHANNEL = 1
+    WITHIN_CHANNELS = 1      # the reference's spelling (types/NormalisationRegion.java); same member
+
+
+class CudnnKernelType(_NamedEnum):
+    """types/CudnnKernelType.java: which library descriptor family a kernel used in the reference.  Kept for programs that
+    name it; the kernels here are hand-written and need no such tag."""
+    UNDEFINED = 0
+    CONV = 1
+    POOL = 2
+    RELU = 3
+    SOFTMAX = 4
+    BATCHNORM = 5
+    DROPOUT = 6
 
 
 class DatasetType(_NamedEnum):
