@@ -128,6 +128,20 @@ class Replica:
 
 
 def run(args, cfg, json_out):
+    """Stand-alone arm (`bench.py --impl cudnn`): measure, print the JSON line, leave the process group."""
+    import torch.distributed as dist
+    out = measure(args, cfg)
+    if int(os.environ.get("RANK", 0)) == 0:
+        print(json_out(out))
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return 0
+
+
+def measure(args, cfg, min_seconds=0.0):
+    """Run the library arm in this process (joining the existing process group if there is one) and return its record.
+    `min_seconds`: repeat the timed block of `args.steps` steps until that much time has been measured; the reported
+    value is the median repeat."""
     import torch.distributed as dist
     torch.backends.cudnn.benchmark = True
     torch.backends.cudnn.allow_tf32 = True
@@ -140,13 +154,11 @@ def run(args, cfg, json_out):
     k, batch = args.replicas or cfg["replicas"], args.batch or cfg["batch"]
     build = {"resnet32": resnet32, "resnet50": resnet50}.get(args.model)
     if build is None:
-        print(json_out({"impl": "cudnn", "unavailable": f"no library arm for {args.model}"}))
-        return 0
+        return {"impl": "cudnn", "unavailable": f"no library arm for {args.model}"}
     if k > 4:
         # eight captured graphs replaying on eight streams did not finish within 15 minutes on this pool (cause not found);
         # the arm is only run at the replica counts that were seen to complete
-        print(json_out({"impl": "cudnn", "unavailable": "library arm is limited to 4 replicas per GPU"}))
-        return 0
+        return {"impl": "cudnn", "unavailable": "library arm is limited to 4 replicas per GPU"}
     torch.manual_seed(1)
     base = build(cfg["classes"]).cuda().to(memory_format=torch.channels_last).train()
     reps = [Replica(copy.deepcopy(base), batch, cfg["shape"], graphs=not args.no_graphs) for _ in range(k)]
@@ -204,41 +216,62 @@ def run(args, cfg, json_out):
                 losses.append(float(r.loss))
         return losses
 
+    def timed_device():
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(sync_stream)
+        for i in range(args.steps):
+            step(False, i)
+        for r in reps:
+            sync_stream.wait_stream(r.stream)
+        e1.record(sync_stream)
+        e1.synchronize()
+        barrier()
+        return mx(e0.elapsed_time(e1))
+
+    def timed_e2e():
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            step(True, i)
+        torch.cuda.synchronize()
+        return mx(time.perf_counter() - t0) * 1e3
+
+    def repeat(fn):
+        first = fn()
+        n = max(1, min(50, int(-(-min_seconds * 1e3 // max(first, 1e-3))))) if min_seconds > 0 else 1
+        v = sorted([first] + [fn() for _ in range(n - 1)])
+        return v[len(v) // 2], v
+
+    sampler = None
+    if getattr(args, "clock_sampler", None) is not None:
+        sampler = args.clock_sampler(local)
+        sampler.start()
     for i in range(max(3, args.warmup)):
         step(False, i)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(sync_stream)
-    for i in range(args.steps):
-        step(False, i)
-    for r in reps:
-        sync_stream.wait_stream(r.stream)
-    e1.record(sync_stream)
-    e1.synchronize()
-    barrier()
-    dev_ms = mx(e0.elapsed_time(e1))
+    dev_ms, dev_all = repeat(timed_device)
     for i in range(3):
         step(True, i)
+    e2e_ms, e2e_all = repeat(timed_e2e)
     barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        step(True, i)
-    torch.cuda.synchronize()
-    e2e_s = mx(time.perf_counter() - t0)
-    barrier()
+    if sampler is not None:
+        sampler.stop_flag.set()
+        sampler.join(timeout=2)
     images = batch * k * world
-    if rank == 0:
-        print(json_out({
-            "metric": f"{args.model} SMA training throughput", "value": round(images * args.steps / (dev_ms / 1e3), 1), "unit": "images/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(dev_ms / args.steps, 4),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32 (cuDNN / cuBLAS), fp32 storage",
-            "data": "synthetic", "impl": "cudnn",
-            "config": {"model": args.model, "global_batch": images, "batch_per_replica": batch, "replicas_per_gpu": k,
-                       "parallelism": f"dp{world} x {k} replicas/GPU, SMA alpha 0.1, wpc = k*G", "sync": "element-wise kernels + NCCL all-reduce",
-                       "cuda_graphs": reps[0].graph is not None, "layout": "channels_last"},
-            "e2e": {"value": round(images * args.steps / e2e_s, 1), "unit": "images/s", "h2d_bytes_per_step": k * batch * (4 * int(torch.tensor(cfg["shape"]).prod()) + 8),
-                    "d2h_bytes_per_step": 4 * k},
-            "gpu_launches": 0, "note": "library kernels only: none of this repository's kernels run in this arm"}))
-    if world > 1:
-        dist.destroy_process_group()
-    return 0
+    out = {
+        "metric": f"{args.model} SMA training throughput", "value": round(images * args.steps / (dev_ms / 1e3), 1), "unit": "images/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(dev_ms / args.steps, 4),
+        "repeats": len(dev_all), "ms_per_step_min_max": [round(dev_all[0] / args.steps, 4), round(dev_all[-1] / args.steps, 4)],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32 (cuDNN / cuBLAS), fp32 storage",
+        "data": "synthetic", "impl": "cudnn",
+        "config": {"model": args.model, "global_batch": images, "batch_per_replica": batch, "replicas_per_gpu": k,
+                   "parallelism": f"dp{world} x {k} replicas/GPU, SMA alpha 0.1, wpc = k*G", "sync": "element-wise kernels + NCCL all-reduce",
+                   "cuda_graphs": reps[0].graph is not None, "layout": "channels_last"},
+        "e2e": {"value": round(images * args.steps / (e2e_ms / 1e3), 1), "unit": "images/s", "repeats": len(e2e_all),
+                "h2d_bytes_per_step": k * batch * (4 * int(torch.tensor(cfg["shape"]).prod()) + 8), "d2h_bytes_per_step": 4 * k},
+        "gpu_launches": 0, "note": "library kernels only: none of this repository's kernels run in this arm"}
+    if sampler is not None:
+        out["clocks"] = sampler.summary()
+    del reps
+    torch.cuda.empty_cache()
+    return out

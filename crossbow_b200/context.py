@@ -3,6 +3,11 @@
 API follows the reference (ExecutionContext.java:92-622): ``init()``, ``train(n, unit)``, ``trainAndTest(n, unit)``,
 ``test()``, ``trainForDuration``, ``trainUntilCondition``, ``trainUntilConditionOrForDuration``, ``destroy()``.
 
+Units on several GPUs (one process per GPU): task counts, `--wpc`, epochs, step values, display and test intervals are
+those of the JOB, as in the reference's single process over all GPUs (ExecutionContext.java:257-283,
+solverconfiguration.c:116-161).  Rank r of G runs the job's tasks r, G + r, 2 G + r, ... and so issues 1/G of every
+count (rounded up); `train(N, "epochs")` is N passes over the data whatever G is.
+
 Scheduling model (what the reference spreads over the dispatcher, task queue, task/callback handler threads, the
 result collector and the model manager): tasks are numbered by a ``WorkClock``; each task goes to the next learner
 in round-robin order whose replica clock satisfies the staleness bound, the learner's previous result is collected
@@ -74,13 +79,16 @@ class ExecutionContext:
         if ds is not None:
             solver.set_tasks_per_epoch(mc.numberOfTasksPerEpoch(Phase.TRAIN))
         init = self.model.initial_values(sys.random_seed)
-        wpc = mc.wpc_in_tasks()
+        from .parallel.peer import dist_info
+        self.rank, self.world, local = dist_info()
+        # `--wpc` counts the job's tasks between two synchronisations; this process issues its share of them
+        wpc = self._local(mc.wpc_in_tasks())
+        if mc.wpc_in_tasks() % self.world and not self.quiet:
+            print(f"warning: --wpc {mc.wpc_in_tasks()} is not a multiple of the {self.world} GPUs; every GPU runs {wpc} tasks per clock", flush=True)
         tg = train_df.getSubGraph()
         sg = test_df.getSubGraph() if test_df is not None else None
         if sys.gpu:
-            from .parallel.peer import dist_info
             from .engine import GpuEngine
-            self.rank, self.world, local = dist_info()
             if sys.number_of_gpu_streams not in (1, sys.number_of_gpu_models) and not self.quiet:
                 # (the reference warns when the two differ, executioncontext.c:1724-1725; here a learner IS a replica bound to
                 # its own stream, so the replica count decides)
@@ -94,12 +102,13 @@ class ExecutionContext:
                                     device_index=local, use_graphs=sys.use_cuda_graphs, seed=sys.random_seed,
                                     use_tc=sys.use_tensor_cores, fused_sync=sys.fused_sync,
                                     sync_timeout_s=sys.sync_timeout, splits=mc.splits, reuse_memory=sys.reuse_memory,
-                                    gradient_buckets=sys.gradient_buckets, debug_canaries=sys.debug_canaries)
+                                    gradient_buckets=sys.gradient_buckets, debug_canaries=sys.debug_canaries,
+                                    overlap_sync=sys.overlap_sync)
         else:
             from .engine import CpuEngine
             self.engine = CpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,
                                     replicas=sys.number_of_cpu_models, wpc=wpc, devices=1, seed=sys.random_seed,
-                                    splits=mc.splits)
+                                    splits=mc.splits, rank=self.rank, world=self.world)
         self.clock = WorkClock(wpc)
         self.monitor = PerformanceMonitor(batch, ds.batch_bytes() if ds is not None else 0, sys.monitor_interval / 1000.0)
         if sys.autotune_models:
@@ -259,18 +268,20 @@ class ExecutionContext:
             di *= max(1, self.mc.numberOfTasksPerEpoch(Phase.TRAIN))           # `--display-interval-unit epochs`
         if di <= 0:
             return
+        di = self._local(di)                                  # the interval counts the job's tasks; `task` is this process's
         self._disp_n += 1
         self._disp_loss += loss
         self._disp_acc += acc
         if (task + 1) % di:
             return
         n = max(1, self._disp_n)
+        shown_task = (task + 1) * getattr(self, "world", 1)                  # the job's task count at this point
         if self.sys.display_accumulated_loss:
             shown_loss, shown_acc = self._disp_loss / n, self._disp_acc / n
-            text = f"[{task + 1:06d}] loss {shown_loss:9.5f} ({loss:9.5f}) accuracy {shown_acc:7.4f} ({acc:7.4f})"
+            text = f"[{shown_task:06d}] loss {shown_loss:9.5f} ({loss:9.5f}) accuracy {shown_acc:7.4f} ({acc:7.4f})"
         else:
             shown_loss, shown_acc = loss, acc
-            text = f"[{task + 1:06d}] loss {loss:9.5f} accuracy {acc:7.4f}"
+            text = f"[{shown_task:06d}] loss {loss:9.5f} accuracy {acc:7.4f}"
         self._disp_n, self._disp_loss, self._disp_acc = 0, 0.0, 0.0
         if self.sys.queue_measurements:
             self.displayed.add(task, shown_loss, shown_acc)
@@ -279,9 +290,14 @@ class ExecutionContext:
         if not self.quiet:
             print(f"{text} ({self.monitor.last_rate():9.1f} examples/s)", flush=True)
 
+    def _local(self, job_tasks: int) -> int:
+        """This process's share of a count given in tasks of the whole job (rounded up, at least one)."""
+        return max(1, -(-int(job_tasks) // max(1, getattr(self, "world", 1))))
+
     def _tasks_of(self, n: int, unit) -> int:
+        """Tasks THIS process issues for `n` tasks / epochs of the job."""
         unit = TrainingUnit.from_string(unit)
-        return n * self.mc.numberOfTasksPerEpoch(Phase.TRAIN) if unit == TrainingUnit.EPOCHS else n
+        return self._local(n * self.mc.numberOfTasksPerEpoch(Phase.TRAIN) if unit == TrainingUnit.EPOCHS else n)
 
     # ---- public API ----
     def train(self, n: int, unit=TrainingUnit.TASKS):

@@ -8,9 +8,10 @@
 //          [5%, 100%] of the image, up to 100 attempts, else the whole image), crop, random horizontal flip, bilinear
 //          resize to SxS, scale to [-1, 1] (x/127.5 - 1), interleaved HWC -> planar CHW;
 //   test : aspect-preserving resize so that the shorter side is 1.145*S, centre crop SxS, same scaling.
-// The reference links libjpeg; this file carries its own baseline (sequential, Huffman) JPEG decoder instead, covering
-// grey-scale and YCbCr with 4:4:4 / 4:2:2 / 4:2:0 sampling (triangle-filter chroma up-sampling) and restart intervals.  Progressive files are reported as
-// unsupported (the caller substitutes a grey image and counts the failure).
+// The reference links libjpeg; this file carries its own Huffman JPEG decoder instead: sequential and progressive
+// frames, grey-scale / YCbCr / RGB / CMYK / YCCK, sampling factors up to 4 (triangle-filter chroma up-sampling for
+// 2:1), restart intervals.  Arithmetic-coded, lossless and 12-bit files are reported as unsupported (the caller
+// substitutes a grey image and counts the failure).
 // Double buffer (clib-multigpu/doublebuffer.c, recorddataset.c): two halves of NB batches each; worker threads decode
 // into the idle half while tasks consume the other; a swap waits (bounded) for the refill and for the tasks in flight.
 #include <algorithm>
@@ -32,10 +33,21 @@
 namespace xb {
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Baseline JPEG decoder
+// JPEG decoder: Huffman-coded baseline / extended sequential (SOF0, SOF1) and progressive (SOF2) files, 8-bit samples,
+// 1 component (grey), 3 (YCbCr, or RGB when an Adobe marker says so) or 4 (CMYK / YCCK, converted to RGB as the
+// reference does after libjpeg, image/image.c:119-139).  Every scan is decoded into a per-component coefficient array;
+// de-quantisation, the inverse DCT, chroma up-sampling and colour conversion run once, after the last scan.
+// The input is untrusted: table selectors, code lengths, run lengths and segment sizes are all checked.
 // ---------------------------------------------------------------------------------------------------------------------
 struct Huff { uint8_t bits[17]; uint8_t vals[256]; int mincode[17], maxcode[18], valptr[17]; bool set = false; };
-struct Comp { int id, h, v, tq, td, ta; int dc_pred; std::vector<uint8_t> plane; int pw, ph; };
+struct Comp {
+  int id = 0, h = 1, v = 1, tq = 0, td = 0, ta = 0;
+  int dc_pred = 0;
+  int bw = 0, bh = 0;                // blocks per row / column of the coefficient array (padded to whole MCUs)
+  int cw = 0, ch = 0;                // samples per row / column that belong to the image
+  std::vector<int16_t> coef;         // bw * bh blocks of 64 coefficients, natural (row-major) order
+  std::vector<uint8_t> plane; int pw = 0, ph = 0;
+};
 
 static const int kZigzag[64] = {0, 1, 8, 16, 9, 2, 3, 10, 17, 24, 32, 25, 18, 11, 4, 5, 12, 19, 26, 33, 40, 48, 41, 34, 27, 20, 13, 6, 7, 14, 21, 28,
                                 35, 42, 49, 56, 57, 50, 43, 36, 29, 22, 15, 23, 30, 37, 44, 51, 58, 59, 52, 45, 38, 31, 39, 46, 53, 60, 61, 54, 47, 55, 62, 63};
@@ -55,7 +67,7 @@ struct BitReader {
     --cnt;
     return (buf >> cnt) & 1;
   }
-  int bits(int n) { int v = 0; while (n--) v = (v << 1) | bit(); return v; }
+  int bits(int n) { int v = 0; while (n-- > 0) v = (v << 1) | bit(); return v; }
   void reset() { cnt = 0; marker = false; }
 };
 
@@ -73,17 +85,26 @@ static int decode_huff(BitReader& br, const Huff& h) {
   int code = 0;
   for (int l = 1; l <= 16; ++l) {
     code = (code << 1) | br.bit();
-    if (h.maxcode[l] >= 0 && code <= h.maxcode[l] && code >= h.mincode[l]) return h.vals[h.valptr[l] + code - h.mincode[l]];
+    if (h.maxcode[l] >= 0 && code <= h.maxcode[l] && code >= h.mincode[l]) {
+      const int idx = h.valptr[l] + code - h.mincode[l];
+      return idx >= 0 && idx < 256 ? h.vals[idx] : -1;
+    }
     if (br.marker) return -1;
   }
   return -1;
 }
+// value of a `t`-bit magnitude category (1 <= t <= 15)
 static inline int extend(int v, int t) { return v < (1 << (t - 1)) ? v - (1 << t) + 1 : v; }
 
+struct IdctTable {
+  float c[8][8];
+  IdctTable() { for (int x = 0; x < 8; ++x) for (int u = 0; u < 8; ++u) c[x][u] = (u == 0 ? std::sqrt(0.125f) : 0.5f) * std::cos((2 * x + 1) * u * 3.14159265358979f / 16.f); }
+};
 static void idct8x8(const float* in, uint8_t* out, int stride) {
-  // separable float IDCT (AAN-free, exact cosine basis): accurate to +-1 of libjpeg's slow integer IDCT
-  static float c[8][8]; static bool init = false;
-  if (!init) { for (int x = 0; x < 8; ++x) for (int u = 0; u < 8; ++u) c[x][u] = (u == 0 ? std::sqrt(0.125f) : 0.5f) * std::cos((2 * x + 1) * u * 3.14159265358979f / 16.f); init = true; }
+  // separable float IDCT on the exact cosine basis: within +-1 of libjpeg's slow integer IDCT.  The table is a
+  // function-local static: initialised once, thread-safe (several decode workers run at the same time).
+  static const IdctTable tab;
+  const float (*c)[8] = tab.c;
   float tmp[64];
   for (int y = 0; y < 8; ++y)
     for (int x = 0; x < 8; ++x) { float s = 0; for (int u = 0; u < 8; ++u) s += c[x][u] * in[y * 8 + u]; tmp[y * 8 + x] = s; }
@@ -95,13 +116,96 @@ static void idct8x8(const float* in, uint8_t* out, int stride) {
     }
 }
 
-// Decodes into interleaved RGB. Returns 0, or a negative code: -1 malformed, -2 unsupported (progressive / arithmetic / CMYK).
+// One block of one scan.  Returns false when the entropy-coded data ends or is malformed (the caller keeps what has been
+// decoded so far).  `eobrun` carries the end-of-band run of progressive AC scans across blocks.
+static bool decode_block(BitReader& br, Comp& c, int16_t* blk, const Huff* dc, const Huff* ac, bool progressive, int Ss, int Se, int Ah, int Al,
+                         int& eobrun) {
+  if (!progressive) {
+    int t = decode_huff(br, dc[c.td]);
+    if (t < 0 || t > 11) return false;
+    int diff = t ? extend(br.bits(t), t) : 0;
+    c.dc_pred += diff;
+    blk[0] = (int16_t)c.dc_pred;
+    for (int k = 1; k < 64;) {
+      int rs = decode_huff(br, ac[c.ta]);
+      if (rs < 0) return false;
+      int r = rs >> 4, s = rs & 15;
+      if (s == 0) { if (r == 15) { k += 16; continue; } break; }
+      k += r;
+      if (k > 63) return false;
+      blk[kZigzag[k]] = (int16_t)extend(br.bits(s), s);
+      ++k;
+    }
+    return true;
+  }
+  if (Ss == 0) {                                   // DC scan
+    if (Ah == 0) {
+      int t = decode_huff(br, dc[c.td]);
+      if (t < 0 || t > 11) return false;
+      int diff = t ? extend(br.bits(t), t) : 0;
+      c.dc_pred += diff;
+      blk[0] = (int16_t)(c.dc_pred * (1 << Al));
+    } else if (br.bit()) {
+      blk[0] = (int16_t)(blk[0] | (1 << Al));
+    }
+    return true;
+  }
+  const int bit = 1 << Al;
+  if (Ah == 0) {                                   // AC scan, first pass of a band
+    if (eobrun > 0) { --eobrun; return true; }
+    for (int k = Ss; k <= Se;) {
+      int rs = decode_huff(br, ac[c.ta]);
+      if (rs < 0) return false;
+      int r = rs >> 4, s = rs & 15;
+      if (s == 0) {
+        if (r < 15) { eobrun = (1 << r) - 1; if (r) eobrun += br.bits(r); break; }
+        k += 16;
+      } else {
+        k += r;
+        if (k > Se) return false;
+        blk[kZigzag[k]] = (int16_t)(extend(br.bits(s), s) * bit);
+        ++k;
+      }
+    }
+    return true;
+  }
+  // AC scan, refinement of a band
+  auto refine = [&](int16_t& v) { if (br.bit() && (v & bit) == 0) v = (int16_t)(v + (v > 0 ? bit : -bit)); };
+  if (eobrun > 0) {
+    --eobrun;
+    for (int k = Ss; k <= Se; ++k) { int16_t& v = blk[kZigzag[k]]; if (v != 0) refine(v); }
+    return true;
+  }
+  for (int k = Ss; k <= Se;) {
+    int rs = decode_huff(br, ac[c.ta]);
+    if (rs < 0) return false;
+    int r = rs >> 4, s = rs & 15, val = 0;
+    if (s == 0) {
+      if (r < 15) { eobrun = (1 << r) - 1; if (r) eobrun += br.bits(r); r = 64; }      // the rest of the band: corrections only
+    } else {
+      if (s != 1) return false;
+      val = br.bit() ? bit : -bit;
+    }
+    while (k <= Se) {
+      int16_t& v = blk[kZigzag[k++]];
+      if (v != 0) refine(v);
+      else { if (r == 0) { v = (int16_t)val; break; } --r; }
+    }
+  }
+  return true;
+}
+
+// Decodes into interleaved RGB. Returns 0, or a negative code: -1 malformed, -2 unsupported (arithmetic coding, lossless,
+// hierarchical, 12-bit samples, sampling factors above 4).
 static int jpeg_decode(const uint8_t* data, size_t size, std::vector<uint8_t>& rgb, int& W, int& H) {
   if (size < 4 || data[0] != 0xFF || data[1] != 0xD8) return -1;
   uint16_t qt[4][64]; bool qset[4] = {false, false, false, false};
   Huff dc[4], ac[4];
   std::vector<Comp> comps;
-  int restart = 0, hmax = 1, vmax = 1;
+  int restart = 0, hmax = 1, vmax = 1, mx = 0, my = 0;
+  bool progressive = false, adobe = false; int adobe_transform = -1;
+  int scans = 0;
+  unsigned seen = 0;
   size_t pos = 2;
   W = H = 0;
   while (pos + 4 <= size) {
@@ -110,155 +214,226 @@ static int jpeg_decode(const uint8_t* data, size_t size, std::vector<uint8_t>& r
     pos += 2;
     if (m == 0xD8 || (m >= 0xD0 && m <= 0xD7) || m == 0x01 || m == 0xFF) { if (m == 0xFF) --pos; continue; }
     if (m == 0xD9) break;
-    if (pos + 2 > size) return -1;
-    size_t len = (data[pos] << 8) | data[pos + 1];
-    if (len < 2 || pos + len > size) return -1;
+    if (pos + 2 > size) break;
+    size_t len = ((size_t)data[pos] << 8) | data[pos + 1];
+    if (len < 2 || pos + len > size) { if (scans) break; return -1; }
     const uint8_t* seg = data + pos + 2; size_t sl = len - 2;
     if (m == 0xDB) {
       size_t i = 0;
       while (i < sl) {
         int pq = seg[i] >> 4, tq = seg[i] & 15; ++i;
-        if (tq > 3) return -1;
-        for (int k = 0; k < 64; ++k) { if (i >= sl) return -1; qt[tq][kZigzag[k]] = pq ? (uint16_t)((seg[i] << 8) | seg[i + 1]) : seg[i]; i += pq ? 2 : 1; }
+        if (tq > 3 || pq > 1) return -1;
+        for (int k = 0; k < 64; ++k) {
+          if (i + (pq ? 2 : 1) > sl) return -1;
+          qt[tq][kZigzag[k]] = pq ? (uint16_t)((seg[i] << 8) | seg[i + 1]) : seg[i];
+          i += pq ? 2 : 1;
+        }
         qset[tq] = true;
       }
     } else if (m == 0xC4) {
       size_t i = 0;
       while (i + 17 <= sl) {
         int tc = seg[i] >> 4, th = seg[i] & 15; ++i;
-        if (th > 3) return -1;
+        if (th > 3 || tc > 1) return -1;
         Huff& h = tc ? ac[th] : dc[th];
         int total = 0; h.bits[0] = 0;
         for (int l = 1; l <= 16; ++l) { h.bits[l] = seg[i++]; total += h.bits[l]; }
         if (total > 256 || i + total > sl) return -1;
+        memset(h.vals, 0, sizeof h.vals);
         memcpy(h.vals, seg + i, total); i += total;
         build_huff(h);
       }
-    } else if (m == 0xC0 || m == 0xC1) {
+    } else if (m == 0xC0 || m == 0xC1 || m == 0xC2) {
+      if (!comps.empty()) return -1;                           // one frame per file
       if (sl < 6 || seg[0] != 8) return -2;
+      progressive = m == 0xC2;
       H = (seg[1] << 8) | seg[2]; W = (seg[3] << 8) | seg[4];
       int nc = seg[5];
-      if ((nc != 1 && nc != 3) || sl < (size_t)(6 + 3 * nc) || W <= 0 || H <= 0) return -2;
+      if ((nc != 1 && nc != 3 && nc != 4) || sl < (size_t)(6 + 3 * nc) || W <= 0 || H <= 0) return -2;
+      if ((long long)W * H > (1LL << 28)) return -2;
       comps.resize(nc);
       for (int i = 0; i < nc; ++i) {
         comps[i].id = seg[6 + 3 * i]; comps[i].h = seg[7 + 3 * i] >> 4; comps[i].v = seg[7 + 3 * i] & 15; comps[i].tq = seg[8 + 3 * i];
-        if (comps[i].h < 1 || comps[i].h > 2 || comps[i].v < 1 || comps[i].v > 2 || comps[i].tq > 3) return -2;
+        if (comps[i].h < 1 || comps[i].h > 4 || comps[i].v < 1 || comps[i].v > 4) return -2;
+        if (comps[i].tq > 3) return -1;
         hmax = std::max(hmax, comps[i].h); vmax = std::max(vmax, comps[i].v);
       }
-    } else if (m == 0xC2 || (m >= 0xC3 && m <= 0xCF && m != 0xC4 && m != 0xC8 && m != 0xCC)) {
-      return -2;
+      mx = (W + 8 * hmax - 1) / (8 * hmax); my = (H + 8 * vmax - 1) / (8 * vmax);
+      for (auto& c : comps) {
+        c.bw = mx * c.h; c.bh = my * c.v;
+        c.cw = (W * c.h + hmax - 1) / hmax; c.ch = (H * c.v + vmax - 1) / vmax;
+        c.coef.assign((size_t)c.bw * c.bh * 64, 0);
+      }
+    } else if (m >= 0xC3 && m <= 0xCF && m != 0xC4 && m != 0xC8 && m != 0xCC) {
+      return -2;                                               // lossless, hierarchical, arithmetic coding
     } else if (m == 0xDD) {
       if (sl < 2) return -1;
       restart = (seg[0] << 8) | seg[1];
+    } else if (m == 0xEE) {
+      if (sl >= 12 && memcmp(seg, "Adobe", 5) == 0) { adobe = true; adobe_transform = seg[11]; }
     } else if (m == 0xDA) {
       if (comps.empty() || sl < 1) return -1;
-      int ns = seg[0];
-      if (ns != (int)comps.size() || sl < (size_t)(1 + 2 * ns + 3)) return -2;
+      const int ns = seg[0];
+      if (ns < 1 || ns > (int)comps.size() || sl < (size_t)(1 + 2 * ns + 3)) return -1;
+      Comp* sc[4];
       for (int i = 0; i < ns; ++i) {
-        int cid = seg[1 + 2 * i];
-        for (auto& c : comps) if (c.id == cid) { c.td = seg[2 + 2 * i] >> 4; c.ta = seg[2 + 2 * i] & 15; }
+        const int cid = seg[1 + 2 * i];
+        sc[i] = nullptr;
+        for (auto& c : comps) if (c.id == cid) sc[i] = &c;
+        if (!sc[i]) return -1;                                 // the scan names a component the frame does not have
+        for (int j = 0; j < i; ++j) if (sc[j] == sc[i]) return -1;
+        sc[i]->td = seg[2 + 2 * i] >> 4; sc[i]->ta = seg[2 + 2 * i] & 15;
+        if (sc[i]->td > 3 || sc[i]->ta > 3) return -1;
       }
-      const int mcuw = 8 * hmax, mcuh = 8 * vmax;
-      const int mx = (W + mcuw - 1) / mcuw, my = (H + mcuh - 1) / mcuh;
-      for (auto& c : comps) {
-        if (!qset[c.tq] || !dc[c.td].set || !ac[c.ta].set) return -1;
-        c.pw = mx * 8 * c.h; c.ph = my * 8 * c.v; c.plane.assign((size_t)c.pw * c.ph, 128); c.dc_pred = 0;
+      int Ss = seg[1 + 2 * ns], Se = seg[2 + 2 * ns], Ah = seg[3 + 2 * ns] >> 4, Al = seg[3 + 2 * ns] & 15;
+      if (!progressive) { Ss = 0; Se = 63; Ah = Al = 0; }
+      else if (Ss > Se || Se > 63 || Al > 13 || Ah > 13 || (Ss == 0 && Se != 0) || (Ss > 0 && ns != 1)) return -1;
+      for (int i = 0; i < ns; ++i) {
+        const bool need_dc = !progressive || Ss == 0, need_ac = !progressive || Ss > 0;
+        if ((need_dc && Ah == 0 && !dc[sc[i]->td].set) || (need_ac && !ac[sc[i]->ta].set)) return -1;
+        sc[i]->dc_pred = 0;
       }
       BitReader br{data + pos + len, data + size};
-      int count = 0;
-      float blk[64];
-      for (int row = 0; row < my; ++row)
-        for (int col = 0; col < mx; ++col) {
-          if (restart && count == restart) {
-            // expect RSTn
-            br.reset();
-            while (br.p + 1 < br.end && !(br.p[0] == 0xFF && br.p[1] >= 0xD0 && br.p[1] <= 0xD7)) ++br.p;
-            if (br.p + 1 < br.end) br.p += 2;
-            for (auto& c : comps) c.dc_pred = 0;
-            count = 0;
+      int count = 0, eobrun = 0;
+      bool ok = true;
+      auto restart_if_due = [&]() {
+        if (!restart || count != restart) return;
+        br.reset();
+        while (br.p + 1 < br.end && !(br.p[0] == 0xFF && br.p[1] >= 0xD0 && br.p[1] <= 0xD7)) ++br.p;
+        if (br.p + 1 < br.end) br.p += 2;
+        for (int i = 0; i < ns; ++i) sc[i]->dc_pred = 0;
+        eobrun = 0; count = 0;
+      };
+      if (ns == 1) {
+        // a scan of one component walks that component's own blocks (those that hold image samples), row by row
+        Comp& c = *sc[0];
+        const int nbx = (c.cw + 7) / 8, nby = (c.ch + 7) / 8;
+        for (int by = 0; by < nby && ok; ++by)
+          for (int bx = 0; bx < nbx && ok; ++bx) {
+            restart_if_due();
+            ok = decode_block(br, c, &c.coef[((size_t)by * c.bw + bx) * 64], dc, ac, progressive, Ss, Se, Ah, Al, eobrun);
+            ++count;
           }
-          for (auto& c : comps)
-            for (int by = 0; by < c.v; ++by)
-              for (int bx = 0; bx < c.h; ++bx) {
-                for (int k = 0; k < 64; ++k) blk[k] = 0.f;
-                int t = decode_huff(br, dc[c.td]);
-                if (t < 0) goto done;                      // truncated stream: keep what has been decoded
-                int diff = t ? extend(br.bits(t), t) : 0;
-                c.dc_pred += diff;
-                blk[0] = (float)(c.dc_pred * qt[c.tq][0]);
-                for (int k = 1; k < 64;) {
-                  int rs = decode_huff(br, ac[c.ta]);
-                  if (rs < 0) goto done;
-                  int r = rs >> 4, s = rs & 15;
-                  if (s == 0) { if (r == 15) { k += 16; continue; } break; }
-                  k += r;
-                  if (k > 63) break;
-                  int z = kZigzag[k];
-                  blk[z] = (float)(extend(br.bits(s), s) * qt[c.tq][z]);
-                  ++k;
-                }
-                idct8x8(blk, c.plane.data() + (size_t)((row * c.v + by) * 8) * c.pw + (col * c.h + bx) * 8, c.pw);
-              }
-          ++count;
-        }
-    done:
-      // chroma up-sampling (libjpeg's "fancy" triangle filter for 2:1 factors, replication otherwise) + colour conversion
-      {
-        std::vector<std::vector<uint8_t>> full(comps.size());
-        for (size_t ci = 0; ci < comps.size(); ++ci) {
-          Comp& c = comps[ci];
-          const int cw = (W * c.h + hmax - 1) / hmax, chh = (H * c.v + vmax - 1) / vmax;
-          std::vector<uint8_t>& out = full[ci];
-          out.resize((size_t)W * H);
-          const bool h2 = c.h * 2 == hmax, v2 = c.v * 2 == vmax, h1 = c.h == hmax, v1 = c.v == vmax;
-          if (h1 && v1) {
-            for (int y = 0; y < H; ++y) memcpy(&out[(size_t)y * W], &c.plane[(size_t)y * c.pw], (size_t)W);
-          } else if (h2 && (v1 || v2)) {
-            std::vector<int> colsum((size_t)cw);
-            for (int y = 0; y < H; ++y) {
-              // vertical: nearer row weight 3, farther row weight 1 (v2), or the row itself times 4 (v1)
-              int yn = v2 ? y / 2 : y;
-              int yf = v2 ? ((y & 1) ? std::min(yn + 1, chh - 1) : std::max(yn - 1, 0)) : yn;
-              const uint8_t* rn = &c.plane[(size_t)yn * c.pw]; const uint8_t* rf = &c.plane[(size_t)yf * c.pw];
-              for (int x = 0; x < cw; ++x) colsum[x] = v2 ? 3 * rn[x] + rf[x] : rn[x];
-              uint8_t* o = &out[(size_t)y * W];
-              for (int x = 0; x < W; ++x) {
-                int i = x / 2, t = colsum[i];
-                int v;
-                if (v2) {
-                  if (cw == 1) v = (t * 4 + 8) >> 4;
-                  else if (!(x & 1)) v = i == 0 ? (t * 4 + 8) >> 4 : (t * 3 + colsum[i - 1] + 8) >> 4;
-                  else v = i == cw - 1 ? (t * 4 + 7) >> 4 : (t * 3 + colsum[i + 1] + 7) >> 4;
-                } else {
-                  if (cw == 1) v = t;
-                  else if (!(x & 1)) v = i == 0 ? t : (t * 3 + colsum[i - 1] + 1) >> 2;
-                  else v = i == cw - 1 ? t : (t * 3 + colsum[i + 1] + 2) >> 2;
-                }
-                o[x] = (uint8_t)v;
-              }
+      } else {
+        for (int row = 0; row < my && ok; ++row)
+          for (int col = 0; col < mx && ok; ++col) {
+            restart_if_due();
+            for (int i = 0; i < ns && ok; ++i) {
+              Comp& c = *sc[i];
+              for (int by = 0; by < c.v && ok; ++by)
+                for (int bx = 0; bx < c.h && ok; ++bx)
+                  ok = decode_block(br, c, &c.coef[((size_t)(row * c.v + by) * c.bw + (col * c.h + bx)) * 64], dc, ac, progressive, Ss, Se, Ah, Al, eobrun);
             }
-          } else {
-            for (int y = 0; y < H; ++y)
-              for (int x = 0; x < W; ++x) out[(size_t)y * W + x] = c.plane[(size_t)(y * c.v / vmax) * c.pw + x * c.h / hmax];
+            ++count;
           }
-        }
-        rgb.resize((size_t)W * H * 3);
-        for (size_t i = 0; i < (size_t)W * H; ++i) {
-          uint8_t* o = &rgb[i * 3];
-          if (comps.size() == 1) { o[0] = o[1] = o[2] = full[0][i]; continue; }
-          // libjpeg's fixed-point YCbCr -> RGB (16-bit fractions, rounded)
-          const int Y = full[0][i], cb = full[1][i] - 128, cr = full[2][i] - 128;
-          int r = Y + ((91881 * cr + 32768) >> 16);
-          int g = Y + ((-22554 * cb - 46802 * cr + 32768) >> 16);
-          int b = Y + ((116130 * cb + 32768) >> 16);
-          o[0] = (uint8_t)std::min(255, std::max(0, r)); o[1] = (uint8_t)std::min(255, std::max(0, g)); o[2] = (uint8_t)std::min(255, std::max(0, b));
-        }
       }
-      return 0;
+      ++scans;
+      // carry on behind the entropy-coded data: the next marker that is neither a stuffed byte nor a restart marker
+      size_t q = (size_t)(br.p - data);
+      while (q + 1 < size && !(data[q] == 0xFF && data[q + 1] != 0x00 && !(data[q + 1] >= 0xD0 && data[q + 1] <= 0xD7) && data[q + 1] != 0xFF)) ++q;
+      pos = q;
+      if (!progressive) {                                      // a sequential frame is complete once every component has had its scan
+        for (int i = 0; i < ns; ++i) seen |= 1u << (int)(sc[i] - comps.data());
+        if (seen == (1u << comps.size()) - 1u) break;
+      }
+      continue;
     }
     pos += len;
   }
-  return -1;
+  if (comps.empty() || scans == 0) return -1;
+  for (auto& c : comps) if (!qset[c.tq]) return -1;
+  // ---- coefficients -> samples -----------------------------------------------------------------------------------------
+  {
+    float blk[64];
+    for (auto& c : comps) {
+      c.pw = c.bw * 8; c.ph = c.bh * 8;
+      c.plane.assign((size_t)c.pw * c.ph, 128);
+      const int nbx = (c.cw + 7) / 8, nby = (c.ch + 7) / 8;
+      for (int by = 0; by < nby; ++by)
+        for (int bx = 0; bx < nbx; ++bx) {
+          const int16_t* q = &c.coef[((size_t)by * c.bw + bx) * 64];
+          for (int k = 0; k < 64; ++k) blk[k] = (float)((int)q[k] * (int)qt[c.tq][k]);
+          idct8x8(blk, c.plane.data() + (size_t)(by * 8) * c.pw + bx * 8, c.pw);
+        }
+      std::vector<int16_t>().swap(c.coef);
+    }
+  }
+  // chroma up-sampling (libjpeg's "fancy" triangle filter for 2:1 factors, replication otherwise) + colour conversion
+  {
+    std::vector<std::vector<uint8_t>> full(comps.size());
+    for (size_t ci = 0; ci < comps.size(); ++ci) {
+      Comp& c = comps[ci];
+      const int cw = c.cw, chh = c.ch;
+      std::vector<uint8_t>& out = full[ci];
+      out.resize((size_t)W * H);
+      const bool h2 = c.h * 2 == hmax, v2 = c.v * 2 == vmax, h1 = c.h == hmax, v1 = c.v == vmax;
+      if (h1 && v1) {
+        for (int y = 0; y < H; ++y) memcpy(&out[(size_t)y * W], &c.plane[(size_t)y * c.pw], (size_t)W);
+      } else if (h2 && (v1 || v2)) {
+        std::vector<int> colsum((size_t)cw);
+        for (int y = 0; y < H; ++y) {
+          // vertical: nearer row weight 3, farther row weight 1 (v2), or the row itself times 4 (v1)
+          int yn = v2 ? y / 2 : y;
+          int yf = v2 ? ((y & 1) ? std::min(yn + 1, chh - 1) : std::max(yn - 1, 0)) : yn;
+          const uint8_t* rn = &c.plane[(size_t)yn * c.pw]; const uint8_t* rf = &c.plane[(size_t)yf * c.pw];
+          for (int x = 0; x < cw; ++x) colsum[x] = v2 ? 3 * rn[x] + rf[x] : rn[x];
+          uint8_t* o = &out[(size_t)y * W];
+          for (int x = 0; x < W; ++x) {
+            int i = x / 2, t = colsum[i];
+            int v;
+            if (v2) {
+              if (cw == 1) v = (t * 4 + 8) >> 4;
+              else if (!(x & 1)) v = i == 0 ? (t * 4 + 8) >> 4 : (t * 3 + colsum[i - 1] + 8) >> 4;
+              else v = i == cw - 1 ? (t * 4 + 7) >> 4 : (t * 3 + colsum[i + 1] + 7) >> 4;
+            } else {
+              if (cw == 1) v = t;
+              else if (!(x & 1)) v = i == 0 ? t : (t * 3 + colsum[i - 1] + 1) >> 2;
+              else v = i == cw - 1 ? t : (t * 3 + colsum[i + 1] + 2) >> 2;
+            }
+            o[x] = (uint8_t)v;
+          }
+        }
+      } else {
+        for (int y = 0; y < H; ++y)
+          for (int x = 0; x < W; ++x) {
+            const int sy = std::min(chh - 1, y * c.v / vmax), sx = std::min(cw - 1, x * c.h / hmax);
+            out[(size_t)y * W + x] = c.plane[(size_t)sy * c.pw + sx];
+          }
+      }
+    }
+    const size_t nc = comps.size();
+    // three components are YCbCr unless an Adobe marker says "no transform" (or the component ids spell R, G, B);
+    // four are CMYK, or YCCK when the Adobe transform code is 2
+    const bool ycc3 = nc == 3 && !(adobe && adobe_transform == 0) && !(comps[0].id == 'R' && comps[1].id == 'G' && comps[2].id == 'B');
+    const bool ycck = nc == 4 && adobe && adobe_transform == 2;
+    auto ycc_to_rgb = [](int Y, int cb, int cr, int& r, int& g, int& b) {
+      // libjpeg's fixed-point YCbCr -> RGB (16-bit fractions, rounded)
+      cb -= 128; cr -= 128;
+      r = Y + ((91881 * cr + 32768) >> 16);
+      g = Y + ((-22554 * cb - 46802 * cr + 32768) >> 16);
+      b = Y + ((116130 * cb + 32768) >> 16);
+      r = std::min(255, std::max(0, r)); g = std::min(255, std::max(0, g)); b = std::min(255, std::max(0, b));
+    };
+    rgb.resize((size_t)W * H * 3);
+    for (size_t i = 0; i < (size_t)W * H; ++i) {
+      uint8_t* o = &rgb[i * 3];
+      if (nc == 1) { o[0] = o[1] = o[2] = full[0][i]; continue; }
+      if (nc == 3) {
+        int r = full[0][i], g = full[1][i], b = full[2][i];
+        if (ycc3) ycc_to_rgb(full[0][i], full[1][i], full[2][i], r, g, b);
+        o[0] = (uint8_t)r; o[1] = (uint8_t)g; o[2] = (uint8_t)b;
+        continue;
+      }
+      // four components: bring them to C, M, Y, K as libjpeg hands them out, then the reference's conversion
+      // (image/image.c:119-139: Adobe files store inverted inks, r = k * c / 255; otherwise r = (255 - k)(255 - c) / 255)
+      int c = full[0][i], mm = full[1][i], y = full[2][i];
+      const int k = full[3][i];
+      if (ycck) { int r, g, b; ycc_to_rgb(c, mm, y, r, g, b); c = 255 - r; mm = 255 - g; y = 255 - b; }
+      if (adobe) { o[0] = (uint8_t)(k * c / 255); o[1] = (uint8_t)(k * mm / 255); o[2] = (uint8_t)(k * y / 255); }
+      else { o[0] = (uint8_t)((255 - k) * (255 - c) / 255); o[1] = (uint8_t)((255 - k) * (255 - mm) / 255); o[2] = (uint8_t)((255 - k) * (255 - y) / 255); }
+    }
+  }
+  return 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

@@ -22,7 +22,17 @@
 // the multi-rank-on-one-GPU test entry uses a cooperative launch) because blocks wait on other GPUs' blocks.
 // Every wait is bounded by a wall-clock limit: on expiry the kernel records XB_TIMEOUT_FLAG in `status`, skips the
 // chunk's update and carries on to the end, so the context stays usable and the host can raise an error.
+//
+// Early release (model averaging without a replica overwrite): a replica's weights are final as soon as phase 1 has
+// corrected them - phases 2 and 3 only touch the central model.  The last block of a GPU to finish phase 1 therefore
+// stores the epoch into a RELEASE word, and the learners' streams wait for that word (a stream memory operation), not
+// for the end of the kernel: the replicas' next forward pass runs under the exchange and the central update, and a
+// learner never waits for another GPU.  The reference gets the same overlap by recording each replica's `updated`
+// event right after its correction, before the all-reduce is issued (clib-multigpu/synch/sma.c:108-118, :130).
+// The kernel also keeps a small time line per GPU (%globaltimer at entry, at the release and at the exit of its last
+// block, plus running sums), which is what the benchmarks report as synchronisation time per step.
 #include "common.cuh"
+#include <cuda.h>
 #include <string.h>
 
 namespace {
@@ -57,7 +67,16 @@ struct SyncArgs {
   unsigned int* ready2[MAXG];  // [nchunks] on every GPU: total of chunk has landed
   int* status;
   unsigned long long timeout_ns;
+  unsigned int* release;       // [0] release word (epoch once every replica of this GPU is corrected), [1] block counter; may be null
+  unsigned long long* stamps;  // time line, see XB_SYNC_STAMP_*; may be null
 };
+
+// Layout of the time line (64-bit words).  ENTRY / RELEASE / EXIT[epoch & 1] describe the most recent launch (the exit
+// stamp is the maximum over the blocks; two slots by epoch parity, so an early block of the next launch cannot disturb
+// it); COUNT, SUM_RELEASE and SUM_TOTAL accumulate (entry -> release) and (entry -> exit) nanoseconds of the launches
+// BEFORE the most recent one.
+enum { XB_SYNC_STAMP_ENTRY = 0, XB_SYNC_STAMP_RELEASE = 1, XB_SYNC_STAMP_EXIT = 2 /* and 3 */, XB_SYNC_STAMP_COUNT = 4,
+       XB_SYNC_STAMP_SUM_RELEASE = 5, XB_SYNC_STAMP_SUM_TOTAL = 6, XB_SYNC_STAMP_WORDS = 8 };
 
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -187,6 +206,38 @@ __device__ __forceinline__ void apply_total(const SyncArgs& a, const long long (
     }
 }
 
+// Called by every block once its share of phase 1 is done (all threads; contains a block barrier).  The last block of
+// the rank to arrive publishes the epoch in the release word: every replica of this GPU then holds its corrected weights.
+__device__ __forceinline__ void release_replicas(const SyncArgs& a) {
+  if (!a.release) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int arrived = atomicAdd(a.release + 1, 1u) + 1u;
+    if (arrived == gridDim.x) {
+      a.release[1] = 0;                                   // launches on one stream do not overlap: ready for the next one
+      if (a.stamps) a.stamps[XB_SYNC_STAMP_RELEASE] = global_ns();
+      __threadfence();
+      st_release_sys(a.release, a.epoch);
+    }
+  }
+}
+__device__ __forceinline__ void stamp_entry(const SyncArgs& a) {
+  if (!a.stamps || blockIdx.x != 0 || threadIdx.x != 0) return;
+  unsigned long long* s = a.stamps;
+  const unsigned long long e0 = s[XB_SYNC_STAMP_ENTRY], r0 = s[XB_SYNC_STAMP_RELEASE], x0 = s[XB_SYNC_STAMP_EXIT + ((a.epoch - 1) & 1)];
+  if (e0 && x0 >= e0) {                                   // fold the previous launch into the running sums
+    s[XB_SYNC_STAMP_COUNT] += 1;
+    s[XB_SYNC_STAMP_SUM_RELEASE] += (r0 >= e0 ? r0 : x0) - e0;
+    s[XB_SYNC_STAMP_SUM_TOTAL] += x0 - e0;
+  }
+  s[XB_SYNC_STAMP_ENTRY] = global_ns();
+  s[XB_SYNC_STAMP_RELEASE] = 0;
+}
+__device__ __forceinline__ void stamp_exit(const SyncArgs& a) {
+  if (a.stamps && threadIdx.x == 0) atomicMax(a.stamps + XB_SYNC_STAMP_EXIT + (a.epoch & 1), global_ns());
+}
+
 __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __restrict__ per_rank) {
   // the argument block is read thousands of times (pointer tables): keep a copy in shared memory
   __shared__ SyncArgs a;
@@ -201,6 +252,7 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
   const int tid = threadIdx.x, B = gridDim.x, G = a.G, me = a.rank;
   const long long n4 = a.n / 4;
   const int parity = a.epoch & 1;
+  stamp_entry(a);
 
   if (G == 1) {   // no exchange: one pass
     for (int c = blockIdx.x; c < a.nchunks; c += B)
@@ -211,6 +263,8 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
         local_part(a, i4, ok, acc);
         apply_total(a, i4, ok, acc);
       }
+    release_replicas(a);
+    stamp_exit(a);
     return;
   }
 
@@ -245,6 +299,8 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
       st_release_sys(a.ready1[tid] + (long long)me * a.nchunks + c, a.epoch);
     }
   }
+  // every replica chunk this block is responsible for now holds its corrected weights
+  if (!(a.copy_to_replicas || a.algo != ALGO_SMA)) release_replicas(a);
 
   // ---- phase 2 (two-shot): owners reduce and broadcast the totals -----------------------------------------
   if (a.two_shot) {
@@ -377,6 +433,9 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
     }
     __syncthreads();
   }
+  // algorithms that rewrite the replicas from the new central model release them only now
+  if (a.copy_to_replicas || a.algo != ALGO_SMA) release_replicas(a);
+  stamp_exit(a);
 }
 
 // replicas <- z (DEFAULT update model, and LR-drop copies when no averaging is due)
@@ -417,6 +476,8 @@ struct XbSyncDesc {
   int* status;
   double timeout_s;
   float* zpeer[MAXG];             // every GPU's central model as seen from this process, or all null
+  unsigned int* release;          // two words owned by the caller (zero-initialised once), or null: see SyncArgs::release
+  unsigned long long* stamps;     // XB_SYNC_STAMP_WORDS 64-bit words owned by the caller (zero-initialised once), or null
 };
 
 static void fill_args(SyncArgs& a, const XbSyncDesc& d) {
@@ -435,6 +496,7 @@ static void fill_args(SyncArgs& a, const XbSyncDesc& d) {
   for (int g = 0; g < MAXG; ++g) a.zpeer[g] = d.zpeer[g];
   a.status = d.status;
   a.timeout_ns = (unsigned long long)(d.timeout_s * 1e9);
+  a.release = d.release; a.stamps = d.stamps;
 }
 
 static int sync_grid(int nchunks, int max_blocks) {
@@ -487,6 +549,37 @@ XB_API int xb_fused_sync_emulated(const XbSyncDesc* descs, int G, void* args_dev
   XB_CUDA_CHECK(cudaLaunchCooperativeKernel((void*)fused_sync_kernel, grid, dim3(NT), kargs, 0, st));
   return (int)cudaGetLastError();
 }
+
+// Make `st` wait (a stream memory operation, no kernel) until the 32-bit word at `word` has reached `value`
+// (cyclic comparison).  Used to hold a learner's next task until its replica has been released by the kernel above.
+// The driver entry point is looked up at run time, so the library loads on machines without a driver.
+typedef CUresult (*StreamWaitValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+static StreamWaitValue32Fn stream_wait_fn() {
+  static StreamWaitValue32Fn fn = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (StreamWaitValue32Fn)p;
+    looked = true;
+  }
+  return fn;
+}
+XB_API int xb_stream_wait_value32(cudaStream_t st, const unsigned int* word, unsigned int value) {
+  StreamWaitValue32Fn fn = stream_wait_fn();
+  if (!fn) return -XB_BAD_ARG;
+  CUresult r = fn((CUstream)st, (CUdeviceptr)word, value, CU_STREAM_WAIT_VALUE_GEQ);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
+}
+// 1 when streams of the current device can wait on a memory word (CUDA 12 drivers: the second generation of stream
+// memory operations is part of the base feature set)
+XB_API int xb_stream_wait_value_supported() {
+  int drv = 0;
+  if (cudaDriverGetVersion(&drv) != cudaSuccess || drv < 12000) return 0;
+  return stream_wait_fn() != nullptr ? 1 : 0;
+}
+XB_API int xb_sync_stamp_words() { return XB_SYNC_STAMP_WORDS; }
 
 XB_API int xb_broadcast_model(const float* z, float* const* w_dev_array, int k, long long n, cudaStream_t st) {
   if (n % 4) return -XB_BAD_ARG;

@@ -393,7 +393,13 @@ XB_API void xb_learner_set_programs(XbLearner* l, XbProgram* train, XbProgram* t
 
 // Enqueue one task: copy the batch from (pinned) host memory, replay the program, record the completion event.
 // phase 0 = train, 1 = test.  Never blocks.
+// `tag` is the number xb_learner_wait_task finds the task by (the submitting scheduler's own task counter, which may
+// differ from the job-wide number in the parameter block).
+static int learner_submit_tagged(XbLearner* l, const void* h_examples, const void* h_labels, const XbTaskParams* params, int phase, unsigned long long tag);
 XB_API int xb_learner_submit(XbLearner* l, const void* h_examples, const void* h_labels, const XbTaskParams* params, int phase) {
+  return learner_submit_tagged(l, h_examples, h_labels, params, phase, params->task_id);
+}
+static int learner_submit_tagged(XbLearner* l, const void* h_examples, const void* h_labels, const XbTaskParams* params, int phase, unsigned long long tag) {
   XbProgram* p = phase == 0 ? l->train : l->test;
   if (!p) return -XB_BAD_ARG;
   *l->h_params = *params;
@@ -418,7 +424,7 @@ XB_API int xb_learner_submit(XbLearner* l, const void* h_examples, const void* h
   int e = xb_program_launch_marked(p, l->stream, l->bucket, XB_MAX_BUCKETS);
   if (timed) { if (!e) e = (int)cudaEventRecord(l->ring_t1[slot], l->stream); nvtxRangePop(); }
   if (e) return e;
-  l->ring_task[slot] = params->task_id; l->ring_phase[slot] = phase;
+  l->ring_task[slot] = tag & 0xffffffffull; l->ring_phase[slot] = phase;
   copy_result_kernel<<<1, 32, 0, l->stream>>>(l->d_result, l->d_result + 4 + 2 * slot);
   XB_CUDA_CHECK(cudaGetLastError());
   XB_CUDA_CHECK(cudaEventRecord(l->ring_done[slot], l->stream));
@@ -557,7 +563,9 @@ struct XbSyncDescMirror {
   float* w[16]; const float* prev[16]; float* z; float* zlast; float* gacc;
   float* inbox[8]; float* result[8]; unsigned int* flags[8]; int* status; double timeout_s;
   float* zpeer[8];
+  unsigned int* release; unsigned long long* stamps;
 };
+XB_API int xb_stream_wait_value32(cudaStream_t st, const unsigned int* word, unsigned int value);
 XB_API int xb_fused_sync(const XbSyncDescMirror* d, void* args_dev, void* args_pinned, int max_blocks, cudaStream_t st);
 XB_API int xb_broadcast_model(const float* z, float* const* w_dev_array, int k, long long n, cudaStream_t st);
 XB_API int xb_sync_args_size();
@@ -578,6 +586,12 @@ struct XbExec {
   float** w_table_dev = nullptr;
   cudaStream_t sync_stream = nullptr; cudaEvent_t sync_event = nullptr;
   unsigned int epoch = 0;
+  // Model averaging: the learners' next tasks wait for the kernel's release word (their replicas are corrected) instead of
+  // the end of the synchronisation; test tasks, which read the central model, wait for the whole of it.
+  int early_release = 0;
+  // Training task t of this process is task t * world + rank of the job: the learning-rate schedule and the random
+  // streams are indexed with the job-wide number, as the reference's single task counter over all GPUs is.
+  int rank = 0, world = 1;
   std::atomic<unsigned long long> bn_updates{0};
   // ring data set in pinned memory: [phase]
   const char* ex_base[2] = {nullptr, nullptr}; const char* lab_base[2] = {nullptr, nullptr};
@@ -655,11 +669,12 @@ XB_API int xb_exec_submit(void* ctx, int learner, const void* ex, const void* la
   XbLearner* l = e->learners[learner];
   XbTaskParams p; memset(&p, 0, sizeof(p));
   const bool training = phase == 0;
-  p.lr = training ? solver_lr(e->solver, task) : 0.f;
+  const unsigned long long job_task = training ? task * (unsigned long long)e->world + (unsigned long long)e->rank : task;
+  p.lr = training ? solver_lr(e->solver, job_task) : 0.f;
   p.momentum = e->solver.momentum; p.weight_decay = e->solver.weight_decay;
   p.bn_factor = 1.0f / (1.0f + (float)(training ? e->bn_updates.fetch_add(1) : e->bn_updates.load()));
   p.clip = e->solver.clip; p.alpha = e->solver.alpha;
-  p.task_id = (unsigned)task; p.seed_lo = (unsigned)(e->seed & 0xffffffffu); p.seed_hi = (unsigned)(e->seed >> 32);
+  p.task_id = (unsigned)job_task; p.seed_lo = (unsigned)(e->seed & 0xffffffffu); p.seed_hi = (unsigned)(e->seed >> 32);
   p.training = training ? 1 : 0; p.l1 = e->solver.l1; p.nesterov = e->solver.nesterov;
   if (ex && e->prefetch && learner < 64) {
     XbExec::Prefetch& pf = e->pf[phase][learner];
@@ -681,9 +696,12 @@ XB_API int xb_exec_submit(void* ctx, int learner, const void* ex, const void* la
     XB_CUDA_CHECK(cudaMemcpyAsync(e->d_ex[phase][learner], ex, (size_t)e->ex_bytes[phase], cudaMemcpyHostToDevice, l->stream));
   }
   if (lab) XB_CUDA_CHECK(cudaMemcpyAsync(e->d_lab[phase][learner], lab, (size_t)e->lab_bytes[phase], cudaMemcpyHostToDevice, l->stream));
-  return xb_learner_submit(l, nullptr, nullptr, &p, phase);
+  if (!training && e->early_release) XB_CUDA_CHECK(cudaStreamWaitEvent(l->stream, e->sync_event, 0));   // reads the central model
+  return learner_submit_tagged(l, nullptr, nullptr, &p, phase, task);
 }
 XB_API void xb_exec_set_prefetch(XbExec* e, int on) { e->prefetch = on ? 1 : 0; }
+XB_API void xb_exec_set_early_release(XbExec* e, int on) { e->early_release = on ? 1 : 0; }
+XB_API void xb_exec_set_rank(XbExec* e, int rank, int world) { e->world = world < 1 ? 1 : world; e->rank = rank; }
 XB_API int xb_exec_wait(void* ctx, int learner, float* loss, float* acc) {
   XbExec* e = (XbExec*)ctx;
   if (learner < 0 || learner >= (int)e->learners.size()) return -XB_BAD_ARG;
@@ -741,8 +759,13 @@ XB_API int xb_exec_synchronise(void* ctx, unsigned long long clock, const unsign
     if (r) return r;
   }
   XB_CUDA_CHECK(cudaEventRecord(e->sync_event, e->sync_stream));
-  for (int i = 0; i < n && i < (int)e->learners.size(); ++i)
-    if (mask[i]) XB_CUDA_CHECK(cudaStreamWaitEvent(e->learners[i]->stream, e->sync_event, 0));
+  // averaging without a replica overwrite, several GPUs: a replica is final once the kernel's phase 1 is through
+  const bool early = e->early_release && !bucketed && e->update_mode == 0 && d.algo == 0 && !d.copy_to_replicas && d.G > 1 && d.release;
+  for (int i = 0; i < n && i < (int)e->learners.size(); ++i) {
+    if (!mask[i]) continue;
+    if (early) { int r = xb_stream_wait_value32(e->learners[i]->stream, d.release, d.epoch); if (r) return r; }
+    else XB_CUDA_CHECK(cudaStreamWaitEvent(e->learners[i]->stream, e->sync_event, 0));
+  }
   return 0;
 }
 XB_API unsigned int xb_exec_epoch(XbExec* e) { return e->epoch; }

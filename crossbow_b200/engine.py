@@ -127,8 +127,11 @@ class GpuEngine:
                  rank: int = 0, world: int = 1, device_index: int = 0, use_tc: bool = True, use_graphs: bool = True,
                  seed: int = 0, fused_sync: bool = True, two_shot: Optional[bool] = None, sync_timeout_s: float = 5.0,
                  splits: int = 1, reuse_memory: bool = False, gradient_buckets: int = 0,
-                 debug_canaries: bool = False):
-        """`gradient_buckets`: synchronous SGD only - number of gradient buckets whose all-reduce + update overlaps the
+                 debug_canaries: bool = False, overlap_sync: bool = True):
+        """`overlap_sync`: model averaging on several GPUs - the learners' next tasks start as soon as their replicas have
+        been corrected (the kernel's release word), under the cross-GPU exchange and the central update; off = they wait
+        for the whole synchronisation.
+        `gradient_buckets`: synchronous SGD only - number of gradient buckets whose all-reduce + update overlaps the
         backward pass (0 = 4 for models of at least 32 MB, otherwise 1; 1 = one synchronisation after the task)."""
         from .ops import lib as L
         from .parallel.sync import FusedSynchroniser, ReferenceSynchroniser
@@ -145,6 +148,8 @@ class GpuEngine:
         nb = int(gradient_buckets) if gradient_buckets else (4 if model.device_elements * 4 >= (32 << 20) else 1)
         self.gradient_buckets = min(8, nb) if (fused_sync and update_model == UpdateModel.WORKER) else 1
         self.bucket_syncs = []
+        # `wpc` counts THIS rank's tasks per clock; a clock of the job is wpc * world tasks, which is what synchronous SGD
+        # divides the summed gradient by (the reference's single process counts all GPUs' tasks, synch/synchronoussgd.c:60-75)
         self.rank, self.world, self.wpc, self.seed = rank, world, wpc, seed
         self.use_tc, self.use_graphs = use_tc, use_graphs
         self.tc_status = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -166,6 +171,7 @@ class GpuEngine:
             self.bucket_syncs = self.synchroniser.make_buckets(ranges)
         self.sync_stream = self.lib.xb_stream_create(-1)
         self.sync_event = self.lib.xb_event_create(0)
+        self.overlap_sync = bool(overlap_sync) and fused_sync and world > 1 and bool(self.lib.xb_stream_wait_value_supported())
         self.poly_count = 0
         self.bn_updates = 0
         self._exec = None
@@ -212,13 +218,23 @@ class GpuEngine:
         self.learners.pop().destroy()
 
     # ---- tasks ----
+    def global_task(self, task: int) -> int:
+        """Job-wide number of this rank's task `task`: rank r of G runs the job's tasks r, G + r, 2 G + r, ...  The
+        learning-rate schedule, the random streams (dropout, crops) and the data set are indexed with it, as the
+        reference's single task counter over all GPUs is (solverconfiguration.c:116-161)."""
+        return task * self.world + self.rank
+
     def params(self, task: int, training: bool):
-        return task_params(self.solver, task, self.seed, training, self.bn_updates)
+        return task_params(self.solver, self.global_task(task) if training else task, self.seed, training, self.bn_updates)
 
     def submit(self, learner: int, examples, labels, task: int, phase=Phase.TRAIN):
         p = self.params(task, phase == Phase.TRAIN)
         if phase == Phase.TRAIN:
             self.bn_updates += 1
+        elif self.overlap_sync:
+            # a test task reads the central model: it waits for the whole synchronisation, not only for the release
+            from .ops import lib as L
+            L.check(self.lib.xb_learner_wait_event(self.learners[learner].handle, self.sync_event), "test task waits for sync")
         self.learners[learner].submit(examples, labels, p, phase)
 
     def wait(self, learner: int):
@@ -236,6 +252,7 @@ class GpuEngine:
         ls = [self.learners[i] for i in (learners if learners is not None else range(len(self.learners)))]
         um, sv = self.update_model, self.solver
         bucketed = bool(self.bucket_syncs) and um == UpdateModel.WORKER
+        early = False
         if not bucketed:
             for l in ls:
                 L.check(lib.xb_stream_wait_learner(ss, l.handle), "sync waits for learner")
@@ -244,9 +261,11 @@ class GpuEngine:
         if um in (UpdateModel.SMA, UpdateModel.SYNCHRONOUSEAMSGD):
             self.synchroniser.synchronise(ss, S.ALGO_SMA, ws, prevs, sh.z, sh.zlast, None, alpha=sv.alpha,
                                           mu=sma_base_momentum(sv), copy=copy, use_prev=True)
+            early = self.overlap_sync and self.synchroniser.releases_early(S.ALGO_SMA, copy)
         elif um == UpdateModel.EAMSGD:
             self.synchroniser.synchronise(ss, S.ALGO_SMA, ws, prevs, sh.z, sh.zlast, None, alpha=sv.alpha,
                                           mu=sv.base_model_momentum, copy=copy, use_prev=False)
+            early = self.overlap_sync and self.synchroniser.releases_early(S.ALGO_SMA, copy)
         elif bucketed:
             # bucket b starts as soon as every learner has accumulated that bucket's gradients (the learners are then still
             # in the backward pass of the earlier layers)
@@ -257,11 +276,11 @@ class GpuEngine:
                 sl = slice(c.offset, c.offset + c.n)
                 c.epoch = self.synchroniser.epoch - 1
                 c.synchronise(ss, S.ALGO_SSGD, [w[sl] for w in ws], None, sh.z[sl], sh.zlast[sl], sh.gacc[sl], mu=sv.momentum,
-                              scale=1.0 / self.wpc)
+                              scale=1.0 / (self.wpc * self.world))
             for l in ls:
                 L.check(lib.xb_stream_wait_learner(ss, l.handle), "sync waits for learner")
         elif um == UpdateModel.WORKER:
-            self.synchroniser.synchronise(ss, S.ALGO_SSGD, ws, None, sh.z, sh.zlast, sh.gacc, mu=sv.momentum, scale=1.0 / self.wpc)
+            self.synchroniser.synchronise(ss, S.ALGO_SSGD, ws, None, sh.z, sh.zlast, sh.gacc, mu=sv.momentum, scale=1.0 / (self.wpc * self.world))
         elif um == UpdateModel.POLYAK_RUPPERT:
             self.synchroniser.synchronise(ss, S.ALGO_POLYAK, ws, None, sh.z, sh.zlast, None, alpha=0.0,
                                           scale=1.0 / (len(ls) * self.world), blend=1.0 / (self.poly_count + 1.0))
@@ -274,7 +293,10 @@ class GpuEngine:
             raise NotImplementedError(f"error: {um} is not supported (a stub in the reference as well)")
         L.check(lib.xb_event_record(self.sync_event, ss), "record sync event")
         for l in ls:
-            L.check(lib.xb_learner_wait_event(l.handle, self.sync_event), "learner waits for sync")
+            if early:        # the replica is final once phase 1 of the kernel is through: the next task runs under the exchange
+                self.synchroniser.wait_release(l.stream)
+            else:
+                L.check(lib.xb_learner_wait_event(l.handle, self.sync_event), "learner waits for sync")
 
     # ---- native scheduling: hand the learners to the C++ runtime ----
     def native_executor(self, train_ds=None, test_ds=None):
@@ -302,6 +324,7 @@ class GpuEngine:
         if self._exec:
             lib.xb_exec_destroy(self._exec)
         self._exec = lib.xb_exec_create(C.byref(st), self.seed, self.sync_stream, getattr(self.synchroniser, "max_blocks", 0))
+        lib.xb_exec_set_rank(self._exec, self.rank, self.world)
         for l in self.learners:
             self._exec_add(l)
         um, sh = self.update_model, self.shared
@@ -313,7 +336,7 @@ class GpuEngine:
         elif um == UpdateModel.EAMSGD:
             d = sy.descriptor(S.ALGO_SMA, ws, prevs, sh.z, sh.zlast, None, sv.alpha, sv.base_model_momentum, 1.0, 0.0, False, False)
         elif um == UpdateModel.WORKER:
-            d = sy.descriptor(S.ALGO_SSGD, ws, None, sh.z, sh.zlast, sh.gacc, 0.0, sv.momentum, 1.0 / self.wpc, 0.0, False, True)
+            d = sy.descriptor(S.ALGO_SSGD, ws, None, sh.z, sh.zlast, sh.gacc, 0.0, sv.momentum, 1.0 / (self.wpc * self.world), 0.0, False, True)
         elif um == UpdateModel.POLYAK_RUPPERT:
             d = sy.descriptor(S.ALGO_POLYAK, ws, None, sh.z, sh.zlast, None, 0.0, 0.0, 1.0, 1.0, False, True)
         elif um == UpdateModel.DEFAULT:
@@ -321,11 +344,12 @@ class GpuEngine:
         else:
             raise NotImplementedError(f"error: {um} is not supported (a stub in the reference as well)")
         lib.xb_exec_set_sync(self._exec, C.byref(d), int(um == UpdateModel.DEFAULT))
+        lib.xb_exec_set_early_release(self._exec, int(self.overlap_sync))
         if um == UpdateModel.WORKER:
             for c in self.bucket_syncs:
                 sl = slice(c.offset, c.offset + c.n)
                 db = c.descriptor(S.ALGO_SSGD, [w[sl] for w in ws], None, sh.z[sl], sh.zlast[sl], sh.gacc[sl], 0.0, sv.momentum,
-                                  1.0 / self.wpc, 0.0, False, True)
+                                  1.0 / (self.wpc * self.world), 0.0, False, True)
                 L.check(min(0, lib.xb_exec_add_bucket(self._exec, C.byref(db), c.offset)), "gradient bucket")
         lib.xb_exec_set_epoch(self._exec, sy.epoch)
         for phase, ds in ((0, train_ds), (1, test_ds)):
@@ -412,8 +436,11 @@ class CpuEngine:
     """Same protocol on the CPU oracle, with k replicas x G virtual devices in one process."""
 
     def __init__(self, train_graph, test_graph, model: Model, init_canonical, batch, input_chw, solver: SolverConf,
-                 update_model: UpdateModel, replicas=1, wpc=1, devices=1, seed=0, splits=1):
+                 update_model: UpdateModel, replicas=1, wpc=1, devices=1, seed=0, splits=1, rank=0, world=1):
+        """`rank` / `world`: when given (one process per device group under torch.distributed), training task t of this
+        process is task t * world + rank of the job for the learning-rate schedule and the random streams."""
         self.model, self.solver, self.update_model, self.wpc, self.seed = model, solver, update_model, wpc, seed
+        self.rank, self.world = rank, max(1, world)
         self.splits = max(1, int(splits))
         w = torch.from_numpy(np.asarray(init_canonical, dtype=np.float32))
         self.devs = [DeviceState(w) for _ in range(devices)]
@@ -435,6 +462,7 @@ class CpuEngine:
         dev, rep = self._slot(learner)
         x, y = torch.as_tensor(examples, dtype=torch.float32), torch.as_tensor(labels)
         if phase == Phase.TRAIN:
+            task = task * self.world + self.rank
             # `--splits`: the graph (optimiser included) runs once per sub-batch; the task reports the mean loss / accuracy
             sub = x.shape[0] // self.splits
             parts = []

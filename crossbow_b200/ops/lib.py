@@ -41,7 +41,8 @@ class XbSyncDesc(C.Structure):
                 ("alpha", c_float), ("mu", c_float), ("scale", c_float), ("blend", c_float),
                 ("w", c_void_p * MAXK), ("prev", c_void_p * MAXK), ("z", c_void_p), ("zlast", c_void_p), ("gacc", c_void_p),
                 ("inbox", c_void_p * MAXG), ("result", c_void_p * MAXG), ("flags", c_void_p * MAXG),
-                ("status", c_void_p), ("timeout_s", C.c_double), ("zpeer", c_void_p * MAXG)]
+                ("status", c_void_p), ("timeout_s", C.c_double), ("zpeer", c_void_p * MAXG),
+                ("release", c_void_p), ("stamps", c_void_p)]
 
 
 class XbBnFuse(C.Structure):
@@ -137,6 +138,11 @@ def load() -> C.CDLL:
     _sig(lib, "xb_fused_sync", I, C.POINTER(XbSyncDesc), P, P, I, P)
     _sig(lib, "xb_fused_sync_emulated", I, C.POINTER(XbSyncDesc), I, P, I, P)
     _sig(lib, "xb_broadcast_model", I, P, P, I, L, P)
+    _sig(lib, "xb_stream_wait_value32", I, P, P, c_uint)
+    _sig(lib, "xb_stream_wait_value_supported", I)
+    _sig(lib, "xb_sync_stamp_words", I)
+    _sig(lib, "xb_exec_set_early_release", None, P, I)
+    _sig(lib, "xb_exec_set_rank", None, P, I, I)
     # program / learner
     _sig(lib, "xb_op_size", I)
     _sig(lib, "xb_program_create", P, C.POINTER(XbOp), I, I, P)

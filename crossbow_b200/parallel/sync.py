@@ -56,6 +56,9 @@ class FusedSynchroniser:
         self.parent, self.offset, self.group = parent, offset, group
         self.children: List["FusedSynchroniser"] = []
         self.inbox = self.result = self.flags = self.zbuf = None
+        # release word + block counter, and the kernel's time line (see sync.cu): plain device memory of this rank
+        self.release = torch.zeros(2, dtype=torch.int32, device="cuda")
+        self.stamps = torch.zeros(lib.xb_sync_stamp_words(), dtype=torch.int64, device="cuda")
         if world > 1:
             self.inbox = PeerBuffer(4 * lib.xb_sync_inbox_floats(n, world, int(self.two_shot)), rank, world, group)
             self.result = PeerBuffer(4 * lib.xb_sync_result_floats(n) if self.two_shot else 256, rank, world, group)
@@ -120,7 +123,31 @@ class FusedSynchroniser:
                     d.zpeer[g] = self.zbuf.ptrs[g]
         d.status = self.status.data_ptr()
         d.timeout_s = self.timeout_s
+        d.release, d.stamps = self.release.data_ptr(), self.stamps.data_ptr()
         return d
+
+    def releases_early(self, algo: int, copy: bool) -> bool:
+        """True when the kernel publishes the release word BEFORE the exchange: model averaging that does not overwrite
+        the replicas, on more than one GPU (a replica is then final once it has been corrected against the old central
+        model; everything after that only touches the central model)."""
+        return algo == ALGO_SMA and not copy and self.world > 1
+
+    def wait_release(self, stream: int):
+        """Make `stream` wait until the replicas of the last enqueued synchronisation have been released."""
+        L.check(self.lib.xb_stream_wait_value32(stream, self.release.data_ptr(), self.epoch & 0xFFFFFFFF), "wait for the release word")
+
+    def timeline(self, reset: bool = False) -> dict:
+        """Device-side time line of this rank's synchronisations (call after the stream has been synchronised): number of
+        launches, mean microseconds from kernel entry to the release of the replicas and from entry to the exit of the
+        last block."""
+        st = [int(v) for v in self.stamps.cpu().tolist()]
+        entry, release, count, sum_rel, sum_tot = st[0], st[1], st[4], st[5], st[6]
+        exit_ = st[2 + (self.epoch & 1)]
+        if entry and exit_ >= entry:                      # the most recent launch has not been folded into the sums yet
+            count, sum_rel, sum_tot = count + 1, sum_rel + ((release if release >= entry else exit_) - entry), sum_tot + (exit_ - entry)
+        if reset:
+            self.stamps.zero_()
+        return {"launches": count, "release_us": sum_rel / max(1, count) / 1e3, "total_us": sum_tot / max(1, count) / 1e3}
 
     def synchronise(self, stream: int, algo: int, replicas_w: List[torch.Tensor], replicas_prev: Optional[List[torch.Tensor]],
                     z, zlast, gacc=None, alpha=0.0, mu=0.0, scale=1.0, blend=0.0, copy=False, use_prev=True):

@@ -76,6 +76,30 @@ def main():
     assert float(eng.shared.z.abs().sum()) > 0 and torch.isfinite(eng.shared.z).all()
     eng.destroy()
     dist.barrier()
+    # model averaging overlapped with the next tasks (the learners follow the kernel's release word) against the serialised
+    # order (they wait for the whole synchronisation): same arithmetic, so the weights must be bit-identical
+    import copy as _copy
+    spec, m, solver = build_model("resnet8", 8)
+    xs, ys = make_batches(spec, 8, 12, seed=200 + rank)
+    finals = []
+    for overlap in (False, True):
+        eng = GpuEngine(spec.train, None, m, m.initial_values(7), 8, spec.input_shape, _copy.deepcopy(solver), UpdateModel.SMA, replicas=2,
+                        wpc=2, rank=rank, world=world, device_index=local, use_tc=True, overlap_sync=overlap)
+        assert eng.overlap_sync == overlap
+        for t in range(0, 12, 2):                     # both learners in flight, nothing waits on the host between clocks
+            eng.submit(0, xs[t].pin_memory(), ys[t].pin_memory(), t, Phase.TRAIN)
+            eng.submit(1, xs[t + 1].pin_memory(), ys[t + 1].pin_memory(), t + 1, Phase.TRAIN)
+            eng.synchronise()
+        eng.wait(0), eng.wait(1)
+        eng.finish()
+        tl = eng.synchroniser.timeline()
+        assert tl["launches"] == 6 and 0 < tl["release_us"] <= tl["total_us"], tl
+        finals.append([eng.shared.z.clone()] + [l.rep.w.clone() for l in eng.learners])
+        eng.destroy()
+        dist.barrier()
+    # (batch-norm sums are accumulated with atomics, so two runs agree to rounding, not to the bit)
+    for a, b in zip(*finals):
+        assert torch.isfinite(a).all() and float((a - b).abs().max()) <= 2e-3 * float(a.abs().max()) + 1e-9, float((a - b).abs().max())
     # synchronous SGD with gradient buckets (owner-apply exchange per bucket, overlapping the backward pass) against one
     # synchronisation per clock; both learners of a rank run concurrently
     import copy
@@ -84,7 +108,7 @@ def main():
     xs, ys = make_batches(spec, 8, 8, seed=100 + rank)
     for nb in (1, 3):
         eng = GpuEngine(spec.train, None, m, m.initial_values(7), 8, spec.input_shape, copy.deepcopy(solver), UpdateModel.WORKER, replicas=2,
-                        wpc=2 * world, rank=rank, world=world, device_index=local, use_tc=False, two_shot=True, gradient_buckets=nb)
+                        wpc=2, rank=rank, world=world, device_index=local, use_tc=False, two_shot=True, gradient_buckets=nb)
         assert (len(eng.bucket_syncs) > 1) == (nb > 1)
         for t in range(0, 8, 2):
             eng.submit(0, xs[t].pin_memory(), ys[t].pin_memory(), t, Phase.TRAIN)

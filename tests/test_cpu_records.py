@@ -1,4 +1,5 @@
-"""Record files, the built-in baseline JPEG decoder (against PIL / libjpeg) and the double-buffered decoding data set."""
+"""Record files, the built-in JPEG decoder (sequential, progressive, CMYK; against PIL / libjpeg) and the double-buffered
+decoding data set."""
 import io
 
 import numpy as np
@@ -30,15 +31,110 @@ def test_decoder_matches_libjpeg(w, h, sub):
     assert np.abs(out - ref).max() <= 2 and np.abs(out - ref).mean() < 0.1
 
 
-def test_decoder_greyscale_restart_and_progressive():
+def test_decoder_greyscale_and_garbage():
     img = _image(50, 50)[..., 0]
     buf = io.BytesIO()
     PIL.fromarray(img).save(buf, format="JPEG", quality=90)
     assert np.abs(decode_jpeg(buf.getvalue())[..., 0].astype(int) - np.array(PIL.open(io.BytesIO(buf.getvalue()))).astype(int)).max() <= 1
     with pytest.raises(ValueError):
-        decode_jpeg(_jpeg(_image(40, 40), progressive=True))
-    with pytest.raises(ValueError):
         decode_jpeg(b"not a jpeg")
+
+
+@pytest.mark.parametrize("w,h,sub,q", [(40, 40, 2, 90), (67, 45, 2, 75), (120, 90, 1, 95), (64, 48, 0, 50), (33, 70, 2, 85)])
+def test_progressive_matches_libjpeg(w, h, sub, q):
+    """Progressive files (spectral selection + successive approximation, separate DC / AC scans per component)."""
+    data = _jpeg(_image(w, h, seed=w), quality=q, subsampling=sub, progressive=True)
+    assert b"\xff\xc2" in data                       # really a progressive frame
+    ref = np.array(PIL.open(io.BytesIO(data)).convert("RGB")).astype(int)
+    out = decode_jpeg(data).astype(int)
+    assert out.shape == ref.shape
+    assert np.abs(out - ref).max() <= 2 and np.abs(out - ref).mean() < 0.1
+
+
+def test_progressive_greyscale_and_natural_content():
+    g = np.random.default_rng(5)
+    yy, xx = np.mgrid[0:96, 0:80]
+    img = (127 + 80 * np.sin(xx / 7.0) * np.cos(yy / 11.0) + g.normal(0, 12, (96, 80))).clip(0, 255).astype(np.uint8)
+    for mode in ("L", "RGB"):
+        im = PIL.fromarray(img) if mode == "L" else PIL.fromarray(np.stack([img, img[::-1], img[:, ::-1]], -1))
+        buf = io.BytesIO()
+        im.save(buf, format="JPEG", quality=88, progressive=True)
+        ref = np.array(PIL.open(io.BytesIO(buf.getvalue())).convert("RGB")).astype(int)
+        out = decode_jpeg(buf.getvalue()).astype(int)
+        assert np.abs(out - ref).max() <= 3 and np.abs(out - ref).mean() < 0.15
+
+
+def test_cmyk_files_are_converted_like_the_reference():
+    """Four-component files: Adobe CMYK / YCCK (inks stored inverted), r = k * c / 255 as image/image.c:119-139 does."""
+    rgb = _image(48, 40, seed=9)
+    cmyk = PIL.fromarray(rgb).convert("CMYK")
+    for progressive in (False, True):
+        buf = io.BytesIO()
+        cmyk.save(buf, format="JPEG", quality=95, subsampling=0, progressive=progressive)
+        dec = PIL.open(io.BytesIO(buf.getvalue()))
+        assert dec.mode == "CMYK"
+        raw = np.array(dec).astype(int)               # PIL hands out the inks non-inverted
+        inv = 255 - raw                               # ... libjpeg itself hands out Adobe files inverted
+        ref = (inv[..., 3:4] * inv[..., :3]) // 255
+        out = decode_jpeg(buf.getvalue()).astype(int)
+        assert out.shape == ref.shape and np.abs(out - ref).max() <= 3
+
+
+def test_restart_intervals():
+    img = _image(96, 64, seed=4)
+    buf = io.BytesIO()
+    PIL.fromarray(img).save(buf, format="JPEG", quality=90, subsampling=2, restart_marker_blocks=3)
+    data = buf.getvalue()
+    if b"\xff\xdd" not in data:
+        pytest.skip("this PIL build does not write restart intervals")
+    ref = np.array(PIL.open(io.BytesIO(data)).convert("RGB")).astype(int)
+    assert np.abs(decode_jpeg(data).astype(int) - ref).max() <= 2
+
+
+def test_malformed_files_fail_cleanly():
+    """Untrusted input: truncations and corrupted table selectors / lengths end in an error or a partial image, never in
+    an out-of-range access (the self-test binary runs the same cases under AddressSanitizer)."""
+    good = _jpeg(_image(64, 48), subsampling=2)
+    prog = _jpeg(_image(64, 48), subsampling=2, progressive=True)
+    for data in (good, prog):
+        for cut in (3, 20, 100, len(data) // 2, len(data) - 2):
+            try:
+                out = decode_jpeg(data[:cut])
+                assert out.shape == (48, 64, 3)       # a truncated scan keeps what was decoded
+            except ValueError:
+                pass
+        sos = data.index(b"\xff\xda")
+        for off, val in ((5, 0x7F), (6, 0xFF), (4, 9), (2, 0), (3, 1)):   # component selector, table ids, count, length
+            bad = bytearray(data)
+            bad[sos + off] = val
+            try:
+                decode_jpeg(bytes(bad))
+            except ValueError:
+                pass
+        dht = data.index(b"\xff\xc4")
+        for off in range(4, 24, 3):
+            bad = bytearray(data)
+            bad[dht + off] = 0xFF
+            try:
+                decode_jpeg(bytes(bad))
+            except ValueError:
+                pass
+        dqt = data.index(b"\xff\xdb")
+        bad = bytearray(data)
+        bad[dqt + 4] = 0x10                           # claims 16-bit entries in a segment sized for 8-bit ones
+        try:
+            decode_jpeg(bytes(bad))
+        except ValueError:
+            pass
+    g = np.random.default_rng(0)
+    for _ in range(200):                              # random byte flips anywhere behind the SOI
+        bad = bytearray(good if g.random() < 0.5 else prog)
+        for _ in range(int(g.integers(1, 6))):
+            bad[int(g.integers(2, len(bad)))] = int(g.integers(0, 256))
+        try:
+            decode_jpeg(bytes(bad))
+        except ValueError:
+            pass
 
 
 def test_test_pipeline_is_centre_crop_resize():

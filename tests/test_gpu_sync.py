@@ -146,6 +146,73 @@ def test_polyak_matches_oracle():
             assert torch.allclose(Z[g].cpu(), devs[g].z, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("G,k,two_shot", [(2, 2, False), (4, 2, True)])
+def test_release_word_orders_the_next_task(G, k, two_shot):
+    """Model averaging releases a GPU's replicas before the exchange: a second stream that waits for the release word
+    and then rewrites the replicas (what a replica's next task does) must see the corrected weights, and the central
+    model must come out as if the two had run one after the other.  G ranks emulated in one cooperative launch."""
+    from crossbow_b200.ops import lib as L
+    lib = L.load()
+    assert lib.xb_stream_wait_value_supported() == 1
+    n = (1 << 20) + 4096 * 3
+    devs = _state(G, k, n, seed=11)
+    dev = torch.device("cuda")
+    W = [[r.w.to(dev) for r in d.replicas] for d in devs]
+    Pv = [[r.prev.to(dev) for r in d.replicas] for d in devs]
+    Z = [d.z.to(dev) for d in devs]
+    ZL = [d.z_last.to(dev) for d in devs]
+    inbox = [torch.zeros(lib.xb_sync_inbox_floats(n, G, int(two_shot)), device=dev) for _ in range(G)]
+    result = [torch.zeros(lib.xb_sync_result_floats(n), device=dev) for _ in range(G)]
+    flags = [torch.zeros(lib.xb_sync_flag_words(n, G), dtype=torch.int32, device=dev) for _ in range(G)]
+    release = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(G)]
+    stamps = [torch.zeros(lib.xb_sync_stamp_words(), dtype=torch.int64, device=dev) for _ in range(G)]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    args = torch.zeros(lib.xb_sync_args_size() * G, dtype=torch.uint8, device=dev)
+    descs = (L.XbSyncDesc * G)()
+    sync_stream, task_stream = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    epochs = 3
+    for e in range(1, epochs + 1):
+        for g in range(G):
+            d = descs[g]
+            d.rank, d.G, d.k, d.algo, d.n, d.epoch = g, G, k, 0, n, e
+            d.two_shot, d.copy_to_replicas, d.use_prev = int(two_shot), 0, 1
+            d.alpha, d.mu, d.scale, d.blend = 0.1, 0.9, 1.0, 0.0
+            for i in range(k):
+                d.w[i], d.prev[i] = W[g][i].data_ptr(), Pv[g][i].data_ptr()
+            d.z, d.zlast, d.gacc = Z[g].data_ptr(), ZL[g].data_ptr(), 0
+            for j in range(G):
+                d.inbox[j], d.result[j], d.flags[j] = inbox[j].data_ptr(), result[j].data_ptr(), flags[j].data_ptr()
+            d.status, d.timeout_s = status.data_ptr(), 2.0
+            d.release, d.stamps = release[g].data_ptr(), stamps[g].data_ptr()
+        # the synchronisation follows the "tasks" of the previous round (an event), the tasks follow the release word only
+        sync_stream.wait_stream(task_stream)
+        L.check(lib.xb_fused_sync_emulated(descs, G, args.data_ptr(), 8, sync_stream.cuda_stream), "emulated sync")
+        with torch.cuda.stream(task_stream):
+            for g in range(G):
+                L.check(lib.xb_stream_wait_value32(task_stream.cuda_stream, release[g].data_ptr(), e), "wait for release")
+                for i in range(k):
+                    Pv[g][i].copy_(W[g][i])          # the next task's optimiser: snapshot, then a step
+                    W[g][i].mul_(1.5)
+        # oracle: synchronise, then the same "task"
+        synchronise_sma(devs, 0.1, 0.9)
+        for dv in devs:
+            for r in dv.replicas:
+                r.prev = r.w.clone()
+                r.w = r.w * 1.5
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    for g in range(G):
+        assert torch.allclose(Z[g].cpu(), devs[g].z, rtol=1e-5, atol=1e-6)
+        assert torch.equal(Z[g], Z[0])
+        for i in range(k):
+            assert torch.allclose(W[g][i].cpu(), devs[g].replicas[i].w, rtol=1e-5, atol=1e-6)
+        st = stamps[g].cpu().tolist()
+        assert int(release[g][0].item()) == epochs and int(release[g][1].item()) == 0
+        assert st[4] == epochs - 1 and 0 < st[5] <= st[6]             # launches folded so far; entry->release <= entry->exit
+        assert st[0] < st[1] <= st[2 + (epochs & 1)]                  # last launch: entry < release <= exit
+
+
 def test_wait_gives_up_with_status():
     """A flag that nothing sets: the kernel must return with a status, not hang."""
     from crossbow_b200.ops import lib as L
