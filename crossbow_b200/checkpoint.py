@@ -5,6 +5,8 @@
 little-endian fp32, no header, variables in operator-id order with weights before bias
 (clib-multigpu/executioncontext.c:2340-2367, modelmanager.c:267-343, model.c:396-405, cudnnbatchnormparams.c:102-143).
 Files always hold the canonical (reference) element order, whatever the device layout is.
+Replica files carry the reference's job-wide replica id: replicas are dealt round-robin over the devices
+(modelmanager.c:51-62), so the j-th replica of device d on G devices is replica j * G + d.
 """
 from __future__ import annotations
 
@@ -26,8 +28,12 @@ def _read(path, n):
     return a
 
 
+def _replica_id(j: int, dev: int, devices: int) -> int:
+    return j * max(1, devices) + dev
+
+
 def _bn_ops(ctx):
-    g = ctx.dataflows[0].getSubGraph()
+    g = ctx.dataflows[0].executable()
     return [n.op for n in g.order if n.op.kernel.kind == "batchnorm"]
 
 
@@ -44,8 +50,9 @@ def save_checkpoint(ctx, directory: str) -> str:
         m = ctx.model
         _write(os.path.join(d, f"gpu-{dev:02d}-theModel-last.dat"), m.to_canonical(e.central_momentum().cpu().numpy()))
         for i, l in enumerate(e.learners):
-            _write(os.path.join(d, f"gpu-{dev:02d}-replica-{i:03d}-data.dat"), e.replica_model(i))
-            _write(os.path.join(d, f"gpu-{dev:02d}-replica-{i:03d}-last.dat"), m.to_canonical(l.rep.last.cpu().numpy()))
+            rid = _replica_id(i, dev, ctx.world)
+            _write(os.path.join(d, f"gpu-{dev:02d}-replica-{rid:03d}-data.dat"), e.replica_model(i))
+            _write(os.path.join(d, f"gpu-{dev:02d}-replica-{rid:03d}-last.dat"), m.to_canonical(l.rep.last.cpu().numpy()))
         for op in _bn_ops(ctx):
             if op.uid in e.shared.run_mean:
                 _write(os.path.join(d, f"gpu-{dev:02d}-bn-avg-{op.id:03d}.dat"), e.shared.run_mean[op.uid].cpu().numpy())
@@ -54,8 +61,9 @@ def save_checkpoint(ctx, directory: str) -> str:
         for di, dv in enumerate(e.devs):
             _write(os.path.join(d, f"gpu-{di:02d}-theModel-last.dat"), dv.z_last.numpy())
             for i, r in enumerate(dv.replicas):
-                _write(os.path.join(d, f"gpu-{di:02d}-replica-{i:03d}-data.dat"), r.w.numpy())
-                _write(os.path.join(d, f"gpu-{di:02d}-replica-{i:03d}-last.dat"), r.last.numpy())
+                rid = _replica_id(i, di, len(e.devs))
+                _write(os.path.join(d, f"gpu-{di:02d}-replica-{rid:03d}-data.dat"), r.w.numpy())
+                _write(os.path.join(d, f"gpu-{di:02d}-replica-{rid:03d}-last.dat"), r.last.numpy())
             for op in _bn_ops(ctx):
                 st = dv.op_state.get(("bn", op.uid))
                 if st:
@@ -85,11 +93,15 @@ def load_checkpoint(ctx, directory: str):
         if os.path.exists(p):
             e.shared.zlast.copy_(torch.from_numpy(m.to_device(_read(p, n))))
         for i, l in enumerate(e.learners):
-            p = os.path.join(d, f"gpu-{dev:02d}-replica-{i:03d}-data.dat")
+            rid = _replica_id(i, dev, ctx.world)
+            p = os.path.join(d, f"gpu-{dev:02d}-replica-{rid:03d}-data.dat")
+            if not os.path.exists(p) and not getattr(ctx, "quiet", False):
+                # (more replicas than the checkpoint was written with: the extra ones start from the central model)
+                print(f"warning: {p} not found; replica {rid} starts from the central model", flush=True)
             src = _read(p, n) if os.path.exists(p) else e.central_model()
             e.load_replica(i, src)
             l.rep.prev.copy_(l.rep.w)
-            p = os.path.join(d, f"gpu-{dev:02d}-replica-{i:03d}-last.dat")
+            p = os.path.join(d, f"gpu-{dev:02d}-replica-{rid:03d}-last.dat")
             if os.path.exists(p):
                 l.rep.last.copy_(torch.from_numpy(m.to_device(_read(p, n))))
         for op in _bn_ops(ctx):
@@ -106,10 +118,11 @@ def load_checkpoint(ctx, directory: str):
             if os.path.exists(p):
                 dv.z_last = torch.from_numpy(_read(p, n)).clone()
             for i, r in enumerate(dv.replicas):
-                p = os.path.join(d, f"gpu-{di:02d}-replica-{i:03d}-data.dat")
+                rid = _replica_id(i, di, len(e.devs))
+                p = os.path.join(d, f"gpu-{di:02d}-replica-{rid:03d}-data.dat")
                 r.w = torch.from_numpy(_read(p, n)).clone() if os.path.exists(p) else dv.z.clone()
                 r.prev = r.w.clone()
-                p = os.path.join(d, f"gpu-{di:02d}-replica-{i:03d}-last.dat")
+                p = os.path.join(d, f"gpu-{di:02d}-replica-{rid:03d}-last.dat")
                 if os.path.exists(p):
                     r.last = torch.from_numpy(_read(p, n)).clone()
             for op in _bn_ops(ctx):

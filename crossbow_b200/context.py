@@ -17,6 +17,7 @@ ordering between tasks and synchronisation is expressed with CUDA events only, t
 """
 from __future__ import annotations
 
+import threading
 import time
 from typing import List, Optional
 
@@ -47,6 +48,7 @@ class ExecutionContext:
         self._disp_n, self._disp_loss, self._disp_acc = 0, 0.0, 0.0
         self.monitor: Optional[PerformanceMonitor] = None
         self.autotuner: Optional[AutoTuner] = None
+        self.autotune_trace = []                          # (replicas per GPU after the decision, job examples/s it was based on)
         self.rank, self.world = 0, 1
         self.tasks_done = 0
         self.last_loss = float("nan")
@@ -55,6 +57,9 @@ class ExecutionContext:
         self._next_learner = 0
         self._checkpoint_version = 0
         self._native = self._native_test = None
+        self._hist_seq, self.results_lost = 0, 0         # native scheduler: results read so far / overwritten before they were read
+        self._pump_lock = threading.Lock()
+        self.emit = lambda line: print(line, flush=True)  # where display and monitor lines go
 
     # ---- set-up ----
     def init(self):
@@ -71,10 +76,10 @@ class ExecutionContext:
             self.input_shape.append(1)
         batch = mc.batch_size
         ishape, lshape = Shape([batch] + self.input_shape), Shape([batch])
-        nid = train_df.getSubGraph().init(ishape, lshape, self.model, 0)
+        nid = train_df.executable().init(ishape, lshape, self.model, 0)
         self.model.finalise()
         if test_df is not None:
-            test_df.getSubGraph().init(ishape, lshape, self.model, nid)
+            test_df.executable().init(ishape, lshape, self.model, nid)
         solver = mc.getSolverConf()
         if ds is not None:
             solver.set_tasks_per_epoch(mc.numberOfTasksPerEpoch(Phase.TRAIN))
@@ -85,8 +90,8 @@ class ExecutionContext:
         wpc = self._local(mc.wpc_in_tasks())
         if mc.wpc_in_tasks() % self.world and not self.quiet:
             print(f"warning: --wpc {mc.wpc_in_tasks()} is not a multiple of the {self.world} GPUs; every GPU runs {wpc} tasks per clock", flush=True)
-        tg = train_df.getSubGraph()
-        sg = test_df.getSubGraph() if test_df is not None else None
+        tg = train_df.executable()                       # (a chain of sub-graphs runs as one program)
+        sg = test_df.executable() if test_df is not None else None
         if sys.gpu:
             from .engine import GpuEngine
             if sys.number_of_gpu_streams not in (1, sys.number_of_gpu_models) and not self.quiet:
@@ -110,7 +115,9 @@ class ExecutionContext:
                                     replicas=sys.number_of_cpu_models, wpc=wpc, devices=1, seed=sys.random_seed,
                                     splits=mc.splits, rank=self.rank, world=self.world)
         self.clock = WorkClock(wpc)
-        self.monitor = PerformanceMonitor(batch, ds.batch_bytes() if ds is not None else 0, sys.monitor_interval / 1000.0)
+        self.monitor = PerformanceMonitor(batch, ds.batch_bytes() if ds is not None else 0, sys.monitor_interval / 1000.0,
+                                          sink=None if self.quiet else (lambda line: self.emit(line)))
+        self.monitor.queue_size = self.getExecutorQueueSize
         if sys.autotune_models:
             self.autotuner = AutoTuner(sys.autotune_threshold, sys.autotune_interval)
         if sys.model_directory:
@@ -147,48 +154,107 @@ class ExecutionContext:
             if hasattr(test_ds, "source"):
                 self._native_test.set_data_source(test_ds.source(stride=1, offset=0, timeout_s=sys.task_timeout))
 
+    def _pump_results(self) -> int:
+        """Native scheduler: read the results collected since the last call, in collection order, and pass them to the
+        display, the measurement queue and the monitor.  Called by the monitor thread while `train` runs and once more
+        when it has returned, so display lines and `[MON]` lines appear while training is in progress
+        (result/TrainingResultHandler.java:231-317, PerformanceMonitor.java:59-104)."""
+        rt, n = self._native, 0
+        if rt is None:
+            return 0
+        with self._pump_lock:
+            while True:
+                first, recs = rt.history_since(self._hist_seq, 8192)
+                if first > self._hist_seq:
+                    self.results_lost += first - self._hist_seq      # the reader fell a whole ring behind
+                for task, loss, acc in recs:
+                    self.measurements.add(task, loss, acc)
+                    self._display(task, loss, acc)
+                self._hist_seq = first + len(recs)
+                n += len(recs)
+                if recs:
+                    self.last_loss, self.last_accuracy = recs[-1][1], recs[-1][2]
+                    self.monitor.task_done(len(recs))
+                if len(recs) < 8192:
+                    return n
+
+    def _job_rate(self, images_per_second: float) -> float:
+        """Throughput of the whole job: the sum over the GPUs, identical on every rank, so that the auto-tuner takes ONE
+        decision for the job (the reference is one process with one monitor, ModelManager.java:257-274)."""
+        if self.world <= 1:
+            return images_per_second
+        import torch
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()):
+            return images_per_second
+        dev = "cuda" if (self.sys.gpu and dist.get_backend() == "nccl") else "cpu"
+        t = torch.tensor([images_per_second], dtype=torch.float64, device=dev)
+        dist.all_reduce(t)
+        return float(t.item())
+
+    def _autotune(self, samples, rt=None) -> int:
+        """One auto-tuner decision, applied to the engine (and the native runtimes); returns the change in replicas."""
+        e = self.engine
+        delta = self.autotuner.decide(samples)
+        if delta > 0 and e.k < 16:
+            e.add_learner()
+            for r in (rt, self._native_test if rt is not None else None):
+                if r is not None:
+                    r.add_learner()
+            if not self.quiet:
+                print(f"[autotune] {samples[-1]:.1f} examples/s: +1 replica -> {e.k}", flush=True)
+        elif delta < 0:
+            for r in (rt, self._native_test if rt is not None else None):
+                if r is not None:
+                    r.remove_learner()
+            e.remove_learner()
+            if not self.quiet:
+                print(f"[autotune] {samples[-1]:.1f} examples/s: -1 replica -> {e.k}; tuning stops", flush=True)
+        self.autotune_trace.append((e.k, float(samples[-1]) if samples else 0.0))
+        return delta
+
     def _train_native(self, ntasks: int) -> int:
         rt, e = self._native, self.engine
         e.epoch_to_native()
-        chunk = ntasks
-        if self.autotuner is not None and self.autotuner.active:
-            chunk = max(self.clock.wpc, self.sys.autotune_interval * self.clock.wpc * 4)
+        wpc = self.clock.wpc
+        ci = self.sys.checkpoint_interval if self.sys.checkpoint_directory else 0
         done = 0
-        while done < ntasks:
-            n = min(chunk, ntasks - done)
-            t0 = time.perf_counter()
-            issued = rt.train(n, 0)
-            rt.drain(max(60.0, self.sys.task_timeout))
-            dt = time.perf_counter() - t0
-            done += issued
-            self.monitor.samples.append(issued * self.mc.batch_size / max(dt, 1e-9))
-            if issued < n:
-                break                                   # target loss reached
-            if self.autotuner is not None and self.autotuner.active:
-                delta = self.autotuner.decide(list(self.monitor.samples))
-                if delta > 0 and e.k < 16:
-                    e.add_learner()
-                    rt.add_learner()
-                    if self._native_test is not None:
-                        self._native_test.add_learner()
-                    if not self.quiet:
-                        print(f"[autotune] +1 replica -> {e.k}", flush=True)
-                elif delta < 0:
-                    rt.remove_learner()
-                    if self._native_test is not None:
-                        self._native_test.remove_learner()
-                    e.remove_learner()
-                    if not self.quiet:
-                        print(f"[autotune] -1 replica -> {e.k}; tuning stops", flush=True)
-            ci = self.sys.checkpoint_interval
-            if ci > 0 and self.sys.checkpoint_directory:
-                self.checkpoint()
-        hist = rt.history(min(max(done, 1), 65536))
-        for task, loss, acc in hist[-done:]:
-            self.measurements.add(task, loss, acc)
-            self._display(task, loss, acc)
-        if hist:
-            self.last_loss, self.last_accuracy = hist[-1][1], hist[-1][2]
+        stop = threading.Event()
+        period = max(0.01, min(0.2, self.sys.monitor_interval / 1000.0 if self.sys.monitor_interval > 0 else 0.2))
+
+        def follow():
+            while not stop.wait(period):
+                self._pump_results()
+        pump = threading.Thread(target=follow, name="xbow-monitor", daemon=True)
+        self._pump_results()
+        rt.follow_history(True)                             # nothing is overwritten before this context has read it
+        pump.start()
+        try:
+            while done < ntasks:
+                # a chunk ends where the host has something to do between two clocks: an auto-tuner decision, a checkpoint
+                n = ntasks - done
+                if self.autotuner is not None and self.autotuner.active:
+                    n = min(n, max(wpc, self.sys.autotune_interval * wpc * 4))
+                if ci > 0:
+                    to_next = (ci - rt.clock() % ci) * wpc - (rt.tasks_issued() % wpc)
+                    n = min(n, max(1, to_next))
+                t0 = time.perf_counter()
+                issued = rt.train(n, 0)
+                rt.drain(max(60.0, self.sys.task_timeout))
+                dt = time.perf_counter() - t0
+                done += issued
+                if issued < n:
+                    break                                   # target loss reached
+                if self.autotuner is not None and self.autotuner.active:
+                    self.monitor.samples.append(self._job_rate(issued * self.mc.batch_size / max(dt, 1e-9)))
+                    self._autotune(list(self.monitor.samples), rt)
+                if ci > 0 and rt.tasks_issued() % wpc == 0 and rt.clock() % ci == 0:
+                    self.checkpoint()
+        finally:
+            stop.set()
+            pump.join()
+            rt.follow_history(False)
+        self._pump_results()
         self.tasks_done += done
         self.clock.clock = rt.clock()
         self.clock.task = rt.tasks_issued() - 1
@@ -239,17 +305,12 @@ class ExecutionContext:
                 copy = solver.consume_copy_signal()
                 e.synchronise(copy=copy)
                 self.clock.tick()
-                if self.autotuner is not None:
+                if self.autotuner is not None and self.autotuner.active:
                     self._drain(inflight)
-                    delta = self.autotuner.decide(self.monitor.throughput_window())
-                    if delta > 0:
-                        e.add_learner()
-                        if not self.quiet:
-                            print(f"[autotune] +1 replica -> {e.k}", flush=True)
-                    elif delta < 0:
-                        e.remove_learner()
-                        if not self.quiet:
-                            print(f"[autotune] -1 replica -> {e.k}; tuning stops", flush=True)
+                    window = self.monitor.throughput_window()
+                    if window:
+                        window[-1] = self._job_rate(window[-1])
+                    self._autotune(window)
                 ci = self.sys.checkpoint_interval
                 if ci > 0 and self.sys.checkpoint_directory and self.clock.clock % ci == 0:
                     self._drain(inflight)
@@ -288,7 +349,7 @@ class ExecutionContext:
             if not self.sys.tee_measurements:
                 return
         if not self.quiet:
-            print(f"{text} ({self.monitor.last_rate():9.1f} examples/s)", flush=True)
+            getattr(self, "emit", print)(f"{text} ({self.monitor.last_rate():9.1f} examples/s)")
 
     def _local(self, job_tasks: int) -> int:
         """This process's share of a count given in tasks of the whole job (rounded up, at least one)."""

@@ -5,7 +5,8 @@
 // (ExecutionContext.java:257-283, dispatcher/TaskDispatcher.java, clib-multigpu/taskhandler.c, callbackhandler.c,
 // resulthandler.c:44-76, result/ResultCollector.java:40-70, modelmanager.c:147-245).  Here it is one C++ object driven
 // through a C ABI.  The device (or a fake) is reached only through four function pointers, so the very same code
-// runs against the CUDA learners, against the CPU oracle, and against a fake executor in host-only tests.
+// runs against the CUDA learners, against the CPU oracle, and against a fake executor in host-only tests (the fake is
+// not part of this library: csrc/selftest/fake_exec.cpp).
 //
 // Threads:   caller of rt_train  = dispatcher (numbers tasks, picks replicas, enqueues synchronisation)
 //            task handlers       (optional) issue the submission so the dispatcher can run ahead
@@ -175,10 +176,29 @@ class Runtime {
   // copy up to n most recent (task, loss, acc) records
   int history(uint64_t* tasks, float* loss, float* acc, int n) {
     std::lock_guard<std::mutex> g(tot_mu_);
-    int m = (int)hist_.size() < n ? (int)hist_.size() : n;
-    for (int i = 0; i < m; ++i) { const auto& h = hist_[hist_.size() - m + i]; tasks[i] = h.task; loss[i] = h.loss; acc[i] = h.acc; }
+    const uint64_t have = hist_seq_ < kHistory ? hist_seq_ : kHistory;
+    const int m = have < (uint64_t)n ? (int)have : n;
+    for (int i = 0; i < m; ++i) { const auto& h = hist_[(hist_seq_ - m + i) % kHistory]; tasks[i] = h.task; loss[i] = h.loss; acc[i] = h.acc; }
     return m;
   }
+  // Incremental read for a monitor that follows a run: records number `from`, `from` + 1, ... (every collected result has
+  // a sequence number, counted from 0 over the life of the runtime), up to n of them.  `*first` receives the number of
+  // the first record returned: larger than `from` when the reader fell more than the ring's capacity behind.
+  int history_since(uint64_t from, uint64_t* first, uint64_t* tasks, float* loss, float* acc, int n) {
+    std::lock_guard<std::mutex> g(tot_mu_);
+    const uint64_t oldest = hist_seq_ > kHistory ? hist_seq_ - kHistory : 0;
+    if (from < oldest) from = oldest;
+    *first = from;
+    int m = 0;
+    for (uint64_t q = from; q < hist_seq_ && m < n; ++q, ++m) { const auto& h = hist_[q % kHistory]; tasks[m] = h.task; loss[m] = h.loss; acc[m] = h.acc; }
+    hist_read_.store(from + (uint64_t)m, std::memory_order_release);
+    return m;
+  }
+  // A follower (the monitor that displays results while a run is in progress) promises to keep calling history_since: the
+  // collector then never overwrites a record the follower has not read yet - it waits for the reader instead, as the
+  // reference's collector finishes displaying a result before it frees the slot (result/ResultCollector.java:40-70).
+  void follow(bool on) { followed_.store(on, std::memory_order_release); }
+  uint64_t history_count() { std::lock_guard<std::mutex> g(tot_mu_); return hist_seq_; }
 
  private:
   double now() const { return seconds_since(t_origin_); }
@@ -293,16 +313,23 @@ class Runtime {
       if (s.state.load(std::memory_order_acquire) != 2 || s.task != next) { cpu_relax(++spins); continue; }
       spins = 0;
       s.state.store(3);
+      bool full = false;
       {
         std::lock_guard<std::mutex> g(tot_mu_);
         if (s.phase == 0 && std::isfinite(s.loss)) { tot_.loss_sum += s.loss; tot_.acc_sum += s.accuracy; tot_.n += 1; tot_.last_loss = s.loss; tot_.last_acc = s.accuracy; }
         else if (s.phase != 0 && std::isfinite(s.accuracy)) { tot_.loss_sum += s.loss; tot_.acc_sum += s.accuracy; tot_.n += 1; }
-        hist_.push_back({s.task, s.loss, s.accuracy});
-        if (hist_.size() > 65536) hist_.erase(hist_.begin(), hist_.begin() + 32768);
+        hist_[hist_seq_ % kHistory] = {s.task, s.loss, s.accuracy};
+        ++hist_seq_;
+        full = followed_.load(std::memory_order_acquire) && hist_seq_ - hist_read_.load(std::memory_order_acquire) >= kHistory;
       }
       if (s.phase == 0 && target_loss_ > 0 && s.loss <= target_loss_) stop_.store(true);
       s.state.store(0, std::memory_order_release);
       collected_.fetch_add(1);
+      // the ring is full of records the follower has not read: let it catch up before the next one is written
+      for (unsigned sp = 0; full && running_.load() && followed_.load(std::memory_order_acquire); ) {
+        { std::lock_guard<std::mutex> g(tot_mu_); full = hist_seq_ - hist_read_.load(std::memory_order_acquire) >= kHistory; }
+        if (full) cpu_relax(++sp);
+      }
     }
   }
   void watchdog_loop() {
@@ -343,46 +370,13 @@ class Runtime {
   std::mutex tot_mu_;
   Totals tot_{0, 0, 0, NAN, NAN};
   struct Hist { uint64_t task; float loss, acc; };
-  std::vector<Hist> hist_;
+  static constexpr uint64_t kHistory = 1 << 16;       // ring of the most recent results (a monitor reads it incrementally)
+  std::vector<Hist> hist_ = std::vector<Hist>(kHistory);
+  uint64_t hist_seq_ = 0;                             // results collected so far = sequence number of the next record
+  std::atomic<uint64_t> hist_read_{0};                // first record the follower has not read
+  std::atomic<bool> followed_{false};
   Clock::time_point t_origin_;
 };
-
-// ---- fake executor for host-only tests ------------------------------------------------------------------------------
-struct FakeExec {
-  int learners;
-  int task_us;
-  std::atomic<int> fail_task{-1};        // task id whose wait returns an error
-  std::atomic<int> hang_task{-1};        // task id whose wait never returns within the deadline
-  std::atomic<uint64_t> syncs{0}, submits{0};
-  std::vector<std::atomic<uint64_t>> current;
-  std::vector<unsigned char> last_mask;
-  std::mutex mu;
-  FakeExec(int n, int us) : learners(n), task_us(us), current(256) { for (auto& c : current) c.store(0); }
-};
-static int fake_submit(void* c, int learner, const void*, const void*, uint64_t task, int) {
-  auto* f = (FakeExec*)c; f->current[learner].store(task); f->submits.fetch_add(1); return 0;
-}
-static int fake_wait(void* c, int learner, float* loss, float* acc) {
-  auto* f = (FakeExec*)c;
-  uint64_t task = f->current[learner].load();
-  if ((int)task == f->hang_task.load()) { std::this_thread::sleep_for(std::chrono::milliseconds(1500)); }
-  else if (f->task_us > 0) std::this_thread::sleep_for(std::chrono::microseconds(f->task_us));
-  if ((int)task == f->fail_task.load()) return 77;
-  *loss = 1.0f / (1.0f + (float)task); *acc = (float)learner;
-  return 0;
-}
-static int fake_wait_task(void* c, int learner, uint64_t task, float* loss, float* acc) {
-  auto* f = (FakeExec*)c;
-  if ((int)task == f->hang_task.load()) { std::this_thread::sleep_for(std::chrono::milliseconds(1500)); }
-  else if (f->task_us > 0) std::this_thread::sleep_for(std::chrono::microseconds(f->task_us));
-  if ((int)task == f->fail_task.load()) return 77;
-  *loss = 1.0f / (1.0f + (float)task); *acc = (float)learner;
-  return 0;
-}
-static int fake_sync(void* c, uint64_t, const unsigned char* mask, int n, int) {
-  auto* f = (FakeExec*)c; f->syncs.fetch_add(1);
-  std::lock_guard<std::mutex> g(f->mu); f->last_mask.assign(mask, mask + n); return 0;
-}
 
 }  // namespace xb
 
@@ -403,7 +397,6 @@ RT_API void rt_set_data_source(void* r, void* take, void* release, void* dctx) {
   ((Runtime*)r)->set_data_source((decltype(Executor::take))take, (decltype(Executor::release))release, dctx);
 }
 RT_API void rt_set_run_ahead(void* r, int depth, void* wait_task) { ((Runtime*)r)->set_run_ahead(depth, (decltype(Executor::wait_task))wait_task); }
-RT_API void rt_fake_run_ahead(void* r, int depth) { ((Runtime*)r)->set_run_ahead(depth, fake_wait_task); }
 RT_API void rt_set_target_loss(void* r, float t) { ((Runtime*)r)->set_target_loss(t); }
 RT_API void rt_set_affinity(void* r, int first_core) { ((Runtime*)r)->set_affinity(first_core); }
 RT_API long long rt_train(void* r, long long ntasks, int phase) { return ((Runtime*)r)->train(ntasks, phase); }
@@ -424,20 +417,11 @@ RT_API void rt_totals(void* r, int reset, double* loss_sum, double* acc_sum, uns
 RT_API int rt_history(void* r, unsigned long long* tasks, float* loss, float* acc, int n) {
   return ((Runtime*)r)->history((uint64_t*)tasks, loss, acc, n);
 }
-
-RT_API void* rt_fake_create(int learners, int task_us) { return new FakeExec(learners, task_us); }
-RT_API void rt_fake_destroy(void* f) { delete (FakeExec*)f; }
-RT_API void rt_fake_attach(void* r, void* f) {
-  Executor e; memset(&e, 0, sizeof(e)); e.submit = fake_submit; e.wait = fake_wait; e.synchronise = fake_sync; e.batch = nullptr; e.ctx = f;
-  ((Runtime*)r)->set_executor(e);
+RT_API int rt_history_since(void* r, unsigned long long from, unsigned long long* first, unsigned long long* tasks, float* loss, float* acc, int n) {
+  return ((Runtime*)r)->history_since(from, (uint64_t*)first, (uint64_t*)tasks, loss, acc, n);
 }
-RT_API void rt_fake_inject(void* f, int fail_task, int hang_task) { ((FakeExec*)f)->fail_task.store(fail_task); ((FakeExec*)f)->hang_task.store(hang_task); }
-RT_API unsigned long long rt_fake_syncs(void* f) { return ((FakeExec*)f)->syncs.load(); }
-RT_API int rt_fake_last_mask(void* f, unsigned char* out, int n) {
-  auto* fe = (FakeExec*)f; std::lock_guard<std::mutex> g(fe->mu);
-  int m = (int)fe->last_mask.size() < n ? (int)fe->last_mask.size() : n;
-  memcpy(out, fe->last_mask.data(), m); return m;
-}
+RT_API unsigned long long rt_history_count(void* r) { return ((Runtime*)r)->history_count(); }
+RT_API void rt_history_follow(void* r, int on) { ((Runtime*)r)->follow(on != 0); }
 
 // ---- theta queue, exposed for tests and for Python-side pools ---------------------------------------------------------
 // ---- micro-benchmarks of the queues (src/test/java/.../microbenchmarks/{queues,slots}) -------------------------------------

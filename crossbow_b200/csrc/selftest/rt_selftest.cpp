@@ -19,12 +19,28 @@ unsigned long long rt_tasks_completed(void* r);
 int rt_failed(void* r);
 const char* rt_error(void* r);
 int rt_history(void* r, unsigned long long* tasks, float* loss, float* acc, int n);
+int rt_history_since(void* r, unsigned long long from, unsigned long long* first, unsigned long long* tasks, float* loss, float* acc, int n);
+void rt_set_executor(void* r, void* submit, void* wait, void* synchronise, void* batch, void* ctx);
+void rt_set_run_ahead(void* r, int depth, void* wait_task);
 void* rt_fake_create(int learners, int task_us);
 void rt_fake_destroy(void* f);
-void rt_fake_attach(void* r, void* f);
+void rt_fake_table(void** submit, void** wait, void** synchronise, void** wait_task);
 void rt_fake_inject(void* f, int fail_task, int hang_task);
 unsigned long long rt_fake_syncs(void* f);
-void rt_fake_run_ahead(void* r, int depth);
+int rec_jpeg_decode(const void* data, long long size, unsigned char* rgb_out, long long capacity, int* w, int* h);
+}
+#include <thread>
+#include <vector>
+
+static void rt_fake_attach(void* rt, void* fake) {
+  void *sub, *wait, *sync, *wt;
+  rt_fake_table(&sub, &wait, &sync, &wt);
+  rt_set_executor(rt, sub, wait, sync, nullptr, fake);
+}
+static void rt_fake_run_ahead(void* rt, int depth) {
+  void *sub, *wait, *sync, *wt;
+  rt_fake_table(&sub, &wait, &sync, &wt);
+  rt_set_run_ahead(rt, depth, wt);
 }
 
 #define CHECK(cond)                                                                  \
@@ -45,6 +61,10 @@ static int scenario(int handlers, int depth) {
   int n = rt_history(rt, tasks, loss, acc, 512);
   CHECK(n == 400);
   for (int i = 0; i < n; ++i) CHECK(tasks[i] == (unsigned long long)i);
+  {
+    unsigned long long first = 0, t2[16]; float l2[16], a2[16];
+    CHECK(rt_history_since(rt, 390, &first, t2, l2, a2, 16) == 10 && first == 390 && t2[9] == 399);
+  }
   if (depth > 1) for (int i = 0; i < n; ++i) CHECK(loss[i] > 0.999f / (1.0f + (float)i) && loss[i] < 1.001f / (1.0f + (float)i));
   // replicas come and go between runs (auto-tuner)
   CHECK(rt_add_learner(rt) == 4 && rt_learners(rt) == 5);
@@ -61,7 +81,45 @@ static int scenario(int handlers, int depth) {
   return 0;
 }
 
-int main() {
+// The JPEG decoder reads untrusted files: every truncation of a small file and a few thousand random corruptions of it
+// must end in an error code or an image, without touching memory outside its buffers (AddressSanitizer) and without a
+// data race between decode workers (ThreadSanitizer: the inverse-DCT table is initialised on first use).
+static int jpeg_scenario(const char* path) {
+  FILE* f = fopen(path, "rb");
+  CHECK(f != nullptr);
+  std::vector<unsigned char> file(1 << 20);
+  size_t n = fread(file.data(), 1, file.size(), f);
+  fclose(f);
+  CHECK(n > 100);
+  file.resize(n);
+  std::vector<std::thread> workers;
+  std::vector<int> good(4, 0);
+  for (int t = 0; t < 4; ++t)
+    workers.emplace_back([&, t] {
+      std::vector<unsigned char> rgb(1 << 22);
+      int w = 0, h = 0;
+      if (rec_jpeg_decode(file.data(), (long long)file.size(), rgb.data(), (long long)rgb.size(), &w, &h) == 0 && w > 0 && h > 0) good[t] = 1;
+      unsigned long long s = 0x9E3779B97F4A7C15ull * (t + 1);
+      auto rnd = [&] { s ^= s << 13; s ^= s >> 7; s ^= s << 17; return s; };
+      for (size_t cut = 2 + t; cut < file.size(); cut += 4) {                       // truncations (exact-size heap copies)
+        std::vector<unsigned char> part(file.begin(), file.begin() + cut);
+        rec_jpeg_decode(part.data(), (long long)part.size(), rgb.data(), (long long)rgb.size(), &w, &h);
+      }
+      for (int i = 0; i < 1500; ++i) {                                              // corruptions
+        std::vector<unsigned char> bad(file);
+        const int flips = 1 + (int)(rnd() % 6);
+        for (int j = 0; j < flips; ++j) bad[2 + rnd() % (bad.size() - 2)] = (unsigned char)rnd();
+        rec_jpeg_decode(bad.data(), (long long)bad.size(), rgb.data(), (long long)rgb.size(), &w, &h);
+      }
+    });
+  for (auto& th : workers) th.join();
+  for (int g : good) CHECK(g == 1);
+  return 0;
+}
+
+int main(int argc, char** argv) {
+  for (int a = 1; a < argc; ++a)
+    if (jpeg_scenario(argv[a])) return 1;
   for (int handlers = 0; handlers <= 2; handlers += 2)
     for (int depth = 1; depth <= 2; ++depth)
       if (scenario(handlers, depth)) return 1;

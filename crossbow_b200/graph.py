@@ -327,6 +327,29 @@ class Dataflow:
             g = g.next_graph
         return out
 
+    def executable(self) -> SubGraph:
+        """The graph a task of this dataflow runs.  A single sub-graph is returned as it is.  A chain built with
+        ``SubGraph.connectTo`` is executed back to back on one replica, the output batch of a sub-graph being the input
+        of the next (dispatcher/TransientTaskDispatcher.java:41-52 hands the batch on with the replica id); here the chain
+        is joined once - the last forward operator of every sub-graph gets an edge to the head of the next - and lowered
+        as ONE program, so the hand-over costs nothing and fusion works across the seam."""
+        chain = self.subgraphs()
+        if len(chain) == 1:
+            return self.graph
+        if getattr(self, "_joined", None) is None:
+            for a, b in zip(chain, chain[1:]):
+                tails = [n for n in a.order if not (n.op.kernel.is_gradient or n.op.kernel.is_optimiser or n.op.kernel.is_loss
+                                                    or n.op.kernel.is_accuracy or getattr(n.op.kernel, "is_gradient_merge", False))
+                         and not any(not (m.op.kernel.is_gradient or m.op.kernel.is_optimiser) for m in n.next)]
+                if not tails:
+                    raise ValueError(f"error: {a.getName()} has no output to feed {b.getName()}")
+                if b.head not in tails[-1].next:
+                    tails[-1].connectTo(b.head)
+            joined = SubGraph(self.graph.head)
+            joined.id, joined.phase = self.graph.id, self.phase
+            self._joined = joined
+        return self._joined
+
     def isTest(self):
         return self.phase == Phase.CHECK
 
@@ -352,11 +375,8 @@ class Dataflow:
         return "\n".join(g.dumpMemoryRequirements() for g in self.subgraphs())
 
     def init(self, input_shape, label_shape, model, first_id=0):
-        """Initialise every sub-graph of the chain; returns the next free operator id."""
-        nid = first_id
-        for g in self.subgraphs():
-            nid = g.init(input_shape, label_shape, model, nid)
-        return nid
+        """Initialise the executable graph (the whole chain of sub-graphs); returns the next free operator id."""
+        return self.executable().init(input_shape, label_shape, model, first_id)
 
     def export(self) -> str:
         return "\n".join(g.exportDot() for g in self.subgraphs())

@@ -78,13 +78,23 @@ def build_cuda(force=False, verbose=False) -> Path:
 def build_rt_selftest(sanitize: str = "thread") -> Path:
     """Stand-alone self-test of the host runtime (csrc/selftest/rt_selftest.cpp) built with -fsanitize=<thread|address>."""
     exe = LIBDIR / f"rt_selftest_{sanitize}"
-    srcs = rt_sources() + [CSRC / "selftest" / "rt_selftest.cpp"]
+    srcs = rt_sources() + [CSRC / "selftest" / "rt_selftest.cpp", CSRC / "selftest" / "fake_exec.cpp"]
     if _stale(exe, srcs + _headers()):
         LIBDIR.mkdir(parents=True, exist_ok=True)
         OBJDIR.mkdir(parents=True, exist_ok=True)
         _run(["g++", "-O1", "-g", "-std=c++17", "-pthread", f"-fsanitize={sanitize}", "-fno-omit-frame-pointer", "-o", str(exe),
               *map(str, srcs), "-lpthread", "-ldl"], OBJDIR / f"rt_selftest_{sanitize}.log")
     return exe
+
+
+def build_rt_fake() -> Path:
+    """Test-only library with the fake executor (csrc/selftest/fake_exec.cpp); it is not part of libxbow_rt.so."""
+    lib = LIBDIR / "libxbow_rt_fake.so"
+    src = CSRC / "selftest" / "fake_exec.cpp"
+    if _stale(lib, [src]):
+        OBJDIR.mkdir(parents=True, exist_ok=True)
+        _run(["g++", *CXX_FLAGS, "-shared", "-o", str(lib), str(src), "-lpthread"], OBJDIR / "link_rt_fake.log")
+    return lib
 
 
 def build_rt(force=False) -> Path:

@@ -28,7 +28,6 @@ def load() -> C.CDLL:
     _sig(lib, "rt_set_executor", None, P, P, P, P, P, P)
     _sig(lib, "rt_set_target_loss", None, P, C.c_float)
     _sig(lib, "rt_set_run_ahead", None, P, I, P)
-    _sig(lib, "rt_fake_run_ahead", None, P, I)
     _sig(lib, "rt_set_affinity", None, P, I)
     _sig(lib, "rt_train", L, P, L, I)
     _sig(lib, "rt_drain", I, P, D)
@@ -43,12 +42,9 @@ def load() -> C.CDLL:
     _sig(lib, "rt_error", C.c_char_p, P)
     _sig(lib, "rt_totals", None, P, I, C.POINTER(D), C.POINTER(D), C.POINTER(U), C.POINTER(C.c_float), C.POINTER(C.c_float))
     _sig(lib, "rt_history", I, P, C.POINTER(U), C.POINTER(C.c_float), C.POINTER(C.c_float), I)
-    _sig(lib, "rt_fake_create", P, I, I)
-    _sig(lib, "rt_fake_destroy", None, P)
-    _sig(lib, "rt_fake_attach", None, P, P)
-    _sig(lib, "rt_fake_inject", None, P, I, I)
-    _sig(lib, "rt_fake_syncs", U, P)
-    _sig(lib, "rt_fake_last_mask", I, P, C.c_char_p, I)
+    _sig(lib, "rt_history_since", I, P, U, C.POINTER(U), C.POINTER(U), C.POINTER(C.c_float), C.POINTER(C.c_float), I)
+    _sig(lib, "rt_history_count", U, P)
+    _sig(lib, "rt_history_follow", None, P, I)
     _sig(lib, "rt_bench_mpmc", D, I, I, L)
     _sig(lib, "rt_bench_theta", D, I, L)
     _sig(lib, "rt_taskq_create", P, I)
@@ -91,6 +87,25 @@ def load() -> C.CDLL:
     _sig(lib, "rt_cpu_count", I)
     _lib = lib
     return lib
+
+
+_fake_lib: Optional[C.CDLL] = None
+
+
+def load_fake() -> C.CDLL:
+    """Test-only library with the fake executor (it is not part of the runtime library)."""
+    global _fake_lib
+    if _fake_lib is None:
+        lib = C.CDLL(str(_build.build_rt_fake()))
+        P, I, U = C.c_void_p, C.c_int, C.c_ulonglong
+        _sig(lib, "rt_fake_create", P, I, I)
+        _sig(lib, "rt_fake_destroy", None, P)
+        _sig(lib, "rt_fake_table", None, C.POINTER(P), C.POINTER(P), C.POINTER(P), C.POINTER(P))
+        _sig(lib, "rt_fake_inject", None, P, I, I)
+        _sig(lib, "rt_fake_syncs", U, P)
+        _sig(lib, "rt_fake_last_mask", I, P, C.c_char_p, I)
+        _fake_lib = lib
+    return _fake_lib
 
 
 class RuntimeError_(RuntimeError):
@@ -168,7 +183,7 @@ class Runtime:
         self.h = self.lib.rt_create(learners, wpc, slack, sync_model, result_slots, task_handlers, callback_handlers, task_timeout_s)
         if not self.h:
             raise ValueError("invalid runtime configuration")
-        self._fake = None
+        self._fake, self._fake_lib, self._fake_wait_task = None, None, 0
 
     def set_executor(self, submit: int, wait: int, synchronise: int, batch: int, ctx: int):
         self.lib.rt_set_executor(self.h, submit, wait, synchronise, batch, ctx)
@@ -176,10 +191,7 @@ class Runtime:
     def set_run_ahead(self, depth: int, wait_task: int = 0):
         """Let every replica hold up to ``depth`` tasks in flight (``wait_task``: address of the executor's per-task wait;
         0 with an attached fake executor uses the fake's)."""
-        if wait_task:
-            self.lib.rt_set_run_ahead(self.h, depth, wait_task)
-        else:
-            self.lib.rt_fake_run_ahead(self.h, depth)
+        self.lib.rt_set_run_ahead(self.h, depth, wait_task or self._fake_wait_task)
 
     def set_data_source(self, source_handle: int):
         """Batches come from a native data set (``crossbow_b200.data.native``) instead of the executor's own ring."""
@@ -187,19 +199,24 @@ class Runtime:
         self.lib.rt_set_data_source(self.h, addr("ds_source_take"), addr("ds_source_release"), source_handle)
 
     def attach_fake(self, learners: int, task_us: int = 100):
-        self._fake = self.lib.rt_fake_create(learners, task_us)
-        self.lib.rt_fake_attach(self.h, self._fake)
+        """Drive this runtime with the fake executor of the test library (host-only tests)."""
+        fl = self._fake_lib = load_fake()
+        self._fake = fl.rt_fake_create(learners, task_us)
+        sub, wait, sync, wt = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+        fl.rt_fake_table(C.byref(sub), C.byref(wait), C.byref(sync), C.byref(wt))
+        self._fake_wait_task = wt.value
+        self.lib.rt_set_executor(self.h, sub.value, wait.value, sync.value, 0, self._fake)
         return self._fake
 
     def inject(self, fail_task: int = -1, hang_task: int = -1):
-        self.lib.rt_fake_inject(self._fake, fail_task, hang_task)
+        self._fake_lib.rt_fake_inject(self._fake, fail_task, hang_task)
 
     def fake_syncs(self) -> int:
-        return self.lib.rt_fake_syncs(self._fake)
+        return self._fake_lib.rt_fake_syncs(self._fake)
 
     def fake_last_mask(self):
         buf = C.create_string_buffer(256)
-        n = self.lib.rt_fake_last_mask(self._fake, buf, 256)
+        n = self._fake_lib.rt_fake_last_mask(self._fake, buf, 256)
         return list(buf.raw[:n])
 
     def train(self, ntasks: int, phase: int = 0) -> int:
@@ -252,12 +269,28 @@ class Runtime:
         m = self.lib.rt_history(self.h, t, l, a, n)
         return [(t[i], l[i], a[i]) for i in range(m)]
 
+    def history_since(self, seq: int, n: int = 4096):
+        """Results number ``seq``, ``seq + 1``, ... in collection order (every collected result has a sequence number,
+        counted from 0).  Returns ``(first, records)``; ``first > seq`` means the reader fell behind the ring and the
+        records in between are gone."""
+        t, l, a, first = (C.c_ulonglong * n)(), (C.c_float * n)(), (C.c_float * n)(), C.c_ulonglong()
+        m = self.lib.rt_history_since(self.h, seq, C.byref(first), t, l, a, n)
+        return first.value, [(t[i], l[i], a[i]) for i in range(m)]
+
+    def follow_history(self, on: bool):
+        """While on, the runtime never overwrites a result that `history_since` has not returned yet (it waits for the
+        reader), so a monitor that keeps reading loses nothing however long the run is."""
+        self.lib.rt_history_follow(self.h, int(on))
+
+    def results_collected(self) -> int:
+        return int(self.lib.rt_history_count(self.h))
+
     def close(self):
         if self.h:
             self.lib.rt_destroy(self.h)
             self.h = None
         if self._fake:
-            self.lib.rt_fake_destroy(self._fake)
+            self._fake_lib.rt_fake_destroy(self._fake)
             self._fake = None
 
     def __del__(self):

@@ -26,23 +26,33 @@ class PerformanceMonitor:
     """Counts finished tasks and turns them into examples/s and MB/s per interval; keeps a bounded window of samples
     that feeds the auto-tuner."""
 
-    def __init__(self, batch_size: int, batch_bytes: int, interval_s: float = 1.0, window: int = 64):
+    def __init__(self, batch_size: int, batch_bytes: int, interval_s: float = 1.0, window: int = 64, sink=None):
+        """`sink`: called with every `[MON]` line as it is produced (the execution context prints it); the most recent
+        lines are also kept in `lines`."""
         self.batch_size, self.batch_bytes, self.interval = batch_size, batch_bytes, interval_s
         self.samples = deque(maxlen=window)
         self.t0 = time.perf_counter()
         self.count = 0
         self.total = 0
-        self.lines = []
+        self.lines = deque(maxlen=256)
+        self.sink = sink
+        self.queue_size = None           # callable returning the number of tasks in flight, if known
 
     def task_done(self, n: int = 1):
+        """`n` more tasks have finished.  Once per interval this produces the reference's monitor line
+        (PerformanceMonitor.java:75-98: examples/s and MB/s of sub-graph S000, executor queue length)."""
         self.count += n
         self.total += n
         now = time.perf_counter()
         dt = now - self.t0
-        if dt >= self.interval:
+        if dt >= self.interval > 0:
             rate = self.count * self.batch_size / dt
             self.samples.append(rate)
-            self.lines.append(f"[MON] {rate:10.1f} examples/s {self.count * self.batch_bytes / dt / 1e6:9.2f} MB/s")
+            q = int(self.queue_size()) if self.queue_size is not None else 0
+            line = f"[MON] S000 {rate:10.3f} examples/s {self.count * self.batch_bytes / dt / 1048576.0:10.3f} MB/s q {q:6d}"
+            self.lines.append(line)
+            if self.sink is not None:
+                self.sink(line)
             self.t0, self.count = now, 0
 
     def flush(self):

@@ -465,3 +465,59 @@ def test_graph_and_model_accessors_under_reference_names():
     assert s.dimensions() == 5
     g2 = SubGraph(DataflowNode(Operator("x", ReLU(ReLUConf()))))
     assert g.connectTo(g2) is g2 and g2.getPrevious() is g and not g2.isMostUpstream()
+
+
+def _two_halves(joined_by_nodes: bool):
+    """LeNet-like network cut after the first pooling layer: (head of the first half, head of the second half)."""
+    from crossbow_b200.graph import append_gradients
+    from crossbow_b200.models._builder import Net
+    from crossbow_b200.types import PoolMethod
+    a = Net()
+    a.conv("Conv", 8, 5, bias=True)
+    a.pool("Pool", PoolMethod.MAX, 2, 2)
+    b = Net()
+    if joined_by_nodes:
+        b.cur = a.cur
+    b.conv("Conv", 12, 5, bias=True)
+    head_b = b.cur
+    b.pool("Pool", PoolMethod.MAX, 2, 2)
+    b.fc("InnerProduct", 32)
+    b.relu("ReLU")
+    b.fc("InnerProduct", 10)
+    b.classifier_tail()
+    append_gradients(head_b, ModelConf.getInstance().getSolverConf())     # the second half is trained, the first is not
+    return a.head, head_b
+
+
+def test_chained_subgraphs_run_as_one_program():
+    """`SubGraph.connectTo`: the output batch of a sub-graph feeds the next one on the same replica
+    (dispatcher/TransientTaskDispatcher.java:41-52).  A two-sub-graph dataflow must train exactly like the same operators
+    wired into one graph."""
+    from crossbow_b200.context import ExecutionContext
+    from crossbow_b200.data import SyntheticDataset
+    from crossbow_b200.graph import SubGraph
+    losses = []
+    for chained in (True, False):
+        SystemConf.reset().setNumberOfCpuModels(2).setDisplayInterval(0)
+        mc = ModelConf.reset()
+        mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.05).setMomentum(0.9).setAlpha(0.1)
+        mc.setBatchSize(8).setWpc(2).setUpdateModel("SMA")
+        mc.setDataset(Phase.TRAIN, SyntheticDataset([1, 28, 28], 10, 8, batches=4, seed=2, distribution="uniform"))
+        head_a, head_b = _two_halves(joined_by_nodes=not chained)
+        if chained:
+            first, second = SubGraph(head_a), SubGraph(head_b)
+            assert first.connectTo(second) is second and first.getNext() is second and second.getPrevious() is first
+            df = Dataflow(first).setPhase(Phase.TRAIN)
+            assert df.numberOfSubGraphs() == 2
+            joined = df.executable()
+            assert joined.numberOfOperators() == first.numberOfOperators() + second.numberOfOperators()
+            assert joined.getLossNode() is not None and df.executable() is joined
+        else:
+            df = Dataflow(SubGraph(head_a)).setPhase(Phase.TRAIN)
+        ctx = ExecutionContext([df, None], quiet=True)
+        ctx.init()
+        ctx.train(8, "tasks")
+        losses.append(ctx.measurements.losses())
+        ctx.destroy()
+    assert len(losses[0]) == 8 and losses[0] == losses[1]
+    assert losses[0][-1] < losses[0][0]

@@ -211,3 +211,50 @@ def test_cpu_affinity():
     assert cpu_bind(0) == 0
     assert cpu_id() == 0
     assert cpu_unbind() == 0
+
+
+def test_results_are_displayed_while_training_runs_and_none_are_lost():
+    """Native scheduler: a monitor thread reads the result ring incrementally while `train` runs, so display lines and
+    `[MON]` lines appear during training (result/TrainingResultHandler.java:231-317, PerformanceMonitor.java:59-104) and a
+    run far longer than the ring loses nothing."""
+    import time
+    from crossbow_b200 import ModelConf, SystemConf
+    from crossbow_b200.context import ExecutionContext
+    from crossbow_b200.runtime import Runtime
+    from crossbow_b200.utils.measure import MeasurementQueue, PerformanceMonitor
+    from crossbow_b200.workclock import WorkClock
+
+    class Engine:                      # what _train_native needs from an engine
+        k = 4
+        def epoch_to_native(self): pass
+        def epoch_from_native(self): pass
+        def finish(self): pass
+
+    total = 200_000
+    ctx = ExecutionContext([None], SystemConf.reset(), ModelConf.reset(), quiet=False)
+    ctx.sys.display_interval, ctx.sys.monitor_interval = 1000, 50
+    ctx.mc.setBatchSize(8)
+    ctx.engine, ctx.clock = Engine(), WorkClock(4)
+    lines = []
+    ctx.emit = lambda line: lines.append((time.perf_counter(), line))
+    ctx.monitor = PerformanceMonitor(8, 1024, 0.05, sink=ctx.emit)
+    ctx.monitor.queue_size = ctx.getExecutorQueueSize
+    ctx.measurements = MeasurementQueue(capacity=total)
+    rt = Runtime(learners=4, wpc=4, result_slots=256, callback_handlers=2, task_timeout_s=30.0)
+    rt.attach_fake(4, task_us=0)
+    ctx._native = rt
+    try:
+        done = ctx._train_native(total)
+        t_end = time.perf_counter()
+    finally:
+        rt.close()
+    assert done == total and ctx.results_lost == 0 and ctx.tasks_done == total
+    assert len(ctx.measurements) == total
+    assert sorted(m[1] for m in ctx.measurements.items) == list(range(total))          # every task's result, once
+    shown = [l for _, l in lines if l.startswith("[") and not l.startswith("[MON]")]
+    assert len(shown) == total // 1000 and shown[0].startswith("[001000]") and shown[-1].startswith(f"[{total:06d}]")
+    mon = [(t, l) for t, l in lines if l.startswith("[MON]")]
+    assert mon and "examples/s" in mon[0][1] and " q " in mon[0][1]
+    # lines appeared while training was in progress, not after it
+    early = [t for t, _ in lines if t < t_end - 0.5 * (t_end - lines[0][0])]
+    assert len(early) > 5
