@@ -447,26 +447,41 @@ struct Rng {           // splitmix64: one independent stream per (seed, record)
 };
 struct Box { float xmin, ymin, xmax, ymax; };   // normalised [0,1]
 
-// tf.image.sample_distorted_bounding_box semantics as restated by the reference (image/image.c:826-975)
-static Box sample_distorted_box(Rng& rng, const std::vector<Box>& boxes, int W, int H, float min_cover = 0.1f, float ar_lo = 0.75f, float ar_hi = 1.33f,
-                                float area_lo = 0.05f, float area_hi = 1.0f, int attempts = 100) {
-  std::vector<Box> bs = boxes;
-  if (bs.empty()) bs.push_back({0.f, 0.f, 1.f, 1.f});
+// Random crop with the distribution of the reference's sampler (image/image.c:826-975, itself a restatement of
+// tf.image.sample_distorted_bounding_box): per attempt an aspect ratio uniform in [ar_lo, ar_hi]; the HEIGHT uniform over
+// the integers between the heights that the smallest and the largest allowed area imply for that ratio (the largest
+// lowered until the rounded width fits the image); width = round(height * ratio); one more row if rounding took the area
+// below the minimum; the position uniform over the placements that fit; accepted when some labelled box (in whole
+// pixels) covers at least `min_cover` of the CROP's area.  After `attempts` failures the whole image is used.
+struct PixelRect { int x0, y0, x1, y1; };
+static PixelRect sample_distorted_box(Rng& rng, const std::vector<Box>& boxes, int W, int H, float min_cover = 0.1f, float ar_lo = 0.75f, float ar_hi = 1.33f,
+                                      float area_lo = 0.05f, float area_hi = 1.0f, int attempts = 100) {
+  std::vector<PixelRect> rects;
+  for (const Box& b : boxes) rects.push_back({(int)(b.xmin * W), (int)(b.ymin * H), (int)(b.xmax * W), (int)(b.ymax * H)});
+  if (rects.empty()) rects.push_back({0, 0, W, H});
+  auto uniform_int = [&](int n) { return n <= 0 ? 0 : (int)(rng.next() % (uint64_t)(n + 1)); };      // closed range [0, n]
+  const float min_area = area_lo * W * H, max_area = area_hi * W * H;
   for (int a = 0; a < attempts; ++a) {
-    float ar = rng.uniform(ar_lo, ar_hi);
-    float area = rng.uniform(area_lo, area_hi) * W * H;
-    int h = (int)std::lrintf(std::sqrt(area / ar)), w = (int)std::lrintf(h * ar);
-    if (w <= 0 || h <= 0 || w > W || h > H) continue;
-    int x0 = (int)(rng.next() % (uint64_t)(W - w + 1)), y0 = (int)(rng.next() % (uint64_t)(H - h + 1));
-    Box c{x0 / (float)W, y0 / (float)H, (x0 + w) / (float)W, (y0 + h) / (float)H};
-    for (const Box& b : bs) {
-      float ix = std::max(0.f, std::min(c.xmax, b.xmax) - std::max(c.xmin, b.xmin));
-      float iy = std::max(0.f, std::min(c.ymax, b.ymax) - std::max(c.ymin, b.ymin));
-      float barea = std::max(1e-12f, (b.xmax - b.xmin) * (b.ymax - b.ymin));
-      if (ix * iy / barea >= min_cover) return c;
+    const float ratio = rng.uniform(ar_lo, ar_hi);
+    int hmin = (int)std::lrintf(std::sqrt(min_area / ratio)), hmax = (int)std::lrintf(std::sqrt(max_area / ratio));
+    if (std::lrintf(hmax * ratio) > W) hmax = (int)((W + 0.5 - 1e-7) / ratio);
+    hmax = std::min(hmax, H);
+    hmin = std::min(hmin, hmax);
+    int h = hmin + uniform_int(hmax - hmin);
+    int w = (int)std::lrintf(h * ratio);
+    if (w > W) continue;
+    if ((float)(h * w) < min_area) { h += 1; w = (int)std::lrintf(h * ratio); }
+    const float area = (float)(h * w);
+    if (area < min_area || area > max_area || w <= 0 || w > W || h <= 0 || h > H) continue;
+    const int y = uniform_int(H - h), x = uniform_int(W - w);
+    const PixelRect c{x, y, x + w, y + h};
+    for (const PixelRect& r : rects) {
+      if (r.x1 - r.x0 < 1 || r.y1 - r.y0 < 1) continue;
+      const int ix = std::max(0, std::min(c.x1, r.x1) - std::max(c.x0, r.x0)), iy = std::max(0, std::min(c.y1, r.y1) - std::max(c.y0, r.y0));
+      if ((float)ix * (float)iy / area >= min_cover) return c;
     }
   }
-  return {0.f, 0.f, 1.f, 1.f};
+  return {0, 0, W, H};
 }
 
 // bilinear resize of the crop [x0,x0+cw) x [y0,y0+ch) of an interleaved uint8 RGB image into S x S planar floats,
@@ -490,24 +505,29 @@ static void crop_resize_to_chw(const uint8_t* rgb, int W, int H, int x0, int y0,
 
 struct Record { int label; std::vector<Box> boxes; int height, width; const uint8_t* jpeg; size_t jpeg_bytes; };
 
+// Which part of a decoded W x H image becomes the example: the crop window and whether it is mirrored.  The same plan
+// drives the CPU path below and the CUDA kernel (csrc/kernels/image.cu), so the two produce identical examples.
+struct CropPlan { int x0, y0, cw, ch, flip; };
+static CropPlan plan_crop(int W, int H, const std::vector<Box>& boxes, bool training, uint64_t seed) {
+  if (training) {
+    Rng rng(seed);
+    const PixelRect c = sample_distorted_box(rng, boxes, W, H);
+    const int flip = (int)(rng.next() & 1);
+    return {c.x0, c.y0, std::max(1, c.x1 - c.x0), std::max(1, c.y1 - c.y0), flip};
+  }
+  // shorter side -> 1.145 * S, then centre crop: equivalent to resizing a centred square crop of side min(W,H)/1.145
+  const float side = std::min(W, H) / 1.145f;
+  const int cs = std::max(1, (int)std::lrintf(side));
+  return {(W - cs) / 2, (H - cs) / 2, cs, cs, 0};
+}
+
 // Process one record into out[3*S*S]; returns 0 or the decoder's error code (the output is then a grey image).
 static int process_record(const Record& r, bool training, int S, uint64_t seed, float* out) {
   std::vector<uint8_t> rgb; int W = 0, H = 0;
   int e = jpeg_decode(r.jpeg, r.jpeg_bytes, rgb, W, H);
   if (e != 0) { for (size_t i = 0; i < (size_t)3 * S * S; ++i) out[i] = 0.f; return e; }
-  if (training) {
-    Rng rng(seed);
-    Box b = sample_distorted_box(rng, r.boxes, W, H);
-    int x0 = (int)(b.xmin * W), y0 = (int)(b.ymin * H);
-    int cw = std::max(1, std::min(W - x0, (int)std::lrintf((b.xmax - b.xmin) * W))), ch = std::max(1, std::min(H - y0, (int)std::lrintf((b.ymax - b.ymin) * H)));
-    bool flip = rng.next() & 1;
-    crop_resize_to_chw(rgb.data(), W, H, x0, y0, cw, ch, flip, S, out);
-  } else {
-    // shorter side -> 1.145*S, then centre crop: equivalent to resizing a centred square crop of side min(W,H)/1.145
-    float side = std::min(W, H) / 1.145f;
-    int cs = std::max(1, (int)std::lrintf(side));
-    crop_resize_to_chw(rgb.data(), W, H, (W - cs) / 2, (H - cs) / 2, cs, cs, false, S, out);
-  }
+  const CropPlan p = plan_crop(W, H, r.boxes, training, seed);
+  crop_resize_to_chw(rgb.data(), W, H, p.x0, p.y0, p.cw, p.ch, p.flip != 0, S, out);
   return 0;
 }
 
@@ -648,6 +668,14 @@ RT_API int rec_process(const void* jpeg, long long size, const float* boxes_xyxy
 }
 // writer
 struct RecWriter { FILE* f; int32_t count; };
+// Crop plan of one decoded image (x0, y0, width, height, flip) for the given boxes / phase / seed: what rec_process uses.
+RT_API void rec_plan(int W, int H, const float* boxes_xyxy, int nboxes, int training, unsigned long long seed, int* plan5) {
+  std::vector<Box> boxes((size_t)(nboxes > 0 ? nboxes : 0));
+  for (int k = 0; k < nboxes; ++k) boxes[k] = {boxes_xyxy[4 * k], boxes_xyxy[4 * k + 1], boxes_xyxy[4 * k + 2], boxes_xyxy[4 * k + 3]};
+  const CropPlan p = plan_crop(W, H, boxes, training != 0, seed);
+  plan5[0] = p.x0; plan5[1] = p.y0; plan5[2] = p.cw; plan5[3] = p.ch; plan5[4] = p.flip;
+}
+
 RT_API void* rec_writer_open(const char* path) {
   FILE* f = fopen(path, "wb");
   if (!f) return nullptr;

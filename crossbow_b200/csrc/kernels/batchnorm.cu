@@ -379,9 +379,12 @@ XB_API int xb_bn_backward_apply(const float* dy, const float* x, const float* y,
 // only a handle for cudaGetSymbolAddress, never a device address.
 static __device__ __align__(256) float g_bn_static_sums[2 * XB_BN_STATIC_MAX_CHANNELS];
 
+#include <atomic>
 namespace {
 constexpr int kMaxDevices = 64;
-float* g_bn_static_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device, filled on first use
+// device address of the array, per device, filled on first use; atomic because several host threads may make their
+// first call on a device at the same time (they all store the same value)
+std::atomic<float*> g_bn_static_ptr[kMaxDevices];
 }
 
 extern "C" __attribute__((visibility("default")))
@@ -399,20 +402,21 @@ int xb_bn_backward_static(const float* dy, const float* x, const float* y, const
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return XB_BN_STATIC_BAD_ARGUMENT;
-  if (!g_bn_static_ptr[dev]) {
+  float* sums = g_bn_static_ptr[dev].load(std::memory_order_acquire);
+  if (!sums) {
     // once per device, with that device current: translate the symbol into the address the kernels can use
-    float* p = nullptr;
-    e = cudaGetSymbolAddress((void**)&p, g_bn_static_sums);
+    e = cudaGetSymbolAddress((void**)&sums, g_bn_static_sums);
     if (e != cudaSuccess) return (int)e;
-    g_bn_static_ptr[dev] = p;
+    g_bn_static_ptr[dev].store(sums, std::memory_order_release);
   }
-  float* sums = g_bn_static_ptr[dev];
   e = cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)C, stream);     // the sums accumulate from zero
   if (e != cudaSuccess) return (int)e;
   BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, sums, dx, dres, dgamma, dbeta, M, C, relu ? 1 : 0, accum_dx, accum_dres, 0, nullptr};
   bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
-  int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
-  if (v4) { bn_bwd_reduce_kernel<4><<<blocks, NT, 0, stream>>>(a); bn_bwd_apply_kernel<4><<<blocks, NT, 0, stream>>>(a); }
-  else    { bn_bwd_reduce_kernel<1><<<blocks, NT, 0, stream>>>(a); bn_bwd_apply_kernel<1><<<blocks, NT, 0, stream>>>(a); }
+  // same launch shapes as xb_bn_backward: fewer, longer blocks for the reduction (its tail is same-address atomics)
+  int blocks, rblocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, rblocks, g_bn_reduce_blocks, 8);
+  if (v4) bn_bwd_reduce_kernel<4><<<rblocks, NT, 0, stream>>>(a); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, stream>>>(a);
+  a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
+  if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, stream>>>(a); else bn_bwd_apply_kernel<1><<<blocks, NT, 0, stream>>>(a);
   return (int)cudaGetLastError();
 }

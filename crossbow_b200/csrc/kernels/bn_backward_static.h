@@ -11,7 +11,8 @@
 //     loaded carries it until the process exits.  A call with more channels is refused with XB_BN_STATIC_TOO_MANY_CHANNELS
 //     (and one line on stderr); nothing is launched.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress) with that device current.
-//     Make that first call outside any stream capture.  Later calls only enqueue work on `stream`: one memset of the
+//     Make that first call outside any stream capture.  Host threads may make their first calls concurrently (the looked-up
+//     address is kept in an atomic).  Later calls only enqueue work on `stream`: one memset of the
 //     part of the array that is used (the sums must start from zero) and the two backward kernels.
 //   * All calls share the one array, which keeps the previous call's sums.  Two calls that overlap on the GPU (different
 //     streams, or different host threads without ordering) race on it; serialise them.

@@ -438,6 +438,19 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
   stamp_exit(a);
 }
 
+// Plain copy with 16-byte accesses: the yardstick for what st.global over NVLink sustains when every GPU pushes to every
+// peer at once (the synchronisation micro-benchmark measures the exchange against it).
+__global__ void __launch_bounds__(NT) peer_copy_kernel(float4* __restrict__ dst, const float4* __restrict__ src, long long n4) {
+  const long long stride = (long long)gridDim.x * NT * U;
+  for (long long i0 = (long long)blockIdx.x * NT * U + threadIdx.x; i0 < n4; i0 += stride) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (i0 + u * NT < n4) v[u] = src[i0 + u * NT];
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (i0 + u * NT < n4) dst[i0 + u * NT] = v[u];
+  }
+}
+
 // replicas <- z (DEFAULT update model, and LR-drop copies when no averaging is due)
 __global__ void broadcast_z_kernel(const float* __restrict__ z, float* const* w, int k, long long n4) {
   for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n4; i += (long long)gridDim.x * NT) {
@@ -580,6 +593,13 @@ XB_API int xb_stream_wait_value_supported() {
   return stream_wait_fn() != nullptr ? 1 : 0;
 }
 XB_API int xb_sync_stamp_words() { return XB_SYNC_STAMP_WORDS; }
+
+// dst (possibly another GPU's memory) <- src (this GPU's), n floats (multiple of 4), `blocks` CTAs
+XB_API int xb_peer_copy(float* dst, const float* src, long long n, int blocks, cudaStream_t st) {
+  if (n % 4 || blocks < 1) return -XB_BAD_ARG;
+  peer_copy_kernel<<<blocks, NT, 0, st>>>(reinterpret_cast<float4*>(dst), reinterpret_cast<const float4*>(src), n / 4);
+  return (int)cudaGetLastError();
+}
 
 XB_API int xb_broadcast_model(const float* z, float* const* w_dev_array, int k, long long n, cudaStream_t st) {
   if (n % 4) return -XB_BAD_ARG;

@@ -24,6 +24,7 @@ def _lib():
         V = C.POINTER(C.c_void_p)
         lib.rec_jpeg_decode.restype, lib.rec_jpeg_decode.argtypes = I, [P, L, P, L, C.POINTER(I), C.POINTER(I)]
         lib.rec_process.restype, lib.rec_process.argtypes = I, [P, L, C.POINTER(F), I, I, I, C.c_ulonglong, P]
+        lib.rec_plan.restype, lib.rec_plan.argtypes = None, [I, I, C.POINTER(F), I, I, C.c_ulonglong, C.POINTER(I)]
         lib.rec_writer_open.restype, lib.rec_writer_open.argtypes = P, [C.c_char_p]
         lib.rec_writer_append.restype, lib.rec_writer_append.argtypes = I, [P, P, L, I, C.POINTER(F), I, I, I]
         lib.rec_writer_close.restype, lib.rec_writer_close.argtypes = I, [P]
@@ -41,7 +42,7 @@ def _lib():
 
 
 def decode_jpeg(data: bytes) -> np.ndarray:
-    """Baseline JPEG -> uint8 RGB array [H, W, 3]."""
+    """JPEG (sequential or progressive; grey, YCbCr, RGB, CMYK / YCCK) -> uint8 RGB array [H, W, 3]."""
     lib = _lib()
     w, h = C.c_int(), C.c_int()
     out = np.zeros(1, dtype=np.uint8)
@@ -63,6 +64,52 @@ def preprocess(data: bytes, boxes: Sequence[Sequence[float]] = (), training: boo
     rc = lib.rec_process(data, len(data), b.ctypes.data_as(C.POINTER(C.c_float)), b.shape[0], int(training), size, seed, out.ctypes.data)
     if rc != 0:
         raise ValueError(f"JPEG decoder error {rc}")
+    return out
+
+
+def crop_plan(width: int, height: int, boxes: Sequence[Sequence[float]] = (), training: bool = True, seed: int = 0):
+    """(x0, y0, crop width, crop height, flip) the pipeline uses for a decoded ``width`` x ``height`` image: the sampled
+    distorted bounding box and mirror flag of a training example, or the centre crop of a test example."""
+    lib = _lib()
+    b = np.asarray(boxes, dtype=np.float32).reshape(-1, 4)
+    plan = (C.c_int * 5)()
+    lib.rec_plan(width, height, b.ctypes.data_as(C.POINTER(C.c_float)), b.shape[0], int(training), seed, plan)
+    return tuple(int(v) for v in plan)
+
+
+def preprocess_batch_gpu(images: Sequence[np.ndarray], plans: Sequence[Sequence[int]], size: int = 224, device=None, stream: int = 0) -> torch.Tensor:
+    """Decoded uint8 RGB images [H, W, 3] + their crop plans -> float32 [N, 3, size, size] in [-1, 1] ON THE GPU, in one
+    kernel launch (csrc/kernels/image.cu): crop, mirror, bilinear resize, x / 127.5 - 1, planar layout.  Bit-identical to
+    ``preprocess`` for the same plan; the host only uploads 3 bytes per source pixel."""
+    from ..ops import lib as L
+    cl = L.load()
+    device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    n = len(images)
+    if n == 0 or n != len(plans):
+        raise ValueError("one crop plan per image is required")
+    desc = np.zeros((n, cl.xb_image_desc_size() // 4), dtype=np.int32)
+    offsets, total = [], 0
+    for img in images:
+        if img.dtype != np.uint8 or img.ndim != 3 or img.shape[2] != 3:
+            raise ValueError("images must be uint8 arrays of shape [H, W, 3]")
+        offsets.append(total)
+        total += (img.size + 15) // 16 * 16
+    packed = torch.empty(total, dtype=torch.uint8).pin_memory() if torch.cuda.is_available() else torch.empty(total, dtype=torch.uint8)
+    pk = packed.numpy()
+    for i, (img, plan) in enumerate(zip(images, plans)):
+        h, w = img.shape[:2]
+        x0, y0, cw, ch, flip = [int(v) for v in plan]
+        if not (0 <= x0 and 0 <= y0 and cw >= 1 and ch >= 1 and x0 + cw <= w and y0 + ch <= h):
+            raise ValueError(f"crop window {plan} does not fit a {w} x {h} image")
+        pk[offsets[i]:offsets[i] + img.size] = np.ascontiguousarray(img).reshape(-1)
+        desc[i].view(np.int64)[0] = offsets[i]
+        desc[i, 2:9] = (w, h, x0, y0, cw, ch, flip)
+    d_rgb = packed.to(device, non_blocking=True)
+    d_desc = torch.from_numpy(desc).to(device)
+    out = torch.empty((n, 3, size, size), dtype=torch.float32, device=device)
+    s = stream or torch.cuda.current_stream(device).cuda_stream
+    L.check(cl.xb_image_crop_resize(d_rgb.data_ptr(), d_desc.data_ptr(), n, size, out.data_ptr(), s), "image crop / resize")
+    out._keep = (d_rgb, d_desc)          # the kernel may still be reading them when this returns
     return out
 
 

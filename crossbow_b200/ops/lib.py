@@ -128,6 +128,8 @@ def load() -> C.CDLL:
     _sig(lib, "xb_classify", I, P, P, I, I, P)
     _sig(lib, "xb_grad_sumsq", I, P, P, L, P)
     _sig(lib, "xb_fused_optimiser", I, P, P, P, P, P, P, P, P, L, I, P)
+    _sig(lib, "xb_image_desc_size", I)
+    _sig(lib, "xb_image_crop_resize", I, P, P, I, I, P, P)
     # sync
     _sig(lib, "xb_sync_chunk", L, L)
     _sig(lib, "xb_sync_nchunks", L, L)
@@ -138,6 +140,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_fused_sync", I, C.POINTER(XbSyncDesc), P, P, I, P)
     _sig(lib, "xb_fused_sync_emulated", I, C.POINTER(XbSyncDesc), I, P, I, P)
     _sig(lib, "xb_broadcast_model", I, P, P, I, L, P)
+    _sig(lib, "xb_peer_copy", I, P, P, L, I, P)
     _sig(lib, "xb_stream_wait_value32", I, P, P, c_uint)
     _sig(lib, "xb_stream_wait_value_supported", I)
     _sig(lib, "xb_sync_stamp_words", I)

@@ -8,7 +8,10 @@ replicas per GPU: device time per synchronisation (CUDA events around ``--iters`
 maximum over ranks) of
   fused      one persistent kernel per GPU: replica reduction + peer-memory all-reduce + central update + correction
   reference  per-replica difference/axpy kernels + NCCL all_reduce + central update (the reference's sequence)
-and the fused kernel's fraction of its roofline = max(HBM bytes / measured copy bandwidth, NVLink bytes / 770 GB/s).
+and the fused kernel's fraction of its roofline = max(HBM bytes / measured copy bandwidth, NVLink bytes / link rate),
+printed for TWO link rates: the rate a plain copy kernel reaches here when every GPU stores into every peer at once
+(measured by this program on the same buffers, ``peer_store_gbs``) and the nominal 900 GB/s per direction of NVLink 5.
+Every row carries the SM clocks and throttle reasons sampled (NVML, read-only) while it was measured.
 Consecutive calls touch 4*n*(3k+4) bytes; for the small model that fits in L2, so the small-model rows are L2-resident
 numbers (as they are inside training); the large model exceeds L2 for every k.
 """
@@ -38,7 +41,9 @@ def main():
     init_process_group("nccl")
     lib = L.init_device()
     bw, _, how = peaks()
-    nvlink = 770.0
+    from ..utils.gpumon import ClockSampler
+    from .peer import PeerBuffer
+    NOMINAL_LINK = 900.0                      # GB/s per direction per GPU (NVLink 5, 18 links)
     stream = torch.cuda.Stream()
 
     def timed(fn):
@@ -58,8 +63,30 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def peer_store_rate(n):
+        """GB/s leaving one GPU when every rank copies (G - 1) / G of an n-float vector into its peers' buffers at once
+        with a plain 16-byte copy kernel (slice g goes to rank g): the all-to-all pattern of the two-shot exchange."""
+        if world == 1:
+            return None
+        part = (n // world + 3) // 4 * 4
+        buf = PeerBuffer(4 * part * world, rank, world)
+        src = torch.randn(part * world, device="cuda")
+        s = stream.cuda_stream
+
+        def push():
+            for g in range(world):
+                if g != rank:
+                    L.check(lib.xb_peer_copy(buf.ptrs[g] + 4 * part * rank, src.data_ptr() + 4 * part * g, part, 148, s), "peer copy")
+        with torch.cuda.stream(stream):
+            us = timed(push)
+        torch.cuda.synchronize()
+        dist.barrier()
+        buf.close()
+        return 4.0 * part * (world - 1) / (us * 1e3)
+
     for n in [int(v) for v in a.sizes.split(",")]:
         n = (n + 3) // 4 * 4
+        peer_gbs = peer_store_rate(n)
         for k in [int(v) for v in a.replicas.split(",")]:
             g = torch.Generator(device="cuda").manual_seed(1 + rank)
             ws = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
@@ -72,22 +99,30 @@ def main():
             zl = torch.zeros(n, device="cuda")
             rs = ReferenceSynchroniser(n, rank, world)
             s = stream.cuda_stream
+            sampler = ClockSampler(local)
+            sampler.start()
             with torch.cuda.stream(stream):
                 t_f = timed(lambda: fs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9))
                 torch.cuda.synchronize()
                 fs.check()
+                clocks = sampler.stop()
+                tl = fs.timeline()
                 t_r = timed(lambda: rs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9))
             # bytes this implementation moves through one GPU's HBM: replicas 3k, central model and its momentum 4, plus the
             # exchange (one-shot: G partials written and read; two-shot with owner-apply: partials once in, once out, 3/G)
             extra = 0.0 if world == 1 else (2.0 * world if not fs.two_shot else (3.0 / world if fs.owner_apply else 4.0))
             hbm = 4.0 * n * (3 * k + 4 + extra)
             link = 4.0 * n * ((world - 1) if not fs.two_shot else 2.0 * (world - 1) / world) if world > 1 else 0.0
-            t_roof = max(hbm / (bw * 1e3), link / (nvlink * 1e3))            # microseconds
+            roof = lambda gbs: max(hbm / (bw * 1e3), link / (gbs * 1e3)) if gbs else hbm / (bw * 1e3)     # microseconds
+            t_meas, t_nom = roof(peer_gbs), roof(NOMINAL_LINK if world > 1 else None)
             if rank == 0:
                 print(json.dumps({"op": "sma_sync", "n": n, "replicas": k, "gpus": world, "two_shot": fs.two_shot, "owner_apply": bool(fs.owner_apply and world > 1),
                                   "fused_us": round(t_f, 2), "reference_us": round(t_r, 2), "speedup": round(t_r / t_f, 2),
-                                  "roofline_us": round(t_roof, 2), "fraction_of_roofline": round(t_roof / t_f, 3),
-                                  "hbm_bytes": hbm, "nvlink_bytes_per_gpu": link, "peaks": how}), flush=True)
+                                  "release_us": round(tl["release_us"], 2),
+                                  "peer_store_gbs": round(peer_gbs, 1) if peer_gbs else None,
+                                  "roofline_us_measured_link": round(t_meas, 2), "fraction_of_roofline_measured_link": round(t_meas / t_f, 3),
+                                  "roofline_us_900": round(t_nom, 2), "fraction_of_roofline_900": round(t_nom / t_f, 3),
+                                  "hbm_bytes": hbm, "nvlink_bytes_per_gpu": link, "hbm_peak": how, "clocks": clocks}), flush=True)
             fs.close()
             del ws, ps, z, zl
             torch.cuda.empty_cache()

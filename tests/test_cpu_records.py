@@ -202,3 +202,24 @@ def test_record_file_and_double_buffer(tmp_path):
     assert np.allclose(x[0].numpy(), first)
     ds.close()
     ds2.close()
+
+
+def test_crop_plan_follows_the_reference_sampler():
+    """Training crops: aspect ratio in [0.75, 1.33], area in [5 %, 100 %] of the image, inside the image, covering part of a
+    labelled box; heights are spread over the whole admissible range (the reference draws the HEIGHT uniformly,
+    image/image.c:838-860).  Test crops: the centred square of side min(W, H) / 1.145."""
+    from crossbow_b200.data.records import crop_plan
+    W, H = 320, 240
+    hs, flips = [], 0
+    for seed in range(400):
+        x0, y0, cw, ch, flip = crop_plan(W, H, [[0.25, 0.25, 0.75, 0.75]], True, seed)
+        assert 0 <= x0 and 0 <= y0 and x0 + cw <= W and y0 + ch <= H and cw >= 1 and ch >= 1
+        if (cw, ch) != (W, H):
+            assert 0.05 * W * H - 1 <= cw * ch <= W * H and 0.74 <= cw / ch <= 1.35
+            ix = max(0, min(x0 + cw, 240) - max(x0, 80)); iy = max(0, min(y0 + ch, 180) - max(y0, 60))
+            assert ix * iy / (cw * ch) >= 0.1
+        hs.append(ch)
+        flips += flip
+    assert min(hs) < 0.45 * H and max(hs) > 0.9 * H and 120 < flips < 280
+    assert crop_plan(W, H, [], False, 0) == ((W - 210) // 2, (H - 210) // 2, 210, 210, 0)
+    assert crop_plan(W, H, [], True, 5) == crop_plan(W, H, [], True, 5)           # a function of the seed

@@ -26,7 +26,7 @@ def _args(M, Cc, relu, seed):
     return x, dy, y, mean.contiguous(), invstd.contiguous(), gamma
 
 
-@pytest.mark.parametrize("M,Cc,relu", [(4096, 64, 1), (1000, 20, 0), (8192, 16, 1)])
+@pytest.mark.parametrize("M,Cc,relu", [(4096, 64, 1), (1000, 20, 0), (8192, 16, 1), (512, 4096, 1), (300, 4095, 0)])
 def test_static_scratch_entry_point_matches_regular(M, Cc, relu):
     from crossbow_b200.ops import lib as L
     lib = L.load()
