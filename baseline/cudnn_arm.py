@@ -130,7 +130,7 @@ class Replica:
 def run(args, cfg, json_out):
     """Stand-alone arm (`bench.py --impl cudnn`): measure, print the JSON line, leave the process group."""
     import torch.distributed as dist
-    out = measure(args, cfg)
+    out = measure(args, cfg, getattr(args, "min_seconds", 0.0))
     if int(os.environ.get("RANK", 0)) == 0:
         print(json_out(out))
     if dist.is_initialized():
@@ -150,7 +150,8 @@ def measure(args, cfg, min_seconds=0.0):
     torch.cuda.set_device(local)
     if world > 1 and not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl")
+        import datetime
+        dist.init_process_group("nccl", timeout=datetime.timedelta(seconds=180))
     k, batch = args.replicas or cfg["replicas"], args.batch or cfg["batch"]
     build = {"resnet32": resnet32, "resnet50": resnet50}.get(args.model)
     if build is None:

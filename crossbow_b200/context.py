@@ -108,7 +108,7 @@ class ExecutionContext:
                                     use_tc=sys.use_tensor_cores, fused_sync=sys.fused_sync,
                                     sync_timeout_s=sys.sync_timeout, splits=mc.splits, reuse_memory=sys.reuse_memory,
                                     gradient_buckets=sys.gradient_buckets, debug_canaries=sys.debug_canaries,
-                                    overlap_sync=sys.overlap_sync)
+                                    overlap_sync=sys.overlap_sync, operator_branches=sys.operator_branches)
         else:
             from .engine import CpuEngine
             self.engine = CpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,
@@ -219,6 +219,7 @@ class ExecutionContext:
         wpc = self.clock.wpc
         ci = self.sys.checkpoint_interval if self.sys.checkpoint_directory else 0
         done = 0
+        tuned_tasks, tuned_time = 0, 0.0                    # since the last auto-tuner decision
         stop = threading.Event()
         period = max(0.01, min(0.2, self.sys.monitor_interval / 1000.0 if self.sys.monitor_interval > 0 else 0.2))
 
@@ -246,8 +247,13 @@ class ExecutionContext:
                 if issued < n:
                     break                                   # target loss reached
                 if self.autotuner is not None and self.autotuner.active:
-                    self.monitor.samples.append(self._job_rate(issued * self.mc.batch_size / max(dt, 1e-9)))
-                    self._autotune(list(self.monitor.samples), rt)
+                    # one throughput sample per monitor interval, as the reference's monitor takes them
+                    # (PerformanceMonitor.java:59-104); the tuner compares the latest sample with the one before
+                    tuned_tasks, tuned_time = tuned_tasks + issued, tuned_time + dt
+                    if tuned_time >= self.sys.monitor_interval / 1000.0 or done >= ntasks:
+                        self.monitor.samples.append(self._job_rate(tuned_tasks * self.mc.batch_size / max(tuned_time, 1e-9)))
+                        self._autotune(list(self.monitor.samples), rt)
+                        tuned_tasks, tuned_time = 0, 0.0
                 if ci > 0 and rt.tasks_issued() % wpc == 0 and rt.clock() % ci == 0:
                     self.checkpoint()
         finally:

@@ -86,6 +86,8 @@ struct XbProgram {
   int launches = 0;       // kernel launches issued by one replay (for accounting)
   int use_tc = 1;         // allow tensor-core convolution kernels
   int* tc_status = nullptr;
+  std::vector<cudaEvent_t> capture_events;   // fork / join events of a capture with operator branches (live only during it)
+  cudaStream_t side_stream = nullptr;
 };
 
 static inline XbConvGeom geom_of(const XbOp& o) {
@@ -263,16 +265,69 @@ XB_API int xb_program_run_range(XbProgram* p, int first, int last, cudaStream_t 
   return 0;
 }
 
+// Operator branches inside a task.  An operator flagged XB_OP_SIDE does not feed the operators that follow it in the list:
+// the weight (and bias) gradient of a layer is only read by the optimiser at the end of the task, while the chain
+// data gradient -> normalisation backward -> data gradient ... is what the task's latency consists of.  When the program
+// is captured, such operators are recorded on a second stream that forks off the main one right where the operator stands
+// and joins it again in front of the next operator that reads the gradient vector (the optimiser, or the gradient-norm
+// reduction of clipping); in the CUDA graph they become a parallel branch, so the device runs them next to the main
+// chain.  (The reference has per-operator stream "branches" with event dependencies, executioncontext.c:657-671, but
+// its labelling pass is switched off and the branch factor stays 1, SubGraph.java:208-212.)  A program that is issued
+// directly, not captured, runs its operators in list order on one stream.
+constexpr int XB_OP_SIDE = 0x1000;
+static inline bool joins_side(int kind) { return kind == OP_OPTIMISER || kind == OP_GRAD_SUMSQ; }
+
+static int capture_with_branches(XbProgram* p, cudaStream_t st) {
+  cudaStream_t side = nullptr;
+  std::vector<cudaEvent_t> events;
+  auto event = [&]() { cudaEvent_t ev = nullptr; cudaEventCreateWithFlags(&ev, cudaEventDisableTiming); events.push_back(ev); return ev; };
+  int e = 0;
+  bool open = false;
+  auto join = [&]() -> int {
+    if (!open) return 0;
+    cudaEvent_t ev = event();
+    XB_CUDA_CHECK(cudaEventRecord(ev, side));
+    XB_CUDA_CHECK(cudaStreamWaitEvent(st, ev, 0));
+    open = false;
+    return 0;
+  };
+  for (size_t i = 0; i < p->ops.size() && e == 0; ++i) {
+    const XbOp& o = p->ops[i];
+    if (o.flags & XB_OP_SIDE) {
+      if (!side && cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess) { e = -XB_BAD_ARG; break; }
+      cudaEvent_t ev = event();                                  // fork: everything issued on the main stream so far
+      if ((e = (int)cudaEventRecord(ev, st)) != 0) break;
+      if ((e = (int)cudaStreamWaitEvent(side, ev, 0)) != 0) break;
+      open = true;
+      e = run_op_traced(p, o, side);
+      if (e != 0) e = (int)(1000 * (i + 1) + (e < 0 ? -e : e));
+      continue;
+    }
+    if (joins_side(o.kind) && (e = join()) != 0) break;
+    e = run_op_traced(p, o, st);
+    if (e != 0) e = (int)(1000 * (i + 1) + (e < 0 ? -e : e));
+  }
+  if (e == 0) e = join(); else join();                             // a capture can only end with every branch joined
+  p->capture_events = events;                                      // destroyed with the program (after the capture has ended)
+  p->side_stream = side;
+  return e;
+}
+
 // Record the program into a CUDA graph (the stream must not be the legacy default stream).
 XB_API int xb_program_capture_segments(XbProgram* p, cudaStream_t st);
 XB_API int xb_program_capture(XbProgram* p, cudaStream_t st) {
   if (p->marks > 0) return xb_program_capture_segments(p, st);
   if (p->exec) { cudaGraphExecDestroy(p->exec); p->exec = nullptr; }
   if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
+  bool branches = false;
+  for (const XbOp& o : p->ops) branches |= (o.flags & XB_OP_SIDE) != 0;
   XB_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-  int e = xb_program_run(p, st);
+  int e = branches ? capture_with_branches(p, st) : xb_program_run(p, st);
   cudaGraph_t g = nullptr;
   cudaError_t ce = cudaStreamEndCapture(st, &g);
+  for (cudaEvent_t ev : p->capture_events) cudaEventDestroy(ev);
+  p->capture_events.clear();
+  if (p->side_stream) { cudaStreamDestroy(p->side_stream); p->side_stream = nullptr; }
   if (e != 0) { if (g) cudaGraphDestroy(g); return e; }
   if (ce != cudaSuccess) return (int)ce;
   p->graph = g;

@@ -71,7 +71,7 @@ class Learner:
         self.low_train = Lowering(e.train_graph, e.model, e.batch, e.input_chw, e.device, self.rep.w, self.rep, e.shared,
                                   self.params_dev, params_host, result_dev, update_model=e.update_model, training=True,
                                   use_tc=e.use_tc, clip=e.solver.clip_gradient_threshold >= 0, lr_mult=e.lr_mult, splits=e.splits, reuse_memory=e.reuse_memory,
-                                  gradient_buckets=e.gradient_buckets, canaries=e.debug_canaries)
+                                  gradient_buckets=e.gradient_buckets, canaries=e.debug_canaries, operator_branches=e.operator_branches)
         ops = self.low_train.op_array()
         self.prog_train = lib.xb_program_create(ops, len(ops), int(e.use_tc), e.tc_status.data_ptr())
         self.prog_test = None
@@ -127,7 +127,7 @@ class GpuEngine:
                  rank: int = 0, world: int = 1, device_index: int = 0, use_tc: bool = True, use_graphs: bool = True,
                  seed: int = 0, fused_sync: bool = True, two_shot: Optional[bool] = None, sync_timeout_s: float = 5.0,
                  splits: int = 1, reuse_memory: bool = False, gradient_buckets: int = 0,
-                 debug_canaries: bool = False, overlap_sync: bool = True):
+                 debug_canaries: bool = False, overlap_sync: bool = True, operator_branches: bool = True):
         """`overlap_sync`: model averaging on several GPUs - the learners' next tasks start as soon as their replicas have
         been corrected (the kernel's release word), under the cross-GPU exchange and the central update; off = they wait
         for the whole synchronisation.
@@ -144,6 +144,7 @@ class GpuEngine:
         self.batch, self.input_chw, self.solver, self.update_model = batch, tuple(input_chw), solver, update_model
         self.splits = max(1, int(splits))
         self.reuse_memory = bool(reuse_memory)
+        self.operator_branches = bool(operator_branches)   # weight gradients on a parallel branch of the task graph
         self.debug_canaries = bool(debug_canaries)      # guard words behind every activation buffer, checked in finish()
         nb = int(gradient_buckets) if gradient_buckets else (4 if model.device_elements * 4 >= (32 << 20) else 1)
         self.gradient_buckets = min(8, nb) if (fused_sync and update_model == UpdateModel.WORKER) else 1

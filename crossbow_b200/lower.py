@@ -155,7 +155,11 @@ class Lowering:
                  result_dev_ptr: int,
                  update_model: UpdateModel = UpdateModel.SMA, training=True, use_tc=True, clip=False,
                  lr_mult: Optional[torch.Tensor] = None, seed_stream_base=0, splits: int = 1, reuse_memory: bool = False,
-                 gradient_buckets: int = 1, canaries: bool = False):
+                 gradient_buckets: int = 1, canaries: bool = False, operator_branches: bool = True):
+        """`operator_branches`: put every layer's weight / bias gradient on a parallel branch of the task graph (they are
+        only read by the optimiser), so that the backward pass's critical path is the chain of data gradients alone.  Off
+        with `reuse_memory` (buffer lifetimes are derived from the list order) and with gradient buckets (their segments
+        are cut where the optimiser steps stand)."""
         if splits < 1 or batch % splits:
             raise ValueError("error: the batch size must be a multiple of the number of splits")
         # `--splits` (taskhandler.c:65-114): one task runs the whole graph `splits` times over consecutive sub-batches of
@@ -173,6 +177,8 @@ class Lowering:
         self.all_tensors: List[T] = []
         self.reuse_memory = reuse_memory
         self.gradient_buckets = gradient_buckets
+        self.side = L.F_SIDE if (operator_branches and training and not reuse_memory
+                                 and not (gradient_buckets > 1 and update_model == UpdateModel.WORKER)) else 0
         self.buckets: List[tuple] = []      # (offset, elements) of each gradient bucket, in the order the backward pass completes them
         self.bytes_before_reuse = 0
         self.ops: List[L.XbOp] = []
@@ -629,9 +635,10 @@ class Lowering:
                 scratch = info.get("im2col") if (tc and L.load().xb_conv_im2col_wanted(self._geom_struct(geom), 2)) else None
                 # 0x20: the layer's forward pass went through the same patch matrix and left it in the scratch
                 keep = 0x20 if (scratch is not None and L.load().xb_conv_im2col_wanted(self._geom_struct(geom), 0)) else 0
-                self.emit(_op(L.OP_CONV_WGRAD, tc | keep, ia=geom, p=[dy, x.buf, self.wptr(wv, rep.g), scratch]))
+                # (weight and bias gradients feed nothing but the optimiser: a parallel branch of the task graph)
+                self.emit(_op(L.OP_CONV_WGRAD, tc | keep | self.side, ia=geom, p=[dy, x.buf, self.wptr(wv, rep.g), scratch]))
                 if len(k.variables) > 1:
-                    self.emit(_op(L.OP_COLSUM, ia=[out.rows, out.c], p=[dy, self.wptr(k.variables[1], rep.g)]))
+                    self.emit(_op(L.OP_COLSUM, self.side, ia=[out.rows, out.c], p=[dy, self.wptr(k.variables[1], rep.g)]))
                 if x.needs_grad:
                     gx, acc = self.gout(x)
                     K, R, S, Cc = geom[4], geom[5], geom[6], geom[3]

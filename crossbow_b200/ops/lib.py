@@ -62,6 +62,7 @@ class XbSolverState(C.Structure):
  OP_SOFTMAX_XENT, OP_CLASSIFY, OP_TRANSPOSE_W, OP_GRAD_SUMSQ, OP_OPTIMISER, OP_COPY, OP_MATFACT, OP_MARK) = range(27)
 
 F_RELU, F_ACCUM, F_STATS, F_TC = 1, 2, 4, 0x100
+F_SIDE = 0x1000          # operator runs on a parallel branch of the captured task graph (csrc/runtime/program.cu)
 
 _lib: Optional[C.CDLL] = None
 

@@ -124,6 +124,38 @@ def main():
         dist.barrier()
     for a, b in zip(outs[0], outs[1]):
         assert torch.isfinite(a).all() and float((a - b).abs().max()) <= 3e-4 * float(a.abs().max()) + 1e-9, float((a - b).abs().max())
+    # the auto-tuner takes ONE decision for the job: every rank sees the same (summed) throughput sample, so all ranks add
+    # and remove replicas together
+    from crossbow_b200 import Dataflow, ModelConf, SystemConf
+    from crossbow_b200.context import ExecutionContext
+    from crossbow_b200.data import SyntheticDataset
+    from crossbow_b200.models import build
+    sysc, mc = SystemConf.reset(), ModelConf.reset()
+    sysc.setGPU(True).setCPU(False).setNumberOfGpuModels(1).setDisplayInterval(0)
+    sysc.autotune_models, sysc.autotune_threshold, sysc.monitor_interval = True, -1.0, 1
+    sv = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.01).setMomentum(0.9).setAlpha(0.1)
+    mc.setBatchSize(16).setWpc(2 * world).setUpdateModel("SMA")
+    mc.setDataset(Phase.TRAIN, SyntheticDataset([1, 28, 28], 10, 16, batches=8 * world, seed=1, distribution="uniform"))
+    spec = build("lenet-caffe", solver_conf=sv)
+    ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), None], quiet=True)
+    ctx.init()
+    assert ctx.world == world and ctx.clock.wpc == 2          # --wpc counts the job's tasks
+    ctx.train(16 * world, "tasks")
+    ctx.train(16 * world, "tasks")
+    ctx.autotuner.threshold = 1e9
+    ctx.train(16 * world, "tasks")
+    mine = torch.tensor([ctx.engine.k, int(ctx.autotuner.active), len(ctx.autotune_trace)] + [k for k, _ in ctx.autotune_trace][:6], device="cuda")
+    alls = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(alls, mine)
+    assert all(torch.equal(alls[0], t) for t in alls), [t.tolist() for t in alls]
+    ks = [k for k, _ in ctx.autotune_trace]
+    assert not ctx.autotuner.active and max(ks) >= 3 and ctx.engine.k == max(ks) - 1 == ks[-1], (ctx.engine.k, ctx.autotune_trace)
+    assert ctx.tasks_done == 48                                # this rank's share of 3 x 16 x world job tasks
+    zs = [torch.empty_like(ctx.engine.shared.z) for _ in range(world)]
+    dist.all_gather(zs, ctx.engine.shared.z.clone())
+    assert all(torch.equal(zs[0], t) for t in zs), "central models diverged across ranks (context, auto-tuned)"
+    ctx.destroy()
+    dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK", world)
     dist.destroy_process_group()

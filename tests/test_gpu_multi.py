@@ -18,4 +18,7 @@ def test_fused_sync_and_training_across_gpus():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", str(29700 + os.getpid() % 200), os.path.join(ROOT, "tests", "multi_gpu_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    if r.returncode != 0:                      # (shown by pytest with the failure; the assertion message itself is truncated)
+        print(r.stdout[-3000:])
+        print(r.stderr[-12000:])
     assert r.returncode == 0 and "MULTI_GPU_OK" in r.stdout, (r.stdout[-1500:], r.stderr[-3000:])

@@ -234,3 +234,34 @@ def test_full_size_models_run():
             assert all(np.isfinite(losses)) and all(l >= 0 for l in losses), losses
         finally:
             gpu.destroy()
+
+
+@pytest.mark.parametrize("name,use_tc", [("lenet-caffe", False), ("resnet8", True)])
+def test_operator_branches_change_nothing_but_the_schedule(name, use_tc):
+    """Weight / bias gradients on a parallel branch of the task graph (joined in front of the optimiser) against the same
+    program captured as one chain: same losses and weights up to the rounding of the atomic gradient sums."""
+    from crossbow_b200.engine import GpuEngine
+    from helpers import build_model
+    import copy
+    spec, m, solver = build_model(name, 8)
+    xs, ys = make_batches(spec, 8, 6, seed=5)
+    outs = []
+    for branches in (False, True):
+        eng = GpuEngine(spec.train, spec.test, m, m.initial_values(7), 8, spec.input_shape, copy.deepcopy(solver), UpdateModel.SMA, replicas=2,
+                        wpc=2, use_tc=use_tc, operator_branches=branches)
+        side = sum(1 for o in eng.learners[0].low_train.ops if o.flags & 0x1000)
+        assert (side > 0) == branches
+        losses = []
+        try:
+            for t in range(0, 6, 2):
+                eng.submit(0, xs[t].pin_memory(), ys[t].pin_memory(), t, Phase.TRAIN)
+                eng.submit(1, xs[t + 1].pin_memory(), ys[t + 1].pin_memory(), t + 1, Phase.TRAIN)
+                losses += [eng.wait(0)[0], eng.wait(1)[0]]
+                eng.synchronise()
+            eng.finish()
+            outs.append((losses, eng.central_model(), eng.replica_model(1)))
+        finally:
+            eng.destroy()
+    (la, za, ra), (lb, zb, rb) = outs
+    assert np.allclose(la, lb, rtol=2e-3, atol=1e-5)
+    assert np.abs(za - zb).max() <= 2e-3 * np.abs(za).max() and np.abs(ra - rb).max() <= 2e-3 * np.abs(ra).max()
