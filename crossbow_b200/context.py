@@ -141,6 +141,7 @@ class ExecutionContext:
                                  result_slots=sys.number_of_result_slots, task_handlers=handlers,
                                  callback_handlers=max(1, sys.number_of_callback_handlers), task_timeout_s=sys.task_timeout)
         self._native = mk(self.clock.wpc)
+        self._native.set_scheduling_policy(sys.scheduling_policy)
         self._native.set_executor(sub, wait, sync, batch, ctx)
         if sys.run_ahead > 1:
             # the next task of a replica is handed to the device while the previous one is still running

@@ -180,20 +180,22 @@ class MpmcQueue {
 //        here: skip cost = sum over skipped tasks of 1 / matrix[other][graph] >= 1 / matrix[p][graph].
 //   NONE: never hands out a task (the reference's NULL policy).
 // Tasks may carry the replica they are bound to and the oldest clock they accept (-1 / 0 = any), the reference's
-// select() filter.  Not on a hot path here (the native scheduler hands tasks straight to learners): a mutex is enough.
+// select() filter.  The native scheduler uses it between the dispatcher and its task handlers when scheduling is queued
+// (--direct-scheduling false); a task costs microseconds to hand over against hundreds to run, so a mutex is enough.
 class PolicyTaskQueue {
  public:
   enum Policy { HLS = 0, FIFO = 1, NONE = 2 };
   struct Task { long long id; int graph; int replica; long long clock; };
   explicit PolicyTaskQueue(int policy) : policy_(policy) {}
+  void set_policy(int policy) { std::lock_guard<std::mutex> g(mu_); policy_ = policy; }
   void push(long long id, int graph, int replica, long long clock) {
     std::lock_guard<std::mutex> g(mu_);
     q_.push_back(Task{id, graph, replica, clock});
   }
   // matrix: [2][graphs] tasks per second; returns the task id or -1
   long long poll(int p, const int* matrix, int graphs, int replica, long long clock) {
-    if (policy_ == NONE) return -1;
     std::lock_guard<std::mutex> g(mu_);
+    if (policy_ == NONE) return -1;
     const int other = (p + 1) % 2;
     double skip_cost = 0.0;
     for (auto it = q_.begin(); it != q_.end(); ++it) {

@@ -74,7 +74,7 @@ class Runtime {
           double task_timeout_s)
       : theta_(learners), wpc_(wpc), slack_(slack), sync_model_(sync_model), nslots_(result_slots), slots_(new ResultSlot[result_slots]),
         n_task_handlers_(task_handlers), n_callback_handlers_(callback_handlers < 1 ? 1 : callback_handlers), timeout_(task_timeout_s),
-        task_q_(4096), cb_q_(4096) {
+        cb_q_(4096) {
     for (int i = 0; i < nslots_; ++i) slots_[i].state.store(0);
     for (int i = 0; i < ThetaQueue::kMaxSlots; ++i) { replica_clock_[i].store(0); replica_updates_[i].store(0); busy_since_[i].store(0.0); inflight_[i].store(0); }
     memset(&exec_, 0, sizeof(exec_));
@@ -96,6 +96,7 @@ class Runtime {
     exec_.wait_task = wait_task;
   }
   void set_data_source(decltype(Executor::take) take, decltype(Executor::release) release, void* dctx) { exec_.take = take; exec_.release = release; exec_.dctx = dctx; }
+  void set_policy(int policy) { policy_q_.set_policy(policy); }
   void set_target_loss(float t) { target_loss_ = t; }
   void set_affinity(int first_core) { first_core_ = first_core; }
 
@@ -126,7 +127,12 @@ class Runtime {
       } else if (exec_.batch && exec_.batch(exec_.ctx, task, phase, &ex, &lab) != 0) return fail("data set could not provide a batch");
       TaskItem it{task, learner, phase, ex, lab, slot};
       if (n_task_handlers_ > 0) {
-        if (!push_bounded(task_q_, it)) return fail("task queue stayed full");
+        // queued scheduling (ExecutionContext.java:272-277 with --direct-scheduling false): the task waits in the policy
+        // queue until a task handler takes it according to --scheduling-policy
+        auto t0 = Clock::now(); unsigned spins = 0;
+        while (policy_q_.size() >= kPending) { cpu_relax(++spins); if (failed_.load() || seconds_since(t0) > timeout_) return fail("task queue stayed full"); }
+        pending_[task % kPending] = it;
+        policy_q_.push((long long)task, phase, -1, 0);
       } else {
         if (!issue(it)) return -1;
       }
@@ -273,9 +279,10 @@ class Runtime {
   }
   void task_loop() {
     unsigned spins = 0;
-    TaskItem it;
     while (running_.load()) {
-      if (task_q_.pop(it)) { spins = 0; if (!failed_.load()) issue(it); handed_.fetch_add(1); }
+      // this process drives one GPU: it polls as processor 1 of the policy's two (0 = CPU workers, 1 = GPU worker)
+      const long long id = policy_q_.poll(1, nullptr, 1, -1, (long long)1 << 62);
+      if (id >= 0) { spins = 0; TaskItem it = pending_[(uint64_t)id % kPending]; if (!failed_.load()) issue(it); handed_.fetch_add(1); }
       else cpu_relax(++spins);
     }
   }
@@ -355,7 +362,10 @@ class Runtime {
   double timeout_;
   int first_core_ = -1;
   Executor exec_;
-  MpmcQueue<TaskItem> task_q_, cb_q_;
+  static constexpr uint64_t kPending = 4096;
+  MpmcQueue<TaskItem> cb_q_;
+  PolicyTaskQueue policy_q_{PolicyTaskQueue::FIFO};   // dispatcher -> task handlers, ordered by --scheduling-policy
+  std::vector<TaskItem> pending_ = std::vector<TaskItem>(kPending);   // the queued tasks' payloads, by task number
   std::atomic<uint64_t> next_task_{0}, completed_{0}, collected_{0}, handed_{0}, clock_{0};
   std::atomic<uint64_t> replica_clock_[ThetaQueue::kMaxSlots];
   std::atomic<uint64_t> replica_updates_[ThetaQueue::kMaxSlots];
@@ -397,6 +407,7 @@ RT_API void rt_set_data_source(void* r, void* take, void* release, void* dctx) {
   ((Runtime*)r)->set_data_source((decltype(Executor::take))take, (decltype(Executor::release))release, dctx);
 }
 RT_API void rt_set_run_ahead(void* r, int depth, void* wait_task) { ((Runtime*)r)->set_run_ahead(depth, (decltype(Executor::wait_task))wait_task); }
+RT_API void rt_set_scheduling_policy(void* r, int policy) { ((Runtime*)r)->set_policy(policy); }
 RT_API void rt_set_target_loss(void* r, float t) { ((Runtime*)r)->set_target_loss(t); }
 RT_API void rt_set_affinity(void* r, int first_core) { ((Runtime*)r)->set_affinity(first_core); }
 RT_API long long rt_train(void* r, long long ntasks, int phase) { return ((Runtime*)r)->train(ntasks, phase); }

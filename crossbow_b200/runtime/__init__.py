@@ -27,6 +27,7 @@ def load() -> C.CDLL:
     _sig(lib, "rt_destroy", None, P)
     _sig(lib, "rt_set_executor", None, P, P, P, P, P, P)
     _sig(lib, "rt_set_target_loss", None, P, C.c_float)
+    _sig(lib, "rt_set_scheduling_policy", None, P, I)
     _sig(lib, "rt_set_run_ahead", None, P, I, P)
     _sig(lib, "rt_set_affinity", None, P, I)
     _sig(lib, "rt_train", L, P, L, I)
@@ -231,6 +232,13 @@ class Runtime:
 
     def stop(self):
         self.lib.rt_stop(self.h)
+
+    def set_scheduling_policy(self, policy):
+        """Order in which the task handlers take queued tasks (``--scheduling-policy``: FIFO, HLS or NULL); only matters
+        when tasks are queued, i.e. with task handlers."""
+        from ..types import SchedulingPolicy
+        p = SchedulingPolicy.from_string(policy) if isinstance(policy, str) else policy
+        self.lib.rt_set_scheduling_policy(self.h, int(p))
 
     def set_target_loss(self, t: float):
         self.lib.rt_set_target_loss(self.h, t)

@@ -258,3 +258,26 @@ def test_results_are_displayed_while_training_runs_and_none_are_lost():
     # lines appeared while training was in progress, not after it
     early = [t for t, _ in lines if t < t_end - 0.5 * (t_end - lines[0][0])]
     assert len(early) > 5
+
+
+def test_scheduling_policy_orders_the_queued_tasks():
+    """With task handlers (queued scheduling) the dispatcher's tasks pass through the policy queue: FIFO and HLS hand them
+    to the handlers, the NULL policy never does, so nothing runs and the run is reported as stuck."""
+    from crossbow_b200.runtime import Runtime, RuntimeError_
+    for policy in ("FIFO", "HLS"):
+        rt = Runtime(learners=3, wpc=3, task_handlers=2, callback_handlers=2, task_timeout_s=5.0)
+        rt.attach_fake(3, task_us=20)
+        rt.set_scheduling_policy(policy)
+        assert rt.train(300) == 300
+        rt.drain(20.0)
+        assert rt.tasks_completed() == 300 and rt.clock() == 100 and rt.fake_syncs() == 100
+        assert [t for t, _, _ in rt.history(300)] == list(range(300))
+        rt.close()
+    rt = Runtime(learners=2, wpc=2, task_handlers=1, callback_handlers=1, task_timeout_s=0.5)
+    rt.attach_fake(2, task_us=0)
+    rt.set_scheduling_policy("NULL")
+    with pytest.raises(RuntimeError_):
+        rt.train(8)
+        rt.drain(2.0)
+    assert rt.tasks_completed() == 0
+    rt.close()
