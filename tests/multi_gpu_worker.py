@@ -79,12 +79,12 @@ def main():
     # model averaging overlapped with the next tasks (the learners follow the kernel's release word) against the serialised
     # order (they wait for the whole synchronisation): same arithmetic, so the weights must be bit-identical
     import copy as _copy
-    spec, m, solver = build_model("resnet8", 8)
+    spec, m, solver = build_model("lenet-caffe", 8)          # well conditioned: rounding noise is not amplified
     xs, ys = make_batches(spec, 8, 12, seed=200 + rank)
     finals = []
     for overlap in (False, True):
         eng = GpuEngine(spec.train, None, m, m.initial_values(7), 8, spec.input_shape, _copy.deepcopy(solver), UpdateModel.SMA, replicas=2,
-                        wpc=2, rank=rank, world=world, device_index=local, use_tc=True, overlap_sync=overlap)
+                        wpc=2, rank=rank, world=world, device_index=local, use_tc=False, overlap_sync=overlap)
         assert eng.overlap_sync == overlap
         for t in range(0, 12, 2):                     # both learners in flight, nothing waits on the host between clocks
             eng.submit(0, xs[t].pin_memory(), ys[t].pin_memory(), t, Phase.TRAIN)
@@ -97,9 +97,10 @@ def main():
         finals.append([eng.shared.z.clone()] + [l.rep.w.clone() for l in eng.learners])
         eng.destroy()
         dist.barrier()
-    # (batch-norm sums are accumulated with atomics, so two runs agree to rounding, not to the bit)
+    # (gradient sums are accumulated with atomics, so two runs agree to rounding, not to the bit; a task that started
+    # before its replica was corrected would be off by the size of the correction, orders of magnitude more)
     for a, b in zip(*finals):
-        assert torch.isfinite(a).all() and float((a - b).abs().max()) <= 2e-3 * float(a.abs().max()) + 1e-9, float((a - b).abs().max())
+        assert torch.isfinite(a).all() and float((a - b).abs().max()) <= 3e-4 * float(a.abs().max()) + 1e-9, float((a - b).abs().max())
     # synchronous SGD with gradient buckets (owner-apply exchange per bucket, overlapping the backward pass) against one
     # synchronisation per clock; both learners of a rank run concurrently
     import copy
