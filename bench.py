@@ -70,6 +70,7 @@ def measure_ours(args, model_name, steps, warmup, k=0, batch=0, min_seconds=1.0)
     sysc.fused_sync = args.sync == "fused"
     sysc.overlap_sync = not args.no_overlap
     sysc.operator_branches = not args.no_branches
+    sysc.nvls_sync = args.nvls
     solver = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.1).setMomentum(0.9) \
         .setWeightDecay(1e-4).setAlpha(0.1)
     # work per clock counts the job's tasks: every replica of every GPU runs one task between two synchronisations
@@ -215,6 +216,7 @@ def measure_ours(args, model_name, steps, warmup, k=0, batch=0, min_seconds=1.0)
                    "optimizer": "momentum 0.9, wd 1e-4, lr 0.1", "sync": args.sync,
                    "sync_overlap": bool(getattr(eng, "overlap_sync", False)),
                    "operator_branches": bool(getattr(eng, "operator_branches", False)),
+                   "nvls": bool(getattr(eng.synchroniser, "nvls", False)),
                    "l2": f"no explicit flush: per-step working set {arena_mb:.0f} MB of activations/gradients exceeds the 126 MB L2"
                          if arena_mb > 252 else f"working set {arena_mb:.0f} MB",
                    "cuda_graphs": eng.use_graphs},
@@ -251,6 +253,7 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="the learners wait for the whole synchronisation (no early release)")
     ap.add_argument("--no-branches", action="store_true", help="weight gradients stay on the task's main chain (no parallel branch in the task graph)")
+    ap.add_argument("--nvls", action="store_true", help="two-shot exchange through NVLink multicast (multimem) instead of peer stores")
     ap.add_argument("--no-library-arm", action="store_true", help="skip the library (cuDNN) arm that gives vs_baseline")
     ap.add_argument("--no-resnet50", action="store_true", help="skip the nested ResNet-50 run of the default benchmark")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="repeat the timed block until this much has been measured")

@@ -108,7 +108,7 @@ class ExecutionContext:
                                     use_tc=sys.use_tensor_cores, fused_sync=sys.fused_sync,
                                     sync_timeout_s=sys.sync_timeout, splits=mc.splits, reuse_memory=sys.reuse_memory,
                                     gradient_buckets=sys.gradient_buckets, debug_canaries=sys.debug_canaries,
-                                    overlap_sync=sys.overlap_sync, operator_branches=sys.operator_branches)
+                                    overlap_sync=sys.overlap_sync, operator_branches=sys.operator_branches, nvls_sync=sys.nvls_sync)
         else:
             from .engine import CpuEngine
             self.engine = CpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,

@@ -6,7 +6,10 @@
 // (operator, device) shared by all replicas on that device, as in the reference
 // (clib-multigpu/kernels/cudnnbatchnorm.cu:99-151, cudnn/cudnnbatchnormparams.c:91-100).
 // Backward is (1) per-channel sums of dz and dz*xhat, (2) dx (+ residual gradient) and dgamma/dbeta
-// (cudnnbatchnormgradient.cu:77-93).  dz = dy masked by the fused ReLU.
+// (cudnnbatchnormgradient.cu:77-93).  dz = dy masked by the fused ReLU.  The mask comes from one of three places: the
+// layer's output y (> 0); x itself, re-normalised with the forward pass's own expressions (no residual input); or a
+// packed sign mask the forward pass wrote next to y - one byte per four channels, a sixteenth of y's size - which is what
+// layers with a residual input use, so that neither backward pass reads y.
 //
 // Thread mapping: a thread keeps the same 4 channels for its whole life ("column-persistent"), so the per-channel
 // constants are computed once and rows are streamed with 16-byte loads.
@@ -83,6 +86,7 @@ struct BnArgs {
   const XbTaskParams* tp;
   int M, C; float eps; int relu; int training; int cma; float fraction_factor;
   int rows_per_block;
+  unsigned char* mask;            // VEC == 4 only, may be null: bit e of byte (row * C + c) / 4 = (y[c + e] > 0)
 };
 
 template <int VEC>
@@ -141,6 +145,9 @@ __global__ void __launch_bounds__(NT) bn_fwd_kernel(BnArgs a) {
           v[u][e] = o;
         }
         st<VEC>(a.y + off + u * step, v[u]);
+        if constexpr (VEC == 4) {
+          if (a.mask) a.mask[(off + u * step) >> 2] = (unsigned char)((v[u][0] > 0.f) | ((v[u][1] > 0.f) << 1) | ((v[u][2] > 0.f) << 2) | ((v[u][3] > 0.f) << 3));
+        }
       }
     }
     for (; r < r_end; r += t.rows_per_iter) {
@@ -156,6 +163,9 @@ __global__ void __launch_bounds__(NT) bn_fwd_kernel(BnArgs a) {
         v[e] = o;
       }
       st<VEC>(a.y + off, v);
+      if constexpr (VEC == 4) {
+        if (a.mask) a.mask[off >> 2] = (unsigned char)((v[0] > 0.f) | ((v[1] > 0.f) << 1) | ((v[2] > 0.f) << 2) | ((v[3] > 0.f) << 3));
+      }
     }
   }
 }
@@ -165,7 +175,7 @@ struct BnBwdArgs {
   const float* save_mean; const float* save_invstd; const float* gamma;
   float* dsums;                                      // [2C]: sum dz, sum dz*xhat
   float* dx; float* dres; float* dgamma; float* dbeta;
-  int M, C; int relu; int accum_dx; int accum_dres; int rows_per_block;
+  int M, C; int relu; int accum_dx; int accum_dres; int rows_per_block;   // relu == 3: `y` is the packed sign mask (bytes)
   const float* beta;   // relu == 2: the mask is re-derived from x (fma(x, gamma*istd, beta - mean*gamma*istd) > 0) and y is not read
 };
 
@@ -181,7 +191,8 @@ __global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
     float s1[VEC], s2[VEC], mean[VEC], istd[VEC], msc[VEC], msh[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) { s1[e] = 0.f; s2[e] = 0.f; mean[e] = 0.f; istd[e] = 0.f; msc[e] = 0.f; msh[e] = 0.f; }
-    const bool from_y = a.relu == 1, from_x = a.relu == 2;
+    const bool from_y = a.relu == 1, from_x = a.relu == 2, from_m = (VEC == 4) && a.relu == 3;
+    const unsigned char* mk = reinterpret_cast<const unsigned char*>(a.y);
     if (active) {
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
@@ -195,17 +206,22 @@ __global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
       for (; r + (RU - 1) * t.rows_per_iter < r_end; r += RU * t.rows_per_iter) {
         const long long off = (long long)r * a.C + cg * VEC;
         float g[RU][VEC], xv[RU][VEC], yv[RU][VEC];
+        unsigned int mb[RU];
 #pragma unroll
-        for (int u = 0; u < RU; ++u) { ld<VEC>(a.dy + off + u * step, g[u]); ld<VEC>(a.x + off + u * step, xv[u]); }
+        for (int u = 0; u < RU; ++u) { ld<VEC>(a.dy + off + u * step, g[u]); ld<VEC>(a.x + off + u * step, xv[u]); mb[u] = 0; }
         if (from_y) {
 #pragma unroll
           for (int u = 0; u < RU; ++u) ld<VEC>(a.y + off + u * step, yv[u]);
+        }
+        if (from_m) {
+#pragma unroll
+          for (int u = 0; u < RU; ++u) mb[u] = mk[(off + u * step) >> 2];
         }
 #pragma unroll
         for (int u = 0; u < RU; ++u)
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
-            const bool off_ = from_y ? !(yv[u][e] > 0.f) : (from_x && !(__fmaf_rn(xv[u][e], msc[e], msh[e]) > 0.f));
+            const bool off_ = from_m ? !((mb[u] >> e) & 1u) : from_y ? !(yv[u][e] > 0.f) : (from_x && !(__fmaf_rn(xv[u][e], msc[e], msh[e]) > 0.f));
             float dz = off_ ? 0.f : g[u][e];
             s1[e] += dz; s2[e] += dz * (xv[u][e] - mean[e]) * istd[e];
           }
@@ -215,9 +231,10 @@ __global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
         float g[VEC], xv[VEC], yv[VEC];
         ld<VEC>(a.dy + off, g); ld<VEC>(a.x + off, xv);
         if (from_y) ld<VEC>(a.y + off, yv);
+        const unsigned int mb = from_m ? mk[off >> 2] : 0u;
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-          const bool off_ = from_y ? !(yv[e] > 0.f) : (from_x && !(__fmaf_rn(xv[e], msc[e], msh[e]) > 0.f));
+          const bool off_ = from_m ? !((mb >> e) & 1u) : from_y ? !(yv[e] > 0.f) : (from_x && !(__fmaf_rn(xv[e], msc[e], msh[e]) > 0.f));
           float dz = off_ ? 0.f : g[e];
           s1[e] += dz; s2[e] += dz * (xv[e] - mean[e]) * istd[e];
         }
@@ -249,7 +266,8 @@ __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
     int rsub = (t.col_passes == 1) ? (threadIdx.x / t.cv) : 0;
     if (cg >= t.cv || rsub >= t.rows_per_iter) continue;
     float mean[VEC], istd[VEC], k0[VEC], k1[VEC], k2[VEC], msh[VEC];
-    const bool from_y = a.relu == 1, from_x = a.relu == 2;
+    const bool from_y = a.relu == 1, from_x = a.relu == 2, from_m = (VEC == 4) && a.relu == 3;
+    const unsigned char* mk = reinterpret_cast<const unsigned char*>(a.y);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
       int c = cg * VEC + e;
@@ -265,10 +283,11 @@ __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
       float g[VEC], xv[VEC], yv[VEC], o[VEC], old[VEC];
       ld<VEC>(a.dy + off, g); ld<VEC>(a.x + off, xv);
       if (from_y) ld<VEC>(a.y + off, yv);
+      const unsigned int mb = from_m ? mk[off >> 2] : 0u;
       if (a.accum_dx) ld<VEC>(a.dx + off, old);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        const bool off_ = from_y ? !(yv[e] > 0.f) : (from_x && !(__fmaf_rn(xv[e], k0[e], msh[e]) > 0.f));
+        const bool off_ = from_m ? !((mb >> e) & 1u) : from_y ? !(yv[e] > 0.f) : (from_x && !(__fmaf_rn(xv[e], k0[e], msh[e]) > 0.f));
         float dz = off_ ? 0.f : g[e];
         g[e] = dz;
         float xhat = (xv[e] - mean[e]) * istd[e];
@@ -318,11 +337,25 @@ XB_API int xb_bn_stats(const float* x, float* sums, int M, int C, cudaStream_t s
   return (int)cudaGetLastError();
 }
 
+// `mask` (may be null; needs C % 4 == 0 and 16-byte aligned tensors): M * C / 4 bytes that receive the signs of y, four
+// channels per byte, for xb_bn_backward with relu == 3.
+XB_API int xb_bn_forward_mask(const float* x, const float* res, float* y, const float* sums, const float* gamma, const float* beta,
+                              float* run_mean, float* run_var, float* save_mean, float* save_invstd, const XbTaskParams* tp,
+                              int M, int C, float eps, int relu, int training, int cma, float fraction_factor, unsigned char* mask,
+                              cudaStream_t st);
 XB_API int xb_bn_forward(const float* x, const float* res, float* y, const float* sums, const float* gamma, const float* beta,
                          float* run_mean, float* run_var, float* save_mean, float* save_invstd, const XbTaskParams* tp,
                          int M, int C, float eps, int relu, int training, int cma, float fraction_factor, cudaStream_t st) {
-  BnArgs a{x, res, y, sums, gamma, beta, run_mean, run_var, save_mean, save_invstd, tp, M, C, eps, relu, training, cma, fraction_factor, 0};
+  return xb_bn_forward_mask(x, res, y, sums, gamma, beta, run_mean, run_var, save_mean, save_invstd, tp, M, C, eps, relu, training, cma,
+                            fraction_factor, nullptr, st);
+}
+XB_API int xb_bn_forward_mask(const float* x, const float* res, float* y, const float* sums, const float* gamma, const float* beta,
+                              float* run_mean, float* run_var, float* save_mean, float* save_invstd, const XbTaskParams* tp,
+                              int M, int C, float eps, int relu, int training, int cma, float fraction_factor, unsigned char* mask,
+                              cudaStream_t st) {
+  BnArgs a{x, res, y, sums, gamma, beta, run_mean, run_var, save_mean, save_invstd, tp, M, C, eps, relu, training, cma, fraction_factor, 0, mask};
   bool v4 = can_vec4(C, x, res, y, nullptr);
+  if (mask && !v4) return -XB_BAD_ARG;
   int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
   if (v4) bn_fwd_kernel<4><<<blocks, NT, 0, st>>>(a);
   else    bn_fwd_kernel<1><<<blocks, NT, 0, st>>>(a);
@@ -333,8 +366,10 @@ XB_API int xb_bn_forward(const float* x, const float* res, float* y, const float
 XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const float* save_mean, const float* save_invstd,
                           const float* gamma, float* dsums, float* dx, float* dres, float* dgamma, float* dbeta,
                           int M, int C, int relu, int accum_dx, int accum_dres, cudaStream_t st) {
-  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, dsums, dx, dres, dgamma, dbeta, M, C, relu ? 1 : 0, accum_dx, accum_dres, 0, nullptr};
-  bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
+  // relu: 0 none, 1 mask from y (> 0), 3 `y` is the packed sign mask written by xb_bn_forward_mask
+  BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, dsums, dx, dres, dgamma, dbeta, M, C, relu == 3 ? 3 : (relu ? 1 : 0), accum_dx, accum_dres, 0, nullptr};
+  bool v4 = can_vec4(C, dy, x, relu == 3 ? nullptr : y, dx) && (((uintptr_t)dres) % 16 == 0);
+  if (relu == 3 && !v4) return -XB_BAD_ARG;
   int blocks, rblocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, rblocks, g_bn_reduce_blocks, 8);
   if (v4) bn_bwd_reduce_kernel<4><<<rblocks, NT, 0, st>>>(a); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, st>>>(a);
   a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);

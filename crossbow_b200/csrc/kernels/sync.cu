@@ -29,6 +29,11 @@
 // for the end of the kernel: the replicas' next forward pass runs under the exchange and the central update, and a
 // learner never waits for another GPU.  The reference gets the same overlap by recording each replica's `updated`
 // event right after its correction, before the all-reduce is issued (clib-multigpu/synch/sma.c:108-118, :130).
+// NVLS variant (two-shot with owner-apply, optional): the partial sums stay in each GPU's own memory, which is bound to an
+// NVLink multicast object; the owner of a chunk reads the SUM of all GPUs' partials with one multimem.ld_reduce per 16
+// bytes (the switch fetches and adds the eight copies) and stores the new central model into every GPU with one
+// multimem.st.  That moves about 4n (1 + 1/G) bytes per direction per GPU instead of the (G-1)/G * 4n of pushed partials
+// plus (G-1)/G * 4n of unicast stores of the peer-store path, and the adds happen in the switch.  These are multimem instructions on multicast ADDRESSES; no TMA is involved.
 // The kernel also keeps a small time line per GPU (%globaltimer at entry, at the release and at the exit of its last
 // block, plus running sums), which is what the benchmarks report as synchronisation time per step.
 #include "common.cuh"
@@ -67,6 +72,9 @@ struct SyncArgs {
   unsigned int* ready2[MAXG];  // [nchunks] on every GPU: total of chunk has landed
   int* status;
   unsigned long long timeout_ns;
+  // NVLS variant: this GPU's partial buffer (2 x n floats, by epoch parity), the multicast address of the same buffer on
+  // all GPUs, and the multicast address of every GPU's central model; all null when the variant is off
+  float* part_local; const float* part_mc; float* z_mc;
   unsigned int* release;       // [0] release word (epoch once every replica of this GPU is corrected), [1] block counter; may be null
   unsigned long long* stamps;  // time line, see XB_SYNC_STAMP_*; may be null
 };
@@ -103,6 +111,18 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int ep
     }
     if (global_ns() - t0 > timeout_ns) return false;
   }
+}
+
+// sum over all GPUs of the multicast group of the 16 bytes at `mc` (in-switch reduction)
+__device__ __forceinline__ float4 multimem_ld_reduce_add(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+// the same 16 bytes stored into every GPU of the multicast group
+__device__ __forceinline__ void multimem_st(float* mc, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
 __device__ __forceinline__ float4 f4add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
@@ -281,7 +301,12 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
 #pragma unroll
       for (int u = 0; u < U; ++u) { i4[u] = (long long)c * (CHUNK / 4) + j0 + u * NT; ok[u] = i4[u] < n4; }
       local_part(a, i4, ok, acc);                         // (lanes past the end contribute zeros)
-      if (a.two_shot) {
+      if (a.part_local) {
+        // NVLS: the partial stays here; the owner will read the sum of all GPUs' copies through the switch
+        float4* dst = reinterpret_cast<float4*>(a.part_local) + ((long long)parity * a.nchunks + c) * (CHUNK / 4);
+#pragma unroll
+        for (int u = 0; u < U; ++u) dst[j0 + u * NT] = acc[u];
+      } else if (a.two_shot) {
 #pragma unroll
         for (int u = 0; u < U; ++u) reinterpret_cast<float4*>(a.inbox[owner])[off4 + j0 + u * NT] = acc[u];
       } else {
@@ -311,12 +336,18 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
       __syncthreads();
       if (tid < G && !wait_flag(a.ready1[me] + (long long)tid * a.nchunks + c, a.epoch, a.timeout_ns)) { s_fail = 1; atomicExch(a.status, XB_TIMEOUT_FLAG); }
       __syncthreads();
+      if (a.part_mc) __threadfence_system();               // the multimem loads below follow the flags observed above
       const bool ok = !s_fail;
       const long long res4 = ((long long)parity * a.nchunks + c) * (CHUNK / 4);
       for (int j0 = tid; j0 < CHUNK / 4 && ok; j0 += U * NT) {
         float4 t[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) t[u] = make_float4(0, 0, 0, 0);
+        if (a.part_mc) {
+          const float* mc = a.part_mc + ((long long)parity * a.nchunks + c) * CHUNK;
+#pragma unroll
+          for (int u = 0; u < U; ++u) t[u] = multimem_ld_reduce_add(mc + 4 * (j0 + u * NT));
+        } else
         for (int src = 0; src < G; ++src) {               // rank order: every owner adds in the same order
           const long long o4 = (((long long)parity * G + src) * slot_elems + (long long)(c / G) * CHUNK) / 4 + j0;
           float4 v[U];
@@ -360,6 +391,10 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
 #pragma unroll
             for (int u = 0; u < U; ++u) z[u] = f4add(z[u], t[u]);
           }
+          if (a.z_mc) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) if (okk[u]) multimem_st(a.z_mc + 4 * i4[u], z[u]);
+          } else
           for (int g = 0; g < G; ++g) {
 #pragma unroll
             for (int u = 0; u < U; ++u) if (okk[u]) reinterpret_cast<float4*>(a.zpeer[g])[i4[u]] = z[u];
@@ -489,6 +524,7 @@ struct XbSyncDesc {
   int* status;
   double timeout_s;
   float* zpeer[MAXG];             // every GPU's central model as seen from this process, or all null
+  float* part_local; const float* part_mc; float* z_mc;   // NVLS variant (see SyncArgs), or all null
   unsigned int* release;          // two words owned by the caller (zero-initialised once), or null: see SyncArgs::release
   unsigned long long* stamps;     // XB_SYNC_STAMP_WORDS 64-bit words owned by the caller (zero-initialised once), or null
 };
@@ -510,7 +546,10 @@ static void fill_args(SyncArgs& a, const XbSyncDesc& d) {
   a.status = d.status;
   a.timeout_ns = (unsigned long long)(d.timeout_s * 1e9);
   a.release = d.release; a.stamps = d.stamps;
+  const bool nvls = a.owner_apply && d.part_local && d.part_mc && d.z_mc;
+  a.part_local = nvls ? d.part_local : nullptr; a.part_mc = nvls ? d.part_mc : nullptr; a.z_mc = nvls ? d.z_mc : nullptr;
 }
+XB_API long long xb_sync_part_floats(long long n) { return 2LL * xb_sync_nchunks(n) * chunk_for(n); }
 
 static int sync_grid(int nchunks, int max_blocks) {
   int b = nchunks < max_blocks ? nchunks : max_blocks;

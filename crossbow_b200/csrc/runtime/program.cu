@@ -29,8 +29,8 @@ XB_API int xb_conv_wgrad_im2col(const float*, const float*, float*, const XbConv
 XB_API int xb_tc_supported(const XbConvGeom*, int which);
 XB_API int xb_transpose_weights(const float*, float*, const XbTransposeDesc*, int, int, cudaStream_t);
 XB_API int xb_bn_stats(const float*, float*, int, int, cudaStream_t);
-XB_API int xb_bn_forward(const float*, const float*, float*, const float*, const float*, const float*, float*, float*, float*, float*,
-                         const XbTaskParams*, int, int, float, int, int, int, float, cudaStream_t);
+XB_API int xb_bn_forward_mask(const float*, const float*, float*, const float*, const float*, const float*, float*, float*, float*, float*,
+                              const XbTaskParams*, int, int, float, int, int, int, float, unsigned char*, cudaStream_t);
 XB_API int xb_bn_backward_remask(const float*, const float*, const float*, const float*, const float*, const float*, float*, float*, float*, float*, int, int,
                                  int, cudaStream_t);
 XB_API int xb_bn_backward_apply(const float*, const float*, const float*, const float*, const float*, const float*, const float*, float*, float*, float*,
@@ -136,9 +136,10 @@ static int run_op(XbProgram* pr, const XbOp& o, cudaStream_t st) {
     case OP_COLSUM: return xb_colsum((const float*)o.p[0], (float*)o.p[1], o.ia[0], o.ia[1], st);
     case OP_BN_STATS: return xb_bn_stats((const float*)o.p[0], (float*)o.p[1], o.ia[0], o.ia[1], st);
     case OP_BN_FWD:
-      return xb_bn_forward((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], (const float*)o.p[3], (const float*)o.p[4],
-                           (const float*)o.p[5], (float*)o.p[6], (float*)o.p[7], (float*)o.p[8], (float*)o.p[9], (const XbTaskParams*)o.p[10],
-                           o.ia[0], o.ia[1], o.fa[0], o.ia[2], o.ia[3], o.ia[4], o.fa[1], st);
+      // p[11]: packed sign mask of the output (layers with ReLU and a residual input; their backward pass reads it instead of y)
+      return xb_bn_forward_mask((const float*)o.p[0], (const float*)o.p[1], (float*)o.p[2], (const float*)o.p[3], (const float*)o.p[4],
+                                (const float*)o.p[5], (float*)o.p[6], (float*)o.p[7], (float*)o.p[8], (float*)o.p[9], (const XbTaskParams*)o.p[10],
+                                o.ia[0], o.ia[1], o.fa[0], o.ia[2], o.ia[3], o.ia[4], o.fa[1], (unsigned char*)o.p[11], st);
     case OP_BN_BWD:
       if (o.p[11] && !o.ia[5])   // ReLU without residual: mask re-derived from x, the layer's output is not read
         return xb_bn_backward_remask((const float*)o.p[0], (const float*)o.p[1], (const float*)o.p[3], (const float*)o.p[4], (const float*)o.p[5],
@@ -618,6 +619,7 @@ struct XbSyncDescMirror {
   float* w[16]; const float* prev[16]; float* z; float* zlast; float* gacc;
   float* inbox[8]; float* result[8]; unsigned int* flags[8]; int* status; double timeout_s;
   float* zpeer[8];
+  float* part_local; const float* part_mc; float* z_mc;
   unsigned int* release; unsigned long long* stamps;
 };
 XB_API int xb_stream_wait_value32(cudaStream_t st, const unsigned int* word, unsigned int value);

@@ -127,7 +127,7 @@ class GpuEngine:
                  rank: int = 0, world: int = 1, device_index: int = 0, use_tc: bool = True, use_graphs: bool = True,
                  seed: int = 0, fused_sync: bool = True, two_shot: Optional[bool] = None, sync_timeout_s: float = 5.0,
                  splits: int = 1, reuse_memory: bool = False, gradient_buckets: int = 0,
-                 debug_canaries: bool = False, overlap_sync: bool = True, operator_branches: bool = True):
+                 debug_canaries: bool = False, overlap_sync: bool = True, operator_branches: bool = True, nvls_sync: bool = False):
         """`overlap_sync`: model averaging on several GPUs - the learners' next tasks start as soon as their replicas have
         been corrected (the kernel's release word), under the cross-GPU exchange and the central update; off = they wait
         for the whole synchronisation.
@@ -159,7 +159,8 @@ class GpuEngine:
         n = model.device_elements
         Sync = FusedSynchroniser if fused_sync else ReferenceSynchroniser
         # (created first: with several GPUs and a large model it provides the peer-visible home of the central model)
-        self.synchroniser = Sync(n, rank, world, two_shot, sync_timeout_s) if fused_sync else Sync(n, rank, world)
+        # (`nvls_sync`: exchange through NVLink multicast - multimem.ld_reduce / multimem.st - where the two-shot path applies)
+        self.synchroniser = Sync(n, rank, world, two_shot, sync_timeout_s, nvls=nvls_sync) if fused_sync else Sync(n, rank, world)
         z_storage = self.synchroniser.central_storage() if hasattr(self.synchroniser, "central_storage") else None
         self.shared = DeviceShared(model, self.device, init, z_storage)
         self.lr_mult = torch.from_numpy(model.to_device(model.lr_multipliers())).to(self.device) if model.has_lr_multipliers() else None

@@ -36,6 +36,10 @@ from .types import (ActivationMode, BatchNormEstimatedMeanAndVarianceType, Eleme
 # lean stand-alone reduction it saves.  Off; the kernels keep the capability (tests/test_gpu_conv_kernels.py).
 FUSE_BN_BACKWARD_SUMS = False
 
+# Normalisation layers with ReLU and a residual input write a packed sign mask of their output (a sixteenth of its size) in
+# the forward pass; both backward passes read the mask instead of the output.
+PACKED_RELU_MASK = True
+
 
 class Arena:
     """Bump allocator over one CUDA allocation (activations, gradients of activations, scratch of one learner)."""
@@ -584,12 +588,17 @@ class Lowering:
         rm, rv = self.shared.running(bn_node.op.uid, x.c)
         sm = self.arena.alloc(x.c)
         si = self.arena.alloc(x.c)
-        info.update(save_mean=sm, save_invstd=si, x=x, res=res, relu_fused=relu, out=out)
+        # ReLU with a residual input: the mask cannot be re-derived from x alone, so the forward pass leaves a packed sign
+        # mask (one byte per four channels) and the backward passes read that instead of the whole output
+        mask = None
+        if self.training and self.has_backward and relu and res is not None and x.c % 4 == 0 and PACKED_RELU_MASK:
+            mask = self.arena.alloc((x.numel // 4 + 3) // 4 + 4)
+        info.update(save_mean=sm, save_invstd=si, x=x, res=res, relu_fused=relu, out=out, mask=mask)
         out.bn_info = info
         cma = int(conf.estimated_mean_and_variance_type == BatchNormEstimatedMeanAndVarianceType.CMA)
         self.emit(_op(L.OP_BN_FWD, ia=[x.rows, x.c, int(relu), int(self.training), cma], fa=[k.epsilon(), 1.0 - float(conf.fraction)],
                       p=[x.buf, res.buf if res is not None else None, out.buf, info.get("stats_buf"), self.wptr(k.variables[0]),
-                         self.wptr(k.variables[1]), rm, rv, sm, si, self.params_dev]))
+                         self.wptr(k.variables[1]), rm, rv, sm, si, self.params_dev, mask]))
         self.tensors[id(at if at is not None else bn_node)] = out
         if at is not None:
             self.tensors[id(bn_node)] = None
@@ -673,8 +682,9 @@ class Lowering:
                     gres, accr = self.gout(res)
                 # ReLU fused, no residual: the kernels re-derive the mask from x and never read the layer's output
                 remask = self.wptr(bk.variables[1]) if (relu and res is None and fused is None) else None
-                self.emit(_op(L.OP_BN_BWD, ia=[x.rows, x.c, int(relu), accx, accr, int(fused is not None)],
-                              p=[dy, x.buf, out.buf, bi["save_mean"], bi["save_invstd"], self.wptr(bk.variables[0]), dsums, gx, gres,
+                packed = bi.get("mask") if fused is None else None
+                self.emit(_op(L.OP_BN_BWD, ia=[x.rows, x.c, 3 if packed is not None else int(relu), accx, accr, int(fused is not None)],
+                              p=[dy, x.buf, packed if packed is not None else out.buf, bi["save_mean"], bi["save_invstd"], self.wptr(bk.variables[0]), dsums, gx, gres,
                                  self.wptr(bk.variables[0], rep.g), self.wptr(bk.variables[1], rep.g), remask]))
                 continue
             x = self.out_tensor(ins_nodes[0])

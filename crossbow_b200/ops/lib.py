@@ -42,6 +42,7 @@ class XbSyncDesc(C.Structure):
                 ("w", c_void_p * MAXK), ("prev", c_void_p * MAXK), ("z", c_void_p), ("zlast", c_void_p), ("gacc", c_void_p),
                 ("inbox", c_void_p * MAXG), ("result", c_void_p * MAXG), ("flags", c_void_p * MAXG),
                 ("status", c_void_p), ("timeout_s", C.c_double), ("zpeer", c_void_p * MAXG),
+                ("part_local", c_void_p), ("part_mc", c_void_p), ("z_mc", c_void_p),
                 ("release", c_void_p), ("stamps", c_void_p)]
 
 
@@ -112,6 +113,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_transpose_blocks", I, I, I, I)
     _sig(lib, "xb_bn_stats", I, P, P, I, I, P)
     _sig(lib, "xb_bn_forward", I, P, P, P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, F, P)
+    _sig(lib, "xb_bn_forward_mask", I, P, P, P, P, P, P, P, P, P, P, P, I, I, F, I, I, I, F, P, P)
     _sig(lib, "xb_bn_backward", I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P)
     _sig(lib, "xb_act_forward", I, P, P, L, I, F, F, P)
     _sig(lib, "xb_act_backward", I, P, P, P, P, L, I, F, F, I, P)
@@ -138,6 +140,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_sync_result_floats", L, L)
     _sig(lib, "xb_sync_flag_words", L, L, I)
     _sig(lib, "xb_sync_args_size", I)
+    _sig(lib, "xb_sync_part_floats", L, L)
     _sig(lib, "xb_fused_sync", I, C.POINTER(XbSyncDesc), P, P, I, P)
     _sig(lib, "xb_fused_sync_emulated", I, C.POINTER(XbSyncDesc), I, P, I, P)
     _sig(lib, "xb_broadcast_model", I, P, P, I, L, P)

@@ -36,10 +36,39 @@ class _PeerView:
         pass
 
 
+class _MulticastBuffer:
+    """A buffer of ``numel`` floats on every rank that is ALSO bound to an NVLink multicast object, so kernels can address
+    all copies at once with ``multimem`` instructions (``mc``) next to the ordinary peer pointers (``ptrs``).  Allocation,
+    the exchange of handles between the processes and the multicast binding are torch's symmetric memory
+    (``torch.distributed._symmetric_memory``); the kernels that use the addresses are this repository's."""
+
+    def __init__(self, numel: int, rank: int, world: int, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.tensor = symm.empty(int(numel), dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+        self.tensor.zero_()
+        self.handle = symm.rendezvous(self.tensor, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.local = self.ptrs[rank]
+        self.mc = int(self.handle.multicast_ptr or 0)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+
+    def as_tensor(self, numel: int, device=None) -> torch.Tensor:
+        return self.tensor[:numel]
+
+    def close(self):
+        self.handle = None
+        self.tensor = None
+
+
 class FusedSynchroniser:
     def __init__(self, n: int, rank: int = 0, world: int = 1, two_shot: Optional[bool] = None, timeout_s: float = 5.0,
-                 max_blocks: int = 0, group=None, parent: Optional["FusedSynchroniser"] = None, offset: int = 0):
-        """`parent` / `offset`: this synchroniser covers elements [offset, offset + n) of the parent's vectors (a gradient
+                 max_blocks: int = 0, group=None, parent: Optional["FusedSynchroniser"] = None, offset: int = 0, nvls: bool = False):
+        """`nvls`: two-shot exchange through NVLink multicast (in-switch reduction with ``multimem.ld_reduce``, broadcast of
+        the new central model with ``multimem.st``) instead of unicast peer stores.  Off by default; falls back to the
+        peer-store path (with a warning) where the GPUs or the driver offer no multicast.
+        `parent` / `offset`: this synchroniser covers elements [offset, offset + n) of the parent's vectors (a gradient
         bucket).  It has exchange buffers and flags of its own, so buckets of different sizes never share a flag slot or
         an inbox region, and it shares the parent's status word and central-model storage."""
         lib = L.load()
@@ -55,7 +84,8 @@ class FusedSynchroniser:
         self.status = parent.status if parent is not None else torch.zeros(1, dtype=torch.int32, device="cuda")
         self.parent, self.offset, self.group = parent, offset, group
         self.children: List["FusedSynchroniser"] = []
-        self.inbox = self.result = self.flags = self.zbuf = None
+        self.inbox = self.result = self.flags = self.zbuf = self.part = None
+        self.nvls = False
         # release word + block counter, and the kernel's time line (see sync.cu): plain device memory of this rank
         self.release = torch.zeros(2, dtype=torch.int32, device="cuda")
         self.stamps = torch.zeros(lib.xb_sync_stamp_words(), dtype=torch.int64, device="cuda")
@@ -65,6 +95,17 @@ class FusedSynchroniser:
             self.flags = PeerBuffer(4 * lib.xb_sync_flag_words(n, world), rank, world, group)
             if self.two_shot and parent is not None:
                 self.zbuf = _PeerView(parent.zbuf, 4 * offset) if parent.zbuf is not None else None
+            elif self.two_shot and nvls:
+                try:
+                    zb = _MulticastBuffer(n, rank, world, group)
+                    pb = _MulticastBuffer(lib.xb_sync_part_floats(n), rank, world, group)
+                    if not zb.mc or not pb.mc:
+                        raise RuntimeError("no multicast address")
+                    self.zbuf, self.part, self.nvls = zb, pb, True
+                except Exception as e:           # no NVLink multicast here: the peer-store path does the same job
+                    import warnings
+                    warnings.warn(f"NVLS synchronisation is not available ({type(e).__name__}: {e}); using peer stores")
+                    self.zbuf = PeerBuffer(4 * n, rank, world, group)
             elif self.two_shot:
                 # peer-visible home for the central model: chunk owners then store the updated model straight into it
                 self.zbuf = PeerBuffer(4 * n, rank, world, group)
@@ -121,6 +162,8 @@ class FusedSynchroniser:
             if self.zbuf is not None and z.data_ptr() == self.zbuf.local:
                 for g in range(self.world):
                     d.zpeer[g] = self.zbuf.ptrs[g]
+                if self.nvls:
+                    d.part_local, d.part_mc, d.z_mc = self.part.local, self.part.mc, self.zbuf.mc
         d.status = self.status.data_ptr()
         d.timeout_s = self.timeout_s
         d.release, d.stamps = self.release.data_ptr(), self.stamps.data_ptr()
@@ -169,7 +212,7 @@ class FusedSynchroniser:
         for c in self.children:
             c.close()
         self.children = []
-        for b in (self.inbox, self.result, self.flags, self.zbuf):
+        for b in (self.inbox, self.result, self.flags, self.zbuf, self.part):
             if b is not None:
                 b.close()
         self.lib.xb_device_free(self.args_dev)

@@ -30,6 +30,7 @@ def main():
     ap.add_argument("--sizes", default="464154,25557032")
     ap.add_argument("--replicas", default="1,2,4")
     ap.add_argument("--two-shot", default="auto")
+    ap.add_argument("--nvls", action="store_true", help="also time the NVLink-multicast (multimem) variant of the two-shot exchange")
     a = ap.parse_args()
     import torch.distributed as dist
     from ..ops import lib as L
@@ -93,6 +94,7 @@ def main():
             ps = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
             two = None if a.two_shot == "auto" else a.two_shot == "1"
             fs = FusedSynchroniser(n, rank, world, two_shot=two)
+            fn = FusedSynchroniser(n, rank, world, two_shot=two, nvls=True) if (a.nvls and world > 1 and fs.two_shot) else None
             # the central model lives where the synchroniser wants it (peer-visible memory when chunk owners store into it)
             z = fs.central_storage()
             z = z.zero_() if z is not None else torch.zeros(n, device="cuda")
@@ -107,6 +109,12 @@ def main():
                 fs.check()
                 clocks = sampler.stop()
                 tl = fs.timeline()
+                t_n = None
+                if fn is not None and fn.nvls:
+                    zn = fn.central_storage().zero_()
+                    t_n = timed(lambda: fn.synchronise(s, ALGO_SMA, ws, ps, zn, zl, alpha=0.1, mu=0.9))
+                    torch.cuda.synchronize()
+                    fn.check()
                 t_r = timed(lambda: rs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9))
             # bytes this implementation moves through one GPU's HBM: replicas 3k, central model and its momentum 4, plus the
             # exchange (one-shot: G partials written and read; two-shot with owner-apply: partials once in, once out, 3/G)
@@ -119,11 +127,15 @@ def main():
                 print(json.dumps({"op": "sma_sync", "n": n, "replicas": k, "gpus": world, "two_shot": fs.two_shot, "owner_apply": bool(fs.owner_apply and world > 1),
                                   "fused_us": round(t_f, 2), "reference_us": round(t_r, 2), "speedup": round(t_r / t_f, 2),
                                   "release_us": round(tl["release_us"], 2),
+                                  "nvls_us": round(t_n, 2) if t_n else None,
+                                  "nvls_fraction_of_roofline_900": round(t_nom / t_n, 3) if t_n else None,
                                   "peer_store_gbs": round(peer_gbs, 1) if peer_gbs else None,
                                   "roofline_us_measured_link": round(t_meas, 2), "fraction_of_roofline_measured_link": round(t_meas / t_f, 3),
                                   "roofline_us_900": round(t_nom, 2), "fraction_of_roofline_900": round(t_nom / t_f, 3),
                                   "hbm_bytes": hbm, "nvlink_bytes_per_gpu": link, "hbm_peak": how, "clocks": clocks}), flush=True)
             fs.close()
+            if fn is not None:
+                fn.close()
             del ws, ps, z, zl
             torch.cuda.empty_cache()
     if world > 1:

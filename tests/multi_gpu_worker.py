@@ -56,6 +56,51 @@ def main():
         assert float(gacc.abs().max()) == 0.0 and torch.equal(ws[0], z)
         dist.barrier()
         fs.close()
+    # NVLink multicast variant of the two-shot exchange (multimem.ld_reduce / multimem.st), where the box offers multicast.
+    # Nothing is asserted while memory is bound to the multicast object: a rank that left at that point would take the
+    # others' NVLink traffic down with it.  The verdicts are collected, every rank unbinds, and only then are they checked.
+    if os.environ.get("XBOW_TEST_NVLS", "1") == "1":
+        import gc
+        n, k = 4096 * 9 + 2048, 2
+        fs = FusedSynchroniser(n, rank, world, two_shot=True, timeout_s=10.0, nvls=True)
+        used, problems = fs.nvls, []
+        if used:
+            g = torch.Generator(device="cuda").manual_seed(40 + rank)
+            ws = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
+            ps = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
+            z, zl = fs.central_storage(), torch.zeros(n, device="cuda")
+            z.zero_()
+            ws2, ps2, z2, zl2 = [w.clone() for w in ws], [p.clone() for p in ps], z.clone(), zl.clone()
+            rs = ReferenceSynchroniser(n, rank, world)
+            for it in range(3):
+                fs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9)
+                rs.synchronise(s, ALGO_SMA, ws2, ps2, z2, zl2, alpha=0.1, mu=0.9)
+                torch.cuda.synchronize()
+                if int(fs.status.item()) != 0:
+                    problems.append(f"status {int(fs.status.item())} at iteration {it}")
+                    fs.status.zero_()
+                if not torch.allclose(z, z2, rtol=1e-4, atol=1e-7):
+                    problems.append(f"central model differs at iteration {it}: {float((z - z2).abs().max())}")
+                if not all(torch.allclose(a_, b_, rtol=1e-4, atol=1e-7) for a_, b_ in zip(ws, ws2)):
+                    problems.append(f"replicas differ at iteration {it}")
+                zs = [torch.empty_like(z) for _ in range(world)]
+                dist.all_gather(zs, z.clone())
+                if not all(torch.equal(zs[0], t) for t in zs):
+                    problems.append(f"central models differ across ranks at iteration {it}")
+                if not torch.allclose(fs.gather_momentum(zl), zl2, rtol=1e-4, atol=1e-7):
+                    problems.append(f"momentum differs at iteration {it}")
+            del z, zs
+        torch.cuda.synchronize()
+        dist.barrier()
+        fs.close()
+        del fs
+        gc.collect()
+        torch.cuda.empty_cache()
+        torch.cuda.synchronize()
+        dist.barrier()
+        assert not problems, problems
+        if rank == 0:
+            print("NVLS_SYNC_OK" if used else "NVLS_SYNC_UNAVAILABLE")
     # end to end: two ranks train with SMA through the engine and stay in step
     from crossbow_b200 import Phase, UpdateModel
     from crossbow_b200.engine import GpuEngine

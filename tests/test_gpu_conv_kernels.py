@@ -277,3 +277,36 @@ def test_wgrad_tensor_core_slab(env, shape):
         assert float((dw - dw_ref).abs().max()) / float(dw_ref.abs().max()) < 4e-3
     finally:
         lib.xb_tc_set_slab(3)
+
+
+@pytest.mark.parametrize("M,C", [(4096, 64), (777, 256), (50, 1024), (3000, 16)])
+def test_batch_norm_packed_sign_mask_equals_mask_from_output(M, C):
+    """Residual + ReLU normalisation layers: the forward pass writes one byte per four channels with the signs of its
+    output, and a backward pass that reads those bytes gives exactly what the one reading the output itself gives."""
+    from crossbow_b200.ops import lib as L
+    lib = L.load()
+    g = torch.Generator(device="cuda").manual_seed(M + C)
+    x, res, dy = (torch.randn(M, C, device="cuda", generator=g) for _ in range(3))
+    gamma, beta = torch.rand(C, device="cuda", generator=g) + 0.5, torch.randn(C, device="cuda", generator=g) * 0.1
+    sums = torch.stack([x.sum(0), (x * x).sum(0)]).contiguous()
+    y = torch.empty_like(x)
+    rm, rv, sm, si = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda"), torch.empty(C, device="cuda"), torch.empty(C, device="cuda")
+    mask = torch.zeros(M * C // 4, dtype=torch.uint8, device="cuda")
+    tp = torch.zeros(16, dtype=torch.int32, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    L.check(lib.xb_bn_forward_mask(x.data_ptr(), res.data_ptr(), y.data_ptr(), sums.data_ptr(), gamma.data_ptr(), beta.data_ptr(), rm.data_ptr(),
+                                   rv.data_ptr(), sm.data_ptr(), si.data_ptr(), tp.data_ptr(), M, C, 1e-5, 1, 1, 0, 0.1, mask.data_ptr(), s), "bn forward")
+    torch.cuda.synchronize()
+    bits = torch.stack([(mask >> e) & 1 for e in range(4)], -1).reshape(M, C).bool()
+    assert torch.equal(bits, y > 0)
+    outs = []
+    for relu, ysrc in ((1, y), (3, mask)):
+        dsums, dx, dres = torch.zeros(2 * C, device="cuda"), torch.empty_like(x), torch.empty_like(x)
+        dg, db = torch.zeros(C, device="cuda"), torch.zeros(C, device="cuda")
+        L.check(lib.xb_bn_backward(dy.data_ptr(), x.data_ptr(), ysrc.data_ptr(), sm.data_ptr(), si.data_ptr(), gamma.data_ptr(), dsums.data_ptr(),
+                                   dx.data_ptr(), dres.data_ptr(), dg.data_ptr(), db.data_ptr(), M, C, relu, 0, 0, s), "bn backward")
+        torch.cuda.synchronize()
+        outs.append((dx, dres, dg, db))
+    for a, b in zip(*outs):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-5 * float(a.abs().max()))      # (the sums are atomic: rounding only)
+    assert torch.equal(outs[0][1], outs[1][1])                                            # dres = masked dy, no arithmetic
