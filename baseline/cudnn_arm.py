@@ -1,7 +1,7 @@
 """Library baseline for bench.py (`--impl cudnn`): the same workload with stock PyTorch operators.
 
 Same model family, batch size, replicas per GPU, optimiser and synchronous-model-averaging arithmetic as the product arm,
-but every operator is a library kernel (cuDNN convolutions and batch norm with TF32 allowed, cuBLAS, NCCL all-reduce), in
+but every operator is a library kernel (cuDNN convolutions with TF32 allowed, PyTorch's batch-norm kernels, cuBLAS, NCCL all-reduce), in
 channels-last layout, with each replica's whole task (forward, loss, backward, momentum-SGD step) captured in a CUDA graph
 and the k replicas running on k streams.  The synchronisation is reference-style: a handful of element-wise kernels over
 flat parameter vectors around one `all_reduce` (what clib-multigpu/synch/sma.c does with cuBLAS level-1 calls around
@@ -16,8 +16,19 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 
+class _BatchNorm(nn.BatchNorm2d):
+    """Batch norm through PyTorch's own kernels.  cuDNN's spatial-persistent batch-norm kernels synchronise their blocks
+    with one another inside the kernel and so assume they have the GPU to themselves; with several replicas' graphs
+    replaying on several streams such kernels can wait for each other for ever (this arm stalled that way with four
+    replicas, always with eight).  The convolutions stay on cuDNN."""
+
+    def forward(self, x):
+        with torch.backends.cudnn.flags(enabled=False):
+            return super().forward(x)
+
+
 def _bn(c):
-    return nn.BatchNorm2d(c, eps=1e-5, momentum=0.1)
+    return _BatchNorm(c, eps=1e-5, momentum=0.1)
 
 
 class Basic(nn.Module):

@@ -286,15 +286,12 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     if args.gpus > 1 and world == 1:
         raise SystemExit("launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
-    torch.cuda.set_device(local)
-    init_process_group("nccl", timeout_s=300)
-
-    out = measure_ours(args, args.model, args.steps, args.warmup, args.replicas, args.batch, args.min_seconds)
-
     # ---------------- same box, same run: the library arm (none of this repository's kernels) --------------------------
-    # It runs as a child process with a deadline: stock library kernels replayed from several CUDA graphs on several
-    # streams have stalled on this hardware before (with and without NCCL), and a stall there must not take this
-    # program's own measurement down with it.  One GPU only: a child cannot join this job's process group.
+    # It runs FIRST, as a child process with a deadline, before this process creates its own CUDA context: stock library
+    # kernels replayed from several CUDA graphs on several streams have stalled on this hardware before, and a stall
+    # there must not take this program's own measurement down with it.  One GPU only: a child cannot join this job's
+    # process group.
+    base = None
     if not args.no_library_arm and args.update_model == "sma" and args.sync == "fused" and world == 1:
         import subprocess
         cmd = [sys.executable, os.path.abspath(__file__), "--impl", "cudnn", "--gpus", "1", "--steps", str(args.steps), "--warmup", str(args.warmup),
@@ -303,19 +300,26 @@ def main():
             cmd += ["--replicas", str(args.replicas)]
         if args.batch:
             cmd += ["--batch", str(args.batch)]
-        torch.cuda.synchronize()
         try:
-            r = subprocess.run(cmd, capture_output=True, text=True, timeout=240)
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=150)
             lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
             base = json.loads(lines[-1]) if lines else {"impl": "cudnn", "unavailable": f"exit code {r.returncode}: {r.stderr[-200:]}"}
         except subprocess.TimeoutExpired:
-            base = {"impl": "cudnn", "unavailable": "the library arm did not finish within 240 s"}
+            base = {"impl": "cudnn", "unavailable": "the library arm did not finish within 150 s"}
         except Exception as e:                                   # the product's number stands without it
             base = {"impl": "cudnn", "unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+    torch.cuda.set_device(local)
+    init_process_group("nccl", timeout_s=300)
+
+    out = measure_ours(args, args.model, args.steps, args.warmup, args.replicas, args.batch, args.min_seconds)
+
+    if base is not None:
         if "value" in base:
             out["vs_baseline"] = round(out["value"] / base["value"], 3)
             out["baseline_value"] = base["value"]
-            out["baseline_impl"] = "pytorch-cudnn-tf32-graphs + reference-style averaging (element-wise kernels + NCCL all-reduce), child process, same box"
+            out["baseline_impl"] = ("pytorch: cuDNN convolutions (TF32), PyTorch batch norm, CUDA graphs on k streams, channels-last + reference-style "
+                                    "averaging (element-wise kernels); child process on the same GPU, run before this arm")
             out["baseline"] = {"ms_per_step": base["ms_per_step"], "repeats": base["repeats"], "e2e_value": base["e2e"]["value"],
                                "clocks": base.get("clocks"), "vs_baseline_e2e": round(out["e2e"]["value"] / base["e2e"]["value"], 3)}
         else:

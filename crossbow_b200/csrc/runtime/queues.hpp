@@ -75,9 +75,14 @@ class ThetaQueue {
   }
   void release(int i) { slots_[i].state.store(FREE, std::memory_order_release); }
   int state(int i) const { return slots_[i].state.load(std::memory_order_acquire); }
-  // Grow by one slot, born BUSY (the caller releases it once the new replica is ready). Returns its index or -1.
+  // One more enabled slot, born BUSY (the caller releases it once the new replica is ready): the lowest slot that was
+  // disabled by shrink() if there is one, else a new slot at the end.  Returns its index or -1.
   int expand() {
     int n = size();
+    for (int i = 0; i < n; ++i) {
+      int expect = SKIP;
+      if (slots_[i].state.compare_exchange_strong(expect, BUSY, std::memory_order_acq_rel)) return i;
+    }
     if (n >= kMaxSlots) return -1;
     slots_[n].state.store(BUSY, std::memory_order_release);
     size_.store(n + 1, std::memory_order_release);
