@@ -29,8 +29,9 @@ def test_theta_queue_round_robin_expand_shrink():
     assert q.next(0.05) == -1
     # growing again re-enables the disabled slot (the replica that takes it gets the same index as the one removed)
     assert q.expand() == 3 and q.size() == 4 and q.enabled() == 4
-    q.release(3)
-    assert q.next() == 3
+    for i in range(4):
+        q.release(i)
+    assert sorted(q.next() for _ in range(4)) == [0, 1, 2, 3]
 
 
 @pytest.mark.parametrize("handlers", [0, 2])
