@@ -54,6 +54,7 @@ class Learner:
         self.handle = None
         self.clock = 0
         self.pending = None          # (task_id, phase) in flight
+        self._held = []              # host tensors of submitted tasks whose asynchronous copies may not have run yet
         c, h, w = engine.input_chw
         # the first lowering allocates the staging buffers the native learner copies into
         self.handle_placeholder = None
@@ -102,12 +103,19 @@ class Learner:
         L.check(lib.xb_memcpy_h2d_async(lab.data_ptr(), labels.data_ptr(), labels.numel() * 4, s), "H2D labels")
         L.check(lib.xb_learner_submit(self.handle, None, None, C.byref(params), int(phase)), "task submit")
         self.pending = (params.task_id, phase)
+        # The copies above are asynchronous: the (pinned) source must stay alive - and out of the pinned allocator's
+        # free list - until they have run.  A caller that passes a temporary (`x.pin_memory()`) is covered by these
+        # references; they are dropped once a wait has shown the tasks to be complete.
+        self._held.append((examples, labels))
+        if len(self._held) > 256:
+            del self._held[0]
 
     def wait(self):
         from .ops import lib as L
         loss, acc = C.c_float(), C.c_float()
         L.check(self.engine.lib.xb_learner_wait(self.handle, C.byref(loss), C.byref(acc)), "task wait")
         self.pending = None
+        self._held.clear()           # the learner's last task has finished, so every copy before it has run
         return loss.value, acc.value
 
     def destroy(self):

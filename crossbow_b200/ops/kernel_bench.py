@@ -134,6 +134,16 @@ def bench_bn(lib, timer, op, M, Cc, iters):
     elif op == "bn_stats":
         fn = lambda: lib.xb_bn_stats(x.data_ptr(), sums.data_ptr(), M, Cc, s)
         bytes_ = 4 * M * Cc
+    elif op in ("bn_bwd_res", "bn_bwd_res_mask"):
+        # layer with ReLU and a residual input: the mask comes from the output y, or from the packed sign bytes
+        dres = torch.empty(M, Cc, device=dev)
+        mask = torch.randint(0, 16, (M * Cc // 4,), dtype=torch.uint8, device=dev)
+        packed = op.endswith("mask")
+        ysrc, relu = (mask, 3) if packed else (y, 1)
+        fn = lambda: lib.xb_bn_backward(dy.data_ptr(), x.data_ptr(), ysrc.data_ptr(), sm.data_ptr(), si.data_ptr(), gamma.data_ptr(), dsums.data_ptr(),
+                                        dx.data_ptr(), dres.data_ptr(), dg.data_ptr(), db.data_ptr(), M, Cc, relu, 0, 0, s)
+        # reduce reads dy, x, mask source; apply reads the same and writes dx and dres
+        bytes_ = 4 * M * Cc * 6 + 2 * (M * Cc // 4 if packed else 4 * M * Cc)
     else:
         fn = lambda: lib.xb_bn_backward(dy.data_ptr(), x.data_ptr(), y.data_ptr(), sm.data_ptr(), si.data_ptr(), gamma.data_ptr(), dsums.data_ptr(),
                                         dx.data_ptr(), 0, dg.data_ptr(), db.data_ptr(), M, Cc, 1, 0, 0, s)
@@ -141,6 +151,27 @@ def bench_bn(lib, timer, op, M, Cc, iters):
     L.check(fn(), op)
     med, best = timer.run(fn, iters)
     return dict(op=op, rows=M, channels=Cc, us=round(med, 2), best_us=round(best, 2), bytes=bytes_, flops=0)
+
+
+def bench_image(lib, timer, n, W, H, S, iters):
+    """Crop / mirror / bilinear resize / scaling of `n` decoded W x H images into S x S examples (csrc/kernels/image.cu)."""
+    import numpy as np
+    g = np.random.default_rng(0)
+    stride = (W * H * 3 + 15) // 16 * 16
+    rgb = torch.randint(0, 256, (n * stride,), dtype=torch.uint8, device="cuda")
+    desc = np.zeros((n, lib.xb_image_desc_size() // 4), dtype=np.int32)
+    for i in range(n):
+        cw, ch = int(g.integers(W // 3, W + 1)), int(g.integers(H // 3, H + 1))
+        desc[i].view(np.int64)[0] = i * stride
+        desc[i, 2:9] = (W, H, int(g.integers(0, W - cw + 1)), int(g.integers(0, H - ch + 1)), cw, ch, int(g.integers(0, 2)))
+    d = torch.from_numpy(desc).cuda()
+    out = torch.empty(n, 3, S, S, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    fn = lambda: lib.xb_image_crop_resize(rgb.data_ptr(), d.data_ptr(), n, S, out.data_ptr(), s)
+    L.check(fn(), "image")
+    med, best = timer.run(fn, iters)
+    # every output value reads (up to) four source bytes that are mostly shared with its neighbours: the output dominates
+    return dict(op="image_crop_resize", images=n, source=[W, H], size=S, us=round(med, 2), best_us=round(best, 2), bytes=12 * n * S * S + int(desc[:, 6].astype(np.int64) @ desc[:, 7].astype(np.int64)) * 3, flops=0)
 
 
 def bench_sync(lib, timer, n, k, iters):
@@ -292,6 +323,8 @@ def main():
         report(bench_conv(lib, timer, a.op, a.impl, tuple(int(v) for v in a.shape.split(",")), a.iters, 4 if a.stats else 0))
     elif a.op.startswith("bn"):
         report(bench_bn(lib, timer, a.op, a.rows, a.channels, a.iters))
+    elif a.op == "image":
+        report(bench_image(lib, timer, a.rows, 500, 375, 224, a.iters))
     elif a.op == "sync":
         report(bench_sync(lib, timer, a.n, a.replicas, a.iters))
     elif a.op == "optimiser":
