@@ -276,6 +276,8 @@ XB_API int xb_program_run_range(XbProgram* p, int first, int last, cudaStream_t 
 // its labelling pass is switched off and the branch factor stays 1, SubGraph.java:208-212.)  A program that is issued
 // directly, not captured, runs its operators in list order on one stream.
 constexpr int XB_OP_SIDE = 0x1000;
+static int g_side_low = 0;
+XB_API void xb_program_side_priority(int low) { g_side_low = low ? 1 : 0; }
 static inline bool joins_side(int kind) { return kind == OP_OPTIMISER || kind == OP_GRAD_SUMSQ; }
 
 static int capture_with_branches(XbProgram* p, cudaStream_t st) {
@@ -295,7 +297,13 @@ static int capture_with_branches(XbProgram* p, cudaStream_t st) {
   for (size_t i = 0; i < p->ops.size() && e == 0; ++i) {
     const XbOp& o = p->ops[i];
     if (o.flags & XB_OP_SIDE) {
-      if (!side && cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess) { e = -XB_BAD_ARG; break; }
+      if (!side) {
+        // the branch's kernels inherit this stream's priority in the graph: with g_side_low they only take what the main
+        // chain leaves free
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        if (cudaStreamCreateWithPriority(&side, cudaStreamNonBlocking, g_side_low ? lo : 0) != cudaSuccess) { e = -XB_BAD_ARG; break; }
+      }
       cudaEvent_t ev = event();                                  // fork: everything issued on the main stream so far
       if ((e = (int)cudaEventRecord(ev, st)) != 0) break;
       if ((e = (int)cudaStreamWaitEvent(side, ev, 0)) != 0) break;

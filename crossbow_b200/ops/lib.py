@@ -160,6 +160,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_program_run_range", I, P, I, I, P)
     _sig(lib, "xb_program_capture", I, P, P)
     _sig(lib, "xb_program_marks", I, P)
+    _sig(lib, "xb_program_side_priority", None, I)
     _sig(lib, "xb_program_launch", I, P, P)
     _sig(lib, "xb_learner_create", P, I, P, L, P, L)
     _sig(lib, "xb_learner_destroy", None, P)
