@@ -200,8 +200,11 @@ class GpuEngine:
         from .ops import lib as L
         if getattr(L, "launch_shapes_pinned", False):      # a benchmark set them by hand
             return
-        wide = k <= 2 and self.model.elements < (2 << 20)
-        self.lib.xb_conv3x3_wgrad_set_ctas(296 if wide else 148)
+        small = self.model.elements < (2 << 20)
+        wide = k <= 2 and small
+        # (with the weight gradients on a parallel branch of the task graph they are off the critical path: for small models
+        # at three or more replicas 74 long-lived CTAs measured +0.9 % over 148)
+        self.lib.xb_conv3x3_wgrad_set_ctas(296 if wide else (74 if small and self.operator_branches else 148))
         self.lib.xb_gemm_set_tn_ctas(148 if wide else 111)
         self.lib.xb_bn_set_reduce_blocks(592 if wide else 296)
 
