@@ -45,6 +45,7 @@ def save_checkpoint(ctx, directory: str) -> str:
     os.makedirs(d, exist_ok=True)
     e, dev = ctx.engine, ctx.rank
     gpu = hasattr(e, "shared")
+    e.finish()                       # the last synchronisation may still be updating the central model on its own stream
     _write(os.path.join(d, f"gpu-{dev:02d}-theModel-data.dat"), e.central_model())
     if gpu:
         m = ctx.model

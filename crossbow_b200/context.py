@@ -126,6 +126,15 @@ class ExecutionContext:
         self._native = self._native_test = None
         if sys.gpu and sys.native_scheduler and sys.fused_sync and (hasattr(ds, "examples") or hasattr(ds, "source")):
             self._setup_native()
+        if self.world > 1:
+            # lowering and graph capture take seconds and not the same number on every rank; the first synchronisation's
+            # device-side waits are bounded, so the ranks leave init() together
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized():
+                if sys.gpu:
+                    import torch
+                    torch.cuda.synchronize()
+                dist.barrier()
         return self
 
     def _setup_native(self):

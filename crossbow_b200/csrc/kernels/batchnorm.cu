@@ -179,8 +179,11 @@ struct BnBwdArgs {
   const float* beta;   // relu == 2: the mask is re-derived from x (fma(x, gamma*istd, beta - mean*gamma*istd) > 0) and y is not read
 };
 
-template <int VEC>
-__global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
+// MODE: where the ReLU mask comes from - 0 none, 1 the output y, 2 re-derived from x, 3 the packed sign bytes; -1 = read
+// it from the arguments at run time (the scalar kernels).  A compile-time mode keeps the registers of the unused mask
+// sources out of the kernel, which is what lets three blocks share an SM.
+template <int VEC, int MODE = -1>
+__global__ void __launch_bounds__(NT, MODE >= 0 ? 3 : 1) bn_bwd_reduce_kernel(BnBwdArgs a) {
   const Tiling t = make_tiling(a.C, VEC);
   __shared__ float red[2][NT * VEC];
   const int r_begin = blockIdx.x * a.rows_per_block, r_end = min(a.M, r_begin + a.rows_per_block);
@@ -191,7 +194,8 @@ __global__ void __launch_bounds__(NT) bn_bwd_reduce_kernel(BnBwdArgs a) {
     float s1[VEC], s2[VEC], mean[VEC], istd[VEC], msc[VEC], msh[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) { s1[e] = 0.f; s2[e] = 0.f; mean[e] = 0.f; istd[e] = 0.f; msc[e] = 0.f; msh[e] = 0.f; }
-    const bool from_y = a.relu == 1, from_x = a.relu == 2, from_m = (VEC == 4) && a.relu == 3;
+    const int mode = MODE >= 0 ? MODE : a.relu;
+    const bool from_y = mode == 1, from_x = mode == 2, from_m = (VEC == 4) && mode == 3;
     const unsigned char* mk = reinterpret_cast<const unsigned char*>(a.y);
     if (active) {
 #pragma unroll
@@ -307,6 +311,15 @@ __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
   }
 }
 
+template <class A> static void launch_reduce_v4(const A& a, int blocks, cudaStream_t st) {
+  switch (a.relu) {
+    case 0: bn_bwd_reduce_kernel<4, 0><<<blocks, NT, 0, st>>>(a); break;
+    case 1: bn_bwd_reduce_kernel<4, 1><<<blocks, NT, 0, st>>>(a); break;
+    case 2: bn_bwd_reduce_kernel<4, 2><<<blocks, NT, 0, st>>>(a); break;
+    default: bn_bwd_reduce_kernel<4, 3><<<blocks, NT, 0, st>>>(a); break;
+  }
+}
+
 // Reductions end in 2C same-address atomics per block, which serialise in L2: they get fewer, longer blocks.
 static int g_bn_reduce_blocks = 296;
 static int g_bn_stream_blocks = 592;                   // normalise / apply passes (no atomics): ~4 resident blocks per SM
@@ -371,7 +384,7 @@ XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const
   bool v4 = can_vec4(C, dy, x, relu == 3 ? nullptr : y, dx) && (((uintptr_t)dres) % 16 == 0);
   if (relu == 3 && !v4) return -XB_BAD_ARG;
   int blocks, rblocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, rblocks, g_bn_reduce_blocks, 8);
-  if (v4) bn_bwd_reduce_kernel<4><<<rblocks, NT, 0, st>>>(a); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, st>>>(a);
+  if (v4) launch_reduce_v4(a, rblocks, st); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, st>>>(a);
   a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
   if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); else bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a);
   return (int)cudaGetLastError();
@@ -388,7 +401,7 @@ XB_API int xb_bn_backward_remask(const float* dy, const float* x, const float* s
   BnBwdArgs a{dy, x, nullptr, save_mean, save_invstd, gamma, dsums, dx, nullptr, dgamma, dbeta, M, C, 2, accum_dx, 0, 0, beta};
   bool v4 = can_vec4(C, dy, x, nullptr, dx);
   int blocks, rblocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, rblocks, g_bn_reduce_blocks, 8);
-  if (v4) bn_bwd_reduce_kernel<4><<<rblocks, NT, 0, st>>>(a); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, st>>>(a);
+  if (v4) launch_reduce_v4(a, rblocks, st); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, st>>>(a);
   a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
   if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); else bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a);
   return (int)cudaGetLastError();
@@ -450,7 +463,7 @@ int xb_bn_backward_static(const float* dy, const float* x, const float* y, const
   bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
   // same launch shapes as xb_bn_backward: fewer, longer blocks for the reduction (its tail is same-address atomics)
   int blocks, rblocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, rblocks, g_bn_reduce_blocks, 8);
-  if (v4) bn_bwd_reduce_kernel<4><<<rblocks, NT, 0, stream>>>(a); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, stream>>>(a);
+  if (v4) launch_reduce_v4(a, rblocks, stream); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, stream>>>(a);
   a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
   if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, stream>>>(a); else bn_bwd_apply_kernel<1><<<blocks, NT, 0, stream>>>(a);
   return (int)cudaGetLastError();

@@ -317,11 +317,14 @@ int make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims,
 }
 
 constexpr size_t kSmemLimit = 200 * 1024;
+// Shared-memory budgets of the operand pipeline (tuning): `g_budget_many` when the grid has more CTAs than SMs (two CTAs
+// then share an SM), `g_budget_few` otherwise.  Smaller budgets leave room for other replicas' CTAs on the same SM.
+static size_t g_budget_many = 108 * 1024, g_budget_few = kSmemLimit;
 inline size_t stage_bytes(int BN, int kc = 1) { return (size_t)kc * (A_BYTES + (size_t)BN * 128); }
 // Pipeline depth: as deep as the reduction, within a shared-memory budget that still lets two CTAs share an SM when the
 // grid has more CTAs than SMs (the second CTA's loads and MMAs then overlap the first one's epilogue).
 inline int pick_stages(int steps, int BN, long long ctas, int kc = 1) {
-  const size_t budget = ctas > 148 ? 108 * 1024 : kSmemLimit;
+  const size_t budget = ctas > 148 ? g_budget_many : g_budget_few;
   int s = steps < MAX_STAGES ? steps : MAX_STAGES;
   while (s > 2 && (size_t)s * stage_bytes(BN, kc) > budget) --s;
   return s;
@@ -329,7 +332,7 @@ inline int pick_stages(int steps, int BN, long long ctas, int kc = 1) {
 // Reduction blocks per stage: as many as divide `blocks` (channel blocks per tap, or k-blocks of a plain GEMM) while at
 // least two stages still fit; wide tiles keep one (their MMAs are long enough to hide the per-stage overhead).
 inline int pick_kc(int blocks, int BN, long long ctas) {
-  const size_t budget = ctas > 148 ? 108 * 1024 : kSmemLimit;     // (same budget as pick_stages: keep two CTAs per SM)
+  const size_t budget = ctas > 148 ? g_budget_many : g_budget_few;     // (same budget as pick_stages: keep two CTAs per SM)
   const int order[3] = {4, 2, 3};                        // (3 only where neither 4 nor 2 divides: nine taps of a 32-channel layer)
   for (int kc : order)
     if (blocks % kc == 0 && 2 * stage_bytes(BN, kc) <= budget && (BN <= 64 || kc <= 2)) return kc;
@@ -381,6 +384,10 @@ inline bool is_1x1(const XbConvGeom* g) { return g->R == 1 && g->S == 1 && g->ph
 }  // namespace
 
 XB_API void xb_gemm_set_tn_ctas(int n) { g_tn_ctas = n > 0 ? n : 111; }
+XB_API void xb_gemm_set_smem_budgets(int many_kb, int few_kb) {
+  g_budget_many = many_kb > 0 ? (size_t)(many_kb < 200 ? many_kb : 200) * 1024 : 108 * 1024;
+  g_budget_few = few_kb > 0 ? (size_t)(few_kb < 200 ? few_kb : 200) * 1024 : kSmemLimit;
+}
 XB_API int xb_gemm_tma_init() {
   int e;
   if (!encode_fn()) return 0;                            // no driver entry point: the callers keep to the gather kernels

@@ -486,6 +486,22 @@ __global__ void __launch_bounds__(NT) peer_copy_kernel(float4* __restrict__ dst,
   }
 }
 
+// The same, to every peer in ONE launch (blockIdx.y = destination): what a GPU can push when all its outgoing traffic is in
+// flight at once, as it is in the exchange.
+struct PeerCopyAll { float4* dst[MAXG]; const float4* src[MAXG]; long long n4; };
+__global__ void __launch_bounds__(NT) peer_copy_all_kernel(PeerCopyAll a) {
+  float4* __restrict__ dst = a.dst[blockIdx.y];
+  const float4* __restrict__ src = a.src[blockIdx.y];
+  const long long stride = (long long)gridDim.x * NT * U;
+  for (long long i0 = (long long)blockIdx.x * NT * U + threadIdx.x; i0 < a.n4; i0 += stride) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (i0 + u * NT < a.n4) v[u] = src[i0 + u * NT];
+#pragma unroll
+    for (int u = 0; u < U; ++u) if (i0 + u * NT < a.n4) dst[i0 + u * NT] = v[u];
+  }
+}
+
 // replicas <- z (DEFAULT update model, and LR-drop copies when no averaging is due)
 __global__ void broadcast_z_kernel(const float* __restrict__ z, float* const* w, int k, long long n4) {
   for (long long i = blockIdx.x * (long long)NT + threadIdx.x; i < n4; i += (long long)gridDim.x * NT) {
@@ -497,7 +513,14 @@ __global__ void broadcast_z_kernel(const float* __restrict__ z, float* const* w,
 }  // namespace
 
 // Sizes (in floats / words) of the peer-visible buffers a GPU must allocate for vectors of n elements.
-static inline long long chunk_for(long long n) { return n >= LARGE_N ? CHUNK_LARGE : CHUNK_SMALL; }
+// (tuning: floats per chunk of a large vector; a multiple of 4 * U * NT.  Must be the same on every rank and set before the
+// buffers of a synchroniser are sized.)
+static int g_chunk_large = CHUNK_LARGE;
+XB_API void xb_sync_set_large_chunk(int floats) {
+  const int unit = 4 * U * NT;
+  g_chunk_large = floats >= unit ? floats / unit * unit : CHUNK_LARGE;
+}
+static inline long long chunk_for(long long n) { return n >= LARGE_N ? g_chunk_large : CHUNK_SMALL; }
 XB_API long long xb_sync_chunk(long long n) { return chunk_for(n); }
 XB_API long long xb_sync_nchunks(long long n) { return (n + chunk_for(n) - 1) / chunk_for(n); }
 XB_API long long xb_sync_inbox_floats(long long n, int G, int two_shot) {
@@ -637,6 +660,16 @@ XB_API int xb_sync_stamp_words() { return XB_SYNC_STAMP_WORDS; }
 XB_API int xb_peer_copy(float* dst, const float* src, long long n, int blocks, cudaStream_t st) {
   if (n % 4 || blocks < 1) return -XB_BAD_ARG;
   peer_copy_kernel<<<blocks, NT, 0, st>>>(reinterpret_cast<float4*>(dst), reinterpret_cast<const float4*>(src), n / 4);
+  return (int)cudaGetLastError();
+}
+
+// dsts[i] <- srcs[i], n floats each (multiple of 4), for i < count <= 8, in one launch of blocks x count CTAs
+XB_API int xb_peer_copy_all(float* const* dsts, const float* const* srcs, int count, long long n, int blocks, cudaStream_t st) {
+  if (n % 4 || blocks < 1 || count < 1 || count > MAXG) return -XB_BAD_ARG;
+  PeerCopyAll a{};
+  for (int i = 0; i < count; ++i) { a.dst[i] = reinterpret_cast<float4*>(dsts[i]); a.src[i] = reinterpret_cast<const float4*>(srcs[i]); }
+  a.n4 = n / 4;
+  peer_copy_all_kernel<<<dim3(blocks, count), NT, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
 

@@ -86,6 +86,11 @@ struct XbProgram {
   int launches = 0;       // kernel launches issued by one replay (for accounting)
   int use_tc = 1;         // allow tensor-core convolution kernels
   int* tc_status = nullptr;
+  // Set by the learner that owns the program: the task parameters are then copied to `params_dst` by the learner itself
+  // at submission (from a per-task slot of a pinned ring), and the program's own first operator - the upload from the
+  // learner's single parameter block - is left out of captures and replays.
+  bool skip_upload = false;
+  void* params_dst = nullptr;
   std::vector<cudaEvent_t> capture_events;   // fork / join events of a capture with operator branches (live only during it)
   cudaStream_t side_stream = nullptr;
 };
@@ -250,21 +255,20 @@ static inline int run_op_traced(XbProgram* p, const XbOp& o, cudaStream_t st) {
   nvtxRangePop();
   return e;
 }
-XB_API int xb_program_run(XbProgram* p, cudaStream_t st) {
-  for (size_t i = 0; i < p->ops.size(); ++i) {
-    int e = run_op_traced(p, p->ops[i], st);
-    if (e != 0) return (int)(1000 * (i + 1) + (e < 0 ? -e : e));
-  }
-  return 0;
-}
-// Run a sub-range [first, last) - used by tests that inspect intermediate tensors.
-XB_API int xb_program_run_range(XbProgram* p, int first, int last, cudaStream_t st) {
+// (captures and the learner's own replays leave the upload operator out when the learner copies the parameters itself;
+// a program that is run directly - xb_program_run, xb_program_run_range - executes every operator)
+static inline bool skipped(const XbProgram* p, size_t i) { return p->skip_upload && i == 0 && p->ops[0].kind == OP_UPLOAD; }
+static int run_ops(XbProgram* p, int first, int last, cudaStream_t st, bool for_learner) {
   for (int i = first; i < last && i < (int)p->ops.size(); ++i) {
+    if (for_learner && skipped(p, (size_t)i)) continue;
     int e = run_op_traced(p, p->ops[i], st);
     if (e != 0) return 1000 * (i + 1) + (e < 0 ? -e : e);
   }
   return 0;
 }
+XB_API int xb_program_run(XbProgram* p, cudaStream_t st) { return run_ops(p, 0, (int)p->ops.size(), st, false); }
+// Run a sub-range [first, last) - used by tests that inspect intermediate tensors.
+XB_API int xb_program_run_range(XbProgram* p, int first, int last, cudaStream_t st) { return run_ops(p, first, last, st, false); }
 
 // Operator branches inside a task.  An operator flagged XB_OP_SIDE does not feed the operators that follow it in the list:
 // the weight (and bias) gradient of a layer is only read by the optimiser at the end of the task, while the chain
@@ -296,6 +300,7 @@ static int capture_with_branches(XbProgram* p, cudaStream_t st) {
   };
   for (size_t i = 0; i < p->ops.size() && e == 0; ++i) {
     const XbOp& o = p->ops[i];
+    if (skipped(p, i)) continue;
     if (o.flags & XB_OP_SIDE) {
       if (!side) {
         // the branch's kernels inherit this stream's priority in the graph: with g_side_low they only take what the main
@@ -331,7 +336,7 @@ XB_API int xb_program_capture(XbProgram* p, cudaStream_t st) {
   bool branches = false;
   for (const XbOp& o : p->ops) branches |= (o.flags & XB_OP_SIDE) != 0;
   XB_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-  int e = branches ? capture_with_branches(p, st) : xb_program_run(p, st);
+  int e = branches ? capture_with_branches(p, st) : run_ops(p, 0, (int)p->ops.size(), st, true);
   cudaGraph_t g = nullptr;
   cudaError_t ce = cudaStreamEndCapture(st, &g);
   for (cudaEvent_t ev : p->capture_events) cudaEventDestroy(ev);
@@ -353,7 +358,7 @@ XB_API int xb_program_capture_segments(XbProgram* p, cudaStream_t st) {
     while (last < n && p->ops[last].kind != OP_MARK) ++last;
     if (last < n) { mark = p->ops[last].ia[0]; ++last; }          // the mark closes the segment
     XB_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-    int e = xb_program_run_range(p, first, last, st);
+    int e = run_ops(p, first, last, st, true);
     cudaGraph_t g = nullptr;
     cudaError_t ce = cudaStreamEndCapture(st, &g);
     if (e != 0 || ce != cudaSuccess) { if (g) cudaGraphDestroy(g); drop_segments(p); return e != 0 ? e : (int)ce; }
@@ -380,6 +385,7 @@ XB_API int xb_program_launch_marked(XbProgram* p, cudaStream_t st, cudaEvent_t* 
   if (p->exec && p->marks == 0) return (int)cudaGraphLaunch(p->exec, st);
   for (size_t i = 0; i < p->ops.size(); ++i) {
     const XbOp& o = p->ops[i];
+    if (skipped(p, i)) continue;
     if (o.kind == OP_MARK) {
       if (o.ia[0] >= 0 && o.ia[0] < nmarks && marks && marks[o.ia[0]]) XB_CUDA_CHECK(cudaEventRecord(marks[o.ia[0]], st));
       continue;
@@ -404,7 +410,13 @@ struct XbLearner {
   XbProgram* test = nullptr;
   void* d_examples = nullptr; size_t examples_bytes = 0;
   void* d_labels = nullptr; size_t labels_bytes = 0;
-  XbTaskParams* h_params = nullptr;   // pinned; uploaded by the program's first node
+  XbTaskParams* h_params = nullptr;   // pinned; what a program's own upload operator reads (programs run outside a learner)
+  // A learner may hold several tasks in flight, and a copy enqueued on its stream reads its source when it EXECUTES, not
+  // when the task is submitted: each submission therefore writes its parameters into its own slot of this pinned ring and
+  // enqueues the host-to-device copy from that slot, so a task can never see the parameters of a later one (the learning
+  // rate at a schedule boundary, the task number that seeds dropout and crops).
+  static constexpr int PARAM_RING = 16;
+  XbTaskParams* h_params_ring = nullptr;
   float* h_result = nullptr;          // pinned + mapped: [loss, accuracy] written by the loss kernel
   float* d_result = nullptr;          // device alias of h_result
   // Run-ahead: a learner may hold several tasks in flight.  After each task a one-thread kernel copies the live result pair
@@ -429,6 +441,7 @@ XB_API XbLearner* xb_learner_create(int priority, void* d_examples, long long ex
   cudaEventCreateWithFlags(&l->done, cudaEventDisableTiming);
   cudaEventCreate(&l->start);
   cudaHostAlloc((void**)&l->h_params, sizeof(XbTaskParams), cudaHostAllocDefault);
+  cudaHostAlloc((void**)&l->h_params_ring, sizeof(XbTaskParams) * XbLearner::PARAM_RING, cudaHostAllocDefault);
   cudaHostAlloc((void**)&l->h_result, 64, cudaHostAllocMapped);
   for (int i = 0; i < XbLearner::RING; ++i) { cudaEventCreateWithFlags(&l->ring_done[i], cudaEventDisableTiming); l->ring_task[i] = ~0ull; }
   memset(l->h_params, 0, sizeof(XbTaskParams));
@@ -445,7 +458,7 @@ XB_API void xb_learner_destroy(XbLearner* l) {
   for (cudaEvent_t ev : l->bucket) if (ev) cudaEventDestroy(ev);
   for (cudaEvent_t ev : l->ring_done) if (ev) cudaEventDestroy(ev);
   for (int i = 0; i < XbLearner::RING; ++i) { if (l->ring_t0[i]) cudaEventDestroy(l->ring_t0[i]); if (l->ring_t1[i]) cudaEventDestroy(l->ring_t1[i]); }
-  cudaFreeHost(l->h_params); cudaFreeHost(l->h_result);
+  cudaFreeHost(l->h_params); cudaFreeHost(l->h_params_ring); cudaFreeHost(l->h_result);
   cudaStreamDestroy(l->stream);
   delete l;
 }
@@ -453,7 +466,14 @@ XB_API void* xb_learner_stream(XbLearner* l) { return (void*)l->stream; }
 XB_API XbTaskParams* xb_learner_params(XbLearner* l) { return l->h_params; }
 XB_API float* xb_learner_result_host(XbLearner* l) { return l->h_result; }
 XB_API float* xb_learner_result_dev(XbLearner* l) { return l->d_result; }
-XB_API void xb_learner_set_programs(XbLearner* l, XbProgram* train, XbProgram* test) { l->train = train; l->test = test; }
+XB_API void xb_learner_set_programs(XbLearner* l, XbProgram* train, XbProgram* test) {
+  l->train = train; l->test = test;
+  for (XbProgram* p : {train, test})
+    if (p && !p->ops.empty() && p->ops[0].kind == OP_UPLOAD && p->ops[0].p[1] == (void*)l->h_params
+        && (size_t)p->ops[0].la[0] == sizeof(XbTaskParams)) {
+      p->skip_upload = true; p->params_dst = p->ops[0].p[0];      // (call this before the program is captured)
+    }
+}
 
 // Enqueue one task: copy the batch from (pinned) host memory, replay the program, record the completion event.
 // phase 0 = train, 1 = test.  Never blocks.
@@ -467,6 +487,11 @@ static int learner_submit_tagged(XbLearner* l, const void* h_examples, const voi
   XbProgram* p = phase == 0 ? l->train : l->test;
   if (!p) return -XB_BAD_ARG;
   *l->h_params = *params;
+  if (p->skip_upload) {
+    XbTaskParams* mine = l->h_params_ring + (l->submitted.load() % XbLearner::PARAM_RING);
+    *mine = *params;
+    XB_CUDA_CHECK(cudaMemcpyAsync(p->params_dst, mine, sizeof(XbTaskParams), cudaMemcpyHostToDevice, l->stream));
+  }
   if (h_examples) XB_CUDA_CHECK(cudaMemcpyAsync(l->d_examples, h_examples, l->examples_bytes, cudaMemcpyHostToDevice, l->stream));
   if (h_labels) XB_CUDA_CHECK(cudaMemcpyAsync(l->d_labels, h_labels, l->labels_bytes, cudaMemcpyHostToDevice, l->stream));
   if (p->marks > 0)

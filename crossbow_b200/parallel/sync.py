@@ -109,6 +109,12 @@ class FusedSynchroniser:
             elif self.two_shot:
                 # peer-visible home for the central model: chunk owners then store the updated model straight into it
                 self.zbuf = PeerBuffer(4 * n, rank, world, group)
+        if world > 1 and parent is None:
+            # every rank has mapped every peer's buffers before anyone launches a kernel that waits on a peer: mapping
+            # can take seconds on one rank and milliseconds on another, more than a bounded device wait allows
+            import torch.distributed as dist
+            torch.cuda.synchronize()
+            dist.barrier(group)
 
     def make_buckets(self, ranges) -> List["FusedSynchroniser"]:
         """One child synchroniser per (offset, elements) range, in the given order (collective: every rank must pass the

@@ -30,6 +30,8 @@ def main():
     ap.add_argument("--sizes", default="464154,25557032")
     ap.add_argument("--replicas", default="1,2,4")
     ap.add_argument("--two-shot", default="auto")
+    ap.add_argument("--large-chunk", type=int, default=0, help="tuning: floats per chunk of the two-shot exchange (default 16384)")
+    ap.add_argument("--max-blocks", type=int, default=0, help="tuning: CTAs of the fused kernel (default: two per SM)")
     ap.add_argument("--nvls", action="store_true", help="also time the NVLink-multicast (multimem) variant of the two-shot exchange")
     a = ap.parse_args()
     import torch.distributed as dist
@@ -41,6 +43,8 @@ def main():
     torch.cuda.set_device(local)
     init_process_group("nccl")
     lib = L.init_device()
+    if a.large_chunk:
+        lib.xb_sync_set_large_chunk(a.large_chunk)
     bw, _, how = peaks()
     from ..utils.gpumon import ClockSampler
     from .peer import PeerBuffer
@@ -74,10 +78,14 @@ def main():
         src = torch.randn(part * world, device="cuda")
         s = stream.cuda_stream
 
+        import ctypes as C
+        peers = [g for g in range(world) if g != rank]
+        dsts = (C.c_void_p * len(peers))(*[buf.ptrs[g] + 4 * part * rank for g in peers])
+        srcs = (C.c_void_p * len(peers))(*[src.data_ptr() + 4 * part * g for g in peers])
+        blocks = max(16, 592 // len(peers))            # ~4 CTAs per SM in total, all destinations in flight at once
+
         def push():
-            for g in range(world):
-                if g != rank:
-                    L.check(lib.xb_peer_copy(buf.ptrs[g] + 4 * part * rank, src.data_ptr() + 4 * part * g, part, 148, s), "peer copy")
+            L.check(lib.xb_peer_copy_all(dsts, srcs, len(peers), part, blocks, s), "peer copy")
         with torch.cuda.stream(stream):
             us = timed(push)
         torch.cuda.synchronize()
@@ -93,8 +101,8 @@ def main():
             ws = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
             ps = [torch.randn(n, device="cuda", generator=g) * 0.01 for _ in range(k)]
             two = None if a.two_shot == "auto" else a.two_shot == "1"
-            fs = FusedSynchroniser(n, rank, world, two_shot=two)
-            fn = FusedSynchroniser(n, rank, world, two_shot=two, nvls=True) if (a.nvls and world > 1 and fs.two_shot) else None
+            fs = FusedSynchroniser(n, rank, world, two_shot=two, max_blocks=a.max_blocks)
+            fn = FusedSynchroniser(n, rank, world, two_shot=two, nvls=True, max_blocks=a.max_blocks) if (a.nvls and world > 1 and fs.two_shot) else None
             # the central model lives where the synchroniser wants it (peer-visible memory when chunk owners store into it)
             z = fs.central_storage()
             z = z.zero_() if z is not None else torch.zeros(n, device="cuda")
@@ -126,7 +134,7 @@ def main():
             if rank == 0:
                 print(json.dumps({"op": "sma_sync", "n": n, "replicas": k, "gpus": world, "two_shot": fs.two_shot, "owner_apply": bool(fs.owner_apply and world > 1),
                                   "fused_us": round(t_f, 2), "reference_us": round(t_r, 2), "speedup": round(t_r / t_f, 2),
-                                  "release_us": round(tl["release_us"], 2),
+                                  "release_us": round(tl["release_us"], 2), "chunk_floats": int(lib.xb_sync_chunk(n)), "max_blocks": a.max_blocks,
                                   "nvls_us": round(t_n, 2) if t_n else None,
                                   "nvls_fraction_of_roofline_900": round(t_nom / t_n, 3) if t_n else None,
                                   "peer_store_gbs": round(peer_gbs, 1) if peer_gbs else None,

@@ -265,3 +265,33 @@ def test_operator_branches_change_nothing_but_the_schedule(name, use_tc):
     (la, za, ra), (lb, zb, rb) = outs
     assert np.allclose(la, lb, rtol=2e-3, atol=1e-5)
     assert np.abs(za - zb).max() <= 2e-3 * np.abs(za).max() and np.abs(ra - rb).max() <= 2e-3 * np.abs(ra).max()
+
+
+def test_tasks_in_flight_keep_their_own_parameters():
+    """A learner may hold several tasks in flight; the parameters of a task (learning rate, task number) are read on the
+    device when the task runs, which can be after the NEXT task has been submitted.  Each task must still see its own:
+    task A runs with learning rate 0 (the weights stay put), task B on the same batch must report exactly A's loss."""
+    import ctypes as C
+    from crossbow_b200.engine import GpuEngine
+    from crossbow_b200.ops import lib as L
+    from helpers import build_model
+    spec, m, solver = build_model("lenet-caffe", 8)
+    eng = GpuEngine(spec.train, None, m, m.initial_values(7), 8, spec.input_shape, solver, UpdateModel.SMA, replicas=1, wpc=1)
+    try:
+        lib, ln = eng.lib, eng.learners[0]
+        xs, ys = make_batches(spec, 8, 1, seed=9)
+        x, y = xs[0].pin_memory(), ys[0].pin_memory()
+        w0 = ln.rep.w.clone()
+        L.check(lib.xb_sleep(30_000_000, ln.stream), "sleep")          # ~15 ms: both submissions happen before task A starts
+        pa, pb = eng.params(0, True), eng.params(1, True)
+        pa.lr, pb.lr = 0.0, 0.5
+        ln.submit(x, y, pa, Phase.TRAIN)
+        ln.submit(x, y, pb, Phase.TRAIN)
+        la, lb, acc = C.c_float(), C.c_float(), C.c_float()
+        L.check(lib.xb_learner_wait_task(ln.handle, pa.task_id, 0, C.byref(la), C.byref(acc)), "wait A")
+        L.check(lib.xb_learner_wait_task(ln.handle, pb.task_id, 0, C.byref(lb), C.byref(acc)), "wait B")
+        eng.finish()
+        assert la.value == lb.value and la.value > 0                     # A did not move the weights
+        assert float((ln.rep.w - w0).abs().max()) > 0                    # B did
+    finally:
+        eng.destroy()
