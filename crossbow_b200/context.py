@@ -230,6 +230,7 @@ class ExecutionContext:
         ci = self.sys.checkpoint_interval if self.sys.checkpoint_directory else 0
         done = 0
         tuned_tasks, tuned_time = 0, 0.0                    # since the last auto-tuner decision
+        settle = 0                                          # chunks left out of the next sample (a new replica's first tasks)
         stop = threading.Event()
         period = max(0.01, min(0.2, self.sys.monitor_interval / 1000.0 if self.sys.monitor_interval > 0 else 0.2))
 
@@ -259,10 +260,16 @@ class ExecutionContext:
                 if self.autotuner is not None and self.autotuner.active:
                     # one throughput sample per monitor interval, as the reference's monitor takes them
                     # (PerformanceMonitor.java:59-104); the tuner compares the latest sample with the one before
-                    tuned_tasks, tuned_time = tuned_tasks + issued, tuned_time + dt
-                    if tuned_time >= self.sys.monitor_interval / 1000.0 or done >= ntasks:
+                    # (the first chunk after a replica has been added is left out: its graphs are uploaded to the device on
+                    # their first launch, which is not the throughput the new replica count will have)
+                    if settle > 0 and done < ntasks:
+                        settle -= 1
+                    else:
+                        tuned_tasks, tuned_time = tuned_tasks + issued, tuned_time + dt
+                    if tuned_tasks and (tuned_time >= self.sys.monitor_interval / 1000.0 or done >= ntasks):
                         self.monitor.samples.append(self._job_rate(tuned_tasks * self.mc.batch_size / max(tuned_time, 1e-9)))
-                        self._autotune(list(self.monitor.samples), rt)
+                        if self._autotune(list(self.monitor.samples), rt) != 0:
+                            settle = 1
                         tuned_tasks, tuned_time = 0, 0.0
                 if ci > 0 and rt.tasks_issued() % wpc == 0 and rt.clock() % ci == 0:
                     self.checkpoint()
