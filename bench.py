@@ -266,7 +266,7 @@ def main():
     ap.add_argument("--nvls", action="store_true", help="two-shot exchange through NVLink multicast (multimem) instead of peer stores")
     ap.add_argument("--side-low-priority", action="store_true", help="tuning: the weight-gradient branch of the task graph runs at the lowest stream priority")
     ap.add_argument("--fuse-bn-sums", action="store_true", help="tuning: data-gradient kernels produce the batch-norm backward sums in their epilogue")
-    ap.add_argument("--gemm-smem", default="", help="tuning: shared-memory budgets of the TMA GEMM pipeline in KB, 'many,few' (default 108,200)")
+    ap.add_argument("--gemm-smem", default="", help="tuning: shared-memory budgets of the TMA GEMM pipeline in KB, 'many,few' (default 54,100)")
     ap.add_argument("--tma-conv-min", type=int, default=0, help="tuning: fewest channels for which R x S convolutions take the TMA implicit GEMM (default 32)")
     ap.add_argument("--no-library-arm", action="store_true", help="skip the library (cuDNN) arm that gives vs_baseline")
     ap.add_argument("--no-resnet50", action="store_true", help="skip the nested ResNet-50 run of the default benchmark")

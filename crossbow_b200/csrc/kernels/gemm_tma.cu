@@ -317,9 +317,12 @@ int make_map(CUtensorMap* m, const void* base, int rank, const cuuint64_t* dims,
 }
 
 constexpr size_t kSmemLimit = 200 * 1024;
-// Shared-memory budgets of the operand pipeline (tuning): `g_budget_many` when the grid has more CTAs than SMs (two CTAs
-// then share an SM), `g_budget_few` otherwise.  Smaller budgets leave room for other replicas' CTAs on the same SM.
-static size_t g_budget_many = 108 * 1024, g_budget_few = kSmemLimit;
+// Shared-memory budgets of the operand pipeline: `g_budget_many` when the grid has more CTAs than SMs, `g_budget_few`
+// otherwise.  A CTA of a small grid used to take up to 200 KB for a deep pipeline; that kept every other replica's
+// GEMM CTAs off its SM, and with four replicas per GPU the whole step paid for it: at 54 / 100 KB ResNet-32 (k = 4) went
+// from 105.8 K to 117.0 K images/s, VGG-16 (k = 4) from 84.1 K to 87.7 K, ResNet-50 (k = 2) from 5.24 K to 5.28 K, and one
+// replica alone lost nothing (47.7 K -> 47.9 K).
+static size_t g_budget_many = 54 * 1024, g_budget_few = 100 * 1024;
 inline size_t stage_bytes(int BN, int kc = 1) { return (size_t)kc * (A_BYTES + (size_t)BN * 128); }
 // Pipeline depth: as deep as the reduction, within a shared-memory budget that still lets two CTAs share an SM when the
 // grid has more CTAs than SMs (the second CTA's loads and MMAs then overlap the first one's epilogue).
@@ -385,8 +388,8 @@ inline bool is_1x1(const XbConvGeom* g) { return g->R == 1 && g->S == 1 && g->ph
 
 XB_API void xb_gemm_set_tn_ctas(int n) { g_tn_ctas = n > 0 ? n : 111; }
 XB_API void xb_gemm_set_smem_budgets(int many_kb, int few_kb) {
-  g_budget_many = many_kb > 0 ? (size_t)(many_kb < 200 ? many_kb : 200) * 1024 : 108 * 1024;
-  g_budget_few = few_kb > 0 ? (size_t)(few_kb < 200 ? few_kb : 200) * 1024 : kSmemLimit;
+  g_budget_many = many_kb > 0 ? (size_t)(many_kb < 200 ? many_kb : 200) * 1024 : 54 * 1024;
+  g_budget_few = few_kb > 0 ? (size_t)(few_kb < 200 ? few_kb : 200) * 1024 : 100 * 1024;
 }
 XB_API int xb_gemm_tma_init() {
   int e;
