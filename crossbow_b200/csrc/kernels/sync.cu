@@ -29,12 +29,6 @@
 // for the end of the kernel: the replicas' next forward pass runs under the exchange and the central update, and a
 // learner never waits for another GPU.  The reference gets the same overlap by recording each replica's `updated`
 // event right after its correction, before the all-reduce is issued (clib-multigpu/synch/sma.c:108-118, :130).
-// Bulk stores (two-shot with owner-apply, the path large vectors take on several GPUs): the 16 KB a block produces per
-// step - a slice of its partial sums in phase 1, of the new central model in phase 2 - is staged in shared memory and
-// leaves the SM as ONE cp.async.bulk (shared -> global, a plain store to one destination) per destination GPU instead of 1024 16-byte stores
-// per destination.  The copies are asynchronous: the threads go on with the next step's loads while the copy engine of
-// the SM streams the slot over NVLink, a ring of three slots decouples the two, and the ready flag of a chunk is raised
-// one step into the next chunk, after cp.async.bulk.wait_group has shown the chunk's copies complete.
 // NVLS variant (two-shot with owner-apply, optional): the partial sums stay in each GPU's own memory, which is bound to an
 // NVLink multicast object; the owner of a chunk reads the SUM of all GPUs' partials with one multimem.ld_reduce per 16
 // bytes (the switch fetches and adds the eight copies) and stores the new central model into every GPU with one
@@ -81,7 +75,6 @@ struct SyncArgs {
   // NVLS variant: this GPU's partial buffer (2 x n floats, by epoch parity), the multicast address of the same buffer on
   // all GPUs, and the multicast address of every GPU's central model; all null when the variant is off
   float* part_local; const float* part_mc; float* z_mc;
-  int bulk;                    // stage outgoing slices in shared memory and send them with cp.async.bulk
   unsigned int* release;       // [0] release word (epoch once every replica of this GPU is corrected), [1] block counter; may be null
   unsigned long long* stamps;  // time line, see XB_SYNC_STAMP_*; may be null
 };
@@ -93,7 +86,6 @@ struct SyncArgs {
 enum { XB_SYNC_STAMP_ENTRY = 0, XB_SYNC_STAMP_RELEASE = 1, XB_SYNC_STAMP_EXIT = 2 /* and 3 */, XB_SYNC_STAMP_COUNT = 4,
        XB_SYNC_STAMP_SUM_RELEASE = 5, XB_SYNC_STAMP_SUM_TOTAL = 6, XB_SYNC_STAMP_WORDS = 8 };
 
-__device__ __forceinline__ uint32_t smem_addr_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -131,42 +123,6 @@ __device__ __forceinline__ float4 multimem_ld_reduce_add(const float* mc) {
 // the same 16 bytes stored into every GPU of the multicast group
 __device__ __forceinline__ void multimem_st(float* mc, float4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
-}
-
-// ---- asynchronous bulk copies shared -> global (this GPU's or a peer's memory; 16-byte aligned, size a multiple of 16) ----
-__device__ __forceinline__ void bulk_store(void* gdst, uint32_t ssrc, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(ssrc), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
-template <int N> __device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
-
-constexpr int BULK_SLOTS = 3;
-constexpr int BULK_SLOT_BYTES = 4 /* = U */ * 256 /* = NT */ * 16;       // one step of a block: U float4 lanes per thread
-// Ring of staging slots in dynamic shared memory.  Every thread of the block calls stage() with the same sequence of
-// steps (it contains block barriers); thread 0 alone issues, commits and waits for the copies.
-struct BulkRing {
-  unsigned char* base; uint32_t base_u32; int steps;
-  __device__ __forceinline__ uint32_t stage(const float4 (&v)[4]) {
-    const int slot = steps % BULK_SLOTS;
-    if (threadIdx.x == 0) bulk_wait_read<BULK_SLOTS - 1>();       // the copies that last read this slot are done reading
-    __syncthreads();
-    float4* sl = reinterpret_cast<float4*>(base + slot * BULK_SLOT_BYTES);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) sl[threadIdx.x + u * NT] = v[u];
-    fence_proxy_async_smem();                                     // generic-proxy writes before the async-proxy reads
-    __syncthreads();
-    ++steps;
-    return base_u32 + slot * BULK_SLOT_BYTES;
-  }
-};
-// thread 0: every copy it has committed (but the newest `keep`) has completed; order them before the flag stores that follow
-template <int KEEP> __device__ __forceinline__ void bulk_complete() {
-  bulk_wait<KEEP>();
-  fence_proxy_async_all();
-  __threadfence_system();
 }
 
 __device__ __forceinline__ float4 f4add(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
@@ -306,7 +262,6 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
   // the argument block is read thousands of times (pointer tables): keep a copy in shared memory
   __shared__ SyncArgs a;
   __shared__ int s_fail;
-  extern __shared__ __align__(128) unsigned char s_bulk[];   // BULK_SLOTS staging slots when the launch uses bulk stores
   {
     const int* src = reinterpret_cast<const int*>(per_rank + blockIdx.y);
     int* dst = reinterpret_cast<int*>(&a);
@@ -333,14 +288,10 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
     return;
   }
 
-  static_assert(U == 4 && BULK_SLOT_BYTES == U * NT * 16, "staging slot = one step of a block");
-  BulkRing ring{s_bulk, smem_addr_u32(s_bulk), 0};
-  const bool bulk = a.bulk != 0;
   const int owned_slots = (a.nchunks + G - 1) / G;
   const long long slot_elems = (long long)(a.two_shot ? owned_slots : a.nchunks) * CHUNK;
 
   // ---- phase 1: local reduce, replica correction, push partials -------------------------------------------
-  int pend_c = -1;                  // (thread 0, bulk stores) chunk whose copies are in flight and whose flag is still due
   for (int c = blockIdx.x; c < a.nchunks; c += B) {
     const int owner = c % G;
     const long long dst_chunk = a.two_shot ? (c / G) : c;
@@ -355,18 +306,6 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
         float4* dst = reinterpret_cast<float4*>(a.part_local) + ((long long)parity * a.nchunks + c) * (CHUNK / 4);
 #pragma unroll
         for (int u = 0; u < U; ++u) dst[j0 + u * NT] = acc[u];
-      } else if (bulk) {
-        // one asynchronous 16 KB copy into the owner's inbox instead of U * NT stores
-        const uint32_t slot = ring.stage(acc);
-        if (tid == 0) {
-          bulk_store(reinterpret_cast<float4*>(a.inbox[owner]) + off4 + (j0 - tid), slot, BULK_SLOT_BYTES);
-          bulk_commit();
-          if (pend_c >= 0) {        // the previous chunk's copies have had a whole step to finish: raise its flag now
-            bulk_complete<1>();
-            st_release_sys(a.ready1[pend_c % G] + (long long)me * a.nchunks + pend_c, a.epoch);
-            pend_c = -1;
-          }
-        }
       } else if (a.two_shot) {
 #pragma unroll
         for (int u = 0; u < U; ++u) reinterpret_cast<float4*>(a.inbox[owner])[off4 + j0 + u * NT] = acc[u];
@@ -377,7 +316,6 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
         }
       }
     }
-    if (bulk && !a.part_local) { pend_c = c; continue; }
     __syncthreads();
     if (a.two_shot) {
       if (tid == 0) { __threadfence_system(); st_release_sys(a.ready1[owner] + (long long)me * a.nchunks + c, a.epoch); }
@@ -385,11 +323,6 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
       __threadfence_system();
       st_release_sys(a.ready1[tid] + (long long)me * a.nchunks + c, a.epoch);
     }
-  }
-  if (tid == 0 && pend_c >= 0) {     // the last chunk's copies
-    bulk_complete<0>();
-    st_release_sys(a.ready1[pend_c % G] + (long long)me * a.nchunks + pend_c, a.epoch);
-    pend_c = -1;
   }
   // every replica chunk this block is responsible for now holds its corrected weights
   if (!(a.copy_to_replicas || a.algo != ALGO_SMA)) release_replicas(a);
@@ -461,21 +394,6 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
           if (a.z_mc) {
 #pragma unroll
             for (int u = 0; u < U; ++u) if (okk[u]) multimem_st(a.z_mc + 4 * i4[u], z[u]);
-          } else if (bulk) {
-            // the new slice of the central model goes to every GPU as one asynchronous copy each
-            const uint32_t slot = ring.stage(z);
-            if (tid == 0) {
-              const long long first4 = (long long)c * (CHUNK / 4) + (j0 - tid);
-              const long long valid4 = n4 - first4 < (long long)(U * NT) ? n4 - first4 : (long long)(U * NT);
-              if (valid4 > 0)
-                for (int g = 0; g < G; ++g) bulk_store(reinterpret_cast<float4*>(a.zpeer[g]) + first4, slot, (uint32_t)(valid4 * 16));
-              bulk_commit();
-              if (pend_c >= 0) {
-                bulk_complete<1>();
-                for (int g = 0; g < G; ++g) st_release_sys(a.ready2[g] + pend_c, a.epoch);
-                pend_c = -1;
-              }
-            }
           } else
           for (int g = 0; g < G; ++g) {
 #pragma unroll
@@ -484,13 +402,7 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
         }
       }
       __syncthreads();
-      if (bulk && a.owner_apply && !a.z_mc) { if (ok) pend_c = c; }      // (the flags follow the copies, one step into the next chunk)
-      else if (ok && tid < G) { __threadfence_system(); st_release_sys(a.ready2[tid] + c, a.epoch); }
-    }
-    if (tid == 0 && pend_c >= 0) {
-      bulk_complete<0>();
-      for (int g = 0; g < G; ++g) st_release_sys(a.ready2[g] + pend_c, a.epoch);
-      pend_c = -1;
+      if (ok && tid < G) { __threadfence_system(); st_release_sys(a.ready2[tid] + c, a.epoch); }
     }
   }
 
@@ -640,19 +552,6 @@ struct XbSyncDesc {
   unsigned long long* stamps;     // XB_SYNC_STAMP_WORDS 64-bit words owned by the caller (zero-initialised once), or null
 };
 
-static int g_sync_bulk = 1;
-XB_API void xb_sync_set_bulk(int on) { g_sync_bulk = on ? 1 : 0; }
-static size_t bulk_smem(const SyncArgs& a) { return a.bulk ? (size_t)BULK_SLOTS * BULK_SLOT_BYTES : 0; }
-static int allow_bulk_smem() {
-  static int done = 0;
-  if (!done) {
-    cudaError_t e = cudaFuncSetAttribute(fused_sync_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BULK_SLOTS * BULK_SLOT_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    done = 1;
-  }
-  return 0;
-}
-
 static void fill_args(SyncArgs& a, const XbSyncDesc& d) {
   memset(&a, 0, sizeof(a));
   a.rank = d.rank; a.G = d.G; a.k = d.k; a.algo = d.algo; a.n = d.n; a.nchunks = (int)xb_sync_nchunks(d.n); a.chunk = (int)chunk_for(d.n);
@@ -671,7 +570,6 @@ static void fill_args(SyncArgs& a, const XbSyncDesc& d) {
   a.timeout_ns = (unsigned long long)(d.timeout_s * 1e9);
   a.release = d.release; a.stamps = d.stamps;
   const bool nvls = a.owner_apply && d.part_local && d.part_mc && d.z_mc;
-  a.bulk = (g_sync_bulk && a.owner_apply && !nvls && a.chunk % (4 * U * NT) == 0) ? 1 : 0;
   a.part_local = nvls ? d.part_local : nullptr; a.part_mc = nvls ? d.part_mc : nullptr; a.z_mc = nvls ? d.z_mc : nullptr;
 }
 XB_API long long xb_sync_part_floats(long long n) { return 2LL * xb_sync_nchunks(n) * chunk_for(n); }
@@ -696,15 +594,13 @@ XB_API int xb_fused_sync(const XbSyncDesc* d, void* args_dev, void* args_pinned,
       int dev = 0, sms = 148, per_sm = 1;
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      // (occupancy with the bulk path's staging slots: the larger footprint of the two)
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_sync_kernel, NT, (size_t)BULK_SLOTS * BULK_SLOT_BYTES);
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_sync_kernel, NT, 0);
       cached = sms * (per_sm >= 2 ? 2 : 1);
     }
     max_blocks = cached;
   }
   dim3 grid(sync_grid(h->nchunks, max_blocks), 1);
-  if (h->bulk) { int e = allow_bulk_smem(); if (e) return e; }
-  fused_sync_kernel<<<grid, NT, bulk_smem(*h), st>>>(reinterpret_cast<const SyncArgs*>(args_dev));
+  fused_sync_kernel<<<grid, NT, 0, st>>>(reinterpret_cast<const SyncArgs*>(args_dev));
   return (int)cudaGetLastError();
 }
 
@@ -719,16 +615,13 @@ XB_API int xb_fused_sync_emulated(const XbSyncDesc* descs, int G, void* args_dev
   int dev = 0, sms = 0, per_sm = 0;
   XB_CUDA_CHECK(cudaGetDevice(&dev));
   XB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  size_t smem = 0;
-  for (int g = 0; g < G; ++g) if (bulk_smem(h[g]) > smem) smem = bulk_smem(h[g]);
-  if (smem) { int e = allow_bulk_smem(); if (e) return e; }
-  XB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_sync_kernel, NT, smem));
+  XB_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_sync_kernel, NT, 0));
   int bpr = sync_grid(h[0].nchunks, blocks_per_rank > 0 ? blocks_per_rank : 16);
   while (bpr > 1 && (long long)bpr * G > (long long)sms * per_sm) --bpr;
   dim3 grid(bpr, G);
   const SyncArgs* p = reinterpret_cast<const SyncArgs*>(args_dev);
   void* kargs[] = {(void*)&p};
-  XB_CUDA_CHECK(cudaLaunchCooperativeKernel((void*)fused_sync_kernel, grid, dim3(NT), kargs, smem, st));
+  XB_CUDA_CHECK(cudaLaunchCooperativeKernel((void*)fused_sync_kernel, grid, dim3(NT), kargs, 0, st));
   return (int)cudaGetLastError();
 }
 

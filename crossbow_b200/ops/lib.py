@@ -147,7 +147,6 @@ def load() -> C.CDLL:
     _sig(lib, "xb_peer_copy", I, P, P, L, I, P)
     _sig(lib, "xb_peer_copy_all", I, P, P, I, L, I, P)
     _sig(lib, "xb_sync_set_large_chunk", None, I)
-    _sig(lib, "xb_sync_set_bulk", None, I)
     _sig(lib, "xb_gemm_set_smem_budgets", None, I, I)
     _sig(lib, "xb_stream_wait_value32", I, P, P, c_uint)
     _sig(lib, "xb_stream_wait_value_supported", I)

@@ -32,7 +32,6 @@ def main():
     ap.add_argument("--two-shot", default="auto")
     ap.add_argument("--large-chunk", type=int, default=0, help="tuning: floats per chunk of the two-shot exchange (default 16384)")
     ap.add_argument("--max-blocks", type=int, default=0, help="tuning: CTAs of the fused kernel (default: two per SM)")
-    ap.add_argument("--no-bulk", action="store_true", help="tuning: plain 16-byte stores instead of cp.async.bulk slices in the two-shot exchange")
     ap.add_argument("--nvls", action="store_true", help="also time the NVLink-multicast (multimem) variant of the two-shot exchange")
     a = ap.parse_args()
     import torch.distributed as dist
@@ -44,8 +43,6 @@ def main():
     torch.cuda.set_device(local)
     init_process_group("nccl")
     lib = L.init_device()
-    if a.no_bulk:
-        lib.xb_sync_set_bulk(0)
     if a.large_chunk:
         lib.xb_sync_set_large_chunk(a.large_chunk)
     bw, _, how = peaks()
@@ -137,7 +134,7 @@ def main():
             if rank == 0:
                 print(json.dumps({"op": "sma_sync", "n": n, "replicas": k, "gpus": world, "two_shot": fs.two_shot, "owner_apply": bool(fs.owner_apply and world > 1),
                                   "fused_us": round(t_f, 2), "reference_us": round(t_r, 2), "speedup": round(t_r / t_f, 2),
-                                  "release_us": round(tl["release_us"], 2), "chunk_floats": int(lib.xb_sync_chunk(n)), "max_blocks": a.max_blocks, "bulk_stores": not a.no_bulk,
+                                  "release_us": round(tl["release_us"], 2), "chunk_floats": int(lib.xb_sync_chunk(n)), "max_blocks": a.max_blocks,
                                   "nvls_us": round(t_n, 2) if t_n else None,
                                   "nvls_fraction_of_roofline_900": round(t_nom / t_n, 3) if t_n else None,
                                   "peer_store_gbs": round(peer_gbs, 1) if peer_gbs else None,

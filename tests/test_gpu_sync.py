@@ -93,9 +93,8 @@ def _owned(n, G, g):
                                         (2, 1, 0, (4 << 20) + 16384 * 5 + 4096 + 8), (3, 2, 0, (4 << 20) + 16384 * 2 + 12)])
 def test_owner_apply_matches_oracle(G, k, algo, n):
     """Two-shot exchange in which the owner of a chunk updates the central model and stores it on every GPU; the
-    momentum of the central model is then kept by the owners only.  The slices travel as asynchronous bulk copies staged in
-    shared memory: one step per 16 KB chunk for the small vectors, four steps per 64 KB chunk (and a ragged last chunk) for
-    the vectors above four million elements."""
+    momentum of the central model is then kept by the owners only.  Small vectors use 16 KB chunks; the two cases above four
+    million elements use 64 KB chunks, four steps per chunk, with a ragged last chunk."""
     devs = _state(G, k, n, seed=7)
     kw = {0: dict(alpha=0.1, mu=0.9), 1: dict(mu=0.9, scale=1.0 / (G * k)), 2: dict(alpha=0.05, scale=1.0 / (G * k), blend=1.0, epochs=1)}[algo]
     for e, W, Z, ZL, GA in _run_emulated(devs, n, algo, True, owner_apply=True, **kw):
