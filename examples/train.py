@@ -30,7 +30,7 @@ def main(argv=None):
     CommandLine(opts).parse(argv)
     sysc, mc = SystemConf.getInstance(), ModelConf.getInstance()
     spec = build(opts.get("--model").get(), solver_conf=mc.getSolverConf())
-    if sysc.gpu:
+    if int(os.environ.get("WORLD_SIZE", 1)) > 1:      # one process per GPU (nccl) or per CPU device group (gloo)
         from crossbow_b200.parallel.peer import init_process_group
         init_process_group()
     if opts.get("--metadata").get():
