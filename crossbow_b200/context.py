@@ -48,6 +48,8 @@ class ExecutionContext:
         self._disp_n, self._disp_loss, self._disp_acc = 0, 0.0, 0.0
         self.monitor: Optional[PerformanceMonitor] = None
         self.autotuner: Optional[AutoTuner] = None
+        self._tune = {"tasks": 0, "time": 0.0, "settle": 0, "rate": 0.0}   # since the last decision; tasks/s of the last chunk
+        self.autotune_chunks = []                         # (replicas, tasks, seconds, settling) of every chunk issued while tuning
         self.autotune_trace = []                          # (replicas per GPU after the decision, job examples/s it was based on)
         self.rank, self.world = 0, 1
         self.tasks_done = 0
@@ -202,6 +204,19 @@ class ExecutionContext:
         dist.all_reduce(t)
         return float(t.item())
 
+    def _slowest(self, seconds: float) -> float:
+        """The largest of the ranks' values (the value itself in a one-process job)."""
+        if self.world <= 1:
+            return seconds
+        import torch
+        import torch.distributed as dist
+        if not (dist.is_available() and dist.is_initialized()):
+            return seconds
+        dev = "cuda" if (self.sys.gpu and dist.get_backend() == "nccl") else "cpu"
+        t = torch.tensor([seconds], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     def _autotune(self, samples, rt=None) -> int:
         """One auto-tuner decision, applied to the engine (and the native runtimes); returns the change in replicas."""
         e = self.engine
@@ -229,8 +244,8 @@ class ExecutionContext:
         wpc = self.clock.wpc
         ci = self.sys.checkpoint_interval if self.sys.checkpoint_directory else 0
         done = 0
-        tuned_tasks, tuned_time = 0, 0.0                    # since the last auto-tuner decision
-        settle = 0                                          # chunks left out of the next sample (a new replica's first tasks)
+        tune = self._tune                                   # sampling state of the auto-tuner: outlives the call, as the
+                                                            # reference's monitor thread does (PerformanceMonitor.java:59-104)
         stop = threading.Event()
         period = max(0.01, min(0.2, self.sys.monitor_interval / 1000.0 if self.sys.monitor_interval > 0 else 0.2))
 
@@ -245,8 +260,14 @@ class ExecutionContext:
             while done < ntasks:
                 # a chunk ends where the host has something to do between two clocks: an auto-tuner decision, a checkpoint
                 n = ntasks - done
-                if self.autotuner is not None and self.autotuner.active:
-                    n = min(n, max(wpc, self.sys.autotune_interval * wpc * 4))
+                tuning = self.autotuner is not None and self.autotuner.active
+                if tuning:
+                    # about one chunk per monitor interval (every chunk ends with a drained pipeline, and a sample made of
+                    # many short chunks reads several per cent low, more so the more replicas there are to refill); the
+                    # chunk that lets a new replica settle, and the first one of all, are short
+                    short = max(wpc, self.sys.autotune_interval * wpc * 4)
+                    per_interval = int(tune["rate"] * self.sys.monitor_interval / 1000.0) // wpc * wpc if tune["settle"] == 0 else 0
+                    n = min(n, max(short, per_interval))
                 if ci > 0:
                     to_next = (ci - rt.clock() % ci) * wpc - (rt.tasks_issued() % wpc)
                     n = min(n, max(1, to_next))
@@ -257,20 +278,26 @@ class ExecutionContext:
                 done += issued
                 if issued < n:
                     break                                   # target loss reached
-                if self.autotuner is not None and self.autotuner.active:
-                    # one throughput sample per monitor interval, as the reference's monitor takes them
-                    # (PerformanceMonitor.java:59-104); the tuner compares the latest sample with the one before
-                    # (the first chunk after a replica has been added is left out: its graphs are uploaded to the device on
-                    # their first launch, which is not the throughput the new replica count will have)
-                    if settle > 0 and done < ntasks:
-                        settle -= 1
+                if tuning:
+                    # Every rank issues the same chunks, so the slowest rank's time is the job's: with it the chunk sizes,
+                    # the moment of a decision and the decision itself are the same on every GPU.
+                    dt = self._slowest(dt)
+                    tune["rate"] = issued / max(dt, 1e-9)
+                    if len(self.autotune_chunks) < 4096:
+                        self.autotune_chunks.append((e.k, issued, dt, tune["settle"]))
+                    # one throughput sample per monitor interval, as the reference's monitor takes them; the tuner compares
+                    # the latest sample with the one before.  (The first chunk after a replica has been added is left out:
+                    # its graphs are uploaded to the device on their first launch, which is not the throughput the new
+                    # replica count will have.)
+                    if tune["settle"] > 0:
+                        tune["settle"] -= 1
                     else:
-                        tuned_tasks, tuned_time = tuned_tasks + issued, tuned_time + dt
-                    if tuned_tasks and (tuned_time >= self.sys.monitor_interval / 1000.0 or done >= ntasks):
-                        self.monitor.samples.append(self._job_rate(tuned_tasks * self.mc.batch_size / max(tuned_time, 1e-9)))
+                        tune["tasks"], tune["time"] = tune["tasks"] + issued, tune["time"] + dt
+                    if tune["tasks"] and tune["time"] >= self.sys.monitor_interval / 1000.0:
+                        self.monitor.samples.append(self._job_rate(tune["tasks"] * self.mc.batch_size / tune["time"]))
                         if self._autotune(list(self.monitor.samples), rt) != 0:
-                            settle = 1
-                        tuned_tasks, tuned_time = 0, 0.0
+                            tune["settle"] = 1
+                        tune["tasks"], tune["time"] = 0, 0.0
                 if ci > 0 and rt.tasks_issued() % wpc == 0 and rt.clock() % ci == 0:
                     self.checkpoint()
         finally:

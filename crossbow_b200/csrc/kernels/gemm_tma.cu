@@ -37,6 +37,7 @@ __host__ __device__ constexpr int gemm_threads(int BN, int MODE) { return (BN <=
 constexpr int EPI_BYTES = 8 * 32 * 33 * 4;              // one 32 x 32 transpose block per epilogue warp
 constexpr int MAX_STAGES = 8;
 constexpr int G_RELU = 1, G_ACCUM = 2, G_STATS = 4, G_BNBWD = 8;   // G_BNBWD: `stats` receives batch-norm backward sums (XbBnFuse)
+constexpr int G_SPLITK = 16;                            // NT: the reduction is split over gridDim.z; every CTA adds its partial tile to D
 constexpr uint32_t A_BYTES = 128 * 128;                 // 128 rows (or 4 planes x 32 positions) x 128 B
 
 struct GemmArgs {
@@ -47,7 +48,8 @@ struct GemmArgs {
   int a_bytes;         // NT: bytes one A box delivers
   int ldd;             // floats between rows of D
   int stages;
-  int kb_per_split;    // TN: position blocks per gridDim.z slice
+  int kb_per_split;    // TN: position blocks per gridDim.z slice.  NT: reduction blocks per slice, 0 = no split (G_SPLITK)
+  int planes2d;        // TN: the operands are rank-2 maps (channel, position) and every 32-channel plane is a load of its own
   // CONV: the A box is {32 channels, bw columns, bh rows, bn images}; tiles are numbered (image group, row group, column group)
   int c32, R, S, ph, pw, H, W, NI, bw, bh, bn, tiles_w, tiles_h, mirrored, krow;
   // NT with a strided output (data gradient of a stride-2 1x1 convolution): row m = (n, p, q) of the GEMM is written to
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(gemm_threads(BN, MODE)) gemm_tma_kernel(const 
   const int stages = g.stages;
   const uint32_t base = smem_u32(smem);
   int kb0 = 0, kb1 = g.kblocks;
-  if (MODE == 1) { kb0 = blockIdx.z * g.kb_per_split; kb1 = kb0 + g.kb_per_split < g.kblocks ? kb0 + g.kb_per_split : g.kblocks; }
+  if (MODE == 1 || (MODE == 0 && g.kb_per_split)) { kb0 = blockIdx.z * g.kb_per_split; kb1 = kb0 + g.kb_per_split < g.kblocks ? kb0 + g.kb_per_split : g.kblocks; }
   const int nkb = kb1 - kb0;
 
   if (tid == 0) {
@@ -129,10 +131,16 @@ __global__ void __launch_bounds__(gemm_threads(BN, MODE)) gemm_tma_kernel(const 
               tma_load_2d(sb + u * B_BYTES, &tmB, btap * g.krow + ccb * 32, n0, &full_bar[s]);
               if (++ccb == g.c32) { ccb = 0; if (++cs == g.S) { cs = 0; ++cr; } }
             }
-          } else if (g.rpb == 0) {
+          } else if (g.rpb == 0 && !g.planes2d) {
             mbar_expect_tx(&full_bar[s], STAGE);
             tma_load_3d(sa, &tmA, 0, kb * 32, tile * 4, &full_bar[s]);
             tma_load_3d(sb, &tmB, 0, kb * 32, n0 >> 5, &full_bar[s]);
+          } else if (g.rpb == 0) {
+            // channel counts that are no multiple of 32: a plane that starts inside the tensor and ends outside it (or lies
+            // outside altogether) arrives with zeros in the missing channels, which a plane-strided map cannot express
+            mbar_expect_tx(&full_bar[s], STAGE);
+            for (int pl = 0; pl < 4; ++pl) tma_load_2d(sa + pl * 4096, &tmA, (tile * 4 + pl) * 32, kb * 32, &full_bar[s]);
+            for (int pl = 0; pl < BN / 32; ++pl) tma_load_2d(sb + pl * 4096, &tmB, n0 + pl * 32, kb * 32, &full_bar[s]);
           } else {
             // one box per 32-channel plane, so that the planes keep their 4096-byte pitch although a box has fewer than 32 rows
             mbar_expect_tx(&full_bar[s], (uint32_t)g.ppb * 128u * (4u + BN / 32u));
@@ -219,7 +227,7 @@ __global__ void __launch_bounds__(gemm_threads(BN, MODE)) gemm_tma_kernel(const 
             const int n = n0 + c0 + cq;                    // first of this lane's four columns
             const bool ncol = n < g.N;                     // (N is a multiple of 4)
             float b4[4] = {0.f, 0.f, 0.f, 0.f};
-            if (bias && ncol) { b4[0] = bias[n]; b4[1] = bias[n + 1]; b4[2] = bias[n + 2]; b4[3] = bias[n + 3]; }
+            if (bias && ncol && !((flags & G_SPLITK) && blockIdx.z)) { b4[0] = bias[n]; b4[1] = bias[n + 1]; b4[2] = bias[n + 2]; b4[3] = bias[n + 3]; }
             float sx[4] = {0.f, 0.f, 0.f, 0.f}, sq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -233,6 +241,7 @@ __global__ void __launch_bounds__(gemm_threads(BN, MODE)) gemm_tma_kernel(const 
                   for (int k = 0; k < 4; ++k) x[k] = fmaxf(x[k], 0.f);
                 }
                 float4* o = reinterpret_cast<float4*>(D + off + n);
+                if (flags & G_SPLITK) { red_add_v4(D + off + n, x[0], x[1], x[2], x[3]); continue; }
                 if (flags & G_ACCUM) { const float4 old = *o; x[0] += old.x; x[1] += old.y; x[2] += old.z; x[3] += old.w; }
                 *o = make_float4(x[0], x[1], x[2], x[3]);
                 if (flags & G_BNBWD) {                     // x = final dy of a normalisation layer: its backward sums
@@ -387,6 +396,8 @@ inline bool is_1x1(const XbConvGeom* g) { return g->R == 1 && g->S == 1 && g->ph
 }  // namespace
 
 XB_API void xb_gemm_set_tn_ctas(int n) { g_tn_ctas = n > 0 ? n : 111; }
+static int g_split_k = 1;
+XB_API void xb_gemm_set_split_k(int on) { g_split_k = on; }   // (A/B comparisons: 0 keeps every reduction inside one CTA)
 XB_API void xb_gemm_set_smem_budgets(int many_kb, int few_kb) {
   g_budget_many = many_kb > 0 ? (size_t)(many_kb < 200 ? many_kb : 200) * 1024 : 54 * 1024;
   g_budget_few = few_kb > 0 ? (size_t)(few_kb < 200 ? few_kb : 200) * 1024 : 100 * 1024;
@@ -411,10 +422,11 @@ XB_API int xb_conv1x1_tma_supported(const XbConvGeom* g, int which) {
   }
   if (g->sh != 1 && (g->H % 2 || g->W % 2)) return 0;
   if (which == 1) return 1;
-  // K below 32 (first layers): one partial 32-channel plane of dY; the loads read the fill value (zero) for the missing
-  // channels and the epilogue only writes rows below K
-  if (g->C % 32 || (g->K % 32 && !(g->K < 32 && g->sh == 1))) return 0;
-  return (g->sh == 1 || g->Q <= 32) ? 1 : 0;
+  // stride 1: any channel counts (multiples of 4); where they are no multiples of 32 the planes are loaded one by one
+  // from rank-2 maps, the missing channels read the fill value (zero) and the epilogue only writes rows below K
+  if (g->sh == 1) return 1;
+  if (g->C % 32 || g->K % 32) return 0;
+  return g->Q <= 32 ? 1 : 0;
 }
 
 // which 0: In = X (N,H,W,C), Wb = weights (K,C), Out = Y (N,P,Q,K).  which 1: In = dY (N,P,Q,K), Wb = transposed weights (C,K), Out = dX.
@@ -464,7 +476,29 @@ XB_API int xb_conv1x1_tma(const float* In, const float* Wb, const float* bias, f
   }
   g.N = Nout; g.kblocks = (Kred + 31) / 32; g.ldd = Nout;
   dim3 grid((unsigned)tiles_m, (unsigned)((Nout + BN - 1) / BN), 1);
-  g.stages = pick_stages(g.kblocks, BN, (long long)grid.x * grid.y);
+  int steps = g.kblocks;
+  // A product with few output tiles and a long reduction (an inner-product layer at batch size: 32 x 2048 x 1000 is 16
+  // tiles) leaves most SMs idle while 16 CTAs stream the whole weight matrix: split the reduction over gridDim.z and let
+  // every CTA add its partial tile.  Only where the epilogue is linear in the accumulator (no ReLU, no sums of the output).
+  const long long tiles = (long long)grid.x * grid.y;
+  if (g_split_k && cg->sh == 1 && !(flags & (G_RELU | G_STATS | G_BNBWD)) && tiles * 4 <= 148 && g.kblocks >= 8) {
+    int splits = (int)((148 + tiles - 1) / tiles);
+    if (splits > g.kblocks / 2) splits = g.kblocks / 2;
+    g.kb_per_split = (g.kblocks + splits - 1) / splits;
+    splits = (g.kblocks + g.kb_per_split - 1) / g.kb_per_split;
+    if (splits > 1) {
+      if (!(flags & G_ACCUM)) {
+        cudaError_t e = cudaMemsetAsync(Out, 0, (size_t)g.M * Nout * sizeof(float), st);
+        if (e != cudaSuccess) return (int)e;
+      }
+      flags |= G_SPLITK;
+      grid.z = (unsigned)splits;
+      steps = g.kb_per_split;
+    } else {
+      g.kb_per_split = 0;
+    }
+  }
+  g.stages = pick_stages(steps, BN, tiles * grid.z);
   return launch_bn<0>(BN, ta, tb, Out, bias, stats, g, grid, flags, status, st, bn);
 }
 
@@ -474,14 +508,22 @@ XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, cons
   const long long P = (long long)cg->N * cg->P * cg->Q;   // positions of dY
   const int BN = cg->C <= 32 ? 32 : cg->C <= 64 ? 64 : cg->C <= 128 ? 128 : 256;
   const int rpb = cg->sh == 1 ? 0 : (32 / cg->Q < cg->N * cg->P ? 32 / cg->Q : cg->N * cg->P), ppb = rpb * cg->Q;
+  const int planes2d = cg->sh == 1 && (cg->C % 32 || (cg->K % 32 && cg->K > 32));
   CUtensorMap ta, tb;
-  {
+  if (planes2d) {
+    const cuuint64_t da[2] = {(cuuint64_t)cg->K, (cuuint64_t)P}, sa[1] = {(cuuint64_t)cg->K * 4};
+    const cuuint64_t db[2] = {(cuuint64_t)cg->C, (cuuint64_t)P}, sb[1] = {(cuuint64_t)cg->C * 4};
+    const cuuint32_t box[2] = {32, 32};
+    if (make_map(&ta, dY, 2, da, sa, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
+    if (make_map(&tb, X, 2, db, sb, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
+  } else {
     const cuuint64_t dims[3] = {(cuuint64_t)(cg->K < 32 ? cg->K : 32), (cuuint64_t)P, (cuuint64_t)((cg->K + 31) / 32)};
     const cuuint64_t strides[2] = {(cuuint64_t)cg->K * 4, 128};
     const cuuint32_t box[3] = {32, (cuuint32_t)(rpb ? ppb : 32), (cuuint32_t)(rpb ? 1 : 4)};
     if (make_map(&ta, dY, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
   }
-  if (rpb == 0) {
+  if (planes2d) {
+  } else if (rpb == 0) {
     const cuuint64_t dims[3] = {32, (cuuint64_t)P, (cuuint64_t)(cg->C / 32)};
     const cuuint64_t strides[2] = {(cuuint64_t)cg->C * 4, 128};
     const cuuint32_t box[3] = {32, 32, (cuuint32_t)(BN / 32)};
@@ -494,7 +536,7 @@ XB_API int xb_conv1x1_wgrad_tma(const float* dY, const float* X, float* dW, cons
     if (make_map(&tb, X, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return -XB_BAD_ARG;
   }
   GemmArgs g{};
-  g.M = cg->K; g.N = cg->C; g.ldd = cg->C; g.rpb = rpb; g.ppb = ppb; g.kc = 1;
+  g.M = cg->K; g.N = cg->C; g.ldd = cg->C; g.rpb = rpb; g.ppb = ppb; g.kc = 1; g.planes2d = planes2d;
   g.kblocks = rpb ? (cg->N * cg->P + rpb - 1) / rpb : (int)((P + 31) / 32);
   const int tiles = ((cg->K + 127) / 128) * ((cg->C + BN - 1) / BN);
   int splits = (g_tn_ctas + tiles - 1) / tiles;

@@ -285,12 +285,15 @@ def main():
     ap.add_argument("--warm", action="store_true", help="do not flush L2 between launches")
     ap.add_argument("--stats", action="store_true", help="convolution epilogue also produces batch-norm sums")
     ap.add_argument("--opt-blocks", type=int, default=0, help="tuning: blocks of the fused optimiser kernel")
+    ap.add_argument("--no-split-k", action="store_true", help="A/B: inner products keep their whole reduction in one CTA")
     ap.add_argument("--suite", default=None, choices=[None, "resnet32", "resnet50", "pointwise"])
     a = ap.parse_args()
     lib = L.init_device()
     lib.xb_tc_set_slab(3)
     if a.opt_blocks:
         lib.xb_optimiser_set_blocks(a.opt_blocks)
+    if a.no_split_k:
+        lib.xb_gemm_set_split_k(0)
     timer = Timer(flush=not a.warm)
     if a.suite == "pointwise":
         for op in POINTWISE:

@@ -96,6 +96,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_tc_set_tma", None, I)
     _sig(lib, "xb_sleep", I, C.c_longlong, P)
     _sig(lib, "xb_gemm_set_tn_ctas", None, I)
+    _sig(lib, "xb_gemm_set_split_k", None, I)
     _sig(lib, "xb_conv3x3_wgrad_set_ctas", None, I)
     _sig(lib, "xb_bn_set_stream_blocks", None, I)
     _sig(lib, "xb_bn_set_reduce_blocks", None, I)

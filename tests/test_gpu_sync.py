@@ -90,11 +90,11 @@ def _owned(n, G, g):
 
 @pytest.mark.parametrize("G,k,algo,n", [(2, 2, 0, 4096 * 9 + 2048), (4, 1, 0, 4096 * 9 + 2048), (8, 2, 0, 4096 * 9 + 2048),
                                         (4, 2, 1, 4096 * 9 + 2048), (4, 2, 2, 4096 * 9 + 2048),
-                                        (2, 1, 0, (4 << 20) + 16384 * 5 + 4096 + 8), (3, 2, 0, (4 << 20) + 16384 * 2 + 12)])
+                                        (2, 1, 0, (4 << 20) + 32768 * 5 + 4096 + 8), (3, 2, 0, (4 << 20) + 32768 * 2 + 12)])
 def test_owner_apply_matches_oracle(G, k, algo, n):
     """Two-shot exchange in which the owner of a chunk updates the central model and stores it on every GPU; the
     momentum of the central model is then kept by the owners only.  Small vectors use 16 KB chunks; the two cases above four
-    million elements use 64 KB chunks, four steps per chunk, with a ragged last chunk."""
+    million elements use 128 KB chunks, eight steps per chunk, with a ragged last chunk."""
     devs = _state(G, k, n, seed=7)
     kw = {0: dict(alpha=0.1, mu=0.9), 1: dict(mu=0.9, scale=1.0 / (G * k)), 2: dict(alpha=0.05, scale=1.0 / (G * k), blend=1.0, epochs=1)}[algo]
     for e, W, Z, ZL, GA in _run_emulated(devs, n, algo, True, owner_apply=True, **kw):
