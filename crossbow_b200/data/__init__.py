@@ -14,4 +14,7 @@ def __getattr__(name):
     if name in ("RecordDataset", "RecordWriter"):
         from . import records
         return getattr(records, name)
+    if name in ("convert_imagenet", "read_tfrecord", "parse_example"):
+        from . import tfrecords
+        return getattr(tfrecords, name)
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -6,6 +6,8 @@ ratings/RatingsEncoder.java, random/RandomEncoder.java}).
     python -m crossbow_b200.data.convert cifar10 --input data_batch_1.bin data_batch_2.bin ... -o out --name cifar-train -b 64
     python -m crossbow_b200.data.convert ratings --input ratings.txt -o out --name ratings-train -b 1024
     python -m crossbow_b200.data.convert random  --shape 3,32,32 --classes 10 --count 1024 -o out --name random-train -b 64
+    python -m crossbow_b200.data.convert imagenet --input 'train-*-of-*' --subset train -o out     (TFRecords -> record files,
+        scripts/datasets/imagenet/parse-records.py; see tfrecords.py)
 
 Pixel handling follows the reference: MNIST pixels are scaled by 1/256 (its default ``-s 0.00390625``), CIFAR pixels go to
 [-1, 1] (``p / 127.5 - 1``) and the mean image of the converted set is written beside it (``<name>.mean``, raw fp32) for
@@ -100,17 +102,26 @@ def convert_random(shape: Sequence[int], classes: int, count: int, directory: st
 
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(description="convert public data-set files to binary partitions")
-    ap.add_argument("kind", choices=["mnist", "cifar10", "cifar100", "ratings", "random"])
+    ap.add_argument("kind", choices=["mnist", "cifar10", "cifar100", "ratings", "random", "imagenet"])
     ap.add_argument("--images"), ap.add_argument("--labels")
     ap.add_argument("--input", nargs="*", default=[])
     ap.add_argument("-o", "--output", required=True)
-    ap.add_argument("--name", required=True)
-    ap.add_argument("-b", "--batch", type=int, required=True)
+    ap.add_argument("--name", default=None)
+    ap.add_argument("-b", "--batch", type=int, default=0, help="examples per batch (every kind but imagenet: record files hold single images)")
+    ap.add_argument("--subset", default="train", help="imagenet: train or validation (part of the output file names)")
+    ap.add_argument("--records-per-file", type=int, default=2048)
     ap.add_argument("--scale", type=float, default=0.00390625)
     ap.add_argument("--coarse", action="store_true")
     ap.add_argument("--shape", default="3,32,32"), ap.add_argument("--classes", type=int, default=10)
     ap.add_argument("--count", type=int, default=1024), ap.add_argument("--seed", type=int, default=0)
     a = ap.parse_args(argv)
+    if a.kind == "imagenet":
+        from .tfrecords import convert_imagenet
+        for path in convert_imagenet(a.input, a.output, a.subset, a.records_per_file):
+            print(path)
+        return 0
+    if a.batch <= 0 or not a.name:
+        ap.error("--batch and --name are required")
     if a.kind == "mnist":
         meta = convert_mnist(a.images, a.labels, a.output, a.name, a.batch, a.scale)
     elif a.kind == "cifar10":

@@ -223,3 +223,47 @@ def test_crop_plan_follows_the_reference_sampler():
     assert min(hs) < 0.45 * H and max(hs) > 0.9 * H and 120 < flips < 280
     assert crop_plan(W, H, [], False, 0) == ((W - 210) // 2, (H - 210) // 2, 210, 210, 0)
     assert crop_plan(W, H, [], True, 5) == crop_plan(W, H, [], True, 5)           # a function of the seed
+
+
+def test_tfrecord_files_become_record_files(tmp_path):
+    """ImageNet TFRecords -> record files without TensorFlow: the container's checksums, the three protobuf messages of an
+    Example (packed and one-field-per-value lists), labels moved to 0..999, boxes kept, files rotated by record count."""
+    import struct
+    from crossbow_b200.data import tfrecords as T
+    assert T.crc32c(b"123456789") == 0xE3069283
+    examples, labels = [], []
+    for i in range(5):
+        lab = 1 + 37 * i
+        examples.append(T.make_example({"image/encoded": [_jpeg(_image(40 + i, 36, seed=i))], "image/class/label": [lab],
+                                        "image/height": [36], "image/width": [40 + i], "image/class/text": [b"n0%d" % i],
+                                        "image/object/bbox/xmin": [0.1, 0.2][:1 + i % 2], "image/object/bbox/ymin": [0.1, 0.2][:1 + i % 2],
+                                        "image/object/bbox/xmax": [0.9, 0.8][:1 + i % 2], "image/object/bbox/ymax": [0.9, 0.8][:1 + i % 2]}))
+        labels.append(lab - 1)
+    src = [str(tmp_path / "train-00000-of-00002"), str(tmp_path / "train-00001-of-00002")]
+    assert T.write_tfrecord(src[0], examples[:3]) == 3 and T.write_tfrecord(src[1], examples[3:]) == 2
+    ex = T.parse_example(next(T.read_tfrecord(src[0], verify=True)))
+    assert ex["image/class/label"] == [1] and ex["image/width"] == [40] and ex["image/class/text"] == [b"n00"]
+    assert ex["image/object/bbox/xmin"] == pytest.approx([0.1]) and decode_jpeg(ex["image/encoded"][0]).shape == (36, 40, 3)
+    # lists written one value per field (the unpacked form older writers emit) and negative integers
+    unpacked = T._ld(1, T._ld(1, T._ld(1, b"k") + T._ld(2, T._ld(3, T._put_varint(1 << 3) + T._put_varint(-5) + T._put_varint(1 << 3) + T._put_varint(7))))
+                        + T._ld(1, T._ld(1, b"f") + T._ld(2, T._ld(2, bytes([1 << 3 | 5]) + struct.pack("<f", 0.25)))))
+    assert T.parse_example(unpacked) == {"k": [-5, 7], "f": [0.25]}
+    out = T.convert_imagenet([str(tmp_path / "train-*-of-*")], str(tmp_path / "out"), "train", max_records_per_file=2, verify=True)
+    assert [p.rsplit("/", 1)[1] for p in out] == ["crossbow-train.records.1", "crossbow-train.records.2", "crossbow-train.records.3"]
+    ds = RecordDataset(out, batch_size=5, batches_per_half=1, image_size=32, workers=2, training=False, timeout_s=20)
+    assert ds.number_of_examples() == 5
+    x, y = ds.batch(0)
+    assert [int(v) for v in y] == labels and ds.decode_failures() == 0
+    assert np.allclose(x[0].numpy(), preprocess(_jpeg(_image(40, 36, seed=0)), training=False, size=32))
+    ds.close()
+    # damage: a flipped payload byte is caught by verify, a flipped length byte always
+    raw = bytearray(open(src[1], "rb").read())
+    raw[40] ^= 0xFF
+    open(src[1], "wb").write(bytes(raw))
+    with pytest.raises(ValueError, match="checksum"):
+        list(T.read_tfrecord(src[1], verify=True))
+    raw[40] ^= 0xFF
+    raw[2] ^= 0x01
+    open(src[1], "wb").write(bytes(raw))
+    with pytest.raises(ValueError, match="length"):
+        list(T.read_tfrecord(src[1]))
