@@ -303,12 +303,7 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
 #pragma unroll
       for (int u = 0; u < U; ++u) { i4[u] = (long long)c * (CHUNK / 4) + j0 + u * NT; ok[u] = i4[u] < n4; }
       local_part(a, i4, ok, acc);                         // (lanes past the end contribute zeros)
-      if (a.part_local) {
-        // NVLS: the partial stays here; the owner will read the sum of all GPUs' copies through the switch
-        float4* dst = reinterpret_cast<float4*>(a.part_local) + ((long long)parity * a.nchunks + c) * (CHUNK / 4);
-#pragma unroll
-        for (int u = 0; u < U; ++u) dst[j0 + u * NT] = acc[u];
-      } else if (a.two_shot) {
+      if (a.two_shot) {
 #pragma unroll
         for (int u = 0; u < U; ++u) reinterpret_cast<float4*>(a.inbox[owner])[off4 + j0 + u * NT] = acc[u];
       } else {
@@ -338,18 +333,12 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
       __syncthreads();
       if (tid < G && !wait_flag(a.ready1[me] + (long long)tid * a.nchunks + c, a.epoch, a.timeout_ns)) { s_fail = 1; atomicExch(a.status, XB_TIMEOUT_FLAG); }
       __syncthreads();
-      if (a.part_mc) __threadfence_system();               // the multimem loads below follow the flags observed above
       const bool ok = !s_fail;
       const long long res4 = ((long long)parity * a.nchunks + c) * (CHUNK / 4);
       for (int j0 = tid; j0 < CHUNK / 4 && ok; j0 += U * NT) {
         float4 t[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) t[u] = make_float4(0, 0, 0, 0);
-        if (a.part_mc) {
-          const float* mc = a.part_mc + ((long long)parity * a.nchunks + c) * CHUNK;
-#pragma unroll
-          for (int u = 0; u < U; ++u) t[u] = multimem_ld_reduce_add(mc + 4 * (j0 + u * NT));
-        } else
         for (int src = 0; src < G; ++src) {               // rank order: every owner adds in the same order
           const long long o4 = (((long long)parity * G + src) * slot_elems + (long long)(c / G) * CHUNK) / 4 + j0;
           float4 v[U];
@@ -393,10 +382,6 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
 #pragma unroll
             for (int u = 0; u < U; ++u) z[u] = f4add(z[u], t[u]);
           }
-          if (a.z_mc) {
-#pragma unroll
-            for (int u = 0; u < U; ++u) if (okk[u]) multimem_st(a.z_mc + 4 * i4[u], z[u]);
-          } else
           for (int g = 0; g < G; ++g) {
 #pragma unroll
             for (int u = 0; u < U; ++u) if (okk[u]) reinterpret_cast<float4*>(a.zpeer[g])[i4[u]] = z[u];
@@ -472,6 +457,149 @@ __global__ void __launch_bounds__(NT, 2) fused_sync_kernel(const SyncArgs* __res
   }
   // algorithms that rewrite the replicas from the new central model release them only now
   if (a.copy_to_replicas || a.algo != ALGO_SMA) release_replicas(a);
+  stamp_exit(a);
+}
+
+// The NVLS variant as a kernel of its own.  The partial sums never leave their GPU by a store: the owner of a chunk pulls
+// the SUM of all GPUs' copies through the switch (multimem.ld_reduce) and pushes the new central model with multimem.st.
+// Run as "all local reductions, then all owner reductions" the links idle during the first half and the HBM during the
+// second, so every block interleaves the two: after each chunk of its local reduction it looks whether the next chunk it
+// owns has been flagged by every GPU and, if so, reduces it; only when its local work is done does it wait (bounded) for
+// the rest.  All GPUs walk the chunks in the same order, so the first owned chunks become ready one wave of local work
+// after the start.  No wait sits in front of local work, hence no cycle: every flag a block waits for is raised by work
+// that waits for nothing.
+__global__ void __launch_bounds__(NT, 2) fused_sync_nvls_kernel(const SyncArgs* __restrict__ per_rank) {
+  __shared__ SyncArgs a;
+  __shared__ int s_fail;
+  {
+    const int* src = reinterpret_cast<const int*>(per_rank + blockIdx.y);
+    int* dst = reinterpret_cast<int*>(&a);
+    for (int i = threadIdx.x; i < (int)(sizeof(SyncArgs) / sizeof(int)); i += NT) dst[i] = src[i];
+  }
+  __syncthreads();
+  const int CHUNK = a.chunk, C4 = CHUNK / 4;
+  const int tid = threadIdx.x, B = gridDim.x, G = a.G, me = a.rank;
+  const long long n4 = a.n / 4;
+  const int parity = a.epoch & 1;
+  const bool early = !(a.copy_to_replicas || a.algo != ALGO_SMA);
+  stamp_entry(a);
+
+  int c1 = blockIdx.x;          // next chunk of the local reduction
+  int j2 = blockIdx.x;          // next of the chunks this GPU owns (chunk me + j2 * G) to reduce across the GPUs
+  bool released = false;
+  for (;;) {
+    const bool more1 = c1 < a.nchunks;
+    const int c2 = me + j2 * G;
+    const bool more2 = c2 < a.nchunks;
+    if (!more1 && !more2) break;
+    if (more1) {
+      float4* dst = reinterpret_cast<float4*>(a.part_local) + ((long long)parity * a.nchunks + c1) * C4;
+      for (int j0 = tid; j0 < C4; j0 += U * NT) {
+        long long i4[U]; bool ok[U]; float4 acc[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) { i4[u] = (long long)c1 * C4 + j0 + u * NT; ok[u] = i4[u] < n4; }
+        local_part(a, i4, ok, acc);                       // (lanes past the end contribute zeros)
+#pragma unroll
+        for (int u = 0; u < U; ++u) dst[j0 + u * NT] = acc[u];
+      }
+      __syncthreads();
+      if (tid == 0) { __threadfence_system(); st_release_sys(a.ready1[c1 % G] + (long long)me * a.nchunks + c1, a.epoch); }
+      c1 += B;
+      if (c1 >= a.nchunks && early) { release_replicas(a); released = true; }
+    }
+    if (more2) {
+      const bool must = c1 >= a.nchunks;                  // nothing local left: wait instead of looking
+      int ready = 1;
+      if (tid < G) {
+        const unsigned int* f = a.ready1[me] + (long long)tid * a.nchunks + c2;
+        if (must) {
+          if (!wait_flag(f, a.epoch, a.timeout_ns)) { ready = 0; atomicExch(a.status, XB_TIMEOUT_FLAG); }
+        } else {
+          ready = (int)(ld_acquire_sys(f) - a.epoch) >= 0;
+        }
+      }
+      ready = __syncthreads_and(ready);
+      if (ready) {
+        __threadfence_system();                           // the multimem loads below follow the flags observed above
+        const float* mc = a.part_mc + ((long long)parity * a.nchunks + c2) * CHUNK;
+        for (int j0 = tid; j0 < C4; j0 += U * NT) {
+          float4 t[U], z[U]; long long i4[U]; bool ok[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) { i4[u] = (long long)c2 * C4 + j0 + u * NT; ok[u] = i4[u] < n4; }
+#pragma unroll
+          for (int u = 0; u < U; ++u) t[u] = multimem_ld_reduce_add(mc + 4 * (j0 + u * NT));
+#pragma unroll
+          for (int u = 0; u < U; ++u) if (ok[u]) z[u] = reinterpret_cast<const float4*>(a.z)[i4[u]];
+          if (a.algo == ALGO_POLYAK) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const float4 mean = f4scale(a.scale, t[u]);
+              z[u] = make_float4(z[u].x + a.blend * (mean.x - z[u].x), z[u].y + a.blend * (mean.y - z[u].y), z[u].z + a.blend * (mean.z - z[u].z),
+                                 z[u].w + a.blend * (mean.w - z[u].w));
+            }
+          } else {
+            if (a.algo == ALGO_SSGD) {
+#pragma unroll
+              for (int u = 0; u < U; ++u) t[u] = f4scale(a.scale, t[u]);
+            }
+            if (a.mu > 0.f) {
+              float4* lp = reinterpret_cast<float4*>(a.zlast);
+              float4 l[U];
+#pragma unroll
+              for (int u = 0; u < U; ++u) if (ok[u]) l[u] = lp[i4[u]];
+#pragma unroll
+              for (int u = 0; u < U; ++u) if (ok[u]) { t[u] = f4axpy(a.mu, l[u], t[u]); lp[i4[u]] = t[u]; }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) z[u] = f4add(z[u], t[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) if (ok[u]) multimem_st(a.z_mc + 4 * i4[u], z[u]);
+        }
+        __syncthreads();
+        if (tid < G) { __threadfence_system(); st_release_sys(a.ready2[tid] + c2, a.epoch); }
+        j2 += B;
+      } else if (must) {
+        j2 += B;                                          // gave up on this chunk: the status word says so
+      }
+    }
+  }
+  if (early && !released) release_replicas(a);
+
+  // the central model is complete on this GPU once every owner has flagged its chunks
+  for (int c = blockIdx.x; c < a.nchunks; c += B) {
+    if (tid == 0) s_fail = 0;
+    __syncthreads();
+    if (tid == 0 && !wait_flag(a.ready2[me] + c, a.epoch, a.timeout_ns)) { s_fail = 1; atomicExch(a.status, XB_TIMEOUT_FLAG); }
+    __syncthreads();
+    const bool fail = s_fail != 0;
+    __syncthreads();            // everyone has read s_fail before thread 0 may reset it in the next iteration
+    if (fail) continue;
+    const bool pull = a.algo == ALGO_POLYAK && a.alpha > 0.f;
+    if (!(a.copy_to_replicas || a.algo == ALGO_SSGD || pull)) continue;
+    for (int j0 = tid; j0 < C4; j0 += U * NT) {
+      long long i4[U]; bool ok[U]; float4 z[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) { i4[u] = (long long)c * C4 + j0 + u * NT; ok[u] = i4[u] < n4; }
+#pragma unroll
+      for (int u = 0; u < U; ++u) if (ok[u]) z[u] = __ldcg(reinterpret_cast<const float4*>(a.z) + i4[u]);
+      for (int r = 0; r < a.k; ++r) {
+        float4* wp = reinterpret_cast<float4*>(a.w[r]);
+        if (pull) {
+          float4 w[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) if (ok[u]) w[u] = wp[i4[u]];
+#pragma unroll
+          for (int u = 0; u < U; ++u) if (ok[u]) wp[i4[u]] = f4sub(w[u], f4scale(a.alpha, f4sub(w[u], z[u])));
+        } else {
+#pragma unroll
+          for (int u = 0; u < U; ++u) if (ok[u]) wp[i4[u]] = z[u];
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (!early) release_replicas(a);
   stamp_exit(a);
 }
 
@@ -596,13 +724,16 @@ XB_API int xb_fused_sync(const XbSyncDesc* d, void* args_dev, void* args_pinned,
       int dev = 0, sms = 148, per_sm = 1;
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      int per_sm_nvls = 1;
       cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_sync_kernel, NT, 0);
-      cached = sms * (per_sm >= 2 ? 2 : 1);
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm_nvls, fused_sync_nvls_kernel, NT, 0);
+      cached = sms * ((per_sm >= 2 && per_sm_nvls >= 2) ? 2 : 1);
     }
     max_blocks = cached;
   }
   dim3 grid(sync_grid(h->nchunks, max_blocks), 1);
-  fused_sync_kernel<<<grid, NT, 0, st>>>(reinterpret_cast<const SyncArgs*>(args_dev));
+  if (h->part_mc) fused_sync_nvls_kernel<<<grid, NT, 0, st>>>(reinterpret_cast<const SyncArgs*>(args_dev));
+  else fused_sync_kernel<<<grid, NT, 0, st>>>(reinterpret_cast<const SyncArgs*>(args_dev));
   return (int)cudaGetLastError();
 }
 

@@ -117,12 +117,13 @@ def main():
                 fs.check()
                 clocks = sampler.stop()
                 tl = fs.timeline()
-                t_n = None
+                t_n, tln = None, None
                 if fn is not None and fn.nvls:
                     zn = fn.central_storage().zero_()
                     t_n = timed(lambda: fn.synchronise(s, ALGO_SMA, ws, ps, zn, zl, alpha=0.1, mu=0.9))
                     torch.cuda.synchronize()
                     fn.check()
+                    tln = fn.timeline()
                 t_r = timed(lambda: rs.synchronise(s, ALGO_SMA, ws, ps, z, zl, alpha=0.1, mu=0.9))
             # bytes this implementation moves through one GPU's HBM: replicas 3k, central model and its momentum 4, plus the
             # exchange (one-shot: G partials written and read; two-shot with owner-apply: partials once in, once out, 3/G)
@@ -135,7 +136,7 @@ def main():
                 print(json.dumps({"op": "sma_sync", "n": n, "replicas": k, "gpus": world, "two_shot": fs.two_shot, "owner_apply": bool(fs.owner_apply and world > 1),
                                   "fused_us": round(t_f, 2), "reference_us": round(t_r, 2), "speedup": round(t_r / t_f, 2),
                                   "release_us": round(tl["release_us"], 2), "chunk_floats": int(lib.xb_sync_chunk(n)), "max_blocks": a.max_blocks,
-                                  "nvls_us": round(t_n, 2) if t_n else None,
+                                  "nvls_us": round(t_n, 2) if t_n else None, "nvls_release_us": round(tln["release_us"], 2) if tln else None,
                                   "nvls_fraction_of_roofline_900": round(t_nom / t_n, 3) if t_n else None,
                                   "peer_store_gbs": round(peer_gbs, 1) if peer_gbs else None,
                                   "roofline_us_measured_link": round(t_meas, 2), "fraction_of_roofline_measured_link": round(t_meas / t_f, 3),
