@@ -98,6 +98,8 @@ def measure_ours(args, model_name, steps, warmup, k=0, batch=0, min_seconds=1.0)
         L.init_device().xb_tc_set_tma_conv_min(args.tma_conv_min)
     if args.side_low_priority:
         L.init_device().xb_program_side_priority(1)
+    if args.pdl is not None:
+        L.init_device().xb_set_pdl(args.pdl)
     if args.fuse_bn_sums:
         import crossbow_b200.lower as _lower
         _lower.FUSE_BN_BACKWARD_SUMS = True
@@ -264,6 +266,7 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="the learners wait for the whole synchronisation (no early release)")
     ap.add_argument("--no-branches", action="store_true", help="weight gradients stay on the task's main chain (no parallel branch in the task graph)")
     ap.add_argument("--nvls", action="store_true", help="two-shot exchange through NVLink multicast (multimem) instead of peer stores")
+    ap.add_argument("--pdl", type=int, default=None, help="tuning: 1 / 0 = launch the kernels of a task's critical path with / without programmatic dependent launch")
     ap.add_argument("--side-low-priority", action="store_true", help="tuning: the weight-gradient branch of the task graph runs at the lowest stream priority")
     ap.add_argument("--fuse-bn-sums", action="store_true", help="tuning: data-gradient kernels produce the batch-norm backward sums in their epilogue")
     ap.add_argument("--gemm-smem", default="", help="tuning: shared-memory budgets of the TMA GEMM pipeline in KB, 'many,few' (default 54,100)")

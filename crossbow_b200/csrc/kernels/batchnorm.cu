@@ -44,6 +44,8 @@ __host__ __device__ inline Tiling make_tiling(int C, int vec) {
 // sums[0..C) += sum_x, sums[C..2C) += sum_x^2 ; optionally of a*(mask) for backward
 template <int VEC>
 __global__ void __launch_bounds__(NT) bn_stats_kernel(const float* __restrict__ x, float* __restrict__ sums, int M, int C, int rows_per_block) {
+  xb_pdl_wait();
+  xb_pdl_launch();
   const Tiling t = make_tiling(C, VEC);
   __shared__ float red[2][NT * VEC];
   const int r_begin = blockIdx.x * rows_per_block, r_end = min(M, r_begin + rows_per_block);
@@ -91,6 +93,8 @@ struct BnArgs {
 
 template <int VEC>
 __global__ void __launch_bounds__(NT) bn_fwd_kernel(BnArgs a) {
+  xb_pdl_wait();
+  xb_pdl_launch();
   const Tiling t = make_tiling(a.C, VEC);
   const int r_begin = blockIdx.x * a.rows_per_block, r_end = min(a.M, r_begin + a.rows_per_block);
   const float invM = 1.f / (float)a.M;
@@ -184,6 +188,8 @@ struct BnBwdArgs {
 // sources out of the kernel, which is what lets three blocks share an SM.
 template <int VEC, int MODE = -1>
 __global__ void __launch_bounds__(NT, MODE >= 0 ? 3 : 1) bn_bwd_reduce_kernel(BnBwdArgs a) {
+  xb_pdl_wait();
+  xb_pdl_launch();
   const Tiling t = make_tiling(a.C, VEC);
   __shared__ float red[2][NT * VEC];
   const int r_begin = blockIdx.x * a.rows_per_block, r_end = min(a.M, r_begin + a.rows_per_block);
@@ -262,6 +268,8 @@ __global__ void __launch_bounds__(NT, MODE >= 0 ? 3 : 1) bn_bwd_reduce_kernel(Bn
 
 template <int VEC>
 __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
+  xb_pdl_wait();
+  xb_pdl_launch();
   const Tiling t = make_tiling(a.C, VEC);
   const int r_begin = blockIdx.x * a.rows_per_block, r_end = min(a.M, r_begin + a.rows_per_block);
   const float invM = 1.f / (float)a.M;
@@ -313,10 +321,10 @@ __global__ void __launch_bounds__(NT) bn_bwd_apply_kernel(BnBwdArgs a) {
 
 template <class A> static void launch_reduce_v4(const A& a, int blocks, cudaStream_t st) {
   switch (a.relu) {
-    case 0: bn_bwd_reduce_kernel<4, 0><<<blocks, NT, 0, st>>>(a); break;
-    case 1: bn_bwd_reduce_kernel<4, 1><<<blocks, NT, 0, st>>>(a); break;
-    case 2: bn_bwd_reduce_kernel<4, 2><<<blocks, NT, 0, st>>>(a); break;
-    default: bn_bwd_reduce_kernel<4, 3><<<blocks, NT, 0, st>>>(a); break;
+    case 0: xb_launch(bn_bwd_reduce_kernel<4, 0>, dim3(blocks), dim3(NT), 0, st, a); break;
+    case 1: xb_launch(bn_bwd_reduce_kernel<4, 1>, dim3(blocks), dim3(NT), 0, st, a); break;
+    case 2: xb_launch(bn_bwd_reduce_kernel<4, 2>, dim3(blocks), dim3(NT), 0, st, a); break;
+    default: xb_launch(bn_bwd_reduce_kernel<4, 3>, dim3(blocks), dim3(NT), 0, st, a); break;
   }
 }
 
@@ -345,8 +353,8 @@ inline bool can_vec4(int C, const void* a, const void* b, const void* c, const v
 XB_API int xb_bn_stats(const float* x, float* sums, int M, int C, cudaStream_t st) {
   bool v4 = can_vec4(C, x, nullptr, nullptr, nullptr);
   int blocks; int rpb = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
-  if (v4) bn_stats_kernel<4><<<blocks, NT, 0, st>>>(x, sums, M, C, rpb);
-  else    bn_stats_kernel<1><<<blocks, NT, 0, st>>>(x, sums, M, C, rpb);
+  if (v4) xb_launch(bn_stats_kernel<4>, dim3(blocks), dim3(NT), 0, st, x, sums, M, C, rpb);
+  else    xb_launch(bn_stats_kernel<1>, dim3(blocks), dim3(NT), 0, st, x, sums, M, C, rpb);
   return (int)cudaGetLastError();
 }
 
@@ -370,8 +378,8 @@ XB_API int xb_bn_forward_mask(const float* x, const float* res, float* y, const 
   bool v4 = can_vec4(C, x, res, y, nullptr);
   if (mask && !v4) return -XB_BAD_ARG;
   int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
-  if (v4) bn_fwd_kernel<4><<<blocks, NT, 0, st>>>(a);
-  else    bn_fwd_kernel<1><<<blocks, NT, 0, st>>>(a);
+  if (v4) xb_launch(bn_fwd_kernel<4>, dim3(blocks), dim3(NT), 0, st, a);
+  else    xb_launch(bn_fwd_kernel<1>, dim3(blocks), dim3(NT), 0, st, a);
   return (int)cudaGetLastError();
 }
 
@@ -384,9 +392,9 @@ XB_API int xb_bn_backward(const float* dy, const float* x, const float* y, const
   bool v4 = can_vec4(C, dy, x, relu == 3 ? nullptr : y, dx) && (((uintptr_t)dres) % 16 == 0);
   if (relu == 3 && !v4) return -XB_BAD_ARG;
   int blocks, rblocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, rblocks, g_bn_reduce_blocks, 8);
-  if (v4) launch_reduce_v4(a, rblocks, st); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, st>>>(a);
+  if (v4) launch_reduce_v4(a, rblocks, st); else xb_launch(bn_bwd_reduce_kernel<1>, dim3(rblocks), dim3(NT), 0, st, a);
   a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
-  if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); else bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a);
+  if (v4) xb_launch(bn_bwd_apply_kernel<4>, dim3(blocks), dim3(NT), 0, st, a); else xb_launch(bn_bwd_apply_kernel<1>, dim3(blocks), dim3(NT), 0, st, a);
   return (int)cudaGetLastError();
 }
 XB_API void xb_bn_set_reduce_blocks(int n) { g_bn_reduce_blocks = n > 0 ? n : 296; }
@@ -401,9 +409,9 @@ XB_API int xb_bn_backward_remask(const float* dy, const float* x, const float* s
   BnBwdArgs a{dy, x, nullptr, save_mean, save_invstd, gamma, dsums, dx, nullptr, dgamma, dbeta, M, C, 2, accum_dx, 0, 0, beta};
   bool v4 = can_vec4(C, dy, x, nullptr, dx);
   int blocks, rblocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, rblocks, g_bn_reduce_blocks, 8);
-  if (v4) launch_reduce_v4(a, rblocks, st); else bn_bwd_reduce_kernel<1><<<rblocks, NT, 0, st>>>(a);
+  if (v4) launch_reduce_v4(a, rblocks, st); else xb_launch(bn_bwd_reduce_kernel<1>, dim3(rblocks), dim3(NT), 0, st, a);
   a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
-  if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a); else bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a);
+  if (v4) xb_launch(bn_bwd_apply_kernel<4>, dim3(blocks), dim3(NT), 0, st, a); else xb_launch(bn_bwd_apply_kernel<1>, dim3(blocks), dim3(NT), 0, st, a);
   return (int)cudaGetLastError();
 }
 
@@ -414,8 +422,8 @@ XB_API int xb_bn_backward_apply(const float* dy, const float* x, const float* y,
   BnBwdArgs a{dy, x, y, save_mean, save_invstd, gamma, const_cast<float*>(dsums), dx, dres, dgamma, dbeta, M, C, relu ? 1 : 0, accum_dx, accum_dres, 0, nullptr};
   bool v4 = can_vec4(C, dy, x, y, dx) && (((uintptr_t)dres) % 16 == 0);
   int blocks; a.rows_per_block = rows_per_block_for(M, C, v4 ? 4 : 1, blocks);
-  if (v4) bn_bwd_apply_kernel<4><<<blocks, NT, 0, st>>>(a);
-  else    bn_bwd_apply_kernel<1><<<blocks, NT, 0, st>>>(a);
+  if (v4) xb_launch(bn_bwd_apply_kernel<4>, dim3(blocks), dim3(NT), 0, st, a);
+  else    xb_launch(bn_bwd_apply_kernel<1>, dim3(blocks), dim3(NT), 0, st, a);
   return (int)cudaGetLastError();
 }
 

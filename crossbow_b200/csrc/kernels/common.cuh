@@ -48,6 +48,35 @@ enum XbStatus : int { XB_OK = 0, XB_TIMEOUT_FLAG = 1, XB_TIMEOUT_MBAR = 2, XB_BA
     if (_e != cudaSuccess) return (int)_e;                    \
   } while (0)
 
+// ---- programmatic dependent launch -------------------------------------------------------------------------------------
+// A task is a chain of ~150 kernels of 5-15 us each, every one of which needs the results of the one before.  With a plain
+// launch the next kernel's blocks are only scheduled once the previous grid has drained and its memory has been flushed;
+// launched with the programmatic-serialisation attribute (an edge of that kind in a captured graph) they are scheduled
+// while the previous grid's last blocks still run, set up what does not depend on it (shared-memory copies of their
+// arguments, barriers, descriptor prefetch) and then sit in xb_pdl_wait() until the previous grid has completed and its
+// writes are visible.  Rules for a kernel launched through xb_launch:
+//   * no access to global memory that another kernel of the stream produces, or consumes and this one overwrites, before
+//     xb_pdl_wait();
+//   * xb_pdl_wait() is executed by every thread that touches such memory afterwards (put it on a block-uniform path);
+//   * xb_pdl_launch() AFTER the wait: the kernel after this one may then be scheduled as soon as all blocks of this one
+//     have started, never more than one kernel ahead.
+// Both instructions do nothing in a kernel that was launched the plain way.
+__device__ __forceinline__ void xb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void xb_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_xb_pdl;                                     // defined in train_ops.cu; xb_set_pdl()
+
+template <class... KArgs, class... Args>
+static inline cudaError_t xb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = g_xb_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 static inline int xb_ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 // ---- Philox4x32-10 (bit-identical to crossbow_b200/utils/philox.py) ----

@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_kernel(const float* __r
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  xb_pdl_wait();                                       // nothing above reads or writes global memory
+  xb_pdl_launch();
   if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);
 
   // ---- stage the slab: one (position, chunk) = 16 bytes per copy, zero fill for padding positions ----
@@ -227,6 +229,8 @@ __global__ void __launch_bounds__(WG_THREADS) conv3x3_wgrad_mn_kernel(const floa
   const uint32_t xbytes = (uint32_t)S * 128u, stage_bytes = xbytes + NP * yplane;
   const uint32_t base_u32 = smem_u32(smem);
   if (tid == 0) { mbar_init(&bar_free[0], 3); mbar_init(&bar_free[1], 3); s_abort = 0; asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+  xb_pdl_wait();                                       // nothing above reads or writes global memory
+  xb_pdl_launch();
   if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -394,6 +398,8 @@ __global__ void __launch_bounds__(NTHREADS) conv3x3_slab_pipe_kernel(const float
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  xb_pdl_wait();                                       // nothing above reads or writes global memory
+  xb_pdl_launch();
   if (warp == 0) tmem_alloc(&s_tmem, TMEM_COLS);
 
   // per-thread slab positions are the same for every chunk: decode them once (at most 3 positions per thread)
@@ -555,7 +561,7 @@ int launch_slab(const float* X, const float* Wb, const float* bias, float* Out, 
                 cudaStream_t st, const XbBnFuse& bn) {
   size_t smem = slab_smem_bytes(g.W, g.C, BN);
   dim3 grid((unsigned)((g.positions + BM - 1) / BM), (unsigned)((g.K + BN - 1) / BN));
-  conv3x3_slab_kernel<BN><<<grid, NTHREADS, smem, st>>>(X, Wb, bias, Out, stats, g, flags, status, bn);
+  xb_launch(conv3x3_slab_kernel<BN>, grid, dim3(NTHREADS), smem, st, X, Wb, bias, Out, stats, g, flags, status, bn);
   return (int)cudaGetLastError();
 }
 inline int pick_bn(int K) { return K <= 16 ? 16 : K <= 32 ? 32 : K <= 64 ? 64 : K <= 128 ? 128 : 256; }
@@ -583,7 +589,7 @@ int launch_pipe(const float* X, const float* Wb, const float* bias, float* Out, 
                 cudaStream_t st, const XbBnFuse& bn) {
   size_t smem = pipe_smem_bytes(g.W, 16, BN);
   dim3 grid((unsigned)((g.positions + BM - 1) / BM), (unsigned)((g.K + BN - 1) / BN));
-  conv3x3_slab_pipe_kernel<BN, 16><<<grid, NTHREADS, smem, st>>>(X, Wb, bias, Out, stats, g, flags, status, bn);
+  xb_launch(conv3x3_slab_pipe_kernel<BN, 16>, grid, dim3(NTHREADS), smem, st, X, Wb, bias, Out, stats, g, flags, status, bn);
   return (int)cudaGetLastError();
 }
 inline int choose_pipe_bn(long long positions, int W, int Kout) {
@@ -643,10 +649,10 @@ XB_API int xb_conv3x3_wgrad_slab(const float* dY, const float* X, float* dW, con
   dim3 grid((unsigned)gx, gy, gz);
   const size_t smem = wgrad_smem_bytes(g.W, NK);
   switch (NK) {
-    case 16: conv3x3_wgrad_mn_kernel<16><<<grid, WG_THREADS, smem, st>>>(dY, X, dW, g, ntiles, status); break;
-    case 32: conv3x3_wgrad_mn_kernel<32><<<grid, WG_THREADS, smem, st>>>(dY, X, dW, g, ntiles, status); break;
-    case 64: conv3x3_wgrad_mn_kernel<64><<<grid, WG_THREADS, smem, st>>>(dY, X, dW, g, ntiles, status); break;
-    default: conv3x3_wgrad_mn_kernel<128><<<grid, WG_THREADS, smem, st>>>(dY, X, dW, g, ntiles, status); break;
+    case 16: xb_launch(conv3x3_wgrad_mn_kernel<16>, grid, dim3(WG_THREADS), smem, st, dY, X, dW, g, ntiles, status); break;
+    case 32: xb_launch(conv3x3_wgrad_mn_kernel<32>, grid, dim3(WG_THREADS), smem, st, dY, X, dW, g, ntiles, status); break;
+    case 64: xb_launch(conv3x3_wgrad_mn_kernel<64>, grid, dim3(WG_THREADS), smem, st, dY, X, dW, g, ntiles, status); break;
+    default: xb_launch(conv3x3_wgrad_mn_kernel<128>, grid, dim3(WG_THREADS), smem, st, dY, X, dW, g, ntiles, status); break;
   }
   return (int)cudaGetLastError();
 }

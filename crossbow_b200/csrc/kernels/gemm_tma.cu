@@ -92,6 +92,8 @@ __global__ void __launch_bounds__(gemm_threads(BN, MODE)) gemm_tma_kernel(const 
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
+  xb_pdl_wait();                                       // nothing above reads or writes global memory (the maps are arguments)
+  xb_pdl_launch();
   if (warp == 1) tmem_alloc(&s_tmem, TMEM_COLS);
   for (int i = tid; i < 2 * BN; i += NTH) s_red[i] = 0.f;
   if (MODE == 1 && g.rpb) {                              // rows the boxes never write must read as zero
@@ -356,8 +358,7 @@ int launch_kc(const CUtensorMap& a, const CUtensorMap& b, float* D, const float*
               cudaStream_t st, const XbBnFuse& bn) {
   size_t smem = (size_t)g.stages * stage_bytes(BN, KC);
   if (smem < (size_t)EPI_BYTES) smem = EPI_BYTES;          // the idle stages double as the epilogue's transpose blocks
-  gemm_tma_kernel<BN, MODE, KC><<<grid, gemm_threads(BN, MODE), smem, st>>>(a, b, D, bias, stats, g, flags, status, bn);
-  return (int)cudaGetLastError();
+  return (int)xb_launch(gemm_tma_kernel<BN, MODE, KC>, grid, dim3(gemm_threads(BN, MODE)), smem, st, a, b, D, bias, stats, g, flags, status, bn);
 }
 template <int BN, int MODE>
 int launch(const CUtensorMap& a, const CUtensorMap& b, float* D, const float* bias, float* stats, GemmArgs g, dim3 grid, int flags, int* status,

@@ -6,6 +6,7 @@ library is a hard error: there is no PyTorch fallback for the device path.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 from . import build as _build
@@ -97,6 +98,8 @@ def load() -> C.CDLL:
     _sig(lib, "xb_sleep", I, C.c_longlong, P)
     _sig(lib, "xb_gemm_set_tn_ctas", None, I)
     _sig(lib, "xb_gemm_set_split_k", None, I)
+    _sig(lib, "xb_set_pdl", None, I)
+    _sig(lib, "xb_get_pdl", I)
     _sig(lib, "xb_conv3x3_wgrad_set_ctas", None, I)
     _sig(lib, "xb_bn_set_stream_blocks", None, I)
     _sig(lib, "xb_bn_set_reduce_blocks", None, I)
@@ -237,6 +240,8 @@ def init_device():
     lib = load()
     if not _tc_ready:
         check(lib.xb_tc_init(), "tensor-core kernel set-up")
+        if os.environ.get("XBOW_PDL", "") != "":             # programmatic dependent launch between a task's kernels: 1 on, 0 off
+            lib.xb_set_pdl(int(os.environ["XBOW_PDL"]))
         _tc_ready = True
     return lib
 

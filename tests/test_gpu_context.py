@@ -117,48 +117,53 @@ def test_auto_tuner_adds_and_removes_replicas():
 def test_auto_tuner_finds_the_knee_of_resnet32():
     """`--autotune-models true` with the default threshold (0.1) on the headline workload, starting from one replica: the
     tuner must climb while throughput rises by more than 10 % per added replica, stop for good at the first sample that
-    does not, and end where a fixed replica count would be (nearly) as fast as the best one."""
+    does not and step back by one; throughput measured at fixed replica counts in the same context must agree with what it
+    decided.  (12 tasks per clock, so that one to four replicas all divide a clock evenly.)"""
     import time
     sysc, mc = SystemConf.reset(), ModelConf.reset()
     sysc.setGPU(True).setCPU(False).setNumberOfGpuModels(1).setDisplayInterval(0)
     sysc.autotune_models, sysc.monitor_interval = True, 300
     assert sysc.autotune_threshold == 0.1 and sysc.autotune_interval == 1
     solver = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.01).setMomentum(0.9).setAlpha(0.1).setWeightDecay(1e-4)
-    mc.setBatchSize(64).setWpc(8).setUpdateModel("SMA")
-    mc.setDataset(Phase.TRAIN, SyntheticDataset([3, 32, 32], 10, 64, batches=16, seed=1))
+    mc.setBatchSize(64).setWpc(12).setUpdateModel("SMA")
+    mc.setDataset(Phase.TRAIN, SyntheticDataset([3, 32, 32], 10, 64, batches=24, seed=1))
     spec = build("resnet32", solver_conf=solver)
     ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), None], quiet=True)
     ctx.init()
     try:
         assert ctx._native is not None
-        ctx.train(64, "tasks")                                      # warm-up without a decision (shorter than one interval)
+        ctx.train(48, "tasks")                                      # warm-up without a decision (shorter than one interval)
         for _ in range(40):
             if not ctx.autotuner.active:
                 break
-            ctx.train(400, "tasks")
+            ctx.train(480, "tasks")
         trace = list(ctx.autotune_trace)
         print("auto-tuner trace (replicas after the decision, job examples/s it was based on):", [(k, round(r)) for k, r in trace])
         print("chunks while tuning (replicas, tasks, ms, settling):", [(k, n, round(dt * 1e3, 1), st) for k, n, dt, st in ctx.autotune_chunks])
         assert not ctx.autotuner.active, "the tuner never stopped"
         k_final = ctx.engine.k
         ks = [k for k, _ in trace]
-        assert k_final >= 2 and max(ks) == k_final + 1 and ks[-1] == k_final        # climbed, overshot by one, stepped back
-        # throughput at fixed replica counts, same context: k_final - 1 .. k_final + 3
+        samples = [r for _, r in trace]
+        assert k_final >= 2 and ks == list(range(2, k_final + 2)) + [k_final]       # climbed one by one, overshot by one, stepped back
+        assert all(b > 1.1 * a for a, b in zip(samples[:-2], samples[1:-1]))        # every step it kept had brought more than 10 %
+        assert samples[-1] <= 1.1 * samples[-2]                                     # the one it undid had not
+        # throughput at fixed replica counts, same context: what the samples claimed must hold there too
         rates = {}
 
         def rate():
-            ctx.train(32, "tasks")
+            ctx.train(48, "tasks")
             torch.cuda.synchronize()
             t0 = time.perf_counter()
             n = ctx.train(480, "tasks")
             return n * 64 / (time.perf_counter() - t0)
         rates[k_final] = rate()
-        for k in range(k_final + 1, k_final + 4):
+        for k in range(k_final + 1, k_final + 3):
             ctx.engine.add_learner()
             ctx._native.add_learner()
             rates[k] = rate()
         print("fixed replica counts:", {k: round(v) for k, v in rates.items()}, "tuner stopped at", k_final)
-        assert rates[k_final] >= 0.88 * max(rates.values())
+        assert rates[k_final] > 1.3 * samples[0]                                    # well above one replica
+        assert rates[k_final + 1] < 1.15 * rates[k_final]                           # and the next replica is indeed not worth 10 % (5 % slack)
         assert np.isfinite(ctx.measurements.losses()).all()
     finally:
         ctx.destroy()
