@@ -16,7 +16,7 @@ namespace {
 
 struct FakeExec {
   int learners;
-  int task_us;
+  std::atomic<int> task_us;
   std::atomic<int> fail_task{-1};        // task id whose wait returns an error
   std::atomic<int> hang_task{-1};        // task id whose wait does not return within the deadline
   std::atomic<uint64_t> syncs{0}, submits{0};
@@ -31,7 +31,7 @@ int fake_submit(void* c, int learner, const void*, const void*, uint64_t task, i
 }
 int finish(FakeExec* f, int learner, uint64_t task, float* loss, float* acc) {
   if ((int)task == f->hang_task.load()) std::this_thread::sleep_for(std::chrono::milliseconds(1500));
-  else if (f->task_us > 0) std::this_thread::sleep_for(std::chrono::microseconds(f->task_us));
+  else if (f->task_us.load() > 0) std::this_thread::sleep_for(std::chrono::microseconds(f->task_us.load()));
   if ((int)task == f->fail_task.load()) return 77;
   *loss = 1.0f / (1.0f + (float)task); *acc = (float)learner;
   return 0;
@@ -54,6 +54,7 @@ FAKE_API void rt_fake_destroy(void* f) { delete (FakeExec*)f; }
 FAKE_API void rt_fake_table(void** submit, void** wait, void** synchronise, void** wait_task) {
   *submit = (void*)fake_submit; *wait = (void*)fake_wait; *synchronise = (void*)fake_sync; *wait_task = (void*)fake_wait_task;
 }
+FAKE_API void rt_fake_set_task_us(void* f, int us) { ((FakeExec*)f)->task_us.store(us); }
 FAKE_API void rt_fake_inject(void* f, int fail_task, int hang_task) { ((FakeExec*)f)->fail_task.store(fail_task); ((FakeExec*)f)->hang_task.store(hang_task); }
 FAKE_API unsigned long long rt_fake_syncs(void* f) { return ((FakeExec*)f)->syncs.load(); }
 FAKE_API int rt_fake_last_mask(void* f, unsigned char* out, int n) {

@@ -103,6 +103,7 @@ def load_fake() -> C.CDLL:
         _sig(lib, "rt_fake_destroy", None, P)
         _sig(lib, "rt_fake_table", None, C.POINTER(P), C.POINTER(P), C.POINTER(P), C.POINTER(P))
         _sig(lib, "rt_fake_inject", None, P, I, I)
+        _sig(lib, "rt_fake_set_task_us", None, P, I)
         _sig(lib, "rt_fake_syncs", U, P)
         _sig(lib, "rt_fake_last_mask", I, P, C.c_char_p, I)
         _fake_lib = lib
@@ -208,6 +209,9 @@ class Runtime:
         self._fake_wait_task = wt.value
         self.lib.rt_set_executor(self.h, sub.value, wait.value, sync.value, 0, self._fake)
         return self._fake
+
+    def set_fake_task_us(self, task_us: int):
+        self._fake_lib.rt_fake_set_task_us(self._fake, int(task_us))
 
     def inject(self, fail_task: int = -1, hang_task: int = -1):
         self._fake_lib.rt_fake_inject(self._fake, fail_task, hang_task)

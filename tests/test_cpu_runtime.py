@@ -286,3 +286,66 @@ def test_scheduling_policy_orders_the_queued_tasks():
         rt.drain(2.0)
     assert rt.tasks_completed() == 0
     rt.close()
+
+
+def test_auto_tuner_samples_chunks_of_one_monitor_interval_across_calls():
+    """The auto-tuner's throughput samples under the native scheduler: one drained chunk per monitor interval, the chunk
+    right after a replica change is short and left out, the state survives `train()` calls that are shorter than an
+    interval, and the hill climb of the reference (ModelManager.java:257-274) ends one below the first replica count that
+    did not bring 10 %.  The fake executor's task time follows a throughput curve with its knee at three replicas."""
+    from crossbow_b200 import ModelConf, SystemConf
+    from crossbow_b200.autotune import AutoTuner
+    from crossbow_b200.context import ExecutionContext
+    from crossbow_b200.runtime import Runtime
+    from crossbow_b200.utils.measure import MeasurementQueue, PerformanceMonitor
+    from crossbow_b200.workclock import WorkClock
+
+    rate = {1: 500.0, 2: 900.0, 3: 1100.0, 4: 1150.0, 5: 1175.0}           # tasks/s of the whole "GPU" at k replicas
+    rt = Runtime(learners=1, wpc=12, result_slots=256, callback_handlers=8, task_timeout_s=30.0)    # a task "runs" in its callback handler
+    rt.attach_fake(8, task_us=int(1e6 / rate[1]))
+
+    class Engine:
+        k = 1
+        def epoch_to_native(self): pass
+        def epoch_from_native(self): pass
+        def finish(self): pass
+        def add_learner(self):
+            self.k += 1
+            rt.set_fake_task_us(int(1e6 * self.k / rate[self.k]))
+        def remove_learner(self):
+            self.k -= 1
+            rt.set_fake_task_us(int(1e6 * self.k / rate[self.k]))
+
+    ctx = ExecutionContext([None], SystemConf.reset(), ModelConf.reset(), quiet=True)
+    ctx.sys.display_interval, ctx.sys.monitor_interval = 0, 100
+    ctx.mc.setBatchSize(8)
+    ctx.engine, ctx.clock = Engine(), WorkClock(12)
+    ctx.monitor = PerformanceMonitor(8, 1024, 0.1)
+    ctx.measurements = MeasurementQueue(capacity=1 << 16)
+    ctx.autotuner = AutoTuner(0.1, 1)
+    ctx._native = rt
+    try:
+        assert ctx._train_native(12) == 12 and ctx._train_native(12) == 12      # ~25 ms each: no sample yet
+        assert ctx.autotune_trace == [] and ctx._tune["tasks"] == 24
+        for _ in range(60):
+            if not ctx.autotuner.active:
+                break
+            ctx._train_native(240)
+    finally:
+        rt.close()
+    assert not ctx.autotuner.active
+    ks = [k for k, _ in ctx.autotune_trace]
+    assert ks == [2, 3, 4, 3] and ctx.engine.k == 3, ctx.autotune_trace
+    samples = [r for _, r in ctx.autotune_trace]
+    for k, r in zip((1, 2, 3, 4), samples):                                   # examples/s = 8 x tasks/s, a little below the curve
+        assert 0.75 * 8 * rate[k] < r < 1.02 * 8 * rate[k], (k, r)
+    chunks = ctx.autotune_chunks
+    # the first chunk after every change is a short one that is marked as settling; no other chunk is
+    changes = [i for i in range(1, len(chunks)) if chunks[i][0] != chunks[i - 1][0]]
+    assert len(changes) == 3
+    for i, (k, n, dt, settling) in enumerate(chunks):
+        assert settling == (1 if i in changes else 0), (i, chunks[i])
+        if settling:
+            assert n == 48
+    # once the rate is known, a chunk is sized to one monitor interval (or to what is left of the call)
+    assert max(n for _, n, _, s in chunks if not s) >= 0.6 * 0.1 * rate[1] // 12 * 12
