@@ -94,6 +94,9 @@ def measure_ours(args, model_name, steps, warmup, k=0, batch=0, min_seconds=1.0)
     if args.gemm_smem:
         many, few = (int(v) for v in args.gemm_smem.split(","))
         L.init_device().xb_gemm_set_smem_budgets(many, few)
+    if args.gemm_max_bn:
+        nt, tn = (int(v) for v in args.gemm_max_bn.split(","))
+        L.init_device().xb_gemm_set_max_bn(nt, tn)
     if args.tma_conv_min:
         L.init_device().xb_tc_set_tma_conv_min(args.tma_conv_min)
     if args.side_low_priority:
@@ -270,6 +273,7 @@ def main():
     ap.add_argument("--side-low-priority", action="store_true", help="tuning: the weight-gradient branch of the task graph runs at the lowest stream priority")
     ap.add_argument("--fuse-bn-sums", action="store_true", help="tuning: data-gradient kernels produce the batch-norm backward sums in their epilogue")
     ap.add_argument("--gemm-smem", default="", help="tuning: shared-memory budgets of the TMA GEMM pipeline in KB, 'many,few' (default 54,100)")
+    ap.add_argument("--gemm-max-bn", default="", help="tuning: widest output tile of the TMA GEMM, 'nt,tn' (forward / data gradient, weight gradient; default 128,256)")
     ap.add_argument("--tma-conv-min", type=int, default=0, help="tuning: fewest channels for which R x S convolutions take the TMA implicit GEMM (default 32)")
     ap.add_argument("--no-library-arm", action="store_true", help="skip the library (cuDNN) arm that gives vs_baseline")
     ap.add_argument("--no-resnet50", action="store_true", help="skip the nested ResNet-50 run of the default benchmark")

@@ -98,6 +98,7 @@ def load() -> C.CDLL:
     _sig(lib, "xb_sleep", I, C.c_longlong, P)
     _sig(lib, "xb_gemm_set_tn_ctas", None, I)
     _sig(lib, "xb_gemm_set_split_k", None, I)
+    _sig(lib, "xb_gemm_set_max_bn", None, I, I)
     _sig(lib, "xb_set_pdl", None, I)
     _sig(lib, "xb_get_pdl", I)
     _sig(lib, "xb_conv3x3_wgrad_set_ctas", None, I)
