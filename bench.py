@@ -272,7 +272,7 @@ def main():
     ap.add_argument("--pdl", type=int, default=None, help="tuning: 1 / 0 = launch the kernels of a task's critical path with / without programmatic dependent launch")
     ap.add_argument("--side-low-priority", action="store_true", help="tuning: the weight-gradient branch of the task graph runs at the lowest stream priority")
     ap.add_argument("--fuse-bn-sums", action="store_true", help="tuning: data-gradient kernels produce the batch-norm backward sums in their epilogue")
-    ap.add_argument("--gemm-smem", default="", help="tuning: shared-memory budgets of the TMA GEMM pipeline in KB, 'many,few' (default 54,100)")
+    ap.add_argument("--gemm-smem", default="", help="tuning: shared-memory budgets of the TMA GEMM pipeline in KB, 'many,few' (default 72,100)")
     ap.add_argument("--gemm-max-bn", default="", help="tuning: widest output tile of the TMA GEMM, 'nt,tn' (forward / data gradient, weight gradient; default 128,256)")
     ap.add_argument("--tma-conv-min", type=int, default=0, help="tuning: fewest channels for which R x S convolutions take the TMA implicit GEMM (default 32)")
     ap.add_argument("--no-library-arm", action="store_true", help="skip the library (cuDNN) arm that gives vs_baseline")

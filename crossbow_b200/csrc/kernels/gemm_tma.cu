@@ -333,7 +333,9 @@ constexpr size_t kSmemLimit = 200 * 1024;
 // GEMM CTAs off its SM, and with four replicas per GPU the whole step paid for it: at 54 / 100 KB ResNet-32 (k = 4) went
 // from 105.8 K to 117.0 K images/s, VGG-16 (k = 4) from 84.1 K to 87.7 K, ResNet-50 (k = 2) from 5.24 K to 5.28 K, and one
 // replica alone lost nothing (47.7 K -> 47.9 K).
-static size_t g_budget_many = 54 * 1024, g_budget_few = 100 * 1024;
+// (with output tiles capped at 128 columns a third 24 KB / a second 32 KB stage pays again for the wide layers: ResNet-50
+// (k = 2) 5.41 K at 54 KB, 5.47 - 5.49 K at 72 - 80 KB, 5.29 K at 36 and at 108 KB; ResNet-32 is flat from 64 to 80 KB)
+static size_t g_budget_many = 72 * 1024, g_budget_few = 100 * 1024;
 inline size_t stage_bytes(int BN, int kc = 1) { return (size_t)kc * (A_BYTES + (size_t)BN * 128); }
 // Pipeline depth: as deep as the reduction, within a shared-memory budget that still lets two CTAs share an SM when the
 // grid has more CTAs than SMs (the second CTA's loads and MMAs then overlap the first one's epilogue).
