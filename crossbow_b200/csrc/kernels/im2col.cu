@@ -95,7 +95,6 @@ XB_API long long xb_conv_im2col_scratch(const XbConvGeom* g, int which) {
   const long long M = (long long)g->N * g->P * g->Q;
   const int Kp = padded_k(g);
   if (M * Kp >= (1ll << 31) || M >= (1ll << 31) || g->K % 4 || Kp > 1024) return 0;
-  if (which == 2 && g->K % 32 && g->K > 32) return 0;
   XbConvGeom f = as_gemm(g, Kp, M);
   if (!xb_conv1x1_tma_supported(&f, which)) return 0;
   return (long long)(align256((size_t)M * Kp * 4) + align256((size_t)g->K * Kp * 4));

@@ -168,7 +168,8 @@ def test_inner_products_at_batch_size(env, shape, accum):
 
 
 @pytest.mark.parametrize("shape", [(2, 64, 64, 3, 64, 7, 7, 2, 3), (4, 32, 32, 16, 32, 3, 3, 2, 1), (2, 12, 12, 4, 32, 5, 5, 1, 2),
-                                   (3, 28, 28, 1, 20, 5, 5, 1, 0), (8, 32, 32, 3, 64, 3, 3, 1, 1), (8, 32, 32, 3, 16, 3, 3, 1, 1)])
+                                   (3, 28, 28, 1, 20, 5, 5, 1, 0), (8, 32, 32, 3, 64, 3, 3, 1, 1), (8, 32, 32, 3, 16, 3, 3, 1, 1),
+                                   (2, 17, 17, 8, 48, 5, 5, 2, 2), (2, 9, 9, 12, 208, 3, 3, 2, 1)])
 def test_patch_matrix_gemm_path(env, shape):
     """Layers without a direct tensor-core kernel: gather to a patch matrix, then the TMA GEMM (forward, weight gradient)."""
     L, lib = env
@@ -198,15 +199,16 @@ def test_patch_matrix_gemm_path(env, shape):
     assert float((y - y_ref).abs().max()) / float(y_ref.abs().max()) < 4e-3
     m = y_ref.reshape(-1, K)
     assert torch.allclose(stats[:K], m.sum(0), rtol=4e-2, atol=4e-2 * m.shape[0] ** 0.5)
-    if K % 32 == 0 or K < 32:          # (fewer than 32 output channels: one partial plane, the loads read zeros for the rest)
-        dw = torch.zeros(K, R, S, Cc, device=dev)
-        for reuse in (0, 1):          # 1: the patch matrix written by the forward call above is still in the scratch
-            dw.zero_()
-            L.check(lib.xb_conv_wgrad_im2col(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), scratch.data_ptr(), reuse, status.data_ptr(), s), "wgrad")
-        torch.cuda.synchronize()
-        assert int(status[0]) == 0
-        dw_ref = wr.grad.permute(0, 2, 3, 1)
-        assert float((dw - dw_ref).abs().max()) / float(dw_ref.abs().max()) < 4e-3
+    # (output channel counts that are no multiples of 32: partial planes, the loads read zeros for the missing channels)
+    assert lib.xb_conv_im2col_scratch(C.byref(g), 2) > 0
+    dw = torch.zeros(K, R, S, Cc, device=dev)
+    for reuse in (0, 1):          # 1: the patch matrix written by the forward call above is still in the scratch
+        dw.zero_()
+        L.check(lib.xb_conv_wgrad_im2col(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), C.byref(g), scratch.data_ptr(), reuse, status.data_ptr(), s), "wgrad")
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    dw_ref = wr.grad.permute(0, 2, 3, 1)
+    assert float((dw - dw_ref).abs().max()) / float(dw_ref.abs().max()) < 4e-3
 
 
 @pytest.mark.parametrize("shape", [(4, 32, 32, 16, 32, 3, 3, 2, 1), (3, 16, 16, 32, 64, 3, 3, 2, 1), (2, 8, 12, 8, 24, 3, 3, 2, 1)])
