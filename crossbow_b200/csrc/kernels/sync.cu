@@ -34,6 +34,7 @@
 // bytes (the switch fetches and adds the eight copies) and stores the new central model into every GPU with one
 // multimem.st.  That moves about 4n (1 + 1/G) bytes per direction per GPU instead of the (G-1)/G * 4n of pushed partials
 // plus (G-1)/G * 4n of unicast stores of the peer-store path, and the adds happen in the switch.  These are multimem instructions on multicast ADDRESSES; no TMA is involved.
+// The variant is a kernel of its own (fused_sync_nvls_kernel) whose blocks interleave local and owner reductions.
 // The kernel also keeps a small time line per GPU (%globaltimer at entry, at the release and at the exit of its last
 // block, plus running sums), which is what the benchmarks report as synchronisation time per step.
 #include "common.cuh"
