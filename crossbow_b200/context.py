@@ -252,10 +252,15 @@ class ExecutionContext:
         def follow():
             while not stop.wait(period):
                 self._pump_results()
-        pump = threading.Thread(target=follow, name="xbow-monitor", daemon=True)
+        # (a call that will be over before the monitor's first look needs no monitor thread: starting and joining one
+        # costs more than such a call's bookkeeping; the rate of the previous call tells)
+        rate = getattr(self, "_call_rate", 0.0)
+        pump = threading.Thread(target=follow, name="xbow-monitor", daemon=True) if not (rate > 0 and ntasks / rate < 0.5 * period and ntasks <= 16384) else None   # (16384: a followed ring blocks the scheduler when nobody reads it)
         self._pump_results()
         rt.follow_history(True)                             # nothing is overwritten before this context has read it
-        pump.start()
+        t_call = time.perf_counter()
+        if pump is not None:
+            pump.start()
         try:
             while done < ntasks:
                 # a chunk ends where the host has something to do between two clocks: an auto-tuner decision, a checkpoint
@@ -302,8 +307,11 @@ class ExecutionContext:
                     self.checkpoint()
         finally:
             stop.set()
-            pump.join()
+            if pump is not None:
+                pump.join()
             rt.follow_history(False)
+        if done > 0:
+            self._call_rate = done / max(time.perf_counter() - t_call, 1e-9)
         self._pump_results()
         self.tasks_done += done
         self.clock.clock = rt.clock()
