@@ -48,6 +48,7 @@ class ExecutionContext:
         self._disp_n, self._disp_loss, self._disp_acc = 0, 0.0, 0.0
         self.monitor: Optional[PerformanceMonitor] = None
         self.autotuner: Optional[AutoTuner] = None
+        self._call_rate = 0.0                             # tasks/s of the last call of the native training loop
         self._tune = {"tasks": 0, "time": 0.0, "settle": 0, "rate": 0.0}   # since the last decision; tasks/s of the last chunk
         self.autotune_chunks = []                         # (replicas, tasks, seconds, settling) of every chunk issued while tuning
         self.autotune_trace = []                          # (replicas per GPU after the decision, job examples/s it was based on)
@@ -254,7 +255,7 @@ class ExecutionContext:
                 self._pump_results()
         # (a call that will be over before the monitor's first look needs no monitor thread: starting and joining one
         # costs more than such a call's bookkeeping; the rate of the previous call tells)
-        rate = getattr(self, "_call_rate", 0.0)
+        rate = self._call_rate
         pump = threading.Thread(target=follow, name="xbow-monitor", daemon=True) if not (rate > 0 and ntasks / rate < 0.5 * period and ntasks <= 16384) else None   # (16384: a followed ring blocks the scheduler when nobody reads it)
         self._pump_results()
         rt.follow_history(True)                             # nothing is overwritten before this context has read it

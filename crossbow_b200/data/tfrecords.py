@@ -109,6 +109,8 @@ def _fields(buf: bytes) -> Iterator[Tuple[int, int, Union[int, bytes]]]:
         if wire == 0:
             v, i = _varint(buf, i)
         elif wire == 1:
+            if i + 8 > len(buf):
+                raise ValueError("64-bit field runs past the end of its message")
             v, i = buf[i:i + 8], i + 8
         elif wire == 2:
             n, i = _varint(buf, i)
@@ -116,6 +118,8 @@ def _fields(buf: bytes) -> Iterator[Tuple[int, int, Union[int, bytes]]]:
                 raise ValueError("length-delimited field runs past the end of its message")
             v, i = buf[i:i + n], i + n
         elif wire == 5:
+            if i + 4 > len(buf):
+                raise ValueError("32-bit field runs past the end of its message")
             v, i = buf[i:i + 4], i + 4
         else:
             raise ValueError(f"unsupported wire type {wire}")

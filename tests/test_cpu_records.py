@@ -248,6 +248,9 @@ def test_tfrecord_files_become_record_files(tmp_path):
     unpacked = T._ld(1, T._ld(1, T._ld(1, b"k") + T._ld(2, T._ld(3, T._put_varint(1 << 3) + T._put_varint(-5) + T._put_varint(1 << 3) + T._put_varint(7))))
                         + T._ld(1, T._ld(1, b"f") + T._ld(2, T._ld(2, bytes([1 << 3 | 5]) + struct.pack("<f", 0.25)))))
     assert T.parse_example(unpacked) == {"k": [-5, 7], "f": [0.25]}
+    for cut in (1, 3, len(unpacked) - 2):                       # truncated messages are refused, not misread
+        with pytest.raises(ValueError):
+            T.parse_example(unpacked[:cut])
     out = T.convert_imagenet([str(tmp_path / "train-*-of-*")], str(tmp_path / "out"), "train", max_records_per_file=2, verify=True)
     assert [p.rsplit("/", 1)[1] for p in out] == ["crossbow-train.records.1", "crossbow-train.records.2", "crossbow-train.records.3"]
     ds = RecordDataset(out, batch_size=5, batches_per_half=1, image_size=32, workers=2, training=False, timeout_s=20)
