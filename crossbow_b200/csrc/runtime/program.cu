@@ -279,7 +279,10 @@ XB_API int xb_program_run_range(XbProgram* p, int first, int last, cudaStream_t 
 // chain.  (The reference has per-operator stream "branches" with event dependencies, executioncontext.c:657-671, but
 // its labelling pass is switched off and the branch factor stays 1, SubGraph.java:208-212.)  A program that is issued
 // directly, not captured, runs its operators in list order on one stream.
-constexpr int XB_OP_SIDE = 0x1000;
+// XB_OP_JOIN on an operator of the main chain: it reads what the branch has produced so far (the first data gradient
+// reads the transposed weight copy, which is written on the branch while the forward pass runs), so the main stream waits
+// for the branch in front of it.
+constexpr int XB_OP_SIDE = 0x1000, XB_OP_JOIN = 0x2000;
 static int g_side_low = 0;
 XB_API void xb_program_side_priority(int low) { g_side_low = low ? 1 : 0; }
 static inline bool joins_side(int kind) { return kind == OP_OPTIMISER || kind == OP_GRAD_SUMSQ; }
@@ -317,7 +320,7 @@ static int capture_with_branches(XbProgram* p, cudaStream_t st) {
       if (e != 0) e = (int)(1000 * (i + 1) + (e < 0 ? -e : e));
       continue;
     }
-    if (joins_side(o.kind) && (e = join()) != 0) break;
+    if ((joins_side(o.kind) || (o.flags & XB_OP_JOIN)) && (e = join()) != 0) break;
     e = run_op_traced(p, o, st);
     if (e != 0) e = (int)(1000 * (i + 1) + (e < 0 ? -e : e));
   }

@@ -737,7 +737,14 @@ class Lowering:
             blocks += L.load().xb_transpose_blocks(K, RS, Cc)
         raw = torch.frombuffer(bytearray(bytes(descs)), dtype=torch.uint8).to(self.device)
         self.keep.append(raw)
-        self.ops[slot] = _op(L.OP_TRANSPOSE_W, ia=[len(self.transposes), blocks], p=[self.weights, self.replica.wt, raw])
+        # The transposed copy is only read by the data gradients: it is written on the task graph's parallel branch, under
+        # the forward pass, and the first data gradient joins that branch.
+        self.ops[slot] = _op(L.OP_TRANSPOSE_W, self.side, ia=[len(self.transposes), blocks], p=[self.weights, self.replica.wt, raw])
+        if self.side:
+            for o in self.ops[slot + 1:]:
+                if o.kind == L.OP_CONV_DGRAD:
+                    o.flags |= L.F_JOIN
+                    break
 
     def _optimiser(self):
         rep, sh = self.replica, self.shared

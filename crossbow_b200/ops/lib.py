@@ -65,6 +65,7 @@ class XbSolverState(C.Structure):
 
 F_RELU, F_ACCUM, F_STATS, F_TC = 1, 2, 4, 0x100
 F_SIDE = 0x1000          # operator runs on a parallel branch of the captured task graph (csrc/runtime/program.cu)
+F_JOIN = 0x2000          # operator of the main chain that reads what the branch has produced so far: the branch is joined in front of it
 
 _lib: Optional[C.CDLL] = None
 
