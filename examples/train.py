@@ -12,7 +12,8 @@ Data: ``--metadata <file>`` of a binary data set written by ``DatasetWriter``, o
 --data-directory <dir>`` holding ``<alias>-train.metadata`` / ``<alias>-test.metadata`` (ImageNet: ``crossbow-train.records.*``
 record files of JPEGs are used when the directory has them); without either a synthetic data set of the model's input shape
 is generated.  ``--model resnet --layers 50`` picks the depth; ``--time-limit true --D 30 --duration-unit minutes`` trains
-for a duration instead of ``--N`` units; ``--unit`` is an alias of ``--training-unit``.
+for a duration instead of ``--N`` units; ``--unit`` is an alias of ``--training-unit``; ``--weight-initialiser constant|gaussian`` overrides the initialisers of the
+convolution and inner-product layers.
 """
 import os
 import sys
@@ -34,7 +35,7 @@ def main(argv=None):
     # the flags of the reference's applications
     opts.add(Option("--layers", int, 0)).add(Option("--dataset-name", str, None)).add(Option("--data-directory", str, None))
     opts.add(Option("--time-limit", str, "false")).add(Option("--D", float, 1.0)).add(Option("--duration-unit", str, "minutes"))
-    opts.add(Option("--unit", str, None))
+    opts.add(Option("--unit", str, None)).add(Option("--weight-initialiser", str, None))
     CommandLine(opts).parse(argv)
     sysc, mc = SystemConf.getInstance(), ModelConf.getInstance()
     name, layers, dataset = opts.get("--model").get(), opts.get("--layers").get(), opts.get("--dataset-name").get()
@@ -44,6 +45,21 @@ def main(argv=None):
             raise SystemExit(f"error: invalid number of layers for {dataset or 'cifar-10'} dataset")
         name = f"resnet{layers}"
     spec = build(name, solver_conf=mc.getSolverConf())
+    wi = opts.get("--weight-initialiser").get()
+    if wi:                                            # LeNetBatchNorm.java:118-139, ConvNet.java: constant (0, bias 1) or gaussian (std 0.1, bias 0)
+        from crossbow_b200 import InitialiserConf, InitialiserType
+        kind = InitialiserType.from_string(wi)
+        if kind not in (InitialiserType.CONSTANT, InitialiserType.GAUSSIAN):
+            raise SystemExit("error: weight initialiser must be either constant or gaussian")
+        for g in (spec.train, spec.test):
+            for node in (g.nodes() if g is not None else []):
+                k = node.op.kernel
+                if getattr(k, "kind", "") in ("conv", "innerproduct") and not k.is_gradient:
+                    if kind == InitialiserType.CONSTANT:
+                        k.conf.setWeightInitialiser(InitialiserConf().setType(kind).setValue(0)).setBiasInitialiser(InitialiserConf().setType(kind).setValue(1))
+                    else:
+                        k.conf.setWeightInitialiser(InitialiserConf().setType(kind).setStd(0.1))
+                        k.conf.setBiasInitialiser(InitialiserConf().setType(InitialiserType.CONSTANT).setValue(0))
     if int(os.environ.get("WORLD_SIZE", 1)) > 1:      # one process per GPU (nccl) or per CPU device group (gloo)
         from crossbow_b200.parallel.peer import init_process_group
         init_process_group()
