@@ -17,7 +17,14 @@ REGISTRY = {
 }
 
 
+REGISTRY["baby-resnet"] = REGISTRY["resnet8"]          # the reference's BabyResNet.java: one basic block per stage
+
+
 def build(name: str, **kw) -> ModelSpec:
+    import re
+    m = re.fullmatch(r"resnet(\d+)", name)
+    if name not in REGISTRY and m and (int(m.group(1)) - 2) % 6 == 0 and int(m.group(1)) >= 8:
+        return resnet_cifar(int(m.group(1)), **kw)        # any CIFAR depth 6n + 2 (ResNetv1ForCifar.java:952-960)
     if name not in REGISTRY:
         raise ValueError(f"error: unknown model {name}; choose from {sorted(REGISTRY)}")
     return REGISTRY[name](**kw)

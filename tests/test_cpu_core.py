@@ -318,6 +318,11 @@ def test_all_models_build_and_infer_shapes():
         assert spec.test is None or spec.test.getAccuracyNode() is not None      # (matrix factorisation has no test graph)
     spec, m, _ = build_model("resnet32", 2)
     assert 460000 < m.elements < 470000
+    # any CIFAR depth 6n + 2 builds (ResNetv1ForCifar.java:952-960), anything else is refused
+    from crossbow_b200.models import build as build_spec
+    assert build_spec("resnet14").name == "resnet-14" and build_spec("baby-resnet").name == "resnet-8"
+    with pytest.raises(ValueError):
+        build_spec("resnet15")
     spec, m, _ = build_model("resnet50", 2, size=224)
     assert 25.5e6 < m.elements < 25.7e6
 
