@@ -1,6 +1,6 @@
 """Converters from the public data-set files to the binary partition format (``DatasetWriter``): what the reference's
 pre-processing encoders do (src/test/java/.../preprocess/{mnist/MNISTEncoder.java, cifar/CifarEncoder.java,
-ratings/RatingsEncoder.java, random/RandomEncoder.java}).
+ratings/RatingsEncoder.java, yahoomusic/YahooMusicEncoder.java, random/RandomEncoder.java}).
 
     python -m crossbow_b200.data.convert mnist   --images train-images-idx3-ubyte --labels train-labels-idx1-ubyte -o out --name mnist-train -b 128
     python -m crossbow_b200.data.convert cifar10 --input data_batch_1.bin data_batch_2.bin ... -o out --name cifar-train -b 64
@@ -102,7 +102,7 @@ def convert_random(shape: Sequence[int], classes: int, count: int, directory: st
 
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(description="convert public data-set files to binary partitions")
-    ap.add_argument("kind", choices=["mnist", "cifar10", "cifar100", "ratings", "random", "imagenet"])
+    ap.add_argument("kind", choices=["mnist", "cifar10", "cifar100", "ratings", "yahoomusic", "random", "imagenet"])
     ap.add_argument("--images"), ap.add_argument("--labels")
     ap.add_argument("--input", nargs="*", default=[])
     ap.add_argument("-o", "--output", required=True)
@@ -128,7 +128,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         meta = convert_cifar10(a.input, a.output, a.name, a.batch)
     elif a.kind == "cifar100":
         meta = convert_cifar100(a.input, a.output, a.name, a.batch, a.coarse)
-    elif a.kind == "ratings":
+    elif a.kind in ("ratings", "yahoomusic"):           # the same "row column rating" lines (yahoomusic/YahooMusicEncoder.java:47-56)
         meta = convert_ratings(a.input[0], a.output, a.name, a.batch)
     else:
         meta = convert_random([int(v) for v in a.shape.split(",")], a.classes, a.count, a.output, a.name, a.batch, a.seed)
