@@ -607,7 +607,7 @@ class SystemConf(_OptionHolder):
                   random_seed=123456789, reuse_memory=False, mapped_partitions_window=4, monitor_interval=1000,
                   tee_measurements=True, autotune_models=False, autotune_threshold=0.1, autotune_interval=1,
                   direct_scheduling=False, core_mapper_offset=1, use_cuda_graphs=True, use_tensor_cores=True,
-                  fused_sync=True, overlap_sync=True, operator_branches=True, nvls_sync=False, sync_timeout=5.0, native_scheduler=True, task_timeout=60.0, gradient_buckets=0, run_ahead=2, trace_level=0, debug_canaries=False)
+                  fused_sync=True, overlap_sync=True, operator_branches=True, nvls_sync=False, sync_timeout=5.0, native_scheduler=True, task_timeout=60.0, gradient_buckets=0, run_ahead=2, trace_level=0, debug_canaries=False, debug_checksums=False)
     ALIASES = {"gpu_models": "number_of_gpu_models", "gpu_streams": "number_of_gpu_streams"}
 
     OPTIONS = {
@@ -640,7 +640,7 @@ class SystemConf(_OptionHolder):
         "--use-cuda-graphs": ("use_cuda_graphs", _parse_bool),
         "--use-tensor-cores": ("use_tensor_cores", _parse_bool), "--fused-sync": ("fused_sync", _parse_bool), "--overlap-sync": ("overlap_sync", _parse_bool), "--operator-branches": ("operator_branches", _parse_bool), "--nvls-sync": ("nvls_sync", _parse_bool),
         "--sync-timeout": ("sync_timeout", float), "--native-scheduler": ("native_scheduler", _parse_bool),
-        "--task-timeout": ("task_timeout", float), "--gradient-buckets": ("gradient_buckets", int), "--run-ahead": ("run_ahead", int), "--trace-level": ("trace_level", int), "--debug-canaries": ("debug_canaries", _parse_bool),
+        "--task-timeout": ("task_timeout", float), "--gradient-buckets": ("gradient_buckets", int), "--run-ahead": ("run_ahead", int), "--trace-level": ("trace_level", int), "--debug-canaries": ("debug_canaries", _parse_bool), "--debug-checksums": ("debug_checksums", _parse_bool),
     }
 
     _instance: Optional["SystemConf"] = None

@@ -112,11 +112,17 @@ class ExecutionContext:
                                     sync_timeout_s=sys.sync_timeout, splits=mc.splits, reuse_memory=sys.reuse_memory,
                                     gradient_buckets=sys.gradient_buckets, debug_canaries=sys.debug_canaries,
                                     overlap_sync=sys.overlap_sync, operator_branches=sys.operator_branches, nvls_sync=sys.nvls_sync)
+            if sys.debug_checksums and not self.quiet:
+                print("warning: --debug-checksums prints the CPU engine's operator outputs; the device program fuses operators "
+                      "(compare device and CPU group by group with tests/test_gpu_groups.py)", flush=True)
         else:
             from .engine import CpuEngine
             self.engine = CpuEngine(tg, sg, self.model, init, batch, self.input_shape, solver, mc.update_model,
                                     replicas=sys.number_of_cpu_models, wpc=wpc, devices=1, seed=sys.random_seed,
                                     splits=mc.splits, rank=self.rank, world=self.world)
+            if sys.debug_checksums:                       # (Operator.java:232-259: one line per operator and task)
+                from .oracle import OracleExecutor
+                OracleExecutor.checksum_sink = lambda line: self.emit(line)
         self.clock = WorkClock(wpc)
         self.monitor = PerformanceMonitor(batch, ds.batch_bytes() if ds is not None else 0, sys.monitor_interval / 1000.0,
                                           sink=None if self.quiet else (lambda line: self.emit(line)))
@@ -504,6 +510,9 @@ class ExecutionContext:
         return save_checkpoint(self, directory or self.sys.checkpoint_directory)
 
     def destroy(self):
+        if getattr(self.sys, "debug_checksums", False):
+            from .oracle import OracleExecutor
+            OracleExecutor.checksum_sink = None
         for rt in (getattr(self, "_native", None), getattr(self, "_native_test", None)):
             if rt is not None:
                 rt.close()

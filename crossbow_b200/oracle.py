@@ -68,10 +68,26 @@ class DeviceState:
 # --------------------------------------------------------------------------------------------
 
 class OracleExecutor:
+    # Debug cross-check of the reference (Operator.java:232-259, SubGraph.java:261-262: under debug logging every operator
+    # prints the checksum of its output): when `checksum_sink` is set, it is called with one line per operator and task,
+    # "Kernel's <name> output checksum is <sum, 5 decimals>" (gradient operators: one sum per input gradient).
+    checksum_sink = None
+
     def __init__(self, graph: SubGraph, model: Model, seed: int = 0):
         self.graph = graph
         self.model = model
         self.seed = seed
+
+    def _checksum(self, op, value):
+        sink = OracleExecutor.checksum_sink
+        if sink is None:
+            return
+        vals = [v for v in (value if isinstance(value, list) else [value]) if v is not None]
+        if not vals:
+            sink(f"Kernel's {op.name} output list is empty")
+            return
+        sums = ", ".join(f"{float(v.double().sum()):.5f}" for v in vals)
+        sink(f"Kernel's {op.name} output checksum{'s are' if len(vals) > 1 else ' is'} {sums}")
 
     def _params(self, kernel, w: torch.Tensor, requires_grad: bool):
         out = []
@@ -108,6 +124,7 @@ class OracleExecutor:
                     y = k.forward(xin, params, env)
                 saved[op.uid] = (xin, params, y)
                 outs[id(node)] = y.detach()
+                self._checksum(op, outs[id(node)])
                 if k.is_loss:
                     result["loss"] = float(y.detach().reshape(-1)[0])
                 elif k.kind == "accuracy":
@@ -129,6 +146,7 @@ class OracleExecutor:
                 g = g * valid.unsqueeze(1)
                 denom = p.shape[0] if pk.conf.mode != NormalisationMode.VALID else max(1, int(valid.sum()))
                 outs[id(node)] = [g / denom]
+                self._checksum(op, outs[id(node)])
                 continue
             ups = [self._pick(outs[id(p)], p, node) for p in node.prev]
             if pk.is_loss:
@@ -151,6 +169,7 @@ class OracleExecutor:
                 if gp is not None:
                     grad_out[v.offset:v.offset + v.elements()] += gp.reshape(-1)
             outs[id(node)] = gin
+            self._checksum(op, gin)
         if keep_outputs:
             result["outputs"] = {n.op.uid: (o if not isinstance(o, list) else o) for n in self.graph.order
                                  for o in [outs.get(id(n))] if o is not None}

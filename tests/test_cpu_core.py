@@ -526,3 +526,33 @@ def test_chained_subgraphs_run_as_one_program():
         ctx.destroy()
     assert len(losses[0]) == 8 and losses[0] == losses[1]
     assert losses[0][-1] < losses[0][0]
+
+
+def test_debug_checksums_print_one_line_per_operator(tmp_path):
+    """`--debug-checksums true`: the CPU engine prints the checksum of every operator's output, as the reference does under
+    debug logging (Operator.java:232-259, SubGraph.java:261-262)."""
+    from crossbow_b200.context import ExecutionContext
+    from crossbow_b200.data import SyntheticDataset
+    from crossbow_b200.models import build
+    from crossbow_b200.oracle import OracleExecutor
+    sysc, mc = SystemConf.reset(), ModelConf.reset()
+    sysc.setCPU(True).setGPU(False).setNumberOfCPUModels(1).setDisplayInterval(0)
+    sysc.debug_checksums = True
+    sc = mc.getSolverConf().setLearningRateDecayPolicy("FIXED").setBaseLearningRate(0.01)
+    mc.setBatchSize(4).setWpc(1).setUpdateModel("DEFAULT")
+    mc.setDataset(Phase.TRAIN, SyntheticDataset([1, 28, 28], 10, 4, batches=2, seed=1))
+    spec = build("lenet-caffe", solver_conf=sc)
+    ctx = ExecutionContext([Dataflow(spec.train).setPhase(Phase.TRAIN), None], quiet=True)
+    lines = []
+    ctx.emit = lines.append
+    ctx.init()
+    try:
+        ctx.train(1, "tasks")
+    finally:
+        ctx.destroy()
+    assert OracleExecutor.checksum_sink is None                      # switched off again with the context
+    sums = [l for l in lines if l.startswith("Kernel's ")]
+    names = [l.split("'s ")[1].split(" output")[0] for l in sums]
+    assert names[:3] == ["Conv", "Pool", "Conv"] and "SoftMaxLossGradient" in names and names[-1] == "ConvGradient"
+    soft = next(l for l in sums if "SoftMax output" in l)
+    assert soft.endswith("is 4.00000")                               # four rows of probabilities
