@@ -556,3 +556,28 @@ def test_debug_checksums_print_one_line_per_operator(tmp_path):
     assert names[:3] == ["Conv", "Pool", "Conv"] and "SoftMaxLossGradient" in names and names[-1] == "ConvGradient"
     soft = next(l for l in sums if "SoftMax output" in l)
     assert soft.endswith("is 4.00000")                               # four rows of probabilities
+
+
+def test_measurement_log_parser_matches_the_reference_tool(tmp_path):
+    """tools/measurements/parse-measurements.py: percentiles of GPU and memory utilisation per device from an nvidia-smi
+    CSV log, optionally between two moments; idle devices stay out of the aggregate."""
+    from datetime import datetime
+    from crossbow_b200.utils import gpumon
+    assert gpumon.sampler_command(200)[:2] == ["nvidia-smi", "--query-gpu=timestamp,gpu_serial,temperature.gpu,utilization.gpu,utilization.memory,memory.used,memory.free"]
+    p = tmp_path / "measurements.csv"
+    rows = ["# Thu Jan  1 00:00:00 UTC 2026", "timestamp, gpu_serial, temperature.gpu, utilization.gpu, utilization.memory, memory.used, memory.free"]
+    for i in range(100):
+        ts = f"2026/01/01 00:00:{i // 5:02d}.{(i % 5) * 200:03d}"
+        rows.append(f"{ts}, A1, 50, {i}, {i / 2}, 1000, 179000")
+        rows.append(f"{ts}, B2, 40, 0, 0, 10, 180000")                  # an idle device
+    p.write_text("\n".join(rows) + "\n")
+    st = gpumon.parse_measurements(str(p))
+    assert st["A1"]["samples"] == 100 and st["B2"]["samples"] == 100
+    g = st["A1"]["gpu_util"]
+    assert g["min"] == 0 and g["max"] == 99 and abs(g["mean"] - 49.5) < 1e-9 and abs(g["p50"] - 49.5) < 1e-9 and abs(g["p99"] - 98.01) < 1e-6
+    assert abs(st["A1"]["mem_util"]["p25"] - 12.375) < 1e-9
+    assert st["all"]["samples"] == 100                                   # the idle device is left out of the aggregate
+    t0 = int(datetime.strptime("2026/01/01 00:00:10.000", "%Y/%m/%d %H:%M:%S.%f").timestamp() * 1000)
+    half = gpumon.parse_measurements(str(p), start_ms=t0)
+    assert half["A1"]["samples"] == 50 and half["A1"]["gpu_util"]["min"] == 50
+    assert gpumon.main(["parse", str(p)]) == 0
