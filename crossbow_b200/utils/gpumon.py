@@ -160,7 +160,6 @@ def main(argv=None):
     """python -m crossbow_b200.utils.gpumon sample [file]  |  python -m crossbow_b200.utils.gpumon parse <file> [--start ms] [--end ms]"""
     import argparse
     import json
-    import subprocess
     ap = argparse.ArgumentParser(description=main.__doc__)
     ap.add_argument("what", choices=["sample", "parse"])
     ap.add_argument("file", nargs="?", default="measurements.csv")
@@ -181,7 +180,11 @@ def main(argv=None):
     with open(a.file, "w") as f:
         f.write(f"# {time.ctime()}\n")
         f.flush()
-        return subprocess.call(sampler_command(a.period_ms), stdout=f, stderr=subprocess.STDOUT)     # until interrupted; reads only
+        # this process BECOMES the sampler (so that stopping it stops nvidia-smi): it runs until interrupted and only reads
+        os.dup2(f.fileno(), 1)
+        os.dup2(f.fileno(), 2)
+        cmd = sampler_command(a.period_ms)
+        os.execvp(cmd[0], cmd)
 
 
 if __name__ == "__main__":
