@@ -175,8 +175,11 @@ def main(argv=None):
         print(json.dumps({k: d["samples"] for k, d in stats.items()}))
         return 0
     import os
+    import shutil
     if os.path.exists(a.file):
         raise SystemExit(f"error: {a.file} already exists")
+    if shutil.which("nvidia-smi") is None:
+        raise SystemExit("error: nvidia-smi is not on this machine's PATH")
     with open(a.file, "w") as f:
         f.write(f"# {time.ctime()}\n")
         f.flush()
