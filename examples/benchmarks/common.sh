@@ -28,7 +28,7 @@ run_train () {
   fi
   if [ -n "$sampler" ]; then
     kill "$sampler" 2>/dev/null; wait "$sampler" 2>/dev/null
-    PYTHONPATH="$ROOT" python -m crossbow_b200.utils.gpumon parse "$log"
+    [ -s "$log" ] && PYTHONPATH="$ROOT" python -m crossbow_b200.utils.gpumon parse "$log"
   fi
   return $rc
 }
